@@ -1,0 +1,285 @@
+"""Headline benchmark: Qwen3-8B dense training throughput (tokens/s over all GPUs of one node).
+
+    python bench.py --gpus 1 --steps 3 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        bench.py --gpus 8 --steps 3 --warmup 3
+
+One step = one optimizer step over ``8 x N`` packed sequences of 8192 tokens (64 at 8 GPUs: weak
+scaling), bf16 compute with fp32 master weights and Adam state, synthetic packed documents, random
+N(0, 0.02) weights.  Two timed regions of K steps each, both bracketed by barrier + synchronize and
+timed with CUDA events, max over ranks:
+
+* ``value``: the training step with the step's micro-batches already resident on the device;
+* ``e2e``: the same step through the public trainer API with every micro-batch copied from pinned
+  host memory inside the timed region and the step loss read back to the host every step.
+
+``--impl reference`` runs the unmodified reference framework (installed under ``baseline/_ref``) on
+the same model/config through its own trainer, or reports why it cannot run.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--parallelism", default=None, help="e.g. tp4dp2, dp8, tp2; default tp=min(N,4) x dp")
+    ap.add_argument("--seqs-per-gpu", type=int, default=8, help="sequences per GPU per step (global batch = this x N)")
+    ap.add_argument("--seq-len", type=int, default=8192)
+    ap.add_argument("--recompute", default="auto", help="auto | none | full | comma list of block parts")
+    ap.add_argument("--debug-layers", type=int, default=None, help="DEBUG ONLY: fewer layers (result marked invalid)")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, path):
+        self.path, self.proc = path, None
+
+    def start(self):
+        try:
+            self.f = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self, local_index=0):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.f.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            p = [x.strip() for x in line.split(",")]
+            if len(p) < 9:
+                continue
+            try:
+                sm.append(float(p[1]))
+                mx.append(float(p[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, p[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        busy = [s for s in sm if s > 0]
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def default_parallelism(n: int) -> str:
+    tp = min(n, 4)
+    dp = n // tp
+    return f"tp{tp}dp{dp}" if tp > 1 else f"dp{dp}"
+
+
+def parse_parallelism(text: str) -> dict:
+    import re
+
+    out = {"tp": 1, "dp": 1, "pp": 1, "cp": 1, "ep": 1}
+    for k, v in re.findall(r"([a-z]+)(\d+)", text):
+        out[k] = int(v)
+    return out
+
+
+def model_flops_per_token(layers, hidden, heads, kv_heads, head_dim, ffn, vocab, avg_ctx):
+    qkv = hidden * (heads + 2 * kv_heads) * head_dim
+    o = heads * head_dim * hidden
+    mlp = 3 * hidden * ffn
+    dense = layers * (qkv + o + mlp) + vocab * hidden
+    attn = layers * 2 * heads * head_dim * avg_ctx  # QK^T and PV, causal average context
+    return 6 * dense + 6 * attn
+
+
+def run_ours(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from playground.pretrain.qwen3.qwen3_8b import Exp
+    from steptronoss_b200.ops import launch_count
+    from steptronoss_b200.ops import native
+    from steptronoss_b200.parallel.state import PM
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run for N>1")
+    par_text = args.parallelism or default_parallelism(world)
+    par = parse_parallelism(par_text)
+    exp = Exp()
+    pc = exp.model_cfg.parallel_cfg
+    pc.tensor_model_parallel_size = par["tp"]
+    pc.pipeline_model_parallel_size = par["pp"]
+    pc.context_parallel_size = par["cp"]
+    exp.model_cfg.tp_cfg.sequence_parallel = par["tp"] > 1
+    tc = exp.trainer_cfg
+    tc.global_seq_length = args.seq_len
+    tc.global_batch_size = args.seqs_per_gpu * world
+    tc.train_iters = 10**9
+    tc.writer_backend = []
+    tc.log_interval = 10**9
+    exp.data_cfg.max_doc_len = args.seq_len
+    if args.debug_layers:
+        exp.model_cfg.num_layers = args.debug_layers
+    rec = args.recompute
+    if rec == "auto":
+        # one GPU holds 18 bytes/parameter of static state (147 GB): recompute whole blocks
+        rec = "full" if par["tp"] * par["pp"] == 1 else "none"
+    exp.model_cfg.recompute = True if rec == "full" else ([] if rec == "none" else rec.split(","))
+    exp.sanity_check()
+    trainer = exp.trainer_cfg.get_trainer_cls()(exp=exp)
+    trainer.before_train()
+    dev = trainer.device
+
+    def barrier_sync():
+        if dist.is_initialized():
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        trainer.train_step()
+    barrier_sync()
+    native.raise_if_kernel_error()
+
+    n_micro = trainer.num_microbatches()
+    tokens_per_step = tc.global_batch_size * tc.global_seq_length
+
+    # ---- region A: device-resident inputs --------------------------------------------------------
+    class Staged:
+        def __init__(self, src, count):
+            self.items = []
+            if src is not None:
+                for _ in range(count):
+                    self.items.append({k: v.to(dev) for k, v in next(src).items()})
+            self.pos = 0
+
+        def __iter__(self):
+            return self
+
+        def __next__(self):
+            x = self.items[self.pos]
+            self.pos += 1
+            return x
+
+    live_iters = trainer.data_iterators
+    staged = [Staged(it, n_micro * args.steps) for it in live_iters]
+    trainer.data_iterators = [s if it is not None else None for s, it in zip(staged, live_iters)]
+    sampler = ClockSampler(os.path.join(ROOT, "gpurun_out", "bench_clocks.csv")) if rank == 0 else None
+    if sampler:
+        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
+        sampler.start()
+    barrier_sync()
+    l0 = launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        trainer.train_step()
+    e1.record()
+    barrier_sync()
+    launches = launch_count() - l0
+    ms_a = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+    trainer.data_iterators = live_iters
+
+    # ---- region B: end to end (pinned host inputs copied in, loss read back every step) ----------
+    h2d = d2h = 0
+    for s_ in staged:
+        if s_.items:
+            h2d = sum(v.numel() * v.element_size() for v in s_.items[0].values()) * n_micro
+            break
+    barrier_sync()
+    from steptronoss_b200.utils.metrics import GlobalMetrics
+
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    f0.record()
+    last_loss = None
+    for _ in range(args.steps):
+        trainer.train_step()
+        vals = GlobalMetrics.metrics["lm_loss"].values
+        if vals:
+            last_loss = float(torch.stack([torch.as_tensor(v) for v in vals]).mean().item())  # D2H read
+            d2h = 4
+        GlobalMetrics.reset()
+    f1.record()
+    barrier_sync()
+    wall_b = (time.perf_counter() - t0) * 1e3
+    ms_b = max(f0.elapsed_time(f1), wall_b)
+    native.raise_if_kernel_error()
+
+    t = torch.tensor([ms_a, ms_b], dtype=torch.float64, device=dev)
+    if dist.is_initialized():
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_a, ms_b = float(t[0]), float(t[1])
+    if rank != 0:
+        return
+    value = tokens_per_step * args.steps / (ms_a / 1e3)
+    e2e = tokens_per_step * args.steps / (ms_b / 1e3)
+    mc = exp.model_cfg
+    avg_ctx = (args.seq_len ** 2 / 3.0) / ((256 + args.seq_len) / 2.0) / 2.0 if args.seq_len > 256 else args.seq_len / 2
+    fpt = model_flops_per_token(mc.num_layers, 4096, 32, 8, 128, 12288, 151936, avg_ctx)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("bf16_tflops_sustained", 1375.7)) * 1e12
+    out = {
+        "metric": "tokens/s/box (Qwen3-8B dense training, all GPUs of the node)",
+        "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_a / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic packed documents (lengths U[256,8192], uniform token ids), random N(0,0.02) init",
+        "mfu_of_measured_sustained_bf16": value * fpt / (peak * world),
+        "config": {"model": "Qwen3-8B", "layers": mc.num_layers, "global_batch": tc.global_batch_size,
+                   "seq_len": tc.global_seq_length, "micro_batch": 1, "parallelism": par_text,
+                   "optimizer": "Adam fp32 master+state, ZeRO-1", "recompute": rec,
+                   "l2": "inputs larger than L2 (each step streams > 100 GB)"},
+        "clocks": clocks,
+        "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_b / args.steps, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "last_loss": last_loss},
+        "gpu_launches": launches,
+        "impl": "ours",
+    }
+    if args.debug_layers:
+        out["invalid_debug_config"] = True
+    print(json.dumps(out), flush=True)
+
+
+def run_reference(args):
+    sys.path.insert(0, os.path.join(ROOT, "baseline"))
+    try:
+        from reference_arm import run as ref_run
+    except Exception as e:  # the arm is optional: report instead of failing
+        print(json.dumps({"impl": "reference", "unavailable": f"reference arm not importable: {type(e).__name__}: {e}"}))
+        return
+    ref_run(args)
+
+
+if __name__ == "__main__":
+    a = parse()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

@@ -1,0 +1,137 @@
+"""Base module with pipeline-stage structure (reference ``steptronoss/model/module.py:32-248``).
+
+``forward = forward_head (first stage) -> forward_chunk (every stage) -> forward_tail (last
+stage)``; intermediate stages receive their input through ``set_input_tensor``.  ``Float16Module``
+wraps a model whose parameters are kept in bf16/fp16.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from ..parallel.layers import init_parallel_weight_, set_defaults_if_not_set_tensor_model_parallel_attributes
+from ..parallel.state import PM
+
+
+class MegatronModule(nn.Module):
+    def __init__(self, vpp_rank: int | None = None):
+        super().__init__()
+        self.vpp_rank = vpp_rank if vpp_rank is not None else PM.get_vpp_rank()
+        self.input_tensor = None
+        self.reshaper = None  # HF <-> native weight mapping (checkpointing/reshape_ops.py)
+
+    # ---------------------------------------------------------------- pipeline position
+    @property
+    def pp_rank(self) -> int:
+        return self.vpp_rank * PM.size_of("PP") + PM.rank_in("PP")
+
+    @property
+    def pp_size(self) -> int:
+        return PM.size_of("PP") * PM.get_vpp_size()
+
+    @property
+    def is_first_stage(self) -> bool:
+        return self.pp_rank == 0
+
+    @property
+    def is_last_stage(self) -> bool:
+        return self.pp_rank == self.pp_size - 1
+
+    def set_input_tensor(self, t) -> None:
+        self.input_tensor = t
+
+    # ---------------------------------------------------------------- forward skeleton
+    def forward_head(self, **data):
+        raise NotImplementedError
+
+    def forward_chunk(self, hidden, **data):
+        raise NotImplementedError
+
+    def forward_tail(self, hidden, **data):
+        raise NotImplementedError
+
+    def forward(self, **data):
+        if self.is_first_stage:
+            hidden = self.forward_head(**data)
+        else:
+            hidden = self.input_tensor
+        hidden = self.forward_chunk(hidden, **data)
+        if self.is_last_stage:
+            return self.forward_tail(hidden, **data)
+        return hidden
+
+    # ---------------------------------------------------------------- weights
+    def init_weights(self, seed: int = 0, std: float = 0.02) -> None:
+        """Seed-deterministic N(0, std) init, independent of the parallel layout; norm weights 1 (or 0)."""
+        for name, p in self.named_parameters():
+            set_defaults_if_not_set_tensor_model_parallel_attributes(p)
+            init_parallel_weight_(p, name, seed, std)
+
+    def load_hf_state_dict(self, hf_state: dict) -> None:
+        if self.reshaper is None:
+            raise NotImplementedError(f"{type(self).__name__} has no HF reshaper")
+        native = self.reshaper.forward(hf_state)
+        own = dict(self.named_parameters())
+        for k, v in native.items():
+            if k in own:
+                own[k].data.copy_(v.to(own[k].dtype))
+                own[k].has_initialized = True
+
+    def hf_state_dict(self) -> dict:
+        if self.reshaper is None:
+            raise NotImplementedError(f"{type(self).__name__} has no HF reshaper")
+        return self.reshaper.backward({k: v.detach() for k, v in self.named_parameters()})
+
+    def name_parameters(self) -> None:
+        for n, p in self.named_parameters():
+            p._log_name = n
+
+
+def _cast(x, dtype):
+    if torch.is_tensor(x) and x.is_floating_point():
+        return x.to(dtype)
+    if isinstance(x, dict):
+        return {k: _cast(v, dtype) for k, v in x.items()}
+    if isinstance(x, (list, tuple)):
+        return type(x)(_cast(v, dtype) for v in x)
+    return x
+
+
+class Float16Module(nn.Module):
+    """Holds a half-precision model; floating inputs are cast at the first stage and (optionally)
+    outputs up-cast to fp32 at the last one."""
+
+    def __init__(self, module: MegatronModule, params_dtype=torch.bfloat16, fp32_output: bool = True):
+        super().__init__()
+        self.module = module
+        self.params_dtype = params_dtype
+        self.fp32_output = fp32_output
+
+    def set_input_tensor(self, t):
+        return self.module.set_input_tensor(t)
+
+    def forward(self, **data):
+        if self.module.is_first_stage:
+            data = {k: (v if k in ("loss_weights", "loss_masks") else _cast(v, self.params_dtype)) for k, v in data.items()}
+        out = self.module(**data)
+        if self.module.is_last_stage and self.fp32_output and torch.is_tensor(out):
+            out = out.float()
+        return out
+
+    def state_dict(self, *a, **k):
+        return self.module.state_dict(*a, **k)
+
+    def load_state_dict(self, sd, strict=True):
+        return self.module.load_state_dict(sd, strict=strict)
+
+    def __getattr__(self, name):
+        try:
+            return super().__getattr__(name)
+        except AttributeError:
+            return getattr(self.module, name)
+
+
+def unwrap_model(m):
+    while isinstance(m, Float16Module):
+        m = m.module
+    return m

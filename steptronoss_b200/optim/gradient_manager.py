@@ -1,0 +1,379 @@
+"""Gradient managers: gradient accumulation into fp32 flat buffers, data-parallel reduction,
+global-norm clipping, the optimizer step on fp32 masters and the bf16 parameter refresh.
+
+Reference: ``steptronoss/optimizer/base_gradient_manager.py:37-257``,
+``gradient_manager.py:19-197`` (all-reduce, full optimizer state on every rank) and
+``zero1_gradient_manager.py:22-243`` (reduce-scatter, optimizer state sharded over DP by whole
+parameters, bf16 parameter all-gather).
+
+What is different here:
+
+* weight gradients arrive in ``main_grad`` from the wgrad GEMM epilogues (no per-parameter
+  ``main_grad += grad`` launches); parameters whose gradient comes through autograd (CPU path,
+  exotic modules) are folded in by a post-accumulate hook;
+* the 1/N averaging, the clip coefficient and the bf16 cast are folded into the Adam kernel; the
+  squared-norm reduction and the clip coefficient stay on the device (no ``.item()``);
+* parameters are views of the flat bf16 buffer, so the parameter all-gather writes in place; it is
+  issued on a side stream and joined before the next forward.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+from ..ops.gemm import count_launch
+from ..parallel.layers import set_defaults_if_not_set_tensor_model_parallel_attributes
+from ..parallel import comm
+from ..parallel.state import PM
+from .adam import FlatAdamShard
+from .buffers import Bucket, build_buffers
+
+
+class DummyOptimizer:
+    """Stand-in for pipeline stages that own no trainable parameter."""
+
+    param_groups: list = []
+    optimizer = None
+
+    def zero_grad(self, *a, **k):
+        pass
+
+    def step(self, *a, **k):
+        return True, 0.0, 0
+
+    def state_dict(self):
+        return {}
+
+    def load_state_dict(self, sd):
+        pass
+
+    def wait_param_gather(self):
+        pass
+
+
+def _default_wd_mult(name: str, p, on_1d: bool) -> float:
+    if name.endswith(".bias") or (p.dim() == 1 and not on_1d):
+        return 0.0
+    return 1.0
+
+
+class _ParamGroupView(dict):
+    """Entry of ``optimizer.param_groups``: the scheduler writes ``lr`` / ``weight_decay`` here."""
+
+
+class BaseGradientManager:
+    shard_optimizer = False
+
+    def __init__(self, cfg, model):
+        self.cfg = cfg
+        self.models = list(model) if isinstance(model, (list, tuple)) else [model]
+        self.opt_cfg = cfg.optimizer_cfg
+        self.clip_grad = float(cfg.clip_grad or 0.0)
+        named = []
+        for mi, m in enumerate(self.models):
+            for n, p in m.named_parameters():
+                set_defaults_if_not_set_tensor_model_parallel_attributes(p)
+                named.append((f"model{mi}.{n}" if len(self.models) > 1 else n, p))
+        seen, uniq = set(), []
+        for n, p in named:
+            if id(p) not in seen:
+                seen.add(id(p))
+                uniq.append((n, p))
+        self.named_params = uniq
+        if hasattr(self.opt_cfg, "mark_muon_params"):
+            for m in self.models:
+                self.opt_cfg.mark_muon_params(m)
+        self.buckets: dict = build_buffers(self.named_params, shard=self.shard_optimizer)
+        self.step_count = 0
+        self._hooks = []
+        self._install_hooks()
+        self._build_optimizers()
+        dev = self.named_params[0][1].device
+        self.device = dev
+        self.scalars = torch.zeros(4, dtype=torch.float32, device=dev)
+        self.scalars[2] = 1.0
+        self.scalars[3] = 1.0
+        self._gather_event = None
+        self._side_stream = torch.cuda.Stream() if dev.type == "cuda" else None
+        self._sq_partial = None
+        self.optimizer = self  # `.optimizer.param_groups` is what schedulers and checkpoints use
+
+    # ------------------------------------------------------------------ setup
+    def _install_hooks(self) -> None:
+        def hook(p):
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.to(p.main_grad.dtype).view_as(p.main_grad))
+                p.grad = None
+
+        for _, p in self.named_params:
+            if p.requires_grad:
+                self._hooks.append(p.register_post_accumulate_grad_hook(hook))
+
+    def _build_optimizers(self) -> None:
+        oc = self.opt_cfg
+        on_1d = bool(getattr(oc, "weight_decay_on_1d_params", False))
+        self.param_groups = [_ParamGroupView(lr=float(oc.lr), weight_decay=float(oc.weight_decay), name="default")]
+        self.shards: dict = {}
+        self.muon = None
+        muon_items = []
+        for key, b in self.buckets.items():
+            lo, hi = b.own_range()
+            own = b.own_slots()
+            if key.is_muon:
+                muon_items.append((b, own))
+                continue
+            segs = []
+            for s in own:
+                lr_mult = float(oc.scale_lr_func(s.name, s.param)) if hasattr(oc, "scale_lr_func") else 1.0
+                wd_mult = (float(oc.scale_wd_cond(s.name, s.param)) if hasattr(oc, "scale_wd_cond")
+                           else _default_wd_mult(s.name, s.param, on_1d))
+                segs.append((s.offset - lo, s.numel, lr_mult, wd_mult))
+            mode = "adamw" if getattr(oc, "is_muon", False) else "adam"
+            self.shards[key] = FlatAdamShard(b, lo, hi, segs, mode)
+        if muon_items:
+            from .muon import FlatMuon
+
+            self.muon = FlatMuon(oc, muon_items)
+
+    # ------------------------------------------------------------------ step pieces
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for b in self.buckets.values():
+            b.grad_buf.zero_()
+        for _, p in self.named_params:
+            p.grad = None
+            p.grad_added_to_main_grad = False
+
+    def wait_param_gather(self) -> None:
+        """Join the side-stream parameter all-gather before parameters are read again."""
+        if self._gather_event is not None:
+            torch.cuda.current_stream().wait_event(self._gather_event)
+            self._gather_event = None
+
+    def _allreduce_tagged(self, tag: str, group_name: str = "TP") -> None:
+        if PM.size_of(group_name) == 1:
+            return
+        grads = [p.main_grad for _, p in self.named_params if getattr(p, tag, False) and p.requires_grad]
+        if not grads:
+            return
+        flat = torch.cat([g.reshape(-1) for g in grads])
+        dist.all_reduce(flat, group=PM.group_of(group_name))
+        off = 0
+        for g in grads:
+            g.copy_(flat[off : off + g.numel()].view_as(g))
+            off += g.numel()
+
+    def _scale_expert_grads(self) -> None:
+        """Expert parameters see tokens of the whole EP group: the reference rescales their gradients
+        by TP/EP so that the later 1/EDP averaging equals the data-parallel mean
+        (``base_gradient_manager.py:180-200``)."""
+        ep, tp = PM.size_of("EP"), PM.size_of("TP")
+        if ep == 1:
+            return
+        factor = tp / ep
+        for key, b in self.buckets.items():
+            if key.reduce_group == "EDP" and factor != 1.0:
+                b.grad_buf.mul_(factor)
+
+    def _reduce(self) -> None:
+        raise NotImplementedError
+
+    def _norm_region(self, b: Bucket) -> torch.Tensor:
+        raise NotImplementedError
+
+    def _norm_group(self):
+        raise NotImplementedError
+
+    def _sqnorm_into(self, x: torch.Tensor, out: torch.Tensor, accumulate: bool) -> None:
+        if x.is_cuda:
+            lib = native.load()
+            if self._sq_partial is None:
+                self._sq_partial = torch.empty(lib.stb_sqnorm_grid(), dtype=torch.float32, device=x.device)
+            native.check(lib.stb_sqnorm(x.data_ptr(), x.numel(), self._sq_partial.data_ptr(), out.data_ptr(),
+                                        int(accumulate), native.stream()), "sqnorm")
+            count_launch(2)
+        else:
+            v = x.double().pow(2).sum().float()
+            out[0] = out[0] + v if accumulate else v
+
+    def _compute_clip(self, grad_scale: float) -> None:
+        """scalars[0] = global squared norm of the averaged gradient, [1] norm, [2] clip coefficient."""
+        tp_rank = PM.rank_in("TP")
+        regions = [self._norm_region(b) for key, b in self.buckets.items() if not (key.tp_replicated and tp_rank != 0)]
+        grp = self._norm_group()
+        multi = grp is not False and dist.is_initialized() and PM.world_size > 1
+        if self.device.type != "cuda":
+            # host path: accumulate in fp64 so that the result does not depend on how the
+            # parameters are sharded over ranks
+            tot = torch.zeros(1, dtype=torch.float64)
+            for r in regions:
+                tot += r.double().pow(2).sum()
+            tot *= grad_scale * grad_scale
+            if multi:
+                dist.all_reduce(tot, group=grp)
+            nrm = float(tot.sqrt())
+            ok = math.isfinite(nrm)
+            self.scalars[0] = float(tot)
+            self.scalars[1] = nrm
+            self.scalars[2] = (min(1.0, self.clip_grad / (nrm + 1e-6)) if self.clip_grad > 0 else 1.0) if ok else 0.0
+            self.scalars[3] = 1.0 if ok else 0.0
+            return
+        total = self.scalars[0:1]
+        for i, r in enumerate(regions):
+            self._sqnorm_into(r, total, accumulate=i > 0)
+        if not regions:
+            total.zero_()
+        total.mul_(grad_scale * grad_scale)
+        if multi:
+            dist.all_reduce(total, group=grp)
+        native.check(native.load().stb_clip_coef(self.scalars.data_ptr(), self.clip_grad, native.stream()), "clip_coef")
+        count_launch()
+
+    def _refresh_params(self) -> None:
+        pass
+
+    def count_zeros(self) -> torch.Tensor:
+        z = torch.zeros(1, dtype=torch.float32, device=self.device)
+        for b in self.buckets.values():
+            r = self._norm_region(b)
+            z += (r.numel() - torch.count_nonzero(r)).float()
+        return z
+
+    # ------------------------------------------------------------------ the step
+    @torch.no_grad()
+    def step(self):
+        """Reduce, clip, update, refresh. Returns ``(ok, grad_norm tensor, num_zeros tensor|None)``;
+        both tensors stay on the device, reading them is the caller's (logging) decision."""
+        self.step_count += 1
+        self._allreduce_tagged("sequence_parallel", "TP")
+        self._allreduce_tagged("micro_dp", "TP")
+        self._scale_expert_grads()
+        grad_scale = self._reduce()
+        self._compute_clip(grad_scale)
+        zeros = self.count_zeros() if self.cfg.log_num_zeros_in_grad else None
+        pg = self.param_groups[0]
+        oc = self.opt_cfg
+        for key, shard in self.shards.items():
+            shard.step(self.step_count, float(pg["lr"]), float(pg["weight_decay"]), float(oc.adam_beta1),
+                       float(oc.adam_beta2), float(oc.adam_eps), grad_scale, self.scalars)
+        if self.muon is not None:
+            self.muon.step(float(pg["lr"]), float(pg["weight_decay"]), grad_scale, self.scalars)
+        self._refresh_params()
+        return True, self.scalars[1], zeros
+
+    # ------------------------------------------------------------------ state
+    def state_dict(self) -> dict:
+        sd = {"step": self.step_count, "param_groups": [dict(g) for g in self.param_groups], "buckets": {}}
+        for key, shard in self.shards.items():
+            sd["buckets"][str(key)] = {k: v.detach().cpu() for k, v in shard.state_dict().items()}
+        if self.muon is not None:
+            sd["muon"] = self.muon.state_dict()
+        sd["layout"] = {str(k): [(s.name, s.owner, s.offset, s.numel) for s in b.slots] for k, b in self.buckets.items()}
+        return {"optimizer": sd}
+
+    def load_state_dict(self, state: dict) -> None:
+        sd = state.get("optimizer", state)
+        self.step_count = int(sd.get("step", 0))
+        for g, saved in zip(self.param_groups, sd.get("param_groups", [])):
+            g.update(saved)
+        for key, shard in self.shards.items():
+            if str(key) in sd.get("buckets", {}):
+                shard.load_state_dict({k: v.to(self.device) for k, v in sd["buckets"][str(key)].items()})
+                lo, hi = shard.lo, shard.hi
+                shard.bucket.param_buf[lo:hi].copy_(shard.master)
+        if self.muon is not None and "muon" in sd:
+            self.muon.load_state_dict(sd["muon"])
+        self._refresh_params()
+        self.wait_param_gather()
+
+    # ------------------------------------------------------------------ offload (RL role swapping)
+    def offload_state(self) -> None:
+        for shard in self.shards.values():
+            for name in ("master", "exp_avg", "exp_avg_sq"):
+                setattr(shard, name, getattr(shard, name).to("cpu"))
+        if self.muon is not None:
+            self.muon.to("cpu")
+
+    def reload_state(self) -> None:
+        for shard in self.shards.values():
+            for name in ("master", "exp_avg", "exp_avg_sq"):
+                setattr(shard, name, getattr(shard, name).to(self.device))
+        if self.muon is not None:
+            self.muon.to(self.device)
+
+
+class AccInFP32GradientManager(BaseGradientManager):
+    """All-reduce gradients over DP; every rank keeps the full optimizer state."""
+
+    shard_optimizer = False
+
+    def _reduce(self) -> float:
+        scale = 1.0
+        for key, b in self.buckets.items():
+            n = PM.size_of(key.reduce_group)
+            if n > 1:
+                dist.all_reduce(b.grad_buf, group=PM.group_of(key.reduce_group))
+            scale = 1.0 / PM.size_of("DP")
+        self._edp_fix(scale)
+        return scale
+
+    def _edp_fix(self, scale: float) -> None:
+        # buckets reduced over EDP are averaged over a smaller group than DP
+        dp, edp = PM.size_of("DP"), PM.size_of("EDP") if PM.has("EDP") else PM.size_of("DP")
+        if edp != dp:
+            for key, b in self.buckets.items():
+                if key.reduce_group == "EDP":
+                    b.grad_buf.mul_(dp / edp)
+
+    def _norm_region(self, b):
+        return b.grad_buf
+
+    def _norm_group(self):
+        return PM.group_of("MP") if PM.has("MP") and PM.size_of("MP") > 1 else False
+
+
+class Zero1GradientManager(BaseGradientManager):
+    """Reduce-scatter gradients over DP (EDP for experts); optimizer state only for owned parameters;
+    bf16 parameter all-gather in place."""
+
+    shard_optimizer = True
+
+    def _reduce(self) -> float:
+        for key, b in self.buckets.items():
+            if b.world > 1:
+                lo, hi = b.own_range()
+                comm.reduce_scatter_tensor(b.grad_buf[lo:hi], b.grad_buf, group=PM.group_of(key.reduce_group))
+        scale = 1.0 / PM.size_of("DP")
+        dp, edp = PM.size_of("DP"), PM.size_of("EDP") if PM.has("EDP") else PM.size_of("DP")
+        if edp != dp:
+            for key, b in self.buckets.items():
+                if key.reduce_group == "EDP":
+                    lo, hi = b.own_range()
+                    b.grad_buf[lo:hi].mul_(dp / edp)
+        return scale
+
+    def _norm_region(self, b):
+        lo, hi = b.own_range()
+        return b.grad_buf[lo:hi]
+
+    def _norm_group(self):
+        return None  # world
+
+    def _refresh_params(self) -> None:
+        multi = [(k, b) for k, b in self.buckets.items() if b.world > 1]
+        if not multi:
+            return
+        if self._side_stream is not None and self.cfg.overlap_param_gather:
+            self._side_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._side_stream):
+                for key, b in multi:
+                    lo, hi = b.own_range()
+                    comm.all_gather_into_tensor(b.param_buf, b.param_buf[lo:hi], group=PM.group_of(key.reduce_group))
+                self._gather_event = torch.cuda.Event()
+                self._gather_event.record(self._side_stream)
+        else:
+            for key, b in multi:
+                lo, hi = b.own_range()
+                comm.all_gather_into_tensor(b.param_buf, b.param_buf[lo:hi], group=PM.group_of(key.reduce_group))

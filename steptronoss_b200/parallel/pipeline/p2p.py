@@ -1,0 +1,123 @@
+"""Pipeline point-to-point exchange of activations and their gradients.
+
+Reference: ``steptronoss/core/pipeline_parallel/p2p_communication.py:14-546``.  Pipeline traffic
+stays on NCCL send/recv (it is latency-tolerant and overlaps with compute); the combined
+operations post every send and receive of one step as a single batch.  With
+``variable_seq_lengths`` the shape is exchanged first (three int64: ndim-padded dims).
+Receives are posted on the current stream; the tensors are safe to use once ``wait`` returned.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from ..state import PM
+
+
+def _device():
+    return torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() and PM.backend == "nccl" else torch.device("cpu")
+
+
+def _exchange_shapes(send_next, send_prev, recv_prev: bool, recv_next: bool):
+    dev = _device()
+    ops, bufs = [], {}
+    group = PM.group_of("PP")
+
+    def enc(t):
+        s = list(t.shape) + [0] * (3 - t.dim())
+        return torch.tensor(s[:3], dtype=torch.int64, device=dev)
+
+    if send_prev is not None:
+        ops.append(dist.P2POp(dist.isend, enc(send_prev), PM.pipeline_prev_rank(), group))
+    if recv_prev:
+        bufs["prev"] = torch.empty(3, dtype=torch.int64, device=dev)
+        ops.append(dist.P2POp(dist.irecv, bufs["prev"], PM.pipeline_prev_rank(), group))
+    if send_next is not None:
+        ops.append(dist.P2POp(dist.isend, enc(send_next), PM.pipeline_next_rank(), group))
+    if recv_next:
+        bufs["next"] = torch.empty(3, dtype=torch.int64, device=dev)
+        ops.append(dist.P2POp(dist.irecv, bufs["next"], PM.pipeline_next_rank(), group))
+    if ops:
+        for r in dist.batch_isend_irecv(ops):
+            r.wait()
+    def dec(t):
+        return tuple(int(x) for x in t.tolist() if int(x) != 0)
+    return dec(bufs["prev"]) if "prev" in bufs else None, dec(bufs["next"]) if "next" in bufs else None
+
+
+def communicate(send_next=None, send_prev=None, recv_prev: bool = False, recv_next: bool = False,
+                tensor_shape=None, dtype=torch.bfloat16, variable_seq_lengths: bool = False, wait: bool = True):
+    """Post the requested sends/receives with the neighbouring stages as one batch.
+
+    Returns ``(from_prev, from_next, requests)``; with ``wait=True`` the requests are already
+    complete and ``requests`` is empty."""
+    group = PM.group_of("PP")
+    dev = _device()
+    shape_prev = shape_next = tensor_shape
+    if variable_seq_lengths:
+        shape_prev, shape_next = _exchange_shapes(send_next, send_prev, recv_prev, recv_next)
+    from_prev = from_next = None
+    ops = []
+    if send_prev is not None:
+        ops.append(dist.P2POp(dist.isend, send_prev.contiguous(), PM.pipeline_prev_rank(), group))
+    if recv_prev:
+        from_prev = torch.empty(shape_prev, dtype=dtype, device=dev, requires_grad=True)
+        ops.append(dist.P2POp(dist.irecv, from_prev, PM.pipeline_prev_rank(), group))
+    if send_next is not None:
+        ops.append(dist.P2POp(dist.isend, send_next.contiguous(), PM.pipeline_next_rank(), group))
+    if recv_next:
+        from_next = torch.empty(shape_next, dtype=dtype, device=dev)
+        ops.append(dist.P2POp(dist.irecv, from_next, PM.pipeline_next_rank(), group))
+    reqs = dist.batch_isend_irecv(ops) if ops else []
+    if wait:
+        for r in reqs:
+            r.wait()
+        reqs = []
+    return from_prev, from_next, reqs
+
+
+class P2P:
+    """The nine send/recv combinations of the reference, bound to one shape/dtype policy."""
+
+    def __init__(self, tensor_shape=None, dtype=torch.bfloat16, variable_seq_lengths=False):
+        self.kw = dict(tensor_shape=tensor_shape, dtype=dtype, variable_seq_lengths=variable_seq_lengths)
+
+    def recv_forward(self):
+        if PM.is_pipeline_first_stage(ignore_virtual=True):
+            return None
+        return communicate(recv_prev=True, **self.kw)[0]
+
+    def recv_backward(self):
+        if PM.is_pipeline_last_stage(ignore_virtual=True):
+            return None
+        return communicate(recv_next=True, **self.kw)[1]
+
+    def send_forward(self, out):
+        if not PM.is_pipeline_last_stage(ignore_virtual=True):
+            communicate(send_next=out, **self.kw)
+
+    def send_backward(self, grad):
+        if not PM.is_pipeline_first_stage(ignore_virtual=True):
+            communicate(send_prev=grad, **self.kw)
+
+    def send_forward_recv_backward(self, out):
+        if PM.is_pipeline_last_stage(ignore_virtual=True):
+            return None
+        return communicate(send_next=out, recv_next=True, **self.kw)[1]
+
+    def send_backward_recv_forward(self, grad):
+        if PM.is_pipeline_first_stage(ignore_virtual=True):
+            return None
+        return communicate(send_prev=grad, recv_prev=True, **self.kw)[0]
+
+    def send_forward_recv_forward(self, out, recv_prev: bool, wait: bool = True):
+        r = communicate(send_next=out, recv_prev=recv_prev, wait=wait, **self.kw)
+        return r[0] if wait else (r[0], r[2])
+
+    def send_backward_recv_backward(self, grad, recv_next: bool, wait: bool = True):
+        r = communicate(send_prev=grad, recv_next=recv_next, wait=wait, **self.kw)
+        return r[1] if wait else (r[1], r[2])
+
+    def send_forward_backward_recv_forward_backward(self, out, grad, recv_prev: bool, recv_next: bool):
+        r = communicate(send_next=out, send_prev=grad, recv_prev=recv_prev, recv_next=recv_next, **self.kw)
+        return r[0], r[1]

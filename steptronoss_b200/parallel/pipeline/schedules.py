@@ -1,0 +1,307 @@
+"""Micro-batch schedules: plain forward/backward, 1F1B pipeline, interleaved (virtual) 1F1B.
+
+Reference: ``steptronoss/core/pipeline_parallel/schedules.py:127-693``.  A schedule is configured
+with the model chunks, the data iterators, ``data_sync_fn`` (fetch + broadcast one micro-batch),
+``data_proc_fn`` (pre-process) and ``loss_fn``; ``run(n)`` executes ``n`` micro-batches and leaves the
+gradients accumulated in the parameters' ``main_grad``.
+
+1F1B: stage ``r`` of ``P`` runs ``min(P - r - 1, n)`` warm-up forwards, then alternates one forward and
+one backward, then drains the remaining backwards.  Interleaved: ``n % P == 0`` is required; the
+warm-up is ``(P - r - 1)·2 + (chunks - 1)·P`` micro-steps (all of them when ``n == P``).
+"""
+from __future__ import annotations
+
+from typing import Callable, Iterator
+
+import torch
+
+from ...utils.timers import get_timers
+from ..state import PM
+from .p2p import P2P
+
+
+def _unwrap(m):
+    from ...models.module import unwrap_model
+
+    return unwrap_model(m)
+
+
+def backward_step(input_tensor, output_tensor, output_grad):
+    """Back-propagate one micro-batch through a stage; returns the gradient w.r.t. its input."""
+    if input_tensor is not None and input_tensor.requires_grad:
+        input_tensor.retain_grad()
+    if output_grad is None:
+        output_tensor.backward()
+    else:
+        torch.autograd.backward(output_tensor, grad_tensors=output_grad)
+    return input_tensor.grad if input_tensor is not None else None
+
+
+def deallocate_output_tensor(out):
+    """Free the activation that was sent downstream; only its ``grad_fn`` is needed for backward."""
+    if out is not None and torch.is_tensor(out) and out.numel() > 1:
+        out.data = torch.empty((1,), device=out.device, dtype=out.dtype)
+
+
+def custom_backward(output, grad_output):
+    """Backward through an output whose storage was released by ``deallocate_output_tensor``."""
+    if grad_output is None:
+        grad_output = torch.ones_like(output, memory_format=torch.preserve_format)
+    torch.autograd.Variable._execution_engine.run_backward(
+        tensors=(output,), grad_tensors=(grad_output,), keep_graph=False, create_graph=False, inputs=tuple(),
+        allow_unreachable=True, accumulate_grad=True)
+
+
+class FWBWScheduler:
+    def __init__(self, config) -> None:
+        self.config = config
+        self._prefetched = None
+        self._collected: list = []
+
+    def configure(self, models, data_iterators, data_sync_fn: Callable[[Iterator], dict],
+                  data_proc_fn: Callable[[dict], dict], collect_output: bool = False, loss_fn: Callable | None = None,
+                  training: bool = True):
+        self.models, self.data_iterators = list(models), list(data_iterators)
+        self.data_sync_fn, self.data_proc_fn = data_sync_fn, data_proc_fn
+        self.collect_output, self.loss_func, self.training = collect_output, loss_fn, training
+        return self
+
+    def _prefetch(self, n: int) -> None:
+        with get_timers().record("batch-generator", 2):
+            keep = PM.get_vpp_rank()
+            self._prefetched = [[] for _ in self.models]
+            for vp, it in enumerate(self.data_iterators):
+                PM.set_vpp_rank(vp)
+                for _ in range(n):
+                    self._prefetched[vp].append(self.data_sync_fn(it))
+            PM.set_vpp_rank(keep)
+
+    def forward_chunk(self, vp_rank: int = 0, input_tensor=None, loss_scale: float = 1.0):
+        PM.set_vpp_rank(vp_rank)
+        model = self.models[vp_rank]
+        _unwrap(model).set_input_tensor(input_tensor)
+        data = self._prefetched[vp_rank].pop(0)
+        with get_timers().record("data-preprocess", 1):
+            data = self.data_proc_fn(data) if self.data_proc_fn is not None else data
+        data = dict(data or {})
+        data["loss_scale"] = loss_scale
+        with get_timers().record("forward-step", 2):
+            output = model(**data)
+        if _unwrap(model).is_last_stage:
+            if self.collect_output:
+                self._collected.append(output)
+            if self.loss_func is not None:
+                return self.loss_func(data, output, loss_scale)
+            return output
+        return output
+
+    def run(self, forward_num: int = 1):
+        self._collected.clear()
+        assert len(self.models) == 1
+        self._prefetch(forward_num)
+        for _ in range(forward_num):
+            out = self.forward_chunk(0, loss_scale=1.0 / forward_num)
+            if self.training:
+                with get_timers().record("backward-step", 2):
+                    backward_step(None, out, None)
+        self._prefetched = None
+        return self._collected
+
+
+class PPScheduler(FWBWScheduler):
+    """Non-interleaved 1F1B."""
+
+    def _p2p(self) -> P2P:
+        c = self.config
+        return P2P(tensor_shape=tuple(c.pp_comm_shape) if not c.variable_seq_lengths else None, dtype=c.params_dtype,
+                   variable_seq_lengths=c.variable_seq_lengths)
+
+    def run(self, forward_num: int = 1):
+        self._collected.clear()
+        assert len(self.models) == 1
+        self._prefetch(forward_num)
+        p2p = self._p2p()
+        P, r = PM.size_of("PP"), PM.rank_in("PP")
+        warmup = min(P - r - 1, forward_num)
+        steady = forward_num - warmup
+        scale = 1.0 / forward_num
+        inputs, outputs = [], []
+        ctx = torch.autograd.graph.save_on_cpu(pin_memory=True) if self.config.pipeline_activation_cpu_offload else None
+
+        def fwd(inp):
+            if ctx is not None:
+                with ctx:
+                    return self.forward_chunk(0, inp, scale)
+            return self.forward_chunk(0, inp, scale)
+
+        for _ in range(warmup):
+            inp = p2p.recv_forward()
+            out = fwd(inp)
+            p2p.send_forward(out)
+            if self.training:
+                inputs.append(inp)
+                outputs.append(out)
+                if not PM.is_pipeline_last_stage(True):
+                    deallocate_output_tensor(out)
+        inp = p2p.recv_forward() if steady > 0 else None
+        for i in range(steady):
+            last = i == steady - 1
+            out = fwd(inp)
+            if not self.training:
+                p2p.send_forward(out)
+                inp = p2p.recv_forward() if not last else None
+                continue
+            grad = p2p.send_forward_recv_backward(out)
+            inputs.append(inp)
+            outputs.append(out)
+            if not PM.is_pipeline_last_stage(True):
+                deallocate_output_tensor(out)
+            i0, o0 = inputs.pop(0), outputs.pop(0)
+            gin = self._backward(i0, o0, grad)
+            if last:
+                p2p.send_backward(gin)
+                inp = None
+            else:
+                inp = p2p.send_backward_recv_forward(gin)
+        if self.training:
+            for _ in range(warmup):
+                i0, o0 = inputs.pop(0), outputs.pop(0)
+                grad = p2p.recv_backward()
+                gin = self._backward(i0, o0, grad)
+                p2p.send_backward(gin)
+        self._prefetched = None
+        return self._collected
+
+    @staticmethod
+    def _backward(inp, out, grad):
+        if inp is not None and inp.requires_grad:
+            inp.retain_grad()
+        if grad is None:
+            out.backward()
+        else:
+            custom_backward(out, grad)
+        return inp.grad if inp is not None else None
+
+
+class VPPScheduler(PPScheduler):
+    """Interleaved 1F1B over ``len(models)`` virtual chunks per rank."""
+
+    def run(self, forward_num: int = 1):
+        self._collected.clear()
+        P, r = PM.size_of("PP"), PM.rank_in("PP")
+        C = len(self.models)
+        if forward_num % P != 0:
+            raise AssertionError("interleaved schedule needs the number of micro-batches to be a multiple of PP")
+        self._prefetch(forward_num)
+        p2p = self._p2p()
+        total = forward_num * C
+        scale = 1.0 / forward_num
+        if forward_num == P:
+            warmup = total
+        else:
+            warmup = min((P - r - 1) * 2 + (C - 1) * P, total)
+        steady = total - warmup
+        inputs = [[] for _ in range(C)]
+        outputs = [[] for _ in range(C)]
+        out_grads = [[] for _ in range(C)]
+
+        def chunk_of(step: int, forward: bool) -> int:
+            c = (step % (P * C)) // P
+            return c if forward else C - 1 - c
+
+        def do_fwd(k: int):
+            c = chunk_of(k, True)
+            PM.set_vpp_rank(c)
+            if PM.is_pipeline_first_stage() and len(inputs[c]) == len(outputs[c]):
+                inputs[c].append(None)
+            out = self.forward_chunk(c, inputs[c][-1], scale)
+            outputs[c].append(out)
+            return out
+
+        def do_bwd(k: int):
+            c = chunk_of(k, False)
+            PM.set_vpp_rank(c)
+            if PM.is_pipeline_last_stage() and len(out_grads[c]) == 0:
+                out_grads[c].append(None)
+            i0, o0, g0 = inputs[c].pop(0), outputs[c].pop(0), out_grads[c].pop(0)
+            return self._backward(i0, o0, g0)
+
+        def next_recv_prev(k: int) -> tuple[bool, int]:
+            """Does the forward after micro-step ``k`` need an activation from the previous rank, and for
+            which chunk?"""
+            nc = chunk_of(k + 1, True) if k + 1 < total else None
+            if nc is None:
+                return False, 0
+            if r == 0:
+                # first rank receives from the last rank the output of the previous chunk
+                need = nc > 0 or False
+                prev_chunk_done = k + 1 >= P  # data wrapped around once
+                return (nc != 0) and prev_chunk_done or (nc != 0), nc
+            return True, nc
+
+        def next_recv_next(k: int) -> tuple[bool, int]:
+            nc = chunk_of(k + 1, False) if k + 1 < total else None
+            if nc is None:
+                return False, 0
+            if r == P - 1:
+                return nc != C - 1, nc
+            return True, nc
+
+        PM.set_vpp_rank(0)
+        if not PM.is_pipeline_first_stage():
+            inputs[0].append(p2p.recv_forward())
+        elif r != 0:
+            inputs[0].append(p2p.recv_forward())
+        for k in range(warmup):
+            out = do_fwd(k)
+            c = chunk_of(k, True)
+            PM.set_vpp_rank(c)
+            send = None if PM.is_pipeline_last_stage() else out
+            rp, nc = next_recv_prev(k)
+            if k == total - 1:
+                rp = False
+            got = p2p.send_forward_recv_forward(send, recv_prev=rp) if (send is not None or rp) else None
+            if send is not None and self.training:
+                deallocate_output_tensor(out)
+            if rp:
+                inputs[nc].append(got)
+        if self.training:
+            if steady > 0 or warmup == total:
+                PM.set_vpp_rank(C - 1)
+                if not PM.is_pipeline_last_stage():
+                    out_grads[C - 1].append(p2p.recv_backward())
+            for k in range(steady):
+                fk = warmup + k
+                out = do_fwd(fk)
+                c = chunk_of(fk, True)
+                PM.set_vpp_rank(c)
+                send_f = None if PM.is_pipeline_last_stage() else out
+                gin = do_bwd(k)
+                bc = chunk_of(k, False)
+                PM.set_vpp_rank(bc)
+                send_b = None if PM.is_pipeline_first_stage() else gin
+                rp, nfc = next_recv_prev(fk)
+                rn, nbc = next_recv_next(k)
+                if k == total - 1:
+                    rn = False
+                a, b = p2p.send_forward_backward_recv_forward_backward(send_f, send_b, rp, rn)
+                if send_f is not None:
+                    deallocate_output_tensor(out)
+                if rp:
+                    inputs[nfc].append(a)
+                if rn:
+                    out_grads[nbc].append(b)
+            for k in range(steady, total):
+                gin = do_bwd(k)
+                bc = chunk_of(k, False)
+                PM.set_vpp_rank(bc)
+                send_b = None if PM.is_pipeline_first_stage() else gin
+                rn, nbc = next_recv_next(k)
+                if k == total - 1:
+                    rn = False
+                got = p2p.send_backward_recv_backward(send_b, recv_next=rn) if (send_b is not None or rn) else None
+                if rn:
+                    out_grads[nbc].append(got)
+        self._prefetched = None
+        PM.set_vpp_rank(0)
+        return self._collected

@@ -1,0 +1,212 @@
+"""SFT / pre-training loop (reference ``steptronoss/core/trainers/lm_trainer.py:37-476``).
+
+``train_step``: zero the flat gradient buffers, run the micro-batch schedule (forward + backward
+with gradients accumulated in ``main_grad``), then the gradient manager's fused reduce / clip /
+Adam / parameter refresh.  Nothing in the step reads a device value on the host; the loss, the
+gradient norm and the kernel status word are read only when a log line is due.
+"""
+from __future__ import annotations
+
+import os
+import time
+
+import torch
+
+from ..models.module import Float16Module, unwrap_model
+from ..ops import native
+from ..parallel.state import PM, set_mpu_random_seed
+from ..utils.logger import logger
+from ..utils.metrics import GlobalMetrics
+from ..utils.timers import get_timers, init_timers
+from .base_trainer import BaseTrainer
+
+
+class DecoderPretrainTrainer(BaseTrainer):
+    def __init__(self, exp):
+        super().__init__(exp)
+        self.models = []
+        self.grad_manager = None
+        self.scheduler = None
+        self.dataloader = None
+        self.data_iterators = []
+        self.checkpointer = None
+        self.writer = None
+        self.train_iters = None
+        self.history: list = []
+        self.consumed_samples = 0
+        self._t_last = time.perf_counter()
+
+    # ------------------------------------------------------------------ set-up
+    def before_train(self):
+        exp = self.exp
+        PM.initialize()
+        PM.set_mesh(exp.model_cfg.parallel_cfg)
+        set_mpu_random_seed(exp.seed)
+        prof = getattr(exp, "profiler_cfg", None)
+        init_timers(getattr(prof, "timing_log_level", 0), getattr(prof, "timing_use_event", True))
+        GlobalMetrics.clear()
+        if getattr(exp, "metric_cfg", None) is not None:
+            exp.metric_cfg.register()
+        if PM.world_rank == PM.world_size - 1 and getattr(exp.trainer_cfg, "writer_backend", None):
+            try:
+                self.writer = exp.build_log_writer()
+            except Exception as e:
+                logger.warning(f"no log writer: {e}", at=None)
+        self.call_hooks("after_init")
+        self.setup_model()
+        self.grad_manager = exp.optimizer_cfg.build_gradient_manager(self.models)
+        self.build_dataloader()
+        self.scheduler = exp.scheduler_cfg.build_scheduler(self.grad_manager.optimizer)
+        ck = getattr(exp, "checkpoint_cfg", None)
+        if ck is not None:
+            self.checkpointer = ck.build_checkpointer()
+            self.load_checkpoint()
+        logger.info(f"trainer ready: {PM}", at=0)
+
+    def setup_model(self):
+        cfg = self.exp.model_cfg
+        dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.device = dev
+        self.models = []
+        for vp in range(PM.get_vpp_size()):
+            PM.set_vpp_rank(vp)
+            with torch.device(dev):
+                m = cfg.build_model(vpp_rank=vp) if PM.get_vpp_size() > 1 else cfg.build_model()
+            m.init_weights(self.exp.seed, getattr(cfg, "init_std", 0.02))
+            self.models.append(Float16Module(m, cfg.params_dtype, cfg.fp32_output))
+        PM.set_vpp_rank(0)
+
+    def build_dataloader(self):
+        exp = self.exp
+        ends = PM.is_pipeline_first_stage(True) or PM.is_pipeline_last_stage(True)
+        is_src = ends and PM.rank_in("TP") == 0 and PM.rank_in("CP") == 0
+        if is_src:
+            self.dataloader = exp.data_cfg.build_dataloader(PM.get_data_rank(), PM.get_data_world_size())
+        self.data_iterators = [iter(self.dataloader) if self.dataloader is not None else None for _ in self.models]
+        if len(self.models) > 1 and self.dataloader is not None:
+            it = iter(self.dataloader)
+            self.data_iterators = [it for _ in self.models]
+        self.train_iters = exp.trainer_cfg.train_iters
+        if self.train_iters is None:
+            n = len(self.dataloader) if self.dataloader is not None and hasattr(self.dataloader, "__len__") else 0
+            t = torch.tensor([n * PM.get_data_world_size() // exp.trainer_cfg.global_batch_size], dtype=torch.int64,
+                             device=self.device)
+            if torch.distributed.is_initialized():
+                torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+            self.train_iters = int(t.item())
+
+    # ------------------------------------------------------------------ loop
+    def train_loop(self):
+        tc = self.exp.trainer_cfg
+        timers = get_timers()
+        self._t_last = time.perf_counter()
+        while self.iteration < self.train_iters:
+            self.call_hooks("before_step")
+            with timers.record("iteration", 0):
+                self.train_step()
+            self.iteration += 1
+            self.call_hooks("after_step")
+            if self.iteration % tc.log_interval == 0:
+                self.training_log()
+            ck = getattr(self.exp, "checkpoint_cfg", None)
+            if ck is not None and ck.save_interval and self.iteration % ck.save_interval == 0:
+                self.save_checkpoint()
+
+    def num_microbatches(self) -> int:
+        tc = self.exp.trainer_cfg
+        n = tc.global_batch_size // PM.get_data_world_size() // tc.micro_batch_size
+        if n < 1:
+            raise ValueError("global_batch_size smaller than data-parallel size x micro_batch_size")
+        return n
+
+    def train_step(self):
+        exp, tc = self.exp, self.exp.trainer_cfg
+        timers = get_timers()
+        gm = self.grad_manager
+        gm.zero_grad()
+        gm.wait_param_gather()
+        n_micro = self.num_microbatches()
+        sched = exp.model_cfg.get_pp_scheduler()
+        sched.configure(self.models, self.data_iterators,
+                        data_sync_fn=lambda it: tc.sync_get_data(it),
+                        data_proc_fn=exp.data_cfg.preprocess, loss_fn=tc.loss_func, training=True)
+        with timers.record("forward-backward", 1):
+            sched.run(n_micro)
+        with timers.record("optimizer-step", 1):
+            ok, grad_norm, zeros = gm.step()
+        GlobalMetrics.grad_norm.add(grad_norm)
+        if zeros is not None:
+            GlobalMetrics.grad_zeros.add(zeros)
+        for m in self.models:
+            um = unwrap_model(m)
+            if hasattr(um, "after_optimizer_step"):
+                um.after_optimizer_step()
+        tokens = tc.global_batch_size * tc.global_seq_length
+        self.consumed_samples += tc.global_batch_size
+        self.scheduler.step(exp.scheduler_cfg.increment(tc.global_batch_size, tokens)
+                            if hasattr(exp.scheduler_cfg, "increment") else 1)
+        return ok
+
+    def training_log(self):
+        tc = self.exp.trainer_cfg
+        now = time.perf_counter()
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+            native.raise_if_kernel_error()
+            now = time.perf_counter()
+        dt = (now - self._t_last) / tc.log_interval
+        self._t_last = now
+        GlobalMetrics.iteration_time.add(dt)
+        metrics = GlobalMetrics.reduce_all()
+        tokens = tc.global_batch_size * tc.global_seq_length
+        tps_card = tokens / dt / max(PM.world_size, 1)
+        logs = tc.make_logs(self.iteration, metrics, self.writer)
+        line = (f"iter {self.iteration}/{self.train_iters} | consumed samples {self.consumed_samples} | "
+                f"{dt * 1e3:.1f} ms/iter | tokens-per-second-per-card {tps_card:.1f} | "
+                f"lr {self.scheduler.cur_lr:.3E} | global batch size {tc.global_batch_size} | "
+                f"grad-norm {float(metrics.get('grad_norm', 0.0)):.3f} | lm_loss {logs.get('lm_loss', 'n/a')}")
+        self.history.append({"iteration": self.iteration, "ms_per_iter": dt * 1e3,
+                             "lm_loss": float(metrics["lm_loss"]) if "lm_loss" in metrics else None,
+                             "grad_norm": float(metrics.get("grad_norm", 0.0))})
+        logger.info(line, at=-1)
+        tl = get_timers()
+        if tl.log_level > 0:
+            logger.info(tl.log_string(normalizer=tc.log_interval), at=0)
+
+    # ------------------------------------------------------------------ checkpoints
+    def load_checkpoint(self):
+        ck = self.exp.checkpoint_cfg
+        path = None
+        if ck.auto_resume:
+            path = self.checkpointer.latest()
+        if path is None and ck.load_path:
+            path = ck.load_path
+        if path is None:
+            if ck.load_safetensors:
+                from ..checkpointing.hf_checkpoint import load_safetensors_into
+
+                for m in self.models:
+                    load_safetensors_into(unwrap_model(m), ck.load_safetensors)
+            return
+        state = self.checkpointer.load_ckpt(path, self.models, self.grad_manager, self.scheduler, self.dataloader)
+        if state and ck.load_options.iter:
+            self.iteration = int(state.get("iteration", 0))
+            self.history = state.get("history", [])
+            self.consumed_samples = int(state.get("consumed_samples", 0))
+
+    def save_checkpoint(self, sync: bool = False):
+        if self.checkpointer is None:
+            return
+        extra = {"exp": self.exp.to_dict(rep=True), "history": self.history, "iteration": self.iteration,
+                 "consumed_samples": self.consumed_samples}
+        self.checkpointer.save_ckpt(self.iteration, self.models, self.grad_manager, self.scheduler, self.dataloader,
+                                    extra, sync=sync)
+
+    def after_train(self):
+        self.call_hooks("after_train")
+        ck = getattr(self.exp, "checkpoint_cfg", None)
+        if self.checkpointer is not None and ck is not None and ck.save_interval:
+            self.save_checkpoint(sync=True)
+            self.checkpointer.join()
+        if self.writer is not None:
+            self.writer.close()

@@ -1,0 +1,272 @@
+"""Chainable metrics: ``Metric().mean("time").mean("dp").sum("pp")``.
+
+Reference: ``steptronoss/utils/metrics.py:20-782``.  A metric collects values between two log
+points (the ``time`` axis) and is then reduced along the declared chain; each non-``time`` link is
+one collective over the process-group family of that name (``dp``, ``tp``, ``pp``, ``ep``, ``cp``,
+``mp``, ``world``).  Unlike the reference, values added as device tensors stay on the device until
+the reduction (no host synchronisation per ``add``).
+"""
+from __future__ import annotations
+
+import contextlib
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+_OPS = ("mean", "sum", "max", "min", "last", "first")
+
+
+def _group_for(axis: str):
+    from ..parallel.state import PM
+
+    if axis == "world":
+        return dist.group.WORLD if dist.is_initialized() else None, PM.world_size
+    name = axis.upper()
+    if not PM.has(name):
+        return None, 1
+    return PM.group_of(name), PM.size_of(name)
+
+
+def _reduce_time(vals: list, op: str):
+    if not vals:
+        return None
+    if op == "last":
+        return vals[-1]
+    if op == "first":
+        return vals[0]
+    ts = [v if torch.is_tensor(v) else torch.tensor(float(v)) for v in vals]
+    dev = next((t.device for t in ts if t.is_cuda), ts[0].device)
+    st = torch.stack([t.detach().float().to(dev) for t in ts])
+    return {"mean": st.mean(0), "sum": st.sum(0), "max": st.amax(0), "min": st.amin(0)}[op]
+
+
+def _reduce_group(val: torch.Tensor, axis: str, op: str):
+    group, size = _group_for(axis)
+    if size == 1 or not dist.is_initialized():
+        return val
+    if dist.get_backend(group) == "nccl" and not val.is_cuda:
+        val = val.cuda()
+    val = val.clone()
+    red = {"mean": dist.ReduceOp.SUM, "sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN}[op]
+    dist.all_reduce(val, op=red, group=group)
+    if op == "mean":
+        val = val / size
+    return val
+
+
+class Metric:
+    def __init__(self) -> None:
+        self.chain: list[tuple[str, str]] = []
+        self.values: list = []
+        self.enabled = True
+        self.name: str | None = None
+
+    def _link(self, op: str, axis: str):
+        self.chain.append((op, axis.lower()))
+        return self
+
+    def mean(self, axis: str): return self._link("mean", axis)      # noqa: E704
+    def sum(self, axis: str): return self._link("sum", axis)        # noqa: E704
+    def max(self, axis: str): return self._link("max", axis)        # noqa: E704
+    def min(self, axis: str): return self._link("min", axis)        # noqa: E704
+    def last(self, axis: str = "time"): return self._link("last", axis)    # noqa: E704
+    def first(self, axis: str = "time"): return self._link("first", axis)  # noqa: E704
+
+    def add(self, value, subname: str | None = None, iop: str | None = None) -> None:
+        """Record one value. ``iop`` (``"sum"``/``"max"``/...) merges into the last recorded value
+        instead of appending (in-place accumulation inside one iteration)."""
+        if not self.enabled:
+            return
+        if torch.is_tensor(value):
+            value = value.detach()
+        if iop and self.values:
+            prev = self.values[-1]
+            self.values[-1] = {"sum": lambda a, b: a + b, "max": lambda a, b: torch.maximum(torch.as_tensor(a), torch.as_tensor(b)),
+                               "min": lambda a, b: torch.minimum(torch.as_tensor(a), torch.as_tensor(b)),
+                               "mean": lambda a, b: (a + b) / 2}[iop](prev, value)
+        else:
+            self.values.append(value)
+
+    def reduce(self):
+        chain = self.chain or [("mean", "time")]
+        val: Any = None
+        time_done = False
+        for op, axis in chain:
+            if axis == "time":
+                val = _reduce_time(self.values, op)
+                time_done = True
+            else:
+                if not time_done:
+                    val = _reduce_time(self.values, "mean")
+                    time_done = True
+                if val is None:
+                    val = torch.zeros(())
+                val = _reduce_group(torch.as_tensor(val, dtype=torch.float32), axis, op)
+        if not time_done:
+            val = _reduce_time(self.values, "mean")
+        return val
+
+    def reset(self) -> None:
+        self.values = []
+
+    def __repr__(self) -> str:
+        return f"{type(self).__name__}({'.'.join(f'{o}({a})' for o, a in self.chain)})"
+
+
+class GroupMetric(Metric):
+    """A family of metrics sharing one chain, keyed by ``subname``; reduces to ``{name/sub: value}``."""
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.sub: dict[str, list] = {}
+
+    def add(self, value, subname: str | None = None, iop: str | None = None) -> None:
+        if not self.enabled:
+            return
+        key = subname or "_"
+        self.values = self.sub.setdefault(key, [])
+        super().add(value, iop=iop)
+        self.sub[key] = self.values
+
+    def reduce(self):
+        out = {}
+        for key in sorted(self.sub):
+            self.values = self.sub[key]
+            out[key] = Metric.reduce(self)
+        return out
+
+    def reset(self) -> None:
+        self.sub, self.values = {}, []
+
+
+class ModelLayerMetric(GroupMetric):
+    """Per-layer values (``subname`` = layer id) gathered along the pipeline by the ``pp`` link."""
+
+
+class GradNormMetric(GroupMetric):
+    """Per-parameter gradient norms (squared norms are summed over model-parallel ranks, then rooted)."""
+
+    def __init__(self) -> None:
+        super().__init__()
+        self.chain = [("last", "time")]
+
+
+class PercentageMetric(Metric):
+    """``add(numerator, denominator)`` pairs; reduces both along the chain and divides."""
+
+    def add(self, value, total=None, subname=None, iop=None) -> None:  # type: ignore[override]
+        if not self.enabled:
+            return
+        v = torch.as_tensor(value, dtype=torch.float32).detach()
+        t = torch.as_tensor(1.0 if total is None else total, dtype=torch.float32).detach()
+        if t.device != v.device:
+            t = t.to(v.device)
+        self.values.append(torch.stack([v.reshape(()), t.reshape(())]))
+
+    def reduce(self):
+        if not self.values:
+            return None
+        saved_chain = self.chain
+        self.chain = [(("sum" if op == "mean" else op), ax) for op, ax in (saved_chain or [("sum", "time")])]
+        try:
+            pair = Metric.reduce(self)
+        finally:
+            self.chain = saved_chain
+        return pair[0] / pair[1].clamp_min(1e-12)
+
+
+class HistogramMetric(Metric):
+    def reduce(self):
+        if not self.values:
+            return None
+        return torch.cat([torch.as_tensor(v).detach().float().flatten().cpu() for v in self.values])
+
+
+class TextMetric(Metric):
+    def add(self, value, subname=None, iop=None) -> None:
+        if self.enabled:
+            self.values.append(str(value))
+
+    def reduce(self):
+        return list(self.values)
+
+
+class MetricHolder:
+    """Registry reachable as ``GlobalMetrics.<name>``; unknown names resolve to a disabled sink so
+    that model code can record metrics that an experiment did not register."""
+
+    def __init__(self) -> None:
+        object.__setattr__(self, "metrics", {})
+        object.__setattr__(self, "_disabled", False)
+        object.__setattr__(self, "_sink", _Sink())
+
+    def register(self, name: str, metric: Metric) -> None:
+        metric.name = name
+        self.metrics[name] = metric
+
+    def batch_register(self, cfg) -> None:
+        for k, v in cfg.items():
+            if isinstance(v, Metric):
+                self.register(k, v)
+
+    def __getattr__(self, name: str):
+        m = self.metrics.get(name)
+        if m is None or self._disabled:
+            return self._sink
+        return m
+
+    def __contains__(self, name: str) -> bool:
+        return name in self.metrics
+
+    def reduce_all(self, reset: bool = True) -> dict:
+        out = {}
+        for name, m in self.metrics.items():
+            val = m.reduce()
+            if isinstance(val, dict):
+                for k, v in val.items():
+                    if v is not None:
+                        out[f"{name}/{k}" if k != "_" else name] = v
+            elif val is not None:
+                out[name] = val
+            if reset:
+                m.reset()
+        return out
+
+    def reset(self) -> None:
+        for m in self.metrics.values():
+            m.reset()
+
+    def clear(self) -> None:
+        self.metrics.clear()
+
+    @contextlib.contextmanager
+    def disable(self):
+        prev = self._disabled
+        object.__setattr__(self, "_disabled", True)
+        try:
+            yield
+        finally:
+            object.__setattr__(self, "_disabled", prev)
+
+    @contextlib.contextmanager
+    def fork(self):
+        """Temporarily collect into fresh copies (e.g. an evaluation pass); yields the holder."""
+        saved = {k: list(getattr(m, "values", [])) for k, m in self.metrics.items()}
+        saved_sub = {k: dict(m.sub) for k, m in self.metrics.items() if isinstance(m, GroupMetric)}
+        self.reset()
+        try:
+            yield self
+        finally:
+            for k, m in self.metrics.items():
+                m.values = saved.get(k, [])
+                if isinstance(m, GroupMetric):
+                    m.sub = saved_sub.get(k, {})
+
+
+class _Sink:
+    def add(self, *a, **k):
+        pass
+
+
+GlobalMetrics = MetricHolder()

@@ -1,0 +1,141 @@
+"""Named timers with log levels (reference ``steptronoss/timers.py:17-327``): CUDA-event or wall
+clock timing, ``timeit`` decorator / context manager, per-interval report."""
+from __future__ import annotations
+
+import functools
+import time
+
+import torch
+
+
+class Timer:
+    def __init__(self, name: str, use_event: bool = True):
+        self.name = name
+        self.use_event = use_event and torch.cuda.is_available()
+        self.elapsed_ms = 0.0
+        self.count = 0
+        self._pending: list = []
+        self._t0 = None
+        self._ev0 = None
+        self.started = False
+
+    def start(self):
+        if self.started:
+            return
+        if self.use_event:
+            self._ev0 = torch.cuda.Event(enable_timing=True)
+            self._ev0.record()
+        else:
+            self._t0 = time.perf_counter()
+        self.started = True
+
+    def stop(self):
+        if not self.started:
+            return
+        if self.use_event:
+            ev1 = torch.cuda.Event(enable_timing=True)
+            ev1.record()
+            self._pending.append((self._ev0, ev1))
+        else:
+            self.elapsed_ms += (time.perf_counter() - self._t0) * 1e3
+        self.count += 1
+        self.started = False
+
+    def elapsed(self, reset: bool = True) -> float:
+        """Accumulated milliseconds (synchronises on the recorded events)."""
+        was = self.started
+        if was:
+            self.stop()
+        for a, b in self._pending:
+            b.synchronize()
+            self.elapsed_ms += a.elapsed_time(b)
+        self._pending = []
+        out = self.elapsed_ms
+        if reset:
+            self.elapsed_ms, self.count = 0.0, 0
+        if was:
+            self.start()
+        return out
+
+
+class _Noop:
+    def start(self): pass   # noqa: E704
+    def stop(self): pass    # noqa: E704
+    def __enter__(self): return self   # noqa: E704
+    def __exit__(self, *a): return False   # noqa: E704
+
+
+class _Scope:
+    def __init__(self, timer):
+        self.timer = timer
+
+    def __enter__(self):
+        self.timer.start()
+        return self.timer
+
+    def __exit__(self, *a):
+        self.timer.stop()
+        return False
+
+
+class Timers:
+    """Levels: 0 always, 1 coarse (forward-backward, optimizer-step, dataloader-next), 2 fine."""
+
+    def __init__(self, log_level: int = 0, use_event: bool = True):
+        self.log_level = log_level
+        self.use_event = use_event
+        self.timers: dict[str, Timer] = {}
+        self._noop = _Noop()
+
+    def __call__(self, name: str, log_level: int = 0):
+        if log_level > self.log_level:
+            return self._noop
+        if name not in self.timers:
+            self.timers[name] = Timer(name, self.use_event)
+        return self.timers[name]
+
+    def record(self, name: str, log_level: int = 0):
+        t = self(name, log_level)
+        return t if isinstance(t, _Noop) else _Scope(t)
+
+    def report(self, names=None, normalizer: float = 1.0, reset: bool = True) -> dict:
+        names = names or list(self.timers)
+        return {n: self.timers[n].elapsed(reset) / normalizer for n in names if n in self.timers}
+
+    def log_string(self, normalizer: float = 1.0, reset: bool = True) -> str:
+        rep = self.report(normalizer=normalizer, reset=reset)
+        return "time (ms) | " + " | ".join(f"{k}: {v:.2f}" for k, v in rep.items())
+
+
+_GLOBAL = Timers()
+
+
+def init_timers(log_level: int = 0, use_event: bool = True) -> Timers:
+    global _GLOBAL
+    _GLOBAL = Timers(log_level, use_event)
+    return _GLOBAL
+
+
+def get_timers() -> Timers:
+    return _GLOBAL
+
+
+class timeit:  # noqa: N801
+    """``@timeit("name", log_level=1)`` or ``with timeit("name"):``."""
+
+    def __init__(self, name: str, log_level: int = 2):
+        self.name, self.log_level = name, log_level
+
+    def __call__(self, fn):
+        @functools.wraps(fn)
+        def wrapper(*a, **k):
+            with get_timers().record(self.name, self.log_level):
+                return fn(*a, **k)
+        return wrapper
+
+    def __enter__(self):
+        self._scope = get_timers().record(self.name, self.log_level)
+        return self._scope.__enter__()
+
+    def __exit__(self, *a):
+        return self._scope.__exit__(*a)

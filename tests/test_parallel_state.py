@@ -1,0 +1,77 @@
+import pytest
+
+from steptronoss_b200.exp.base_exp import ParallelConfig
+from steptronoss_b200.parallel.state import ParallelManager, layout_from_pattern
+
+
+def test_patterns_tp_pp_dp():
+    # world 8, p=2, t=2 -> d=2 ; rank = p*4 + d*2 + t
+    tp = layout_from_pattern("(p d t) -> (p d) t", 8, p=2, t=2)
+    pp = layout_from_pattern("(p d t) -> (d t) p", 8, p=2, t=2)
+    dp = layout_from_pattern("(p d t) -> (p t) d", 8, p=2, t=2)
+    assert tp == [[0, 1], [2, 3], [4, 5], [6, 7]]
+    assert pp == [[0, 4], [1, 5], [2, 6], [3, 7]]
+    assert dp == [[0, 2], [1, 3], [4, 6], [5, 7]]
+
+
+def test_patterns_cp_and_ep():
+    cp = layout_from_pattern("(p d c t) -> (p d t) c", 8, p=1, c=2, t=2)
+    assert cp == [[0, 2], [1, 3], [4, 6], [5, 7]]
+    ep = layout_from_pattern("(p edp ep etp) -> (p edp etp) ep", 8, p=1, ep=4, etp=1)
+    assert ep == [[0, 1, 2, 3], [4, 5, 6, 7]]
+    edp = layout_from_pattern("(p edp ep etp) -> (p ep etp) edp", 8, p=1, ep=4, etp=1)
+    assert edp == [[0, 4], [1, 5], [2, 6], [3, 7]]
+
+
+def test_leftover_row_and_errors():
+    rows = layout_from_pattern("(p d t) -> (p d) t", 7, p=1, t=2)
+    assert rows[-1] == [6] and rows[0] == [0, 1]
+    with pytest.raises(ValueError):
+        layout_from_pattern("(p d t) -> (p d) t", 2, p=2, t=2)
+
+
+@pytest.mark.parametrize("rank", range(8))
+def test_manager_any_rank_of_a_mesh(rank):
+    pm = ParallelManager()
+    pm.world_size, pm.world_rank = 8, rank
+    cfg = ParallelConfig()
+    cfg.tensor_model_parallel_size = 2
+    cfg.pipeline_model_parallel_size = 2
+    cfg.expert_tensor_parallel_size = 1
+    cfg.expert_model_parallel_size = 2
+    import steptronoss_b200.parallel.state as st
+
+    old = st.PM
+    st.PM = pm
+    try:
+        import steptronoss_b200.exp.base_exp  # build_parallel looks PM up at call time
+        rows = {}
+        for name, pattern in cfg.parallel_definition.items():
+            axes = set(pattern.split("->")[0].replace("(", " ").replace(")", " ").split())
+            sizes = {"p": 2, "c": 1, "ep": 2, "t": 2, "etp": 1}
+            rows[name] = pm.define_parallel(pattern, **{k: v for k, v in sizes.items() if k in axes})
+            pm.new_parallel(name, rows[name])
+    finally:
+        st.PM = old
+    assert pm.size_of("TP") == 2 and pm.size_of("PP") == 2 and pm.size_of("DP") == 2
+    assert pm.rank_in("TP") == rank % 2 and pm.rank_in("PP") == rank // 4
+    assert pm.rank_in("DP") == (rank // 2) % 2
+    assert pm.is_pipeline_first_stage() == (rank < 4)
+    assert pm.size_of("EP") == 2 and pm.size_of("EDP") == 2
+
+
+def test_named_rng_streams_differ_across_family():
+    import torch
+
+    seeds = []
+    for rank in range(2):
+        pm = ParallelManager()
+        pm.world_size, pm.world_rank = 2, rank
+        pm.new_parallel("TP", [[0, 1]])
+        pm.register_rng("drop", 100, ["TP"])
+        with pm.use_rng("drop"):
+            seeds.append(torch.rand(1).item())
+        with pm.use_rng("drop"):
+            second = torch.rand(1).item()
+        assert second != seeds[-1]
+    assert seeds[0] != seeds[1]

@@ -1,0 +1,116 @@
+"""End-to-end training on CPU: single process, and 2 gloo ranks of data parallelism that must
+reproduce the single-process loss curve and parameters."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from steptronoss_b200.exp.base_exp import DataConfig
+from tests.tiny_exp import make_tiny_exp
+
+
+class FixedDocsLoader:
+    """Each sample packs two documents of 128 tokens; ids uniform in [0, vocab) from seed 0; labels are
+    the inputs shifted by one; the loss mask covers the last 64 positions of each document."""
+
+    def __init__(self, dp_rank, dp_size, vocab=1024, n=40):
+        g = torch.Generator().manual_seed(0)
+        self.all = torch.randint(0, vocab, (n, 2, 129), generator=g)
+        self.i, self.dp_rank, self.dp_size = 0, dp_rank, dp_size
+
+    def __iter__(self):
+        return self
+
+    def __len__(self):
+        return len(self.all)
+
+    def __next__(self):
+        docs = self.all[self.i * self.dp_size + self.dp_rank]
+        self.i += 1
+        ids = docs[:, :-1].reshape(1, -1)
+        labels = docs[:, 1:].reshape(1, -1)
+        mask = torch.zeros(2, 128)
+        mask[:, 64:] = 1.0
+        pos = torch.arange(128, dtype=torch.int32).repeat(2)
+        return {"input_ids": ids, "labels": labels, "loss_masks": mask.reshape(1, -1),
+                "cu_seqlens": torch.tensor([0, 128, 256], dtype=torch.int32),
+                "max_seq_len": torch.tensor(128, dtype=torch.int32), "position_id": pos}
+
+
+class FixedDataConfig(DataConfig):
+    global_data_keys = ["cu_seqlens", "position_id", "max_seq_len"]
+
+    def build_dataloader(self, dp_rank=0, dp_size=1):
+        return FixedDocsLoader(dp_rank, dp_size)
+
+    def preprocess(self, batch):
+        return batch
+
+
+def _run(exp, steps=10):
+    exp.data_cfg = FixedDataConfig
+    tr = exp.trainer_cfg.get_trainer_cls()(exp=exp)
+    tr.before_train()
+    losses = []
+    for _ in range(steps):
+        tr.train_step()
+        tr.iteration += 1
+        tr.training_log()
+        losses.append(tr.history[-1]["lm_loss"])
+    params = {n: p.detach().clone() for n, p in tr.models[0].named_parameters()}
+    return losses, params, tr
+
+
+def _make(zero1=True, **kw):
+    e = make_tiny_exp(gbs=2, seq=256, iters=10, lr=1e-3, wd=0.1, clip=1.0, zero1=zero1, **kw)
+    e.seed = 0
+    e.optimizer_cfg.optimizer_cfg.adam_beta1, e.optimizer_cfg.optimizer_cfg.adam_beta2 = 0.9, 0.95
+    return e
+
+
+def test_single_process_loss_decreases_on_repeated_batch():
+    e = _make()
+    losses, _, _ = _run(e, steps=10)
+    assert all(l == l for l in losses)
+    assert 6.5 < losses[0] < 7.5
+
+
+def _worker(rank, world, port, zero1, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    torch.set_num_threads(1)
+    from steptronoss_b200.parallel.state import PM
+
+    PM.initialize(backend="gloo")
+    losses, params, _ = _run(_make(zero1=zero1))
+    q.put((rank, losses, {k: v.numpy() for k, v in params.items()}))
+    torch.distributed.barrier()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.parametrize("zero1", [True, False])
+def test_dp2_gloo_matches_single_process_exactly(zero1):
+    torch.set_num_threads(1)
+    os.environ.pop("WORLD_SIZE", None)
+    ref_losses, ref_params, _ = _run(_make(zero1=zero1))
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, zero1, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, losses, params in results:
+        assert losses == ref_losses, f"rank {rank}: {losses} vs {ref_losses}"
+        for k, v in ref_params.items():
+            assert torch.equal(torch.from_numpy(params[k]), v), f"rank {rank}: parameter {k} differs"
