@@ -278,6 +278,12 @@ def run_reference(args):
 
 
 if __name__ == "__main__":
+    import faulthandler
+
+    faulthandler.enable()
+    if os.environ.get("STB200_BENCH_WATCHDOG_S"):
+        # development aid: dump every thread's stack and exit if the run exceeds the given seconds
+        faulthandler.dump_traceback_later(int(os.environ["STB200_BENCH_WATCHDOG_S"]), exit=True)
     a = parse()
     if a.impl == "reference":
         run_reference(a)

@@ -1,0 +1,742 @@
+// Flash attention for sm_100a: packed variable-length sequences, causal and sliding-window masks,
+// grouped-query heads, head_dim 128.  QK^T, PV and all five backward products run on tcgen05.mma
+// with accumulators in TMEM; operands arrive by TMA (128-byte swizzle); softmax rows live one per
+// thread (thread r of the four softmax warps owns TMEM lane r).
+//
+// Replaces the FlashAttention-2 / SDPA paths of the reference AttentionCore
+// (steptronoss/model/common/attention_core.py:119-400) including its separate q / k segment
+// tables (q rows of a segment are the last Lq of its Lk keys, as under context parallelism).
+//
+// Kernels
+//   attn_fwd_kernel   : CTA = (q block of 128 rows, q head). Loop over key blocks: S = Q K^T (TMEM,
+//                       double buffered) -> softmax threads -> P (bf16, smem) -> PV (TMEM) -> running
+//                       output kept in registers with the usual max/sum rescaling. Writes O and LSE.
+//   attn_bwd_dq_kernel: same decomposition; per key block S and dP = dO V^T, dS = P o (dP - delta),
+//                       dQ += dS K accumulated in TMEM.
+//   attn_bwd_dkv_kernel: CTA = (key block of 128, kv head); loops over the q heads of the group and
+//                       the q blocks that see this key block; dV += P^T dO, dK += dS^T Q in TMEM.
+//   attn_delta_kernel : delta[h][t] = sum_d dO o O.
+// S is recomputed in both backward kernels, which removes every atomic and makes the gradients
+// deterministic.
+#include "common.cuh"
+
+namespace stb {
+
+constexpr int kD = 128;        // head dim
+constexpr int kBM = 128;       // q rows per block
+constexpr int kBN = 128;       // keys per block
+constexpr int kTileBytes = 128 * kD * 2;   // 32 KB: one [128][128] bf16 tile as two 64-column slabs
+constexpr int kSlabBytes = 128 * 128;      // 16 KB: [128 rows][64 cols]
+constexpr int kAttnThreads = 192;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+struct AttnParams {
+  const int* cu_q;
+  const int* cu_k;
+  const int* blk_seg;   // per block: segment id or -1
+  const int* blk_row0;  // per block: first absolute row (q rows for fwd/dq, key rows for dkv)
+  int hq, hkv;
+  int causal, window;
+  float scale;          // softmax scale (1/sqrt(D))
+  int total_q, total_k;
+  // forward
+  __nv_bfloat16* O;     // [Tq][hq][D]
+  float* LSE;           // [hq][Tq]  (natural log)
+  // backward
+  const float* delta;   // [hq][Tq]
+  __nv_bfloat16* dQ;    // [Tq][hq][D]
+  __nv_bfloat16* dK;    // [Tk][hkv][D]
+  __nv_bfloat16* dV;    // rows with stride dv_stride
+  long long dv_stride;
+  int* status;
+};
+
+// 128-byte-swizzled address of (row, 16-byte chunk) inside a [128][64 bf16] slab.
+__device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk) { return row * 128 + ((chunk ^ (row & 7)) << 4); }
+
+// One 128x128x128 product out of 8 UMMA (K = 16 each).
+//   A_KMAJOR: A tile is [M rows][K] (slabs split K); otherwise [K rows][M] (slabs split M).
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ void mma_128x128x128(uint32_t d_tmem, uint32_t sa, uint32_t sb, bool accumulate) {
+  constexpr uint32_t idesc = umma_idesc_bf16(128, 128, A_MN ? 1 : 0, B_MN ? 1 : 0);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const uint64_t da = A_MN ? umma_smem_desc(sa + k * 2048, kSlabBytes, 1024)
+                             : umma_smem_desc(sa + (k >> 2) * kSlabBytes + (k & 3) * 32, 16, 1024);
+    const uint64_t db = B_MN ? umma_smem_desc(sb + k * 2048, kSlabBytes, 1024)
+                             : umma_smem_desc(sb + (k >> 2) * kSlabBytes + (k & 3) * 32, 16, 1024);
+    umma_bf16(d_tmem, da, db, idesc, (accumulate || k > 0) ? 1u : 0u);
+  }
+}
+
+__device__ __forceinline__ void load_tile(void* dst, const CUtensorMap* m, uint64_t* bar, int head, int row) {
+  tma_load_3d(dst, m, bar, 0, head, row);
+  tma_load_3d(static_cast<uint8_t*>(dst) + kSlabBytes, m, bar, 64, head, row);
+}
+
+struct SegInfo {
+  int q_begin, q_len, k_begin, k_len, off;
+};
+
+__device__ __forceinline__ SegInfo seg_info(const AttnParams& p, int seg) {
+  SegInfo s;
+  s.q_begin = p.cu_q[seg];
+  s.q_len = p.cu_q[seg + 1] - s.q_begin;
+  s.k_begin = p.cu_k[seg];
+  s.k_len = p.cu_k[seg + 1] - s.k_begin;
+  s.off = s.k_len - s.q_len;
+  return s;
+}
+
+// key-block range [jb0, jb1) visible to q rows [q0, q0+128) of a segment (relative indices)
+__device__ __forceinline__ void kv_range(const AttnParams& p, const SegInfo& s, int q0, int& jb0, int& jb1) {
+  int kend = s.k_len;
+  if (p.causal) kend = min(kend, q0 + kBM + s.off);
+  int kbeg = 0;
+  if (p.window > 0) kbeg = max(0, q0 + s.off - p.window + 1);
+  if (kend <= kbeg) { jb0 = 0; jb1 = 0; return; }
+  jb0 = kbeg / kBN;
+  jb1 = (kend + kBN - 1) / kBN;
+}
+
+__device__ __forceinline__ bool visible(const AttnParams& p, const SegInfo& s, int qi, int kk) {
+  bool ok = (kk < s.k_len) && (qi < s.q_len);
+  if (p.causal) ok = ok && (kk <= qi + s.off);
+  if (p.window > 0) ok = ok && (kk > qi + s.off - p.window);
+  return ok;
+}
+
+// =============================================================================== forward / dQ
+// MODE 0: forward.  MODE 1: dQ.
+template <int MODE>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_rowblock_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                     const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                     const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // fwd : Q | K0 V0 | K1 V1 | P0 | P1              = 32 + 128 + 64 = 224 KB
+  // dq  : Q | K0 V0 | K1 V1 | dO | dS              = 32 + 128 + 64 = 224 KB
+  uint8_t* sQ = smem;
+  uint8_t* sKV = smem + kTileBytes;
+  uint8_t* sX0 = sKV + 4 * kTileBytes;  // fwd: P0, dq: dO
+  uint8_t* sX1 = sX0 + kTileBytes;      // fwd: P1, dq: dS
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sX1 + kTileBytes);
+  uint64_t* q_full = bars;            // 1
+  uint64_t* kv_full = bars + 1;       // 2
+  uint64_t* kv_empty = bars + 3;      // 2
+  uint64_t* s_full = bars + 5;        // 2
+  uint64_t* p_full = bars + 7;        // 2
+  uint64_t* pv_full = bars + 9;       // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int head = blockIdx.x;
+  const int blk = blockIdx.y;
+  const int seg = p.blk_seg[blk];
+  if (seg < 0) return;  // uniform for the CTA, before any barrier or TMEM use
+  const SegInfo s = seg_info(p, seg);
+  const int q_abs0 = p.blk_row0[blk];
+  const int q0 = q_abs0 - s.q_begin;
+  const int kvh = head / (p.hq / p.hkv);
+  int jb0, jb1;
+  kv_range(p, s, q0, jb0, jb1);
+  const int nkb = jb1 - jb0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 128);
+      mbar_init(&pv_full[i], 1);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_q);
+    tma_prefetch_desc(&tmap_k);
+    tma_prefetch_desc(&tmap_v);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  // TMEM columns. fwd: S0 0, S1 128, PV0 256, PV1 384.   dq: S 0, dP 128, dQ 256.
+
+  if (warp == 0) {
+    if (lane == 0 && nkb > 0) {
+      const uint32_t qbytes = (MODE == 1) ? 2 * kTileBytes : kTileBytes;
+      mbar_arrive_expect_tx(q_full, qbytes);
+      load_tile(sQ, &tmap_q, q_full, head, q_abs0);
+      if (MODE == 1) load_tile(sX0, &tmap_do, q_full, head, q_abs0);
+      for (int j = 0; j < nkb && !*abort_flag; ++j) {
+        const int st = j & 1;
+        if (!mbar_wait(&kv_empty[st], ((j >> 1) & 1) ^ 1)) {
+          report_error(p.status, kErrProducerWait);
+          *abort_flag = 1;
+          break;
+        }
+        mbar_arrive_expect_tx(&kv_full[st], 2 * kTileBytes);
+        const int krow = s.k_begin + (jb0 + j) * kBN;
+        load_tile(sKV + st * 2 * kTileBytes, &tmap_k, &kv_full[st], kvh, krow);
+        load_tile(sKV + st * 2 * kTileBytes + kTileBytes, &tmap_v, &kv_full[st], kvh, krow);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && nkb > 0) {
+      bool ok = mbar_wait(q_full, 0);
+      if (!ok) { report_error(p.status, kErrMmaWaitFull); *abort_flag = 1; }
+      const uint32_t aQ = smem_u32(sQ);
+      if (MODE == 0) {
+        if (ok) {
+          ok = mbar_wait(&kv_full[0], 0);
+          if (ok) {
+            tc_fence_after();
+            mma_128x128x128<false, false>(tmem + 0, aQ, smem_u32(sKV), false);
+            umma_commit(&s_full[0]);
+          }
+        }
+        for (int j = 0; j < nkb && ok && !*abort_flag; ++j) {
+          const int st = j & 1;
+          if (j + 1 < nkb) {
+            const int sn = (j + 1) & 1;
+            ok = mbar_wait(&kv_full[sn], ((j + 1) >> 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            mma_128x128x128<false, false>(tmem + sn * 128, aQ, smem_u32(sKV + sn * 2 * kTileBytes), false);
+            umma_commit(&s_full[sn]);
+          }
+          ok = mbar_wait(&p_full[st], (j >> 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          // O_j = P_j V_j : A = P (K-major over keys), B = V ([keys][D] -> MN-major)
+          mma_128x128x128<false, true>(tmem + 256 + st * 128, smem_u32(st ? sX1 : sX0),
+                                       smem_u32(sKV + st * 2 * kTileBytes + kTileBytes), false);
+          umma_commit(&pv_full[st]);
+          umma_commit(&kv_empty[st]);
+        }
+      } else {
+        for (int j = 0; j < nkb && ok && !*abort_flag; ++j) {
+          const int st = j & 1;
+          ok = mbar_wait(&kv_full[st], (j >> 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t aK = smem_u32(sKV + st * 2 * kTileBytes), aV = aK + kTileBytes;
+          mma_128x128x128<false, false>(tmem + 0, aQ, aK, false);                // S  = Q K^T
+          mma_128x128x128<false, false>(tmem + 128, smem_u32(sX0), aV, false);   // dP = dO V^T
+          umma_commit(&s_full[0]);
+          ok = mbar_wait(&p_full[0], j & 1);
+          if (!ok) break;
+          tc_fence_after();
+          // dQ += dS K : A = dS (K-major over keys), B = K ([keys][D] -> MN-major)
+          mma_128x128x128<false, true>(tmem + 256, smem_u32(sX1), aK, j > 0);
+          umma_commit(&kv_empty[st]);
+          if (j == nkb - 1) umma_commit(&pv_full[0]);
+        }
+      }
+      if (!ok) { report_error(p.status, kErrMmaWaitFull); *abort_flag = 1; }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax / epilogue threads
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;           // row of the block owned by this thread
+    const int qi = q0 + r;                       // row inside the segment
+    const long long q_abs = static_cast<long long>(q_abs0) + r;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const float sl2 = p.scale * kLog2e;
+    if (MODE == 0) {
+      float acc[kD];
+#pragma unroll
+      for (int i = 0; i < kD; ++i) acc[i] = 0.f;
+      float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
+      bool ok = true;
+      for (int j = 0; j < nkb && ok && !*abort_flag; ++j) {
+        const int st = j & 1;
+        ok = mbar_wait(&s_full[st], (j >> 1) & 1);
+        if (!ok) break;
+        tc_fence_after();
+        const int kb = (jb0 + j) * kBN;
+        // a block needs element masks when it touches the diagonal, the window edge or the segment end
+        const bool need_mask = (kb + kBN > s.k_len) || (p.causal && kb + kBN - 1 > q0 + s.off) ||
+                               (p.window > 0 && kb <= q0 + kBM - 1 + s.off - p.window) || (q0 + kBM > s.q_len);
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem + lane_addr + st * 128 + c * 32, v);
+          tmem_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = __uint_as_float(v[i]);
+            if (need_mask && !visible(p, s, qi, kb + c * 32 + i)) x = -INFINITY;
+            mx = fmaxf(mx, x);
+          }
+        }
+        const float m_new = fmaxf(m, mx * sl2);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_use);
+        float rowsum = 0.f;
+        uint8_t* sP = st ? sX1 : sX0;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem + lane_addr + st * 128 + c * 32, v);
+          tmem_wait_ld();
+          uint32_t packed[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float x0 = __uint_as_float(v[i]), x1 = __uint_as_float(v[i + 1]);
+            if (need_mask) {
+              if (!visible(p, s, qi, kb + c * 32 + i)) x0 = -INFINITY;
+              if (!visible(p, s, qi, kb + c * 32 + i + 1)) x1 = -INFINITY;
+            }
+            const float p0 = exp2f(x0 * sl2 - m_use), p1 = exp2f(x1 * sl2 - m_use);
+            rowsum += p0 + p1;
+            packed[i >> 1] = pack_bf16(p0, p1);
+          }
+          // 32 keys = 4 chunks of 16 B; slab = (c*32)/64, chunk index inside the 128 B row
+          uint8_t* slab = sP + (c >> 1) * kSlabBytes;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const uint32_t chunk = (c & 1) * 4 + q4;
+            *reinterpret_cast<uint4*>(slab + swz(r, chunk)) =
+                make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+          }
+        }
+        l = l * alpha + rowsum;
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(&p_full[st]);
+        if (j > 0) {
+          const int sp = (j - 1) & 1;
+          ok = mbar_wait(&pv_full[sp], ((j - 1) >> 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem + lane_addr + 256 + sp * 128 + c * 32, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[c * 32 + i] = acc[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
+          }
+        }
+        alpha_prev = alpha;
+        m = m_new;
+      }
+      if (ok && nkb > 0 && !*abort_flag) {
+        const int sp = (nkb - 1) & 1;
+        ok = mbar_wait(&pv_full[sp], ((nkb - 1) >> 1) & 1);
+        if (ok) {
+          tc_fence_after();
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            tmem_ld_32x32(tmem + lane_addr + 256 + sp * 128 + c * 32, v);
+            tmem_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) acc[c * 32 + i] = acc[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
+          }
+        }
+      }
+      if (!ok) { report_error(p.status, kErrSoftmaxWait); *abort_flag = 1; }
+      if (qi < s.q_len && q_abs < p.total_q) {
+        const float inv = (l > 0.f) ? 1.f / l : 0.f;
+        __nv_bfloat16* orow = p.O + (q_abs * p.hq + head) * kD;
+#pragma unroll
+        for (int i = 0; i < kD; i += 8) {
+          uint4 o;
+          o.x = pack_bf16(acc[i] * inv, acc[i + 1] * inv);
+          o.y = pack_bf16(acc[i + 2] * inv, acc[i + 3] * inv);
+          o.z = pack_bf16(acc[i + 4] * inv, acc[i + 5] * inv);
+          o.w = pack_bf16(acc[i + 6] * inv, acc[i + 7] * inv);
+          *reinterpret_cast<uint4*>(orow + i) = o;
+        }
+        p.LSE[static_cast<long long>(head) * p.total_q + q_abs] = (l > 0.f) ? (m * kLn2 + logf(l)) : -INFINITY;
+      }
+    } else {
+      // dQ mode
+      const bool row_ok = (qi < s.q_len) && (q_abs < p.total_q);
+      const float lse2 = row_ok ? p.LSE[static_cast<long long>(head) * p.total_q + q_abs] * kLog2e : 0.f;
+      const float dl = row_ok ? p.delta[static_cast<long long>(head) * p.total_q + q_abs] : 0.f;
+      bool ok = true;
+      for (int j = 0; j < nkb && ok && !*abort_flag; ++j) {
+        ok = mbar_wait(&s_full[0], j & 1);
+        if (!ok) break;
+        tc_fence_after();
+        const int kb = (jb0 + j) * kBN;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t sv[32], dv[32];
+          tmem_ld_32x32(tmem + lane_addr + c * 32, sv);
+          tmem_ld_32x32(tmem + lane_addr + 128 + c * 32, dv);
+          tmem_wait_ld();
+          uint32_t packed[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            float d0 = 0.f, d1 = 0.f;
+            if (row_ok && visible(p, s, qi, kb + c * 32 + i)) {
+              const float pr = exp2f(__uint_as_float(sv[i]) * sl2 - lse2);
+              d0 = pr * (__uint_as_float(dv[i]) - dl) * p.scale;
+            }
+            if (row_ok && visible(p, s, qi, kb + c * 32 + i + 1)) {
+              const float pr = exp2f(__uint_as_float(sv[i + 1]) * sl2 - lse2);
+              d1 = pr * (__uint_as_float(dv[i + 1]) - dl) * p.scale;
+            }
+            packed[i >> 1] = pack_bf16(d0, d1);
+          }
+          uint8_t* slab = sX1 + (c >> 1) * kSlabBytes;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const uint32_t chunk = (c & 1) * 4 + q4;
+            *reinterpret_cast<uint4*>(slab + swz(r, chunk)) =
+                make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+          }
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(&p_full[0]);
+      }
+      if (ok && nkb > 0 && !*abort_flag) ok = mbar_wait(&pv_full[0], 0);
+      if (!ok) { report_error(p.status, kErrSoftmaxWait); *abort_flag = 1; }
+      if (nkb > 0) tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        if (nkb > 0 && ok) {
+          tmem_ld_32x32(tmem + lane_addr + 256 + c * 32, v);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        if (row_ok) {
+          __nv_bfloat16* drow = p.dQ + (q_abs * p.hq + head) * kD + c * 32;
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+            o.y = pack_bf16(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+            o.z = pack_bf16(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+            o.w = pack_bf16(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+            *reinterpret_cast<uint4*>(drow + i) = o;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  if (*abort_flag) drain_delay();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// =============================================================================== dK / dV
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                    const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = smem;
+  uint8_t* sV = sK + kTileBytes;
+  uint8_t* sQ = sV + kTileBytes;
+  uint8_t* sdO = sQ + kTileBytes;
+  uint8_t* sP = sdO + kTileBytes;
+  uint8_t* sdS = sP + kTileBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sdS + kTileBytes);
+  uint64_t* kv_full = bars;       // K,V tile landed
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = bars + 2;
+  uint64_t* sdp_full = bars + 3;  // S and dP in TMEM
+  uint64_t* pds_full = bars + 4;  // P and dS in smem (128 arrivals)
+  uint64_t* acc_full = bars + 5;  // all MMAs done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = blockIdx.x;
+  const int blk = blockIdx.y;
+  const int seg = p.blk_seg[blk];
+  if (seg < 0) return;
+  const SegInfo s = seg_info(p, seg);
+  const int k_abs0 = p.blk_row0[blk];
+  const int k0 = k_abs0 - s.k_begin;
+  const int group = p.hq / p.hkv;
+  // q blocks that can see keys [k0, k0+128): causal -> q >= k0 - off ; window -> q <= k0+127 - off + window - 1
+  int qlo = 0, qhi = s.q_len;
+  if (p.causal) qlo = max(0, k0 - s.off);
+  if (p.window > 0) qhi = min(s.q_len, k0 + kBN - 1 - s.off + p.window);
+  const int ib0 = qlo / kBM;
+  const int ib1 = (qhi > qlo) ? (qhi + kBM - 1) / kBM : ib0;
+  const int nqb = ib1 - ib0;
+  const int iters = nqb * group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(qdo_full, 1);
+    mbar_init(qdo_empty, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_full, 128);
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;  // S 0, dP 128, dV 256, dK 384
+
+  if (warp == 0) {
+    if (lane == 0 && iters > 0) {
+      mbar_arrive_expect_tx(kv_full, 2 * kTileBytes);
+      load_tile(sK, &tmap_k, kv_full, kvh, k_abs0);
+      load_tile(sV, &tmap_v, kv_full, kvh, k_abs0);
+      for (int it = 0; it < iters && !*abort_flag; ++it) {
+        if (!mbar_wait(qdo_empty, (it & 1) ^ 1)) {
+          report_error(p.status, kErrProducerWait);
+          *abort_flag = 1;
+          break;
+        }
+        const int h = kvh * group + it / nqb;
+        const int qrow = s.q_begin + (ib0 + it % nqb) * kBM;
+        mbar_arrive_expect_tx(qdo_full, 2 * kTileBytes);
+        load_tile(sQ, &tmap_q, qdo_full, h, qrow);
+        load_tile(sdO, &tmap_do, qdo_full, h, qrow);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && iters > 0) {
+      bool ok = mbar_wait(kv_full, 0);
+      for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
+        ok = mbar_wait(qdo_full, it & 1);
+        if (!ok) break;
+        tc_fence_after();
+        mma_128x128x128<false, false>(tmem + 0, smem_u32(sQ), smem_u32(sK), false);     // S  = Q K^T
+        mma_128x128x128<false, false>(tmem + 128, smem_u32(sdO), smem_u32(sV), false);  // dP = dO V^T
+        umma_commit(sdp_full);
+        ok = mbar_wait(pds_full, it & 1);
+        if (!ok) break;
+        tc_fence_after();
+        // dV += P^T dO : A = P stored [q][keys] read as [K = q][M = keys]; B = dO stored [q][D]
+        mma_128x128x128<true, true>(tmem + 256, smem_u32(sP), smem_u32(sdO), it > 0);
+        // dK += dS^T Q
+        mma_128x128x128<true, true>(tmem + 384, smem_u32(sdS), smem_u32(sQ), it > 0);
+        umma_commit(qdo_empty);
+      }
+      if (ok) umma_commit(acc_full);
+      if (!ok) { report_error(p.status, kErrMmaWaitFull); *abort_flag = 1; }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const float sl2 = p.scale * kLog2e;
+    bool ok = true;
+    for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
+      const int h = kvh * group + it / nqb;
+      const int q0 = (ib0 + it % nqb) * kBM;
+      const int qi = q0 + r;
+      const long long q_abs = static_cast<long long>(s.q_begin) + qi;
+      const bool row_ok = (qi < s.q_len) && (q_abs < p.total_q);
+      const float lse2 = row_ok ? p.LSE[static_cast<long long>(h) * p.total_q + q_abs] * kLog2e : 0.f;
+      const float dl = row_ok ? p.delta[static_cast<long long>(h) * p.total_q + q_abs] : 0.f;
+      ok = mbar_wait(sdp_full, it & 1);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t sv[32], dv[32];
+        tmem_ld_32x32(tmem + lane_addr + c * 32, sv);
+        tmem_ld_32x32(tmem + lane_addr + 128 + c * 32, dv);
+        tmem_wait_ld();
+        uint32_t pp[16], dd[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
+          if (row_ok && visible(p, s, qi, k0 + c * 32 + i)) {
+            p0 = exp2f(__uint_as_float(sv[i]) * sl2 - lse2);
+            d0 = p0 * (__uint_as_float(dv[i]) - dl) * p.scale;
+          }
+          if (row_ok && visible(p, s, qi, k0 + c * 32 + i + 1)) {
+            p1 = exp2f(__uint_as_float(sv[i + 1]) * sl2 - lse2);
+            d1 = p1 * (__uint_as_float(dv[i + 1]) - dl) * p.scale;
+          }
+          pp[i >> 1] = pack_bf16(p0, p1);
+          dd[i >> 1] = pack_bf16(d0, d1);
+        }
+        const uint32_t slab_off = (c >> 1) * kSlabBytes;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const uint32_t a = slab_off + swz(r, (c & 1) * 4 + q4);
+          *reinterpret_cast<uint4*>(sP + a) = make_uint4(pp[q4 * 4], pp[q4 * 4 + 1], pp[q4 * 4 + 2], pp[q4 * 4 + 3]);
+          *reinterpret_cast<uint4*>(sdS + a) = make_uint4(dd[q4 * 4], dd[q4 * 4 + 1], dd[q4 * 4 + 2], dd[q4 * 4 + 3]);
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(pds_full);
+    }
+    if (ok && iters > 0 && !*abort_flag) ok = mbar_wait(acc_full, 0);
+    if (!ok) { report_error(p.status, kErrSoftmaxWait); *abort_flag = 1; }
+    if (iters > 0) tc_fence_after();
+    // thread r owns key row r of this block
+    const int kk = k0 + r;
+    const long long k_abs = static_cast<long long>(k_abs0) + r;
+    const bool key_ok = (kk < s.k_len) && (k_abs < p.total_k);
+#pragma unroll 1
+    for (int which = 0; which < 2; ++which) {
+      __nv_bfloat16* base = which == 0 ? p.dV + k_abs * p.dv_stride + static_cast<long long>(kvh) * kD
+                                       : p.dK + (k_abs * p.hkv + kvh) * kD;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        if (iters > 0 && ok) {
+          tmem_ld_32x32(tmem + lane_addr + 256 + which * 128 + c * 32, v);
+          tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = 0u;
+        }
+        if (key_ok) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+            o.y = pack_bf16(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+            o.z = pack_bf16(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+            o.w = pack_bf16(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+            *reinterpret_cast<uint4*>(base + c * 32 + i) = o;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  if (*abort_flag) drain_delay();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// delta[h][t] = sum_d dO[t][h][d] * O[t][h][d]; one warp per (t, h)
+__global__ void __launch_bounds__(256)
+attn_delta_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO, float* __restrict__ delta,
+                  int T, int hq) {
+  const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (wid >= static_cast<long long>(T) * hq) return;
+  const long long t = wid / hq;
+  const int h = static_cast<int>(wid % hq);
+  const uint2 a = *reinterpret_cast<const uint2*>(O + wid * kD + lane * 4);
+  const uint2 b = *reinterpret_cast<const uint2*>(dO + wid * kD + lane * 4);
+  float sum = bf16_lo(a.x) * bf16_lo(b.x) + bf16_hi(a.x) * bf16_hi(b.x) + bf16_lo(a.y) * bf16_lo(b.y) +
+              bf16_hi(a.y) * bf16_hi(b.y);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane == 0) delta[static_cast<long long>(h) * T + t] = sum;
+}
+
+constexpr int kAttnSmem = 7 * kTileBytes + 1024 + 256;      // fwd / dq
+constexpr int kAttnSmemDkv = 6 * kTileBytes + 1024 + 256;   // dkv
+
+static int make_head_map(CUtensorMap* m, const void* base, int heads, long long rows, long long row_stride_elems) {
+  // dims: D (inner), heads, rows; a box is 64 columns of one head for 128 rows
+  return make_tmap_3d_bf16(m, base, kD, heads, rows, static_cast<uint64_t>(kD) * 2,
+                           static_cast<uint64_t>(row_stride_elems) * 2, 64, 1, 128, 1);
+}
+
+}  // namespace stb
+
+using namespace stb;
+
+// q [Tq][hq][D] with row stride q_stride (elements); k, v [Tk][hkv][D] with row strides k_stride, v_stride.
+// blk_seg / blk_row0: schedule of q blocks (num_blocks entries, seg < 0 = unused).
+extern "C" int stb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_q,
+                            const int* cu_k, const int* blk_seg, const int* blk_row0, int num_blocks, int total_q,
+                            int total_k, int hq, int hkv, int head_dim, long long q_stride, long long k_stride,
+                            long long v_stride, int causal, int window, float scale, int* status, cudaStream_t st) {
+  if (num_blocks <= 0 || total_q <= 0) return 0;
+  if (head_dim != kD || hq % hkv) return -kErrBadArgument;
+  CUtensorMap tq, tk, tv;
+  int r;
+  if ((r = make_head_map(&tq, q, hq, total_q, q_stride))) return r;
+  if ((r = make_head_map(&tk, k, hkv, total_k, k_stride))) return r;
+  if ((r = make_head_map(&tv, v, hkv, total_k, v_stride))) return r;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_rowblock_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
+    if (e != cudaSuccess) return -static_cast<int>(e);
+    configured = true;
+  }
+  AttnParams p{};
+  p.cu_q = cu_q; p.cu_k = cu_k; p.blk_seg = blk_seg; p.blk_row0 = blk_row0;
+  p.hq = hq; p.hkv = hkv; p.causal = causal; p.window = window; p.scale = scale;
+  p.total_q = total_q; p.total_k = total_k;
+  p.O = static_cast<__nv_bfloat16*>(o); p.LSE = lse; p.status = status;
+  attn_rowblock_kernel<0><<<dim3(hq, num_blocks), kAttnThreads, kAttnSmem, st>>>(tq, tk, tv, tq, p);
+  return -static_cast<int>(cudaGetLastError());
+}
+
+// Backward. dq [Tq][hq][D], dk [Tk][hkv][D] contiguous; dv rows with stride dv_stride.
+// q_blk_*: schedule over q blocks; k_blk_*: schedule over key blocks. delta: scratch [hq][Tq] floats.
+extern "C" int stb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                            const float* lse, float* delta, void* dq, void* dk, void* dv, const int* cu_q,
+                            const int* cu_k, const int* q_blk_seg, const int* q_blk_row0, int num_q_blocks,
+                            const int* k_blk_seg, const int* k_blk_row0, int num_k_blocks, int total_q, int total_k,
+                            int hq, int hkv, int head_dim, long long q_stride, long long k_stride, long long v_stride,
+                            long long dv_stride, int causal, int window, float scale, int* status, cudaStream_t st) {
+  if (total_q <= 0 || total_k <= 0) return 0;
+  if (head_dim != kD || hq % hkv) return -kErrBadArgument;
+  CUtensorMap tq, tk, tv, tdo;
+  int r;
+  if ((r = make_head_map(&tq, q, hq, total_q, q_stride))) return r;
+  if ((r = make_head_map(&tk, k, hkv, total_k, k_stride))) return r;
+  if ((r = make_head_map(&tv, v, hkv, total_k, v_stride))) return r;
+  if ((r = make_head_map(&tdo, d_o, hq, total_q, static_cast<long long>(hq) * kD))) return r;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_rowblock_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem);
+    if (e != cudaSuccess) return -static_cast<int>(e);
+    e = cudaFuncSetAttribute(attn_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmemDkv);
+    if (e != cudaSuccess) return -static_cast<int>(e);
+    configured = true;
+  }
+  const long long warps = static_cast<long long>(total_q) * hq;
+  attn_delta_kernel<<<static_cast<unsigned>((warps + 7) / 8), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(d_o), delta, total_q, hq);
+  AttnParams p{};
+  p.cu_q = cu_q; p.cu_k = cu_k;
+  p.hq = hq; p.hkv = hkv; p.causal = causal; p.window = window; p.scale = scale;
+  p.total_q = total_q; p.total_k = total_k;
+  p.LSE = const_cast<float*>(lse); p.delta = delta;
+  p.dQ = static_cast<__nv_bfloat16*>(dq); p.dK = static_cast<__nv_bfloat16*>(dk);
+  p.dV = static_cast<__nv_bfloat16*>(dv); p.dv_stride = dv_stride; p.status = status;
+  p.blk_seg = q_blk_seg; p.blk_row0 = q_blk_row0;
+  if (num_q_blocks > 0)
+    attn_rowblock_kernel<1><<<dim3(hq, num_q_blocks), kAttnThreads, kAttnSmem, st>>>(tq, tk, tv, tdo, p);
+  p.blk_seg = k_blk_seg; p.blk_row0 = k_blk_row0;
+  if (num_k_blocks > 0)
+    attn_bwd_dkv_kernel<<<dim3(hkv, num_k_blocks), kAttnThreads, kAttnSmemDkv, st>>>(tq, tk, tv, tdo, p);
+  return -static_cast<int>(cudaGetLastError());
+}

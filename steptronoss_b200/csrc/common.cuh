@@ -11,7 +11,8 @@
 
 namespace stb {
 
-constexpr uint32_t kSpinLimit = 1u << 24;  // polls of mbarrier.try_wait (each suspends up to ~1 us)
+constexpr uint32_t kSpinLimit = 1u << 26;          // hard cap on polls of mbarrier.try_wait
+constexpr uint64_t kWaitBudgetNs = 2000000000ull;  // 2 s of device wall time per wait
 
 enum ErrCode : int {
   kErrNone = 0,
@@ -63,10 +64,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait. Returns false when the phase did not complete within the poll budget.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit = kSpinLimit) {
-  for (uint32_t i = 0; i < limit; ++i) {
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait. Returns false when the phase did not complete within kWaitBudgetNs (wall time on the
+// device, checked every 256 polls) or within kSpinLimit polls, whichever comes first.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t i = 1; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 0 && global_timer_ns() - t0 > kWaitBudgetNs) return false;
   }
   return false;
 }

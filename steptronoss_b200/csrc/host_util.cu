@@ -20,8 +20,20 @@ EncodeTiledFn get_encode_tiled() {
   return fn;
 }
 
+// The tensor-map encoder is a driver call and needs a current context on the calling thread; autograd
+// runs backward on worker threads that have only selected a device through the runtime API, which binds
+// the primary context lazily.  One cheap runtime call per thread makes the binding happen.
+static void ensure_context_on_this_thread() {
+  static thread_local bool ready = false;
+  if (!ready) {
+    cudaFree(nullptr);
+    ready = true;
+  }
+}
+
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t pitch_bytes,
                       uint32_t box0, uint32_t box1, int swizzle128) {
+  ensure_context_on_this_thread();
   EncodeTiledFn enc = get_encode_tiled();
   if (enc == nullptr) return -1;
   cuuint64_t dims[2] = {d0, d1};
@@ -36,6 +48,7 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t 
 
 int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1,
                       uint64_t pitch2, uint32_t box0, uint32_t box1, uint32_t box2, int swizzle128) {
+  ensure_context_on_this_thread();
   EncodeTiledFn enc = get_encode_tiled();
   if (enc == nullptr) return -1;
   cuuint64_t dims[3] = {d0, d1, d2};

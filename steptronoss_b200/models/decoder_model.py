@@ -202,3 +202,17 @@ class _null:
 
     def __exit__(self, *a):
         return False
+
+
+def _moe_types():
+    from .common.moe_block import MoEConfig, MoEFeedForwardConfig
+
+    return MoEConfig, MoEFeedForwardConfig
+
+
+class MoEDecoderLLMConfig(DecoderLLMConfig):
+    """Decoder whose feed-forward blocks are routed experts on the layers of ``moe_cfg.moe_layer_list``
+    (dense SwiGLU elsewhere).  After every optimizer step the aux-loss-free router bias is updated."""
+
+    moe_cfg = _moe_types()[0]
+    ffn_cfg = _moe_types()[1]

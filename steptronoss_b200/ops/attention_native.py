@@ -1,0 +1,127 @@
+"""Autograd wrapper of the tcgen05 flash-attention kernels (``csrc/attention_sm100.cu``).
+
+The block schedule (which 128-row block belongs to which packed segment) is computed on the device
+from ``cu_seqlens`` with a handful of tiny tensor ops and cached per ``cu_seqlens`` tensor, so all
+layers of a micro-batch share it and nothing synchronises with the host.
+"""
+from __future__ import annotations
+
+import math
+import weakref
+
+import torch
+
+from . import native
+from .gemm import count_launch
+
+native._SIGNATURES.update({
+    "stb_attn_fwd": [native.P] * 9 + [native.I] * 6 + [native.L] * 3 + [native.I, native.I, native.F, native.P, native.P],
+    "stb_attn_bwd": [native.P] * 14 + [native.I] + [native.P] * 2 + [native.I] * 6 + [native.L] * 4
+                    + [native.I, native.I, native.F, native.P, native.P],
+})
+
+_BLOCK = 128
+_SCHED_CACHE: dict = {}
+
+
+def _schedule(cu: torch.Tensor, total_rows: int):
+    """(blk_seg, blk_row0, num_blocks) for 128-row blocks that never straddle two segments."""
+    key = (cu.data_ptr(), cu._version, total_rows, cu.numel())
+    hit = _SCHED_CACHE.get(key)
+    if hit is not None and hit[0]() is cu:
+        return hit[1]
+    nseg = cu.numel() - 1
+    max_blocks = (total_rows + _BLOCK - 1) // _BLOCK + nseg
+    cu64 = cu.to(torch.int64)
+    lens = cu64[1:] - cu64[:-1]
+    nblk = (lens + _BLOCK - 1) // _BLOCK
+    ends = torch.cumsum(nblk, 0)
+    starts = ends - nblk
+    b = torch.arange(max_blocks, device=cu.device, dtype=torch.int64)
+    seg = torch.searchsorted(ends, b, right=True)
+    valid = seg < nseg
+    seg_c = seg.clamp(max=nseg - 1)
+    row0 = cu64[:-1][seg_c] + (b - starts[seg_c]) * _BLOCK
+    blk_seg = torch.where(valid, seg, torch.full_like(seg, -1)).to(torch.int32)
+    blk_row0 = torch.where(valid, row0, torch.zeros_like(row0)).to(torch.int32)
+    out = (blk_seg, blk_row0, max_blocks)
+    if len(_SCHED_CACHE) > 64:
+        _SCHED_CACHE.clear()
+    _SCHED_CACHE[key] = (weakref.ref(cu), out)
+    return out
+
+
+def _default_cu(total: int, device) -> torch.Tensor:
+    key = ("default", total, str(device))
+    hit = _SCHED_CACHE.get(key)
+    if hit is None:
+        t = torch.tensor([0, total], dtype=torch.int32, device=device)
+        _SCHED_CACHE[key] = (lambda: None, t)
+        return t
+    return hit[1]
+
+
+class _FlashAttnFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, cu_q, cu_k, causal, window, scale):
+        lib = native.load()
+        Tq, hq, D = q.shape
+        Tk, hkv, _ = k.shape
+        if q.stride(2) != 1 or q.stride(1) != D:
+            q = q.contiguous()
+        if k.stride(2) != 1 or k.stride(1) != D:
+            k = k.contiguous()
+        if v.stride(2) != 1 or v.stride(1) != D:
+            v = v.contiguous()
+        o = torch.empty((Tq, hq, D), dtype=q.dtype, device=q.device)
+        lse = torch.empty((hq, Tq), dtype=torch.float32, device=q.device)
+        qs, qr, nq = _schedule(cu_q, Tq)
+        rc = lib.stb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), cu_q.data_ptr(),
+                              cu_k.data_ptr(), qs.data_ptr(), qr.data_ptr(), nq, Tq, Tk, hq, hkv, D, q.stride(0),
+                              k.stride(0), v.stride(0), int(causal), int(window), float(scale),
+                              native.status_word(q.device).data_ptr(), native.stream())
+        native.check(rc, "attention forward")
+        count_launch()
+        ctx.save_for_backward(q, k, v, o, lse, cu_q, cu_k)
+        ctx.cfg = (causal, window, scale)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        lib = native.load()
+        q, k, v, o, lse, cu_q, cu_k = ctx.saved_tensors
+        causal, window, scale = ctx.cfg
+        Tq, hq, D = q.shape
+        Tk, hkv, _ = k.shape
+        do = do.contiguous()
+        dq = torch.empty((Tq, hq, D), dtype=q.dtype, device=q.device)
+        dk = torch.empty((Tk, hkv, D), dtype=q.dtype, device=q.device)
+        dv = torch.empty((Tk, hkv, D), dtype=q.dtype, device=q.device)
+        delta = torch.empty((hq, Tq), dtype=torch.float32, device=q.device)
+        qs, qr, nq = _schedule(cu_q, Tq)
+        ks, kr, nk = _schedule(cu_k, Tk)
+        rc = lib.stb_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                              delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu_q.data_ptr(),
+                              cu_k.data_ptr(), qs.data_ptr(), qr.data_ptr(), nq, ks.data_ptr(), kr.data_ptr(), nk, Tq, Tk,
+                              hq, hkv, D, q.stride(0), k.stride(0), v.stride(0), dv.stride(0), int(causal), int(window),
+                              float(scale), native.status_word(q.device).data_ptr(), native.stream())
+        native.check(rc, "attention backward")
+        count_launch(3)
+        return dq, dk, dv, None, None, None, None, None
+
+
+def flash_attention(q, k, v, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen=None, causal=True, window=0, scale=None):
+    """q ``[Tq,hq,128]``, k/v ``[Tk,hkv,128]`` (v may be a strided view) -> ``[Tq,hq,128]``."""
+    Tq, hq, D = q.shape
+    if D != 128 or q.dtype != torch.bfloat16:
+        raise NotImplementedError("native attention: head_dim 128, bf16")
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if cu_seqlens_q is None:
+        cu_seqlens_q = _default_cu(Tq, q.device)
+    if cu_seqlens_k is None:
+        cu_seqlens_k = cu_seqlens_q if k.shape[0] == Tq else _default_cu(k.shape[0], q.device)
+    if cu_seqlens_q.dtype != torch.int32:
+        cu_seqlens_q = cu_seqlens_q.to(torch.int32)
+    if cu_seqlens_k.dtype != torch.int32:
+        cu_seqlens_k = cu_seqlens_k.to(torch.int32)
+    return _FlashAttnFn.apply(q, k, v, cu_seqlens_q, cu_seqlens_k, bool(causal), int(window or 0), float(scale))
