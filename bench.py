@@ -148,6 +148,8 @@ def run_ours(args):
         # one GPU holds 18 bytes/parameter of static state (147 GB): recompute whole blocks
         rec = "full" if par["tp"] * par["pp"] == 1 else "none"
     exp.model_cfg.recompute = True if rec == "full" else ([] if rec == "none" else rec.split(","))
+    exp.resource_cfg.gpu = world
+    os.environ.setdefault("WORLD_SIZE", str(world))
     exp.sanity_check()
     trainer = exp.trainer_cfg.get_trainer_cls()(exp=exp)
     trainer.before_train()

@@ -105,6 +105,13 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* d, const void* s
                "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
                : "memory");
 }
+// C[tile] += smem tile (fp32 add performed by the TMA unit in L2)
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* d, const void* smem_src, int c0, int c1) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(d)),
+               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
+               : "memory");
+}
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void tma_store_wait_read() {
@@ -223,6 +230,9 @@ EncodeTiledFn get_encode_tiled();
 // rank-2 bf16 tensor map: inner extent `d0` (contiguous), outer `d1` with row pitch `pitch_bytes`.
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t pitch_bytes,
                       uint32_t box0, uint32_t box1, int swizzle128);
+// generic rank-2 map; elem_bytes 2 = bf16, 4 = fp32
+int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d0, uint64_t d1, uint64_t pitch_bytes,
+                 uint32_t box0, uint32_t box1, int swizzle128);
 int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1,
                       uint64_t pitch2, uint32_t box0, uint32_t box1, uint32_t box2, int swizzle128);
 int sm_count();

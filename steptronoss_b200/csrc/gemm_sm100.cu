@@ -44,12 +44,13 @@ struct GemmParams {
 
 template <int BLOCK_N>
 struct GemmSmem {
-  static constexpr int kStages = (BLOCK_N == 256) ? 4 : 6;
+  static constexpr int kStages = (BLOCK_N == 256) ? 4 : 5;
   static constexpr int kABytes = kBlockM * kBlockK * 2;
   static constexpr int kBBytes = BLOCK_N * kBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+  static constexpr int kStoreBytes = 4 * 2 * 4096;  // per epilogue warp: two 32-row x 128-byte staging tiles
+  static constexpr int kTotal = kStages * kStageBytes + kStoreBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
 struct TileCoord {
@@ -93,12 +94,13 @@ __device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int n
 template <int BLOCK_N, bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 void* __restrict__ Cptr, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_c, void* __restrict__ Cptr, const GemmParams p) {
   using S = GemmSmem<BLOCK_N>;
   constexpr int kStages = S::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes);
+  uint8_t* store_stage = smem + kStages * S::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(store_stage + S::kStoreBytes);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tmem_full = empty_bar + kStages;
   uint64_t* tmem_empty = tmem_full + 2;
@@ -230,6 +232,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32)
     uint32_t local_tile = 0;
+    uint32_t store_count = 0;
     for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
       TileCoord t;
       decode_tile(p, tile, num_m, num_n, t);
@@ -242,10 +245,70 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         break;
       }
       tc_fence_after();
-      const int row = t.m_tile * kBlockM + quarter * 32 + lane;
       const int n0 = t.n_tile * BLOCK_N;
-      const bool row_ok = row < p.M;
       const bool zero_acc = (t.k_blocks == 0);
+      // rows of this warp inside C (grouped reduction: every group owns M consecutive rows of the map)
+      const int row0 = t.m_tile * kBlockM + quarter * 32 + (p.mode == 2 ? t.group * p.M : 0);
+      constexpr bool kTmaStore = OUT_F32 || !ACCUM;  // bf16 read-modify-write keeps the direct path
+      if constexpr (kTmaStore) {
+        // Stage 32 rows x 128 bytes (32 fp32 or 64 bf16 columns) in shared memory with the 128-byte
+        // swizzle, then one TMA store (or TMA fp32 reduce-add for beta = 1) per staged tile.  The TMA
+        // unit clips rows and columns outside C, so there are no edge guards here.
+        constexpr int kColsPerStore = OUT_F32 ? 32 : 64;
+        uint8_t* my_stage = store_stage + (warp - 2) * 8192;
+#pragma unroll 1
+        for (int c = 0; c < BLOCK_N / kColsPerStore; ++c) {
+          uint32_t v[OUT_F32 ? 32 : 64];
+          {
+            uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&v[0]);
+            tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BLOCK_N + c * kColsPerStore, lo);
+            if constexpr (!OUT_F32) {
+              uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&v[32]);
+              tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BLOCK_N + c * 64 + 32, hi);
+            }
+            tmem_wait_ld();
+          }
+          const int col0 = n0 + c * kColsPerStore;
+          if (col0 >= p.N) continue;  // warp-uniform
+          uint8_t* buf = my_stage + (store_count & 1) * 4096;
+          if (store_count >= 2) {
+            if (lane == 0) tma_store_wait_read<1>();
+            __syncwarp();
+          }
+          uint4 chunks[8];
+          if constexpr (OUT_F32) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              chunks[j].x = __float_as_uint(zero_acc ? 0.f : __uint_as_float(v[4 * j]) * p.alpha);
+              chunks[j].y = __float_as_uint(zero_acc ? 0.f : __uint_as_float(v[4 * j + 1]) * p.alpha);
+              chunks[j].z = __float_as_uint(zero_acc ? 0.f : __uint_as_float(v[4 * j + 2]) * p.alpha);
+              chunks[j].w = __float_as_uint(zero_acc ? 0.f : __uint_as_float(v[4 * j + 3]) * p.alpha);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float f[8];
+#pragma unroll
+              for (int q = 0; q < 8; ++q) f[q] = zero_acc ? 0.f : __uint_as_float(v[8 * j + q]) * p.alpha;
+              chunks[j].x = pack_bf16(f[0], f[1]); chunks[j].y = pack_bf16(f[2], f[3]);
+              chunks[j].z = pack_bf16(f[4], f[5]); chunks[j].w = pack_bf16(f[6], f[7]);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = chunks[j];
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if constexpr (ACCUM) tma_reduce_add_2d(&tmap_c, buf, col0, row0);
+            else tma_store_2d(&tmap_c, buf, col0, row0);
+            tma_store_commit();
+          }
+          ++store_count;
+        }
+      } else {
+      const int row = t.m_tile * kBlockM + quarter * 32 + lane;
+      const bool row_ok = row < p.M;
       const long long cbase =
           (p.mode == 2 ? static_cast<long long>(t.group) * p.group_c_stride : 0) + static_cast<long long>(row) * p.ldc;
 #pragma unroll 1
@@ -255,49 +318,30 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tmem_wait_ld();
         const int col0 = n0 + c * 32;
         if (!row_ok || col0 >= p.N) continue;
-        if constexpr (OUT_F32) {
-          float* crow = reinterpret_cast<float*>(Cptr) + cbase + col0;
+        __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(Cptr) + cbase + col0;
 #pragma unroll
-          for (int j = 0; j < 32; j += 4) {
-            if (col0 + j < p.N) {  // N is a multiple of 8
-              float4 o;
-              o.x = zero_acc ? 0.f : __uint_as_float(v[j]) * p.alpha;
-              o.y = zero_acc ? 0.f : __uint_as_float(v[j + 1]) * p.alpha;
-              o.z = zero_acc ? 0.f : __uint_as_float(v[j + 2]) * p.alpha;
-              o.w = zero_acc ? 0.f : __uint_as_float(v[j + 3]) * p.alpha;
-              if constexpr (ACCUM) {
-                const float4 old = *reinterpret_cast<const float4*>(crow + j);
-                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-              }
-              *reinterpret_cast<float4*>(crow + j) = o;
-            }
-          }
-        } else {
-          __nv_bfloat16* crow = reinterpret_cast<__nv_bfloat16*>(Cptr) + cbase + col0;
+        for (int j = 0; j < 32; j += 8) {
+          if (col0 + j < p.N) {
+            float f[8];
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            if (col0 + j < p.N) {
-              float f[8];
-#pragma unroll
-              for (int q = 0; q < 8; ++q) f[q] = zero_acc ? 0.f : __uint_as_float(v[j + q]) * p.alpha;
-              if constexpr (ACCUM) {
-                const uint4 old = *reinterpret_cast<const uint4*>(crow + j);
-                f[0] += bf16_lo(old.x); f[1] += bf16_hi(old.x); f[2] += bf16_lo(old.y); f[3] += bf16_hi(old.y);
-                f[4] += bf16_lo(old.z); f[5] += bf16_hi(old.z); f[6] += bf16_lo(old.w); f[7] += bf16_hi(old.w);
-              }
-              uint4 o;
-              o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
-              o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
-              *reinterpret_cast<uint4*>(crow + j) = o;
-            }
+            for (int q = 0; q < 8; ++q) f[q] = zero_acc ? 0.f : __uint_as_float(v[j + q]) * p.alpha;
+            const uint4 old = *reinterpret_cast<const uint4*>(crow + j);
+            f[0] += bf16_lo(old.x); f[1] += bf16_hi(old.x); f[2] += bf16_lo(old.y); f[3] += bf16_hi(old.y);
+            f[4] += bf16_lo(old.z); f[5] += bf16_hi(old.z); f[6] += bf16_lo(old.w); f[7] += bf16_hi(old.w);
+            uint4 o;
+            o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+            o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+            *reinterpret_cast<uint4*>(crow + j) = o;
           }
         }
+      }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tmem_empty[acc]);
       ++local_tile;
     }
+    if (lane == 0) tma_store_wait<0>();  // this warp's bulk stores have completed before the CTA retires
   }
 
   __syncthreads();
@@ -310,7 +354,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 }
 
 template <int BLOCK_N, bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const GemmParams& p, cudaStream_t st) {
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tc, void* C,
+                       const GemmParams& p, cudaStream_t st) {
   using S = GemmSmem<BLOCK_N>;
   auto kern = gemm_bf16_kernel<BLOCK_N, A_MN, B_MN, OUT_F32, ACCUM>;
   static bool configured = false;
@@ -324,7 +369,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, co
   const long long tiles = static_cast<long long>(num_m) * num_n * (p.mode == 2 ? p.num_groups : 1);
   if (tiles == 0) return 0;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-  kern<<<grid, kGemmThreads, S::kTotal, st>>>(ta, tb, C, p);
+  kern<<<grid, kGemmThreads, S::kTotal, st>>>(ta, tb, tc, C, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }
@@ -332,12 +377,18 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, void* C, co
 template <int BLOCK_N, bool A_MN, bool B_MN>
 static int dispatch_out(const CUtensorMap& ta, const CUtensorMap& tb, void* C, const GemmParams& p, int out_f32,
                         int accumulate, cudaStream_t st) {
+  // C as a 2-D map of 32-row x 128-byte boxes for the epilogue's TMA stores / reduce-adds
+  CUtensorMap tc;
+  const uint64_t rows = static_cast<uint64_t>(p.M) * (p.mode == 2 ? p.num_groups : 1);
+  int r = out_f32 ? make_tmap_2d(&tc, C, 4, p.N, rows, static_cast<uint64_t>(p.ldc) * 4, 32, 32, 1)
+                  : make_tmap_2d(&tc, C, 2, p.N, rows, static_cast<uint64_t>(p.ldc) * 2, 64, 32, 1);
+  if (r) return r;
   if (out_f32) {
-    return accumulate ? launch_gemm<BLOCK_N, A_MN, B_MN, true, true>(ta, tb, C, p, st)
-                      : launch_gemm<BLOCK_N, A_MN, B_MN, true, false>(ta, tb, C, p, st);
+    return accumulate ? launch_gemm<BLOCK_N, A_MN, B_MN, true, true>(ta, tb, tc, C, p, st)
+                      : launch_gemm<BLOCK_N, A_MN, B_MN, true, false>(ta, tb, tc, C, p, st);
   }
-  return accumulate ? launch_gemm<BLOCK_N, A_MN, B_MN, false, true>(ta, tb, C, p, st)
-                    : launch_gemm<BLOCK_N, A_MN, B_MN, false, false>(ta, tb, C, p, st);
+  return accumulate ? launch_gemm<BLOCK_N, A_MN, B_MN, false, true>(ta, tb, tc, C, p, st)
+                    : launch_gemm<BLOCK_N, A_MN, B_MN, false, false>(ta, tb, tc, C, p, st);
 }
 
 template <int BLOCK_N>
@@ -421,7 +472,7 @@ extern "C" int stb_gemm_bf16_grouped_reduce(const void* A, const void* B, void* 
                                             int total_rows, int M, int N, int num_groups, int lda, int ldb, int ldc,
                                             int out_f32, int accumulate, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || num_groups <= 0) return 0;
-  if ((N & 7) || (M & 7) || (lda & 7) || (ldb & 7) || (ldc & 3)) return -kErrBadArgument;
+  if ((N & 7) || (M & 127) || (lda & 7) || (ldb & 7) || (ldc & 3)) return -kErrBadArgument;
   const int bn = (N % 256 == 0) ? 256 : 128;
   CUtensorMap ta, tb;
   int r = make_tmap_2d_bf16(&ta, A, M, total_rows, static_cast<uint64_t>(lda) * 2, 64, kBlockK, 1);

@@ -46,6 +46,22 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t 
   return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 1000;
 }
 
+int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d0, uint64_t d1, uint64_t pitch_bytes,
+                 uint32_t box0, uint32_t box1, int swizzle128) {
+  ensure_context_on_this_thread();
+  EncodeTiledFn enc = get_encode_tiled();
+  if (enc == nullptr) return -1;
+  cuuint64_t dims[2] = {d0, d1};
+  cuuint64_t strides[1] = {pitch_bytes};
+  cuuint32_t box[2] = {box0, box1};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r) - 1000;
+}
+
 int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t pitch1,
                       uint64_t pitch2, uint32_t box0, uint32_t box1, uint32_t box2, int swizzle128) {
   ensure_context_on_this_thread();

@@ -303,6 +303,15 @@ class BaseExp(Config):
                           backend=list(getattr(self.trainer_cfg, "writer_backend", ["tensorboard"])), exp=self)
 
     def sanity_check(self):
+        """Validate the tree. When no launcher has set ``WORLD_SIZE`` the expected world size of the
+        resource config is assumed for the duration of the check (and removed again afterwards, so a
+        plain single-process run does not try to rendezvous with ranks that do not exist)."""
         expected = self.resource_cfg.replica * max(self.resource_cfg.gpu, 1)
-        os.environ["WORLD_SIZE"] = os.environ.get("WORLD_SIZE", str(expected))
-        super().sanity_check()
+        had = "WORLD_SIZE" in os.environ
+        if not had:
+            os.environ["WORLD_SIZE"] = str(expected)
+        try:
+            super().sanity_check()
+        finally:
+            if not had:
+                del os.environ["WORLD_SIZE"]
