@@ -288,6 +288,11 @@ class BaseGradientManager:
         self._refresh_params()
         self.wait_param_gather()
 
+    def refresh_masters_from_params(self) -> None:
+        """After loading model weights without optimizer state: fp32 masters follow the parameters."""
+        for shard in self.shards.values():
+            shard.master.copy_(shard.bucket.param_buf[shard.lo:shard.hi])
+
     # ------------------------------------------------------------------ offload (RL role swapping)
     def offload_state(self) -> None:
         for shard in self.shards.values():
