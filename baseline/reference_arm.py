@@ -1,0 +1,235 @@
+"""Baseline arm of ``bench.py``: the unmodified reference framework training the same model.
+
+The reference tree is copied verbatim to ``baseline/_ref`` (it is pure Python; its own build backend,
+hatchling, is not installable offline) and imported from there.  Two of its dependencies are not
+installable either and are replaced by the small stand-ins under ``baseline/shims``:
+``configurize`` (mapped to this repository's implementation of the same config-tree API) and
+``megfile`` (local file system).  Everything on the training path — models, tensor-parallel layers,
+flash-attn attention core, gradient manager, optimizer, schedule, trainer — is the reference's own
+code, driven through its own ``Exp`` / trainer API with its own Qwen3-8B configuration file.
+
+Only two things are supplied from outside, because the reference does not ship them: a synthetic
+packed-document data config producing the reference's batch contract, and a weight initialiser
+(the reference leaves parameters uninitialised and expects a checkpoint).
+"""
+from __future__ import annotations
+
+import importlib.util
+import json
+import os
+import statistics
+import sys
+import time
+import traceback
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+REF = os.path.join(HERE, "_ref")
+
+
+def _load_file(path: str, name: str):
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def _unavailable(why: str):
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")[:400]}), flush=True)
+
+
+def run(args) -> None:
+    if not os.path.isdir(os.path.join(REF, "steptronoss")):
+        return _unavailable("baseline/_ref/steptronoss is absent: copy the reference tree there first")
+    sys.path.insert(0, os.path.join(HERE, "shims"))
+    sys.path.insert(0, REF)
+    try:
+        _run(args)
+    except BaseException as e:  # report instead of failing the driver
+        tb = traceback.format_exc().strip().splitlines()
+        _unavailable(f"{type(e).__name__}: {e} | {tb[-3] if len(tb) > 3 else ''}")
+
+
+def _run(args) -> None:
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "1")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    os.environ.setdefault("WORLD_SIZE", "1")
+    os.environ.setdefault("RANK", "0")
+    os.environ.setdefault("LOCAL_RANK", "0")
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+
+    from steptronoss.exp.base_exp import DataConfig
+    from steptronoss.core.trainers.lm_trainer import DecoderPretrainTrainer
+    from steptronoss.utils.optimizable import set_optimization
+
+    sft_base = _load_file(os.path.join(REF, "playground/sft/qwen3/qwen3_sft_base.py"), "_ref_qwen3_sft_base")
+    q8 = _load_file(os.path.join(REF, "playground/pretrain/qwen3/qwen3_8b.py"), "_ref_qwen3_8b")
+
+    sys.path.insert(0, os.path.dirname(HERE))
+    from bench import ClockSampler, default_parallelism, model_flops_per_token, parse_parallelism
+    from steptronoss_b200.data.synthetic import make_packed_sample  # data generator only (numpy)
+
+    par_text = args.parallelism or default_parallelism(world)
+    par = parse_parallelism(par_text)
+    seq = args.seq_len
+
+    class Loader:
+        def __init__(self, dp_rank, dp_size):
+            self.i, self.dp_rank, self.dp_size = 0, dp_rank, dp_size
+
+        def __iter__(self):
+            return self
+
+        def __len__(self):
+            return 1 << 40
+
+        def __next__(self):
+            rng = np.random.default_rng([0, self.i * self.dp_size + self.dp_rank])
+            self.i += 1
+            s = make_packed_sample(rng, seq, 151936, 256, seq)
+            return {k: v.pin_memory() for k, v in s.items()}
+
+        def state_dict(self):
+            return {"i": self.i}
+
+        def load_state_dict(self, sd):
+            self.i = sd["i"]
+
+    class SyntheticData(DataConfig):
+        global_data_keys = ["cu_seqlens", "position_id", "max_seq_len"]
+
+        def build_dataloader(self, dp_rank=0, dp_size=1):
+            return Loader(dp_rank, dp_size)
+
+    class Trainer(DecoderPretrainTrainer):
+        def setup_model(self, model_config):
+            models = super().setup_model(model_config)
+            gen = torch.Generator(device="cuda")
+            gen.manual_seed(1234 + rank)
+            with torch.no_grad():
+                for m in models:
+                    for n, p in m.named_parameters():
+                        if p.dim() == 1:
+                            p.fill_(1.0)
+                        else:
+                            p.normal_(0.0, 0.02, generator=gen)
+            return models
+
+    class Exp(sft_base.Exp):
+        model_cfg = q8.Qwen3_8BConfig
+        data_cfg = SyntheticData
+
+        def __init__(self):
+            super().__init__()
+            pc = self.model_cfg.parallel_cfg
+            pc.tensor_model_parallel_size = par["tp"]
+            pc.pipeline_model_parallel_size = par["pp"]
+            pc.context_parallel_size = par["cp"]
+            self.model_cfg.tp_cfg.sequence_parallel = par["tp"] > 1
+            self.model_cfg.check_nan = False
+            if args.debug_layers:
+                self.model_cfg.num_layers = args.debug_layers
+            rec = args.recompute
+            if rec == "auto":
+                rec = "full" if par["tp"] * par["pp"] == 1 else "none"
+            self.model_cfg.recompute = True if rec == "full" else ([] if rec == "none" else rec.split(","))
+            self._recompute_text = rec
+            t = self.trainer_cfg
+            t.global_batch_size = args.seqs_per_gpu * world
+            t.global_seq_length = seq
+            t.micro_batch_size = 1
+            t.train_iters = 10 ** 9
+            t.log_interval = 10 ** 9
+            t.log_num_zeros_in_grad = False
+            self.resource_cfg.gpu = world
+            self.scheduler_cfg.lr = 1e-5
+            self.scheduler_cfg.weight_decay = 0.1
+            self.scheduler_cfg.total_schedule = 10 ** 6
+            self.scheduler_cfg.warmup_schedule = 0
+            self.checkpoint_cfg.save_interval = None
+            self.log_dir = os.path.join(os.path.dirname(HERE), "gpurun_out", "reference_logs")
+
+    exp = Exp()
+    exp.sanity_check()
+    os.environ["WORLD_SIZE"] = str(world)
+    trainer = Trainer(exp=exp)
+    exp.configure_optimizable()  # the reference experiment's own choice: flash-attn attention core
+    trainer.before_train()
+    for m in trainer.models:
+        m.train()
+    trainer.iteration = 0
+
+    def barrier_sync():
+        if dist.is_initialized():
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    from steptronoss.utils import GlobalMetrics
+
+    def step():
+        trainer.train_step()
+        trainer.iteration += 1
+
+    for _ in range(args.warmup):
+        step()
+        GlobalMetrics.reset() if hasattr(GlobalMetrics, "reset") else None
+    barrier_sync()
+    sampler = ClockSampler(os.path.join(os.path.dirname(HERE), "gpurun_out", "bench_clocks_reference.csv")) if rank == 0 else None
+    if sampler:
+        os.makedirs(os.path.dirname(sampler.path), exist_ok=True)
+        sampler.start()
+    barrier_sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier_sync()
+    wall = (time.perf_counter() - t0) * 1e3
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+    t = torch.tensor([ms, wall], dtype=torch.float64, device="cuda")
+    if dist.is_initialized():
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, wall = float(t[0]), float(t[1])
+    if rank != 0:
+        return
+    tc = exp.trainer_cfg
+    tokens = tc.global_batch_size * tc.global_seq_length
+    value = tokens * args.steps / (ms / 1e3)
+    # the reference's step already copies every micro-batch from pinned host memory and reads the loss,
+    # the gradient norm and a NaN flag back to the host, so its end-to-end figure is the same run
+    e2e = tokens * args.steps / (max(ms, wall) / 1e3)
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(os.path.dirname(HERE), "MEASURED_PEAKS.json")))
+    except Exception:
+        pass
+    peak = float(peaks.get("bf16_tflops_sustained", 1375.7)) * 1e12
+    avg_ctx = (seq ** 2 / 3.0) / ((256 + seq) / 2.0) / 2.0
+    fpt = model_flops_per_token(exp.model_cfg.num_layers, 4096, 32, 8, 128, 12288, 151936, avg_ctx)
+    out = {
+        "metric": "tokens/s/box (Qwen3-8B dense training, all GPUs of the node)", "value": value, "unit": "tokens/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic packed documents (lengths U[256,8192], uniform token ids), random N(0,0.02) init",
+        "mfu_of_measured_sustained_bf16": value * fpt / (peak * world),
+        "config": {"model": "Qwen3-8B", "layers": exp.model_cfg.num_layers, "global_batch": tc.global_batch_size,
+                   "seq_len": seq, "micro_batch": 1, "parallelism": par_text, "optimizer": "Adam fp32 master+state, ZeRO-1",
+                   "recompute": exp._recompute_text, "attention": "flash-attn 2 (reference AttentionCore)",
+                   "l2": "inputs larger than L2"},
+        "clocks": clocks,
+        "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": max(ms, wall) / args.steps},
+        "impl": "reference",
+    }
+    if args.debug_layers:
+        out["invalid_debug_config"] = True
+    print(json.dumps(out), flush=True)

@@ -9,8 +9,9 @@
 //
 // Kernels
 //   attn_fwd_kernel   : CTA = (q block of 128 rows, q head). Loop over key blocks: S = Q K^T (TMEM,
-//                       double buffered) -> softmax threads -> P (bf16, smem) -> PV (TMEM) -> running
-//                       output kept in registers with the usual max/sum rescaling. Writes O and LSE.
+//                       double buffered) -> softmax threads -> P (bf16, smem) -> O += P V (TMEM), with
+//                       the accumulator rescaled only when a row maximum moves by more than 2^8.
+//                       Writes O and LSE.
 //   attn_bwd_dq_kernel: same decomposition; per key block S and dP = dO V^T, dS = P o (dP - delta),
 //                       dQ += dS K accumulated in TMEM.
 //   attn_bwd_dkv_kernel: CTA = (key block of 128, kv head); loops over the q heads of the group and
@@ -134,7 +135,8 @@ attn_rowblock_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int head = blockIdx.x;
-  const int blk = blockIdx.y;
+  // later q blocks of a causal document see more keys: launch them first so the tail of the grid is light
+  const int blk = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);
   const int seg = p.blk_seg[blk];
   if (seg < 0) return;  // uniform for the CTA, before any barrier or TMEM use
   const SegInfo s = seg_info(p, seg);
@@ -168,7 +170,7 @@ attn_rowblock_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  // TMEM columns. fwd: S0 0, S1 128, PV0 256, PV1 384.   dq: S 0, dP 128, dQ 256.
+  // TMEM columns. fwd: S0 0, S1 128, O 256.   dq: S 0, dP 128, dQ 256.
 
   if (warp == 0) {
     if (lane == 0 && nkb > 0) {
@@ -216,10 +218,10 @@ attn_rowblock_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           ok = mbar_wait(&p_full[st], (j >> 1) & 1);
           if (!ok) break;
           tc_fence_after();
-          // O_j = P_j V_j : A = P (K-major over keys), B = V ([keys][D] -> MN-major)
-          mma_128x128x128<false, true>(tmem + 256 + st * 128, smem_u32(st ? sX1 : sX0),
-                                       smem_u32(sKV + st * 2 * kTileBytes + kTileBytes), false);
-          umma_commit(&pv_full[st]);
+          // O += P_j V_j : A = P (K-major over keys), B = V ([keys][D] -> MN-major)
+          mma_128x128x128<false, true>(tmem + 256, smem_u32(st ? sX1 : sX0),
+                                       smem_u32(sKV + st * 2 * kTileBytes + kTileBytes), j > 0);
+          umma_commit(&pv_full[0]);
           umma_commit(&kv_empty[st]);
         }
       } else {
@@ -252,10 +254,13 @@ attn_rowblock_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float sl2 = p.scale * kLog2e;
     if (MODE == 0) {
-      float acc[kD];
-#pragma unroll
-      for (int i = 0; i < kD; ++i) acc[i] = 0.f;
-      float m = -INFINITY, l = 0.f, alpha_prev = 1.f;
+      // The output accumulates in TMEM (PV issued with accumulate = 1). The exponent reference m_ref of a
+      // row only moves when the row maximum outgrows it by more than kRescaleGap (in log2 units): until
+      // then probabilities are at most 2^kRescaleGap, which fp32 accumulation and bf16 P hold without loss,
+      // and the accumulator is left untouched.  When a row does move its reference, its warp reads the
+      // accumulator rows back, scales them and stores them again before releasing P for the next PV.
+      constexpr float kRescaleGap = 8.f;
+      float m_ref = -INFINITY, l = 0.f;
       bool ok = true;
       for (int j = 0; j < nkb && ok && !*abort_flag; ++j) {
         const int st = j & 1;
@@ -266,101 +271,101 @@ attn_rowblock_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         // a block needs element masks when it touches the diagonal, the window edge or the segment end
         const bool need_mask = (kb + kBN > s.k_len) || (p.causal && kb + kBN - 1 > q0 + s.off) ||
                                (p.window > 0 && kb <= q0 + kBM - 1 + s.off - p.window) || (q0 + kBM > s.q_len);
-        float mx = -INFINITY;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(tmem + lane_addr + st * 128 + c * 32, v);
-          tmem_wait_ld();
+        uint32_t v[128];
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float x = __uint_as_float(v[i]);
-            if (need_mask && !visible(p, s, qi, kb + c * 32 + i)) x = -INFINITY;
-            mx = fmaxf(mx, x);
-          }
+        for (int c = 0; c < 4; ++c) {
+          uint32_t (&part)[32] = *reinterpret_cast<uint32_t (*)[32]>(&v[c * 32]);
+          tmem_ld_32x32(tmem + lane_addr + st * 128 + c * 32, part);
         }
-        const float m_new = fmaxf(m, mx * sl2);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = (m == -INFINITY) ? 0.f : exp2f(m - m_use);
+        tmem_wait_ld();
+        float mx = -INFINITY;
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 128; ++i) {
+            if (!visible(p, s, qi, kb + i)) v[i] = 0xff800000u;  // -inf
+            mx = fmaxf(mx, __uint_as_float(v[i]));
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+        }
+        const float m_cand = mx * sl2;
+        const bool moves = m_cand > m_ref + kRescaleGap || (m_ref == -INFINITY && m_cand > -INFINITY);
+        if (__any_sync(0xffffffffu, moves)) {
+          const float m_new = moves ? m_cand : m_ref;
+          const float factor = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
+          if (j > 0) {
+            // every PV issued so far must have landed before the accumulator is rewritten
+            ok = mbar_wait(&pv_full[0], (j - 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+              uint32_t o[32];
+              tmem_ld_32x32(tmem + lane_addr + 256 + c * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+              tmem_st_32x32(tmem + lane_addr + 256 + c * 32, o);
+            }
+            tmem_wait_st();
+          }
+          l *= factor;
+          m_ref = m_new;
+        }
+        const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
         float rowsum = 0.f;
         uint8_t* sP = st ? sX1 : sX0;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(tmem + lane_addr + st * 128 + c * 32, v);
-          tmem_wait_ld();
-          uint32_t packed[16];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float x0 = __uint_as_float(v[i]), x1 = __uint_as_float(v[i + 1]);
-            if (need_mask) {
-              if (!visible(p, s, qi, kb + c * 32 + i)) x0 = -INFINITY;
-              if (!visible(p, s, qi, kb + c * 32 + i + 1)) x1 = -INFINITY;
-            }
-            const float p0 = exp2f(x0 * sl2 - m_use), p1 = exp2f(x1 * sl2 - m_use);
-            rowsum += p0 + p1;
-            packed[i >> 1] = pack_bf16(p0, p1);
-          }
-          // 32 keys = 4 chunks of 16 B; slab = (c*32)/64, chunk index inside the 128 B row
-          uint8_t* slab = sP + (c >> 1) * kSlabBytes;
+        for (int c8 = 0; c8 < 16; ++c8) {  // 16 chunks of 8 keys = 16 bytes of bf16
+          float pr[8];
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const uint32_t chunk = (c & 1) * 4 + q4;
-            *reinterpret_cast<uint4*>(slab + swz(r, chunk)) =
-                make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+          for (int i = 0; i < 8; ++i) {
+            pr[i] = exp2f(__uint_as_float(v[c8 * 8 + i]) * sl2 - m_use);
+            rowsum += pr[i];
           }
+          uint8_t* slab = sP + (c8 >> 3) * kSlabBytes;
+          *reinterpret_cast<uint4*>(slab + swz(r, c8 & 7)) =
+              make_uint4(pack_bf16(pr[0], pr[1]), pack_bf16(pr[2], pr[3]), pack_bf16(pr[4], pr[5]), pack_bf16(pr[6], pr[7]));
         }
-        l = l * alpha + rowsum;
+        l += rowsum;
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(&p_full[st]);
-        if (j > 0) {
-          const int sp = (j - 1) & 1;
-          ok = mbar_wait(&pv_full[sp], ((j - 1) >> 1) & 1);
-          if (!ok) break;
-          tc_fence_after();
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32(tmem + lane_addr + 256 + sp * 128 + c * 32, v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c * 32 + i] = acc[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
-          }
-        }
-        alpha_prev = alpha;
-        m = m_new;
       }
+      float inv = 0.f;
       if (ok && nkb > 0 && !*abort_flag) {
-        const int sp = (nkb - 1) & 1;
-        ok = mbar_wait(&pv_full[sp], ((nkb - 1) >> 1) & 1);
-        if (ok) {
-          tc_fence_after();
-#pragma unroll
-          for (int c = 0; c < 4; ++c) {
-            uint32_t v[32];
-            tmem_ld_32x32(tmem + lane_addr + 256 + sp * 128 + c * 32, v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) acc[c * 32 + i] = acc[c * 32 + i] * alpha_prev + __uint_as_float(v[i]);
-          }
-        }
+        ok = mbar_wait(&pv_full[0], (nkb - 1) & 1);
+        if (ok) tc_fence_after();
+        inv = (l > 0.f) ? 1.f / l : 0.f;
       }
       if (!ok) { report_error(p.status, kErrSoftmaxWait); *abort_flag = 1; }
-      if (qi < s.q_len && q_abs < p.total_q) {
-        const float inv = (l > 0.f) ? 1.f / l : 0.f;
-        __nv_bfloat16* orow = p.O + (q_abs * p.hq + head) * kD;
+      const bool store_row = qi < s.q_len && q_abs < p.total_q;
+      __nv_bfloat16* orow = p.O + (q_abs * p.hq + head) * kD;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t o[32];
+        if (nkb > 0 && ok) {
+          tmem_ld_32x32(tmem + lane_addr + 256 + c * 32, o);
+          tmem_wait_ld();
+        } else {
 #pragma unroll
-        for (int i = 0; i < kD; i += 8) {
-          uint4 o;
-          o.x = pack_bf16(acc[i] * inv, acc[i + 1] * inv);
-          o.y = pack_bf16(acc[i + 2] * inv, acc[i + 3] * inv);
-          o.z = pack_bf16(acc[i + 4] * inv, acc[i + 5] * inv);
-          o.w = pack_bf16(acc[i + 6] * inv, acc[i + 7] * inv);
-          *reinterpret_cast<uint4*>(orow + i) = o;
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
         }
-        p.LSE[static_cast<long long>(head) * p.total_q + q_abs] = (l > 0.f) ? (m * kLn2 + logf(l)) : -INFINITY;
+        if (store_row) {
+#pragma unroll
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack_bf16(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+            w.y = pack_bf16(__uint_as_float(o[i + 2]) * inv, __uint_as_float(o[i + 3]) * inv);
+            w.z = pack_bf16(__uint_as_float(o[i + 4]) * inv, __uint_as_float(o[i + 5]) * inv);
+            w.w = pack_bf16(__uint_as_float(o[i + 6]) * inv, __uint_as_float(o[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + i) = w;
+          }
+        }
       }
+      if (store_row)
+        p.LSE[static_cast<long long>(head) * p.total_q + q_abs] = (l > 0.f) ? (m_ref * kLn2 + logf(l)) : -INFINITY;
     } else {
       // dQ mode
       const bool row_ok = (qi < s.q_len) && (q_abs < p.total_q);
@@ -373,31 +378,31 @@ attn_rowblock_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
         tc_fence_after();
         const int kb = (jb0 + j) * kBN;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t sv[32], dv[32];
-          tmem_ld_32x32(tmem + lane_addr + c * 32, sv);
-          tmem_ld_32x32(tmem + lane_addr + 128 + c * 32, dv);
-          tmem_wait_ld();
-          uint32_t packed[16];
+        for (int hblk = 0; hblk < 2; ++hblk) {  // 64 keys per TMEM round trip
+          uint32_t sv[64], dv[64];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float d0 = 0.f, d1 = 0.f;
-            if (row_ok && visible(p, s, qi, kb + c * 32 + i)) {
-              const float pr = exp2f(__uint_as_float(sv[i]) * sl2 - lse2);
-              d0 = pr * (__uint_as_float(dv[i]) - dl) * p.scale;
-            }
-            if (row_ok && visible(p, s, qi, kb + c * 32 + i + 1)) {
-              const float pr = exp2f(__uint_as_float(sv[i + 1]) * sl2 - lse2);
-              d1 = pr * (__uint_as_float(dv[i + 1]) - dl) * p.scale;
-            }
-            packed[i >> 1] = pack_bf16(d0, d1);
+          for (int c = 0; c < 2; ++c) {
+            uint32_t (&a)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[c * 32]);
+            uint32_t (&b)[32] = *reinterpret_cast<uint32_t (*)[32]>(&dv[c * 32]);
+            tmem_ld_32x32(tmem + lane_addr + hblk * 64 + c * 32, a);
+            tmem_ld_32x32(tmem + lane_addr + 128 + hblk * 64 + c * 32, b);
           }
-          uint8_t* slab = sX1 + (c >> 1) * kSlabBytes;
+          tmem_wait_ld();
+          uint8_t* slab = sX1 + hblk * kSlabBytes;
 #pragma unroll
-          for (int q4 = 0; q4 < 4; ++q4) {
-            const uint32_t chunk = (c & 1) * 4 + q4;
-            *reinterpret_cast<uint4*>(slab + swz(r, chunk)) =
-                make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+          for (int c8 = 0; c8 < 8; ++c8) {
+            float d[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int col = c8 * 8 + i;
+              d[i] = 0.f;
+              if (row_ok && visible(p, s, qi, kb + hblk * 64 + col)) {
+                const float pr = exp2f(__uint_as_float(sv[col]) * sl2 - lse2);
+                d[i] = pr * (__uint_as_float(dv[col]) - dl) * p.scale;
+              }
+            }
+            *reinterpret_cast<uint4*>(slab + swz(r, c8)) =
+                make_uint4(pack_bf16(d[0], d[1]), pack_bf16(d[2], d[3]), pack_bf16(d[4], d[5]), pack_bf16(d[6], d[7]));
           }
         }
         fence_proxy_async_smem();
@@ -561,32 +566,34 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       if (!ok) break;
       tc_fence_after();
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sv[32], dv[32];
-        tmem_ld_32x32(tmem + lane_addr + c * 32, sv);
-        tmem_ld_32x32(tmem + lane_addr + 128 + c * 32, dv);
-        tmem_wait_ld();
-        uint32_t pp[16], dd[16];
+      for (int hblk = 0; hblk < 2; ++hblk) {  // 64 keys per TMEM round trip
+        uint32_t sv[64], dv[64];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
-          if (row_ok && visible(p, s, qi, k0 + c * 32 + i)) {
-            p0 = exp2f(__uint_as_float(sv[i]) * sl2 - lse2);
-            d0 = p0 * (__uint_as_float(dv[i]) - dl) * p.scale;
-          }
-          if (row_ok && visible(p, s, qi, k0 + c * 32 + i + 1)) {
-            p1 = exp2f(__uint_as_float(sv[i + 1]) * sl2 - lse2);
-            d1 = p1 * (__uint_as_float(dv[i + 1]) - dl) * p.scale;
-          }
-          pp[i >> 1] = pack_bf16(p0, p1);
-          dd[i >> 1] = pack_bf16(d0, d1);
+        for (int c = 0; c < 2; ++c) {
+          uint32_t (&a)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[c * 32]);
+          uint32_t (&b)[32] = *reinterpret_cast<uint32_t (*)[32]>(&dv[c * 32]);
+          tmem_ld_32x32(tmem + lane_addr + hblk * 64 + c * 32, a);
+          tmem_ld_32x32(tmem + lane_addr + 128 + hblk * 64 + c * 32, b);
         }
-        const uint32_t slab_off = (c >> 1) * kSlabBytes;
+        tmem_wait_ld();
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const uint32_t a = slab_off + swz(r, (c & 1) * 4 + q4);
-          *reinterpret_cast<uint4*>(sP + a) = make_uint4(pp[q4 * 4], pp[q4 * 4 + 1], pp[q4 * 4 + 2], pp[q4 * 4 + 3]);
-          *reinterpret_cast<uint4*>(sdS + a) = make_uint4(dd[q4 * 4], dd[q4 * 4 + 1], dd[q4 * 4 + 2], dd[q4 * 4 + 3]);
+        for (int c8 = 0; c8 < 8; ++c8) {
+          float pv[8], dd[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int col = c8 * 8 + i;
+            pv[i] = 0.f;
+            dd[i] = 0.f;
+            if (row_ok && visible(p, s, qi, k0 + hblk * 64 + col)) {
+              pv[i] = exp2f(__uint_as_float(sv[col]) * sl2 - lse2);
+              dd[i] = pv[i] * (__uint_as_float(dv[col]) - dl) * p.scale;
+            }
+          }
+          const uint32_t a = hblk * kSlabBytes + swz(r, c8);
+          *reinterpret_cast<uint4*>(sP + a) =
+              make_uint4(pack_bf16(pv[0], pv[1]), pack_bf16(pv[2], pv[3]), pack_bf16(pv[4], pv[5]), pack_bf16(pv[6], pv[7]));
+          *reinterpret_cast<uint4*>(sdS + a) =
+              make_uint4(pack_bf16(dd[0], dd[1]), pack_bf16(dd[2], dd[3]), pack_bf16(dd[4], dd[5]), pack_bf16(dd[6], dd[7]));
         }
       }
       fence_proxy_async_smem();

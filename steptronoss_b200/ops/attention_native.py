@@ -14,12 +14,6 @@ import torch
 from . import native
 from .gemm import count_launch
 
-native._SIGNATURES.update({
-    "stb_attn_fwd": [native.P] * 9 + [native.I] * 6 + [native.L] * 3 + [native.I, native.I, native.F, native.P, native.P],
-    "stb_attn_bwd": [native.P] * 14 + [native.I] + [native.P] * 2 + [native.I] * 6 + [native.L] * 4
-                    + [native.I, native.I, native.F, native.P, native.P],
-})
-
 _BLOCK = 128
 _SCHED_CACHE: dict = {}
 
