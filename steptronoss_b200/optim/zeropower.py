@@ -1,0 +1,153 @@
+"""Matrix orthogonalisation routines for Muon.
+
+``zeropower`` is the quintic Newton-Schulz iteration ``X <- a X + (b A + c A^2) X`` with
+``A = X X^T`` on the spectrally-normalised input; the coefficient sets are the ones the reference
+ships (``steptronoss/optimizer/_helpers.py:36-98``) together with its non-orthogonalising
+alternatives (SVD, double normalisation, Sinkhorn-Knopp, dualisations).
+
+On CUDA the three products of an iteration are tcgen05 GEMMs (``A`` and ``A^2`` are symmetric, so
+both are plain ``X X^T``-type products without a transposed copy); the iteration runs in bf16.  The
+reference casts to fp16 for the same step ("run_ns_in_fp16"); bf16 is what the sm_100a kernel takes
+and has the wider exponent range.
+"""
+from __future__ import annotations
+
+from functools import partial
+
+import torch
+
+from ..ops.gemm import gemm
+
+_PE = [
+    (8.28721201814563, -23.595886519098837, 17.300387312530933),
+    (4.107059111542203, -2.9478499167379106, 0.5448431082926601),
+    (3.9486908534822946, -2.908902115962949, 0.5518191394370137),
+    (3.3184196573706015, -2.488488024314874, 0.51004894012372),
+    (2.300652019954817, -1.6689039845747493, 0.4188073119525673),
+    (1.891301407787398, -1.2679958271945868, 0.37680408948524835),
+    (1.8750014808534479, -1.2500016453999487, 0.3750001645474248),
+    (1.875, -1.25, 0.375),
+]
+_PE_SLOW = [
+    (2.6708353888008127, -3.2853566190584504, 1.6385678673837945),
+    (1.8756101482892078, -1.25067777555517, 0.3750677840207064),
+    (1.8750001724801866, -1.2500003448894914, 0.37500017240930517),
+    (1.875, -1.25, 0.375),
+]
+
+
+def _with_safety(table):
+    """All but the last polynomial are deflated by 1.01 per odd power for numerical headroom."""
+    return [(a / 1.01, b / 1.01 ** 3, c / 1.01 ** 5) for a, b, c in table[:-1]] + [table[-1]]
+
+
+ZEROPOWER_COEFFS = {
+    "default": (3.4445, -4.7750, 2.0315),
+    "youjc_250416": [(4.0848, -6.8946, 2.9270), (3.9505, -6.3029, 2.6377), (3.7418, -5.5913, 2.3037),
+                     (2.8769, -3.1427, 1.2046), (2.8366, -3.0525, 1.2012)],
+    "youjc_6": [(3955 / 1024, -8306 / 1024, 5008 / 1024), (3735 / 1024, -6681 / 1024, 3463 / 1024),
+                (3799 / 1024, -6499 / 1024, 3211 / 1024), (4019 / 1024, -6385 / 1024, 2906 / 1024),
+                (2677 / 1024, -3029 / 1024, 1162 / 1024), (2172 / 1024, -1833 / 1024, 682 / 1024)],
+    "sujl_6": [(4140 / 1024, -7553 / 1024, 3571 / 1024), (3892 / 1024, -6637 / 1024, 2973 / 1024),
+               (3668 / 1024, -6456 / 1024, 3021 / 1024), (3248 / 1024, -6211 / 1024, 3292 / 1024),
+               (2792 / 1024, -5759 / 1024, 3796 / 1024), (3176 / 1024, -5507 / 1024, 4048 / 1024)],
+    "polar_express": _with_safety(_PE),
+    "polar_express_slow_convergence": _with_safety(_PE_SLOW),
+}
+
+
+def _schedule(coeffs, steps: int):
+    table = [tuple(coeffs)] if isinstance(coeffs[0], (int, float)) else [tuple(c) for c in coeffs]
+    if len(table) < steps:
+        table = table + [table[-1]] * (steps - len(table))
+    return table[:steps]
+
+
+def _ns_native_2d(X: torch.Tensor, table) -> torch.Tensor:
+    """X ``[m, n]`` bf16 CUDA with ``m <= n`` and both multiples of 8."""
+    for a, b, c in table:
+        A = gemm(X, X)                                   # X X^T            [m, m]
+        A2 = gemm(A, A)                                  # A A^T = A^2 (A symmetric)
+        B = torch.add(A2, A, alpha=b / c).mul_(c)        # b A + c A^2
+        BX = gemm(B, X, b_mn_major=True)                 # B X              [m, n]
+        X = BX.add_(X, alpha=a)
+    return X
+
+
+def zeropower(G: torch.Tensor, steps: int = 5, run_ns_in_fp16: bool = True, coeffs=ZEROPOWER_COEFFS["default"]):
+    """Approximate ``U V^T`` of ``G = U S V^T`` (last two dims; leading dims are a batch)."""
+    assert G.ndim >= 2
+    tall = G.size(-2) > G.size(-1)
+    X = G.mT if tall else G
+    X = X / (X.float().norm(dim=(-2, -1), keepdim=True) * 1.01 + 1e-7).to(X.dtype)
+    table = _schedule(coeffs, steps)
+    native_ok = X.is_cuda and run_ns_in_fp16 and X.size(-1) % 8 == 0 and X.size(-2) % 8 == 0
+    if native_ok:
+        Xb = X.to(torch.bfloat16).contiguous()
+        if Xb.dim() == 2:
+            out = _ns_native_2d(Xb, table)
+        else:
+            flat = Xb.reshape(-1, Xb.size(-2), Xb.size(-1))
+            out = torch.stack([_ns_native_2d(m.contiguous(), table) for m in flat]).view(Xb.shape)
+        X = out
+    else:
+        if run_ns_in_fp16:
+            X = X.to(torch.bfloat16 if not X.is_cuda else torch.float16)
+        for a, b, c in table:
+            A = X @ X.mT
+            B = b * A + c * (A @ A)
+            X = a * X + B @ X
+    return X.mT.contiguous() if tall else X
+
+
+def zeropower_via_svd(G, steps=None):
+    U, _, Vh = torch.linalg.svd(G.float(), full_matrices=False)
+    return U @ Vh
+
+
+def double_normalize(G, steps):
+    order = [-2, -1] if G.shape[-2] < G.shape[-1] else [-1, -2]
+    for _ in range(steps):
+        for dim in order:
+            G = G / (G.norm(dim=dim, keepdim=True, p=2) + 1e-7)
+    return G
+
+
+def sinkhorn_knopp(G, steps):
+    order = [-2, -1] if G.shape[-2] < G.shape[-1] else [-1, -2]
+    for _ in range(steps):
+        for dim in order:
+            G = G / (G.norm(dim=dim, keepdim=True, p=1) + 1e-7)
+    return G * G.shape[order[-1]] ** 0.5
+
+
+def dualize_1_to_p(G, steps=None, p=1):
+    return G / (torch.linalg.vector_norm(G, dim=-2, keepdim=True, ord=p) + 1e-7) * G.shape[-2] ** 0.5
+
+
+def dualize_p_to_infinity(G, steps=None, p=1):
+    q = 1 if p == float("inf") else p / (p - 1)
+    return G / (torch.linalg.vector_norm(G, dim=-1, keepdim=True, ord=q) + 1e-7) * (G.shape[-1] / G.shape[-2] ** 0.5)
+
+
+def dualize_schatten_2_norm(G, steps=None):
+    return G / (torch.linalg.matrix_norm(G, ord="fro", dim=(-2, -1), keepdim=True) + 1e-7) * min(G.shape[-2:]) ** 0.5
+
+
+def get_zeropower_fn(name: str, run_ns_in_fp16: bool = True):
+    table = {
+        "svd": zeropower_via_svd,
+        "double_normalize": double_normalize,
+        "sinkhorn_knopp": sinkhorn_knopp,
+        "dualize_1_to_1": partial(dualize_1_to_p, p=1),
+        "dualize_inf_to_inf": partial(dualize_p_to_infinity, p=float("inf")),
+        "dualize_schatten_2_norm": dualize_schatten_2_norm,
+    }
+    if name in table:
+        return table[name]
+    return partial(zeropower, run_ns_in_fp16=run_ns_in_fp16, coeffs=ZEROPOWER_COEFFS[name])
+
+
+def adjust_ratio_for_muon(matched_adamw_rms: float, shape) -> float:
+    """Scale that gives an orthogonalised update the RMS of an AdamW update: ``rms * sqrt(max(m, n))``."""
+    return matched_adamw_rms * (max(shape[-2], shape[-1]) ** 0.5)
