@@ -28,11 +28,15 @@ def causal_flops(lens, hq, d):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--library", action="store_true")
+    ap.add_argument("--only", default=None, help="comma list of case names")
+    ap.add_argument("--iters", type=int, default=10)
     args = ap.parse_args()
     peak = measured_peaks()["bf16_tflops"]
     hq, hkv, d = 32, 8, 128
     cases = {"1x8192": [8192], "2x4096": [4096, 4096], "mixed": [3000, 700, 2500, 1992], "8x1024": [1024] * 8}
     for name, lens in cases.items():
+        if args.only and name not in args.only.split(","):
+            continue
         T = sum(lens)
         cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
         q = torch.randn(T, hq, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
@@ -40,13 +44,13 @@ def main():
         v = torch.randn(T, hkv, d, device="cuda", dtype=torch.bfloat16, requires_grad=True)
         g = torch.randn(T, hq, d, device="cuda", dtype=torch.bfloat16)
         fl = causal_flops(lens, hq, d)
-        tf = time_cuda(lambda: attention(q, k, v, cu, cu, max(lens)))
+        tf = time_cuda(lambda: attention(q, k, v, cu, cu, max(lens)), iters=args.iters)
         o = attention(q, k, v, cu, cu, max(lens))
 
         def bwd():
             o.backward(g, retain_graph=True)
 
-        tb = time_cuda(bwd)
+        tb = time_cuda(bwd, iters=args.iters)
         row = {"case": name, "tokens": T, "fwd_ms": tf["best_ms"], "fwd_tflops": fl / tf["best_ms"] / 1e9,
                "fwd_frac_of_measured_peak": fl / tf["best_ms"] / 1e9 / peak, "bwd_ms": tb["best_ms"],
                "bwd_tflops_useful": 2.5 * fl / tb["best_ms"] / 1e9,
