@@ -22,6 +22,7 @@ constexpr int kStreamTile = kSB * kD * 2;     // 16 KB: [64][128] bf16 as two [6
 constexpr int kStreamSlab = kSB * 128;        // 8 KB
 constexpr int kPTile = 128 * kSB * 2;         // 16 KB: [128][64] bf16, one swizzled slab
 constexpr int kBwdStages = 3;
+constexpr int kBwdThreads = 320;                // producer warp, MMA warp, 8 softmax warps (2 per TMEM lane quarter)
 constexpr int kBwdSmem = 2 * kTileBytes + kBwdStages * 2 * kStreamTile + 2 * 2 * kPTile + 1024 + 1024 + 512;
 
 // A [128][K] K-major (two 64-col slabs of 16 KB) x B [64][K] K-major (two slabs of 8 KB) -> D [128 x 64]
@@ -52,7 +53,7 @@ __device__ __forceinline__ void load_stream_tile(void* dst, const CUtensorMap* m
 }
 
 template <bool DKV>
-__global__ void __launch_bounds__(kAttnThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_constant__ CUtensorMap tmap_f2,
                 const __grid_constant__ CUtensorMap tmap_g1, const __grid_constant__ CUtensorMap tmap_g2,
                 const AttnParams p) {
@@ -108,7 +109,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&pds_full[i], 128);
+      mbar_init(&pds_full[i], 256);
     }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
@@ -181,9 +182,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
       if (!ok) { report_error(p.status, kErrMmaWaitFull); *abort_flag = 1; }
     }
   } else {
+    // Two warps share each TMEM lane quarter: warps 2..5 take columns [0,32) of every streamed tile,
+    // warps 6..9 columns [32,64).  A scheduler then always has two softmax warps to alternate between.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;               // 0 or 1
     const int r = quarter * 32 + lane;              // fixed row owned by this thread
-    const int t128 = threadIdx.x - 64;              // 0..127 among the softmax threads
+    const int t128 = threadIdx.x - 64;              // 0..255 among the softmax threads
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     const float sl2 = p.scale * kLog2e;
     const int fi = f0 + r;                          // row inside the segment (key for dkv, query for dq)
@@ -200,36 +204,36 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
       }
     }
     bool ok = true;
-    for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
+    // All softmax threads run every iteration (the dK/dV pass meets at a named barrier in each one); after
+    // a timed-out wait the remaining waits are skipped, so a failure cannot strand the other threads.
+    for (int it = 0; it < iters; ++it) {
       const int g0 = (sb0 + it % nsb) * kSB;        // first streamed row of this tile (segment relative)
       const int buf = it & 1;
+      if (*abort_flag) ok = false;
       if (DKV) {
         // per-column constants of the 64 streamed queries: threads 0..63 fetch lse, 64..127 fetch delta
         const int hq_i = kvh * group + it / nsb;
         const int c = t128 & 63;
         const long long q_abs = static_cast<long long>(s.q_begin) + g0 + c;
         const bool qok = (g0 + c < s.q_len) && (q_abs < p.total_q);
-        float val = 0.f;
-        if (qok) {
-          val = (t128 < 64) ? p.LSE[static_cast<long long>(hq_i) * p.total_q + q_abs] * kLog2e
-                            : p.delta[static_cast<long long>(hq_i) * p.total_q + q_abs];
-        } else if (t128 < 64) {
-          val = INFINITY;  // exp2(x - inf) = 0 for rows past the segment
+        if (t128 < 128) {
+          float val = 0.f;
+          if (qok) {
+            val = (t128 < 64) ? p.LSE[static_cast<long long>(hq_i) * p.total_q + q_abs] * kLog2e
+                              : p.delta[static_cast<long long>(hq_i) * p.total_q + q_abs];
+          } else if (t128 < 64) {
+            val = INFINITY;  // exp2(x - inf) = 0 for rows past the segment
+          }
+          s_lse[buf * 128 + t128] = val;
         }
-        s_lse[buf * 128 + t128] = val;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
       }
-      ok = mbar_wait(&sdp_full[buf], (it >> 1) & 1);
-      if (!ok) break;
+      if (ok) ok = mbar_wait(&sdp_full[buf], (it >> 1) & 1);
+      if (!ok) continue;
       tc_fence_after();
-      uint32_t sv[64], dv[64];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t (&a)[32] = *reinterpret_cast<uint32_t (*)[32]>(&sv[c * 32]);
-        uint32_t (&b)[32] = *reinterpret_cast<uint32_t (*)[32]>(&dv[c * 32]);
-        tmem_ld_32x32(tmem + lane_addr + buf * kSB + c * 32, a);
-        tmem_ld_32x32(tmem + lane_addr + 128 + buf * kSB + c * 32, b);
-      }
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32(tmem + lane_addr + buf * kSB + half * 32, sv);
+      tmem_ld_32x32(tmem + lane_addr + 128 + buf * kSB + half * 32, dv);
       tmem_wait_ld();
       // does any (fixed row, streamed row) pair of this tile fall outside the mask?
       bool need_mask;
@@ -244,21 +248,23 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
       uint8_t* pdS = pP + kPTile;
       const float* cl = s_lse + buf * 128;
 #pragma unroll
-      for (int c8 = 0; c8 < 8; ++c8) {
+      for (int c8l = 0; c8l < 4; ++c8l) {
+        const int c8 = half * 4 + c8l;
         float pv[8], dd[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const int col = c8 * 8 + i;
+          const int lc = c8l * 8 + i;          // index into this thread's 32 columns
+          const int col = half * 32 + lc;      // column of the streamed tile
           const float lse2 = DKV ? cl[col] : row_lse2;
           const float dl = DKV ? cl[64 + col] : row_delta;
-          float pr = exp2f(__uint_as_float(sv[col]) * sl2 - lse2);
+          float pr = exp2f(__uint_as_float(sv[lc]) * sl2 - lse2);
           if (need_mask) {
             const bool vis = DKV ? visible(p, s, g0 + col, fi) : visible(p, s, fi, g0 + col);
             if (!vis) pr = 0.f;
           }
           if (!frow_ok) pr = 0.f;
           pv[i] = pr;
-          dd[i] = pr * (__uint_as_float(dv[col]) - dl) * p.scale;
+          dd[i] = pr * (__uint_as_float(dv[lc]) - dl) * p.scale;
         }
         const uint32_t a = swz(r, c8);
         if (DKV)
@@ -283,7 +289,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
                                  : p.dK + (f_abs * p.hkv + kvh) * kD;
       else base = p.dQ + (f_abs * p.hq + head_f) * kD;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = half * 2; c < half * 2 + 2; ++c) {
         uint32_t v[32];
         if (iters > 0 && ok) {
           tmem_ld_32x32(tmem + lane_addr + 256 + which * 128 + c * 32, v);
@@ -382,10 +388,10 @@ extern "C" int stb_attn_bwd(const void* q, const void* k, const void* v, const v
   // dK / dV: fixed = (K, V) of a kv head, streamed = (Q, dO) of the group's q heads
   p.blk_seg = k_blk_seg; p.blk_row0 = k_blk_row0;
   if (num_k_blocks > 0)
-    attn_bwd_kernel<true><<<dim3(hkv, num_k_blocks), kAttnThreads, kBwdSmem, st>>>(k128, v128, q64, do64, p);
+    attn_bwd_kernel<true><<<dim3(hkv, num_k_blocks), kBwdThreads, kBwdSmem, st>>>(k128, v128, q64, do64, p);
   // dQ: fixed = (Q, dO) of a q head, streamed = (K, V)
   p.blk_seg = q_blk_seg; p.blk_row0 = q_blk_row0;
   if (num_q_blocks > 0)
-    attn_bwd_kernel<false><<<dim3(hq, num_q_blocks), kAttnThreads, kBwdSmem, st>>>(q128, do128, k64, v64, p);
+    attn_bwd_kernel<false><<<dim3(hq, num_q_blocks), kBwdThreads, kBwdSmem, st>>>(q128, do128, k64, v64, p);
   return -static_cast<int>(cudaGetLastError());
 }
