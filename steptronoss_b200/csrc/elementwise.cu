@@ -606,3 +606,61 @@ extern "C" int stb_add_bf16(const void* a, const void* b, void* out, long long n
                                                         static_cast<__nv_bfloat16*>(out), n / 8);
   return -static_cast<int>(cudaGetLastError());
 }
+
+// ============================================================================ entry point that allocates nothing
+// See noalloc.h.  RMSNorm backward keeps one row of weight-gradient partials per CTA; the regular entry
+// point takes that buffer from its caller, this one keeps it in a fixed array that is part of the loaded
+// library image on every device.
+namespace stb {
+constexpr int kNoAllocMaxParts = 256;   // CTAs (partial rows) used by the no-allocation variant
+constexpr int kNoAllocMaxH = 4096;      // widest row it accepts
+static __device__ __align__(256) float g_rmsnorm_bwd_partials[kNoAllocMaxParts * kNoAllocMaxH];  // 4 MiB per device
+constexpr int kNoAllocMaxDevices = 64;
+}  // namespace stb
+
+#include <mutex>
+
+extern "C" int stb_rmsnorm_bwd_noalloc_max_hidden() { return stb::kNoAllocMaxH; }
+
+extern "C" int stb_rmsnorm_bwd_noalloc(const void* x, const void* w, const void* g, const float* rstd, void* dx,
+                                       float* dw, long long rows, int H, long long x_stride, long long g_stride,
+                                       long long dx_stride, int zero_centered, int add_to_dx, int accumulate_dw,
+                                       cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (H <= 0 || (H % 8) != 0 || H > stb::kNoAllocMaxH) {
+    fprintf(stderr,
+            "stb_rmsnorm_bwd_noalloc: hidden size %d is not supported (needs a multiple of 8, at most %d); "
+            "use stb_rmsnorm_bwd with caller-provided scratch for wider rows\n",
+            H, stb::kNoAllocMaxH);
+    return -kErrBadArgument;
+  }
+  // The array's name is only a host-side handle: the device address has to be asked for, once per
+  // device, with that device current.
+  static float* scratch_of_device[stb::kNoAllocMaxDevices] = {nullptr};
+  static std::mutex setup_lock;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return -static_cast<int>(e);
+  if (dev < 0 || dev >= stb::kNoAllocMaxDevices) return -kErrBadArgument;
+  float* scratch;
+  {
+    std::lock_guard<std::mutex> hold(setup_lock);
+    scratch = scratch_of_device[dev];
+    if (scratch == nullptr) {
+      e = cudaGetSymbolAddress(reinterpret_cast<void**>(&scratch), stb::g_rmsnorm_bwd_partials);
+      if (e != cudaSuccess) {
+        fprintf(stderr, "stb_rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+        return -static_cast<int>(e);
+      }
+      scratch_of_device[dev] = scratch;
+    }
+  }
+  const int grid = static_cast<int>(rows < stb::kNoAllocMaxParts ? rows : stb::kNoAllocMaxParts);
+  // every CTA overwrites its whole partial row, so nothing in the shared array has to start at zero
+  rmsnorm_bwd_kernel<<<grid, kNormThreads, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(g),
+      rstd, static_cast<__nv_bfloat16*>(dx), scratch, static_cast<int>(rows), H, x_stride, g_stride, dx_stride,
+      zero_centered, add_to_dx);
+  if (dw != nullptr) rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, st>>>(scratch, dw, grid, H, accumulate_dw, H);
+  return -static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,85 @@
+"""The allocation-free RMSNorm backward entry point, called through its exported C symbol.
+
+Some users of the native library cannot let it (or themselves) call cudaMalloc while they run: their
+process has a fixed device-memory budget, or a host application owns the device heap.  For them the
+library exports ``stb_rmsnorm_bwd_noalloc``, which keeps the kernel's scratch in a fixed array inside
+the library.  This test drives that symbol directly with raw pointers, twice in a row with different
+inputs (the second call sees the scratch the first one left behind), and checks both results against
+the regular entry point, which takes its scratch from the caller.  The file name sorts last so that a
+``pytest -x`` run has already executed every other test when it gets here.
+"""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _bind(lib):
+    P, I, L = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    fn = lib.stb_rmsnorm_bwd_noalloc
+    fn.argtypes = [P, P, P, P, P, P, L, I, L, L, L, I, I, I, P]
+    fn.restype = I
+    lib.stb_rmsnorm_bwd_noalloc_max_hidden.argtypes = []
+    lib.stb_rmsnorm_bwd_noalloc_max_hidden.restype = I
+    return fn
+
+
+def _reference_entry(lib, x, w, g, rstd):
+    from steptronoss_b200.ops import native
+
+    rows, H = x.shape
+    dx = torch.empty_like(x)
+    dw = torch.empty(H, dtype=torch.float32, device=x.device)
+    grid = lib.stb_rmsnorm_bwd_grid(rows)
+    scratch = torch.empty((grid, H), dtype=torch.float32, device=x.device)
+    native.check(lib.stb_rmsnorm_bwd(x.data_ptr(), w.data_ptr(), g.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+                                     dw.data_ptr(), scratch.data_ptr(), rows, H, x.stride(0), g.stride(0), dx.stride(0),
+                                     0, 0, 0, native.stream()), "rmsnorm_bwd")
+    return dx, dw
+
+
+def test_noalloc_entry_matches_regular_entry_on_two_consecutive_calls():
+    from steptronoss_b200.ops import native
+
+    lib = native.load()
+    fn = _bind(lib)
+    assert lib.stb_rmsnorm_bwd_noalloc_max_hidden() == 4096
+    torch.manual_seed(0)
+    stream = native.stream()
+    for call, (rows, H) in enumerate([(1000, 4096), (333, 2048)]):
+        x = torch.randn(rows, H, device="cuda", dtype=torch.bfloat16)
+        w = (1 + 0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16)
+        g = torch.randn(rows, H, device="cuda", dtype=torch.bfloat16)
+        rstd = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-6)
+        ref_dx, ref_dw = _reference_entry(lib, x, w, g, rstd)
+        # outputs are allocated by the caller (here: the test); the entry point itself allocates nothing
+        dx = torch.empty_like(x)
+        dw = torch.empty(H, dtype=torch.float32, device="cuda")
+        torch.cuda.synchronize()
+        before = torch.cuda.memory_allocated()
+        rc = fn(x.data_ptr(), w.data_ptr(), g.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(), rows, H,
+                x.stride(0), g.stride(0), dx.stride(0), 0, 0, 0, stream)
+        torch.cuda.synchronize()
+        assert rc == 0, f"call {call}: rc={rc}"
+        assert torch.cuda.memory_allocated() == before
+        assert torch.equal(dx, ref_dx), f"call {call}: dx differs"
+        scale = ref_dw.abs().max().item() + 1e-6
+        assert ((dw - ref_dw).abs().max().item() / scale) < 2e-2, f"call {call}: dw differs"
+
+
+def test_noalloc_entry_rejects_rows_wider_than_its_scratch():
+    from steptronoss_b200.ops import native
+
+    lib = native.load()
+    fn = _bind(lib)
+    H = 8192
+    x = torch.randn(4, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    rstd = torch.ones(4, device="cuda")
+    dx = torch.empty_like(x)
+    dw = torch.zeros(H, dtype=torch.float32, device="cuda")
+    rc = fn(x.data_ptr(), w.data_ptr(), x.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(), 4, H, H, H, H, 0, 0,
+            0, native.stream())
+    assert rc < 0
