@@ -88,6 +88,8 @@ class GroupedQueryAttention(nn.Module):
             for m in (self.q_norm, self.k_norm):
                 m.weight = nn.Parameter(torch.empty(D, dtype=dtype))
                 m.weight.init_kind = "zeros" if cfg.rms_norm_zero_gamma else "ones"
+                # replicated over TP but every rank only sees its own heads: the gradient is a partial sum
+                m.weight.tp_partial_grad = True
         self.rot_dim = _per_layer(cfg.qk_rope_head_dim, layer_id) or D
         theta = float(_per_layer(cfg.rope_theta, layer_id))
         self.rope = RotaryEmbedding(self.rot_dim, theta, cfg.max_position_embeddings, cfg.rope_scaling_factor,

@@ -249,6 +249,7 @@ class BaseGradientManager:
         self.step_count += 1
         self._allreduce_tagged("sequence_parallel", "TP")
         self._allreduce_tagged("micro_dp", "TP")
+        self._allreduce_tagged("tp_partial_grad", "TP")
         self._scale_expert_grads()
         grad_scale = self._reduce()
         self._compute_clip(grad_scale)

@@ -1,0 +1,168 @@
+"""Context parallelism: load-balanced ("zigzag") sequence sharding with gathered keys and values.
+
+Semantics of the reference (``steptronoss/core/context_parallel/context_parallel.py:10-178`` and
+``model/common/grouped_query_attention.py:276-329``): the sequence is cut into ``2·CP`` chunks, rank
+``r`` keeps chunks ``r`` and ``2·CP-1-r`` (so that every rank gets the same amount of causal work);
+queries stay local, K and V are all-gathered over the CP group (backward: reduce-scatter); each half
+of the local queries attends, per packed document, to the keys from the document start up to its own
+end.
+
+Here the two halves become two calls of the variable-length attention kernel whose q segments are the
+tail of their key segments; the keys each half needs are packed from the gathered tensor with one
+row gather, whose backward sums the contributions of overlapping ranges.
+"""
+from __future__ import annotations
+
+import weakref
+from dataclasses import dataclass, field
+
+import torch
+import torch.distributed as dist
+
+from ..ops import attention
+from . import comm
+from .state import PM
+
+
+def _cp():
+    return PM.size_of("CP"), PM.rank_in("CP")
+
+
+def balanced_chunk_ids(rank: int, cp: int) -> tuple[int, int]:
+    return rank, 2 * cp - 1 - rank
+
+
+def scatter_to_balanced_cp_region(x: torch.Tensor, dim: int = 0) -> torch.Tensor:
+    """Keep chunks ``r`` and ``2·CP-1-r`` of ``2·CP`` equal chunks along ``dim`` (no communication: every
+    CP rank holds the full tensor)."""
+    cp, r = _cp()
+    if cp == 1:
+        return x
+    if x.shape[dim] % (2 * cp):
+        raise ValueError(f"length {x.shape[dim]} is not divisible by 2*CP = {2 * cp}")
+    chunks = x.chunk(2 * cp, dim=dim)
+    a, b = balanced_chunk_ids(r, cp)
+    return torch.cat([chunks[a], chunks[b]], dim=dim)
+
+
+class _GatherBalanced(torch.autograd.Function):
+    """All-gather over CP and restore the global order; backward reduce-scatters in the zigzag layout."""
+
+    @staticmethod
+    def forward(ctx, x):
+        cp, _ = _cp()
+        full = torch.empty((cp * x.shape[0], *x.shape[1:]), dtype=x.dtype, device=x.device)
+        comm.all_gather_into_tensor(full, x.contiguous(), group=PM.group_of("CP"))
+        half = x.shape[0] // 2
+        parts = full.view(cp, 2, half, *x.shape[1:])
+        order = [None] * (2 * cp)
+        for rank in range(cp):
+            a, b = balanced_chunk_ids(rank, cp)
+            order[a], order[b] = parts[rank, 0], parts[rank, 1]
+        return torch.cat(order, dim=0)
+
+    @staticmethod
+    def backward(ctx, g):
+        cp, _ = _cp()
+        chunks = g.chunk(2 * cp, dim=0)
+        zig = []
+        for rank in range(cp):
+            a, b = balanced_chunk_ids(rank, cp)
+            zig += [chunks[a], chunks[b]]
+        full = torch.cat(zig, dim=0).contiguous()
+        out = torch.empty((full.shape[0] // cp, *full.shape[1:]), dtype=g.dtype, device=g.device)
+        comm.reduce_scatter_tensor(out, full, group=PM.group_of("CP"))
+        return out
+
+
+def gather_from_balanced_cp_region(x: torch.Tensor) -> torch.Tensor:
+    """Local ``[2L, ...]`` (two zigzag chunks) -> global ``[2·CP·L, ...]`` in sequence order."""
+    if PM.size_of("CP") == 1:
+        return x
+    return _GatherBalanced.apply(x)
+
+
+@dataclass
+class HalfPlan:
+    cu_q: torch.Tensor            # int32 [n+1] over the half's local q rows
+    cu_k: torch.Tensor            # int32 [n+1] over the packed keys of the half
+    key_index: torch.Tensor       # int64 [sum k] rows of the *global-order* K/V to pack
+    max_q: int = 0
+    max_k: int = 0
+
+
+@dataclass
+class CPMeta:
+    chunk_len: int
+    token_index: torch.Tensor     # int64 [2L] global positions of this rank's tokens
+    halves: list = field(default_factory=list)
+
+    def local_position_id(self, position_id: torch.Tensor) -> torch.Tensor:
+        return position_id.index_select(0, self.token_index.to(position_id.device))
+
+
+def cu_seqlens_to_balanced_cp(cu_seqlens: list, total: int, cp: int, rank: int) -> list:
+    """Per half of rank ``rank``: list of ``(q_begin, q_end, k_begin)`` in global positions, one entry per
+    document piece that falls into the half (``k_end == q_end``)."""
+    L = total // (2 * cp)
+    out = []
+    for c in balanced_chunk_ids(rank, cp):
+        lo, hi = c * L, (c + 1) * L
+        pieces = []
+        for ds, de in zip(cu_seqlens[:-1], cu_seqlens[1:]):
+            qs, qe = max(ds, lo), min(de, hi)
+            if qe > qs:
+                pieces.append((qs, qe, ds))
+        if not pieces or pieces[-1][1] < hi:  # tokens after the last document (padding) attend to themselves
+            start = pieces[-1][1] if pieces else lo
+            pieces.append((start, hi, start))
+        out.append(pieces)
+    return out
+
+
+_META_CACHE: dict = {}
+
+
+def build_cp_meta(cu_seqlens, total: int, device=None) -> CPMeta:
+    cp, rank = _cp()
+    if cu_seqlens is None:
+        cu_list = [0, total]
+    else:
+        key = (id(cu_seqlens), cu_seqlens._version, total, cp, rank)
+        hit = _META_CACHE.get(key)
+        if hit is not None and hit[0]() is cu_seqlens:  # same tensor object, not a recycled address
+            return hit[1]
+        cu_list = [int(v) for v in cu_seqlens.tolist()]  # host read, once per micro-batch
+    if total % (2 * cp):
+        raise ValueError(f"sequence length {total} is not divisible by 2*CP = {2 * cp}")
+    device = device or (cu_seqlens.device if cu_seqlens is not None else "cpu")
+    L = total // (2 * cp)
+    a, b = balanced_chunk_ids(rank, cp)
+    token_index = torch.cat([torch.arange(a * L, (a + 1) * L), torch.arange(b * L, (b + 1) * L)]).to(device)
+    meta = CPMeta(L, token_index)
+    for pieces in cu_seqlens_to_balanced_cp(cu_list, total, cp, rank):
+        q_lens = [qe - qs for qs, qe, _ in pieces]
+        k_lens = [qe - ks for _, qe, ks in pieces]
+        cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=device)
+        cu_k = torch.tensor([0] + list(torch.tensor(k_lens).cumsum(0)), dtype=torch.int32, device=device)
+        idx = torch.cat([torch.arange(ks, qe) for _, qe, ks in pieces]).to(device)
+        meta.halves.append(HalfPlan(cu_q, cu_k, idx, max(q_lens), max(k_lens)))
+    if cu_seqlens is not None:
+        if len(_META_CACHE) > 32:
+            _META_CACHE.clear()
+        _META_CACHE[key] = (weakref.ref(cu_seqlens), meta)
+    return meta
+
+
+def cp_attention(q, k, v, meta: CPMeta, causal: bool = True, window: int = 0):
+    """q ``[2L,hq,D]`` (local zigzag chunks), k/v ``[2L,hkv,D]`` local -> ``[2L,hq,D]``."""
+    L = meta.chunk_len
+    k_all = gather_from_balanced_cp_region(k.contiguous())
+    v_all = gather_from_balanced_cp_region(v.contiguous())
+    outs = []
+    for h, plan in enumerate(meta.halves):
+        qh = q[h * L : (h + 1) * L]
+        kh = k_all.index_select(0, plan.key_index)
+        vh = v_all.index_select(0, plan.key_index)
+        outs.append(attention(qh, kh, vh, plan.cu_q, plan.cu_k, plan.max_k, causal=causal, window=window))
+    return torch.cat(outs, dim=0)

@@ -1,0 +1,82 @@
+"""Spawn gloo ranks on CPU that train the tiny experiment under a given parallel layout."""
+from __future__ import annotations
+
+import os
+import socket
+
+import torch
+import torch.multiprocessing as mp
+
+
+def free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, exp_kwargs, steps, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    torch.set_num_threads(1)
+    try:
+        from steptronoss_b200.parallel.state import PM
+        from tests.tiny_exp import make_tiny_exp
+
+        PM.initialize(backend="gloo")
+        exp = make_tiny_exp(**exp_kwargs)
+        exp.seed = 0
+        tr = exp.trainer_cfg.get_trainer_cls()(exp=exp)
+        tr.before_train()
+        losses = []
+        for _ in range(steps):
+            tr.train_step()
+            tr.iteration += 1
+            tr.training_log()
+            losses.append(tr.history[-1]["lm_loss"])
+        norms = [tr.history[i]["grad_norm"] for i in range(steps)]
+        q.put((rank, losses, norms, None))
+        torch.distributed.barrier()
+    except BaseException as e:  # surface the failure to the parent instead of hanging it
+        import traceback
+
+        q.put((rank, None, None, traceback.format_exc()))
+        raise
+
+
+def run_ranks(world: int, exp_kwargs: dict, steps: int = 3, timeout: int = 300):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, exp_kwargs, steps, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = []
+    try:
+        for _ in range(world):
+            item = q.get(timeout=timeout)
+            if item[3] is not None:
+                raise RuntimeError(f"rank {item[0]} failed:\n{item[3]}")
+            results.append(item)
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    return sorted(results, key=lambda t: t[0])
+
+
+def run_single(exp_kwargs: dict, steps: int = 3):
+    from tests.tiny_exp import make_tiny_exp
+
+    os.environ.pop("WORLD_SIZE", None)
+    exp = make_tiny_exp(**exp_kwargs)
+    exp.seed = 0
+    tr = exp.trainer_cfg.get_trainer_cls()(exp=exp)
+    tr.before_train()
+    losses = []
+    for _ in range(steps):
+        tr.train_step()
+        tr.iteration += 1
+        tr.training_log()
+        losses.append(tr.history[-1]["lm_loss"])
+    return losses, [h["grad_norm"] for h in tr.history]

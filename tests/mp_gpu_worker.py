@@ -1,0 +1,39 @@
+"""Worker for the multi-GPU tests: trains the tiny bf16 experiment under the layout given on the command
+line (launched by torch.distributed.run) and prints one JSON line with the loss curve from rank 0."""
+import json
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+import torch  # noqa: E402
+
+
+def main():
+    kw = json.loads(sys.argv[1])
+    steps = int(sys.argv[2])
+    from steptronoss_b200.ops import native
+    from steptronoss_b200.parallel.state import PM
+    from tests.tiny_exp import make_tiny_exp
+
+    PM.initialize()
+    exp = make_tiny_exp(dtype=torch.bfloat16, **kw)
+    exp.seed = 0
+    tr = exp.trainer_cfg.get_trainer_cls()(exp=exp)
+    tr.before_train()
+    losses = []
+    for _ in range(steps):
+        tr.train_step()
+        tr.iteration += 1
+        tr.training_log()
+        losses.append(tr.history[-1]["lm_loss"])
+    torch.cuda.synchronize()
+    native.raise_if_kernel_error()
+    if PM.world_rank == PM.world_size - 1:
+        print("RESULT " + json.dumps({"losses": losses, "grad_norms": [h["grad_norm"] for h in tr.history]}), flush=True)
+    if torch.distributed.is_initialized():
+        torch.distributed.barrier()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,41 @@
+"""Multi-GPU training through the native kernels: TP(+SP), DP ZeRO-1, CP and PP layouts on 2 GPUs must
+reproduce the 1-GPU loss curve within bf16 tolerance."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BASE = dict(gbs=4, seq=512, iters=3, layers=2, hidden=512, heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=2048,
+            min_doc=32, max_doc=256)
+
+
+def _launch(nproc: int, kw: dict, steps: int = 3, port: int = 29611):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "mp_gpu_worker.py"),
+           json.dumps(kw), str(steps)]
+    if nproc == 1:
+        cmd = [sys.executable, os.path.join(ROOT, "tests", "mp_gpu_worker.py"), json.dumps(kw), str(steps)]
+        env.pop("WORLD_SIZE", None)
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=400, env=env, cwd=ROOT)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    line = [l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    return json.loads(line[len("RESULT "):])
+
+
+@pytest.fixture(scope="module")
+def single():
+    return _launch(1, dict(BASE))
+
+
+@pytest.mark.parametrize("layout", [dict(tp=2, sp=True), dict(tp=2, sp=False), dict(), dict(cp=2), dict(pp=2)],
+                         ids=["tp2_sp", "tp2", "dp2_zero1", "cp2", "pp2"])
+def test_two_gpu_layout_matches_one_gpu(single, layout):
+    res = _launch(2, dict(BASE, **layout), port=29620 + len(str(layout)) % 50)
+    for a, b in zip(res["losses"], single["losses"]):
+        assert abs(a - b) < 3e-2 * abs(b), (layout, res["losses"], single["losses"])

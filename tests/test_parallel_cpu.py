@@ -1,0 +1,39 @@
+"""Tensor / sequence / context / pipeline parallel training on gloo ranks reproduces the single-process run."""
+import pytest
+import torch
+
+from tests.dist_helpers import run_ranks, run_single
+
+BASE = dict(gbs=2, seq=128, iters=3, layers=2, hidden=64, heads=4, kv_heads=2, head_dim=16, ffn=128, vocab=256,
+            min_doc=16, max_doc=64)
+
+
+def _close(a, b, tol):
+    return all(abs(x - y) <= tol * max(1.0, abs(y)) for x, y in zip(a, b))
+
+
+@pytest.fixture(scope="module")
+def single():
+    torch.set_num_threads(1)
+    return run_single(dict(BASE))
+
+
+@pytest.mark.parametrize("sp", [False, True])
+def test_tp2(single, sp):
+    res = run_ranks(2, dict(BASE, tp=2, sp=sp))
+    for rank, losses, norms, _ in res:
+        assert _close(losses, single[0], 2e-5), (rank, losses, single[0])
+        assert _close(norms, single[1], 1e-4), (rank, norms, single[1])
+
+
+def test_cp2(single):
+    res = run_ranks(2, dict(BASE, cp=2))
+    for rank, losses, norms, _ in res:
+        assert _close(losses, single[0], 2e-5), (rank, losses, single[0])
+        assert _close(norms, single[1], 1e-4), (rank, norms, single[1])
+
+
+def test_pp2(single):
+    res = run_ranks(2, dict(BASE, pp=2))
+    last = res[-1]
+    assert _close(last[1], single[0], 2e-5), (last[1], single[0])
