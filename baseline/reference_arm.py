@@ -47,6 +47,7 @@ def run(args) -> None:
     try:
         _run(args)
     except BaseException as e:  # report instead of failing the driver
+        sys.stderr.write(traceback.format_exc())
         tb = traceback.format_exc().strip().splitlines()
         _unavailable(f"{type(e).__name__}: {e} | {tb[-3] if len(tb) > 3 else ''}")
 
@@ -147,7 +148,6 @@ def _run(args) -> None:
             t.micro_batch_size = 1
             t.train_iters = 10 ** 9
             t.log_interval = 10 ** 9
-            t.log_num_zeros_in_grad = False
             self.resource_cfg.gpu = world
             self.scheduler_cfg.lr = 1e-5
             self.scheduler_cfg.weight_decay = 0.1

@@ -1,0 +1,139 @@
+"""Developer aids (reference ``steptronoss/utils/dev_utils.py:10-202``, ``utils/utils.py:377-453``):
+profiler window around a module's forward/backward, collective bandwidth probe, parameter table."""
+from __future__ import annotations
+
+import functools
+import os
+import time
+
+import torch
+import torch.distributed as dist
+
+from .logger import logger
+
+
+def capture_trace(at: int = 0, fw_file: str = "fw_trace.json", bw_file: str | None = None, rank: int = 0,
+                  warmup: int = 1):
+    """Decorator for a module ``forward``: on call number ``warmup + at`` (on global rank ``rank``) open a
+    ``torch.profiler`` window that covers the forward pass and, through a tensor hook, the matching backward
+    pass; export chrome traces (forward and backward separately when ``bw_file`` is given)."""
+
+    def deco(forward):
+        state = {"calls": 0}
+
+        @functools.wraps(forward)
+        def wrapped(*a, **k):
+            state["calls"] += 1
+            if state["calls"] != warmup + at + 1 or int(os.getenv("RANK", "0")) != rank:
+                return forward(*a, **k)
+            acts = [torch.profiler.ProfilerActivity.CPU]
+            if torch.cuda.is_available():
+                acts.append(torch.profiler.ProfilerActivity.CUDA)
+            prof = torch.profiler.profile(activities=acts, record_shapes=False)
+            prof.__enter__()
+            with torch.profiler.record_function("FW"):
+                out = forward(*a, **k)
+            first = out if torch.is_tensor(out) else next((o for o in (out.values() if isinstance(out, dict) else out)
+                                                         if torch.is_tensor(o) and o.requires_grad), None)
+
+            def finish():
+                if torch.cuda.is_available():
+                    torch.cuda.synchronize()
+                prof.__exit__(None, None, None)
+                prof.export_chrome_trace(bw_file or fw_file)
+                logger.info(f"trace written to {bw_file or fw_file}", at=None)
+
+            if first is not None and first.requires_grad and torch.is_grad_enabled():
+                if bw_file:
+                    # close the forward window now, open a second one that ends when backward has run
+                    if torch.cuda.is_available():
+                        torch.cuda.synchronize()
+                    prof.__exit__(None, None, None)
+                    prof.export_chrome_trace(fw_file)
+                    prof2 = torch.profiler.profile(activities=acts)
+                    prof2.__enter__()
+
+                    def done_bw():
+                        if torch.cuda.is_available():
+                            torch.cuda.synchronize()
+                        prof2.__exit__(None, None, None)
+                        prof2.export_chrome_trace(bw_file)
+
+                    first.register_hook(lambda g: (torch.autograd.Variable._execution_engine.queue_callback(done_bw), g)[1])
+                else:
+                    first.register_hook(lambda g: (torch.autograd.Variable._execution_engine.queue_callback(finish), g)[1])
+            else:
+                finish()
+            return out
+
+        return wrapped
+
+    return deco
+
+
+def profile_allreduce(size_bytes: int = 1 << 30, iters: int = 10, groups: dict | None = None) -> dict:
+    """All-reduce bandwidth (GB/s, bus bandwidth) of the world group and of every named family, measured
+    with CUDA events; also warms the communicators up (reference start-up probe, ``utils/utils.py:377-433``)."""
+    from ..parallel.state import PM
+
+    if not dist.is_initialized() or not torch.cuda.is_available():
+        return {}
+    out = {}
+    buf = torch.empty(size_bytes // 4, dtype=torch.float32, device="cuda")
+    targets = {"world": dist.group.WORLD}
+    for name in (groups or PM.parallels):
+        g = PM.group_of(name)
+        if g is not None and PM.size_of(name) > 1:
+            targets[name] = g
+    for name, g in targets.items():
+        n = dist.get_world_size(g)
+        dist.all_reduce(buf, group=g)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            dist.all_reduce(buf, group=g)
+        b.record()
+        torch.cuda.synchronize()
+        sec = a.elapsed_time(b) / 1e3 / iters
+        out[name] = size_bytes / sec / 1e9 * 2 * (n - 1) / n
+    logger.info("all-reduce bus bandwidth (GB/s): " + ", ".join(f"{k}={v:.0f}" for k, v in out.items()), at=0)
+    return out
+
+
+def print_n_params(models) -> dict:
+    """Parameter counts of this rank's model chunks, split into expert / non-expert."""
+    tot = exp = 0
+    for m in models if isinstance(models, (list, tuple, torch.nn.ModuleList)) else [models]:
+        for n, p in m.named_parameters():
+            tot += p.numel()
+            if getattr(p, "expert_model_parallel", False) or ".experts." in n:
+                exp += p.numel()
+    info = {"total": tot, "expert": exp, "dense": tot - exp}
+    logger.info(f"parameters on this rank: total {tot / 1e9:.3f} B (expert {exp / 1e9:.3f} B)", at=None)
+    return info
+
+
+def check_nan(tensor, flag: torch.Tensor | None = None):
+    """Device-side finite check: ORs 1 into ``flag`` (int32 on the device) when ``tensor`` holds a NaN/Inf.
+    Returns the flag without synchronising."""
+    if flag is None:
+        flag = torch.zeros(1, dtype=torch.int32, device=tensor.device)
+    if tensor.is_cuda and tensor.dtype == torch.bfloat16:
+        from ..ops import native
+
+        native.check(native.load().stb_nonfinite_flag(tensor.data_ptr(), tensor.numel(), flag.data_ptr(), native.stream()),
+                     "nonfinite_flag")
+    else:
+        flag |= (~torch.isfinite(tensor)).any().to(torch.int32)
+    return flag
+
+
+class Stopwatch:
+    def __enter__(self):
+        self.t0 = time.perf_counter()
+        return self
+
+    def __exit__(self, *a):
+        self.dt = time.perf_counter() - self.t0
+        return False
