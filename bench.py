@@ -40,6 +40,8 @@ def parse():
     ap.add_argument("--seqs-per-gpu", type=int, default=8, help="sequences per GPU per step (global batch = this x N)")
     ap.add_argument("--seq-len", type=int, default=8192)
     ap.add_argument("--recompute", default="auto", help="auto | none | full | comma list of block parts")
+    ap.add_argument("--recompute-layers", type=int, default=None,
+                    help="recompute only the first N layers (default: 14 of 36 on one GPU, all otherwise)")
     ap.add_argument("--debug-layers", type=int, default=None, help="DEBUG ONLY: fewer layers (result marked invalid)")
     return ap.parse_args()
 
@@ -148,6 +150,12 @@ def run_ours(args):
         # one GPU holds 18 bytes/parameter of static state (147 GB): recompute whole blocks
         rec = "full" if par["tp"] * par["pp"] == 1 else "none"
     exp.model_cfg.recompute = True if rec == "full" else ([] if rec == "none" else rec.split(","))
+    rec_layers = args.recompute_layers
+    if rec_layers is None and rec == "full" and args.recompute == "auto" and not args.debug_layers:
+        rec_layers = 14  # 147 GB of static state leave room for the activations of about 22 layers
+    if rec_layers is not None:
+        exp.model_cfg.recompute_num_layers = rec_layers
+        rec = f"{rec} (first {rec_layers} layers)"
     exp.resource_cfg.gpu = world
     os.environ.setdefault("WORLD_SIZE", str(world))
     exp.sanity_check()
@@ -262,6 +270,7 @@ def run_ours(args):
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_b / args.steps, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "last_loss": last_loss},
         "gpu_launches": launches,
+        "peak_memory_gb": torch.cuda.max_memory_allocated() / 2 ** 30,
         "impl": "ours",
     }
     if args.debug_layers:

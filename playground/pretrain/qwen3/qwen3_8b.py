@@ -38,6 +38,7 @@ class Qwen3FeedForwardConfig(FeedForwardConfig):
         self.hidden_size = 4096
         self.ffn_hidden_size = 12288
         self.layernorm_epsilon = 1e-6
+        self.swiglu_recompute_silu_out_proj = True
 
 
 class Qwen3InputEmbeddingConfig(InputEmbeddingConfig):

@@ -8,6 +8,8 @@ import torch.nn as nn
 
 from ...config import Config, Ref
 from ...ops import swiglu
+from ...ops.fused import swiglu_linear
+from ...parallel.state import PM
 from ...parallel.layers import ColumnParallelLinear, RowParallelLinear
 
 
@@ -37,6 +39,11 @@ class FeedForward(nn.Module):
         if isinstance(lim, (list, tuple)):
             lim = lim[layer_id]
         self.limit = float(lim) if lim else 0.0
+        self.fuse_act = bool(cfg.swiglu_recompute_silu_out_proj) and PM.size_of("TP") == 1
 
     def forward(self, x):
-        return self.w2(swiglu(self.w1(x), self.limit))
+        h = self.w1(x)
+        if self.fuse_act:
+            # the activation is recomputed inside the down projection's backward instead of being stored
+            return swiglu_linear(h, self.w2.weight, self.limit)
+        return self.w2(swiglu(h, self.limit))

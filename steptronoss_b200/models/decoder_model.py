@@ -33,6 +33,9 @@ class DecoderLLMConfig(Megatron3DParallelModelConfig):
     recompute: list | bool = []
     """Per-block recompute: any of 'attention', 'attn_norm', 'feed_forward', 'ffn_norm'; True = all
     (one checkpoint around the whole block). A custom ``pp_vp_allocation`` overrides it per layer."""
+    recompute_num_layers: int | None = None
+    """When set, ``recompute`` applies to the first ``recompute_num_layers`` layers of every pipeline chunk
+    only; the remaining layers keep their activations (a memory / speed dial for 180 GB parts)."""
     tie_embedding: bool = False
     init_std: float = 0.02
 
@@ -52,9 +55,10 @@ class DecoderLLMConfig(Megatron3DParallelModelConfig):
         for vp in range(PM.get_vpp_size()):
             for pp in range(PM.size_of("PP")):
                 chunk = layer_map.setdefault(pp, {}).setdefault(vp, {})
-                for opts in self.pp_vp_allocation(vp * PM.size_of("PP") + pp):
+                for pos, opts in enumerate(self.pp_vp_allocation(vp * PM.size_of("PP") + pp)):
                     opts = dict(opts)
-                    opts.setdefault("recompute", self.recompute)
+                    partial = self.recompute_num_layers is not None and pos >= self.recompute_num_layers
+                    opts.setdefault("recompute", False if partial else self.recompute)
                     chunk[layer_id] = opts
                     layer_id += 1
         return layer_map

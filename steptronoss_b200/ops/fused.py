@@ -290,3 +290,58 @@ def embedding(ids, table, vocab_start: int = 0, vocab_end: int | None = None):
         out = torch.nn.functional.embedding(local, table)
         return out.masked_fill(mask.unsqueeze(-1), 0.0)
     return _EmbeddingFn.apply(ids, table, vocab_start, vocab_end)
+
+
+# --------------------------------------------------------------------------- SwiGLU fused into the down projection
+class _SwiGLULinearFn(torch.autograd.Function):
+    """``swiglu(h) @ w.T`` that keeps only ``h``: the activation is recomputed in backward instead of being
+    stored (the role of the reference's pre-function linear, ``core/tensor_parallel/layers.py:349-524``)."""
+
+    @staticmethod
+    def forward(ctx, h, w, limit):
+        from .gemm import gemm
+
+        lib = native.load()
+        F = h.shape[-1] // 2
+        h2 = h.reshape(-1, 2 * F)
+        a = torch.empty((h2.shape[0], F), dtype=h.dtype, device=h.device)
+        native.check(lib.stb_swiglu_fwd(h2.data_ptr(), a.data_ptr(), h2.shape[0], F, h2.stride(0), a.stride(0),
+                                        float(limit), native.stream()), "swiglu_fwd")
+        count_launch()
+        y = gemm(a, w)
+        ctx.save_for_backward(h2, w)
+        ctx.w_ref, ctx.limit, ctx.in_shape = w, limit, h.shape
+        return y.view(*h.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, gy):
+        from .gemm import gemm
+
+        lib = native.load()
+        h2, w = ctx.saved_tensors
+        F = h2.shape[-1] // 2
+        g2 = gy.reshape(-1, gy.shape[-1]).contiguous()
+        a = torch.empty((h2.shape[0], F), dtype=h2.dtype, device=h2.device)
+        native.check(lib.stb_swiglu_fwd(h2.data_ptr(), a.data_ptr(), h2.shape[0], F, h2.stride(0), a.stride(0),
+                                        float(ctx.limit), native.stream()), "swiglu_fwd")
+        dw = None
+        main_grad = getattr(ctx.w_ref, "main_grad", None)
+        if ctx.needs_input_grad[1]:
+            if main_grad is not None:
+                gemm(g2, a, a_mn_major=True, b_mn_major=True, out=main_grad, accumulate=True)
+                ctx.w_ref.grad_added_to_main_grad = True
+            else:
+                dw = gemm(g2, a, a_mn_major=True, b_mn_major=True, out_dtype=w.dtype)
+        da = gemm(g2, w, b_mn_major=True, out=a)  # reuse the activation buffer for its gradient
+        dh = torch.empty_like(h2)
+        native.check(lib.stb_swiglu_bwd(h2.data_ptr(), da.data_ptr(), dh.data_ptr(), h2.shape[0], F, h2.stride(0),
+                                        da.stride(0), dh.stride(0), float(ctx.limit), native.stream()), "swiglu_bwd")
+        count_launch(2)
+        return dh.view(ctx.in_shape), dw, None
+
+
+def swiglu_linear(h, w, limit: float = 0.0):
+    """``swiglu(h) @ w.T`` without storing the activation (recomputed in backward)."""
+    if not h.is_cuda:
+        return torch.nn.functional.linear(swiglu_reference(h, limit), w)
+    return _SwiGLULinearFn.apply(h, w, limit or 0.0)

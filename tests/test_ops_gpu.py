@@ -74,6 +74,23 @@ def test_swiglu_fwd_bwd(limit):
     _close(x.grad, xr.grad, 2e-2)
 
 
+def test_swiglu_linear_recomputes_activation():
+    from steptronoss_b200.ops.fused import swiglu_linear, swiglu_reference
+
+    torch.manual_seed(7)
+    h = torch.randn(640, 2 * 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (0.1 * torch.randn(384, 256, device="cuda")).to(torch.bfloat16).requires_grad_()
+    g = torch.randn(640, 384, device="cuda", dtype=torch.bfloat16)
+    y = swiglu_linear(h, w, 0.0)
+    y.backward(g)
+    hr, wr = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = swiglu_reference(hr, 0.0) @ wr.t()
+    yr.backward(g.float())
+    _close(y, yr.detach(), 2e-2)
+    _close(h.grad, hr.grad, 3e-2)
+    _close(w.grad, wr.grad, 3e-2)
+
+
 def test_embedding_fwd_bwd_sharded():
     from steptronoss_b200.ops import embedding
 
