@@ -154,7 +154,7 @@ class ColumnParallel(_Split):
 
 
 class RowParallel(_Split):
-    dim = 1
+    dim = -1  # also right for stacked expert weights [E, out, in]
 
 
 class Duplicate(ReshapeOp):
@@ -295,14 +295,15 @@ class FFNMergeGateUp(ReshapeOp):
         n = _size(self.group)
         kg = next(k for k in piece if "gate_proj" in k)
         ku = next(k for k in piece if "up_proj" in k)
-        shards = [torch.cat([piece[kg].chunk(n, 0)[r], piece[ku].chunk(n, 0)[r]], dim=0) for r in range(n)]
+        # dim -2 is the output dimension of both [F, H] and stacked-expert [E, F, H] weights
+        shards = [torch.cat([piece[kg].chunk(n, -2)[r], piece[ku].chunk(n, -2)[r]], dim=-2) for r in range(n)]
         return {kg.replace("gate_proj", "gate_up_proj"): shards}
 
     def backward(self, piece):
         (name, shards), = piece.items()
-        halves = [s.chunk(2, dim=0) for s in shards]
-        return {name.replace("gate_up_proj", "gate_proj"): torch.cat([h[0] for h in halves]),
-                name.replace("gate_up_proj", "up_proj"): torch.cat([h[1] for h in halves])}
+        halves = [s.chunk(2, dim=-2) for s in shards]
+        return {name.replace("gate_up_proj", "gate_proj"): torch.cat([h[0] for h in halves], dim=-2),
+                name.replace("gate_up_proj", "up_proj"): torch.cat([h[1] for h in halves], dim=-2)}
 
 
 class UnbindMoE(ReshapeOp):

@@ -73,6 +73,8 @@ class GroupedQueryAttention(nn.Module):
             raise ValueError(f"heads {nh}/{cfg.num_attention_groups} not divisible by TP={tp}")
         D = self.head_dim
         self.use_gate = bool(cfg.use_headwise_attn_gate)
+        self.num_heads, self.num_kv_heads = nh, cfg.num_attention_groups   # global (un-sharded) counts
+        self.wqkv_extra_dims = nh if self.use_gate else 0                    # head-wise gate rows of wqkv
         sp = bool(cfg.tp_cfg.sequence_parallel)
         dtype = cfg.params_dtype
         blocks = [nh * D, cfg.num_attention_groups * D, cfg.num_attention_groups * D]

@@ -1,0 +1,90 @@
+"""Step-3.5 decoder on CPU: sliding-window and full-attention layers, routed experts with a shared expert,
+head-wise attention gate; one training step and the HF <-> native weight mapping round trip."""
+import torch
+
+from steptronoss_b200.data.synthetic import SyntheticDataConfig
+from steptronoss_b200.exp.base_exp import GradientManagerConfig, ProfilerConfig
+from steptronoss_b200.exp.lr_schedulers import ConstantSchedulerConfig
+from steptronoss_b200.exp.ntp import NTPTrainerConfig, PretrainExp, PretrainMetricConfig
+from steptronoss_b200.models.step3p5 import Step3p5Block, Step3p5ModelConfig
+
+
+class _Exp(PretrainExp):
+    trainer_cfg = NTPTrainerConfig
+    model_cfg = Step3p5ModelConfig
+    optimizer_cfg = GradientManagerConfig
+    scheduler_cfg = ConstantSchedulerConfig
+    data_cfg = SyntheticDataConfig
+    metric_cfg = PretrainMetricConfig
+    profiler_cfg = ProfilerConfig
+
+
+def _make(layers=3, hidden=64, vocab=256):
+    e = _Exp()
+    m = e.model_cfg
+    m.num_layers, m.hidden_size, m.params_dtype = layers, hidden, torch.float32
+    m.variable_seq_lengths = True
+    m.swa_layer_list = [True, False, True][:layers]
+    for a, heads, window in ((m.attn_cfg, 4, None), (m.swa_cfg, 8, 16)):
+        a.num_attention_heads, a.num_attention_groups, a.head_dim, a.hidden_size = heads, 2, 16, hidden
+        a.rope_theta, a.use_qk_norm, a.use_headwise_attn_gate = 1e4, False, True
+        if window:
+            a.use_sliding_window, a.sliding_window_size = True, window
+    f = m.ffn_cfg
+    f.hidden_size, f.ffn_hidden_size = hidden, 96
+    mc = m.moe_cfg
+    mc.hidden_size, mc.moe_num_experts, mc.moe_top_k, mc.moe_hidden_size = hidden, 4, 2, 32
+    mc.moe_layer_list = [1, 2]
+    mc.share_expert_dim = 48
+    mc.enable_sigmoid_router = True
+    mc.enable_auxiliary_loss_free_load_balance = True
+    mc.router_bias_update_rate = 1e-3
+    m.tok_embed_cfg.vocab_size = m.out_embed_cfg.vocab_size = vocab
+    m.tok_embed_cfg.hidden_size = m.out_embed_cfg.hidden_size = hidden
+    m.parallel_cfg.expert_tensor_parallel_size = 1
+    t = e.trainer_cfg
+    t.global_batch_size, t.global_seq_length, t.train_iters, t.writer_backend = 2, 64, 4, []
+    e.scheduler_cfg.lr, e.scheduler_cfg.weight_decay, e.scheduler_cfg.warmup_schedule = 1e-3, 0.0, 0
+    e.data_cfg.min_doc_len, e.data_cfg.max_doc_len, e.data_cfg.pin_memory = 8, 32, False
+    return e
+
+
+def test_step3p5_layers_follow_the_swa_list_and_train():
+    exp = _make()
+    exp.seed = 0
+    tr = exp.trainer_cfg.get_trainer_cls()(exp=exp)
+    tr.before_train()
+    model = tr.models[0]
+    model = getattr(model, "module", model)
+    blocks = [model.layers[str(i)] for i in model.layer_ids]
+    assert all(isinstance(b, Step3p5Block) for b in blocks)
+    assert [b.attention.window for b in blocks] == [16, 0, 16]
+    assert [b.attention.num_heads for b in blocks] == [8, 4, 8]
+    assert not hasattr(blocks[0].feed_forward, "moe") and hasattr(blocks[1].feed_forward, "moe")
+    assert blocks[1].feed_forward.enable_share_expert
+    losses = []
+    for _ in range(4):
+        tr.train_step()
+        tr.iteration += 1
+        tr.training_log()
+        losses.append(tr.history[-1]["lm_loss"])
+    assert all(l == l for l in losses) and losses[-1] < losses[0]
+
+
+def test_step3p5_hf_mapping_round_trip():
+    exp = _make()
+    exp.seed = 1
+    tr = exp.trainer_cfg.get_trainer_cls()(exp=exp)
+    tr.before_train()
+    model = tr.models[0]
+    model = getattr(model, "module", model)
+    native = {k: v.detach().clone() for k, v in model.state_dict().items() if v is not None}
+    hf = model.reshaper.backward({k: v for k, v in native.items()})
+    assert "model.layers.0.self_attn.q_proj.weight" in hf and "model.layers.0.self_attn.g_proj.weight" in hf
+    assert "model.layers.1.moe.gate_proj.weight" in hf and hf["model.layers.1.moe.gate_proj.weight"].shape == (4, 32, 64)
+    assert "model.layers.1.share_expert.down_proj.weight" in hf and "model.layers.1.moe.router_bias" in hf
+    back = model.reshaper.forward(hf)
+    for k, v in native.items():
+        if k in back:
+            assert torch.equal(back[k], v), k
+    assert set(back) >= {k for k in native if "rope" not in k and "tokens_per_expert" not in k}
