@@ -97,6 +97,13 @@ class TrainerConfig(AbstractTrainerConfig):
                     tb_writer.add_text(str(k), "\n\n".join(v), iteration)
         return scalars
 
+    def is_data_source(self) -> bool:
+        """Ranks that read the data loader: (first or last pipeline stage), TP rank 0, CP rank 0."""
+        from ..parallel.state import PM
+
+        ends = PM.is_pipeline_first_stage(ignore_virtual=True) or PM.is_pipeline_last_stage(ignore_virtual=True)
+        return ends and PM.rank_in("TP") == 0 and PM.rank_in("CP") == 0
+
     def sync_get_data(self, data_iterator, preprocess=None) -> dict:
         """Fetch one micro-batch where the data lives and broadcast it to the ranks that need it.
 

@@ -310,6 +310,50 @@ class BaseGradientManager:
             self.muon.to(self.device)
 
 
+    def destroy_buffer(self) -> None:
+        """Free the fp32 gradient buffers (their contents are lost); ``build_buffer`` brings them back."""
+        for b in self.buckets.values():
+            b.grad_buf = None
+            for s in b.slots:
+                s.param.main_grad = None
+
+    def build_buffer(self) -> None:
+        for b in self.buckets.values():
+            if b.grad_buf is not None:
+                continue
+            b.grad_buf = torch.zeros(b.numel, dtype=torch.float32, device=self.device)
+            for s in b.slots:
+                s.param.main_grad = b.grad_buf[s.offset : s.offset + s.numel].view(s.param.shape)
+                s.param.grad_added_to_main_grad = False
+
+    def offload_params(self, non_blocking: bool = True) -> None:
+        """Move the flat parameter buffers to pinned host memory; parameters stay views of them."""
+        self.wait_param_gather()
+        for b in self.buckets.values():
+            if b.param_buf.device.type == "cpu":
+                continue
+            host = torch.empty(b.param_buf.shape, dtype=b.param_buf.dtype, device="cpu",
+                               pin_memory=torch.cuda.is_available())
+            host.copy_(b.param_buf, non_blocking=non_blocking)
+            self._reseat(b, host)
+        if torch.cuda.is_available():
+            torch.cuda.current_stream().synchronize()
+
+    def reload_params(self, non_blocking: bool = True) -> None:
+        for b in self.buckets.values():
+            if b.param_buf.device == self.device:
+                continue
+            dev = torch.empty(b.param_buf.shape, dtype=b.param_buf.dtype, device=self.device)
+            dev.copy_(b.param_buf, non_blocking=non_blocking)
+            self._reseat(b, dev)
+
+    @staticmethod
+    def _reseat(b: Bucket, buf: torch.Tensor) -> None:
+        b.param_buf = buf
+        for s in b.slots:
+            s.param.data = buf[s.offset : s.offset + s.numel].view(s.param.shape)
+
+
 class AccInFP32GradientManager(BaseGradientManager):
     """All-reduce gradients over DP; every rank keeps the full optimizer state."""
 
