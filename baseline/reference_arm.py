@@ -171,15 +171,12 @@ def _run(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    from steptronoss.utils import GlobalMetrics
-
     def step():
         trainer.train_step()
         trainer.iteration += 1
 
     for _ in range(args.warmup):
         step()
-        GlobalMetrics.reset() if hasattr(GlobalMetrics, "reset") else None
     barrier_sync()
     sampler = ClockSampler(os.path.join(os.path.dirname(HERE), "gpurun_out", "bench_clocks_reference.csv")) if rank == 0 else None
     if sampler:

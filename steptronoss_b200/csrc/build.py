@@ -71,7 +71,28 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    build_expstore(force)
     return LIB
+
+
+EXPSTORE_SRC = HERE / "expstore" / "expstore_server.cpp"
+EXPSTORE_BIN = OUT_DIR / "stb_expstore"
+
+
+def build_expstore(force: bool = False) -> Path:
+    """The experiment store server (plain C++, no CUDA): ``_native/stb_expstore``."""
+    OUT_DIR.mkdir(exist_ok=True)
+    stamp = OUT_DIR / "stb_expstore.sha"
+    dig = hashlib.sha256(EXPSTORE_SRC.read_bytes()).hexdigest()
+    if not force and EXPSTORE_BIN.exists() and stamp.exists() and stamp.read_text() == dig:
+        return EXPSTORE_BIN
+    cxx = os.environ.get("CXX", "g++")
+    r = subprocess.run([cxx, "-O2", "-std=c++17", "-o", str(EXPSTORE_BIN), str(EXPSTORE_SRC)],
+                       capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"building the experiment store failed:\n{r.stdout}\n{r.stderr}")
+    stamp.write_text(dig)
+    return EXPSTORE_BIN
 
 
 if __name__ == "__main__":

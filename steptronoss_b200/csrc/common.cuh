@@ -81,6 +81,21 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   return false;
 }
 
+// Same with a caller-chosen budget and an early exit when `*abort_flag` (shared memory) becomes non-zero:
+// for kernels whose pipeline is gated by another rank, where the budget has to cover rank skew.
+__device__ __forceinline__ bool mbar_wait_budget(uint64_t* bar, uint32_t parity, uint64_t budget_ns,
+                                                 const volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > budget_ns) return false;
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* d) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(d)) : "memory");

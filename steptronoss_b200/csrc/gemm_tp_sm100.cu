@@ -1,0 +1,851 @@
+// Sequence-parallel projections as single kernels over NVLink peer memory (sm_100a).
+//
+//   gemm_ag_kernel : C = all_gather_rows(x) * B^T.   Four "comm" warps in every CTA publish this rank's
+//                    rows into a symmetric staging slot and pull the peers' rows over NVLink (plain peer
+//                    loads) into a local gathered buffer, 16-row slices at a time, bumping a per-row-tile
+//                    counter.  The TMA producer of the tcgen05 GEMM waits for the counter of the row tile
+//                    it is about to load, so products of rows that have arrived overlap the transfer of the
+//                    rest.  Row tiles are visited own-rank first, then in ring order.
+//   gemm_rs_kernel : out = reduce_scatter_rows(A * B^T).  The epilogue TMA-stores every bf16 partial tile
+//                    into the row owner's receive slot (peer stores), the last store of a row tile raises a
+//                    flag in the owner's memory, and four "reduce" warps per CTA add the tp slots of the row
+//                    tiles this rank owns in fixed rank order (fp32) as they complete.  Row blocks are
+//                    computed next-rank first, own block last.
+//
+// They replace the NCCL collective + cuBLAS pairs of the reference's sequence-parallel linears
+// (steptronoss/core/tensor_parallel/layers.py:151-346, mappings.py:103-300).
+//
+// Cross-rank protocol.  Flags are uint32 words in each rank's symmetric flag page, written into the peer's
+// page with st.release.sys and read from the own page with ld.acquire.sys; they carry the call number
+// ("epoch", compared wrap-safe), so nothing is ever reset.  Staging and receive buffers have two slots
+// used alternately by epoch parity.  A slot written in call e was last read in call e-2, and no rank can
+// leave call e-1 before every peer has finished call e-2 (each call consumes data that every peer
+// produces inside the same call), so two slots need no further hand-shake.
+// GEMM tiles and the work of the comm / reduce warps are claimed from device counters, not assigned by CTA
+// index, so progress never depends on a CTA that is not resident (for instance while a collective of another
+// stream holds some SMs and is itself waiting for the peer).  Every wait is bounded by the caller's budget; on time-out
+// the kernel records a code in the status word, drains and returns.
+#include "common.cuh"
+#include <string.h>
+
+namespace stb {
+
+constexpr int kTpBlockM = 128;
+constexpr int kTpBlockN = 256;
+constexpr int kTpBlockK = 64;
+constexpr int kTpStages = 4;
+constexpr int kTpThreads = 320;      // producer, MMA, 4 epilogue warps, 4 comm/reduce warps
+constexpr int kTpAuxThreads = 128;
+constexpr int kTpParts = 8;          // a 128-row tile is moved as 8 slices of 16 rows
+constexpr int kTpPartRows = kTpBlockM / kTpParts;
+constexpr int kTpMaxRanks = 8;
+
+// Layout of the symmetric flag page (uint32 words).
+constexpr int kFlagAgReady = 0;                   // [slot 2][src 8]
+constexpr int kFlagRsBase = 64;                   // [slot 2][row tile kTpMaxRowTiles][src 8]
+constexpr int kTpMaxRowTiles = 1024;
+constexpr int kFlagWords = kFlagRsBase + 2 * kTpMaxRowTiles * kTpMaxRanks;
+
+// Layout of the local counter scratch (uint32 words), zeroed by the host function before each launch.
+constexpr int kCtrClaim = 0;      // next comm / reduce unit
+constexpr int kCtrOwnDone = 1;    // AG: own-rank units finished
+constexpr int kCtrTileClaim = 2;  // next GEMM tile
+constexpr int kSchedDepth = 4;    // claimed tiles the producer may run ahead of the slowest consumer
+constexpr int kCtrTiles = 8;      // AG: [row tile] slices landed;  RS: [row tile] epilogue warps finished
+
+constexpr int kTpABytes = kTpBlockM * kTpBlockK * 2;
+constexpr int kTpBBytes = kTpBlockN * kTpBlockK * 2;
+constexpr int kTpStageBytes = kTpABytes + kTpBBytes;
+constexpr int kTpStoreBytes = 4 * 2 * 4096;
+constexpr int kTpSmem = kTpStages * kTpStageBytes + kTpStoreBytes + 256 + 1024;
+
+struct PeerPtrs {
+  void* p[kTpMaxRanks];
+};
+struct TmapArray {
+  CUtensorMap m[kTpMaxRanks];
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_gpu_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
+__device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+// Bounded spin until *p >= target (wrap-safe). Returns false on time-out or when the CTA has aborted.
+template <bool SYS>
+__device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target, uint64_t budget_ns,
+                                             const volatile int* abort_flag) {
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t i = 0;; ++i) {
+    const uint32_t v = SYS ? ld_acquire_sys(p) : ld_acquire_gpu(p);
+    if (static_cast<int32_t>(v - target) >= 0) return true;
+    if ((i & 15u) == 15u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > budget_ns) return false;
+    }
+    if (i >= 4) __nanosleep(i < 64 ? 40 : 200);
+  }
+}
+
+__device__ __forceinline__ void aux_barrier() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+
+// logical row-tile index -> physical row tile; `first_block` is the rank block visited first
+__device__ __forceinline__ int physical_m_tile(int logical, int tiles_per_rank, int first_block, int tp) {
+  const int blk = logical / tiles_per_rank;
+  return ((first_block + blk) % tp) * tiles_per_rank + logical % tiles_per_rank;
+}
+// Round-robin over the rank blocks (next rank first): the tiles bound for each peer are spread over the whole
+// kernel, so the NVLink write rate is 1/tp-th of the epilogue's output rate instead of all of it for a while.
+__device__ __forceinline__ int interleaved_m_tile(int logical, int tiles_per_rank, int rank, int tp) {
+  return ((rank + 1 + logical % tp) % tp) * tiles_per_rank + logical / tp;
+}
+
+// Tile order: bands of 8 row tiles x all column tiles, so concurrently running CTAs share operands in L2
+// and row tiles complete (or are needed) progressively.
+__device__ __forceinline__ void decode_tp_tile(int tile, int num_m, int num_n, int& m_logical, int& n_tile) {
+  constexpr int kBand = 8;
+  const int in_band = kBand * num_n;
+  const int band = tile / in_band;
+  const int first_m = band * kBand;
+  const int band_rows = min(num_m - first_m, kBand);
+  const int r = tile - band * in_band;
+  m_logical = first_m + r % band_rows;
+  n_tile = r / band_rows;
+}
+
+struct TpCommon {
+  int M, N, K;          // M = tp * rows_local
+  int rank, tp, rows_local;
+  uint32_t epoch;
+  uint32_t* ctrs;       // local counter scratch
+  unsigned long long wait_ns;
+  int* status;
+};
+
+struct TpShared {
+  uint8_t* smem;
+  uint8_t* store_stage;
+  uint64_t *full_bar, *empty_bar, *tmem_full, *tmem_empty;
+  uint32_t* tmem_slot;
+  volatile int* abort_flag;
+  volatile int* claim_slot;
+  uint64_t *sched_full, *sched_empty;
+  volatile int* tile_ring;
+};
+
+__device__ __forceinline__ TpShared tp_carve(uint8_t* smem_raw) {
+  TpShared s;
+  s.smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  s.store_stage = s.smem + kTpStages * kTpStageBytes;
+  s.full_bar = reinterpret_cast<uint64_t*>(s.store_stage + kTpStoreBytes);
+  s.empty_bar = s.full_bar + kTpStages;
+  s.tmem_full = s.empty_bar + kTpStages;
+  s.tmem_empty = s.tmem_full + 2;
+  s.tmem_slot = reinterpret_cast<uint32_t*>(s.tmem_empty + 2);
+  s.abort_flag = reinterpret_cast<volatile int*>(s.tmem_slot + 1);
+  s.claim_slot = s.abort_flag + 1;
+  s.sched_full = s.tmem_empty + 4;   // 8-byte aligned, past the three words above
+  s.sched_empty = s.sched_full + kSchedDepth;
+  s.tile_ring = reinterpret_cast<volatile int*>(s.sched_empty + kSchedDepth);
+  return s;
+}
+
+__device__ __forceinline__ void tp_prologue(const TpShared& s, int warp) {
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kTpStages; ++i) {
+      mbar_init(&s.full_bar[i], 1);
+      mbar_init(&s.empty_bar[i], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&s.tmem_full[a], 1);
+      mbar_init(&s.tmem_empty[a], 4);
+    }
+    for (int i = 0; i < kSchedDepth; ++i) {
+      mbar_init(&s.sched_full[i], 1);
+      mbar_init(&s.sched_empty[i], 5);  // MMA thread + 4 epilogue warps
+    }
+    *s.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(s.tmem_slot, 2 * kTpBlockN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+}
+
+__device__ __forceinline__ void tp_epilogue_sync(const TpShared& s, int warp, uint32_t tmem_base) {
+  __syncthreads();
+  if (*s.abort_flag) drain_delay();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * kTpBlockN);
+  }
+}
+
+// Tile scheduler: the producer thread claims tile numbers from a device counter and hands them to the MMA
+// thread and the epilogue warps through a small ring in shared memory.  -1 ends the stream, -2 = failed wait.
+// `claimed` holds a tile number claimed ahead of time, so the latency of the atomic is off the critical path.
+__device__ __forceinline__ int sched_produce(const TpShared& s, const TpCommon& c, uint32_t q, int num_tiles,
+                                             uint32_t& claimed) {
+  const int slot = q % kSchedDepth;
+  if (!mbar_wait_budget(&s.sched_empty[slot], ((q / kSchedDepth) & 1) ^ 1, c.wait_ns, s.abort_flag)) return -2;
+  int tile = static_cast<int>(claimed);
+  if (tile >= num_tiles) tile = -1;
+  else claimed = atomicAdd(&c.ctrs[kCtrTileClaim], 1u);
+  s.tile_ring[slot] = tile;
+  mbar_arrive(&s.sched_full[slot]);
+  return tile;
+}
+__device__ __forceinline__ int sched_consume(const TpShared& s, const TpCommon& c, uint32_t q) {
+  const int slot = q % kSchedDepth;
+  if (!mbar_wait_budget(&s.sched_full[slot], (q / kSchedDepth) & 1, c.wait_ns, s.abort_flag)) return -2;
+  const int tile = s.tile_ring[slot];
+  mbar_arrive(&s.sched_empty[slot]);
+  return tile;
+}
+// Producer side of a failed wait / end of stream: wake the consumers with the end marker where possible.
+__device__ __forceinline__ void sched_fail(const TpShared& s, const TpCommon& c, int code) {
+  if (!*s.abort_flag) report_error(c.status, code);
+  *s.abort_flag = 1;
+}
+
+// One k-block of operand loads for the 128 x 256 tile at (m0, n0).
+template <bool B_MN>
+__device__ __forceinline__ void tp_load_stage(const TpShared& s, int stage, const CUtensorMap* ta, const CUtensorMap* tb,
+                                              int k0, int m0, int n0) {
+  uint8_t* sa = s.smem + stage * kTpStageBytes;
+  uint8_t* sb = sa + kTpABytes;
+  mbar_arrive_expect_tx(&s.full_bar[stage], kTpStageBytes);
+  tma_load_2d(sa, ta, &s.full_bar[stage], k0, m0);
+  if constexpr (!B_MN) {
+    tma_load_2d(sb, tb, &s.full_bar[stage], k0, n0);
+  } else {
+#pragma unroll
+    for (int j = 0; j < kTpBlockN / 64; ++j) tma_load_2d(sb + j * (kTpBlockK * 128), tb, &s.full_bar[stage], n0 + j * 64, k0);
+  }
+}
+
+// MMA issue loop shared by both kernels (A is always K-major here).
+template <bool B_MN>
+__device__ __forceinline__ void tp_mma_loop(const TpShared& s, const TpCommon& c, uint32_t tmem_base, int k_blocks) {
+  constexpr uint32_t idesc = umma_idesc_bf16(kTpBlockM, kTpBlockN, 0, B_MN ? 1 : 0);
+  uint32_t it = 0, local_tile = 0;
+  for (;; ++local_tile) {
+    const int tile = sched_consume(s, c, local_tile);
+    if (tile < 0) {
+      if (tile == -2) sched_fail(s, c, kErrMmaWaitFull);
+      return;
+    }
+    const int acc = local_tile & 1;
+    if (!mbar_wait_budget(&s.tmem_empty[acc], ((local_tile >> 1) & 1) ^ 1, c.wait_ns, s.abort_flag)) {
+      sched_fail(s, c, kErrMmaWaitTmem);
+      return;
+    }
+    tc_fence_after();
+    const uint32_t d_tmem = tmem_base + acc * kTpBlockN;
+    for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+      const int st = it % kTpStages;
+      if (!mbar_wait_budget(&s.full_bar[st], (it / kTpStages) & 1, c.wait_ns, s.abort_flag)) {
+        sched_fail(s, c, kErrMmaWaitFull);
+        return;
+      }
+      tc_fence_after();
+      const uint32_t sa = smem_u32(s.smem + st * kTpStageBytes);
+      const uint32_t sb = sa + kTpABytes;
+#pragma unroll
+      for (int k = 0; k < kTpBlockK / 16; ++k) {
+        const uint64_t da = umma_smem_desc(sa + k * 32, 16, 1024);
+        const uint64_t db = B_MN ? umma_smem_desc(sb + k * (16 * 128), kTpBlockK * 128, 1024)
+                                 : umma_smem_desc(sb + k * 32, 16, 1024);
+        umma_bf16(d_tmem, da, db, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+      }
+      umma_commit(&s.empty_bar[st]);
+    }
+    umma_commit(&s.tmem_full[acc]);
+  }
+}
+
+// Epilogue of one warp for one accumulator: TMEM -> bf16 -> swizzled smem -> TMA stores through `tc` at
+// (n0 + .., row0).  Returns with the stores committed (not waited).
+__device__ __forceinline__ void tp_store_tile(const TpShared& s, uint32_t tmem_base, int acc, int quarter, int ep_warp,
+                                              int lane, const CUtensorMap* tc, int n0, int row0, int N,
+                                              uint32_t& store_count) {
+  uint8_t* my_stage = s.store_stage + ep_warp * 8192;
+#pragma unroll 1
+  for (int c = 0; c < kTpBlockN / 64; ++c) {
+    uint32_t v[64];
+    {
+      uint32_t (&lo)[32] = *reinterpret_cast<uint32_t (*)[32]>(&v[0]);
+      uint32_t (&hi)[32] = *reinterpret_cast<uint32_t (*)[32]>(&v[32]);
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * kTpBlockN + c * 64;
+      tmem_ld_32x32(taddr, lo);
+      tmem_ld_32x32(taddr + 32, hi);
+      tmem_wait_ld();
+    }
+    const int col0 = n0 + c * 64;
+    if (col0 >= N) continue;  // warp-uniform
+    uint8_t* buf = my_stage + (store_count & 1) * 4096;
+    if (store_count >= 2) {
+      if (lane == 0) tma_store_wait_read<1>();
+      __syncwarp();
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint4 ch;
+      ch.x = pack_bf16(__uint_as_float(v[8 * j]), __uint_as_float(v[8 * j + 1]));
+      ch.y = pack_bf16(__uint_as_float(v[8 * j + 2]), __uint_as_float(v[8 * j + 3]));
+      ch.z = pack_bf16(__uint_as_float(v[8 * j + 4]), __uint_as_float(v[8 * j + 5]));
+      ch.w = pack_bf16(__uint_as_float(v[8 * j + 6]), __uint_as_float(v[8 * j + 7]));
+      *reinterpret_cast<uint4*>(buf + lane * 128 + ((j ^ (lane & 7)) << 4)) = ch;
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(tc, buf, col0, row0);
+      tma_store_commit();
+    }
+    ++store_count;
+  }
+}
+
+// Claim the next unit of comm / reduce work for the 128 aux threads of this CTA.
+__device__ __forceinline__ int aux_claim(const TpShared& s, uint32_t* ctrs, int tid) {
+  if (tid == 0) *s.claim_slot = static_cast<int>(atomicAdd(&ctrs[kCtrClaim], 1u));
+  aux_barrier();
+  const int u = *s.claim_slot;
+  aux_barrier();
+  return u;
+}
+
+// Thread 0 of the aux group waits, every aux thread learns the outcome.
+template <bool SYS>
+__device__ __forceinline__ bool aux_wait_flag(const TpShared& s, const TpCommon& c, const uint32_t* flag,
+                                              uint32_t target, int tid) {
+  if (tid == 0) *s.claim_slot = wait_flag_ge<SYS>(flag, target, c.wait_ns, s.abort_flag) ? 1 : 0;
+  aux_barrier();
+  const bool ok = *s.claim_slot != 0;
+  aux_barrier();
+  return ok;
+}
+
+// ===================================================================================== all-gather -> GEMM
+struct AgArgs {
+  TpCommon c;
+  const __nv_bfloat16* x_local;   // [rows_local][ldx]
+  long long ldx;
+  __nv_bfloat16* gathered;        // [M][K] local, contiguous
+  PeerPtrs stage;                 // this call's staging slot of every rank, [rows_local][K]
+  PeerPtrs flags;                 // flag page of every rank
+  int ldc;
+};
+
+template <bool B_MN>
+__global__ void __launch_bounds__(kTpThreads, 1)
+gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_x,
+               const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_c, const AgArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const TpShared s = tp_carve(smem_raw);
+  const TpCommon& c = a.c;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = c.M / kTpBlockM;
+  const int num_n = (c.N + kTpBlockN - 1) / kTpBlockN;
+  const int num_tiles = num_m * num_n;
+  const int tiles_per_rank = c.rows_local / kTpBlockM;
+  const int k_blocks = (c.K + kTpBlockK - 1) / kTpBlockK;
+  const int slot = c.epoch & 1;
+
+  tp_prologue(s, warp);
+  const uint32_t tmem_base = *s.tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      unsigned long long ready_mask = 0;  // row tiles < 64 already seen complete (and proxy-fenced) by this thread
+      uint32_t claimed = atomicAdd(&c.ctrs[kCtrTileClaim], 1u);
+      for (uint32_t q = 0;; ++q) {
+        const int tile = sched_produce(s, c, q, num_tiles, claimed);
+        if (tile < 0) {
+          if (tile == -2) sched_fail(s, c, kErrProducerWait);
+          break;
+        }
+        int m_log, n_tile;
+        decode_tp_tile(tile, num_m, num_n, m_log, n_tile);
+        const int m_tile = physical_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
+        // Own rows are read where the caller left them; peers' rows must have landed in the gathered buffer
+        // (comm warps of any CTA wrote them).
+        const bool own = (m_tile / tiles_per_rank) == c.rank;
+        if (!own && !(m_tile < 64 && ((ready_mask >> m_tile) & 1ull))) {
+          if (!wait_flag_ge<false>(&c.ctrs[kCtrTiles + m_tile], kTpParts, c.wait_ns, s.abort_flag)) {
+            sched_fail(s, c, kErrPeerFlagWait);
+            break;
+          }
+          fence_proxy_async_global();  // generic-proxy stores, acquired above -> visible to the TMA reads
+          if (m_tile < 64) ready_mask |= 1ull << m_tile;
+        }
+        const CUtensorMap* ta = own ? &tmap_x : &tmap_a;
+        const int a_row = own ? (m_tile % tiles_per_rank) * kTpBlockM : m_tile * kTpBlockM;
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int st = it % kTpStages;
+          if (!mbar_wait_budget(&s.empty_bar[st], ((it / kTpStages) & 1) ^ 1, c.wait_ns, s.abort_flag)) {
+            sched_fail(s, c, kErrProducerWait);
+            ok = false;
+            break;
+          }
+          tp_load_stage<B_MN>(s, st, ta, &tmap_b, kb * kTpBlockK, a_row, n_tile * kTpBlockN);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) tp_mma_loop<B_MN>(s, c, tmem_base, k_blocks);
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;
+    uint32_t local_tile = 0, store_count = 0;
+    for (;;) {
+      int tile = 0;
+      if (lane == 0) tile = sched_consume(s, c, local_tile);
+      tile = __shfl_sync(0xffffffffu, tile, 0);
+      if (tile < 0) {
+        if (tile == -2 && lane == 0) sched_fail(s, c, kErrEpilogueWait);
+        break;
+      }
+      int m_log, n_tile;
+      decode_tp_tile(tile, num_m, num_n, m_log, n_tile);
+      const int m_tile = physical_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
+      const int acc = local_tile & 1;
+      if (!mbar_wait_budget(&s.tmem_full[acc], (local_tile >> 1) & 1, c.wait_ns, s.abort_flag)) {
+        sched_fail(s, c, kErrEpilogueWait);
+        break;
+      }
+      tc_fence_after();
+      tp_store_tile(s, tmem_base, acc, quarter, warp - 2, lane, &tmap_c, n_tile * kTpBlockN,
+                    m_tile * kTpBlockM + quarter * 32, c.N, store_count);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s.tmem_empty[acc]);
+      ++local_tile;
+    }
+    if (lane == 0) tma_store_wait<0>();
+  } else {
+    // ------------------------------------------------------------------ comm warps
+    const int tid = threadIdx.x - 192;
+    const int own_units = tiles_per_rank * kTpParts;
+    const int total_units = num_m * kTpParts;
+    const int vec_per_row = c.K / 8;
+    const int total_vec = kTpPartRows * vec_per_row;
+    uint32_t src_ready = 1u << c.rank;
+    bool failed = false;
+    for (;;) {
+      const int u = aux_claim(s, c.ctrs, tid);
+      if (u >= total_units || failed || *s.abort_flag) break;
+      const int m_tile = physical_m_tile(u / kTpParts, tiles_per_rank, c.rank, c.tp);
+      const int part = u % kTpParts;
+      const int src = m_tile / tiles_per_rank;
+      const long long src_row = static_cast<long long>(m_tile % tiles_per_rank) * kTpBlockM + part * kTpPartRows;
+      __nv_bfloat16* dst = a.gathered + (static_cast<long long>(m_tile) * kTpBlockM + part * kTpPartRows) * c.K;
+      const bool own = (src == c.rank);
+      if (!own && !((src_ready >> src) & 1u)) {
+        const uint32_t* flag = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagAgReady + slot * 8 + src;
+        if (!aux_wait_flag<true>(s, c, flag, c.epoch, tid)) {
+          if (tid == 0) {
+            report_error(c.status, kErrPeerFlagWait);
+            *s.abort_flag = 1;
+          }
+          failed = true;
+          continue;  // next claim ends the loop for all 128 threads together
+        }
+        src_ready |= 1u << src;
+      }
+      const __nv_bfloat16* from = own ? a.x_local + src_row * a.ldx
+                                      : reinterpret_cast<const __nv_bfloat16*>(a.stage.p[src]) + src_row * c.K;
+      const long long from_ld = own ? a.ldx : c.K;
+      __nv_bfloat16* stage_dst = own ? reinterpret_cast<__nv_bfloat16*>(a.stage.p[c.rank]) + src_row * c.K : nullptr;
+      for (int base = tid; base < total_vec; base += kTpAuxThreads * 8) {
+        uint4 v[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int idx = base + q * kTpAuxThreads;
+          if (idx < total_vec) {
+            const int r = idx / vec_per_row, col = idx - r * vec_per_row;
+            v[q] = ld_cg_v4(from + r * from_ld + col * 8);
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const int idx = base + q * kTpAuxThreads;
+          if (idx < total_vec) {
+            *reinterpret_cast<uint4*>(dst + static_cast<long long>(idx) * 8) = v[q];
+            if (own) *reinterpret_cast<uint4*>(stage_dst + static_cast<long long>(idx) * 8) = v[q];
+          }
+        }
+      }
+      __threadfence_system();
+      aux_barrier();
+      if (tid == 0) {
+        red_release_gpu_add(&c.ctrs[kCtrTiles + m_tile], 1u);
+        if (own) {
+          const uint32_t done = atomicAdd(&c.ctrs[kCtrOwnDone], 1u);
+          if (done == static_cast<uint32_t>(own_units - 1)) {
+            // every own-rank slice is in the staging slot: tell the peers
+            __threadfence_system();
+            for (int r = 0; r < c.tp; ++r)
+              if (r != c.rank)
+                st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[r]) + kFlagAgReady + slot * 8 + c.rank, c.epoch);
+          }
+        }
+      }
+    }
+  }
+  tp_epilogue_sync(s, warp, tmem_base);
+}
+
+// ===================================================================================== GEMM -> reduce-scatter
+struct RsArgs {
+  TpCommon c;
+  __nv_bfloat16* out;             // [rows_local][ldo]
+  long long ldo;
+  const __nv_bfloat16* recv_self; // this call's receive slot of this rank: [tp src][rows_local][N]
+  PeerPtrs flags;                 // flag page of every rank
+};
+
+template <bool B_MN>
+__global__ void __launch_bounds__(kTpThreads, 1)
+gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ TmapArray tmap_dst, const RsArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const TpShared s = tp_carve(smem_raw);
+  const TpCommon& c = a.c;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_m = c.M / kTpBlockM;
+  const int num_n = (c.N + kTpBlockN - 1) / kTpBlockN;
+  const int num_tiles = num_m * num_n;
+  const int tiles_per_rank = c.rows_local / kTpBlockM;
+  const int k_blocks = (c.K + kTpBlockK - 1) / kTpBlockK;
+  const int slot = c.epoch & 1;
+
+  tp_prologue(s, warp);
+  const uint32_t tmem_base = *s.tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      uint32_t claimed = atomicAdd(&c.ctrs[kCtrTileClaim], 1u);
+      for (uint32_t q = 0;; ++q) {
+        const int tile = sched_produce(s, c, q, num_tiles, claimed);
+        if (tile < 0) {
+          if (tile == -2) sched_fail(s, c, kErrProducerWait);
+          break;
+        }
+        int m_log, n_tile;
+        decode_tp_tile(tile, num_m, num_n, m_log, n_tile);
+        const int m_tile = interleaved_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int st = it % kTpStages;
+          if (!mbar_wait_budget(&s.empty_bar[st], ((it / kTpStages) & 1) ^ 1, c.wait_ns, s.abort_flag)) {
+            sched_fail(s, c, kErrProducerWait);
+            ok = false;
+            break;
+          }
+          tp_load_stage<B_MN>(s, st, &tmap_a, &tmap_b, kb * kTpBlockK, m_tile * kTpBlockM, n_tile * kTpBlockN);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) tp_mma_loop<B_MN>(s, c, tmem_base, k_blocks);
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue: partial tiles to their owners
+    const int quarter = warp & 3;
+    uint32_t local_tile = 0, store_count = 0;
+    int pending_m = -1;  // row tile whose stores are issued but not yet known complete
+    // lane 0: the bulk stores of `m_tile` by this warp have been performed -> count it, last one raises the flag
+    auto signal_tile = [&](int m_tile) {
+      fence_proxy_async_global();
+      __threadfence_system();
+      const uint32_t done = atomicAdd(&c.ctrs[kCtrTiles + m_tile], 1u);
+      if (done == static_cast<uint32_t>(num_n * 4 - 1)) {
+        __threadfence_system();
+        const int dest = m_tile / tiles_per_rank, m_local = m_tile % tiles_per_rank;
+        st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[dest]) + kFlagRsBase +
+                           (slot * kTpMaxRowTiles + m_local) * kTpMaxRanks + c.rank,
+                       c.epoch);
+      }
+    };
+    for (;;) {
+      int tile = 0;
+      if (lane == 0) tile = sched_consume(s, c, local_tile);
+      tile = __shfl_sync(0xffffffffu, tile, 0);
+      if (tile < 0) {
+        if (tile == -2 && lane == 0) sched_fail(s, c, kErrEpilogueWait);
+        break;
+      }
+      int m_log, n_tile;
+      decode_tp_tile(tile, num_m, num_n, m_log, n_tile);
+      const int m_tile = interleaved_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
+      const int dest = m_tile / tiles_per_rank;
+      const int m_local = m_tile % tiles_per_rank;
+      const int acc = local_tile & 1;
+      if (!mbar_wait_budget(&s.tmem_full[acc], (local_tile >> 1) & 1, c.wait_ns, s.abort_flag)) {
+        sched_fail(s, c, kErrEpilogueWait);
+        break;
+      }
+      tc_fence_after();
+      // receive slot of `dest`: rows [rank * rows_local, (rank + 1) * rows_local) belong to this sender
+      const uint32_t before = store_count;
+      tp_store_tile(s, tmem_base, acc, quarter, warp - 2, lane, &tmap_dst.m[dest], n_tile * kTpBlockN,
+                    c.rank * c.rows_local + m_local * kTpBlockM + quarter * 32, c.N, store_count);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&s.tmem_empty[acc]);
+        if (pending_m >= 0) {
+          // bulk groups retire in order: with at most this tile's groups outstanding, the previous tile is done
+          if (store_count - before == 4) tma_store_wait<4>();
+          else tma_store_wait<0>();
+          signal_tile(pending_m);
+          if (store_count - before != 4) {
+            signal_tile(m_tile);
+            pending_m = -1;
+          } else {
+            pending_m = m_tile;
+          }
+        } else {
+          pending_m = m_tile;
+        }
+      }
+      __syncwarp();
+      ++local_tile;
+    }
+    if (lane == 0) {
+      tma_store_wait<0>();
+      if (pending_m >= 0) signal_tile(pending_m);
+    }
+  } else {
+    // ------------------------------------------------------------------ reduce warps: rows this rank owns
+    const int tid = threadIdx.x - 192;
+    const int total_units = tiles_per_rank * kTpParts;
+    const int vec_per_row = c.N / 8;
+    const int total_vec = kTpPartRows * vec_per_row;
+    const long long slot_stride = static_cast<long long>(c.rows_local) * c.N;
+    const uint32_t* my_flags = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagRsBase +
+                               slot * kTpMaxRowTiles * kTpMaxRanks;
+    int ready_tile = -1;
+    bool failed = false;
+    for (;;) {
+      const int u = aux_claim(s, c.ctrs, tid);
+      if (u >= total_units || failed || *s.abort_flag) break;
+      const int m_local = u / kTpParts, part = u % kTpParts;
+      if (m_local != ready_tile) {
+        bool ok = true;
+        for (int src = 0; src < c.tp && ok; ++src)
+          ok = aux_wait_flag<true>(s, c, my_flags + m_local * kTpMaxRanks + src, c.epoch, tid);
+        if (!ok) {
+          if (tid == 0) {
+            report_error(c.status, kErrPeerFlagWait);
+            *s.abort_flag = 1;
+          }
+          failed = true;
+          continue;
+        }
+        ready_tile = m_local;
+      }
+      const long long row0 = static_cast<long long>(m_local) * kTpBlockM + part * kTpPartRows;
+      const __nv_bfloat16* in0 = a.recv_self + row0 * c.N;
+      for (int idx = tid; idx < total_vec; idx += kTpAuxThreads) {
+        const int r = idx / vec_per_row, col = idx - r * vec_per_row;
+        float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        uint4 v[kTpMaxRanks];
+#pragma unroll
+        for (int src = 0; src < kTpMaxRanks; ++src)
+          if (src < c.tp) v[src] = ld_cg_v4(in0 + src * slot_stride + static_cast<long long>(idx) * 8);
+#pragma unroll
+        for (int src = 0; src < kTpMaxRanks; ++src) {
+          if (src < c.tp) {
+            f[0] += bf16_lo(v[src].x); f[1] += bf16_hi(v[src].x); f[2] += bf16_lo(v[src].y); f[3] += bf16_hi(v[src].y);
+            f[4] += bf16_lo(v[src].z); f[5] += bf16_hi(v[src].z); f[6] += bf16_lo(v[src].w); f[7] += bf16_hi(v[src].w);
+          }
+        }
+        uint4 o;
+        o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+        o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+        *reinterpret_cast<uint4*>(a.out + (row0 + r) * a.ldo + col * 8) = o;
+      }
+    }
+  }
+  tp_epilogue_sync(s, warp, tmem_base);
+}
+
+template <typename Kern>
+static int tp_configure(Kern kern) {
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kTpSmem);
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+static int tp_check(int rows_local, int N, int K, int tp, int rank) {
+  if (tp < 2 || tp > kTpMaxRanks || rank < 0 || rank >= tp) return -kErrBadArgument;
+  if (rows_local <= 0 || (rows_local % kTpBlockM) || rows_local / kTpBlockM > kTpMaxRowTiles) return -kErrBadArgument;
+  if (K <= 0 || (K & 7) || N < 0 || (N & 7)) return -kErrBadArgument;
+  return 0;
+}
+
+}  // namespace stb
+
+using namespace stb;
+
+// Words of symmetric flag memory a rank must provide (zero-initialised once, before the first call).
+extern "C" int stb_tp_flag_words() { return kFlagWords; }
+// Words of local counter scratch needed for `row_tiles` = tp * rows_local / 128 row tiles.
+extern "C" int stb_tp_ctr_words(int row_tiles) { return kCtrTiles + row_tiles; }
+
+// C[tp*rows_local, N] = all_gather_rows(x_local) * B^T (b_mn_major = 0, B stored [N][ldb]) or * B
+// (b_mn_major = 1, B stored [K][ldb]); `gathered` [tp*rows_local][K] receives the gathered rows.
+// N = 0 gathers only.  stage_ptrs[r] / flag_ptrs[r]: rank r's staging slot for this call (slot = epoch & 1,
+// at least rows_local*K bf16) and flag page, as mapped into this process.  epoch: 1, 2, 3, ... per group,
+// the same on every rank.  ctrs: local scratch of stb_tp_ctr_words(row tiles) words.
+extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* gathered, void* const* stage_ptrs,
+                                void* const* flag_ptrs, const void* B, void* C, int rows_local, int N, int K, int ldb,
+                                int ldc, int b_mn_major, int rank, int tp, unsigned epoch, void* ctrs,
+                                unsigned long long wait_ns, int* status, cudaStream_t stream) {
+  int r = tp_check(rows_local, N, K, tp, rank);
+  if (r) return r;
+  if ((ldx & 7) || (N > 0 && ((ldb & 7) || (ldc & 7)))) return -kErrBadArgument;
+  const int M = tp * rows_local;
+  CUtensorMap ta, tx, tb, tc;
+  r = make_tmap_2d_bf16(&ta, gathered, K, M, static_cast<uint64_t>(K) * 2, kTpBlockK, kTpBlockM, 1);
+  if (r) return r;
+  r = make_tmap_2d_bf16(&tx, x_local, K, rows_local, static_cast<uint64_t>(ldx) * 2, kTpBlockK, kTpBlockM, 1);
+  if (r) return r;
+  if (N > 0) {
+    if (!b_mn_major) r = make_tmap_2d_bf16(&tb, B, K, N, static_cast<uint64_t>(ldb) * 2, kTpBlockK, kTpBlockN, 1);
+    else r = make_tmap_2d_bf16(&tb, B, N, K, static_cast<uint64_t>(ldb) * 2, 64, kTpBlockK, 1);
+    if (r) return r;
+    r = make_tmap_2d(&tc, C, 2, N, M, static_cast<uint64_t>(ldc) * 2, 64, 32, 1);
+    if (r) return r;
+  } else {
+    tb = ta;
+    tc = ta;
+  }
+  AgArgs a{};
+  a.c.M = M; a.c.N = N; a.c.K = K; a.c.rank = rank; a.c.tp = tp; a.c.rows_local = rows_local;
+  a.c.epoch = epoch; a.c.ctrs = static_cast<uint32_t*>(ctrs); a.c.wait_ns = wait_ns; a.c.status = status;
+  a.x_local = static_cast<const __nv_bfloat16*>(x_local);
+  a.ldx = ldx;
+  a.gathered = static_cast<__nv_bfloat16*>(gathered);
+  a.ldc = ldc;
+  for (int i = 0; i < tp; ++i) {
+    a.stage.p[i] = stage_ptrs[i];
+    a.flags.p[i] = flag_ptrs[i];
+  }
+  cudaError_t e = cudaMemsetAsync(ctrs, 0, sizeof(uint32_t) * (kCtrTiles + M / kTpBlockM), stream);
+  if (e != cudaSuccess) return -static_cast<int>(e);
+  static bool configured[2] = {false, false};
+  if (!configured[b_mn_major ? 1 : 0]) {
+    r = b_mn_major ? tp_configure(gemm_ag_kernel<true>) : tp_configure(gemm_ag_kernel<false>);
+    if (r) return r;
+    configured[b_mn_major ? 1 : 0] = true;
+  }
+  const int grid = sm_count();
+  if (b_mn_major) gemm_ag_kernel<true><<<grid, kTpThreads, kTpSmem, stream>>>(ta, tx, tb, tc, a);
+  else gemm_ag_kernel<false><<<grid, kTpThreads, kTpSmem, stream>>>(ta, tx, tb, tc, a);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+// out[rows_local, N] = reduce_scatter_rows(A[tp*rows_local, K] * B^T or * B).  recv_ptrs[r]: rank r's receive
+// slot for this call (slot = epoch & 1; tp*rows_local*N bf16), flag_ptrs[r]: rank r's flag page.
+extern "C" int stb_gemm_rs_bf16(const void* A, int lda, const void* B, int ldb, int b_mn_major, void* out,
+                                long long ldo, void* const* recv_ptrs, void* const* flag_ptrs, int rows_local, int N,
+                                int K, int rank, int tp, unsigned epoch, void* ctrs, unsigned long long wait_ns,
+                                int* status, cudaStream_t stream) {
+  int r = tp_check(rows_local, N, K, tp, rank);
+  if (r) return r;
+  if (N <= 0 || (lda & 7) || (ldb & 7) || (ldo & 7)) return -kErrBadArgument;
+  const int M = tp * rows_local;
+  CUtensorMap ta, tb;
+  TmapArray td;
+  r = make_tmap_2d_bf16(&ta, A, K, M, static_cast<uint64_t>(lda) * 2, kTpBlockK, kTpBlockM, 1);
+  if (r) return r;
+  if (!b_mn_major) r = make_tmap_2d_bf16(&tb, B, K, N, static_cast<uint64_t>(ldb) * 2, kTpBlockK, kTpBlockN, 1);
+  else r = make_tmap_2d_bf16(&tb, B, N, K, static_cast<uint64_t>(ldb) * 2, 64, kTpBlockK, 1);
+  if (r) return r;
+  for (int i = 0; i < kTpMaxRanks; ++i) {
+    r = make_tmap_2d(&td.m[i], recv_ptrs[i < tp ? i : rank], 2, N, M, static_cast<uint64_t>(N) * 2, 64, 32, 1);
+    if (r) return r;
+  }
+  RsArgs a{};
+  a.c.M = M; a.c.N = N; a.c.K = K; a.c.rank = rank; a.c.tp = tp; a.c.rows_local = rows_local;
+  a.c.epoch = epoch; a.c.ctrs = static_cast<uint32_t*>(ctrs); a.c.wait_ns = wait_ns; a.c.status = status;
+  a.out = static_cast<__nv_bfloat16*>(out);
+  a.ldo = ldo;
+  a.recv_self = static_cast<const __nv_bfloat16*>(recv_ptrs[rank]);
+  for (int i = 0; i < tp; ++i) a.flags.p[i] = flag_ptrs[i];
+  cudaError_t e = cudaMemsetAsync(ctrs, 0, sizeof(uint32_t) * (kCtrTiles + M / kTpBlockM), stream);
+  if (e != cudaSuccess) return -static_cast<int>(e);
+  static bool configured[2] = {false, false};
+  if (!configured[b_mn_major ? 1 : 0]) {
+    r = b_mn_major ? tp_configure(gemm_rs_kernel<true>) : tp_configure(gemm_rs_kernel<false>);
+    if (r) return r;
+    configured[b_mn_major ? 1 : 0] = true;
+  }
+  const int grid = sm_count();
+  if (b_mn_major) gemm_rs_kernel<true><<<grid, kTpThreads, kTpSmem, stream>>>(ta, tb, td, a);
+  else gemm_rs_kernel<false><<<grid, kTpThreads, kTpSmem, stream>>>(ta, tb, td, a);
+  e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+// ------------------------------------------------------------------------------------ peer memory plumbing
+// Device memory that other processes of the node can map (cudaMalloc + CUDA IPC handles).
+extern "C" int stb_symm_alloc(void** ptr, unsigned long long bytes, void* handle64) {
+  cudaFree(nullptr);  // binds the primary context to this thread
+  cudaError_t e = cudaMalloc(ptr, bytes);
+  if (e != cudaSuccess) return -static_cast<int>(e);
+  e = cudaMemset(*ptr, 0, bytes);
+  if (e != cudaSuccess) return -static_cast<int>(e);
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  e = cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), *ptr);
+  if (e != cudaSuccess) return -static_cast<int>(e);
+  e = cudaDeviceSynchronize();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+extern "C" int stb_symm_open(void** ptr, const void* handle64) {
+  cudaFree(nullptr);  // binds the primary context to this thread
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  cudaError_t e = cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess);
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+extern "C" int stb_symm_close(void* ptr) {
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+extern "C" int stb_symm_free(void* ptr) {
+  cudaError_t e = cudaFree(ptr);
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}

@@ -333,3 +333,34 @@ extern "C" int stb_nonfinite_flag(const void* x, long long n, int* flag, cudaStr
   nonfinite_flag_kernel<<<grid_cap(n, 256, 8), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), n, flag);
   return -static_cast<int>(cudaGetLastError());
 }
+
+// ----------------------------------------------------------------------------- generalised advantage estimation
+// adv_t = delta_t + gamma*lambda*adv_{t+1},  delta_t = r_t + gamma*v_{t+1} - v_t, restarted at every segment end
+// (v_{T} = 0).  One thread walks one packed segment backwards; segments run in parallel.  Stands where the
+// reference loops over time steps on the host (steptronoss/utils/rl_utils.py:180-210).
+namespace stb {
+__global__ void gae_kernel(const float* __restrict__ values, const float* __restrict__ rewards,
+                           const int* __restrict__ cu, int n_seg, float gamma, float lambd,
+                           float* __restrict__ adv, float* __restrict__ ret) {
+  const int seg = blockIdx.x * blockDim.x + threadIdx.x;
+  if (seg >= n_seg) return;
+  const int b = cu[seg], e = cu[seg + 1];
+  float next_v = 0.f, run = 0.f;
+  for (int t = e - 1; t >= b; --t) {
+    const float v = values[t];
+    const float delta = rewards[t] + gamma * next_v - v;
+    run = delta + gamma * lambd * run;
+    adv[t] = run;
+    ret[t] = run + v;
+    next_v = v;
+  }
+}
+}  // namespace stb
+
+extern "C" int stb_gae(const float* values, const float* rewards, const int* cu_seqlens, int n_seg, float gamma,
+                       float lambd, float* adv, float* ret, cudaStream_t st) {
+  if (n_seg <= 0) return 0;
+  stb::gae_kernel<<<(n_seg + 63) / 64, 64, 0, st>>>(values, rewards, cu_seqlens, n_seg, gamma, lambd, adv, ret);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}

@@ -5,10 +5,10 @@ one autograd function (``steptronoss/core/tensor_parallel/layers.py:151-346``). 
 one autograd function with two bodies:
 
 * the NCCL statement (any backend, also gloo on CPU): collective, then ``ops.gemm``;
-* the peer-memory path (CUDA + symmetric arena available): the activations live in a symmetric
-  buffer, peers' row blocks are pulled over NVLink chunk by chunk on a copy stream while the
-  tcgen05 GEMM of the chunks that already arrived runs, and the reduce-scatter is performed by a
-  kernel that reads the partial tiles from every peer's buffer in fixed rank order.
+* the peer-memory path (CUDA, all ranks of the group on one node): one kernel per projection
+  (``csrc/gemm_tp_sm100.cu``) whose extra warps pull the peers' rows over NVLink while the tcgen05
+  GEMM consumes the row tiles that have arrived, or whose epilogue stores partial tiles into the
+  owner's memory where they are summed in fixed rank order.
 
 Backward mirrors the reference: the column layer re-gathers its input for the weight gradient and
 reduce-scatters the input gradient; the row layer all-gathers the output gradient.
@@ -39,12 +39,13 @@ def _rs_rows(x, group_name):
     return out
 
 
-def _peer_path(x) -> bool:
-    if not x.is_cuda:
+def _peer(group_name, rows_local, k, n, *tensors) -> bool:
+    """True when this projection runs as one fused kernel over peer memory."""
+    if not tensors[0].is_cuda:
         return False
     from . import symm
 
-    return symm.enabled()
+    return symm.usable(rows_local, k, n, *tensors) and symm.enabled(group_name)
 
 
 def _wgrad(weight, g2, x2):
@@ -61,15 +62,14 @@ class _AllGatherLinearFn(torch.autograd.Function):
     def forward(ctx, x, w, group_name, out_dtype):
         ctx.group_name = group_name
         ctx.weight_ref = w
-        if _peer_path(x):
+        ctx.save_for_backward(x, w)  # only the local 1/TP slice is kept
+        if _peer(group_name, x.shape[0], x.shape[1], w.shape[0], x, w):
             from . import symm
 
-            full = symm.all_gather_rows(x, group_name)
-        else:
-            full = _ag_rows(x, group_name)
-        y = gemm(full, w, out_dtype=out_dtype or x.dtype)
-        ctx.save_for_backward(x, w)  # only the local 1/TP slice is kept
-        return y
+            y, _ = symm.all_gather_gemm(x, w, group_name, out_dtype=out_dtype)
+            return y
+        full = _ag_rows(x, group_name)
+        return gemm(full, w, out_dtype=out_dtype or x.dtype)
 
     @staticmethod
     def backward(ctx, gy):
@@ -78,22 +78,16 @@ class _AllGatherLinearFn(torch.autograd.Function):
         g2 = gy if gy.dtype == w.dtype else gy.to(w.dtype)
         g2 = g2.contiguous()
         dx = dw = None
-        peer = _peer_path(x)
+        peer = _peer(name, x.shape[0], x.shape[1], w.shape[0], x, w, g2)
+        if peer:
+            from . import symm
         if ctx.needs_input_grad[0]:
-            dfull = gemm(g2, w, b_mn_major=True, out_dtype=x.dtype)
             if peer:
-                from . import symm
-
-                dx = symm.reduce_scatter_rows(dfull, name)
+                dx = symm.gemm_reduce_scatter(g2, w, name, b_mn_major=True)
             else:
-                dx = _rs_rows(dfull, name)
+                dx = _rs_rows(gemm(g2, w, b_mn_major=True, out_dtype=x.dtype), name)
         if ctx.needs_input_grad[1]:
-            if peer:
-                from . import symm
-
-                full = symm.all_gather_rows(x, name)
-            else:
-                full = _ag_rows(x, name)
+            full = symm.all_gather_gemm(x, None, name)[1] if peer else _ag_rows(x, name)
             dw = _wgrad(ctx.weight_ref, g2, full)
         return dx, dw, None, None
 
@@ -104,27 +98,29 @@ class _LinearReduceScatterFn(torch.autograd.Function):
         ctx.group_name = group_name
         ctx.weight_ref = w
         ctx.save_for_backward(x, w)
-        y = gemm(x, w, out_dtype=x.dtype)
-        if _peer_path(x):
+        tp = PM.size_of(group_name)
+        if x.shape[0] % tp == 0 and _peer(group_name, x.shape[0] // tp, x.shape[1], w.shape[0], x, w):
             from . import symm
 
-            return symm.reduce_scatter_rows(y, group_name)
-        return _rs_rows(y, group_name)
+            return symm.gemm_reduce_scatter(x, w, group_name)
+        return _rs_rows(gemm(x, w, out_dtype=x.dtype), group_name)
 
     @staticmethod
     def backward(ctx, gy):
         x, w = ctx.saved_tensors
         name = ctx.group_name
         g = gy if gy.dtype == w.dtype else gy.to(w.dtype)
-        if _peer_path(x):
+        g = g.contiguous()
+        dx = dw = None
+        if _peer(name, g.shape[0], g.shape[1], w.shape[1], g, w, x):
             from . import symm
 
-            gfull = symm.all_gather_rows(g, name)
+            # dx = all_gather(g) @ w in the same launch that gathers g for the weight gradient
+            dx, gfull = symm.all_gather_gemm(g, w if ctx.needs_input_grad[0] else None, name, b_mn_major=True)
         else:
             gfull = _ag_rows(g, name)
-        dx = dw = None
-        if ctx.needs_input_grad[0]:
-            dx = gemm(gfull, w, b_mn_major=True, out_dtype=x.dtype)
+            if ctx.needs_input_grad[0]:
+                dx = gemm(gfull, w, b_mn_major=True, out_dtype=x.dtype)
         if ctx.needs_input_grad[1]:
             dw = _wgrad(ctx.weight_ref, gfull, x)
         return dx, dw, None

@@ -1,8 +1,243 @@
-"""Symmetric peer memory for fused compute+collective kernels (filled in by ``enable``)."""
+"""Peer-mapped ("symmetric") device memory of a process group and the fused GEMM+collective launches.
+
+Every rank of a group allocates the same set of buffers with ``cudaMalloc``, publishes their CUDA IPC
+handles through the group and maps the peers' buffers, so that a kernel on one GPU can load from and
+store to the other GPUs of the node over NVLink.  On top of that arena sit the two fused launches of
+``csrc/gemm_tp_sm100.cu``:
+
+* :func:`all_gather_gemm`   ``all_gather_rows(x) @ w.T`` (or ``@ w``), also returning the gathered rows;
+* :func:`gemm_reduce_scatter` ``reduce_scatter_rows(a @ w.T)`` (or ``a @ w``).
+
+They stand where the reference issues an NCCL collective next to a cuBLAS GEMM
+(``steptronoss/core/tensor_parallel/layers.py:151-346``).  The NCCL statement remains as the path for
+CPU/gloo runs, groups that span nodes and shapes the kernels do not take (row blocks that are not a
+multiple of 128).
+
+Environment: ``STB200_PEER_TP=0`` disables the peer path; ``STB200_PEER_WAIT_S`` (default 30) bounds every
+wait on another rank inside the kernels.
+"""
 from __future__ import annotations
 
-_ENABLED = False
+import ctypes
+import os
+from ctypes import c_void_p
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+from ..ops.gemm import count_launch
+from .state import PM
+
+_MAX_RANKS = 8
+_ARENAS: dict[str, "Arena | None"] = {}
+_DISABLED = os.environ.get("STB200_PEER_TP", "1") == "0"
+_WAIT_NS = int(float(os.environ.get("STB200_PEER_WAIT_S", "30")) * 1e9)
+
+P, I, L, U, ULL = c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_uint, ctypes.c_ulonglong
+native.register_signature("stb_tp_flag_words", [])
+native.register_signature("stb_tp_ctr_words", [I])
+native.register_signature("stb_symm_alloc", [P, ULL, P])
+native.register_signature("stb_symm_open", [P, P])
+native.register_signature("stb_symm_close", [P])
+native.register_signature("stb_symm_free", [P])
+native.register_signature(
+    "stb_gemm_ag_bf16", [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, U, P, ULL, P, P]
+)
+native.register_signature(
+    "stb_gemm_rs_bf16", [P, I, P, I, I, P, L, P, P, I, I, I, I, I, U, P, ULL, P, P]
+)
 
 
-def enabled() -> bool:
-    return _ENABLED
+class SymmetricBuffer:
+    """One allocation per rank, mapped on every rank.  ``ptrs[r]`` is rank r's buffer in this process."""
+
+    def __init__(self, nbytes: int, group, lib):
+        self.nbytes = int(nbytes)
+        self.group = group
+        self.lib = lib
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        own = c_void_p()
+        handle = ctypes.create_string_buffer(64)
+        rc = lib.stb_symm_alloc(ctypes.byref(own), self.nbytes, handle)
+        ok = torch.tensor([1 if rc == 0 else 0], device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 0:
+            if rc == 0:
+                lib.stb_symm_free(own)
+            raise RuntimeError(f"peer memory allocation of {nbytes} bytes failed on some rank (rc={rc})")
+        self.own = own.value
+        handles = [None] * self.world
+        dist.all_gather_object(handles, (os.getpid(), handle.raw), group=group)
+        self.ptrs = [0] * self.world
+        opened_ok = 1
+        for r, (_, raw) in enumerate(handles):
+            if r == self.rank:
+                self.ptrs[r] = self.own
+                continue
+            p = c_void_p()
+            rc = lib.stb_symm_open(ctypes.byref(p), raw)
+            if rc != 0:
+                opened_ok = 0
+                break
+            self.ptrs[r] = p.value
+        ok = torch.tensor([opened_ok], device="cuda")
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 0:
+            self.release()
+            raise RuntimeError("mapping a peer's memory failed on some rank")
+
+    def ptr_array(self, offset: int = 0):
+        arr = (c_void_p * _MAX_RANKS)()
+        for r in range(self.world):
+            arr[r] = self.ptrs[r] + offset
+        return arr
+
+    def release(self):
+        """Unmap the peers and free the own buffer; callers synchronise the group first."""
+        for r, p in enumerate(self.ptrs):
+            if p and r != self.rank:
+                self.lib.stb_symm_close(c_void_p(p))
+        if self.own:
+            self.lib.stb_symm_free(c_void_p(self.own))
+        self.ptrs, self.own = [], 0
+
+
+class Arena:
+    """Flag page, staging slots (all-gather) and receive slots (reduce-scatter) of one group."""
+
+    def __init__(self, group_name: str):
+        self.group_name = group_name
+        self.group = PM.group_of(group_name)
+        self.rank = PM.rank_in(group_name)
+        self.world = PM.size_of(group_name)
+        self.lib = native.load()
+        self.flags = SymmetricBuffer(self.lib.stb_tp_flag_words() * 4, self.group, self.lib)
+        self.stage: SymmetricBuffer | None = None   # 2 slots
+        self.recv: SymmetricBuffer | None = None    # 2 slots
+        self.stage_slot = 0
+        self.recv_slot = 0
+        self.ag_epoch = 0
+        self.rs_epoch = 0
+        self.ctrs = torch.zeros(self.lib.stb_tp_ctr_words(_MAX_RANKS * 1024), dtype=torch.int32, device="cuda")
+        self._flag_arr = self.flags.ptr_array()
+        dist.barrier(group=self.group)
+
+    def _grow(self, which: str, slot_bytes: int):
+        """All ranks reach this with the same arguments in the same call, so the exchange lines up."""
+        slot_bytes = (slot_bytes + (1 << 20) - 1) & ~((1 << 20) - 1)
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        old = getattr(self, which)
+        if old is not None:
+            old.release()
+        setattr(self, which, SymmetricBuffer(2 * slot_bytes, self.group, self.lib))
+        setattr(self, which + "_slot", slot_bytes)
+        dist.barrier(group=self.group)
+
+    def stage_ptrs(self, need: int, epoch: int):
+        if need > self.stage_slot:
+            self._grow("stage", need)
+        return self.stage.ptr_array((epoch & 1) * self.stage_slot)
+
+    def recv_ptrs(self, need: int, epoch: int):
+        if need > self.recv_slot:
+            self._grow("recv", need)
+        return self.recv.ptr_array((epoch & 1) * self.recv_slot)
+
+
+def _same_node(group) -> bool:
+    import socket
+
+    names = [None] * dist.get_world_size(group)
+    dist.all_gather_object(names, socket.gethostname(), group=group)
+    return len(set(names)) == 1
+
+
+def arena(group_name: str) -> "Arena | None":
+    """The group's arena, created on first use (collective); ``None`` when the peer path is unavailable."""
+    if group_name in _ARENAS:
+        return _ARENAS[group_name]
+    a = None
+    n = PM.size_of(group_name)
+    if (not _DISABLED and torch.cuda.is_available() and dist.is_initialized() and 2 <= n <= _MAX_RANKS
+            and dist.get_backend(PM.group_of(group_name)) == "nccl" and _same_node(PM.group_of(group_name))):
+        try:
+            a = Arena(group_name)
+        except RuntimeError as e:  # every rank raises together (the outcome is all-reduced)
+            from ..utils.logger import logger
+
+            logger.warning(f"peer-memory path disabled for group {group_name}: {e}")
+            a = None
+    _ARENAS[group_name] = a
+    return a
+
+
+def enabled(group_name: str = "TP") -> bool:
+    return arena(group_name) is not None
+
+
+def usable(rows_local: int, k: int, n: int, *tensors) -> bool:
+    """Shapes and dtypes the fused kernels take."""
+    if rows_local <= 0 or rows_local % 128 or rows_local // 128 > 1024 or k % 8 or n % 8:
+        return False
+    return all(t.is_cuda and t.dtype == torch.bfloat16 and t.stride(-1) == 1 for t in tensors)
+
+
+def all_gather_gemm(x, w, group_name: str = "TP", *, b_mn_major: bool = False, out_dtype=None):
+    """``(all_gather_rows(x) @ w.T  [or @ w], all_gather_rows(x))`` in one launch.  ``w=None`` gathers only."""
+    a = arena(group_name)
+    rows, k = x.shape
+    m = rows * a.world
+    if w is None:
+        n = 0
+    else:
+        n = w.shape[1] if b_mn_major else w.shape[0]
+    gathered = torch.empty((m, k), dtype=x.dtype, device=x.device)
+    y = torch.empty((m, n), dtype=x.dtype, device=x.device) if n else None
+    a.ag_epoch += 1
+    stage = a.stage_ptrs(rows * k * 2, a.ag_epoch)
+    rc = a.lib.stb_gemm_ag_bf16(
+        x.data_ptr(), x.stride(0), gathered.data_ptr(), stage, a._flag_arr,
+        w.data_ptr() if n else None, y.data_ptr() if n else None, rows, n, k,
+        w.stride(0) if n else 8, y.stride(0) if n else 8, int(b_mn_major), a.rank, a.world,
+        a.ag_epoch & 0xFFFFFFFF, a.ctrs.data_ptr(), _WAIT_NS, native.status_word(x.device).data_ptr(), native.stream(),
+    )
+    native.check(rc, f"all_gather_gemm rows={rows} N={n} K={k}")
+    count_launch(2)
+    if y is not None and out_dtype not in (None, y.dtype):
+        y = y.to(out_dtype)
+    return y, gathered
+
+
+def gemm_reduce_scatter(x, w, group_name: str = "TP", *, b_mn_major: bool = False):
+    """``reduce_scatter_rows(x @ w.T)`` (or ``x @ w``) in one launch; ``x`` is ``[tp*rows_local, K]``."""
+    a = arena(group_name)
+    m, k = x.shape
+    rows = m // a.world
+    n = w.shape[1] if b_mn_major else w.shape[0]
+    out = torch.empty((rows, n), dtype=x.dtype, device=x.device)
+    a.rs_epoch += 1
+    recv = a.recv_ptrs(m * n * 2, a.rs_epoch)
+    rc = a.lib.stb_gemm_rs_bf16(
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), int(b_mn_major), out.data_ptr(), out.stride(0),
+        recv, a._flag_arr, rows, n, k, a.rank, a.world, a.rs_epoch & 0xFFFFFFFF, a.ctrs.data_ptr(), _WAIT_NS,
+        native.status_word(x.device).data_ptr(), native.stream(),
+    )
+    native.check(rc, f"gemm_reduce_scatter M={m} N={n} K={k}")
+    count_launch(2)
+    return out
+
+
+def shutdown() -> None:
+    """Release every arena (collective; call before destroying the process groups)."""
+    for name, a in list(_ARENAS.items()):
+        if a is None:
+            continue
+        torch.cuda.synchronize()
+        dist.barrier(group=a.group)
+        for buf in (a.stage, a.recv, a.flags):
+            if buf is not None:
+                buf.release()
+    _ARENAS.clear()

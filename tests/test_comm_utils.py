@@ -1,0 +1,81 @@
+"""Experiment store: file-system election, the native server's commands, queues and futures."""
+import os
+import pickle
+import threading
+from queue import Empty
+
+import pytest
+
+
+@pytest.fixture()
+def store(tmp_path, monkeypatch):
+    from steptronoss_b200.utils import comm_utils
+
+    monkeypatch.setenv("STEPTRON_MEET_DIR", str(tmp_path))
+    monkeypatch.setenv("EXP_ID", "unit")
+    comm_utils.reset_exp_store()
+    s = comm_utils.get_exp_redis()
+    yield s
+    comm_utils.reset_exp_store()
+
+
+def test_store_commands(store):
+    assert store.ping()
+    assert store.get("a") is None
+    store.set("a", "1")
+    assert store.get("a") == b"1" and not store.setnx("a", "2") and store.setnx("b", "2")
+    assert store.incr("n") == 1 and store.incr("n", 5) == 6 and store.decr("n") == 5
+    for i in range(3):
+        store.lpush("q", str(i))
+    assert store.llen("q") == 3 and store.rpop("q") == b"0" and store.lpop("q") == b"2"
+    assert store.lrange("q") == [b"1"]
+    assert sorted(store.keys("")) == [b"a", b"b", b"n", b"q"]
+    assert store.delete("a") and store.get("a") is None
+    store.zadd("z", {"x": 0, "y": 0})
+    first = store.zpopmin_incr("z")
+    second = store.zpopmin_incr("z")
+    assert {first, second} == {b"x", b"y"}
+    big = os.urandom(3 << 20)
+    store.set("big", big)
+    assert store.get("big") == big
+    store.expire("b", 0.0)
+    assert store.get("b") is None
+
+
+def test_election_writes_rendezvous_file_and_second_client_joins(store, tmp_path):
+    from steptronoss_b200.utils import comm_utils
+
+    files = [f for f in os.listdir(tmp_path) if f.startswith("redis-rendezvous-")]
+    assert len(files) == 1
+    state = pickle.load(open(tmp_path / files[0], "rb"))
+    assert state["port"] == comm_utils.STORE_PORT and comm_utils.IS_STORE_HOST
+    other = comm_utils.ExpStore(comm_utils.STORE_ADDR, state["port"])
+    store.set("k", "v")
+    assert other.get("k") == b"v"
+
+
+def test_queue_distributor_and_futures(store):
+    from steptronoss_b200.utils.comm_utils import RedisQueue, RemoteFuture, ReusableDistributor, wait_by_finish_order
+
+    q = RedisQueue()
+    q.register_subqueue("s0")
+    q.register_subqueue("s1")
+    for i in range(4):
+        q.put(i, auto_balance=True)
+    assert q.qsize() == 4
+    got = sorted([q.get(["s0"]), q.get(["s0"]), q.get(["s1"]), q.get(["s1"])])
+    assert got == [0, 1, 2, 3]
+    with pytest.raises(Empty):
+        q.get(["s0", "s1", None])
+    assert not q.closed
+    q.close()
+    assert q.closed
+    d = ReusableDistributor(range(5))
+    seen = [next(d), next(d)]
+    d.push_back(seen[0])
+    rest = list(d)
+    assert sorted(rest + seen[1:]) == [0, 1, 2, 3, 4]
+    futs = [RemoteFuture() for _ in range(3)]
+    clones = [pickle.loads(pickle.dumps(f)) for f in futs]
+    threading.Thread(target=lambda: [c.set_result(i * 10) for i, c in enumerate(clones)]).start()
+    assert sorted(f.get_result(timeout=10) for f in wait_by_finish_order(futs)) == [0, 10, 20]

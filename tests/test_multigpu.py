@@ -39,3 +39,26 @@ def test_two_gpu_layout_matches_one_gpu(single, layout):
     res = _launch(2, dict(BASE, **layout), port=29620 + len(str(layout)) % 50)
     for a, b in zip(res["losses"], single["losses"]):
         assert abs(a - b) < 3e-2 * abs(b), (layout, res["losses"], single["losses"])
+
+
+def _launch_fused(nproc: int, mode: str, port: int):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port),
+           os.path.join(ROOT, "tests", "mp_fused_tp_worker.py"), mode]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=400, env=env, cwd=ROOT)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    line = [l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    return json.loads(line[len("RESULT "):])
+
+
+def test_fused_gemm_collectives_match_nccl_statement():
+    """all-gather->GEMM and GEMM->reduce-scatter over peer memory against NCCL + fp32 matmul on 2 GPUs."""
+    res = _launch_fused(2, "check", 29701)
+    assert res["max_err"] and max(res["max_err"].values()) < 1e-2
+
+
+def test_fused_gemm_collective_wait_runs_out_without_hanging():
+    """A rank that stays away from one call: the peer's bounded wait reports code 5, the next call works."""
+    res = _launch_fused(2, "timeout", 29702)
+    assert res["timeout_code"] == 5
