@@ -120,7 +120,7 @@ class Checkpointer:
             files["world_size"] = str(PM.world_size)
         return files
 
-    def _write(self, files: dict, path: str) -> None:
+    def _write(self, files: dict, path: str, mark_latest: bool = True) -> None:
         for name, obj in files.items():
             dst = os.path.join(path, name)
             tmp = dst + ".tmp"
@@ -134,7 +134,7 @@ class Checkpointer:
                     f.write(str(obj))
             os.replace(tmp, dst)
         open(os.path.join(path, f"{PM.world_rank}.success"), "w").close()
-        if self.is_complete(path, PM.world_size):
+        if mark_latest and self.is_complete(path, PM.world_size):
             marker = os.path.join(self.save_path, "latest_ckpt")
             tmp = marker + f".tmp{PM.world_rank}"
             with open(tmp, "w") as f:
@@ -153,7 +153,7 @@ class Checkpointer:
             shutil.rmtree(os.path.join(self.save_path, d), ignore_errors=True)
 
     def save_ckpt(self, iteration: int, models, grad_manager, scheduler, dataloader, extra: dict, sync: bool = False,
-                  sub_name: str | None = None) -> str:
+                  sub_name: str | None = None, mark_latest: bool = True) -> str:
         self.join()
         path = self.iteration_dir(iteration, sub_name)
         if PM.world_rank == 0:
@@ -170,11 +170,11 @@ class Checkpointer:
 
             dump_safetensors(models, os.path.join(path, "hf"))
         if sync or not self.cfg.async_save:
-            self._write(files, path)
+            self._write(files, path, mark_latest)
         else:
             def run():
                 try:
-                    self._write(files, path)
+                    self._write(files, path, mark_latest)
                 except BaseException as e:  # surfaced by join()
                     self._error = e
 

@@ -138,7 +138,15 @@ struct TpCommon {
   uint32_t* ctrs;       // local counter scratch
   unsigned long long wait_ns;
   int* status;
+  unsigned long long* trace;  // optional [gridDim.x][8] device-timer stamps (ns) of the phases of every CTA
 };
+
+// Phase stamps for performance analysis (no effect when the caller passes no trace buffer).
+enum TraceSlot { kTrEntry = 0, kTrFirstLoad = 1, kTrProducerDone = 2, kTrMmaDone = 3, kTrEpilogueDone = 4,
+                 kTrAuxFirst = 5, kTrAuxDone = 6, kTrExit = 7 };
+__device__ __forceinline__ void tp_trace(const TpCommon& c, int slot) {
+  if (c.trace != nullptr) c.trace[blockIdx.x * 8 + slot] = global_timer_ns();
+}
 
 struct TpShared {
   uint8_t* smem;
@@ -378,6 +386,7 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   tp_prologue(s, warp);
   const uint32_t tmem_base = *s.tmem_slot;
+  if (threadIdx.x == 0) tp_trace(c, kTrEntry);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
@@ -389,6 +398,7 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int tile = sched_produce(s, c, q, num_tiles, claimed);
         if (tile < 0) {
           if (tile == -2) sched_fail(s, c, kErrProducerWait);
+          tp_trace(c, kTrProducerDone);
           break;
         }
         int m_log, n_tile;
@@ -408,6 +418,7 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const CUtensorMap* ta = own ? &tmap_x : &tmap_a;
         const int a_row = own ? (m_tile % tiles_per_rank) * kTpBlockM : m_tile * kTpBlockM;
         bool ok = true;
+        if (q == 0) tp_trace(c, kTrFirstLoad);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int st = it % kTpStages;
           if (!mbar_wait_budget(&s.empty_bar[st], ((it / kTpStages) & 1) ^ 1, c.wait_ns, s.abort_flag)) {
@@ -421,7 +432,10 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) tp_mma_loop<B_MN>(s, c, tmem_base, k_blocks);
+    if (lane == 0) {
+      tp_mma_loop<B_MN>(s, c, tmem_base, k_blocks);
+      tp_trace(c, kTrMmaDone);
+    }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue
     const int quarter = warp & 3;
@@ -451,6 +465,7 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       ++local_tile;
     }
     if (lane == 0) tma_store_wait<0>();
+    if (warp == 2 && lane == 0) tp_trace(c, kTrEpilogueDone);
   } else {
     // ------------------------------------------------------------------ comm warps
     const int tid = threadIdx.x - 192;
@@ -460,9 +475,13 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int total_vec = kTpPartRows * vec_per_row;
     uint32_t src_ready = 1u << c.rank;
     bool failed = false;
+    if (tid == 0) tp_trace(c, kTrAuxFirst);
     for (;;) {
       const int u = aux_claim(s, c.ctrs, tid);
-      if (u >= total_units || failed || *s.abort_flag) break;
+      if (u >= total_units || failed || *s.abort_flag) {
+        if (tid == 0) tp_trace(c, kTrAuxDone);
+        break;
+      }
       const int m_tile = physical_m_tile(u / kTpParts, tiles_per_rank, c.rank, c.tp);
       const int part = u % kTpParts;
       const int src = m_tile / tiles_per_rank;
@@ -522,6 +541,7 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   }
   tp_epilogue_sync(s, warp, tmem_base);
+  if (threadIdx.x == 0) tp_trace(c, kTrExit);
 }
 
 // ===================================================================================== GEMM -> reduce-scatter
@@ -550,6 +570,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
   tp_prologue(s, warp);
   const uint32_t tmem_base = *s.tmem_slot;
+  if (threadIdx.x == 0) tp_trace(c, kTrEntry);
 
   if (warp == 0) {
     if (lane == 0) {
@@ -559,12 +580,14 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const int tile = sched_produce(s, c, q, num_tiles, claimed);
         if (tile < 0) {
           if (tile == -2) sched_fail(s, c, kErrProducerWait);
+          tp_trace(c, kTrProducerDone);
           break;
         }
         int m_log, n_tile;
         decode_tp_tile(tile, num_m, num_n, m_log, n_tile);
         const int m_tile = interleaved_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
         bool ok = true;
+        if (q == 0) tp_trace(c, kTrFirstLoad);
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const int st = it % kTpStages;
           if (!mbar_wait_budget(&s.empty_bar[st], ((it / kTpStages) & 1) ^ 1, c.wait_ns, s.abort_flag)) {
@@ -578,7 +601,10 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) tp_mma_loop<B_MN>(s, c, tmem_base, k_blocks);
+    if (lane == 0) {
+      tp_mma_loop<B_MN>(s, c, tmem_base, k_blocks);
+      tp_trace(c, kTrMmaDone);
+    }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue: partial tiles to their owners
     const int quarter = warp & 3;
@@ -645,6 +671,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (lane == 0) {
       tma_store_wait<0>();
       if (pending_m >= 0) signal_tile(pending_m);
+      if (warp == 2) tp_trace(c, kTrEpilogueDone);
     }
   } else {
     // ------------------------------------------------------------------ reduce warps: rows this rank owns
@@ -657,9 +684,13 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                slot * kTpMaxRowTiles * kTpMaxRanks;
     int ready_tile = -1;
     bool failed = false;
+    if (tid == 0) tp_trace(c, kTrAuxFirst);
     for (;;) {
       const int u = aux_claim(s, c.ctrs, tid);
-      if (u >= total_units || failed || *s.abort_flag) break;
+      if (u >= total_units || failed || *s.abort_flag) {
+        if (tid == 0) tp_trace(c, kTrAuxDone);
+        break;
+      }
       const int m_local = u / kTpParts, part = u % kTpParts;
       if (m_local != ready_tile) {
         bool ok = true;
@@ -699,6 +730,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
   }
   tp_epilogue_sync(s, warp, tmem_base);
+  if (threadIdx.x == 0) tp_trace(c, kTrExit);
 }
 
 template <typename Kern>
@@ -731,7 +763,7 @@ extern "C" int stb_tp_ctr_words(int row_tiles) { return kCtrTiles + row_tiles; }
 extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* gathered, void* const* stage_ptrs,
                                 void* const* flag_ptrs, const void* B, void* C, int rows_local, int N, int K, int ldb,
                                 int ldc, int b_mn_major, int rank, int tp, unsigned epoch, void* ctrs,
-                                unsigned long long wait_ns, int* status, cudaStream_t stream) {
+                                unsigned long long wait_ns, int* status, void* trace, cudaStream_t stream) {
   int r = tp_check(rows_local, N, K, tp, rank);
   if (r) return r;
   if ((ldx & 7) || (N > 0 && ((ldb & 7) || (ldc & 7)))) return -kErrBadArgument;
@@ -754,6 +786,7 @@ extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* gather
   AgArgs a{};
   a.c.M = M; a.c.N = N; a.c.K = K; a.c.rank = rank; a.c.tp = tp; a.c.rows_local = rows_local;
   a.c.epoch = epoch; a.c.ctrs = static_cast<uint32_t*>(ctrs); a.c.wait_ns = wait_ns; a.c.status = status;
+  a.c.trace = static_cast<unsigned long long*>(trace);
   a.x_local = static_cast<const __nv_bfloat16*>(x_local);
   a.ldx = ldx;
   a.gathered = static_cast<__nv_bfloat16*>(gathered);
@@ -782,7 +815,7 @@ extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* gather
 extern "C" int stb_gemm_rs_bf16(const void* A, int lda, const void* B, int ldb, int b_mn_major, void* out,
                                 long long ldo, void* const* recv_ptrs, void* const* flag_ptrs, int rows_local, int N,
                                 int K, int rank, int tp, unsigned epoch, void* ctrs, unsigned long long wait_ns,
-                                int* status, cudaStream_t stream) {
+                                int* status, void* trace, cudaStream_t stream) {
   int r = tp_check(rows_local, N, K, tp, rank);
   if (r) return r;
   if (N <= 0 || (lda & 7) || (ldb & 7) || (ldo & 7)) return -kErrBadArgument;
@@ -801,6 +834,7 @@ extern "C" int stb_gemm_rs_bf16(const void* A, int lda, const void* B, int ldb, 
   RsArgs a{};
   a.c.M = M; a.c.N = N; a.c.K = K; a.c.rank = rank; a.c.tp = tp; a.c.rows_local = rows_local;
   a.c.epoch = epoch; a.c.ctrs = static_cast<uint32_t*>(ctrs); a.c.wait_ns = wait_ns; a.c.status = status;
+  a.c.trace = static_cast<unsigned long long*>(trace);
   a.out = static_cast<__nv_bfloat16*>(out);
   a.ldo = ldo;
   a.recv_self = static_cast<const __nv_bfloat16*>(recv_ptrs[rank]);

@@ -33,6 +33,28 @@ _MAX_RANKS = 8
 _ARENAS: dict[str, "Arena | None"] = {}
 _DISABLED = os.environ.get("STB200_PEER_TP", "1") == "0"
 _WAIT_NS = int(float(os.environ.get("STB200_PEER_WAIT_S", "30")) * 1e9)
+_TRACE = None  # int64 [SMs, 8] tensor set by trace(): per-CTA phase stamps of the next fused launches
+
+
+def trace(enable: bool = True):
+    """Start (or stop) recording the per-CTA phase stamps of the fused kernels; returns the buffer."""
+    global _TRACE
+    _TRACE = torch.zeros((256, 8), dtype=torch.int64, device="cuda") if enable else None
+    return _TRACE
+
+
+def trace_summary() -> dict:
+    """Phase ends relative to the earliest CTA entry, in microseconds (max over CTAs)."""
+    t = _TRACE.cpu()
+    t = t[t[:, 0] > 0]
+    t0 = int(t[:, 0].min())
+    names = ["entry", "first_load", "producer_done", "mma_done", "epilogue_done", "aux_first", "aux_done", "exit"]
+    out = {}
+    for i, n in enumerate(names):
+        col = t[:, i][t[:, i] > 0]
+        if col.numel():
+            out[n] = {"min_us": (int(col.min()) - t0) / 1e3, "max_us": (int(col.max()) - t0) / 1e3}
+    return out
 
 P, I, L, U, ULL = c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_uint, ctypes.c_ulonglong
 native.register_signature("stb_tp_flag_words", [])
@@ -42,10 +64,10 @@ native.register_signature("stb_symm_open", [P, P])
 native.register_signature("stb_symm_close", [P])
 native.register_signature("stb_symm_free", [P])
 native.register_signature(
-    "stb_gemm_ag_bf16", [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, U, P, ULL, P, P]
+    "stb_gemm_ag_bf16", [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, U, P, ULL, P, P, P]
 )
 native.register_signature(
-    "stb_gemm_rs_bf16", [P, I, P, I, I, P, L, P, P, I, I, I, I, I, U, P, ULL, P, P]
+    "stb_gemm_rs_bf16", [P, I, P, I, I, P, L, P, P, I, I, I, I, I, U, P, ULL, P, P, P]
 )
 
 
@@ -202,7 +224,8 @@ def all_gather_gemm(x, w, group_name: str = "TP", *, b_mn_major: bool = False, o
         x.data_ptr(), x.stride(0), gathered.data_ptr(), stage, a._flag_arr,
         w.data_ptr() if n else None, y.data_ptr() if n else None, rows, n, k,
         w.stride(0) if n else 8, y.stride(0) if n else 8, int(b_mn_major), a.rank, a.world,
-        a.ag_epoch & 0xFFFFFFFF, a.ctrs.data_ptr(), _WAIT_NS, native.status_word(x.device).data_ptr(), native.stream(),
+        a.ag_epoch & 0xFFFFFFFF, a.ctrs.data_ptr(), _WAIT_NS, native.status_word(x.device).data_ptr(),
+        _TRACE.data_ptr() if _TRACE is not None else None, native.stream(),
     )
     native.check(rc, f"all_gather_gemm rows={rows} N={n} K={k}")
     count_launch(2)
@@ -223,7 +246,7 @@ def gemm_reduce_scatter(x, w, group_name: str = "TP", *, b_mn_major: bool = Fals
     rc = a.lib.stb_gemm_rs_bf16(
         x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), int(b_mn_major), out.data_ptr(), out.stride(0),
         recv, a._flag_arr, rows, n, k, a.rank, a.world, a.rs_epoch & 0xFFFFFFFF, a.ctrs.data_ptr(), _WAIT_NS,
-        native.status_word(x.device).data_ptr(), native.stream(),
+        native.status_word(x.device).data_ptr(), _TRACE.data_ptr() if _TRACE is not None else None, native.stream(),
     )
     native.check(rc, f"gemm_reduce_scatter M={m} N={n} K={k}")
     count_launch(2)

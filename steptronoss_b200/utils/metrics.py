@@ -56,11 +56,20 @@ def _reduce_group(val: torch.Tensor, axis: str, op: str):
 
 
 class Metric:
-    def __init__(self) -> None:
-        self.chain: list[tuple[str, str]] = []
+    """``Metric(is_group=True)`` gives a :class:`GroupMetric` (the reference spells grouped metrics this way)."""
+
+    def __new__(cls, *args, is_group: bool = False, **kwargs):
+        if is_group and cls is Metric:
+            return object.__new__(GroupMetric)
+        return object.__new__(cls)
+
+    def __init__(self, name: str | None = None, reductions=None, sample_interval: int = 1,
+                 is_group: bool = False) -> None:
+        self.chain: list[tuple[str, str]] = list(reductions or [])
         self.values: list = []
         self.enabled = True
-        self.name: str | None = None
+        self.name: str | None = name
+        self.sample_interval = sample_interval
 
     def _link(self, op: str, axis: str):
         self.chain.append((op, axis.lower()))
@@ -72,12 +81,23 @@ class Metric:
     def min(self, axis: str): return self._link("min", axis)        # noqa: E704
     def last(self, axis: str = "time"): return self._link("last", axis)    # noqa: E704
     def first(self, axis: str = "time"): return self._link("first", axis)  # noqa: E704
+    def gather(self, axis: str = "world"): return self._link("gather", axis)  # noqa: E704
+
+    def enable(self):
+        self.enabled = True
+        return self
+
+    def disable(self):
+        self.enabled = False
+        return self
 
     def add(self, value, subname: str | None = None, iop: str | None = None) -> None:
         """Record one value. ``iop`` (``"sum"``/``"max"``/...) merges into the last recorded value
         instead of appending (in-place accumulation inside one iteration)."""
         if not self.enabled:
             return
+        if callable(iop):  # an input transform such as torch.mean / torch.max / torch.detach
+            value, iop = iop(value), None
         if torch.is_tensor(value):
             value = value.detach()
         if iop and self.values:
@@ -117,8 +137,8 @@ class Metric:
 class GroupMetric(Metric):
     """A family of metrics sharing one chain, keyed by ``subname``; reduces to ``{name/sub: value}``."""
 
-    def __init__(self) -> None:
-        super().__init__()
+    def __init__(self, *args, **kwargs) -> None:
+        super().__init__(*args, **kwargs)
         self.sub: dict[str, list] = {}
 
     def add(self, value, subname: str | None = None, iop: str | None = None) -> None:
@@ -152,11 +172,28 @@ class GradNormMetric(GroupMetric):
         self.chain = [("last", "time")]
 
 
+class AvgMetric(Metric):
+    """Mean over the values recorded in the interval, then the chain over groups."""
+
+    def reduce(self):
+        if not any(ax == "time" for _, ax in self.chain):
+            self.chain = [("mean", "time")] + self.chain
+        return super().reduce()
+
+
 class PercentageMetric(Metric):
-    """``add(numerator, denominator)`` pairs; reduces both along the chain and divides."""
+    """``add(numerator, denominator)`` pairs reduce to one ratio; ``add(count, subname=category)`` entries
+    reduce to ``{category: share of the total}``."""
+
+    def __init__(self, *args, **kwargs) -> None:
+        super().__init__(*args, **kwargs)
+        self.cats: dict[str, float] = {}
 
     def add(self, value, total=None, subname=None, iop=None) -> None:  # type: ignore[override]
         if not self.enabled:
+            return
+        if subname is not None:
+            self.cats[subname] = self.cats.get(subname, 0.0) + float(value)
             return
         v = torch.as_tensor(value, dtype=torch.float32).detach()
         t = torch.as_tensor(1.0 if total is None else total, dtype=torch.float32).detach()
@@ -164,7 +201,27 @@ class PercentageMetric(Metric):
             t = t.to(v.device)
         self.values.append(torch.stack([v.reshape(()), t.reshape(())]))
 
+    def reset(self) -> None:
+        super().reset()
+        self.cats = {}
+
+    def _reduce_categories(self):
+        cats = dict(self.cats)
+        axes = [ax for _, ax in self.chain if ax != "time"]
+        if axes and dist.is_available() and dist.is_initialized():
+            group, _ = _group_for(axes[0])
+            gathered = [None] * dist.get_world_size(group)
+            dist.all_gather_object(gathered, cats, group=group)
+            cats = {}
+            for d in gathered:
+                for k, v in d.items():
+                    cats[k] = cats.get(k, 0.0) + v
+        tot = sum(cats.values())
+        return {k: torch.tensor(v / tot if tot else 0.0) for k, v in sorted(cats.items())}
+
     def reduce(self):
+        if self.cats:
+            return self._reduce_categories()
         if not self.values:
             return None
         saved_chain = self.chain
@@ -184,12 +241,25 @@ class HistogramMetric(Metric):
 
 
 class TextMetric(Metric):
+    """Keeps up to ``max_items`` strings per interval (sample generations for qualitative inspection)."""
+
+    def __init__(self, max_items: int | None = None, *args, **kwargs) -> None:
+        super().__init__(*args, **kwargs)
+        self.max_items = max_items
+
     def add(self, value, subname=None, iop=None) -> None:
-        if self.enabled:
+        if self.enabled and (self.max_items is None or len(self.values) < self.max_items):
             self.values.append(str(value))
 
     def reduce(self):
-        return list(self.values)
+        vals = list(self.values)
+        if any(op == "gather" for op, _ in self.chain) and dist.is_available() and dist.is_initialized():
+            axis = next(ax for op, ax in self.chain if op == "gather")
+            group, _ = _group_for(axis)
+            out = [None] * dist.get_world_size(group)
+            dist.all_gather_object(out, vals, group=group)
+            vals = [v for part in out for v in part]
+        return vals[: self.max_items] if self.max_items else vals
 
 
 class MetricHolder:

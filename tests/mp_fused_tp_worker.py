@@ -137,8 +137,22 @@ def main():
                 return gemm(full, w)
 
             res["timing_ms"][f"ag_{name}_fused"] = _time(lambda: symm.all_gather_gemm(x, w, "TP"))
+            symm.trace(True)
+            symm.all_gather_gemm(x, w, "TP")
+            torch.cuda.synchronize()
+            res.setdefault("trace", {})[f"ag_{name}"] = symm.trace_summary()
+            symm.trace(False)
             res["timing_ms"][f"ag_{name}_nccl+gemm"] = _time(nccl)
             res["timing_ms"][f"ag_{name}_gemm_only"] = _time(lambda: gemm(full, w))
+        xg = torch.randn(rows, hidden, device=dev, generator=g).to(torch.bfloat16)
+        fullg = torch.empty((tokens, hidden), dtype=xg.dtype, device=dev)
+        res["timing_ms"]["gather_only_fused"] = _time(lambda: symm.all_gather_gemm(xg, None, "TP"))
+        res["timing_ms"]["gather_only_nccl"] = _time(lambda: dist.all_gather_into_tensor(fullg, xg, group=group))
+        symm.trace(True)
+        symm.all_gather_gemm(xg, None, "TP")
+        torch.cuda.synchronize()
+        res.setdefault("trace", {})["gather_only"] = symm.trace_summary()
+        symm.trace(False)
         cases = {"o_proj": (hidden // tp, hidden), "down": (ffn // tp, hidden)}
         for name, (k, n) in cases.items():
             a = torch.randn(tokens, k, device=dev, generator=g).to(torch.bfloat16)
@@ -151,6 +165,11 @@ def main():
                 return out
 
             res["timing_ms"][f"rs_{name}_fused"] = _time(lambda: symm.gemm_reduce_scatter(a, w, "TP"))
+            symm.trace(True)
+            symm.gemm_reduce_scatter(a, w, "TP")
+            torch.cuda.synchronize()
+            res.setdefault("trace", {})[f"rs_{name}"] = symm.trace_summary()
+            symm.trace(False)
             res["timing_ms"][f"rs_{name}_nccl+gemm"] = _time(nccl)
             res["timing_ms"][f"rs_{name}_gemm_only"] = _time(lambda: gemm(a, w))
         native.raise_if_kernel_error()

@@ -1,0 +1,163 @@
+"""PPO trainer end to end on CPU: fake in-process generation feeds the flow controller, the reference / actor /
+critic passes fill log-probabilities and values, both models take optimizer steps, and the job checkpoints."""
+import asyncio
+import os
+import random
+
+import pytest
+import torch
+
+from steptronoss_b200.data.nextable import Nextable
+from steptronoss_b200.exp.base_exp import DataConfig, GradientManagerConfig, ProfilerConfig
+from steptronoss_b200.exp.lr_schedulers import ConstantSchedulerConfig
+from steptronoss_b200.exp.rl import (ActorModelConfig, CriticModelConfig, EnvTrajectory, FlowControllerConfig,
+                                     PackedPPOSamples, PPOCheckpointCfg, PPOLikeExp, PPOLikeTrainerConfig,
+                                     PPOMetricConfig, PPOSample)
+from steptronoss_b200.generation.async_generation import SingleGenerationController
+from steptronoss_b200.generation.base_generatable import TrainableItem
+from steptronoss_b200.generators.flow_controller import SimpleFlowController
+from steptronoss_b200.models.common.parallel_embedding import OneDimensionalOutputEmbedding, OutputEmbeddingConfig
+from steptronoss_b200.models.decoder_model import DecoderLLMConfig
+
+VOCAB = 64
+
+
+class FakeRollout(TrainableItem):
+    def __init__(self, idx):
+        super().__init__()
+        self.idx = idx
+
+    async def generate(self):
+        return self.idx
+
+    async def generate_for_train(self):
+        await asyncio.sleep(0)
+        rnd = random.Random(self.idx)
+        out = []
+        for k in range(2):
+            p, g = rnd.randint(3, 6), rnd.randint(4, 9)
+            toks = [rnd.randrange(VOCAB) for _ in range(p + g)]
+            # reward: fraction of even tokens in the response (something a policy can learn)
+            r = sum(t % 2 == 0 for t in toks[p:]) / g
+            out.append(EnvTrajectory(trajectory=toks, is_gen_mask=[0] * p + [1] * g, raw_reward=r,
+                                     logprobs=[-3.0] * g, meta={"idx": self.idx}))
+        return out
+
+
+class Prompts(Nextable):
+    def __init__(self):
+        self.i = 0
+
+    def __iter__(self):
+        return self
+
+    def __next__(self):
+        self.i += 1
+        return FakeRollout(self.i - 1)
+
+    def state_dict(self):
+        return {"i": self.i}
+
+    def load_state_dict(self, sd):
+        self.i = sd["i"]
+
+
+class PromptData(DataConfig):
+    def build_dataloader(self, dp_rank=0, dp_size=1):
+        return Prompts()
+
+
+class ValueHead(OutputEmbeddingConfig):
+    def build_model(self, tied_embedding_weight=None):
+        return OneDimensionalOutputEmbedding(self)
+
+
+class Actor(ActorModelConfig, DecoderLLMConfig):
+    pass
+
+
+class Critic(CriticModelConfig, DecoderLLMConfig):
+    out_embed_cfg = ValueHead
+
+
+class Flow(FlowControllerConfig):
+    def build_flow_controller(self):
+        return SimpleFlowController(self, generator=SingleGenerationController(), deploy_fn=lambda models: None)
+
+
+class Trainer(PPOLikeTrainerConfig):
+    flow_cfg = Flow
+
+
+class Exp(PPOLikeExp):
+    data_cfg = PromptData
+    actor_model_cfg = Actor
+    critic_model_cfg = Critic
+    actor_grad_manager_cfg = GradientManagerConfig
+    critic_grad_manager_cfg = GradientManagerConfig
+    actor_scheduler_cfg = ConstantSchedulerConfig
+    critic_scheduler_cfg = ConstantSchedulerConfig
+    checkpoint_cfg = PPOCheckpointCfg
+    trainer_cfg = Trainer
+    metric_cfg = PPOMetricConfig
+    profiler_cfg = ProfilerConfig
+
+
+def _fill_model(m, hidden=32):
+    m.num_layers, m.hidden_size, m.params_dtype, m.variable_seq_lengths = 2, hidden, torch.float32, True
+    a = m.attn_cfg
+    a.num_attention_heads, a.num_attention_groups, a.head_dim, a.hidden_size = 2, 1, 16, hidden
+    m.ffn_cfg.hidden_size, m.ffn_cfg.ffn_hidden_size = hidden, 64
+    m.tok_embed_cfg.vocab_size = m.out_embed_cfg.vocab_size = VOCAB
+    m.tok_embed_cfg.hidden_size = m.out_embed_cfg.hidden_size = hidden
+    m.parallel_cfg.expert_tensor_parallel_size = 1
+
+
+def _exp(tmp_path, use_critic=True):
+    e = Exp()
+    _fill_model(e.actor_model_cfg)
+    _fill_model(e.critic_model_cfg)
+    t = e.trainer_cfg
+    t.train_iters, t.global_seq_length, t.global_batch_size, t.writer_backend = 3, 64, 1, []
+    t.critic_warmup_iters, t.fix_iters, t.use_critic = 0, 2, use_critic
+    t.flow_cfg.prompt_per_iter, t.flow_cfg.async_strategy = 6, "on-policy"
+    for s in (e.actor_scheduler_cfg, e.critic_scheduler_cfg):
+        s.lr, s.weight_decay, s.warmup_schedule = 1e-3, 0.0, 0
+    e.checkpoint_cfg.save_dir = str(tmp_path)
+    e.checkpoint_cfg.save_interval = 2
+    e.checkpoint_cfg.async_save = False
+    if not use_critic:
+        e.critic_model_cfg = None
+    return e
+
+
+def test_packed_samples_layout():
+    s = [PPOSample(trajectory=torch.arange(5), is_gen_mask=torch.tensor([0, 0, 1, 1, 1]).bool(),
+                   logprobs=torch.zeros(3), raw_reward=1.0, meta={}),
+         PPOSample(trajectory=torch.arange(4), is_gen_mask=torch.tensor([0, 1, 1, 1]).bool(),
+                   logprobs=torch.zeros(3), raw_reward=0.0, meta={})]
+    p = PackedPPOSamples.from_samples(s)
+    assert p.input_ids.shape == (1, 10) and p.cu_seqlens.tolist() == [0, 5, 10] and p.cu_valid_sizes.tolist() == [0, 5, 9]
+    assert p.labels[0, :9].tolist() == [1, 2, 3, 4, 0, 1, 2, 3, 0]
+    # label-aligned mask: position t is trained when token t+1 was generated
+    assert p.is_gen_mask[0].tolist() == [False, True, True, True, False, True, True, True, False, False]
+    assert int(p.is_gen_mask.sum()) == p.logprobs.numel()
+
+
+@pytest.mark.parametrize("use_critic", [True, False])
+def test_ppo_trains_and_checkpoints(tmp_path, use_critic):
+    exp = _exp(tmp_path, use_critic)
+    exp.sanity_check()
+    tr = exp.trainer_cfg.get_trainer_cls()(exp)
+    tr.before_train()
+    before = {n: p.detach().clone() for n, p in tr.actor.models.named_parameters()}
+    tr.train_loop()
+    assert tr.iteration == 3 and tr.actor_iteration >= 3
+    moved = sum(float((p.detach() - before[n]).abs().sum()) for n, p in tr.actor.models.named_parameters())
+    assert moved > 0
+    keys = tr.history[-1]
+    assert "reward_mean" in keys and "ppo_loss" in keys and (not use_critic or "critic_loss" in keys)
+    it_dir = os.path.join(exp.checkpoint_cfg.save_path, "it2")
+    assert os.path.isdir(os.path.join(it_dir, "actor")) and os.path.exists(os.path.join(it_dir, "data.pkl"))
+    assert os.path.isdir(os.path.join(it_dir, "critic")) == use_critic
+    assert open(os.path.join(exp.checkpoint_cfg.save_path, "latest_ckpt")).read().strip() == it_dir
