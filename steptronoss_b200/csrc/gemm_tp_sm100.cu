@@ -41,14 +41,14 @@ constexpr int kTpPartRows = kTpBlockM / kTpParts;
 constexpr int kTpMaxRanks = 8;
 
 // Layout of the symmetric flag page (uint32 words).
-constexpr int kFlagAgReady = 0;                   // [slot 2][src 8]
-constexpr int kFlagRsBase = 64;                   // [slot 2][row tile kTpMaxRowTiles][src 8]
-constexpr int kTpMaxRowTiles = 1024;
-constexpr int kFlagWords = kFlagRsBase + 2 * kTpMaxRowTiles * kTpMaxRanks;
+constexpr int kTpMaxRowTiles = 1024;              // row tiles of 128 per rank
+constexpr int kFlagRsBase = 64;                   // [slot 2][row tile][src 8]   partial tile of `src` has landed
+constexpr int kFlagAgBase = kFlagRsBase + 2 * kTpMaxRowTiles * kTpMaxRanks;  // [slot 2][src 8][row tile] staged
+constexpr int kFlagWords = kFlagAgBase + 2 * kTpMaxRanks * kTpMaxRowTiles;
+constexpr int kAuxLoads = 16;                     // 16-byte loads each aux thread keeps in flight
 
 // Layout of the local counter scratch (uint32 words), zeroed by the host function before each launch.
 constexpr int kCtrClaim = 0;      // next comm / reduce unit
-constexpr int kCtrOwnDone = 1;    // AG: own-rank units finished
 constexpr int kCtrTileClaim = 2;  // next GEMM tile
 constexpr int kSchedDepth = 4;    // claimed tiles the producer may run ahead of the slowest consumer
 constexpr int kCtrTiles = 8;      // AG: [row tile] slices landed;  RS: [row tile] epilogue warps finished
@@ -364,6 +364,7 @@ struct AgArgs {
   const __nv_bfloat16* x_local;   // [rows_local][ldx]
   long long ldx;
   __nv_bfloat16* gathered;        // [M][K] local, contiguous
+  int gather_own;                 // also copy this rank's own rows into `gathered`
   PeerPtrs stage;                 // this call's staging slot of every rank, [rows_local][K]
   PeerPtrs flags;                 // flag page of every rank
   int ldc;
@@ -468,12 +469,13 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (warp == 2 && lane == 0) tp_trace(c, kTrEpilogueDone);
   } else {
     // ------------------------------------------------------------------ comm warps
+    // Unit = 16 rows of one row tile.  Own units stage this rank's rows for the peers (and copy them into the
+    // gathered buffer when asked to); the last unit of a tile raises that tile's READY flag on every peer.
+    // Peer units wait for the tile's flag and pull the rows over NVLink into the gathered buffer.
     const int tid = threadIdx.x - 192;
-    const int own_units = tiles_per_rank * kTpParts;
     const int total_units = num_m * kTpParts;
     const int vec_per_row = c.K / 8;
     const int total_vec = kTpPartRows * vec_per_row;
-    uint32_t src_ready = 1u << c.rank;
     bool failed = false;
     if (tid == 0) tp_trace(c, kTrAuxFirst);
     for (;;) {
@@ -485,29 +487,30 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int m_tile = physical_m_tile(u / kTpParts, tiles_per_rank, c.rank, c.tp);
       const int part = u % kTpParts;
       const int src = m_tile / tiles_per_rank;
-      const long long src_row = static_cast<long long>(m_tile % tiles_per_rank) * kTpBlockM + part * kTpPartRows;
-      __nv_bfloat16* dst = a.gathered + (static_cast<long long>(m_tile) * kTpBlockM + part * kTpPartRows) * c.K;
+      const int m_local = m_tile % tiles_per_rank;
+      const long long src_row = static_cast<long long>(m_local) * kTpBlockM + part * kTpPartRows;
       const bool own = (src == c.rank);
-      if (!own && !((src_ready >> src) & 1u)) {
-        const uint32_t* flag = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagAgReady + slot * 8 + src;
+      if (!own) {
+        const uint32_t* flag = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagAgBase +
+                               (slot * kTpMaxRanks + src) * kTpMaxRowTiles + m_local;
         if (!aux_wait_flag<true>(s, c, flag, c.epoch, tid)) {
-          if (tid == 0) {
-            report_error(c.status, kErrPeerFlagWait);
-            *s.abort_flag = 1;
-          }
+          if (tid == 0) sched_fail(s, c, kErrPeerFlagWait);
           failed = true;
-          continue;  // next claim ends the loop for all 128 threads together
+          continue;  // the next claim ends the loop for all 128 threads together
         }
-        src_ready |= 1u << src;
       }
       const __nv_bfloat16* from = own ? a.x_local + src_row * a.ldx
                                       : reinterpret_cast<const __nv_bfloat16*>(a.stage.p[src]) + src_row * c.K;
       const long long from_ld = own ? a.ldx : c.K;
-      __nv_bfloat16* stage_dst = own ? reinterpret_cast<__nv_bfloat16*>(a.stage.p[c.rank]) + src_row * c.K : nullptr;
-      for (int base = tid; base < total_vec; base += kTpAuxThreads * 8) {
-        uint4 v[8];
+      __nv_bfloat16* dst1 = own ? reinterpret_cast<__nv_bfloat16*>(a.stage.p[c.rank]) + src_row * c.K
+                                : a.gathered + (static_cast<long long>(m_tile) * kTpBlockM + part * kTpPartRows) * c.K;
+      __nv_bfloat16* dst2 = (own && a.gather_own)
+                                ? a.gathered + (static_cast<long long>(m_tile) * kTpBlockM + part * kTpPartRows) * c.K
+                                : nullptr;
+      for (int base = tid; base < total_vec; base += kTpAuxThreads * kAuxLoads) {
+        uint4 v[kAuxLoads];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
+        for (int q = 0; q < kAuxLoads; ++q) {
           const int idx = base + q * kTpAuxThreads;
           if (idx < total_vec) {
             const int r = idx / vec_per_row, col = idx - r * vec_per_row;
@@ -515,33 +518,73 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           }
         }
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
+        for (int q = 0; q < kAuxLoads; ++q) {
           const int idx = base + q * kTpAuxThreads;
           if (idx < total_vec) {
-            *reinterpret_cast<uint4*>(dst + static_cast<long long>(idx) * 8) = v[q];
-            if (own) *reinterpret_cast<uint4*>(stage_dst + static_cast<long long>(idx) * 8) = v[q];
+            *reinterpret_cast<uint4*>(dst1 + static_cast<long long>(idx) * 8) = v[q];
+            if (dst2 != nullptr) *reinterpret_cast<uint4*>(dst2 + static_cast<long long>(idx) * 8) = v[q];
           }
         }
       }
       __threadfence_system();
       aux_barrier();
       if (tid == 0) {
-        red_release_gpu_add(&c.ctrs[kCtrTiles + m_tile], 1u);
         if (own) {
-          const uint32_t done = atomicAdd(&c.ctrs[kCtrOwnDone], 1u);
-          if (done == static_cast<uint32_t>(own_units - 1)) {
-            // every own-rank slice is in the staging slot: tell the peers
+          // count staged slices of this tile; the one that completes it tells the peers
+          const uint32_t done = atomicAdd(&c.ctrs[kCtrTiles + m_tile], 1u);
+          if (done == static_cast<uint32_t>(kTpParts - 1)) {
             __threadfence_system();
             for (int r = 0; r < c.tp; ++r)
               if (r != c.rank)
-                st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[r]) + kFlagAgReady + slot * 8 + c.rank, c.epoch);
+                st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[r]) + kFlagAgBase +
+                                   (slot * kTpMaxRanks + c.rank) * kTpMaxRowTiles + m_local,
+                               c.epoch);
           }
+        } else {
+          red_release_gpu_add(&c.ctrs[kCtrTiles + m_tile], 1u);  // the producer waits for kTpParts of these
         }
       }
     }
   }
   tp_epilogue_sync(s, warp, tmem_base);
   if (threadIdx.x == 0) tp_trace(c, kTrExit);
+}
+
+// Sum the TP partial copies of 16 rows (fixed rank order, fp32) and write bf16.
+template <int TP>
+__device__ __forceinline__ void reduce_unit(const __nv_bfloat16* __restrict__ in0, long long slot_stride,
+                                            __nv_bfloat16* __restrict__ out0, long long ldo, int vec_per_row,
+                                            int total_vec, int tid) {
+  constexpr int U = (8 / TP) > 0 ? (8 / TP) : 1;  // 8 loads in flight per thread
+  for (int base = tid; base < total_vec; base += kTpAuxThreads * U) {
+    uint4 v[U][TP];
+#pragma unroll
+    for (int q = 0; q < U; ++q) {
+      const int idx = base + q * kTpAuxThreads;
+      if (idx < total_vec) {
+#pragma unroll
+        for (int src = 0; src < TP; ++src) v[q][src] = ld_cg_v4(in0 + src * slot_stride + static_cast<long long>(idx) * 8);
+      }
+    }
+#pragma unroll
+    for (int q = 0; q < U; ++q) {
+      const int idx = base + q * kTpAuxThreads;
+      if (idx < total_vec) {
+        float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int src = 0; src < TP; ++src) {
+          f[0] += bf16_lo(v[q][src].x); f[1] += bf16_hi(v[q][src].x); f[2] += bf16_lo(v[q][src].y);
+          f[3] += bf16_hi(v[q][src].y); f[4] += bf16_lo(v[q][src].z); f[5] += bf16_hi(v[q][src].z);
+          f[6] += bf16_lo(v[q][src].w); f[7] += bf16_hi(v[q][src].w);
+        }
+        uint4 o;
+        o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+        o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+        const int r = idx / vec_per_row, col = idx - r * vec_per_row;
+        *reinterpret_cast<uint4*>(out0 + r * ldo + col * 8) = o;
+      }
+    }
+  }
 }
 
 // ===================================================================================== GEMM -> reduce-scatter
@@ -708,24 +751,12 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       const long long row0 = static_cast<long long>(m_local) * kTpBlockM + part * kTpPartRows;
       const __nv_bfloat16* in0 = a.recv_self + row0 * c.N;
-      for (int idx = tid; idx < total_vec; idx += kTpAuxThreads) {
-        const int r = idx / vec_per_row, col = idx - r * vec_per_row;
-        float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        uint4 v[kTpMaxRanks];
-#pragma unroll
-        for (int src = 0; src < kTpMaxRanks; ++src)
-          if (src < c.tp) v[src] = ld_cg_v4(in0 + src * slot_stride + static_cast<long long>(idx) * 8);
-#pragma unroll
-        for (int src = 0; src < kTpMaxRanks; ++src) {
-          if (src < c.tp) {
-            f[0] += bf16_lo(v[src].x); f[1] += bf16_hi(v[src].x); f[2] += bf16_lo(v[src].y); f[3] += bf16_hi(v[src].y);
-            f[4] += bf16_lo(v[src].z); f[5] += bf16_hi(v[src].z); f[6] += bf16_lo(v[src].w); f[7] += bf16_hi(v[src].w);
-          }
-        }
-        uint4 o;
-        o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
-        o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
-        *reinterpret_cast<uint4*>(a.out + (row0 + r) * a.ldo + col * 8) = o;
+      __nv_bfloat16* out0 = a.out + row0 * a.ldo;
+      switch (c.tp) {
+        case 2: reduce_unit<2>(in0, slot_stride, out0, a.ldo, vec_per_row, total_vec, tid); break;
+        case 4: reduce_unit<4>(in0, slot_stride, out0, a.ldo, vec_per_row, total_vec, tid); break;
+        case 8: reduce_unit<8>(in0, slot_stride, out0, a.ldo, vec_per_row, total_vec, tid); break;
+        default: reduce_unit<1>(in0, slot_stride, out0, a.ldo, vec_per_row, total_vec, tid); break;
       }
     }
   }
@@ -740,7 +771,7 @@ static int tp_configure(Kern kern) {
 }
 
 static int tp_check(int rows_local, int N, int K, int tp, int rank) {
-  if (tp < 2 || tp > kTpMaxRanks || rank < 0 || rank >= tp) return -kErrBadArgument;
+  if ((tp != 2 && tp != 4 && tp != 8) || rank < 0 || rank >= tp) return -kErrBadArgument;
   if (rows_local <= 0 || (rows_local % kTpBlockM) || rows_local / kTpBlockM > kTpMaxRowTiles) return -kErrBadArgument;
   if (K <= 0 || (K & 7) || N < 0 || (N & 7)) return -kErrBadArgument;
   return 0;
@@ -757,12 +788,13 @@ extern "C" int stb_tp_ctr_words(int row_tiles) { return kCtrTiles + row_tiles; }
 
 // C[tp*rows_local, N] = all_gather_rows(x_local) * B^T (b_mn_major = 0, B stored [N][ldb]) or * B
 // (b_mn_major = 1, B stored [K][ldb]); `gathered` [tp*rows_local][K] receives the gathered rows.
-// N = 0 gathers only.  stage_ptrs[r] / flag_ptrs[r]: rank r's staging slot for this call (slot = epoch & 1,
+// N = 0 gathers only; gather_own = 0 leaves this rank's own rows of `gathered` unwritten (the product reads
+// them from x_local).  stage_ptrs[r] / flag_ptrs[r]: rank r's staging slot for this call (slot = epoch & 1,
 // at least rows_local*K bf16) and flag page, as mapped into this process.  epoch: 1, 2, 3, ... per group,
 // the same on every rank.  ctrs: local scratch of stb_tp_ctr_words(row tiles) words.
 extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* gathered, void* const* stage_ptrs,
                                 void* const* flag_ptrs, const void* B, void* C, int rows_local, int N, int K, int ldb,
-                                int ldc, int b_mn_major, int rank, int tp, unsigned epoch, void* ctrs,
+                                int ldc, int b_mn_major, int gather_own, int rank, int tp, unsigned epoch, void* ctrs,
                                 unsigned long long wait_ns, int* status, void* trace, cudaStream_t stream) {
   int r = tp_check(rows_local, N, K, tp, rank);
   if (r) return r;
@@ -790,6 +822,7 @@ extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* gather
   a.x_local = static_cast<const __nv_bfloat16*>(x_local);
   a.ldx = ldx;
   a.gathered = static_cast<__nv_bfloat16*>(gathered);
+  a.gather_own = gather_own;
   a.ldc = ldc;
   for (int i = 0; i < tp; ++i) {
     a.stage.p[i] = stage_ptrs[i];

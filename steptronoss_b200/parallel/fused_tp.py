@@ -66,7 +66,7 @@ class _AllGatherLinearFn(torch.autograd.Function):
         if _peer(group_name, x.shape[0], x.shape[1], w.shape[0], x, w):
             from . import symm
 
-            y, _ = symm.all_gather_gemm(x, w, group_name, out_dtype=out_dtype)
+            y, _ = symm.all_gather_gemm(x, w, group_name, out_dtype=out_dtype, need_gathered=False)
             return y
         full = _ag_rows(x, group_name)
         return gemm(full, w, out_dtype=out_dtype or x.dtype)

@@ -64,7 +64,7 @@ native.register_signature("stb_symm_open", [P, P])
 native.register_signature("stb_symm_close", [P])
 native.register_signature("stb_symm_free", [P])
 native.register_signature(
-    "stb_gemm_ag_bf16", [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, U, P, ULL, P, P, P]
+    "stb_gemm_ag_bf16", [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, I, U, P, ULL, P, P, P]
 )
 native.register_signature(
     "stb_gemm_rs_bf16", [P, I, P, I, I, P, L, P, P, I, I, I, I, I, U, P, ULL, P, P, P]
@@ -207,8 +207,10 @@ def usable(rows_local: int, k: int, n: int, *tensors) -> bool:
     return all(t.is_cuda and t.dtype == torch.bfloat16 and t.stride(-1) == 1 for t in tensors)
 
 
-def all_gather_gemm(x, w, group_name: str = "TP", *, b_mn_major: bool = False, out_dtype=None):
-    """``(all_gather_rows(x) @ w.T  [or @ w], all_gather_rows(x))`` in one launch.  ``w=None`` gathers only."""
+def all_gather_gemm(x, w, group_name: str = "TP", *, b_mn_major: bool = False, out_dtype=None,
+                    need_gathered: bool = True):
+    """``(all_gather_rows(x) @ w.T  [or @ w], all_gather_rows(x))`` in one launch.  ``w=None`` gathers only;
+    ``need_gathered=False`` returns ``None`` for the gathered rows and saves the copy of the own block."""
     a = arena(group_name)
     rows, k = x.shape
     m = rows * a.world
@@ -223,7 +225,7 @@ def all_gather_gemm(x, w, group_name: str = "TP", *, b_mn_major: bool = False, o
     rc = a.lib.stb_gemm_ag_bf16(
         x.data_ptr(), x.stride(0), gathered.data_ptr(), stage, a._flag_arr,
         w.data_ptr() if n else None, y.data_ptr() if n else None, rows, n, k,
-        w.stride(0) if n else 8, y.stride(0) if n else 8, int(b_mn_major), a.rank, a.world,
+        w.stride(0) if n else 8, y.stride(0) if n else 8, int(b_mn_major), int(need_gathered), a.rank, a.world,
         a.ag_epoch & 0xFFFFFFFF, a.ctrs.data_ptr(), _WAIT_NS, native.status_word(x.device).data_ptr(),
         _TRACE.data_ptr() if _TRACE is not None else None, native.stream(),
     )
@@ -231,7 +233,7 @@ def all_gather_gemm(x, w, group_name: str = "TP", *, b_mn_major: bool = False, o
     count_launch(2)
     if y is not None and out_dtype not in (None, y.dtype):
         y = y.to(out_dtype)
-    return y, gathered
+    return y, (gathered if need_gathered else None)
 
 
 def gemm_reduce_scatter(x, w, group_name: str = "TP", *, b_mn_major: bool = False):
