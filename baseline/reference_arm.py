@@ -178,7 +178,7 @@ def _run(args) -> None:
     for _ in range(args.warmup):
         step()
     barrier_sync()
-    sampler = ClockSampler(os.path.join(os.path.dirname(HERE), "gpurun_out", "bench_clocks_reference.csv")) if rank == 0 else None
+    sampler = ClockSampler(os.path.join(os.path.dirname(HERE), "gpurun_out", "bench_clocks_reference.csv"), world) if rank == 0 else None
     if sampler:
         os.makedirs(os.path.dirname(sampler.path), exist_ok=True)
         sampler.start()

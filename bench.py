@@ -41,7 +41,7 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=8192)
     ap.add_argument("--recompute", default="auto", help="auto | none | full | comma list of block parts")
     ap.add_argument("--recompute-layers", type=int, default=None,
-                    help="recompute only the first N layers (default: 14 of 36 on one GPU, all otherwise)")
+                    help="recompute only the first N layers (default: 4 of 36 on one GPU, all otherwise)")
     ap.add_argument("--debug-layers", type=int, default=None, help="DEBUG ONLY: fewer layers (result marked invalid)")
     return ap.parse_args()
 
@@ -51,14 +51,19 @@ class ClockSampler:
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, path):
+    def __init__(self, path, n_gpus=None):
         self.path, self.proc = path, None
+        # sample only the GPUs this job runs on: an idle neighbour at its idle clock would skew the median
+        n = int(n_gpus or os.environ.get("WORLD_SIZE", "1"))
+        vis = [v for v in os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",") if v.strip()]
+        self.ids = vis[:n] if vis else [str(i) for i in range(n)]
 
     def start(self):
         try:
             self.f = open(self.path, "w")
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "200"], stdout=self.f, stderr=subprocess.DEVNULL)
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", ",".join(self.ids), f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=self.f, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
@@ -152,7 +157,7 @@ def run_ours(args):
     exp.model_cfg.recompute = True if rec == "full" else ([] if rec == "none" else rec.split(","))
     rec_layers = args.recompute_layers
     if rec_layers is None and rec == "full" and args.recompute == "auto" and not args.debug_layers:
-        rec_layers = 14  # 147 GB of static state leave room for the activations of about 22 layers
+        rec_layers = 4  # 147 GB of static state + the activations of 32 layers peak near 168 GB of the 179 GB
     if rec_layers is not None:
         exp.model_cfg.recompute_num_layers = rec_layers
         rec = f"{rec} (first {rec_layers} layers)"
@@ -196,7 +201,7 @@ def run_ours(args):
     live_iters = trainer.data_iterators
     staged = [Staged(it, n_micro * args.steps) for it in live_iters]
     trainer.data_iterators = [s if it is not None else None for s, it in zip(staged, live_iters)]
-    sampler = ClockSampler(os.path.join(ROOT, "gpurun_out", "bench_clocks.csv")) if rank == 0 else None
+    sampler = ClockSampler(os.path.join(ROOT, "gpurun_out", "bench_clocks.csv"), world) if rank == 0 else None
     if sampler:
         os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
         sampler.start()
