@@ -133,3 +133,79 @@ def test_async_accelerated_stream_is_the_serial_stream_and_resumes():
         assert [int(next(acc)["x"][0]) for _ in range(5)] == [4, 5, 6, 7, 8]
     finally:
         acc.close()
+
+
+def test_sft_pack_contract_and_training_on_packed_chat_samples():
+    import torch
+
+    from steptronoss_b200.exp.base_exp import GradientManagerConfig, ProfilerConfig
+    from steptronoss_b200.exp.lr_schedulers import ConstantSchedulerConfig
+    from steptronoss_b200.exp.ntp import NTPTrainerConfig, PretrainMetricConfig
+    from steptronoss_b200.exp.sft import SFTDataConfig, SFTDatasetsConfig, SFTExp
+    from steptronoss_b200.models.decoder_model import DecoderLLMConfig
+
+    class Chat:
+        """prompt tokens masked out, answer = prompt reversed (learnable)"""
+
+        def __init__(self, n, seed):
+            import random as _r
+
+            rnd = _r.Random(seed)
+            self.items = []
+            for _ in range(n):
+                p = [rnd.randrange(2, 30) for _ in range(rnd.randint(3, 8))]
+                toks = [1] + p + [31] + p[::-1] + [0]
+                mask = [0] * (len(p) + 2) + [1] * (len(p) + 1)
+                self.items.append({"tokens": toks, "loss_mask": mask})
+            self.sample_meta = [len(x["tokens"]) for x in self.items]
+
+        def __len__(self):
+            return len(self.items)
+
+        def __getitem__(self, i):
+            return self.items[i]
+
+    class Sets(SFTDatasetsConfig):
+        def build_datasets(self):
+            return {"a": (Chat(40, 0), 1.0), "b": (Chat(20, 1), 2.0)}
+
+    class Data(SFTDataConfig):
+        dataset_cfg = Sets
+        num_workers = 0
+
+    class Exp(SFTExp):
+        data_cfg = Data
+        scheduler_cfg = ConstantSchedulerConfig
+
+    e = Exp()
+    m = e.model_cfg
+    m.num_layers, m.hidden_size, m.params_dtype, m.variable_seq_lengths = 2, 32, torch.float32, True
+    a = m.attn_cfg
+    a.num_attention_heads, a.num_attention_groups, a.head_dim, a.hidden_size = 2, 1, 16, 32
+    m.ffn_cfg.hidden_size, m.ffn_cfg.ffn_hidden_size = 32, 64
+    m.tok_embed_cfg.vocab_size = m.out_embed_cfg.vocab_size = 32
+    m.tok_embed_cfg.hidden_size = m.out_embed_cfg.hidden_size = 32
+    m.parallel_cfg.expert_tensor_parallel_size = 1
+    t = e.trainer_cfg
+    t.global_batch_size, t.global_seq_length, t.train_iters, t.writer_backend = 2, 64, 8, []
+    e.scheduler_cfg.lr, e.scheduler_cfg.weight_decay, e.scheduler_cfg.warmup_schedule = 3e-3, 0.0, 0
+    e.data_cfg.seqlen_divisible_by = 8
+
+    dl = e.data_cfg.build_dataloader(0, 1)
+    batch = next(dl)
+    n = batch["tokens"].numel()
+    assert n % 8 == 0 and n <= 64 and batch["cu_seqlens"].dtype == torch.int32 and int(batch["cu_seqlens"][-1]) == n
+    first_doc = slice(0, int(batch["cu_seqlens"][1]))
+    assert torch.equal(batch["labels"][first_doc][:-1], batch["tokens"][first_doc][1:])   # shift by one inside a doc
+    assert batch["position_id"][first_doc].tolist() == list(range(first_doc.stop))
+    assert float(batch["loss_mask"][int(batch["cu_seqlens"][-2]):].sum()) >= 0            # padding doc is masked out
+
+    tr = e.trainer_cfg.get_trainer_cls()(exp=e)
+    tr.before_train()
+    losses = []
+    for _ in range(8):
+        tr.train_step()
+        tr.iteration += 1
+        tr.training_log()
+        losses.append(tr.history[-1]["lm_loss"])
+    assert losses[-1] < losses[0]
