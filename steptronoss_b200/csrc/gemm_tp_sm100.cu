@@ -1,11 +1,13 @@
 // Sequence-parallel projections as single kernels over NVLink peer memory (sm_100a).
 //
-//   gemm_ag_kernel : C = all_gather_rows(x) * B^T.   Four "comm" warps in every CTA publish this rank's
-//                    rows into a symmetric staging slot and pull the peers' rows over NVLink (plain peer
-//                    loads) into a local gathered buffer, 16-row slices at a time, bumping a per-row-tile
-//                    counter.  The TMA producer of the tcgen05 GEMM waits for the counter of the row tile
-//                    it is about to load, so products of rows that have arrived overlap the transfer of the
-//                    rest.  Row tiles are visited own-rank first, then in ring order.
+//   gemm_ag_kernel : C = all_gather_rows(x) * B^T.   The gathered matrix lives in symmetric memory.  Four
+//                    "comm" warps in every CTA push this rank's rows, 16-row slices at a time, straight into
+//                    every peer's gathered buffer (plain peer stores: posted writes keep NVLink busier than
+//                    loads, which pay a round trip) and raise a per-row-tile flag on the peer when a tile is
+//                    complete.  The TMA producer of the tcgen05 GEMM waits for the flag of the row tile it is
+//                    about to load, so products of rows that have arrived overlap the transfer of the rest.
+//                    Row tiles are visited own-rank first (read where the caller left them), then in ring
+//                    order.
 //   gemm_rs_kernel : out = reduce_scatter_rows(A * B^T).  The epilogue TMA-stores every bf16 partial tile
 //                    into the row owner's receive slot (peer stores), the last store of a row tile raises a
 //                    flag in the owner's memory, and four "reduce" warps per CTA add the tp slots of the row
@@ -17,10 +19,10 @@
 //
 // Cross-rank protocol.  Flags are uint32 words in each rank's symmetric flag page, written into the peer's
 // page with st.release.sys and read from the own page with ld.acquire.sys; they carry the call number
-// ("epoch", compared wrap-safe), so nothing is ever reset.  Staging and receive buffers have two slots
-// used alternately by epoch parity.  A slot written in call e was last read in call e-2, and no rank can
-// leave call e-1 before every peer has finished call e-2 (each call consumes data that every peer
-// produces inside the same call), so two slots need no further hand-shake.
+// ("epoch", compared wrap-safe), so nothing is ever reset.  Gathered and receive buffers have two slots
+// used alternately by epoch parity.  A slot written in call e was last read in call e-2 (and by what the
+// caller ran right after it), and no rank can leave call e-1 before every peer has entered call e-1 (each
+// call consumes data that every peer produces inside the same call), so two slots need no further hand-shake.
 // GEMM tiles and the work of the comm / reduce warps are claimed from device counters, not assigned by CTA
 // index, so progress never depends on a CTA that is not resident (for instance while a collective of another
 // stream holds some SMs and is itself waiting for the peer).  Every wait is bounded by the caller's budget; on time-out
@@ -46,6 +48,8 @@ constexpr int kFlagRsBase = 64;                   // [slot 2][row tile][src 8]  
 constexpr int kFlagAgBase = kFlagRsBase + 2 * kTpMaxRowTiles * kTpMaxRanks;  // [slot 2][src 8][row tile] staged
 constexpr int kFlagWords = kFlagAgBase + 2 * kTpMaxRanks * kTpMaxRowTiles;
 constexpr int kAuxLoads = 16;                     // 16-byte loads each aux thread keeps in flight
+constexpr int kRsParts = 16;                      // the reduction works on 8-row slices: a short tail after the
+constexpr int kRsPartRows = kTpBlockM / kRsParts; // last partial tile has landed
 
 // Layout of the local counter scratch (uint32 words), zeroed by the host function before each launch.
 constexpr int kCtrClaim = 0;      // next comm / reduce unit
@@ -363,9 +367,8 @@ struct AgArgs {
   TpCommon c;
   const __nv_bfloat16* x_local;   // [rows_local][ldx]
   long long ldx;
-  __nv_bfloat16* gathered;        // [M][K] local, contiguous
-  int gather_own;                 // also copy this rank's own rows into `gathered`
-  PeerPtrs stage;                 // this call's staging slot of every rank, [rows_local][K]
+  PeerPtrs gathered;              // this call's gathered buffer [M][K] of every rank (own entry: local memory)
+  int gather_own;                 // also copy this rank's own rows into the own gathered buffer
   PeerPtrs flags;                 // flag page of every rank
   int ldc;
 };
@@ -405,15 +408,18 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         int m_log, n_tile;
         decode_tp_tile(tile, num_m, num_n, m_log, n_tile);
         const int m_tile = physical_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
-        // Own rows are read where the caller left them; peers' rows must have landed in the gathered buffer
-        // (comm warps of any CTA wrote them).
+        // Own rows are read where the caller left them; a peer's rows must have landed in the gathered buffer
+        // (the peer raises the tile's flag after its stores).
         const bool own = (m_tile / tiles_per_rank) == c.rank;
         if (!own && !(m_tile < 64 && ((ready_mask >> m_tile) & 1ull))) {
-          if (!wait_flag_ge<false>(&c.ctrs[kCtrTiles + m_tile], kTpParts, c.wait_ns, s.abort_flag)) {
+          const uint32_t* flag = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagAgBase +
+                                 (slot * kTpMaxRanks + m_tile / tiles_per_rank) * kTpMaxRowTiles +
+                                 m_tile % tiles_per_rank;
+          if (!wait_flag_ge<true>(flag, c.epoch, c.wait_ns, s.abort_flag)) {
             sched_fail(s, c, kErrPeerFlagWait);
             break;
           }
-          fence_proxy_async_global();  // generic-proxy stores, acquired above -> visible to the TMA reads
+          fence_proxy_async_global();  // the peer's stores, acquired above -> visible to the TMA reads
           if (m_tile < 64) ready_mask |= 1ull << m_tile;
         }
         const CUtensorMap* ta = own ? &tmap_x : &tmap_a;
@@ -469,44 +475,23 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     if (warp == 2 && lane == 0) tp_trace(c, kTrEpilogueDone);
   } else {
     // ------------------------------------------------------------------ comm warps
-    // Unit = 16 rows of one row tile.  Own units stage this rank's rows for the peers (and copy them into the
-    // gathered buffer when asked to); the last unit of a tile raises that tile's READY flag on every peer.
-    // Peer units wait for the tile's flag and pull the rows over NVLink into the gathered buffer.
+    // Unit = 16 rows of one of this rank's row tiles: read once, stored into every peer's gathered buffer
+    // (and the own one when asked to); the unit that completes a tile raises its flag on every peer.
     const int tid = threadIdx.x - 192;
-    const int total_units = num_m * kTpParts;
+    const int total_units = tiles_per_rank * kTpParts;
     const int vec_per_row = c.K / 8;
     const int total_vec = kTpPartRows * vec_per_row;
-    bool failed = false;
     if (tid == 0) tp_trace(c, kTrAuxFirst);
     for (;;) {
       const int u = aux_claim(s, c.ctrs, tid);
-      if (u >= total_units || failed || *s.abort_flag) {
+      if (u >= total_units || *s.abort_flag) {
         if (tid == 0) tp_trace(c, kTrAuxDone);
         break;
       }
-      const int m_tile = physical_m_tile(u / kTpParts, tiles_per_rank, c.rank, c.tp);
-      const int part = u % kTpParts;
-      const int src = m_tile / tiles_per_rank;
-      const int m_local = m_tile % tiles_per_rank;
+      const int m_local = u / kTpParts, part = u % kTpParts;
       const long long src_row = static_cast<long long>(m_local) * kTpBlockM + part * kTpPartRows;
-      const bool own = (src == c.rank);
-      if (!own) {
-        const uint32_t* flag = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagAgBase +
-                               (slot * kTpMaxRanks + src) * kTpMaxRowTiles + m_local;
-        if (!aux_wait_flag<true>(s, c, flag, c.epoch, tid)) {
-          if (tid == 0) sched_fail(s, c, kErrPeerFlagWait);
-          failed = true;
-          continue;  // the next claim ends the loop for all 128 threads together
-        }
-      }
-      const __nv_bfloat16* from = own ? a.x_local + src_row * a.ldx
-                                      : reinterpret_cast<const __nv_bfloat16*>(a.stage.p[src]) + src_row * c.K;
-      const long long from_ld = own ? a.ldx : c.K;
-      __nv_bfloat16* dst1 = own ? reinterpret_cast<__nv_bfloat16*>(a.stage.p[c.rank]) + src_row * c.K
-                                : a.gathered + (static_cast<long long>(m_tile) * kTpBlockM + part * kTpPartRows) * c.K;
-      __nv_bfloat16* dst2 = (own && a.gather_own)
-                                ? a.gathered + (static_cast<long long>(m_tile) * kTpBlockM + part * kTpPartRows) * c.K
-                                : nullptr;
+      const __nv_bfloat16* from = a.x_local + src_row * a.ldx;
+      const long long dst_off = (static_cast<long long>(c.rank) * c.rows_local + src_row) * c.K;
       for (int base = tid; base < total_vec; base += kTpAuxThreads * kAuxLoads) {
         uint4 v[kAuxLoads];
 #pragma unroll
@@ -514,35 +499,44 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           const int idx = base + q * kTpAuxThreads;
           if (idx < total_vec) {
             const int r = idx / vec_per_row, col = idx - r * vec_per_row;
-            v[q] = ld_cg_v4(from + r * from_ld + col * 8);
+            v[q] = ld_cg_v4(from + r * a.ldx + col * 8);
           }
         }
+        for (int pr = 1; pr <= c.tp; ++pr) {
+          const int dst_rank = (c.rank + pr) % c.tp;  // peers in ring order, own buffer last
+          if (dst_rank == c.rank && !a.gather_own) continue;
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.gathered.p[dst_rank]) + dst_off;
 #pragma unroll
-        for (int q = 0; q < kAuxLoads; ++q) {
-          const int idx = base + q * kTpAuxThreads;
-          if (idx < total_vec) {
-            *reinterpret_cast<uint4*>(dst1 + static_cast<long long>(idx) * 8) = v[q];
-            if (dst2 != nullptr) *reinterpret_cast<uint4*>(dst2 + static_cast<long long>(idx) * 8) = v[q];
+          for (int q = 0; q < kAuxLoads; ++q) {
+            const int idx = base + q * kTpAuxThreads;
+            if (idx < total_vec) *reinterpret_cast<uint4*>(dst + static_cast<long long>(idx) * 8) = v[q];
           }
         }
       }
       __threadfence_system();
       aux_barrier();
       if (tid == 0) {
-        if (own) {
-          // count staged slices of this tile; the one that completes it tells the peers
-          const uint32_t done = atomicAdd(&c.ctrs[kCtrTiles + m_tile], 1u);
-          if (done == static_cast<uint32_t>(kTpParts - 1)) {
-            __threadfence_system();
-            for (int r = 0; r < c.tp; ++r)
-              if (r != c.rank)
-                st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[r]) + kFlagAgBase +
-                                   (slot * kTpMaxRanks + c.rank) * kTpMaxRowTiles + m_local,
-                               c.epoch);
-          }
-        } else {
-          red_release_gpu_add(&c.ctrs[kCtrTiles + m_tile], 1u);  // the producer waits for kTpParts of these
+        const uint32_t done = atomicAdd(&c.ctrs[kCtrTiles + m_local], 1u);
+        if (done == static_cast<uint32_t>(kTpParts - 1)) {
+          __threadfence_system();
+          for (int r = 0; r < c.tp; ++r)
+            if (r != c.rank)
+              st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[r]) + kFlagAgBase +
+                                 (slot * kTpMaxRanks + c.rank) * kTpMaxRowTiles + m_local,
+                             c.epoch);
         }
+      }
+    }
+    if (num_tiles == 0) {
+      // Gather only: no product consumes the tiles, so wait here until every peer's rows have landed
+      // (the row tiles are spread over the CTAs).
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_m && ok; t += gridDim.x) {
+        if (t / tiles_per_rank == c.rank) continue;
+        const uint32_t* flag = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagAgBase +
+                               (slot * kTpMaxRanks + t / tiles_per_rank) * kTpMaxRowTiles + t % tiles_per_rank;
+        ok = aux_wait_flag<true>(s, c, flag, c.epoch, tid);
+        if (!ok && tid == 0) sched_fail(s, c, kErrPeerFlagWait);
       }
     }
   }
@@ -719,9 +713,9 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   } else {
     // ------------------------------------------------------------------ reduce warps: rows this rank owns
     const int tid = threadIdx.x - 192;
-    const int total_units = tiles_per_rank * kTpParts;
+    const int total_units = tiles_per_rank * kRsParts;
     const int vec_per_row = c.N / 8;
-    const int total_vec = kTpPartRows * vec_per_row;
+    const int total_vec = kRsPartRows * vec_per_row;
     const long long slot_stride = static_cast<long long>(c.rows_local) * c.N;
     const uint32_t* my_flags = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagRsBase +
                                slot * kTpMaxRowTiles * kTpMaxRanks;
@@ -734,11 +728,18 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         if (tid == 0) tp_trace(c, kTrAuxDone);
         break;
       }
-      const int m_local = u / kTpParts, part = u % kTpParts;
+      const int m_local = u / kRsParts, part = u % kRsParts;
       if (m_local != ready_tile) {
-        bool ok = true;
-        for (int src = 0; src < c.tp && ok; ++src)
-          ok = aux_wait_flag<true>(s, c, my_flags + m_local * kTpMaxRanks + src, c.epoch, tid);
+        // one thread waits for the partial tile of every rank, then everybody learns the outcome
+        if (tid == 0) {
+          int good = 1;
+          for (int src = 0; src < c.tp && good; ++src)
+            good = wait_flag_ge<true>(my_flags + m_local * kTpMaxRanks + src, c.epoch, c.wait_ns, s.abort_flag) ? 1 : 0;
+          *s.claim_slot = good;
+        }
+        aux_barrier();
+        const bool ok = *s.claim_slot != 0;
+        aux_barrier();
         if (!ok) {
           if (tid == 0) {
             report_error(c.status, kErrPeerFlagWait);
@@ -749,7 +750,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         ready_tile = m_local;
       }
-      const long long row0 = static_cast<long long>(m_local) * kTpBlockM + part * kTpPartRows;
+      const long long row0 = static_cast<long long>(m_local) * kTpBlockM + part * kRsPartRows;
       const __nv_bfloat16* in0 = a.recv_self + row0 * c.N;
       __nv_bfloat16* out0 = a.out + row0 * a.ldo;
       switch (c.tp) {
@@ -788,11 +789,12 @@ extern "C" int stb_tp_ctr_words(int row_tiles) { return kCtrTiles + row_tiles; }
 
 // C[tp*rows_local, N] = all_gather_rows(x_local) * B^T (b_mn_major = 0, B stored [N][ldb]) or * B
 // (b_mn_major = 1, B stored [K][ldb]); `gathered` [tp*rows_local][K] receives the gathered rows.
-// N = 0 gathers only; gather_own = 0 leaves this rank's own rows of `gathered` unwritten (the product reads
-// them from x_local).  stage_ptrs[r] / flag_ptrs[r]: rank r's staging slot for this call (slot = epoch & 1,
-// at least rows_local*K bf16) and flag page, as mapped into this process.  epoch: 1, 2, 3, ... per group,
+// N = 0 gathers only; gather_own = 0 leaves this rank's own rows of the gathered matrix unwritten (the product
+// reads them from x_local).  gathered_ptrs[r] / flag_ptrs[r]: rank r's gathered buffer for this call (slot =
+// epoch & 1, tp*rows_local*K bf16, symmetric memory) and flag page, as mapped into this process; the result is
+// in gathered_ptrs[rank] and stays valid until the second-next call on the group.  epoch: 1, 2, 3, ... per group,
 // the same on every rank.  ctrs: local scratch of stb_tp_ctr_words(row tiles) words.
-extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* gathered, void* const* stage_ptrs,
+extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* const* gathered_ptrs,
                                 void* const* flag_ptrs, const void* B, void* C, int rows_local, int N, int K, int ldb,
                                 int ldc, int b_mn_major, int gather_own, int rank, int tp, unsigned epoch, void* ctrs,
                                 unsigned long long wait_ns, int* status, void* trace, cudaStream_t stream) {
@@ -801,7 +803,7 @@ extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* gather
   if ((ldx & 7) || (N > 0 && ((ldb & 7) || (ldc & 7)))) return -kErrBadArgument;
   const int M = tp * rows_local;
   CUtensorMap ta, tx, tb, tc;
-  r = make_tmap_2d_bf16(&ta, gathered, K, M, static_cast<uint64_t>(K) * 2, kTpBlockK, kTpBlockM, 1);
+  r = make_tmap_2d_bf16(&ta, gathered_ptrs[rank], K, M, static_cast<uint64_t>(K) * 2, kTpBlockK, kTpBlockM, 1);
   if (r) return r;
   r = make_tmap_2d_bf16(&tx, x_local, K, rows_local, static_cast<uint64_t>(ldx) * 2, kTpBlockK, kTpBlockM, 1);
   if (r) return r;
@@ -821,11 +823,10 @@ extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* gather
   a.c.trace = static_cast<unsigned long long*>(trace);
   a.x_local = static_cast<const __nv_bfloat16*>(x_local);
   a.ldx = ldx;
-  a.gathered = static_cast<__nv_bfloat16*>(gathered);
   a.gather_own = gather_own;
   a.ldc = ldc;
   for (int i = 0; i < tp; ++i) {
-    a.stage.p[i] = stage_ptrs[i];
+    a.gathered.p[i] = gathered_ptrs[i];
     a.flags.p[i] = flag_ptrs[i];
   }
   cudaError_t e = cudaMemsetAsync(ctrs, 0, sizeof(uint32_t) * (kCtrTiles + M / kTpBlockM), stream);

@@ -27,16 +27,21 @@ def _exchange_shapes(send_next, send_prev, recv_prev: bool, recv_next: bool):
         s = list(t.shape) + [0] * (3 - t.dim())
         return torch.tensor(s[:3], dtype=torch.int64, device=dev)
 
+    prev, nxt = PM.pipeline_prev_rank(), PM.pipeline_next_rank()
+    sends, recvs = [], []
     if send_prev is not None:
-        ops.append(dist.P2POp(dist.isend, enc(send_prev), PM.pipeline_prev_rank(), group))
+        sends.append(dist.P2POp(dist.isend, enc(send_prev), prev, group))
+    if send_next is not None:
+        sends.append(dist.P2POp(dist.isend, enc(send_next), nxt, group))
     if recv_prev:
         bufs["prev"] = torch.empty(3, dtype=torch.int64, device=dev)
-        ops.append(dist.P2POp(dist.irecv, bufs["prev"], PM.pipeline_prev_rank(), group))
-    if send_next is not None:
-        ops.append(dist.P2POp(dist.isend, enc(send_next), PM.pipeline_next_rank(), group))
+        recvs.append(dist.P2POp(dist.irecv, bufs["prev"], prev, group))
     if recv_next:
         bufs["next"] = torch.empty(3, dtype=torch.int64, device=dev)
-        ops.append(dist.P2POp(dist.irecv, bufs["next"], PM.pipeline_next_rank(), group))
+        recvs.append(dist.P2POp(dist.irecv, bufs["next"], nxt, group))
+    if prev == nxt:
+        recvs.reverse()  # see communicate(): one peer on both sides, messages match in issue order
+    ops = sends + recvs
     if ops:
         for r in dist.batch_isend_irecv(ops):
             r.wait()
@@ -57,17 +62,23 @@ def communicate(send_next=None, send_prev=None, recv_prev: bool = False, recv_ne
     if variable_seq_lengths:
         shape_prev, shape_next = _exchange_shapes(send_next, send_prev, recv_prev, recv_next)
     from_prev = from_next = None
-    ops = []
+    prev, nxt = PM.pipeline_prev_rank(), PM.pipeline_next_rank()
+    sends, recvs = [], []
     if send_prev is not None:
-        ops.append(dist.P2POp(dist.isend, send_prev.contiguous(), PM.pipeline_prev_rank(), group))
+        sends.append(dist.P2POp(dist.isend, send_prev.contiguous(), prev, group))
+    if send_next is not None:
+        sends.append(dist.P2POp(dist.isend, send_next.contiguous(), nxt, group))
     if recv_prev:
         from_prev = torch.empty(shape_prev, dtype=dtype, device=dev, requires_grad=True)
-        ops.append(dist.P2POp(dist.irecv, from_prev, PM.pipeline_prev_rank(), group))
-    if send_next is not None:
-        ops.append(dist.P2POp(dist.isend, send_next.contiguous(), PM.pipeline_next_rank(), group))
+        recvs.append(dist.P2POp(dist.irecv, from_prev, prev, group))
     if recv_next:
         from_next = torch.empty(shape_next, dtype=dtype, device=dev)
-        ops.append(dist.P2POp(dist.irecv, from_next, PM.pipeline_next_rank(), group))
+        recvs.append(dist.P2POp(dist.irecv, from_next, nxt, group))
+    if prev == nxt:
+        # two stages: both neighbours are the same rank, and messages between one pair of ranks match in issue
+        # order.  The peer issues (to-prev, to-next); its to-prev is what this rank receives "from next".
+        recvs.reverse()
+    ops = sends + recvs
     reqs = dist.batch_isend_irecv(ops) if ops else []
     if wait:
         for r in reqs:

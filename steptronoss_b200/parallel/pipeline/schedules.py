@@ -70,10 +70,17 @@ class FWBWScheduler:
         with get_timers().record("batch-generator", 2):
             keep = PM.get_vpp_rank()
             self._prefetched = [[] for _ in self.models]
-            for vp, it in enumerate(self.data_iterators):
-                PM.set_vpp_rank(vp)
-                for _ in range(n):
-                    self._prefetched[vp].append(self.data_sync_fn(it))
+            live = [it for it in self.data_iterators if it is not None]
+            if len(self.models) > 1 and len({id(it) for it in live}) <= 1:
+                # one stream feeds every model chunk of this rank: fetch each micro-batch once and share it
+                PM.set_vpp_rank(0)
+                batches = [self.data_sync_fn(self.data_iterators[0]) for _ in range(n)]
+                self._prefetched = [list(batches) for _ in self.models]
+            else:
+                for vp, it in enumerate(self.data_iterators):
+                    PM.set_vpp_rank(vp)
+                    for _ in range(n):
+                        self._prefetched[vp].append(self.data_sync_fn(it))
             PM.set_vpp_rank(keep)
 
     def forward_chunk(self, vp_rank: int = 0, input_tensor=None, loss_scale: float = 1.0):
@@ -184,7 +191,16 @@ class PPScheduler(FWBWScheduler):
 
 
 class VPPScheduler(PPScheduler):
-    """Interleaved 1F1B over ``len(models)`` virtual chunks per rank."""
+    """Interleaved 1F1B: every rank holds ``C = len(models)`` model chunks; virtual stage ``v = c * P + r``.
+
+    Micro-step ``k`` of the forward order works on chunk ``(k mod P*C) // P`` (backward: mirrored), i.e. ``P``
+    micro-batches go through chunk 0, then the same ``P`` through chunk 1, and so on.  After a warm-up of
+    ``2 (P - r - 1) + (C - 1) P`` forward steps every step runs one forward and one backward and exchanges both
+    results with the neighbours in a single batch; the ring wraps from the last rank to the first between
+    chunks.  Needs ``forward_num`` to be a multiple of ``P``.  This is the published Megatron-LM interleaved
+    schedule (Narayanan et al., 2021), which the reference follows too
+    (``steptronoss/core/pipeline_parallel/schedules.py:322-693``).
+    """
 
     def run(self, forward_num: int = 1):
         self._collected.clear()
@@ -196,112 +212,95 @@ class VPPScheduler(PPScheduler):
         p2p = self._p2p()
         total = forward_num * C
         scale = 1.0 / forward_num
-        if forward_num == P:
-            warmup = total
-        else:
-            warmup = min((P - r - 1) * 2 + (C - 1) * P, total)
-        steady = total - warmup
+        train = self.training
+        all_warmup = forward_num == P or not train
+        warmup = total if all_warmup else min((P - r - 1) * 2 + (C - 1) * P, total)
+        remaining = total - warmup
         inputs = [[] for _ in range(C)]
         outputs = [[] for _ in range(C)]
         out_grads = [[] for _ in range(C)]
+        first_rank, last_rank = r == 0, r == P - 1
 
-        def chunk_of(step: int, forward: bool) -> int:
-            c = (step % (P * C)) // P
+        def chunk_of(k: int, forward: bool) -> int:
+            c = (k % (P * C)) // P
             return c if forward else C - 1 - c
 
-        def do_fwd(k: int):
+        def forward_step(k: int):
             c = chunk_of(k, True)
             PM.set_vpp_rank(c)
-            if PM.is_pipeline_first_stage() and len(inputs[c]) == len(outputs[c]):
+            if first_rank and c == 0 and len(inputs[c]) == len(outputs[c]):
                 inputs[c].append(None)
             out = self.forward_chunk(c, inputs[c][-1], scale)
-            outputs[c].append(out)
-            return out
+            if train:
+                outputs[c].append(out)
+            else:
+                inputs[c].pop()
+            return None if (last_rank and c == C - 1) else out  # the last virtual stage sends nothing on
 
-        def do_bwd(k: int):
+        def backward_step(k: int):
             c = chunk_of(k, False)
             PM.set_vpp_rank(c)
-            if PM.is_pipeline_last_stage() and len(out_grads[c]) == 0:
+            if last_rank and c == C - 1 and len(out_grads[c]) == 0:
                 out_grads[c].append(None)
-            i0, o0, g0 = inputs[c].pop(0), outputs[c].pop(0), out_grads[c].pop(0)
-            return self._backward(i0, o0, g0)
-
-        def next_recv_prev(k: int) -> tuple[bool, int]:
-            """Does the forward after micro-step ``k`` need an activation from the previous rank, and for
-            which chunk?"""
-            nc = chunk_of(k + 1, True) if k + 1 < total else None
-            if nc is None:
-                return False, 0
-            if r == 0:
-                # first rank receives from the last rank the output of the previous chunk
-                need = nc > 0 or False
-                prev_chunk_done = k + 1 >= P  # data wrapped around once
-                return (nc != 0) and prev_chunk_done or (nc != 0), nc
-            return True, nc
-
-        def next_recv_next(k: int) -> tuple[bool, int]:
-            nc = chunk_of(k + 1, False) if k + 1 < total else None
-            if nc is None:
-                return False, 0
-            if r == P - 1:
-                return nc != C - 1, nc
-            return True, nc
+            gin = self._backward(inputs[c].pop(0), outputs[c].pop(0), out_grads[c].pop(0))
+            return None if (first_rank and c == 0) else gin   # the first virtual stage sends nothing back
 
         PM.set_vpp_rank(0)
-        if not PM.is_pipeline_first_stage():
-            inputs[0].append(p2p.recv_forward())
-        elif r != 0:
-            inputs[0].append(p2p.recv_forward())
+        inputs[0].append(p2p.recv_forward())
         for k in range(warmup):
-            out = do_fwd(k)
-            c = chunk_of(k, True)
-            PM.set_vpp_rank(c)
-            send = None if PM.is_pipeline_last_stage() else out
-            rp, nc = next_recv_prev(k)
-            if k == total - 1:
-                rp = False
-            got = p2p.send_forward_recv_forward(send, recv_prev=rp) if (send is not None or rp) else None
-            if send is not None and self.training:
+            out = forward_step(k)
+            nxt = chunk_of(k + 1, True)
+            recv_prev = not (first_rank and nxt == 0) and k != total - 1
+            if k == warmup - 1 and train and not all_warmup:
+                got, grad = p2p.send_forward_backward_recv_forward_backward(out, None, recv_prev, not last_rank)
+                out_grads[C - 1].append(grad)
+            else:
+                got = p2p.send_forward_recv_forward(out, recv_prev)
+            if recv_prev or not (k == total - 1):
+                inputs[nxt].append(got)
+            if out is not None and train:
                 deallocate_output_tensor(out)
-            if rp:
-                inputs[nc].append(got)
-        if self.training:
-            if steady > 0 or warmup == total:
-                PM.set_vpp_rank(C - 1)
-                if not PM.is_pipeline_last_stage():
-                    out_grads[C - 1].append(p2p.recv_backward())
-            for k in range(steady):
-                fk = warmup + k
-                out = do_fwd(fk)
-                c = chunk_of(fk, True)
-                PM.set_vpp_rank(c)
-                send_f = None if PM.is_pipeline_last_stage() else out
-                gin = do_bwd(k)
-                bc = chunk_of(k, False)
-                PM.set_vpp_rank(bc)
-                send_b = None if PM.is_pipeline_first_stage() else gin
-                rp, nfc = next_recv_prev(fk)
-                rn, nbc = next_recv_next(k)
-                if k == total - 1:
-                    rn = False
-                a, b = p2p.send_forward_backward_recv_forward_backward(send_f, send_b, rp, rn)
-                if send_f is not None:
-                    deallocate_output_tensor(out)
-                if rp:
-                    inputs[nfc].append(a)
-                if rn:
-                    out_grads[nbc].append(b)
-            for k in range(steady, total):
-                gin = do_bwd(k)
-                bc = chunk_of(k, False)
-                PM.set_vpp_rank(bc)
-                send_b = None if PM.is_pipeline_first_stage() else gin
-                rn, nbc = next_recv_next(k)
-                if k == total - 1:
-                    rn = False
-                got = p2p.send_backward_recv_backward(send_b, recv_next=rn) if (send_b is not None or rn) else None
-                if rn:
-                    out_grads[nbc].append(got)
-        self._prefetched = None
+
+        for k in range(remaining):
+            fk = k + warmup
+            out = forward_step(fk)
+            gin = backward_step(k)
+            # what arrives next: the first rank runs P-1 steps ahead of the last rank around the ring
+            recv_prev = True
+            if first_rank:
+                nf = chunk_of(fk - (P - 1), True)
+                if nf == C - 1:
+                    recv_prev = False
+                nf += 1
+            else:
+                nf = chunk_of(fk + 1, True)
+            recv_next = True
+            if last_rank:
+                nb = chunk_of(k - (P - 1), False)
+                if nb == 0:
+                    recv_next = False
+                nb -= 1
+            else:
+                nb = chunk_of(k + 1, False)
+            if k == remaining - 1:
+                recv_prev = False
+            got, grad = p2p.send_forward_backward_recv_forward_backward(out, gin, recv_prev, recv_next)
+            if out is not None:
+                deallocate_output_tensor(out)
+            if recv_prev:
+                inputs[nf].append(got)
+            if recv_next:
+                out_grads[nb].append(grad)
+
+        if train:
+            if all_warmup:
+                out_grads[C - 1].append(p2p.recv_backward())
+            for k in range(remaining, total):
+                gin = backward_step(k)
+                nb = chunk_of(k + 1, False)
+                recv_next = not (last_rank and nb == C - 1) and k != total - 1
+                grad = p2p.send_backward_recv_backward(gin, recv_next)
+                out_grads[nb].append(grad)
         PM.set_vpp_rank(0)
+        self._prefetched = None
         return self._collected

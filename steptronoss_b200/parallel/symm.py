@@ -64,11 +64,18 @@ native.register_signature("stb_symm_open", [P, P])
 native.register_signature("stb_symm_close", [P])
 native.register_signature("stb_symm_free", [P])
 native.register_signature(
-    "stb_gemm_ag_bf16", [P, L, P, P, P, P, P, I, I, I, I, I, I, I, I, I, U, P, ULL, P, P, P]
+    "stb_gemm_ag_bf16", [P, L, P, P, P, P, I, I, I, I, I, I, I, I, I, U, P, ULL, P, P, P]
 )
 native.register_signature(
     "stb_gemm_rs_bf16", [P, I, P, I, I, P, L, P, P, I, I, I, I, I, U, P, ULL, P, P, P]
 )
+
+
+class _DevicePointer:
+    """Lets torch wrap memory it did not allocate (``__cuda_array_interface__``)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
 
 
 class SymmetricBuffer:
@@ -110,6 +117,12 @@ class SymmetricBuffer:
             self.release()
             raise RuntimeError("mapping a peer's memory failed on some rank")
 
+    def own_tensor(self) -> torch.Tensor:
+        """The own buffer as a uint8 tensor (no copy; the buffer outlives the tensor's uses by contract)."""
+        if getattr(self, "_own_tensor", None) is None:
+            self._own_tensor = torch.as_tensor(_DevicePointer(self.own, self.nbytes), device="cuda")
+        return self._own_tensor
+
     def ptr_array(self, offset: int = 0):
         arr = (c_void_p * _MAX_RANKS)()
         for r in range(self.world):
@@ -124,10 +137,11 @@ class SymmetricBuffer:
         if self.own:
             self.lib.stb_symm_free(c_void_p(self.own))
         self.ptrs, self.own = [], 0
+        self._own_tensor = None
 
 
 class Arena:
-    """Flag page, staging slots (all-gather) and receive slots (reduce-scatter) of one group."""
+    """Flag page, gathered-matrix slots (all-gather) and receive slots (reduce-scatter) of one group."""
 
     def __init__(self, group_name: str):
         self.group_name = group_name
@@ -158,10 +172,12 @@ class Arena:
         setattr(self, which + "_slot", slot_bytes)
         dist.barrier(group=self.group)
 
-    def stage_ptrs(self, need: int, epoch: int):
+    def gathered_slot(self, need: int, epoch: int):
+        """``(pointer array over ranks, own slot as uint8 tensor)`` of this call's gathered matrix."""
         if need > self.stage_slot:
             self._grow("stage", need)
-        return self.stage.ptr_array((epoch & 1) * self.stage_slot)
+        off = (epoch & 1) * self.stage_slot
+        return self.stage.ptr_array(off), self.stage.own_tensor()[off: off + need]
 
     def recv_ptrs(self, need: int, epoch: int):
         if need > self.recv_slot:
@@ -210,7 +226,10 @@ def usable(rows_local: int, k: int, n: int, *tensors) -> bool:
 def all_gather_gemm(x, w, group_name: str = "TP", *, b_mn_major: bool = False, out_dtype=None,
                     need_gathered: bool = True):
     """``(all_gather_rows(x) @ w.T  [or @ w], all_gather_rows(x))`` in one launch.  ``w=None`` gathers only;
-    ``need_gathered=False`` returns ``None`` for the gathered rows and saves the copy of the own block."""
+    ``need_gathered=False`` returns ``None`` for the gathered rows and saves the copy of the own block.
+
+    The gathered matrix is a view of the group's symmetric memory: it stays valid until the second-next
+    fused all-gather on the group (consume it, or copy it, before that)."""
     a = arena(group_name)
     rows, k = x.shape
     m = rows * a.world
@@ -218,12 +237,12 @@ def all_gather_gemm(x, w, group_name: str = "TP", *, b_mn_major: bool = False, o
         n = 0
     else:
         n = w.shape[1] if b_mn_major else w.shape[0]
-    gathered = torch.empty((m, k), dtype=x.dtype, device=x.device)
     y = torch.empty((m, n), dtype=x.dtype, device=x.device) if n else None
     a.ag_epoch += 1
-    stage = a.stage_ptrs(rows * k * 2, a.ag_epoch)
+    ptrs, own = a.gathered_slot(m * k * 2, a.ag_epoch)
+    gathered = own.view(torch.bfloat16).view(m, k)
     rc = a.lib.stb_gemm_ag_bf16(
-        x.data_ptr(), x.stride(0), gathered.data_ptr(), stage, a._flag_arr,
+        x.data_ptr(), x.stride(0), ptrs, a._flag_arr,
         w.data_ptr() if n else None, y.data_ptr() if n else None, rows, n, k,
         w.stride(0) if n else 8, y.stride(0) if n else 8, int(b_mn_major), int(need_gathered), a.rank, a.world,
         a.ag_epoch & 0xFFFFFFFF, a.ctrs.data_ptr(), _WAIT_NS, native.status_word(x.device).data_ptr(),

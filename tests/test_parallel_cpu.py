@@ -37,3 +37,14 @@ def test_pp2(single):
     res = run_ranks(2, dict(BASE, pp=2))
     last = res[-1]
     assert _close(last[1], single[0], 2e-5), (last[1], single[0])
+
+
+def test_pp2_interleaved(single):
+    """Two stages x two virtual chunks (4 layers, one per virtual stage), 2 and 4 micro-batches."""
+    base4 = dict(BASE, layers=4)
+    ref = run_single(dict(base4))
+    res = run_ranks(2, dict(base4, pp=2, vpp=2))
+    assert _close(res[-1][1], ref[0], 2e-5), (res[-1][1], ref[0])
+    ref8 = run_single(dict(base4, gbs=4))
+    res8 = run_ranks(2, dict(base4, pp=2, vpp=2, gbs=4))
+    assert _close(res8[-1][1], ref8[0], 2e-5), (res8[-1][1], ref8[0])

@@ -25,7 +25,7 @@ class TinyExp(PretrainExp):
 
 
 def make_tiny_exp(dtype=torch.float32, hidden=256, heads=4, kv_heads=2, head_dim=64, ffn=512, vocab=1024, layers=2,
-                  seq=128, gbs=4, iters=10, lr=1e-3, wd=0.1, tp=1, pp=1, cp=1, sp=False, zero1=True, recompute=False,
+                  seq=128, gbs=4, iters=10, lr=1e-3, wd=0.1, tp=1, pp=1, cp=1, vpp=1, sp=False, zero1=True, recompute=False,
                   min_doc=16, max_doc=64, clip=1.0) -> TinyExp:
     e = TinyExp()
     m = e.model_cfg
@@ -43,6 +43,7 @@ def make_tiny_exp(dtype=torch.float32, hidden=256, heads=4, kv_heads=2, head_dim
     p = m.parallel_cfg
     p.tensor_model_parallel_size, p.pipeline_model_parallel_size, p.context_parallel_size = tp, pp, cp
     p.expert_tensor_parallel_size = 1
+    p.virtual_pipeline_model_parallel_size = vpp
     t = e.trainer_cfg
     t.global_batch_size, t.global_seq_length, t.train_iters, t.writer_backend = gbs, seq, iters, []
     s = e.scheduler_cfg
