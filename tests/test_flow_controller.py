@@ -137,3 +137,17 @@ def test_fully_async_backpressure_and_staleness():
         bound = (cfg.max_untrained_prompts + 1) // cfg.prompt_per_iter + cfg.max_staleness
         assert all(it - t.meta["version"] <= bound for t in trajs)
         ctrl.weight_dumped()
+
+
+def test_simulator_orders_strategies_by_overlap():
+    from steptronoss_b200.generators.flow_controller_simulator import simulate_flow_controller
+
+    costs = [3, 3, 3] * 4
+    on = simulate_flow_controller("on-policy", 3, 4, costs)
+    off = simulate_flow_controller("one-step-off", 3, 4, costs)
+    fa = simulate_flow_controller("fully-async", 3, 4, costs, max_untrained_prompts=6, max_staleness=2)
+    assert len(on.batches) == len(off.batches) == len(fa.batches) == 4
+    assert on.ticks > off.ticks >= fa.ticks           # more overlap, fewer ticks
+    assert max(b.staleness for b in on.batches) == 0 and max(b.staleness for b in off.batches) <= 1
+    assert all(b.staleness <= 2 + 2 for b in fa.batches)
+    assert "Train:" in on.render() and "Infer:" in on.render()
