@@ -62,3 +62,14 @@ def test_fused_gemm_collective_wait_runs_out_without_hanging():
     """A rank that stays away from one call: the peer's bounded wait reports code 5, the next call works."""
     res = _launch_fused(2, "timeout", 29702)
     assert res["timeout_code"] == 5
+
+
+def test_peer_memory_moe_dispatcher_matches_all_to_all():
+    """Dispatch / combine over peer memory against the NCCL all-to-all statement on 2 GPUs (forward, backward)."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29731", os.path.join(ROOT, "tests", "mp_peer_dispatch_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=400, env=env, cwd=ROOT)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    res = json.loads([l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
+    assert max(v for k, v in res.items() if not k.startswith("ms_")) < 2e-2
