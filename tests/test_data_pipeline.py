@@ -209,3 +209,31 @@ def test_sft_pack_contract_and_training_on_packed_chat_samples():
         tr.training_log()
         losses.append(tr.history[-1]["lm_loss"])
     assert losses[-1] < losses[0]
+
+
+def test_blockchain_write_copy_read_resume(tmp_path):
+    import shutil
+
+    from steptronoss_b200.data.blockchain import Chain
+
+    src = tmp_path / "a"
+    chain = Chain(str(src))
+    with chain.writer(block_size=4) as write:
+        for i in range(10):
+            write({"i": i})
+    with Chain(str(src)).writer(block_size=4) as write:       # append later
+        write({"i": 10})
+    dst = tmp_path / "b"
+    shutil.copytree(src, dst)
+    rd = Chain(str(dst), prefetch=1)
+    got = [rd.get()["i"] for _ in range(11)]
+    assert got == list(range(11))
+    assert rd.get()["i"] == 0                                   # wraps around like a training stream
+    rd2 = Chain(str(dst))
+    for _ in range(6):
+        rd2.get()
+    st = rd2.state_dict()
+    rd3 = Chain(str(dst))
+    rd3.load_state_dict(st)
+    assert rd3.get()["i"] == 6
+    rd.close()

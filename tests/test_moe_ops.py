@@ -54,3 +54,34 @@ def test_routed_ffn_matches_expert_loop_with_grads():
     assert torch.allclose(out, ref, atol=1e-4)
     for a, b in zip(grads, rgrads):
         assert torch.allclose(a, b, atol=1e-4)
+
+
+def test_permute_unpermute_round_trip_mask_and_index():
+    import torch
+
+    from steptronoss_b200.ops.permute import (moe_permute, moe_permute_with_probs, moe_sort_chunks_by_index,
+                                              moe_unpermute)
+
+    torch.manual_seed(0)
+    T, E, K, H = 6, 4, 2, 3
+    x = torch.randn(T, H)
+    ids = torch.stack([torch.randperm(E)[:K] for _ in range(T)])
+    probs_k = torch.rand(T, K)
+    mask = torch.zeros(T, E, dtype=torch.bool).scatter_(1, ids, True)
+    probs_e = torch.zeros(T, E).scatter_(1, ids, probs_k)
+    out, pp, rmap = moe_permute_with_probs(x, probs_e, mask)
+    assert out.shape == (T * K, H)
+    experts = rmap // T
+    assert torch.all(experts[1:] >= experts[:-1])                      # expert-major
+    assert torch.equal(out, x[rmap % T]) and torch.allclose(pp, probs_e.t().reshape(-1)[rmap])
+    back = moe_unpermute(out, rmap, merging_probs=probs_e)
+    want = x * probs_k.sum(1, keepdim=True)
+    assert torch.allclose(back, want, atol=1e-6)
+    out_i, rmap_i = moe_permute(x, ids, map_type="index")
+    assert torch.equal(out_i, x[rmap_i // K])
+    back_i = moe_unpermute(out_i, rmap_i, merging_probs=probs_k, map_type="index")
+    assert torch.allclose(back_i, want, atol=1e-6)
+    padded, rmap_p = moe_permute(x, mask, num_out_tokens=T * K + 3)
+    assert padded.shape[0] == T * K + 3 and int((rmap_p < 0).sum()) == 3 and float(padded[-3:].abs().sum()) == 0
+    chunks = moe_sort_chunks_by_index(torch.arange(6).unsqueeze(1), torch.tensor([1, 2, 3]), torch.tensor([2, 0, 1]))
+    assert chunks.flatten().tolist() == [3, 4, 5, 0, 1, 2]
