@@ -10,8 +10,10 @@ pair has a fixed landing row in the destination's receive buffer: source rank ``
 ``[s*T, (s+1)*T)`` and fills them from the front in token order.  Rows travel with
 ``csrc/peer_rows.cu::stb_peer_scatter_rows`` (plain peer stores); each row of the small metadata buffer
 starts with the call number, which is how the receiver tells fresh rows from stale ones, so no counts are
-exchanged either.  The receive buffers have the worst-case capacity ``world * T`` rows; unused rows carry
-expert id -1 and are skipped by the grouped GEMM's tile table.
+exchanged either.  The receive buffers have the worst-case capacity ``world * T`` rows; the fresh rows are then
+compacted (one device-to-host read of their number per dispatch, where the all-to-all statement needs the
+whole split-size matrix on the host before it can start), so that the expert GEMMs and what autograd keeps
+are sized by the rows that actually arrived.
 
 All ranks of the group must call with the same number of tokens ``T``.  CPU tensors (gloo tests) take the
 all-to-all statement.
@@ -117,11 +119,16 @@ class _Plan:
         self.pair_row = torch.where(hits, pos + rank * T, torch.full_like(pos, -1)).reshape(-1).contiguous()
         # where the answers of rank d for token t come back to: row d*T + pos[t, d] of the back buffer
         self.back_index = (pos.clamp_min(0).long() + torch.arange(world, device=dev).long() * T)   # [T, world]
-        # return moves from this rank: received row i (source i // T, j = i % T) -> row rank*T + j on the source
-        i = torch.arange(world * T, device=dev, dtype=torch.int32)
-        self.ret_rank = (i // T).contiguous()
-        self.ret_row_all = (rank * T + i % T).contiguous()
-        self.valid_rows = None  # set by dispatch: which received rows are fresh
+        # set by dispatch once the rows have arrived: which rows of the receive buffer are fresh (``sel``), and
+        # where the answer to compact row i goes: source sel // T, row rank*T + sel % T of its back buffer
+        self.sel = self.ret_src = self.ret_rank = self.ret_row = None
+
+    def set_received(self, valid: torch.Tensor) -> None:
+        sel = valid.nonzero(as_tuple=False).reshape(-1)          # host sync: number of received rows
+        self.sel = sel
+        self.ret_src = torch.arange(sel.numel(), device=sel.device, dtype=torch.int32)
+        self.ret_rank = (sel // self.T).to(torch.int32)
+        self.ret_row = (self.rank * self.T + sel % self.T).to(torch.int32)
 
 
 def _sum_over_ranks(back: torch.Tensor, plan: "_Plan") -> torch.Tensor:
@@ -147,11 +154,11 @@ class _DispatchFn(torch.autograd.Function):
         meta_src = torch.cat([tag, local, wbits], dim=2).reshape(T * W, 1 + 2 * K).contiguous()
         pair_idx = torch.arange(T * W, device=x.device, dtype=torch.int32)
         meta = _scatter(ar, _META, meta_src, pair_idx, plan.pair_rank, plan.pair_row, cap)
-        valid = meta[:, 0] == (ar.epoch[_META] & 0x7FFFFFFF)
-        plan.valid_rows = valid
-        ids_r = torch.where(valid.unsqueeze(1), meta[:, 1: 1 + K], torch.full_like(meta[:, 1: 1 + K], -1)).long()
-        w_r = torch.where(valid.unsqueeze(1), meta[:, 1 + K:].view(torch.float32), torch.zeros((), device=x.device))
-        xr = torch.where(valid.unsqueeze(1), recv_x, torch.zeros((), dtype=x.dtype, device=x.device))
+        plan.set_received(meta[:, 0] == (ar.epoch[_META] & 0x7FFFFFFF))
+        meta = meta.index_select(0, plan.sel)
+        ids_r = meta[:, 1: 1 + K].long()
+        w_r = meta[:, 1 + K:].contiguous().view(torch.float32)
+        xr = recv_x.index_select(0, plan.sel)
         ctx.disp, ctx.plan, ctx.w_dtype = disp, plan, weights.dtype
         ctx.mark_non_differentiable(ids_r)
         return xr, ids_r, w_r.to(weights.dtype)
@@ -160,13 +167,11 @@ class _DispatchFn(torch.autograd.Function):
     def backward(ctx, g_x, _g_ids, g_w):
         ar, plan = ctx.disp.arena, ctx.plan
         T, K, W = plan.T, plan.K, plan.world
-        ret_row = torch.where(plan.valid_rows, plan.ret_row_all, torch.full_like(plan.ret_row_all, -1))
-        rows = torch.arange(W * T, device=g_x.device, dtype=torch.int32)
-        back = _scatter(ar, _BACK, g_x.contiguous(), rows, plan.ret_rank, ret_row, W * T)
+        back = _scatter(ar, _BACK, g_x.contiguous(), plan.ret_src, plan.ret_rank, plan.ret_row, W * T)
         gx = _sum_over_ranks(back, plan).to(g_x.dtype)
         gw = None
         if g_w is not None:
-            back_w = _scatter(ar, _BACK_W, g_w.float().contiguous(), rows, plan.ret_rank, ret_row, W * T)
+            back_w = _scatter(ar, _BACK_W, g_w.float().contiguous(), plan.ret_src, plan.ret_rank, plan.ret_row, W * T)
             gw = _sum_over_ranks(back_w, plan).to(ctx.w_dtype)
         return gx, gw, None, None
 
@@ -176,9 +181,7 @@ class _CombineFn(torch.autograd.Function):
     def forward(ctx, y, disp):
         ar, plan = disp.arena, disp.plan
         T, W = plan.T, plan.world
-        ret_row = torch.where(plan.valid_rows, plan.ret_row_all, torch.full_like(plan.ret_row_all, -1))
-        rows = torch.arange(W * T, device=y.device, dtype=torch.int32)
-        back = _scatter(ar, _BACK, y.contiguous(), rows, plan.ret_rank, ret_row, W * T)
+        back = _scatter(ar, _BACK, y.contiguous(), plan.ret_src, plan.ret_rank, plan.ret_row, W * T)
         out = _sum_over_ranks(back, plan).to(y.dtype)
         ctx.disp, ctx.plan = disp, plan
         return out
@@ -187,8 +190,7 @@ class _CombineFn(torch.autograd.Function):
     def backward(ctx, g):
         ar, plan = ctx.disp.arena, ctx.plan
         recv = _scatter(ar, _X, g.contiguous(), plan.pair_src, plan.pair_rank, plan.pair_row, plan.world * plan.T)
-        gy = torch.where(plan.valid_rows.unsqueeze(1), recv, torch.zeros((), dtype=g.dtype, device=g.device))
-        return gy, None
+        return recv.index_select(0, plan.sel), None
 
 
 class PeerMemoryDispatcher:

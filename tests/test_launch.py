@@ -26,6 +26,7 @@ EXP_SRC = textwrap.dedent('''
     class Exp(BaseExp):
         resource_cfg = Rsc
         marker = "none"
+        log_dir = os.environ.get("OUT_DIR", os.path.dirname(os.path.abspath(__file__)))
 
         def entrypoint(self):
             self.update_from_args()

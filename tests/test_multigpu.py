@@ -73,3 +73,13 @@ def test_peer_memory_moe_dispatcher_matches_all_to_all():
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     res = json.loads([l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
     assert max(v for k, v in res.items() if not k.startswith("ms_")) < 2e-2
+
+
+def test_expert_parallel_moe_block_peer_vs_all_to_all():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29741", os.path.join(ROOT, "tests", "mp_moe_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=400, env=env, cwd=ROOT)
+    assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
+    res = json.loads([l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
+    assert max(res.values()) < 2e-2
