@@ -139,27 +139,24 @@ class MoEBlock(nn.Module):
     def forward_router(self, logits):
         cfg = self.cfg
         logits = logits.float()
-        prob = torch.sigmoid(logits) if cfg.enable_sigmoid_router else torch.softmax(logits, dim=1)
-        select = prob + self.router_balance_bias.float().unsqueeze(0) if self.router_balance_bias is not None else prob
-        order = torch.sort(select, dim=1, descending=True, stable=True).indices
-        ids = order[:, : self.top_k].contiguous()
+        eps = 1e-20 if self.router_balance_bias is not None else 0.0
+        route = (moe_ops.fused_router if moe_ops.router_native_ok(logits, self.top_k) and not cfg.force_balance
+                 else moe_ops.router_reference)
+        ids, weights, prob_sum, hist, stats = route(logits, self.router_balance_bias, self.top_k,
+                                                    bool(cfg.enable_sigmoid_router), bool(cfg.norm_expert_weight), eps)
         if cfg.force_balance:
             base = torch.arange(logits.shape[0] * self.top_k, device=logits.device)
             ids = (base % self.num_experts).view(-1, self.top_k)
-        top_prob = prob.gather(1, ids)
-        eps = 1e-20 if self.router_balance_bias is not None else 0.0
-        weights = top_prob
-        if cfg.enable_sigmoid_router:
-            weights = top_prob / (top_prob.sum(-1, keepdim=True) + eps)
-            prob = prob / (prob.sum(-1, keepdim=True) + eps)
-        elif cfg.norm_expert_weight:
-            weights = top_prob / (top_prob.sum(-1, keepdim=True) + eps)
-        hist = moe_ops.histogram(ids, self.num_experts)
+            prob = torch.sigmoid(logits) if cfg.enable_sigmoid_router else torch.softmax(logits, dim=1)
+            top_prob = prob.gather(1, ids)
+            weights = (top_prob / (top_prob.sum(-1, keepdim=True) + eps)
+                       if cfg.enable_sigmoid_router or cfg.norm_expert_weight else top_prob)
+            hist = moe_ops.histogram(ids, self.num_experts)
         ce = hist.clone().float()
         for fam in ("TP", "EP"):
             if PM.size_of(fam) > 1:
                 dist.all_reduce(ce, group=PM.group_of(fam))
-        me = prob.mean(0)
+        me = prob_sum / max(logits.shape[0], 1)
         if self.local_tokens_per_expert is not None and self.training:
             with torch.no_grad():
                 self.local_tokens_per_expert += hist
@@ -167,9 +164,9 @@ class MoEBlock(nn.Module):
         aux = (me * ce).sum() * self.num_experts
         sub = f"layer{self.moe_layer_id}"
         with torch.no_grad():
-            GlobalMetrics.router_logits_max.add(logits.abs().max(), subname=sub)
+            GlobalMetrics.router_logits_max.add(stats[0], subname=sub)
             GlobalMetrics.expert_coef.add(hist.max().float() / hist.sum().clamp_min(1).float(), subname=sub)
-            GlobalMetrics.moe_max.add(prob.max(1).values.mean(), subname=sub)
+            GlobalMetrics.moe_max.add(stats[1], subname=sub)
         return ids, weights, aux
 
     # ------------------------------------------------------------------ expert paths

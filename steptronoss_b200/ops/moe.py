@@ -59,12 +59,72 @@ def index_compute(ids: torch.Tensor, num_experts: int):
     return dest.view(T, K), offsets.to(torch.int32), counts.to(torch.int32)
 
 
+def _native_rows(t: torch.Tensor) -> bool:
+    return t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.shape[1] % 8 == 0 and native.available()
+
+
+class RoutePlan:
+    """Everything the routed FFN needs about one routing decision, computed by three small launches (chunk
+    histograms, scan, stable ranks) without a sort or a host synchronisation.
+
+    ``dest [T,k]`` int64 (-1 = ignored slot), ``offsets [E+1]`` int32 (128-aligned segment starts),
+    ``counts [E]`` int32, ``tile_group [rows/128]`` int32 (expert of every 128-row tile, -1 past the last
+    segment), ``slot_of_row [rows]`` int32 (flat slot index ``t*k + j`` held by every row, -1 = padding)."""
+
+    __slots__ = ("dest", "offsets", "counts", "tile_group", "slot_of_row", "rows", "num_experts")
+
+    def __init__(self, ids: torch.Tensor, num_experts: int, rows: int | None = None):
+        T, K = ids.shape
+        self.num_experts = num_experts
+        self.rows = padded_rows(T * K, num_experts) if rows is None else rows
+        dev = ids.device
+        if ids.is_cuda and num_experts <= 2048 and native.available():
+            lib = native.load()
+            ids64 = ids.to(torch.int64).contiguous()
+            n_tiles = self.rows // SEGMENT_ALIGNMENT
+            self.dest = torch.empty((T, K), dtype=torch.int64, device=dev)
+            meta = torch.empty(2 * num_experts + 1 + n_tiles + self.rows, dtype=torch.int32, device=dev)
+            self.offsets, self.counts, self.tile_group, self.slot_of_row = meta.split(
+                [num_experts + 1, num_experts, n_tiles, self.rows])
+            scratch = torch.empty(max(lib.stb_moe_index_chunks(T * K), 1) * num_experts, dtype=torch.int32, device=dev)
+            rc = lib.stb_moe_index(ids64.data_ptr(), T * K, num_experts, self.rows, self.dest.data_ptr(),
+                                   self.offsets.data_ptr(), self.counts.data_ptr(), self.tile_group.data_ptr(), n_tiles,
+                                   self.slot_of_row.data_ptr(), scratch.data_ptr(), native.stream())
+            native.check(rc, "moe_index")
+            count_launch(3)
+        else:
+            self.dest, self.offsets, self.counts = index_compute(ids, num_experts)
+            self.tile_group = tile_groups_from_offsets(self.offsets, self.rows) if ids.is_cuda else None
+            self.slot_of_row = slot_of_row_from_dest(self.dest, self.rows)
+
+
+def slot_of_row_from_dest(dest: torch.Tensor, rows: int) -> torch.Tensor:
+    """Inverse of ``dest``: flat slot index held by every expert-major row, -1 for padding rows."""
+    d = dest.reshape(-1)
+    inv = torch.full((rows + 1,), -1, dtype=torch.int32, device=dest.device)
+    inv.scatter_(0, torch.where(d >= 0, d, torch.full_like(d, rows)),
+                 torch.where(d >= 0, torch.arange(d.numel(), device=d.device, dtype=torch.int32),
+                             torch.full((d.numel(),), -1, dtype=torch.int32, device=d.device)))
+    return inv[:rows]
+
+
 class _ScatterFn(torch.autograd.Function):
     """rows of x copied to ``dest`` (one copy per slot); backward sums the k copies of each token."""
 
     @staticmethod
-    def forward(ctx, x, dest, rows):
+    def forward(ctx, x, dest, rows, plan=None):
         T, K = dest.shape
+        if plan is not None and _native_rows(x):
+            x = x.contiguous()
+            out = torch.empty((rows, x.shape[1]), dtype=x.dtype, device=x.device)
+            rc = native.load().stb_moe_scatter(x.data_ptr(), plan.slot_of_row.data_ptr(), plan.offsets.data_ptr(),
+                                               plan.num_experts, K, x.shape[1], rows, out.data_ptr(), native.stream())
+            native.check(rc, "moe_scatter")
+            count_launch()
+            ctx.save_for_backward(dest)
+            ctx.t, ctx.native = T, True
+            return out
+        ctx.native = False
         out = torch.zeros((rows, x.shape[1]), dtype=x.dtype, device=x.device)
         d = dest.reshape(-1)
         valid = d >= 0
@@ -78,20 +138,42 @@ class _ScatterFn(torch.autograd.Function):
     def backward(ctx, g):
         (dest,) = ctx.saved_tensors
         T, K = dest.shape
+        if ctx.native:
+            g = g.contiguous()
+            dx = torch.empty((T, g.shape[1]), dtype=g.dtype, device=g.device)
+            rc = native.load().stb_moe_gather(g.data_ptr(), dest.data_ptr(), None, T, K, g.shape[1], dx.data_ptr(),
+                                              native.stream())
+            native.check(rc, "moe_scatter_bwd")
+            count_launch()
+            return dx, None, None, None
         d = dest.reshape(-1)
         valid = (d >= 0).unsqueeze(-1)
         picked = g.index_select(0, d.clamp(min=0)).float() * valid
-        return picked.view(T, K, -1).sum(1).to(g.dtype), None, None
+        return picked.view(T, K, -1).sum(1).to(g.dtype), None, None, None
 
 
-def moe_scatter(x, dest, rows):
-    return _ScatterFn.apply(x, dest, rows)
+def moe_scatter(x, dest, rows, plan: RoutePlan | None = None):
+    """Copy the rows of ``x`` into expert-major order.  With a ``plan`` (bf16 on the GPU) one kernel writes
+    every used row exactly once, padding rows as zeros; rows past the last segment stay unwritten."""
+    return _ScatterFn.apply(x, dest, rows, plan)
 
 
 class _WeightedGatherFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, y, dest, weights):
+    def forward(ctx, y, dest, weights, plan=None):
         T, K = dest.shape
+        ctx.plan = None
+        if plan is not None and _native_rows(y) and K <= 16:
+            y = y.contiguous()
+            w32 = weights.to(torch.float32).contiguous()
+            out = torch.empty((T, y.shape[1]), dtype=y.dtype, device=y.device)
+            rc = native.load().stb_moe_gather(y.data_ptr(), dest.data_ptr(), w32.data_ptr(), T, K, y.shape[1],
+                                              out.data_ptr(), native.stream())
+            native.check(rc, "moe_gather")
+            count_launch()
+            ctx.save_for_backward(y, dest, w32)
+            ctx.plan, ctx.w_dtype = plan, weights.dtype
+            return out
         d = dest.reshape(-1)
         valid = (d >= 0).view(T, K, 1)
         picked = y.index_select(0, d.clamp(min=0)).view(T, K, -1).float() * valid
@@ -103,6 +185,17 @@ class _WeightedGatherFn(torch.autograd.Function):
     def backward(ctx, g):
         y, dest, weights = ctx.saved_tensors
         T, K = dest.shape
+        if ctx.plan is not None:
+            plan, g = ctx.plan, g.contiguous()
+            gy = torch.empty_like(y)
+            gw = torch.empty((T, K), dtype=torch.float32, device=y.device)
+            rc = native.load().stb_moe_gather_bwd(g.data_ptr(), y.data_ptr(), dest.data_ptr(), weights.data_ptr(),
+                                                  plan.slot_of_row.data_ptr(), plan.offsets.data_ptr(),
+                                                  plan.num_experts, T, K, y.shape[1], y.shape[0], gy.data_ptr(),
+                                                  gw.data_ptr(), native.stream())
+            native.check(rc, "moe_gather_bwd")
+            count_launch()
+            return gy, None, gw.to(ctx.w_dtype), None
         d = dest.reshape(-1)
         validf = (d >= 0)
         gy = torch.zeros_like(y)
@@ -110,20 +203,95 @@ class _WeightedGatherFn(torch.autograd.Function):
         gy.index_copy_(0, d[validf], contrib[validf].to(y.dtype))
         picked = y.index_select(0, d.clamp(min=0)).view(T, K, -1).float() * validf.view(T, K, 1)
         gw = (picked * g.float().unsqueeze(1)).sum(-1).to(weights.dtype)
-        return gy, None, gw
+        return gy, None, gw, None
 
 
-def moe_weighted_gather(y, dest, weights):
+def moe_weighted_gather(y, dest, weights, plan: RoutePlan | None = None):
     """``out[t] = sum_k weights[t,k] * y[dest[t,k]]`` (ignored slots contribute nothing)."""
-    return _WeightedGatherFn.apply(y, dest, weights)
+    return _WeightedGatherFn.apply(y, dest, weights, plan)
+
+
+class _RouterFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, bias, top_k, sigmoid, norm_topk, eps):
+        lib = native.load()
+        logits = logits.contiguous()
+        T, E = logits.shape
+        dev = logits.device
+        grid = lib.stb_router_grid(T)
+        ids = torch.empty((T, top_k), dtype=torch.int64, device=dev)
+        weights = torch.empty((T, top_k), dtype=torch.float32, device=dev)
+        part_prob = torch.empty((grid, E), dtype=torch.float32, device=dev)
+        part_hist = torch.empty((grid, E), dtype=torch.int32, device=dev)
+        part_stats = torch.empty((grid, 2), dtype=torch.float32, device=dev)
+        b = None if bias is None else bias.to(torch.float32).contiguous()
+        rc = lib.stb_router_fwd(logits.data_ptr(), native.ptr(b), T, E, top_k, int(sigmoid), int(norm_topk), float(eps),
+                                ids.data_ptr(), weights.data_ptr(), part_prob.data_ptr(), part_hist.data_ptr(),
+                                part_stats.data_ptr(), native.stream())
+        native.check(rc, "router_fwd")
+        count_launch()
+        ctx.save_for_backward(logits, ids)
+        ctx.cfg = (top_k, int(sigmoid), int(norm_topk), float(eps))
+        prob_sum, hist = part_prob.sum(0), part_hist.sum(0, dtype=torch.int32)
+        stats = torch.stack([part_stats[:, 0].max(), part_stats[:, 1].sum() / max(T, 1)])
+        ctx.mark_non_differentiable(ids, hist, stats)
+        return ids, weights, prob_sum, hist, stats
+
+    @staticmethod
+    def backward(ctx, _g_ids, g_w, g_ps, _g_hist, _g_stats):
+        logits, ids = ctx.saved_tensors
+        top_k, sigmoid, norm_topk, eps = ctx.cfg
+        T, E = logits.shape
+        g_w = torch.zeros((T, top_k), dtype=torch.float32, device=logits.device) if g_w is None else g_w.float().contiguous()
+        g_ps = None if g_ps is None else g_ps.float().contiguous()
+        dlogits = torch.empty_like(logits)
+        rc = native.load().stb_router_bwd(logits.data_ptr(), T, E, top_k, sigmoid, norm_topk, eps, ids.data_ptr(),
+                                          g_w.data_ptr(), native.ptr(g_ps), dlogits.data_ptr(), native.stream())
+        native.check(rc, "router_bwd")
+        count_launch()
+        return dlogits, None, None, None, None, None
+
+
+def router_native_ok(logits: torch.Tensor, top_k: int) -> bool:
+    return (logits.is_cuda and logits.dim() == 2 and logits.shape[1] <= 512 and top_k <= min(32, logits.shape[1])
+            and native.available())
+
+
+def fused_router(logits, bias, top_k: int, sigmoid: bool, norm_topk: bool, eps: float):
+    """Scores, top-k and the per-expert sums of the auxiliary loss in one kernel (one warp per token).
+
+    ``logits [T,E]`` fp32.  Returns ``ids [T,k]`` int64 (order and tie-break of a stable descending sort of
+    ``prob + bias``), ``weights [T,k]`` fp32, ``prob_sum [E]`` (sum over tokens of the probabilities, for sigmoid
+    scores of the probabilities renormalised per token), ``hist [E]`` int32 and ``stats = [max |logit|,
+    mean over tokens of the largest probability]``.  ``weights`` and ``prob_sum`` are differentiable."""
+    return _RouterFn.apply(logits.float(), bias, top_k, sigmoid, norm_topk, eps)
+
+
+def router_reference(logits, bias, top_k: int, sigmoid: bool, norm_topk: bool, eps: float):
+    """The same quantities with plain tensor ops (oracle and CPU path)."""
+    logits = logits.float()
+    prob = torch.sigmoid(logits) if sigmoid else torch.softmax(logits, dim=1)
+    select = prob + bias.float().unsqueeze(0) if bias is not None else prob
+    ids = torch.sort(select, dim=1, descending=True, stable=True).indices[:, :top_k].contiguous()
+    top = prob.gather(1, ids)
+    weights = top
+    if sigmoid:
+        weights = top / (top.sum(-1, keepdim=True) + eps)
+        prob = prob / (prob.sum(-1, keepdim=True) + eps)
+    elif norm_topk:
+        weights = top / (top.sum(-1, keepdim=True) + eps)
+    stats = torch.stack([logits.detach().abs().max(), (torch.sigmoid(logits) if sigmoid else torch.softmax(logits, 1))
+                         .detach().max(1).values.mean()])
+    return ids, weights, prob.sum(0), histogram(ids, logits.shape[1]), stats
 
 
 class _GroupedLinearFn(torch.autograd.Function):
     """Per-expert ``x_g @ w[g].T`` over expert-major rows; wgrad accumulates into ``w.main_grad``."""
 
     @staticmethod
-    def forward(ctx, x, w, offsets):
-        tile_group = tile_groups_from_offsets(offsets, x.shape[0]) if x.is_cuda else None
+    def forward(ctx, x, w, offsets, tile_group=None):
+        if tile_group is None and x.is_cuda:
+            tile_group = tile_groups_from_offsets(offsets, x.shape[0])
         y = grouped_gemm_rows(x, w, offsets, trans_b=True, tile_group=tile_group)
         ctx.save_for_backward(x, w, offsets, tile_group if tile_group is not None else offsets)
         ctx.w_ref = w
@@ -144,11 +312,11 @@ class _GroupedLinearFn(torch.autograd.Function):
                 ctx.w_ref.grad_added_to_main_grad = True
             else:
                 dw = grouped_gemm_reduce(gy, x, offsets, G)
-        return dx, dw, None
+        return dx, dw, None, None
 
 
-def grouped_linear(x, w, offsets):
-    return _GroupedLinearFn.apply(x, w, offsets)
+def grouped_linear(x, w, offsets, tile_group=None):
+    return _GroupedLinearFn.apply(x, w, offsets, tile_group)
 
 
 def routed_grouped_ffn(x, expert_ids, weights, w1, w2, limit: float = 0.0):
@@ -158,6 +326,13 @@ def routed_grouped_ffn(x, expert_ids, weights, w1, w2, limit: float = 0.0):
     ``w1 [E, 2F, H]`` (gate | up), ``w2 [E, H, F]``.  Returns ``[T,H]``."""
     E = w1.shape[0]
     T, K = expert_ids.shape
+    if _native_rows(x) and K <= 16:
+        plan = RoutePlan(expert_ids, E)
+        xe = moe_scatter(x, plan.dest, plan.rows, plan)
+        h = grouped_linear(xe, w1, plan.offsets, plan.tile_group)
+        a = swiglu(h, limit)
+        y = grouped_linear(a, w2, plan.offsets, plan.tile_group)
+        return moe_weighted_gather(y, plan.dest, weights, plan)
     dest, offsets, _ = index_compute(expert_ids, E)
     rows = padded_rows(T * K, E)
     xe = moe_scatter(x, dest, rows)

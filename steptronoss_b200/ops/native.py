@@ -71,6 +71,14 @@ _SIGNATURES = {
     "stb_add_bf16": [P, P, P, L, P],
     "stb_ce_stats": [P, P, P, P, L, I, L, L, P],
     "stb_ce_grad": [P, P, P, P, P, L, I, L, L, P],
+    "stb_moe_index_chunks": [I],
+    "stb_moe_index": [P, I, I, I, P, P, P, P, I, P, P, P],
+    "stb_moe_scatter": [P, P, P, I, I, I, I, P, P],
+    "stb_moe_gather": [P, P, P, I, I, I, P, P],
+    "stb_moe_gather_bwd": [P, P, P, P, P, P, I, I, I, I, I, P, P, P],
+    "stb_router_grid": [I],
+    "stb_router_fwd": [P, P, I, I, I, I, I, F, P, P, P, P, P, P],
+    "stb_router_bwd": [P, I, I, I, I, I, F, P, P, P, P, P],
     "stb_sqnorm_grid": [],
     "stb_sqnorm": [P, L, P, P, I, P],
     "stb_clip_coef": [P, F, P],

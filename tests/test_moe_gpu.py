@@ -71,3 +71,73 @@ def test_tiny_moe_decoder_trains_on_gpu():
     native.raise_if_kernel_error()
     # uniform random tokens: nothing to learn beyond ln(vocab) = 6.24; the step must stay finite and near it
     assert all(l == l and abs(l - 6.24) < 0.25 for l in losses), losses
+
+
+@pytest.mark.parametrize("T,K,E", [(1000, 2, 8), (8192, 8, 128), (333, 4, 288), (64, 1, 4)])
+def test_native_route_plan_matches_the_sort_based_index(T, K, E):
+    from steptronoss_b200.ops import moe
+
+    g = torch.Generator(device="cuda").manual_seed(T)
+    ids = torch.rand(T, E, device="cuda", generator=g).topk(K, dim=1).indices
+    ids = torch.where(torch.rand(T, K, device="cuda", generator=g) < 0.1, torch.full_like(ids, -1), ids)
+    plan = moe.RoutePlan(ids, E)
+    dest, offsets, counts = moe.index_compute(ids, E)
+    assert torch.equal(plan.dest, dest) and torch.equal(plan.offsets, offsets) and torch.equal(plan.counts, counts)
+    assert torch.equal(plan.tile_group, moe.tile_groups_from_offsets(offsets, plan.rows))
+    assert torch.equal(plan.slot_of_row, moe.slot_of_row_from_dest(dest, plan.rows))
+
+
+@pytest.mark.parametrize("T,K,E,H", [(777, 2, 8, 256), (2048, 8, 64, 512), (100, 3, 5, 136)])
+def test_native_scatter_and_gather_match_the_index_ops(T, K, E, H):
+    from steptronoss_b200.ops import moe
+
+    g = torch.Generator(device="cuda").manual_seed(K)
+    ids = torch.rand(T, E, device="cuda", generator=g).topk(K, dim=1).indices
+    ids = torch.where(torch.rand(T, K, device="cuda", generator=g) < 0.1, torch.full_like(ids, -1), ids)
+    plan = moe.RoutePlan(ids, E)
+    used = int(plan.offsets[-1])
+    x = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16).requires_grad_()
+    w = torch.rand(T, K, device="cuda", generator=g).requires_grad_()
+    gout = torch.randn(plan.rows, H, device="cuda", generator=g).to(torch.bfloat16)
+    gtok = torch.randn(T, H, device="cuda", generator=g).to(torch.bfloat16)
+
+    def run(p):
+        xe = moe.moe_scatter(x, plan.dest, plan.rows, p)
+        (dx,) = torch.autograd.grad(xe[:used], x, gout[:used])
+        y = (torch.randn(plan.rows, H, device="cuda", generator=torch.Generator(device="cuda").manual_seed(1))
+             .to(torch.bfloat16).requires_grad_())
+        o = moe.moe_weighted_gather(y, plan.dest, w, p)
+        gy, gw = torch.autograd.grad(o, [y, w], gtok)
+        return xe.detach()[:used].float(), dx.float(), o.detach().float(), gy[:used].float(), gw.float()
+
+    for name, a, b in zip(("scatter", "dx", "gather", "gy", "gw"), run(plan), run(None)):
+        err = float((a - b).abs().max() / b.abs().max().clamp_min(1e-6))
+        assert err < 1e-2, (name, err)
+
+
+@pytest.mark.parametrize("T,E,K,sigmoid,norm,use_bias", [(1000, 128, 8, False, True, False), (777, 288, 8, True, True, True),
+                                                         (64, 8, 2, False, False, False), (4096, 64, 6, True, False, True)])
+def test_fused_router_matches_tensor_ops(T, E, K, sigmoid, norm, use_bias):
+    from steptronoss_b200.ops import moe
+
+    g = torch.Generator(device="cuda").manual_seed(E)
+    logits = (torch.randn(T, E, device="cuda", generator=g) * 2).requires_grad_()
+    bias = torch.randn(E, device="cuda", generator=g) * 0.05 if use_bias else None
+    eps = 1e-20 if use_bias else 0.0
+    gw = torch.randn(T, K, device="cuda", generator=g)
+    gps = torch.randn(E, device="cuda", generator=g)
+    outs = []
+    for fn in (moe.fused_router, moe.router_reference):
+        ids, w, ps, hist, stats = fn(logits, bias, K, sigmoid, norm, eps)
+        (dl,) = torch.autograd.grad((w * gw).sum() + (ps * gps).sum(), logits)
+        outs.append((ids, w.detach(), ps.detach(), hist, stats, dl))
+    a, b = outs
+    same = (a[0] == b[0]).all(1)                      # rows whose selection is identical (near-ties may differ)
+    assert float(same.float().mean()) > 0.995
+    assert torch.allclose(a[1][same], b[1][same], atol=1e-5, rtol=1e-4)
+    assert torch.allclose(a[2], b[2], atol=1e-3, rtol=1e-4)
+    assert int((a[3] - b[3]).abs().sum()) <= 2 * int((~same).sum()) * K
+    assert torch.allclose(a[4], b[4], atol=1e-4, rtol=1e-4)
+    assert torch.allclose(a[5][same], b[5][same], atol=1e-5, rtol=1e-3)
+    assert int(a[3].sum()) == T * K and bool((a[0] >= 0).all()) and bool((a[0] < E).all())
+    assert bool((a[0].sort(1).values.diff(dim=1) > 0).all())   # k distinct experts per token

@@ -85,3 +85,30 @@ def test_permute_unpermute_round_trip_mask_and_index():
     assert padded.shape[0] == T * K + 3 and int((rmap_p < 0).sum()) == 3 and float(padded[-3:].abs().sum()) == 0
     chunks = moe_sort_chunks_by_index(torch.arange(6).unsqueeze(1), torch.tensor([1, 2, 3]), torch.tensor([2, 0, 1]))
     assert chunks.flatten().tolist() == [3, 4, 5, 0, 1, 2]
+
+
+def test_route_plan_matches_index_compute_and_inverts_dest():
+    torch.manual_seed(4)
+    T, K, E = 200, 3, 7
+    ids = torch.stack([torch.randperm(E)[:K] for _ in range(T)])
+    ids[::5, 2] = -1
+    plan = moe.RoutePlan(ids, E)
+    dest, offsets, counts = moe.index_compute(ids, E)
+    assert torch.equal(plan.dest, dest) and torch.equal(plan.offsets, offsets) and torch.equal(plan.counts, counts)
+    assert plan.rows == moe.padded_rows(T * K, E) and plan.slot_of_row.shape == (plan.rows,)
+    d = dest.reshape(-1)
+    valid = d >= 0
+    assert torch.equal(plan.slot_of_row[d[valid]].long(), torch.arange(T * K)[valid])
+    assert int((plan.slot_of_row >= 0).sum()) == int(valid.sum())
+
+
+def test_router_reference_gives_sorted_top_k_and_normalised_weights():
+    torch.manual_seed(2)
+    logits = torch.randn(50, 12)
+    bias = torch.randn(12) * 0.1
+    ids, w, ps, hist, stats = moe.router_reference(logits, bias, 3, True, True, 1e-20)
+    assert ids.shape == (50, 3) and torch.allclose(w.sum(1), torch.ones(50), atol=1e-5)
+    assert torch.allclose(ps.sum(), torch.tensor(50.0), atol=1e-3) and int(hist.sum()) == 150
+    sel = torch.sigmoid(logits) + bias
+    assert torch.equal(ids, sel.topk(3, dim=1).indices)
+    assert float(stats[0]) == float(logits.abs().max())
