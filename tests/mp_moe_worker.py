@@ -12,14 +12,16 @@ import torch.distributed as dist  # noqa: E402
 
 def main():
     from steptronoss_b200.config import Config
-    from steptronoss_b200.exp.base_exp import MegatronTPConfig
+    from steptronoss_b200.exp.base_exp import MegatronTPConfig, ParallelConfig
     from steptronoss_b200.models.common.moe_block import MoEBlock, MoEConfig
     from steptronoss_b200.ops import native
     from steptronoss_b200.parallel.state import PM
 
     PM.initialize()
-    PM.new_parallel("EP", [list(range(PM.world_size))])
-    dev = torch.device("cuda", torch.cuda.current_device())
+    mesh = ParallelConfig()
+    mesh.expert_model_parallel_size, mesh.expert_tensor_parallel_size = PM.world_size, 1
+    PM.set_mesh(mesh)
+    dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
 
     class Holder(Config):
         tp_cfg = MegatronTPConfig
@@ -62,8 +64,9 @@ def main():
             err = float((a - b).abs().max() / b.abs().max().clamp_min(1e-6))
             res[f"{name}_{it}"] = err
             assert err < 2e-2, (name, it, err)
-    torch.cuda.synchronize()
-    native.raise_if_kernel_error()
+    if dev.type == "cuda":
+        torch.cuda.synchronize()
+        native.raise_if_kernel_error()
     dist.barrier()
     if PM.world_rank == 0:
         print("RESULT " + json.dumps(res), flush=True)

@@ -52,8 +52,8 @@ def test_tiny_moe_decoder_trains_on_gpu():
     m = exp.model_cfg
     m.params_dtype = torch.bfloat16
     for a in (m.attn_cfg, m.swa_cfg):
-        a.head_dim, a.num_attention_heads, a.num_attention_groups = 128, 2, 1
-    m.swa_cfg.num_attention_heads, m.swa_cfg.sliding_window_size = 4, 64
+        a.head_dim, a.num_attention_heads, a.num_attention_groups = 128, 8, 2   # 8 gate columns keep wqkv 16-byte aligned
+    m.swa_cfg.num_attention_heads, m.swa_cfg.sliding_window_size = 16, 64
     m.ffn_cfg.ffn_hidden_size = 256
     m.moe_cfg.moe_hidden_size, m.moe_cfg.share_expert_dim = 128, 128
     exp.trainer_cfg.global_seq_length, exp.trainer_cfg.train_iters = 256, 6

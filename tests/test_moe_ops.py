@@ -112,3 +112,21 @@ def test_router_reference_gives_sorted_top_k_and_normalised_weights():
     sel = torch.sigmoid(logits) + bias
     assert torch.equal(ids, sel.topk(3, dim=1).indices)
     assert float(stats[0]) == float(logits.abs().max())
+
+
+def test_expert_parallel_moe_block_on_two_gloo_ranks():
+    """The worker of the 2-GPU test also runs on CPU ranks: there both dispatcher names resolve to the
+    all-to-all path, which checks the expert-parallel block end to end (router, dispatch, experts, combine)."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29743", os.path.join(root, "tests", "mp_moe_worker.py")]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=root)
+    assert out.returncode == 0, out.stderr[-3000:]
+    res = json.loads([l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
+    assert len(res) == 12 and max(res.values()) < 1e-6

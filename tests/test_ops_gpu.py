@@ -187,3 +187,14 @@ def test_tiny_model_trains_on_gpu_and_matches_cpu_reference_loss():
     losses = [h["lm_loss"] for h in tr.history]
     assert all(math.isfinite(l) for l in losses)
     assert abs(losses[0] - math.log(2048)) < 0.5
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 4, 256), (130, 772, 64)])
+def test_gemm_with_unaligned_row_pitch_uses_the_library(M, N, K):
+    from steptronoss_b200.ops.gemm import gemm
+
+    a = torch.randn(M, K, device="cuda").to(torch.bfloat16)
+    b = torch.randn(N, K, device="cuda").to(torch.bfloat16)
+    out = gemm(a, b)
+    ref = a.float() @ b.float().t()
+    assert out.shape == (M, N) and float((out.float() - ref).abs().max() / ref.abs().max()) < 2e-2
