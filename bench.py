@@ -36,14 +36,25 @@ def parse():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="qwen3_8b", choices=["qwen3_8b", "qwen3_30b_a3b"],
+                    help="qwen3_8b: the headline dense config; qwen3_30b_a3b: the MoE config (EP = N, attention DP = N, "
+                         "sequences of 4096, 32 per GPU; its static state needs N >= 4)")
+    ap.add_argument("--dispatcher", default="peer", choices=["peer", "alltoall"], help="MoE token dispatcher")
     ap.add_argument("--parallelism", default=None, help="e.g. tp4dp2, dp8, tp2; default tp=min(N,4) x dp")
-    ap.add_argument("--seqs-per-gpu", type=int, default=8, help="sequences per GPU per step (global batch = this x N)")
-    ap.add_argument("--seq-len", type=int, default=8192)
+    ap.add_argument("--seqs-per-gpu", type=int, default=None,
+                    help="sequences per GPU per step (global batch = this x N); default 8 (dense) / 32 (MoE)")
+    ap.add_argument("--seq-len", type=int, default=None, help="default 8192 (dense) / 4096 (MoE)")
     ap.add_argument("--recompute", default="auto", help="auto | none | full | comma list of block parts")
     ap.add_argument("--recompute-layers", type=int, default=None,
                     help="recompute only the first N layers (default: 4 of 36 on one GPU, all otherwise)")
     ap.add_argument("--debug-layers", type=int, default=None, help="DEBUG ONLY: fewer layers (result marked invalid)")
-    return ap.parse_args()
+    a = ap.parse_args()
+    moe = a.model == "qwen3_30b_a3b"
+    if a.seqs_per_gpu is None:
+        a.seqs_per_gpu = 32 if moe else 8
+    if a.seq_len is None:
+        a.seq_len = 4096 if moe else 8192
+    return a
 
 
 class ClockSampler:
@@ -110,10 +121,11 @@ def parse_parallelism(text: str) -> dict:
     return out
 
 
-def model_flops_per_token(layers, hidden, heads, kv_heads, head_dim, ffn, vocab, avg_ctx):
+def model_flops_per_token(layers, hidden, heads, kv_heads, head_dim, ffn, vocab, avg_ctx, router_experts=0):
+    """``ffn`` is the SwiGLU width a token passes through (top-k x expert width for a routed FFN)."""
     qkv = hidden * (heads + 2 * kv_heads) * head_dim
     o = heads * head_dim * hidden
-    mlp = 3 * hidden * ffn
+    mlp = 3 * hidden * ffn + hidden * router_experts
     dense = layers * (qkv + o + mlp) + vocab * hidden
     attn = layers * 2 * heads * head_dim * avg_ctx  # QK^T and PV, causal average context
     return 6 * dense + 6 * attn
@@ -124,7 +136,11 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
 
-    from playground.pretrain.qwen3.qwen3_8b import Exp
+    moe = args.model == "qwen3_30b_a3b"
+    if moe:
+        from playground.pretrain.qwen3.qwen3_30a3b import Exp
+    else:
+        from playground.pretrain.qwen3.qwen3_8b import Exp
     from steptronoss_b200.ops import launch_count
     from steptronoss_b200.ops import native
     from steptronoss_b200.parallel.state import PM
@@ -133,10 +149,15 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run for N>1")
-    par_text = args.parallelism or default_parallelism(world)
+    par_text = args.parallelism or (f"ep{world}dp{world}" if moe else default_parallelism(world))
     par = parse_parallelism(par_text)
     exp = Exp()
     pc = exp.model_cfg.parallel_cfg
+    if moe:
+        pc.expert_model_parallel_size, pc.expert_tensor_parallel_size = par["ep"], 1
+        exp.model_cfg.moe_cfg.dispatcher = args.dispatcher
+        if args.debug_layers:
+            exp.model_cfg.moe_cfg.moe_layer_list = list(range(args.debug_layers))
     pc.tensor_model_parallel_size = par["tp"]
     pc.pipeline_model_parallel_size = par["pp"]
     pc.context_parallel_size = par["cp"]
@@ -148,12 +169,14 @@ def run_ours(args):
     tc.writer_backend = []
     tc.log_interval = 10**9
     exp.data_cfg.max_doc_len = args.seq_len
+    if moe:
+        exp.data_cfg.min_doc_len = args.seq_len  # one document per sequence
     if args.debug_layers:
         exp.model_cfg.num_layers = args.debug_layers
     rec = args.recompute
     if rec == "auto":
         # one GPU holds 18 bytes/parameter of static state (147 GB): recompute whole blocks
-        rec = "full" if par["tp"] * par["pp"] == 1 else "none"
+        rec = "full" if par["tp"] * par["pp"] == 1 and not moe else "none"
     exp.model_cfg.recompute = True if rec == "full" else ([] if rec == "none" else rec.split(","))
     rec_layers = args.recompute_layers
     if rec_layers is None and rec == "full" and args.recompute == "auto" and not args.debug_layers:
@@ -254,7 +277,11 @@ def run_ours(args):
     e2e = tokens_per_step * args.steps / (ms_b / 1e3)
     mc = exp.model_cfg
     avg_ctx = (args.seq_len ** 2 / 3.0) / ((256 + args.seq_len) / 2.0) / 2.0 if args.seq_len > 256 else args.seq_len / 2
-    fpt = model_flops_per_token(mc.num_layers, 4096, 32, 8, 128, 12288, 151936, avg_ctx)
+    if moe:
+        avg_ctx = args.seq_len / 2.0  # one document per sequence
+        fpt = model_flops_per_token(mc.num_layers, 2048, 32, 4, 128, 8 * 768, 151936, avg_ctx, router_experts=128)
+    else:
+        fpt = model_flops_per_token(mc.num_layers, 4096, 32, 8, 128, 12288, 151936, avg_ctx)
     peaks = {}
     try:
         peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -262,12 +289,15 @@ def run_ours(args):
         pass
     peak = float(peaks.get("bf16_tflops_sustained", 1375.7)) * 1e12
     out = {
-        "metric": "tokens/s/box (Qwen3-8B dense training, all GPUs of the node)",
+        "metric": ("tokens/s/box (Qwen3-30B-A3B-shape MoE pretraining, all GPUs of the node)" if moe
+                   else "tokens/s/box (Qwen3-8B dense training, all GPUs of the node)"),
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_a / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic packed documents (lengths U[256,8192], uniform token ids), random N(0,0.02) init",
+        "dtype": "bf16",
+        "data": ("synthetic sequences of one document each (uniform token ids), random N(0,0.02) init" if moe else
+                 "synthetic packed documents (lengths U[256,8192], uniform token ids), random N(0,0.02) init"),
         "mfu_of_measured_sustained_bf16": value * fpt / (peak * world),
-        "config": {"model": "Qwen3-8B", "layers": mc.num_layers, "global_batch": tc.global_batch_size,
+        "config": {"model": "Qwen3-30B-A3B-shape MoE" if moe else "Qwen3-8B", "layers": mc.num_layers, "global_batch": tc.global_batch_size,
                    "seq_len": tc.global_seq_length, "micro_batch": 1, "parallelism": par_text,
                    "optimizer": "Adam fp32 master+state, ZeRO-1", "recompute": rec,
                    "l2": "inputs larger than L2 (each step streams > 100 GB)"},

@@ -122,3 +122,248 @@ extern "C" int stb_peer_wait_flags(const void* flag_page_self, int flag_index, i
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }
+
+// ------------------------------------------------------------------------------------------------------------
+// Expert-parallel dispatch / return / sum with fixed landing rows: token t of source rank s lands in row
+// s*T + t of every destination that hosts one of its experts, so no positions, counts or prefix sums are
+// exchanged, and the receiver tells fresh rows from stale ones by the call number in front of each metadata row.
+//
+//   stb_ep_dispatch : per token, the set of destination ranks follows from its k expert ids; the row of x goes to
+//                     each of them (x may be null), together with a metadata row [tag | k local ids (-1 = foreign)
+//                     | k weights as bits (0 = foreign)] (weights may be null: rows only, the backward of combine).
+//   stb_ep_return   : the way back: receive-buffer row r = s*T + t that is marked valid goes to row rank*T + t of
+//                     source s, optionally with a second, small fp32 row (the gradient of the routing weights).
+//   stb_ep_sum      : at the source: out[t] = sum over the destinations of token t, in rank order, of the rows that
+//                     came back (fp32 accumulation), and gw[t, k] = the entry that the host of expert ids[t, k] sent.
+namespace stb {
+
+struct EpShape {
+  int T, K, world, rank, per_rank;
+};
+
+__device__ __forceinline__ void publish_when_grid_done(uint32_t* done_counter, const PeerBases& flags, int flag_index,
+                                                       int world, int rank, uint32_t epoch) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t prev = atomicAdd(done_counter, 1u);
+    if (prev == gridDim.x - 1) {
+      *done_counter = 0;
+      __threadfence_system();
+      for (int r = 0; r < world; ++r)
+        st_release_sys_u32(static_cast<uint32_t*>(flags.p[r]) + flag_index * kPeerMaxRanks + rank, epoch);
+    }
+  }
+}
+
+// destination rank of the lane's slot (lane < K), -1 for ignored slots and idle lanes
+__device__ __forceinline__ int slot_rank(const long long* ids, int t, int lane, const EpShape& s, long long* e_out) {
+  long long e = -1;
+  if (lane < s.K) e = ids[static_cast<long long>(t) * s.K + lane];
+  *e_out = e;
+  if (e < 0) return -1;
+  const int d = static_cast<int>(e / s.per_rank);
+  return d < s.world ? d : -1;
+}
+
+__global__ void ep_dispatch_kernel(const uint4* __restrict__ x, long long x_pitch16, int n16,
+                                   const long long* __restrict__ ids, const float* __restrict__ weights,
+                                   const __grid_constant__ PeerBases xb, long long meta_offset, int tag,
+                                   const __grid_constant__ PeerBases flags, int flag_index, uint32_t epoch,
+                                   uint32_t* done_counter, const EpShape s) {
+  const int wpb = blockDim.x >> 5, lane = threadIdx.x & 31;
+  const int meta_words = 1 + 2 * s.K;
+  for (int t = blockIdx.x * wpb + (threadIdx.x >> 5); t < s.T; t += gridDim.x * wpb) {
+    long long e;
+    const int d_lane = slot_rank(ids, t, lane, s, &e);
+    const float w_lane = (weights && lane < s.K) ? weights[static_cast<long long>(t) * s.K + lane] : 0.f;
+    unsigned hit = 0;
+    for (int d = 0; d < s.world; ++d)
+      if (__any_sync(0xffffffffu, d_lane == d)) hit |= 1u << d;
+    const long long row = static_cast<long long>(s.rank) * s.T + t;
+    if (weights) {
+      // lane 0: tag, lanes 1..K: local ids, lanes K+1..2K: weight bits
+      const int k = lane == 0 ? 0 : (lane <= s.K ? lane - 1 : lane - 1 - s.K);
+      const long long e_k = __shfl_sync(0xffffffffu, e, k);
+      const int d_k = __shfl_sync(0xffffffffu, d_lane, k);
+      const float w_k = __shfl_sync(0xffffffffu, w_lane, k);
+      for (int d = 0; d < s.world; ++d) {
+        if (!(hit >> d & 1u) || lane >= meta_words) continue;
+        int v;
+        if (lane == 0) v = tag;
+        else if (lane <= s.K) v = d_k == d ? static_cast<int>(e_k - static_cast<long long>(d) * s.per_rank) : -1;
+        else v = d_k == d ? __float_as_int(w_k) : 0;
+        int* m = reinterpret_cast<int*>(static_cast<uint8_t*>(xb.p[d]) + meta_offset) + row * meta_words;
+        m[lane] = v;
+      }
+    }
+    if (x) {
+      const uint4* src = x + static_cast<long long>(t) * x_pitch16;
+      for (int base = 0; base < n16; base += 256) {
+        uint4 q[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int j = base + i * 32 + lane;
+          if (j < n16) q[i] = src[j];
+        }
+        for (int d = 0; d < s.world; ++d) {
+          if (!(hit >> d & 1u)) continue;
+          uint4* dst = static_cast<uint4*>(xb.p[d]) + row * n16;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int j = base + i * 32 + lane;
+            if (j < n16) dst[j] = q[i];
+          }
+        }
+      }
+    }
+  }
+  publish_when_grid_done(done_counter, flags, flag_index, s.world, s.rank, epoch);
+}
+
+__global__ void ep_return_kernel(const uint4* __restrict__ rows, int n16, const float* __restrict__ wrows,
+                                 const uint8_t* __restrict__ valid, const __grid_constant__ PeerBases bb,
+                                 long long w_offset, const __grid_constant__ PeerBases flags, int flag_index,
+                                 uint32_t epoch, uint32_t* done_counter, const EpShape s) {
+  const int wpb = blockDim.x >> 5, lane = threadIdx.x & 31;
+  const int total = s.world * s.T;
+  for (int r = blockIdx.x * wpb + (threadIdx.x >> 5); r < total; r += gridDim.x * wpb) {
+    if (!valid[r]) continue;
+    const int src_rank = r / s.T, t = r - src_rank * s.T;
+    const long long row = static_cast<long long>(s.rank) * s.T + t;
+    if (rows) {
+      const uint4* a = rows + static_cast<long long>(r) * n16;
+      uint4* dst = static_cast<uint4*>(bb.p[src_rank]) + row * n16;
+      for (int base = 0; base < n16; base += 256) {
+        uint4 q[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int j = base + i * 32 + lane;
+          if (j < n16) q[i] = a[j];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int j = base + i * 32 + lane;
+          if (j < n16) dst[j] = q[i];
+        }
+      }
+    }
+    if (wrows && lane < s.K) {
+      float* dw = reinterpret_cast<float*>(static_cast<uint8_t*>(bb.p[src_rank]) + w_offset) + row * s.K;
+      dw[lane] = wrows[static_cast<long long>(r) * s.K + lane];
+    }
+  }
+  publish_when_grid_done(done_counter, flags, flag_index, s.world, s.rank, epoch);
+}
+
+__global__ void ep_sum_kernel(const uint4* __restrict__ back, int n16, const float* __restrict__ back_w,
+                              const long long* __restrict__ ids, uint4* __restrict__ out, float* __restrict__ gw,
+                              const EpShape s) {
+  const int wpb = blockDim.x >> 5, lane = threadIdx.x & 31;
+  for (int t = blockIdx.x * wpb + (threadIdx.x >> 5); t < s.T; t += gridDim.x * wpb) {
+    long long e;
+    const int d_lane = slot_rank(ids, t, lane, s, &e);
+    unsigned hit = 0;
+    for (int d = 0; d < s.world; ++d)
+      if (__any_sync(0xffffffffu, d_lane == d)) hit |= 1u << d;
+    if (gw && lane < s.K)
+      gw[static_cast<long long>(t) * s.K + lane] =
+          d_lane >= 0 ? back_w[(static_cast<long long>(d_lane) * s.T + t) * s.K + lane] : 0.f;
+    if (!out) continue;
+    for (int j = lane; j < n16; j += 32) {
+      uint4 q[kPeerMaxRanks];
+#pragma unroll
+      for (int d = 0; d < kPeerMaxRanks; ++d)
+        if (hit >> d & 1u) q[d] = back[(static_cast<long long>(d) * s.T + t) * n16 + j];
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+      for (int d = 0; d < kPeerMaxRanks; ++d) {
+        if (!(hit >> d & 1u)) continue;
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&q[d]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(p[i]);
+          acc[2 * i] += f.x;
+          acc[2 * i + 1] += f.y;
+        }
+      }
+      uint4 o;
+      __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) po[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+      out[static_cast<long long>(t) * n16 + j] = o;
+    }
+  }
+}
+
+static int ep_grid(long long warps, int threads) {
+  const int wpb = threads / 32;
+  long long g = (warps + wpb - 1) / wpb;
+  const long long cap = static_cast<long long>(sm_count()) * 8;
+  if (g > cap) g = cap;
+  return g < 1 ? 1 : static_cast<int>(g);
+}
+
+static bool ep_shape_ok(const EpShape& s) {
+  return s.world >= 1 && s.world <= kPeerMaxRanks && s.K >= 1 && s.K <= 15 && s.per_rank >= 1 && s.T >= 0;
+}
+
+}  // namespace stb
+
+// x: [T, row_bytes] rows with pitch x_pitch_bytes (null: metadata only); weights: fp32 [T, K] (null: rows only).
+// bases[r]: this call's slot of rank r's receive buffer: world*T rows of row_bytes, then at meta_offset world*T
+// metadata rows of (1 + 2K) int32.  row_bytes, pitches and offsets are multiples of 16.
+extern "C" int stb_ep_dispatch(const void* x, long long x_pitch_bytes, int row_bytes, const void* ids,
+                               const void* weights, void* const* bases, long long meta_offset, int tag,
+                               void* const* flag_pages, int flag_index, unsigned epoch, void* done_counter, int T,
+                               int K, int world, int rank, int per_rank, cudaStream_t stream) {
+  EpShape s{T, K, world, rank, per_rank};
+  if (!ep_shape_ok(s) || (row_bytes & 15) || (x_pitch_bytes & 15) || (meta_offset & 15)) return -kErrBadArgument;
+  PeerBases b{}, f{};
+  for (int i = 0; i < world; ++i) {
+    b.p[i] = bases[i];
+    f.p[i] = flag_pages[i];
+  }
+  ep_dispatch_kernel<<<ep_grid(T, 256), 256, 0, stream>>>(
+      static_cast<const uint4*>(x), x_pitch_bytes / 16, row_bytes / 16, static_cast<const long long*>(ids),
+      static_cast<const float*>(weights), b, meta_offset, tag, f, flag_index, epoch,
+      static_cast<uint32_t*>(done_counter), s);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+// rows: [world*T, row_bytes] contiguous (null: none); wrows: fp32 [world*T, K] (null: none); valid: uint8 [world*T].
+// bases[r]: this call's slot of rank r's return buffer: world*T rows of row_bytes, then at w_offset world*T rows of
+// K fp32.
+extern "C" int stb_ep_return(const void* rows, int row_bytes, const void* wrows, const void* valid,
+                             void* const* bases, long long w_offset, void* const* flag_pages, int flag_index,
+                             unsigned epoch, void* done_counter, int T, int K, int world, int rank,
+                             cudaStream_t stream) {
+  EpShape s{T, K, world, rank, 1};
+  if (!ep_shape_ok(s) || (row_bytes & 15) || (w_offset & 15)) return -kErrBadArgument;
+  PeerBases b{}, f{};
+  for (int i = 0; i < world; ++i) {
+    b.p[i] = bases[i];
+    f.p[i] = flag_pages[i];
+  }
+  ep_return_kernel<<<ep_grid(static_cast<long long>(world) * T, 256), 256, 0, stream>>>(
+      static_cast<const uint4*>(rows), row_bytes / 16, static_cast<const float*>(wrows),
+      static_cast<const uint8_t*>(valid), b, w_offset, f, flag_index, epoch, static_cast<uint32_t*>(done_counter), s);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+// back: bf16 rows [world*T, H] of this rank's return buffer (null: none); back_w: fp32 [world*T, K] (null: none).
+extern "C" int stb_ep_sum(const void* back, int H, const void* back_w, const void* ids, void* out, void* gw, int T,
+                          int K, int world, int rank, int per_rank, cudaStream_t stream) {
+  EpShape s{T, K, world, rank, per_rank};
+  if (!ep_shape_ok(s) || (H & 7)) return -kErrBadArgument;
+  ep_sum_kernel<<<ep_grid(T, 256), 256, 0, stream>>>(static_cast<const uint4*>(back), H / 8,
+                                                     static_cast<const float*>(back_w),
+                                                     static_cast<const long long*>(ids), static_cast<uint4*>(out),
+                                                     static_cast<float*>(gw), s);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}

@@ -111,8 +111,8 @@ class GroupedExperts(nn.Module):
         lim = cfg.get_experts_swiglu_limit(layer_id)
         self.limit = float(lim) if lim else 0.0
 
-    def forward(self, x, local_ids, weights):
-        return moe_ops.routed_grouped_ffn(x, local_ids, weights, self.w1, self.w2, self.limit)
+    def forward(self, x, local_ids, weights, max_slots=None):
+        return moe_ops.routed_grouped_ffn(x, local_ids, weights, self.w1, self.w2, self.limit, max_slots)
 
 
 class MoEBlock(nn.Module):
@@ -194,7 +194,7 @@ class MoEBlock(nn.Module):
         with torch.no_grad():
             GlobalMetrics.peak_to_avg_ratio.add((local_ids >= 0).sum().float() / max(n_tok * self.top_k, 1),
                                                 subname=f"layer{self.moe_layer_id}")
-        y = self.experts(xd, local_ids, wd)
+        y = self.experts(xd, local_ids, wd, getattr(self.dispatcher, "received_slots", None))
         return self.dispatcher.combine(y)
 
     def forward(self, x, recompute: bool = False):

@@ -319,15 +319,17 @@ def grouped_linear(x, w, offsets, tile_group=None):
     return _GroupedLinearFn.apply(x, w, offsets, tile_group)
 
 
-def routed_grouped_ffn(x, expert_ids, weights, w1, w2, limit: float = 0.0):
+def routed_grouped_ffn(x, expert_ids, weights, w1, w2, limit: float = 0.0, max_slots: int | None = None):
     """Top-k routed SwiGLU experts on one rank.
 
     ``x [T,H]``, ``expert_ids [T,k]`` (local expert index or -1), ``weights [T,k]``,
-    ``w1 [E, 2F, H]`` (gate | up), ``w2 [E, H, F]``.  Returns ``[T,H]``."""
+    ``w1 [E, 2F, H]`` (gate | up), ``w2 [E, H, F]``.  Returns ``[T,H]``.  ``max_slots``: an upper bound of the
+    slots with an id >= 0 when the caller knows one (rows of a sparse receive buffer); it sizes the expert-major
+    buffers, which otherwise take the worst case ``T*k``."""
     E = w1.shape[0]
     T, K = expert_ids.shape
     if _native_rows(x) and K <= 16:
-        plan = RoutePlan(expert_ids, E)
+        plan = RoutePlan(expert_ids, E, None if max_slots is None else padded_rows(min(max_slots, T * K), E))
         xe = moe_scatter(x, plan.dest, plan.rows, plan)
         h = grouped_linear(xe, w1, plan.offsets, plan.tile_group)
         a = swiglu(h, limit)

@@ -1,22 +1,24 @@
-"""Expert-parallel dispatch / combine over peer memory (NVLink), without host synchronisation.
+"""Expert-parallel dispatch / combine over peer memory (NVLink).
 
 Semantics are those of :class:`~steptronoss_b200.parallel.ep_dispatcher.AllToAllDispatcher` (and of the
 reference ``TokenDispatcher``, ``steptronoss/model/ep_dispatcher/token_dispatcher.py:14-118``): a token goes
 once to every EP rank that hosts one of its top-k experts, with its expert ids rewritten to local indices
-(-1 = foreign) and its weights (0 = foreign); the way back carries one partial row per (token, rank).
+(-1 = foreign) and its weights (0 = foreign); the way back carries one partial row per (token, rank), which
+the source adds up in rank order.
 
-Instead of variable-size all-to-alls whose split sizes go through the host, every (token, destination)
-pair has a fixed landing row in the destination's receive buffer: source rank ``s`` owns rows
-``[s*T, (s+1)*T)`` and fills them from the front in token order.  Rows travel with
-``csrc/peer_rows.cu::stb_peer_scatter_rows`` (plain peer stores); each row of the small metadata buffer
-starts with the call number, which is how the receiver tells fresh rows from stale ones, so no counts are
-exchanged either.  The receive buffers have the worst-case capacity ``world * T`` rows; the fresh rows are then
-compacted (one device-to-host read of their number per dispatch, where the all-to-all statement needs the
-whole split-size matrix on the host before it can start), so that the expert GEMMs and what autograd keeps
-are sized by the rows that actually arrived.
+Instead of variable-size all-to-alls whose split sizes go through the host, every (token, destination) pair
+has a fixed landing row: token ``t`` of source rank ``s`` lands in row ``s*T + t`` of the destination's receive
+buffer, and its answer in row ``d*T + t`` of the source's return buffer.  Nothing is counted, prefix-summed or
+exchanged before the payload moves: ``stb_ep_dispatch`` (``csrc/peer_rows.cu``) derives a token's destinations
+from its k expert ids and stores the row and a small metadata row ``[call number | local ids | weights]`` into
+the peers' memory; the receiver tells fresh rows from stale ones by the call number.  The receive buffer is
+handed to the expert FFN as it is (``[world*T, H]`` with ids of -1 in the rows that did not arrive): the
+expert-major scatter reads the arrived rows straight out of it, so there is no compaction copy.  One number
+goes to the host per dispatch, the count of arrived (token, expert) slots, which sizes the expert-major buffers
+that autograd keeps.
 
-All ranks of the group must call with the same number of tokens ``T``.  CPU tensors (gloo tests) take the
-all-to-all statement.
+All ranks of the group must call with the same number of tokens ``T``.  CPU tensors (gloo tests), dtypes other
+than bf16 and more than 15 experts per token take the all-to-all statement.
 """
 from __future__ import annotations
 
@@ -35,25 +37,34 @@ from .symm import _WAIT_NS, SymmetricBuffer
 P, I, L, U, ULL = c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_uint, ctypes.c_ulonglong
 native.register_signature("stb_peer_scatter_rows", [P, L, I, P, P, P, I, P, L, P, I, I, I, U, P, P])
 native.register_signature("stb_peer_wait_flags", [P, I, I, U, ULL, P, P])
+native.register_signature("stb_ep_dispatch", [P, L, I, P, P, P, L, I, P, I, U, P, I, I, I, I, I, P])
+native.register_signature("stb_ep_return", [P, I, P, P, P, L, P, I, U, P, I, I, I, I, P])
+native.register_signature("stb_ep_sum", [P, I, P, P, P, P, I, I, I, I, I, P])
 
 # buffer kinds: each has its own two slots, flag rows and call counter
-_X, _META, _BACK, _BACK_W = 0, 1, 2, 3
-_KINDS = 4
+_FWD, _BACK = 0, 1
+_KINDS = 2
+
+
+def _align(n: int, a: int = 256) -> int:
+    return (n + a - 1) // a * a
 
 
 class _PeerArena:
-    """Flag page and the double-slotted receive buffers of one EP group."""
+    """Flag page and the double-slotted receive / return buffers of one EP group."""
 
     def __init__(self, group_name: str):
         self.group = PM.group_of(group_name)
         self.rank, self.world = PM.rank_in(group_name), PM.size_of(group_name)
         self.lib = native.load()
         self.flags = SymmetricBuffer(2 * _KINDS * 8 * 4, self.group, self.lib)
+        self.flags.own_tensor().zero_()
         self.bufs: list = [None] * _KINDS
         self.slot_bytes = [0] * _KINDS
         self.epoch = [0] * _KINDS
         self.done = torch.zeros(4, dtype=torch.int32, device="cuda")
         self._flag_arr = self.flags.ptr_array()
+        torch.cuda.synchronize()
         dist.barrier(group=self.group)
 
     def slot(self, kind: int, need: int):
@@ -65,12 +76,20 @@ class _PeerArena:
             if self.bufs[kind] is not None:
                 self.bufs[kind].release()
             self.bufs[kind] = SymmetricBuffer(2 * size, self.group, self.lib)
+            self.bufs[kind].own_tensor().zero_()       # call numbers start at 1: a zeroed row is never fresh
             self.slot_bytes[kind] = size
+            torch.cuda.synchronize()
             dist.barrier(group=self.group)
         self.epoch[kind] += 1
         e = self.epoch[kind]
         off = (e & 1) * self.slot_bytes[kind]
         return e, 2 * kind + (e & 1), self.bufs[kind].ptr_array(off), self.bufs[kind].own_tensor()[off: off + need]
+
+    def wait(self, flag_row: int, epoch: int, device) -> None:
+        rc = self.lib.stb_peer_wait_flags(self.flags.own, flag_row, self.world, epoch & 0xFFFFFFFF, _WAIT_NS,
+                                          native.status_word(device).data_ptr(), native.stream())
+        native.check(rc, "peer wait")
+        count_launch()
 
 
 _ARENAS: dict = {}
@@ -82,115 +101,102 @@ def _arena(group_name: str) -> _PeerArena:
     return _ARENAS[group_name]
 
 
-def _scatter(ar: _PeerArena, kind: int, src: torch.Tensor, src_row, dst_rank, dst_row, rows_cap: int) -> torch.Tensor:
-    """Send rows of the 2-D tensor ``src`` to their landing rows on the peers, wait for everybody's rows and
-    return this rank's receive buffer ``[rows_cap, src.shape[1]]`` (a view of peer-mapped memory: copy what
-    must outlive the second-next call of the same kind)."""
-    row_bytes = src.shape[1] * src.element_size()
-    e, flag_row, ptrs, own = ar.slot(kind, rows_cap * row_bytes)
-    st = native.stream()
-    rc = ar.lib.stb_peer_scatter_rows(src.data_ptr(), src.stride(0) * src.element_size(), row_bytes,
-                                      src_row.data_ptr(), dst_rank.data_ptr(), dst_row.data_ptr(), src_row.numel(),
-                                      ptrs, row_bytes, ar._flag_arr, flag_row, ar.world, ar.rank, e & 0xFFFFFFFF,
-                                      ar.done.data_ptr() + 4 * kind, st)
-    native.check(rc, "peer scatter")
-    rc = ar.lib.stb_peer_wait_flags(ar.flags.own, flag_row, ar.world, e & 0xFFFFFFFF, _WAIT_NS,
-                                    native.status_word(src.device).data_ptr(), st)
-    native.check(rc, "peer wait")
-    count_launch(2)
-    return own.view(src.dtype).view(rows_cap, src.shape[1])
-
-
 class _Plan:
-    """Where the rows of one dispatch go: computed once per call from the routing, reused by all four moves."""
+    """What the four moves of one dispatch share."""
 
     def __init__(self, expert_ids: torch.Tensor, world: int, rank: int, per_rank: int):
-        T, K = expert_ids.shape
-        dev = expert_ids.device
-        dest = (expert_ids // per_rank).clamp(0, world - 1)
-        hits = torch.zeros((T, world), dtype=torch.bool, device=dev)
-        hits.scatter_(1, dest, expert_ids >= 0)
-        pos = hits.to(torch.int32).cumsum(0, dtype=torch.int32) - 1             # row inside this rank's block
-        self.T, self.K, self.world, self.rank = T, K, world, rank
-        self.hits = hits
-        # forward moves: pair (t, d) -> row rank*T + pos[t, d] on rank d
-        self.pair_src = torch.arange(T, device=dev, dtype=torch.int32).repeat_interleave(world)
-        self.pair_rank = torch.arange(world, device=dev, dtype=torch.int32).repeat(T)
-        self.pair_row = torch.where(hits, pos + rank * T, torch.full_like(pos, -1)).reshape(-1).contiguous()
-        # where the answers of rank d for token t come back to: row d*T + pos[t, d] of the back buffer
-        self.back_index = (pos.clamp_min(0).long() + torch.arange(world, device=dev).long() * T)   # [T, world]
-        # set by dispatch once the rows have arrived: which rows of the receive buffer are fresh (``sel``), and
-        # where the answer to compact row i goes: source sel // T, row rank*T + sel % T of its back buffer
-        self.sel = self.ret_src = self.ret_rank = self.ret_row = None
-
-    def set_received(self, valid: torch.Tensor) -> None:
-        sel = valid.nonzero(as_tuple=False).reshape(-1)          # host sync: number of received rows
-        self.sel = sel
-        self.ret_src = torch.arange(sel.numel(), device=sel.device, dtype=torch.int32)
-        self.ret_rank = (sel // self.T).to(torch.int32)
-        self.ret_row = (self.rank * self.T + sel % self.T).to(torch.int32)
+        self.T, self.K = expert_ids.shape
+        self.world, self.rank, self.per_rank = world, rank, per_rank
+        self.ids = expert_ids.to(torch.int64).contiguous()
+        self.valid = None      # uint8 [world*T]: receive-buffer rows that arrived in this dispatch
+        self.slots = None      # number of (token, local expert) slots that arrived (host integer)
 
 
-def _sum_over_ranks(back: torch.Tensor, plan: "_Plan") -> torch.Tensor:
-    """``[world*T, C]`` answers -> ``[T, C]``: per token the fp32 sum over the ranks it was sent to (rows of
-    pairs that were never sent may hold anything, so they are selected out, not multiplied by zero)."""
-    picked = back.index_select(0, plan.back_index.reshape(-1)).view(plan.T, plan.world, -1).float()
-    return torch.where(plan.hits.unsqueeze(2), picked, torch.zeros((), device=back.device)).sum(1)
+def _send_rows(ar: _PeerArena, plan: _Plan, x: torch.Tensor, weights):
+    """Rows of ``x [T, H]`` (and metadata when ``weights`` is given) to the hosts of every token's experts; returns
+    this rank's receive buffer ``[world*T, H]`` and metadata ``[world*T, 1+2K]`` (views of peer-mapped memory:
+    consume them before the second-next call) and the call number that marks fresh metadata rows."""
+    T, K, W = plan.T, plan.K, plan.world
+    x = x.contiguous()
+    row_bytes = x.shape[1] * x.element_size()
+    meta_off = _align(W * T * row_bytes)
+    meta_bytes = W * T * (1 + 2 * K) * 4 if weights is not None else 0
+    e, flag_row, ptrs, own = ar.slot(_FWD, meta_off + meta_bytes)
+    tag = e & 0x7FFFFFFF
+    w32 = None if weights is None else weights.to(torch.float32).contiguous()
+    rc = ar.lib.stb_ep_dispatch(x.data_ptr(), x.stride(0) * x.element_size(), row_bytes, plan.ids.data_ptr(),
+                                native.ptr(w32), ptrs, meta_off, tag, ar._flag_arr, flag_row, e & 0xFFFFFFFF,
+                                ar.done.data_ptr() + 4 * _FWD, T, K, W, plan.rank, plan.per_rank, native.stream())
+    native.check(rc, "ep dispatch")
+    count_launch()
+    ar.wait(flag_row, e, x.device)
+    recv = own[: W * T * row_bytes].view(x.dtype).view(W * T, x.shape[1])
+    meta = own[meta_off: meta_off + meta_bytes].view(torch.int32).view(W * T, 1 + 2 * K) if weights is not None else None
+    return recv, meta, tag
+
+
+def _return_rows(ar: _PeerArena, plan: _Plan, rows: torch.Tensor, wrows, want_sum_dtype):
+    """The way back: arrived rows of ``rows [world*T, H]`` (and ``wrows [world*T, K]`` fp32) go to their sources;
+    returns per token the sum over its destinations ``[T, H]`` and the routing-weight gradients ``[T, K]``."""
+    T, K, W = plan.T, plan.K, plan.world
+    rows = rows.contiguous()
+    H = rows.shape[1]
+    row_bytes = H * rows.element_size()
+    w_off = _align(W * T * row_bytes)
+    w_bytes = W * T * K * 4 if wrows is not None else 0
+    e, flag_row, ptrs, own = ar.slot(_BACK, w_off + w_bytes)
+    w32 = None if wrows is None else wrows.to(torch.float32).contiguous()
+    rc = ar.lib.stb_ep_return(rows.data_ptr(), row_bytes, native.ptr(w32), plan.valid.data_ptr(), ptrs, w_off,
+                              ar._flag_arr, flag_row, e & 0xFFFFFFFF, ar.done.data_ptr() + 4 * _BACK, T, K, W,
+                              plan.rank, native.stream())
+    native.check(rc, "ep return")
+    count_launch()
+    ar.wait(flag_row, e, rows.device)
+    out = torch.empty((T, H), dtype=want_sum_dtype, device=rows.device)
+    gw = torch.empty((T, K), dtype=torch.float32, device=rows.device) if wrows is not None else None
+    back_w = own[w_off: w_off + w_bytes] if wrows is not None else None
+    rc = ar.lib.stb_ep_sum(own.data_ptr(), H, native.ptr(back_w), plan.ids.data_ptr(), out.data_ptr(), native.ptr(gw),
+                           T, K, W, plan.rank, plan.per_rank, native.stream())
+    native.check(rc, "ep sum")
+    count_launch()
+    return out, gw
 
 
 class _DispatchFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weights, expert_ids, disp):
+    def forward(ctx, x, weights, disp):
         ar, plan = disp.arena, disp.plan
-        T, K, W = plan.T, plan.K, plan.world
-        cap = W * T
-        recv_x = _scatter(ar, _X, x.contiguous(), plan.pair_src, plan.pair_rank, plan.pair_row, cap)
-        # metadata row per pair: [call number | local ids (k) | weights as bits (k)]
-        local = expert_ids.unsqueeze(1) - (torch.arange(W, device=x.device) * disp.per_rank).view(1, W, 1)   # [T,W,K]
-        foreign = (local < 0) | (local >= disp.per_rank) | (expert_ids.unsqueeze(1) < 0)
-        local = torch.where(foreign, torch.full_like(local, -1), local).to(torch.int32)
-        wbits = torch.where(foreign, torch.zeros((), device=x.device), weights.float().unsqueeze(1)).view(torch.int32)
-        tag = torch.full((T, W, 1), (ar.epoch[_META] + 1) & 0x7FFFFFFF, dtype=torch.int32, device=x.device)
-        meta_src = torch.cat([tag, local, wbits], dim=2).reshape(T * W, 1 + 2 * K).contiguous()
-        pair_idx = torch.arange(T * W, device=x.device, dtype=torch.int32)
-        meta = _scatter(ar, _META, meta_src, pair_idx, plan.pair_rank, plan.pair_row, cap)
-        plan.set_received(meta[:, 0] == (ar.epoch[_META] & 0x7FFFFFFF))
-        meta = meta.index_select(0, plan.sel)
-        ids_r = meta[:, 1: 1 + K].long()
-        w_r = meta[:, 1 + K:].contiguous().view(torch.float32)
-        xr = recv_x.index_select(0, plan.sel)
-        ctx.disp, ctx.plan, ctx.w_dtype = disp, plan, weights.dtype
+        K = plan.K
+        recv, meta, tag = _send_rows(ar, plan, x, weights)
+        fresh = meta[:, 0] == tag
+        plan.valid = fresh.to(torch.uint8)
+        ids_r = torch.where(fresh.unsqueeze(1), meta[:, 1: 1 + K], torch.full((), -1, dtype=torch.int32, device=x.device)).long()
+        w_r = torch.where(fresh.unsqueeze(1), meta[:, 1 + K:].contiguous().view(torch.float32), torch.zeros((), device=x.device))
+        plan.slots = int((ids_r >= 0).sum())           # the one host read of a dispatch
+        ctx.disp, ctx.plan, ctx.w_dtype, ctx.x_dtype = disp, plan, weights.dtype, x.dtype
         ctx.mark_non_differentiable(ids_r)
-        return xr, ids_r, w_r.to(weights.dtype)
+        return recv, ids_r, w_r.to(weights.dtype)
 
     @staticmethod
     def backward(ctx, g_x, _g_ids, g_w):
-        ar, plan = ctx.disp.arena, ctx.plan
-        T, K, W = plan.T, plan.K, plan.world
-        back = _scatter(ar, _BACK, g_x.contiguous(), plan.ret_src, plan.ret_rank, plan.ret_row, W * T)
-        gx = _sum_over_ranks(back, plan).to(g_x.dtype)
-        gw = None
-        if g_w is not None:
-            back_w = _scatter(ar, _BACK_W, g_w.float().contiguous(), plan.ret_src, plan.ret_rank, plan.ret_row, W * T)
-            gw = _sum_over_ranks(back_w, plan).to(ctx.w_dtype)
-        return gx, gw, None, None
+        plan = ctx.plan
+        if g_w is None:
+            g_w = torch.zeros((plan.world * plan.T, plan.K), dtype=torch.float32, device=g_x.device)
+        gx, gw = _return_rows(ctx.disp.arena, plan, g_x, g_w, ctx.x_dtype)
+        return gx, gw.to(ctx.w_dtype), None
 
 
 class _CombineFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, y, disp):
-        ar, plan = disp.arena, disp.plan
-        T, W = plan.T, plan.world
-        back = _scatter(ar, _BACK, y.contiguous(), plan.ret_src, plan.ret_rank, plan.ret_row, W * T)
-        out = _sum_over_ranks(back, plan).to(y.dtype)
-        ctx.disp, ctx.plan = disp, plan
+        ctx.disp, ctx.plan = disp, disp.plan
+        out, _ = _return_rows(disp.arena, disp.plan, y, None, y.dtype)
         return out
 
     @staticmethod
     def backward(ctx, g):
-        ar, plan = ctx.disp.arena, ctx.plan
-        recv = _scatter(ar, _X, g.contiguous(), plan.pair_src, plan.pair_rank, plan.pair_row, plan.world * plan.T)
-        return recv.index_select(0, plan.sel), None
+        recv, _meta, _tag = _send_rows(ctx.disp.arena, ctx.plan, g, None)
+        return recv, None   # rows that did not arrive hold stale data: their ids are -1, nothing reads them
 
 
 class PeerMemoryDispatcher:
@@ -202,19 +208,25 @@ class PeerMemoryDispatcher:
         self.arena: _PeerArena | None = None
         self.plan: _Plan | None = None
         self._used_fallback = False
+        self.received_slots: int | None = None
+        """(token, local expert) slots that arrived in the last dispatch; None on the all-to-all path."""
 
-    def _peer_ok(self, x: torch.Tensor) -> bool:
-        return (x.is_cuda and dist.is_initialized() and 2 <= self.world <= 8
+    def _peer_ok(self, x: torch.Tensor, expert_ids: torch.Tensor) -> bool:
+        return (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and expert_ids.shape[1] <= 15
+                and dist.is_initialized() and 2 <= self.world <= 8
                 and dist.get_backend(PM.group_of(self.group_name)) == "nccl")
 
     def dispatch(self, x, expert_ids, weights):
-        self._used_fallback = not self._peer_ok(x)
+        self._used_fallback = not self._peer_ok(x, expert_ids)
         if self._used_fallback:
+            self.received_slots = None
             return self._fallback.dispatch(x, expert_ids, weights)
         if self.arena is None:
             self.arena = _arena(self.group_name)
         self.plan = _Plan(expert_ids, self.world, self.rank, self.per_rank)
-        return _DispatchFn.apply(x, weights, expert_ids, self)
+        out = _DispatchFn.apply(x, weights, self)
+        self.received_slots = self.plan.slots
+        return out
 
     def combine(self, y):
         if self._used_fallback:
