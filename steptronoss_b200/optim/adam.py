@@ -33,6 +33,9 @@ class FlatAdamShard:
         self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
         self.segments = segments
+        self.peer = None
+        """``(PeerZeroGroup, pointer array)`` when the bucket's parameter buffers are peer-mapped: the update then
+        stores the new bf16 values into every rank's buffer (``stb_adam_push``)."""
         self._chunks = None
         self._chunk_wd = None
 
@@ -62,6 +65,14 @@ class FlatAdamShard:
             if n == 0:
                 return
             lib = native.load()
+            if self.peer is not None and p_lp.dtype == torch.bfloat16:
+                pz, ptrs = self.peer
+                native.check(lib.stb_adam_push(self.master.data_ptr(), g.data_ptr(), self.exp_avg.data_ptr(),
+                                               self.exp_avg_sq.data_ptr(), ptrs, pz.world, table.data_ptr(), n,
+                                               native.ptr(scalars), lr, beta1, beta2, eps, bc1, bc2, grad_scale,
+                                               0 if self.mode == "adam" else 1, native.stream()), "adam_push")
+                count_launch()
+                return
             lp_ptr = p_lp.data_ptr() if p_lp.dtype == torch.bfloat16 else None
             native.check(lib.stb_adam(self.master.data_ptr(), g.data_ptr(), self.exp_avg.data_ptr(),
                                       self.exp_avg_sq.data_ptr(), lp_ptr, table.data_ptr(), n,

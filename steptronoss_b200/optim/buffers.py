@@ -84,9 +84,11 @@ def bucket_key_of(param, shard_over_dp: bool = True) -> BucketKey:
     return BucketKey(param.dtype, "EDP" if expert else "DP", bool(getattr(param, "is_muon_param", False)), rep)
 
 
-def build_buffers(named_params: list, shard: bool = True) -> dict:
+def build_buffers(named_params: list, shard: bool = True, allocator=None) -> dict:
     """Create the buckets, re-seat every parameter into its bucket's ``param_buf`` and attach
-    ``param.main_grad``.  ``shard=False`` gives one shard per bucket (no ZeRO)."""
+    ``param.main_grad``.  ``shard=False`` gives one shard per bucket (no ZeRO).  ``allocator(key, numel, dtype,
+    kind)`` may supply the zeroed flat buffers (``kind`` is ``"param"`` or ``"grad"``) or return ``None`` to leave a
+    bucket to ``torch.zeros``; it is called for every bucket in the same order on every rank."""
     groups: dict[BucketKey, list] = {}
     for name, p in named_params:
         if not p.requires_grad:
@@ -108,8 +110,13 @@ def build_buffers(named_params: list, shard: bool = True) -> dict:
             s.offset += s.owner * shard_size
         dev = items[0][1].device
         b = Bucket(key, slots, shard_size, world, rank)
-        b.param_buf = torch.zeros(world * shard_size, dtype=key.dtype, device=dev)
-        b.grad_buf = torch.zeros(world * shard_size, dtype=torch.float32, device=dev)
+        n = world * shard_size
+        b.param_buf = allocator(key, n, key.dtype, "param") if allocator is not None else None
+        b.grad_buf = allocator(key, n, torch.float32, "grad") if allocator is not None else None
+        if b.param_buf is None:
+            b.param_buf = torch.zeros(n, dtype=key.dtype, device=dev)
+        if b.grad_buf is None:
+            b.grad_buf = torch.zeros(n, dtype=torch.float32, device=dev)
         for s in slots:
             view = b.param_buf[s.offset : s.offset + s.numel].view(s.param.shape)
             view.copy_(s.param.data)

@@ -86,7 +86,12 @@ class BaseGradientManager:
         if hasattr(self.opt_cfg, "mark_muon_params"):
             for m in self.models:
                 self.opt_cfg.mark_muon_params(m)
-        self.buckets: dict = build_buffers(self.named_params, shard=self.shard_optimizer)
+        self._peer: dict = {}          # reduce group name -> PeerZeroGroup (ZeRO-1 over peer memory)
+        self._peer_sq_store: dict = {}
+        self.buckets: dict = build_buffers(self.named_params, shard=self.shard_optimizer,
+                                           allocator=self._buffer_allocator())
+        for pz in self._peer.values():
+            pz.finish_allocation()
         self.step_count = 0
         self._hooks = []
         self._install_hooks()
@@ -99,9 +104,38 @@ class BaseGradientManager:
         self._gather_event = None
         self._side_stream = torch.cuda.Stream() if dev.type == "cuda" else None
         self._sq_partial = None
+        self._peer_sq = None
         self.optimizer = self  # `.optimizer.param_groups` is what schedulers and checkpoints use
 
     # ------------------------------------------------------------------ setup
+    def _buffer_allocator(self):
+        return None
+
+    def _peer_of(self, key):
+        pz = self._peer.get(key.reduce_group)
+        return pz if pz is not None and key in pz.grad_mem else None
+
+    def _drop_peer_path(self) -> None:
+        """Move the flat buffers back to ordinary allocations (collective); the NCCL statement takes over."""
+        if not self._peer:
+            return
+        self.wait_param_gather()
+        for key, b in self.buckets.items():
+            if self._peer_of(key) is None:
+                continue
+            if b.grad_buf is not None:
+                g = b.grad_buf.clone()
+                b.grad_buf = g
+                for s in b.slots:
+                    s.param.main_grad = g[s.offset: s.offset + s.numel].view(s.param.shape)
+            if b.param_buf.is_cuda:
+                self._reseat(b, b.param_buf.clone())
+        for shard in self.shards.values():
+            shard.peer = None
+        for pz in self._peer.values():
+            pz.release()
+        self._peer = {}
+
     def _install_hooks(self) -> None:
         def hook(p):
             if p.grad is not None:
@@ -140,6 +174,8 @@ class BaseGradientManager:
 
     # ------------------------------------------------------------------ step pieces
     def zero_grad(self, set_to_none: bool = True) -> None:
+        for pz in self._peer.values():
+            pz.wait_params()   # the peers may still be reading last step's gradients
         for b in self.buckets.values():
             b.grad_buf.zero_()
         for _, p in self.named_params:
@@ -148,6 +184,8 @@ class BaseGradientManager:
 
     def wait_param_gather(self) -> None:
         """Join the side-stream parameter all-gather before parameters are read again."""
+        for pz in self._peer.values():
+            pz.wait_params()
         if self._gather_event is not None:
             torch.cuda.current_stream().wait_event(self._gather_event)
             self._gather_event = None
@@ -221,8 +259,23 @@ class BaseGradientManager:
             self.scalars[3] = 1.0 if ok else 0.0
             return
         total = self.scalars[0:1]
-        for i, r in enumerate(regions):
-            self._sqnorm_into(r, total, accumulate=i > 0)
+        if getattr(self, "_peer_sq", None) is not None:
+            # the peer reduce kernels left every shard's squared norm behind: add them up instead of re-reading
+            keys = [key for key in self.buckets if not (key.tp_replicated and tp_rank != 0)]
+            first = True
+            for key in keys:
+                if key in self._peer_sq:
+                    if first:
+                        total.copy_(self._peer_sq[key])
+                    else:
+                        total.add_(self._peer_sq[key])
+                else:
+                    self._sqnorm_into(self._norm_region(self.buckets[key]), total, accumulate=not first)
+                first = False
+            regions = keys
+        else:
+            for i, r in enumerate(regions):
+                self._sqnorm_into(r, total, accumulate=i > 0)
         if not regions:
             total.zero_()
         total.mul_(grad_scale * grad_scale)
@@ -312,6 +365,7 @@ class BaseGradientManager:
 
     def destroy_buffer(self) -> None:
         """Free the fp32 gradient buffers (their contents are lost); ``build_buffer`` brings them back."""
+        self._drop_peer_path()
         for b in self.buckets.values():
             b.grad_buf = None
             for s in b.slots:
@@ -328,6 +382,7 @@ class BaseGradientManager:
 
     def offload_params(self, non_blocking: bool = True) -> None:
         """Move the flat parameter buffers to pinned host memory; parameters stay views of them."""
+        self._drop_peer_path()
         self.wait_param_gather()
         for b in self.buckets.values():
             if b.param_buf.device.type == "cpu":
@@ -390,19 +445,54 @@ class Zero1GradientManager(BaseGradientManager):
 
     shard_optimizer = True
 
+    def _buffer_allocator(self):
+        """Buckets whose reduce group sits inside one node get their flat buffers in peer-mapped memory."""
+        from . import peer_zero
+
+        dev = self.named_params[0][1].device if self.named_params else torch.device("cpu")
+        if dev.type != "cuda":
+            return None
+        supported: dict = {}
+
+        def allocator(key, numel, dtype, kind):
+            if key.is_muon or key.dtype != torch.bfloat16:
+                return None
+            g = key.reduce_group
+            if g not in supported:
+                supported[g] = peer_zero.group_supported(g)
+                if supported[g]:
+                    self._peer[g] = peer_zero.PeerZeroGroup(g)
+            return self._peer[g].allocate(key, numel, dtype, kind) if supported[g] else None
+
+        return allocator
+
+    def _build_optimizers(self) -> None:
+        super()._build_optimizers()
+        for key, shard in self.shards.items():
+            pz = self._peer_of(key)
+            if pz is not None:
+                shard.peer = (pz, pz.param_ptrs(key, self.buckets[key]))
+
     def _reduce(self) -> float:
-        for key, b in self.buckets.items():
-            if b.world > 1:
-                lo, hi = b.own_range()
-                comm.reduce_scatter_tensor(b.grad_buf[lo:hi], b.grad_buf, group=PM.group_of(key.reduce_group))
-        scale = 1.0 / PM.size_of("DP")
         dp, edp = PM.size_of("DP"), PM.size_of("EDP") if PM.has("EDP") else PM.size_of("DP")
-        if edp != dp:
-            for key, b in self.buckets.items():
-                if key.reduce_group == "EDP":
-                    lo, hi = b.own_range()
-                    b.grad_buf[lo:hi].mul_(dp / edp)
-        return scale
+        for pz in self._peer.values():
+            pz.begin_step()
+        self._peer_sq = {} if self._peer else None
+        for key, b in self.buckets.items():
+            fix = dp / edp if key.reduce_group == "EDP" and edp != dp else 1.0
+            pz = self._peer_of(key)
+            if pz is not None:
+                if key not in self._peer_sq_store:
+                    self._peer_sq_store[key] = torch.zeros(1, dtype=torch.float32, device=self.device)
+                self._peer_sq[key] = self._peer_sq_store[key]
+                pz.reduce(key, b, fix, self._peer_sq[key], accumulate=False)
+                continue
+            lo, hi = b.own_range()
+            if b.world > 1:
+                comm.reduce_scatter_tensor(b.grad_buf[lo:hi], b.grad_buf, group=PM.group_of(key.reduce_group))
+            if fix != 1.0:
+                b.grad_buf[lo:hi].mul_(fix)
+        return 1.0 / dp
 
     def _norm_region(self, b):
         lo, hi = b.own_range()
@@ -412,7 +502,9 @@ class Zero1GradientManager(BaseGradientManager):
         return None  # world
 
     def _refresh_params(self) -> None:
-        multi = [(k, b) for k, b in self.buckets.items() if b.world > 1]
+        for pz in self._peer.values():
+            pz.end_step()      # the Adam kernels already stored the new shards into every peer's buffer
+        multi = [(k, b) for k, b in self.buckets.items() if b.world > 1 and self._peer_of(k) is None]
         if not multi:
             return
         if self._side_stream is not None and self.cfg.overlap_param_gather:

@@ -30,7 +30,9 @@ def main():
     torch.cuda.synchronize()
     native.raise_if_kernel_error()
     if PM.world_rank == PM.world_size - 1:
-        print("RESULT " + json.dumps({"losses": losses, "grad_norms": [h["grad_norm"] for h in tr.history]}), flush=True)
+        gm = getattr(tr, "grad_manager", None) or getattr(tr, "gm", None)
+        print("RESULT " + json.dumps({"losses": losses, "grad_norms": [h["grad_norm"] for h in tr.history],
+                                      "peer_zero_groups": sorted(getattr(gm, "_peer", {}) or {})}), flush=True)
     if torch.distributed.is_initialized():
         torch.distributed.barrier()
 

@@ -14,8 +14,8 @@ BASE = dict(gbs=4, seq=512, iters=3, layers=2, hidden=512, heads=4, kv_heads=2, 
             min_doc=32, max_doc=256)
 
 
-def _launch(nproc: int, kw: dict, steps: int = 3, port: int = 29611):
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+def _launch(nproc: int, kw: dict, steps: int = 3, port: int = 29611, extra_env: dict | None = None):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **(extra_env or {}))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", "mp_gpu_worker.py"),
            json.dumps(kw), str(steps)]
@@ -39,6 +39,19 @@ def test_two_gpu_layout_matches_one_gpu(single, layout):
     res = _launch(2, dict(BASE, **layout), port=29620 + len(str(layout)) % 50)
     for a, b in zip(res["losses"], single["losses"]):
         assert abs(a - b) < 3e-2 * abs(b), (layout, res["losses"], single["losses"])
+
+
+def test_zero1_over_peer_memory_equals_the_nccl_statement():
+    """dp2: reduce + Adam + parameter refresh through peer memory gives the loss curve and gradient norms of the
+    reduce-scatter / all-gather path (the gradient sums are identical; the squared norm is added up in another
+    order, so the clip coefficient and what follows agree to fp32 rounding)."""
+    peer = _launch(2, dict(BASE), steps=5, port=29671, extra_env={"STB200_PEER_ZERO": "1"})
+    nccl = _launch(2, dict(BASE), steps=5, port=29672, extra_env={"STB200_PEER_ZERO": "0"})
+    assert peer["peer_zero_groups"] == ["DP"] and nccl["peer_zero_groups"] == []
+    for a, b in zip(peer["losses"], nccl["losses"]):
+        assert abs(a - b) <= 5e-5 * max(1.0, abs(b)), (peer["losses"], nccl["losses"])
+    for a, b in zip(peer["grad_norms"], nccl["grad_norms"]):
+        assert abs(a - b) <= 1e-3 * max(1.0, abs(b)), (peer["grad_norms"], nccl["grad_norms"])
 
 
 def _launch_fused(nproc: int, mode: str, port: int):
