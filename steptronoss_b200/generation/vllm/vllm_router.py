@@ -138,4 +138,8 @@ class VLLMRouter:
                 upstream.release()
             return Response(content=content, status_code=upstream.status, headers=out_headers)
 
+        # annotations of this module are strings (postponed evaluation) and ``Request`` is a local name: hand
+        # FastAPI the class itself, otherwise it takes ``request`` for a query parameter
+        proxy.__annotations__ = {"request": Request}
+
         return proxy

@@ -1,0 +1,192 @@
+"""Generation side-car: in-process and multi-process generation controllers, the round-robin router in front of
+fake replicas, and the per-node server controller with a fake server process."""
+import json
+import threading
+import time
+from http.server import BaseHTTPRequestHandler, HTTPServer
+
+import pytest
+
+from tests.gen_items import Rollout, Square
+
+
+def test_single_controller_runs_items_and_reports_errors():
+    from steptronoss_b200.generation.async_generation import SingleGenerationController
+
+    c = SingleGenerationController()
+    try:
+        got = {item.x: res for item, res in c.generate([Square(2), Square(3), Square(-1)])}
+        assert got[2] == 4 and got[3] == 9 and isinstance(got[-1], RuntimeError) and "negative" in str(got[-1])
+        tr = dict((item.x, res) for item, res in c.generate([Rollout(5)], for_train=True))
+        assert tr[5] == [5, 6]
+        bad = list(c.generate([Square(1)], for_train=True))          # not a TrainableItem
+        assert isinstance(bad[0][1], RuntimeError)
+    finally:
+        c.shutdown()
+
+
+def test_multi_process_controller_caps_items_in_flight():
+    from steptronoss_b200.generation.async_generation import GenerationController
+
+    c = GenerationController(num_workers=2, max_concurrent_genables=2, start_method="spawn")
+    try:
+        seen_inflight = []
+        done = []
+        lock = threading.Lock()
+
+        def cb(item, res):
+            with lock:
+                done.append((item.x, res))
+
+        for i in range(6):
+            c.submit_with_callback(Square(i, delay=0.15), callback=cb)
+            seen_inflight.append(c.inflight_count)
+        deadline = time.time() + 60
+        while len(done) < 6 and time.time() < deadline:
+            seen_inflight.append(c.inflight_count)
+            time.sleep(0.02)
+        assert sorted(done) == [(i, i * i) for i in range(6)]
+        assert max(seen_inflight) <= 2 and c.completed_count == 6
+        with pytest.raises(ValueError):
+            GenerationController(num_workers=1, max_concurrent_genables=0)
+    finally:
+        c.shutdown()
+
+
+class _Replica(BaseHTTPRequestHandler):
+    def do_POST(self):  # noqa: N802
+        n = int(self.headers.get("content-length", 0))
+        body = json.loads(self.rfile.read(n) or b"{}")
+        if body.get("stream"):
+            self.send_response(200)
+            self.send_header("content-type", "text/event-stream")
+            self.end_headers()
+            for i in range(3):
+                self.wfile.write(f"data: {self.server.tag}-{i}\n\n".encode())
+                self.wfile.flush()
+            return
+        out = json.dumps({"replica": self.server.tag, "echo": body.get("prompt"), "path": self.path}).encode()
+        self.send_response(200)
+        self.send_header("content-type", "application/json")
+        self.send_header("content-length", str(len(out)))
+        self.end_headers()
+        self.wfile.write(out)
+
+    def log_message(self, *a):
+        pass
+
+
+def _replica(tag):
+    srv = HTTPServer(("127.0.0.1", 0), _Replica)
+    srv.tag = tag
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+    return srv
+
+
+def test_router_registers_and_forwards_round_robin():
+    from fastapi.testclient import TestClient
+
+    from steptronoss_b200.generation.vllm.vllm_router import VLLMRouter, VLLMRouterConfig
+
+    router = VLLMRouter(VLLMRouterConfig())
+    a, b = _replica("a"), _replica("b")
+    try:
+        with TestClient(router.app) as client:
+            assert client.post("/v1/completions", json={"prompt": "x"}).status_code == 503     # nobody registered
+            ea, eb = f"127.0.0.1:{a.server_port}", f"127.0.0.1:{b.server_port}"
+            assert client.get("/register", params={"endpoint": ea}).json() is True
+            assert client.get("/register", params={"endpoint": ea}).json() is False            # already known
+            assert client.get("/register", params={"endpoint": eb}).json() is True
+            assert [e["endpoint"] for e in client.get("/get_info").json()] == [ea, eb]
+            tags = [client.post("/v1/completions", json={"prompt": f"p{i}"}).json() for i in range(4)]
+            assert [t["replica"] for t in tags] == ["a", "b", "a", "b"]
+            assert tags[0]["echo"] == "p0" and tags[0]["path"] == "/v1/completions"
+            r = client.post("/v1/chat/completions", json={"prompt": "s", "stream": True})
+            assert r.status_code == 200 and r.text.count("data: ") == 3
+            assert client.get("/unregister", params={"endpoint": ea}).json() is True
+            assert client.get("/unregister", params={"endpoint": ea}).json() is False
+            assert {client.post("/v1/completions", json={}).json()["replica"] for _ in range(3)} == {"b"}
+    finally:
+        a.shutdown()
+        b.shutdown()
+
+
+def test_router_answers_502_when_a_replica_is_gone():
+    from fastapi.testclient import TestClient
+
+    from steptronoss_b200.generation.vllm.vllm_router import VLLMRouter, VLLMRouterConfig
+
+    router = VLLMRouter(VLLMRouterConfig())
+    dead = _replica("dead")
+    port = dead.server_port
+    dead.shutdown()
+    dead.server_close()
+    with TestClient(router.app) as client:
+        client.get("/register", params={"endpoint": f"127.0.0.1:{port}"})
+        assert client.post("/v1/completions", json={"prompt": "x"}).status_code == 502
+
+
+class _FakeStore(dict):
+    def set(self, k, v):
+        self[k] = str(v).encode()
+
+    def get(self, k):
+        return dict.get(self, k)
+
+    def rpush(self, k, v):
+        self.setdefault(k, []).append(v)
+
+
+def test_controller_starts_waits_registers_and_stops(monkeypatch):
+    import sys
+
+    import steptronoss_b200.utils.comm_utils as cu
+    from steptronoss_b200.generation.vllm import vllm_controller as vc
+
+    class Cfg:
+        router_addr_key, model_name = "k", "m-e1"
+
+        def get_entrypoint_command_and_envs(self):
+            # the "server": an HTTP process that answers /health on $PORT_SERVING
+            code = ("import os,http.server as h;"
+                    "H=type('H',(h.BaseHTTPRequestHandler,),{'do_GET':lambda s:(s.send_response(200),s.end_headers()),"
+                    "'log_message':lambda *a:None});"
+                    "h.HTTPServer(('127.0.0.1',int(os.environ['PORT_SERVING'])),H).serve_forever()")
+            return f'{sys.executable} -c "{code}"', {"EXTRA": "1"}
+
+    calls = []
+
+    class _Resp:
+        status_code, text = 200, "true"
+
+    store = _FakeStore()
+    store.set("VLLM_ROUTER_ADDR_PORT_k", "127.0.0.1:1")
+    monkeypatch.setattr(cu, "get_exp_redis", lambda: store)
+    monkeypatch.setattr(cu, "block_get_redis", lambda s, k: s.get(k))
+    import requests
+
+    real_get = requests.get
+
+    def fake_get(url, **kw):
+        if url.startswith("http://127.0.0.1:1/"):
+            calls.append((url.rsplit("/", 1)[1], kw["params"]["endpoint"]))
+            return _Resp()
+        return real_get(url, **kw)
+
+    monkeypatch.setattr(requests, "get", fake_get)
+    monkeypatch.setenv("NNODES", "3")
+    c = vc.VLLMController(Cfg(), health_interval=0.2)
+    cmd, env = c.command_and_env()
+    assert env["VLLM_SERVER_DEV_MODE"] == "1" and env["EXTRA"] == "1" and env["PORT_SERVING"] == str(c.vllm_port)
+    c.run_vllm()
+    try:
+        c.wait_for_health()
+        c.register()
+        assert calls == [("register", c.endpoint)] and c.endpoint.endswith(f":{c.vllm_port}")
+        assert store["VLLM_NUM_WORKERS_OF_m-e1"] == b"3" and store["VLLM_WORKERS_OF_m-e1"] == [c.endpoint]
+    finally:
+        c.shutdown()
+    assert calls[-1] == ("unregister", c.endpoint)
+    assert c.process.poll() is not None
+    c.shutdown()                                                        # idempotent
+    assert [x[0] for x in calls].count("unregister") == 1
