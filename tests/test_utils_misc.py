@@ -1,0 +1,129 @@
+"""Small utilities: timers, memory marks, RNG streams with recompute, the step writer, CLI overrides."""
+import os
+import time
+
+import pytest
+import torch
+
+
+def test_timers_levels_scopes_and_report():
+    from steptronoss_b200.utils.timers import get_timers, init_timers, timeit
+
+    t = init_timers(log_level=1, use_event=False)
+    with t.record("coarse", 1):
+        time.sleep(0.02)
+    with t.record("fine", 2):          # above the log level: not recorded
+        time.sleep(0.01)
+    t("manual").start()
+    time.sleep(0.01)
+    t("manual").stop()
+
+    @timeit("decorated", log_level=1)
+    def f(x):
+        time.sleep(0.01)
+        return x + 1
+
+    assert f(1) == 2 and get_timers() is t
+    rep = t.report(reset=False)
+    assert set(rep) == {"coarse", "manual", "decorated"} and rep["coarse"] >= 15.0
+    assert t.report(normalizer=2.0, reset=True)["coarse"] == pytest.approx(rep["coarse"] / 2, rel=0.05)
+    assert t.report()["coarse"] == 0.0 and t.log_string().startswith("time (ms) | ")
+    init_timers()
+
+
+def test_memory_marks_only_when_enabled():
+    from steptronoss_b200.utils.memory_tracker import MemoryTracker
+
+    off = MemoryTracker(enabled=False)
+    assert off.mark("a") is None and off.marks == []
+    on = MemoryTracker(enabled=True)
+    on.mark("start")
+    blob = bytearray(64 << 20)
+    m = on.mark("after-alloc")
+    assert m.rss > 0 and len(on.marks) == 2
+    name, d_gpu, d_rss = on.deltas()[0]
+    assert name == "start -> after-alloc" and d_rss > 32 << 20 and d_gpu == 0
+    rep = on.report()
+    assert "after-alloc" in rep and "largest deltas" in rep
+    del blob
+    on.reset()
+    assert on.marks == []
+
+
+def test_rng_tracker_streams_and_recompute_replays_dropout():
+    from steptronoss_b200.parallel.random import checkpoint, get_rng_tracker
+
+    tr = get_rng_tracker()
+    tr.reset()
+    torch.manual_seed(1)
+    tr.add("model-parallel-rng", 1234)
+    with pytest.raises(RuntimeError):
+        tr.add("other", 1234)           # same seed twice
+    with pytest.raises(RuntimeError):
+        tr.add("model-parallel-rng", 99)
+    before = torch.get_rng_state().clone()
+    with tr.fork():
+        a = torch.rand(4)
+    assert torch.equal(torch.get_rng_state(), before)       # the default stream did not move
+    with tr.fork():
+        b = torch.rand(4)
+    assert not torch.equal(a, b)                            # the named stream did
+    saved = tr.get_states()
+    with tr.fork():
+        c = torch.rand(4)
+    tr.set_states(saved)
+    with tr.fork():
+        assert torch.equal(torch.rand(4), c)
+
+    def block(x):
+        with tr.fork():
+            return torch.nn.functional.dropout(x, 0.5, training=True) * 2
+
+    x = torch.randn(64, requires_grad=True)
+    states = tr.get_states()
+    y = checkpoint(block, x)
+    y.sum().backward()                                       # recompute must draw the same mask
+    tr.set_states(states)
+    x2 = x.detach().clone().requires_grad_()
+    y2 = block(x2)
+    y2.sum().backward()
+    assert torch.equal(y, y2) and torch.equal(x.grad, x2.grad)
+    tr.reset()
+
+
+def test_step_writer_writes_event_files(tmp_path):
+    from steptronoss_b200.utils.logger import StepWriter
+
+    w = StepWriter(str(tmp_path / "tb"), backend=("tensorboard",))
+    for i in range(3):
+        w.add_scalar("loss", 1.0 / (i + 1), i)
+    w.add_text("note", "hello", 0)
+    w.add_histogram("h", torch.randn(10), 0)
+    w.flush()
+    w.close()
+    files = os.listdir(tmp_path / "tb")
+    assert any(f.startswith("events.out.tfevents") for f in files) or w.writers == []
+    none = StepWriter(str(tmp_path / "none"), backend=())
+    none.add_scalar("x", 1.0, 0)                            # no writers: a no-op, not an error
+    none.close()
+
+
+def test_cli_overrides_use_literals_and_existing_keys_only():
+    from steptronoss_b200.config import Config
+    from steptronoss_b200.config.arguments import parse_args
+
+    class Inner(Config):
+        lr: float = 1e-3
+        name: str = "a"
+        dims: list = [1, 2]
+
+    class Exp(Config):
+        inner = Inner
+        steps: int = 10
+
+    e = Exp()
+    changes = e.merge(parse_args(["steps=20", "inner.lr=3e-4", "inner.name=hello", "inner.dims=[4,5]"]), exists_only=True)
+    assert e.steps == 20 and e.inner.lr == 3e-4 and e.inner.name == "hello" and e.inner.dims == [4, 5]
+    assert {c[0] for c in changes} == {"steps", "inner.lr", "inner.name", "inner.dims"}
+    with pytest.raises(Exception):
+        e.merge(parse_args(["inner.nope=1"]), exists_only=True)
