@@ -96,10 +96,14 @@ class Checkpointer:
     # ------------------------------------------------------------------ save
     def make_ckpt(self, models, grad_manager, scheduler, dataloader, extra: dict) -> dict:
         files: dict = {}
-        main: dict = {"extra": recur_to_allowed_types(extra), "rng_state": PM.get_all_rng()}
+        keep = getattr(self.cfg, "save_option", None)
+        want = (lambda part: True) if keep is None else (lambda part: bool(getattr(keep, part, True)))
+        main: dict = {"extra": recur_to_allowed_types(extra)}
+        if want("rng_state"):
+            main["rng_state"] = PM.get_all_rng()
         first_replica = PM.rank_in("DP") == 0
         edp_first = (PM.rank_in("EDP") == 0) if PM.has("EDP") else first_replica
-        if first_replica or edp_first:
+        if want("model") and (first_replica or edp_first):
             for i, m in enumerate(models):
                 sd = unwrap_model(m).state_dict()
                 if not first_replica:
@@ -107,15 +111,15 @@ class Checkpointer:
                 elif not edp_first:
                     sd = {k: v for k, v in sd.items() if ".experts." not in k}
                 main["model" if len(models) == 1 else f"model{i}"] = _to_cpu(sd)
-        if scheduler is not None:
+        if scheduler is not None and want("scheduler"):
             main["scheduler"] = scheduler.state_dict()
         files[rank_file_name()] = main
-        if grad_manager is not None and hasattr(grad_manager, "state_dict"):
+        if want("optimizer") and grad_manager is not None and hasattr(grad_manager, "state_dict"):
             sharded = getattr(grad_manager, "shard_optimizer", False)
             if sharded or first_replica:
                 files[rank_file_name(opt=True)] = _to_cpu(grad_manager.state_dict())
         if PM.world_rank == 0:
-            if dataloader is not None and hasattr(dataloader, "state_dict"):
+            if want("data") and dataloader is not None and hasattr(dataloader, "state_dict"):
                 files["data.pkl"] = dataloader.state_dict()
             files["world_size"] = str(PM.world_size)
         return files
@@ -168,8 +172,8 @@ class Checkpointer:
         if getattr(self.cfg, "save_safetensors", False):
             from .hf_checkpoint import dump_safetensors
 
-            dump_safetensors(models, os.path.join(path, "hf"))
-        if sync or not self.cfg.async_save:
+            dump_safetensors(models, os.path.join(path, "hf"), getattr(self.cfg, "model_config_path", None))
+        if sync or not self.cfg.async_dump:
             self._write(files, path, mark_latest)
         else:
             def run():
@@ -196,7 +200,7 @@ class Checkpointer:
 
         Model files exist only for DP rank 0 (EDP rank 0 for experts): those ranks read and the state
         is broadcast over the DP (EDP) group.  Optimizer shards are read by every rank."""
-        opts = self.cfg.load_options
+        opts = self.cfg.load_option
         layout = analyze_dir(path)
         here = {"tp": PM.size_of("TP"), "pp": PM.size_of("PP")}
         if (layout["tp"], layout["pp"]) != (here["tp"], here["pp"]):
@@ -226,8 +230,11 @@ class Checkpointer:
                 if key in main:
                     um = unwrap_model(m)
                     missing = um.load_state_dict(main[key], strict=False)
-                    if missing.missing_keys:
-                        logger.warning(f"missing keys when loading {key}: {missing.missing_keys[:5]} ...", at=None)
+                    lost = [k for k in missing.missing_keys if not k.endswith("_extra_state")]
+                    if lost and getattr(self.cfg, "strict_load_model", False) and PM.size_of("EP") == 1:
+                        raise RuntimeError(f"checkpoint {path} lacks {len(lost)} tensors of {key}: {lost[:5]} ...")
+                    if lost:
+                        logger.warning(f"missing keys when loading {key}: {lost[:5]} ...", at=None)
         opt_file = os.path.join(path, rank_file_name(opt=True))
         if not os.path.exists(opt_file):
             opt_file = os.path.join(path, src_name.replace(".pt", "_OPT.pt"))

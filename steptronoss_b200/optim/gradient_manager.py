@@ -346,6 +346,9 @@ class BaseGradientManager:
         """After loading model weights without optimizer state: fp32 masters follow the parameters."""
         for shard in self.shards.values():
             shard.master.copy_(shard.bucket.param_buf[shard.lo:shard.hi])
+        if self.muon is not None:
+            for e in self.muon.entries:
+                e["master"].copy_(e["low"])
 
     # ------------------------------------------------------------------ offload (RL role swapping)
     def offload_state(self) -> None:

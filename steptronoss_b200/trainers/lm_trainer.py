@@ -179,17 +179,22 @@ class DecoderPretrainTrainer(BaseTrainer):
         path = None
         if ck.auto_resume:
             path = self.checkpointer.latest()
-        if path is None and ck.load_path:
+        hf_dir = ck.load_safetensors
+        if hf_dir is True:  # the HF view that a native checkpoint carries beside it
+            hf_dir = os.path.join(ck.load_path, "hf")
+        if path is None and ck.load_path and not ck.load_safetensors:
             path = ck.load_path
         if path is None:
-            if ck.load_safetensors:
+            if hf_dir:
                 from ..checkpointing.hf_checkpoint import load_safetensors_into
 
                 for m in self.models:
-                    load_safetensors_into(unwrap_model(m), ck.load_safetensors)
+                    load_safetensors_into(unwrap_model(m), hf_dir)
+                if hasattr(self.grad_manager, "refresh_masters_from_params"):
+                    self.grad_manager.refresh_masters_from_params()   # the fp32 masters follow the loaded weights
             return
         state = self.checkpointer.load_ckpt(path, self.models, self.grad_manager, self.scheduler, self.dataloader)
-        if state and ck.load_options.iter:
+        if state and ck.load_option.iter:
             self.iteration = int(state.get("iteration", 0))
             self.history = state.get("history", [])
             self.consumed_samples = int(state.get("consumed_samples", 0))

@@ -107,12 +107,12 @@ class PPOTrainer(BaseTrainer):
         pm = PackedModel(self.ppo_cfg, model_cfg, gm_cfg, sched_cfg, training=training, name=name, seed=self.exp.seed)
         path = self._resume_dir(name if name != "reference_model" else "reference") or role_ck.load_path
         if path:
-            old = self.exp.checkpoint_cfg.load_options
-            self.exp.checkpoint_cfg.load_options = role_ck.load_option
+            old = self.exp.checkpoint_cfg.load_option
+            self.exp.checkpoint_cfg.load_option = role_ck.load_option
             try:
                 extra = self.checkpointer.load_ckpt(path, pm.models, pm.grad_manager, pm.scheduler, None)
             finally:
-                self.exp.checkpoint_cfg.load_options = old
+                self.exp.checkpoint_cfg.load_option = old
             pm.loaded_iteration = int(extra.get("iteration", 0)) if extra else 0
         elif role_ck.load_safetensors:
             from ..checkpointing.hf_checkpoint import load_safetensors_into

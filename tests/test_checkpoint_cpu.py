@@ -47,3 +47,19 @@ def test_incomplete_checkpoint_is_ignored(tmp_path):
     os.remove(os.path.join(latest, "0.success"))     # simulate a rank that died before finishing its write
     ck = e.checkpoint_cfg.build_checkpointer()
     assert ck.latest() is None
+
+
+def test_checkpoint_config_reference_names_aliases_and_save_options():
+    from steptronoss_b200.exp.checkpointing import CheckpointConfig
+
+    c = CheckpointConfig()
+    c.load_option.none(but=["model"])
+    assert c.load_option.model and not c.load_option.optimizer and c.load_options is c.load_option
+    c.save_option.all(but=["optimizer"])
+    assert c.save_option.model and not c.save_option.optimizer
+    c.async_save = False
+    assert c.async_dump is False
+    c.load_path, c.load_safetensors = "/x", "/y"
+    import pytest
+    with pytest.raises(AssertionError):
+        c.sanity_check()
