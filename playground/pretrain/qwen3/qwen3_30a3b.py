@@ -3,7 +3,7 @@
 no shared expert, vocabulary 151936.  Default layout: experts sharded over EP=8 (16 per rank),
 attention data-parallel.
 
-Run: ``torchrun --nproc-per-node 8 playground/pretrain/qwen3/qwen3_30a3b.py [key=value ...]``.
+Run: ``torchrun --nproc-per-node 8 -m playground.pretrain.qwen3.qwen3_30a3b [key=value ...]``.
 """
 import torch
 

@@ -2,7 +2,7 @@
 RMSNorm + per-head QK-norm (eps 1e-6), RoPE theta 1e6, vocabulary 151936, untied embeddings.
 
 Default layout TP=4 with sequence parallelism (data parallel over the remaining ranks, ZeRO-1).
-Run: ``torchrun --nproc-per-node 8 playground/pretrain/qwen3/qwen3_8b.py [key=value ...]``.
+Run: ``torchrun --nproc-per-node 8 -m playground.pretrain.qwen3.qwen3_8b [key=value ...]``.
 """
 import torch
 

@@ -2,7 +2,7 @@
 ``playground/sft/qwen3/qwen3_1p7b_sft_step3_data.py``).  Start from HF weights with
 ``checkpoint_cfg.load_safetensors=/path/to/Qwen3-1.7B-Base``.
 
-    torchrun --nproc-per-node 8 playground/sft/qwen3/qwen3_1p7b_sft.py checkpoint_cfg.load_safetensors=/models/Qwen3-1.7B-Base
+    torchrun --nproc-per-node 8 -m playground.sft.qwen3.qwen3_1p7b_sft checkpoint_cfg.load_safetensors=/models/Qwen3-1.7B-Base
 """
 from playground.data.sft.chat_sft_data import ChatSFTDataConfig
 from playground.pretrain.qwen3.qwen3_1p7b import Qwen3_1p7BConfig
