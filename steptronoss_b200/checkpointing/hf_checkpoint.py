@@ -65,8 +65,8 @@ class HFWeights:
             yield k, self[k]
 
 
-def load_safetensors_into(model, path: str) -> None:
-    model.load_hf_state_dict(HFWeights(path))
+def load_safetensors_into(model, path: str, strict: bool = True) -> list:
+    return model.load_hf_state_dict(HFWeights(path), strict=strict)
 
 
 def dump_safetensors(models, out_dir: str, config_source: str | None = None) -> None:

@@ -202,7 +202,9 @@ class ParallelConfig(Config):
 
     def sanity_check(self):
         super().sanity_check()
-        world = int(os.getenv("WORLD_SIZE", "1"))
+        if os.getenv("WORLD_SIZE") is None:
+            return  # not inside a launched job: the experiment checks the layout against its resource request
+        world = int(os.environ["WORLD_SIZE"])
         attn = self.pipeline_model_parallel_size * self.tensor_model_parallel_size * self.context_parallel_size
         moe = self.pipeline_model_parallel_size * self.expert_tensor_parallel_size * self.expert_model_parallel_size
         assert world >= attn and world % attn == 0, f"world {world} vs PP*TP*CP {attn}"

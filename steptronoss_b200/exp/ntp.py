@@ -111,7 +111,13 @@ class PretrainExp(BaseExp):
 
     def sanity_check(self):
         super().sanity_check()
-        world = int(os.getenv("WORLD_SIZE", "1"))
+        # inside a launched job the world is known; before launch (cfshow, script generation) the job the
+        # resource configuration asks for is what the layout has to fit
+        world = os.getenv("WORLD_SIZE")
+        if world is None:
+            rc = getattr(self, "resource_cfg", None)
+            world = max(int(getattr(rc, "gpu", 0) or 0) * int(getattr(rc, "replica", 1) or 1), 1) if rc is not None else 1
+        world = int(world)
         pc = self.model_cfg.parallel_cfg
         mp = pc.pipeline_model_parallel_size * pc.tensor_model_parallel_size * pc.context_parallel_size
         assert world >= mp and world % mp == 0, f"world {world} incompatible with PP*TP*CP = {mp}"

@@ -67,15 +67,26 @@ class MegatronModule(nn.Module):
             set_defaults_if_not_set_tensor_model_parallel_attributes(p)
             init_parallel_weight_(p, name, seed, std)
 
-    def load_hf_state_dict(self, hf_state: dict) -> None:
+    def load_hf_state_dict(self, hf_state: dict, strict: bool = True) -> list:
+        """Copy the HF tensors into the parameters they map to.  A tensor whose shape differs from its parameter
+        (a value head in place of the LM head, a resized vocabulary) raises when ``strict``, is skipped otherwise;
+        returns the names of the parameters that were skipped."""
         if self.reshaper is None:
             raise NotImplementedError(f"{type(self).__name__} has no HF reshaper")
         native = self.reshaper.forward(hf_state)
         own = dict(self.named_parameters())
+        skipped = []
         for k, v in native.items():
-            if k in own:
-                own[k].data.copy_(v.to(own[k].dtype))
-                own[k].has_initialized = True
+            if k not in own:
+                continue
+            if tuple(own[k].shape) != tuple(v.shape):
+                if strict:
+                    raise RuntimeError(f"{k}: checkpoint tensor {tuple(v.shape)} does not fit parameter {tuple(own[k].shape)}")
+                skipped.append(k)
+                continue
+            own[k].data.copy_(v.to(own[k].dtype))
+            own[k].has_initialized = True
+        return skipped
 
     def hf_state_dict(self) -> dict:
         if self.reshaper is None:

@@ -189,7 +189,7 @@ class DecoderPretrainTrainer(BaseTrainer):
                 from ..checkpointing.hf_checkpoint import load_safetensors_into
 
                 for m in self.models:
-                    load_safetensors_into(unwrap_model(m), hf_dir)
+                    load_safetensors_into(unwrap_model(m), hf_dir, strict=bool(getattr(ck, "strict_load_model", True)))
                 if hasattr(self.grad_manager, "refresh_masters_from_params"):
                     self.grad_manager.refresh_masters_from_params()   # the fp32 masters follow the loaded weights
             return

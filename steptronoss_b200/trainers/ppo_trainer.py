@@ -119,7 +119,8 @@ class PPOTrainer(BaseTrainer):
             from ..models.module import unwrap_model
 
             for m in pm.models:
-                load_safetensors_into(unwrap_model(m), role_ck.load_safetensors)
+                load_safetensors_into(unwrap_model(m), role_ck.load_safetensors,
+                                      strict=role_ck.strict_load_model is not False)
             if pm.grad_manager is not None:
                 pm.grad_manager.refresh_masters_from_params()
         return pm
