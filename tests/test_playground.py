@@ -15,6 +15,7 @@ EXPERIMENTS = [
     ("playground.eval.qwen3.qwen3_eval_simple_benchmarks", "Exp"),
     ("playground.eval.qwen3.qwen3_eval_simple_benchmarks", "Exp1p7B"),
     ("playground.eval.step3p5.step3p5_eval_simple_benchmarks", "Exp"),
+    ("playground.sft.step3v.step3v_10b_sft_tp8_caption_smoke", "Exp"),
 ]
 
 
@@ -138,3 +139,51 @@ def test_simple_eval_set_runs_and_resumes_from_its_cache(tmp_path, monkeypatch):
     cfg.selected_datasets = "NOPE"
     with pytest.raises(ValueError):
         cfg.build_benchmarks()
+
+
+def test_image_caption_data_feeds_the_vision_language_model(tmp_path):
+    import numpy as np
+    import torch
+    from PIL import Image
+
+    from playground.sft.step3v.image_caption_data import ImageCaptionDataConfig
+    from steptronoss_b200.parallel.state import PM
+    from tests.test_vl_model_cpu import _cfg
+
+    for i in range(2):
+        Image.fromarray((np.random.RandomState(i).rand(40, 50, 3) * 255).astype("uint8")).save(tmp_path / f"im{i}.png")
+    (tmp_path / "captions.jsonl").write_text("\n".join(json.dumps({"image": f"im{i}.png", "caption": f"picture {i}"})
+                                                        for i in range(2)))
+
+    class ByteTok:
+        def encode(self, text, add_special_tokens=False):
+            return [4 + (b % 60) for b in text.encode()]
+
+    class Data(ImageCaptionDataConfig):
+        image_size, patch_size, img_start_token, image_token_id = 32, 4, 3, 2
+        max_seq_len = 256
+
+        def build_tokenizer(self):
+            return ByteTok()
+
+    d = Data()
+    d.captions_file = str(tmp_path / "captions.jsonl")
+    d.seqlen_divisible_by = 8
+    stream = d.build_dataloader(dp_rank=1, dp_size=2)           # the second data-parallel rank starts at sample 1
+    batch = next(stream)
+    toks = batch["tokens"].tolist()
+    assert toks.count(3) == 1 and toks.count(2) == d.features_per_image() == 4
+    assert batch["images"].shape == (1, 3, 32, 32) and len(toks) % 8 == 0
+    n_answer = len(ByteTok().encode("picture 1<|im_end|>\n"))
+    assert int(batch["loss_mask"].sum()) == n_answer            # the loss covers the caption (shifted by one)
+    assert stream.state_dict() == {"pos": 3}
+    PM.initialize()
+    cfg = _cfg()
+    PM.set_mesh(cfg.parallel_cfg)
+    model = cfg.build_model()
+    model.init_weights(0, 0.02)
+    feed = d.preprocess(batch)
+    out = model(**{k: feed[k] for k in ("input_ids", "labels", "cu_seqlens", "max_seq_len", "images")},
+                loss_masks=feed["loss_masks"])
+    out["loss"].backward()
+    assert torch.isfinite(out["loss"])
