@@ -40,6 +40,9 @@ def parse():
                     help="qwen3_8b: the headline dense config; qwen3_30b_a3b: the MoE config (EP = N, attention DP = N, "
                          "sequences of 4096, 32 per GPU; its static state needs N >= 4)")
     ap.add_argument("--dispatcher", default="peer", choices=["peer", "alltoall"], help="MoE token dispatcher")
+    ap.add_argument("--moe-capacity-factor", type=float, default=2.0,
+                    help="MoE + peer dispatcher: size the expert buffers for this multiple of the balanced load instead "
+                         "of reading the arrived count back every layer (0 = exact count); overflow fails the run")
     ap.add_argument("--parallelism", default=None, help="e.g. tp4dp2, dp8, tp2; default tp=min(N,4) x dp")
     ap.add_argument("--seqs-per-gpu", type=int, default=None,
                     help="sequences per GPU per step (global batch = this x N); default 8 (dense) / 32 (MoE)")
@@ -156,6 +159,7 @@ def run_ours(args):
     if moe:
         pc.expert_model_parallel_size, pc.expert_tensor_parallel_size = par["ep"], 1
         exp.model_cfg.moe_cfg.dispatcher = args.dispatcher
+        exp.model_cfg.moe_cfg.capacity_factor = args.moe_capacity_factor or None
         if args.debug_layers:
             exp.model_cfg.moe_cfg.moe_layer_list = list(range(args.debug_layers))
     pc.tensor_model_parallel_size = par["tp"]
@@ -300,6 +304,7 @@ def run_ours(args):
         "config": {"model": "Qwen3-30B-A3B-shape MoE" if moe else "Qwen3-8B", "layers": mc.num_layers, "global_batch": tc.global_batch_size,
                    "seq_len": tc.global_seq_length, "micro_batch": 1, "parallelism": par_text,
                    "optimizer": "Adam fp32 master+state, ZeRO-1", "recompute": rec,
+                   **({"moe_dispatcher": args.dispatcher, "moe_capacity_factor": args.moe_capacity_factor or None} if moe else {}),
                    "l2": "inputs larger than L2 (each step streams > 100 GB)"},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_b / args.steps, "h2d_bytes_per_step": h2d,

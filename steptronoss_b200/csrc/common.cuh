@@ -24,6 +24,7 @@ enum ErrCode : int {
   kErrBadArgument = 6,
   kErrSoftmaxWait = 7,
   kErrCorrectionWait = 8,
+  kErrMoeCapacity = 9,  // more routed slots arrived than the expert-major buffers were sized for
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

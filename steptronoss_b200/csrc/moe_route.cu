@@ -52,8 +52,12 @@ __global__ void moe_hist_kernel(const long long* __restrict__ ids, int n_slots, 
 }
 
 // one block: exclusive scan of chunk_hist over chunks (per expert), counts, 128-aligned segment starts, tile groups
+// Segment starts are clamped to `rows` (a multiple of 128): when the caller sized the buffers by a capacity bound
+// instead of the exact count and more slots arrive, the overflowing slots are dropped (dest -1) and the status
+// word records kErrMoeCapacity, so the step fails loudly instead of writing out of bounds.
 __global__ void moe_scan_kernel(int* __restrict__ chunk_hist, int n_chunks, int E, int* __restrict__ counts,
-                                int* __restrict__ offsets, int* __restrict__ tile_group, int n_tiles) {
+                                int* __restrict__ offsets, int* __restrict__ tile_group, int n_tiles, int rows,
+                                int* status) {
   extern __shared__ int smem[];  // E + 1 segment starts
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int run = 0;
@@ -70,6 +74,8 @@ __global__ void moe_scan_kernel(int* __restrict__ chunk_hist, int n_chunks, int 
   if (threadIdx.x == 0) {
     smem[0] = 0;
     for (int e = 0; e < E; ++e) smem[e + 1] += smem[e];
+    if (smem[E] > rows) report_error(status, kErrMoeCapacity);
+    for (int e = 0; e <= E; ++e) smem[e] = min(smem[e], rows);
   }
   __syncthreads();
   for (int e = threadIdx.x; e <= E; e += blockDim.x) offsets[e] = smem[e];
@@ -87,13 +93,18 @@ __global__ void moe_scan_kernel(int* __restrict__ chunk_hist, int n_chunks, int 
 // dest[i] = offsets[e] + (slots of e in earlier chunks) + (slots of e earlier in this chunk); slot_of_row[dest] = i
 __global__ void moe_rank_kernel(const long long* __restrict__ ids, int n_slots, int E, int n_chunks,
                                 const int* __restrict__ chunk_hist, const int* __restrict__ offsets,
-                                long long* __restrict__ dest, int* __restrict__ slot_of_row) {
+                                long long* __restrict__ dest, int* __restrict__ slot_of_row, int rows) {
   extern __shared__ int smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   int* next = smem + warp * E;
   const int c = blockIdx.x * kIndexWarps + warp;
   if (c >= n_chunks) return;
-  for (int e = lane; e < E; e += 32) next[e] = offsets[e] + chunk_hist[static_cast<long long>(c) * E + e];
+  // offsets[e + 1] bounds expert e's segment (clamped to the buffer); ranks past it are dropped
+  int* limit = next + kIndexWarps * E;
+  for (int e = lane; e < E; e += 32) {
+    next[e] = offsets[e] + chunk_hist[static_cast<long long>(c) * E + e];
+    limit[e] = offsets[e + 1];
+  }
   __syncwarp();
   const int begin = c * kChunk;
   const unsigned lt = (1u << lane) - 1u;
@@ -110,8 +121,12 @@ __global__ void moe_rank_kernel(const long long* __restrict__ ids, int n_slots, 
     __syncwarp();
     if (e >= 0) {
       const int d = base + __popc(same & lt);
-      dest[i] = d;
-      slot_of_row[d] = i;
+      if (d < limit[e] && d < rows) {
+        dest[i] = d;
+        slot_of_row[d] = i;
+      } else {
+        dest[i] = -1;
+      }
     } else if (e == -1) {
       dest[i] = -1;
     }
@@ -275,9 +290,9 @@ extern "C" int stb_moe_index_chunks(int n_slots) { return (n_slots + kChunk - 1)
 
 // chunk_hist: int32 scratch of stb_moe_index_chunks(n_slots) * E words.
 extern "C" int stb_moe_index(const void* ids, int n_slots, int E, int rows, void* dest, void* offsets, void* counts,
-                             void* tile_group, int n_tiles, void* slot_of_row, void* chunk_hist,
+                             void* tile_group, int n_tiles, void* slot_of_row, void* chunk_hist, int* status,
                              cudaStream_t stream) {
-  if (E < 1 || E > 2048 || n_slots < 0 || rows < 0) return -kErrBadArgument;
+  if (E < 1 || E > 1024 || n_slots < 0 || rows < 0 || (rows & 127)) return -kErrBadArgument;
   const int n_chunks = stb_moe_index_chunks(n_slots);
   const size_t smem = static_cast<size_t>(kIndexWarps) * E * sizeof(int);
   int blocks = (n_chunks + kIndexWarps - 1) / kIndexWarps;
@@ -289,12 +304,12 @@ extern "C" int stb_moe_index(const void* ids, int n_slots, int E, int rows, void
       static_cast<int*>(slot_of_row), rows);
   moe_scan_kernel<<<1, 1024, (E + 1) * sizeof(int), stream>>>(static_cast<int*>(chunk_hist), n_chunks, E,
                                                                static_cast<int*>(counts), static_cast<int*>(offsets),
-                                                               static_cast<int*>(tile_group), n_tiles);
-  moe_rank_kernel<<<blocks, kIndexWarps * 32, smem, stream>>>(static_cast<const long long*>(ids), n_slots, E, n_chunks,
+                                                               static_cast<int*>(tile_group), n_tiles, rows, status);
+  moe_rank_kernel<<<blocks, kIndexWarps * 32, 2 * smem, stream>>>(static_cast<const long long*>(ids), n_slots, E, n_chunks,
                                                                static_cast<const int*>(chunk_hist),
                                                                static_cast<const int*>(offsets),
                                                                static_cast<long long*>(dest),
-                                                               static_cast<int*>(slot_of_row));
+                                                               static_cast<int*>(slot_of_row), rows);
   return last_error();
 }
 

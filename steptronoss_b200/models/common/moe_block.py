@@ -47,6 +47,10 @@ class MoEConfig(Config):
     dispatcher: str = "alltoall"
     """``alltoall`` (NCCL all-to-all of packed rows) or ``peer`` (rows written straight into the
     destination rank's expert-major buffer over NVLink)."""
+    capacity_factor: float | None = None
+    """peer dispatcher only.  None: expert buffers sized by the exact number of arrived slots (one host read per
+    layer).  f >= 1: sized for f x (tokens x top-k) without a host read; a rank that receives more fails the step
+    with a capacity error (nothing is dropped silently)."""
     recompute_experts: bool = False
 
     def get_aux_loss_calib_scale(self):
@@ -175,7 +179,8 @@ class MoEBlock(nn.Module):
         if self._dispatcher is None:
             from ...parallel.ep_dispatcher import build_dispatcher
 
-            self._dispatcher = build_dispatcher(self.cfg.dispatcher, "EP", self.num_experts)
+            self._dispatcher = build_dispatcher(self.cfg.dispatcher, "EP", self.num_experts,
+                                                getattr(self.cfg, "capacity_factor", None))
         return self._dispatcher
 
     def forward_experts_tp(self, x, ids, weights):

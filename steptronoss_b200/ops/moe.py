@@ -78,7 +78,7 @@ class RoutePlan:
         self.num_experts = num_experts
         self.rows = padded_rows(T * K, num_experts) if rows is None else rows
         dev = ids.device
-        if ids.is_cuda and num_experts <= 2048 and native.available():
+        if ids.is_cuda and num_experts <= 1024 and native.available():
             lib = native.load()
             ids64 = ids.to(torch.int64).contiguous()
             n_tiles = self.rows // SEGMENT_ALIGNMENT
@@ -89,7 +89,8 @@ class RoutePlan:
             scratch = torch.empty(max(lib.stb_moe_index_chunks(T * K), 1) * num_experts, dtype=torch.int32, device=dev)
             rc = lib.stb_moe_index(ids64.data_ptr(), T * K, num_experts, self.rows, self.dest.data_ptr(),
                                    self.offsets.data_ptr(), self.counts.data_ptr(), self.tile_group.data_ptr(), n_tiles,
-                                   self.slot_of_row.data_ptr(), scratch.data_ptr(), native.stream())
+                                   self.slot_of_row.data_ptr(), scratch.data_ptr(),
+                                   native.status_word(dev).data_ptr(), native.stream())
             native.check(rc, "moe_index")
             count_launch(3)
         else:

@@ -72,7 +72,7 @@ _SIGNATURES = {
     "stb_ce_stats": [P, P, P, P, L, I, L, L, P],
     "stb_ce_grad": [P, P, P, P, P, L, I, L, L, P],
     "stb_moe_index_chunks": [I],
-    "stb_moe_index": [P, I, I, I, P, P, P, P, I, P, P, P],
+    "stb_moe_index": [P, I, I, I, P, P, P, P, I, P, P, P, P],
     "stb_moe_scatter": [P, P, P, I, I, I, I, P, P],
     "stb_moe_gather": [P, P, P, I, I, I, P, P],
     "stb_moe_gather_bwd": [P, P, P, P, P, P, I, I, I, I, I, P, P, P],
@@ -131,6 +131,7 @@ _ERRORS = {
     6: "bad argument (alignment / shape)",
     7: "softmax wait timed out",
     8: "correction wait timed out",
+    9: "MoE capacity exceeded: more routed slots than the expert-major buffers hold (raise moe capacity_factor)",
 }
 
 

@@ -32,14 +32,35 @@ def gather_full_matrix(shard: torch.Tensor, param) -> torch.Tensor:
     if world == 1:
         return shard
     dim = param.partition_dim
-    parts = [torch.empty_like(shard) for _ in range(world)]
-    dist.all_gather(parts, shard.contiguous(), group=PM.group_of(group_name))
     blocks = getattr(param, "partition_blocks", None)
+    peer = _gather_over_peer_memory(shard, dim, group_name, world)
+    if peer is not None:
+        parts = list(peer)
+    else:
+        parts = [torch.empty_like(shard) for _ in range(world)]
+        dist.all_gather(parts, shard.contiguous(), group=PM.group_of(group_name))
     if not blocks:
-        return torch.cat(parts, dim=dim)
+        return torch.cat(parts, dim=dim) if peer is None or dim != 0 else peer.reshape(-1, shard.shape[1])
     per = [b // world for b in blocks]
     pieces = [p.split(per, dim=dim) for p in parts]
     return torch.cat([torch.cat([pieces[r][i] for r in range(world)], dim=dim) for i in range(len(blocks))], dim=dim)
+
+
+def _gather_over_peer_memory(shard: torch.Tensor, dim: int, group_name: str, world: int):
+    """``[world, *shard.shape]`` view of every rank's shard, gathered by the push kernel of the fused
+    all-gather (each rank stores its rows into every peer's buffer over NVLink; no NCCL call), or ``None``
+    when the shard does not fit that kernel (not bf16 on the GPU, not 2-D, row count not a multiple of 128)
+    or the group has no peer-memory arena.  The view lives in the group's symmetric memory and is consumed
+    (copied by ``cat`` / normalised by the first Newton-Schulz step) before the second-next gather."""
+    if not (shard.is_cuda and shard.dim() == 2 and shard.dtype == torch.bfloat16):
+        return None
+    from ..parallel import symm
+
+    x = shard.contiguous()
+    if not (symm.enabled(group_name) and symm.usable(x.shape[0], x.shape[1], 8, x)):
+        return None
+    _, gathered = symm.all_gather_gemm(x, None, group_name, need_gathered=True)
+    return gathered.view(world, x.shape[0], x.shape[1])
 
 
 def slice_own_shard(full: torch.Tensor, param) -> torch.Tensor:

@@ -114,9 +114,9 @@ class AllToAllDispatcher:
         return out.to(y.dtype)
 
 
-def build_dispatcher(kind: str, group_name: str, num_experts: int):
+def build_dispatcher(kind: str, group_name: str, num_experts: int, capacity_factor: float | None = None):
     if kind == "peer":
         from .peer_dispatcher import PeerMemoryDispatcher
 
-        return PeerMemoryDispatcher(group_name, num_experts)
+        return PeerMemoryDispatcher(group_name, num_experts, capacity_factor)
     return AllToAllDispatcher(group_name, num_experts)

@@ -15,7 +15,8 @@ the peers' memory; the receiver tells fresh rows from stale ones by the call num
 handed to the expert FFN as it is (``[world*T, H]`` with ids of -1 in the rows that did not arrive): the
 expert-major scatter reads the arrived rows straight out of it, so there is no compaction copy.  One number
 goes to the host per dispatch, the count of arrived (token, expert) slots, which sizes the expert-major buffers
-that autograd keeps.
+that autograd keeps; with a ``capacity_factor`` not even that (the buffers take factor x the balanced load, and a
+rank that receives more fails the step with an error status).
 
 All ranks of the group must call with the same number of tokens ``T``.  CPU tensors (gloo tests), dtypes other
 than bf16 and more than 15 experts per token take the all-to-all statement.
@@ -172,7 +173,12 @@ class _DispatchFn(torch.autograd.Function):
         plan.valid = fresh.to(torch.uint8)
         ids_r = torch.where(fresh.unsqueeze(1), meta[:, 1: 1 + K], torch.full((), -1, dtype=torch.int32, device=x.device)).long()
         w_r = torch.where(fresh.unsqueeze(1), meta[:, 1 + K:].contiguous().view(torch.float32), torch.zeros((), device=x.device))
-        plan.slots = int((ids_r >= 0).sum())           # the one host read of a dispatch
+        if disp.capacity_factor:
+            # no host read: the expert-major buffers take capacity_factor x the balanced load; the index kernel
+            # drops what does not fit and raises the capacity error in the status word
+            plan.slots = min(int(disp.capacity_factor * plan.T * K), plan.world * plan.T * K)
+        else:
+            plan.slots = int((ids_r >= 0).sum())       # the one host read of a dispatch
         ctx.disp, ctx.plan, ctx.w_dtype, ctx.x_dtype = disp, plan, weights.dtype, x.dtype
         ctx.mark_non_differentiable(ids_r)
         return recv, ids_r, w_r.to(weights.dtype)
@@ -200,8 +206,12 @@ class _CombineFn(torch.autograd.Function):
 
 
 class PeerMemoryDispatcher:
-    def __init__(self, group_name: str, num_experts: int):
+    def __init__(self, group_name: str, num_experts: int, capacity_factor: float | None = None):
         self.group_name, self.num_experts = group_name, num_experts
+        self.capacity_factor = capacity_factor
+        """None: size the expert buffers by the exact number of arrived slots (one host read per dispatch).
+        A factor f >= 1: size them for f x tokens x top-k slots without reading anything back; a rank that
+        receives more fails the step with the capacity error instead of dropping tokens silently."""
         self.world, self.rank = PM.size_of(group_name), PM.rank_in(group_name)
         self.per_rank = num_experts // self.world
         self._fallback = AllToAllDispatcher(group_name, num_experts)

@@ -39,6 +39,8 @@ def main():
         return blk
 
     blocks = {k: build(k) for k in ("alltoall", "peer")}
+    blocks["peer_capacity"] = build("peer")
+    blocks["peer_capacity"].cfg.capacity_factor = 1.5
     gw = torch.Generator(device=dev).manual_seed(3)                     # the router is replicated
     ge = torch.Generator(device=dev).manual_seed(100 + PM.world_rank)   # the experts are not
     first = blocks["alltoall"]
@@ -46,7 +48,8 @@ def main():
         first.gate.weight.copy_(torch.randn(first.gate.weight.shape, device=dev, generator=gw) * 0.1)
         for w in (first.experts.w1, first.experts.w2):
             w.copy_(torch.randn(w.shape, device=dev, generator=ge) * 0.05)
-    blocks["peer"].load_state_dict(first.state_dict())
+    for k in ("peer", "peer_capacity"):
+        blocks[k].load_state_dict(first.state_dict())
 
     g = torch.Generator(device=dev).manual_seed(11 + PM.world_rank)
     res = {}
@@ -60,10 +63,11 @@ def main():
             o = blk(xi)
             o.float().pow(2).sum().backward()
             outs[kind] = (o.detach().float(), xi.grad.float(), blk.experts.w1.grad.float(), blk.gate.weight.grad.float())
-        for name, a, b in zip(("out", "dx", "dw1", "dgate"), outs["peer"], outs["alltoall"]):
-            err = float((a - b).abs().max() / b.abs().max().clamp_min(1e-6))
-            res[f"{name}_{it}"] = err
-            assert err < 2e-2, (name, it, err)
+        for kind in ("peer", "peer_capacity"):
+            for name, a, b in zip(("out", "dx", "dw1", "dgate"), outs[kind], outs["alltoall"]):
+                err = float((a - b).abs().max() / b.abs().max().clamp_min(1e-6))
+                res[f"{kind}_{name}_{it}"] = err
+                assert err < 2e-2, (kind, name, it, err)
     if dev.type == "cuda":
         torch.cuda.synchronize()
         native.raise_if_kernel_error()

@@ -141,3 +141,26 @@ def test_fused_router_matches_tensor_ops(T, E, K, sigmoid, norm, use_bias):
     assert torch.allclose(a[5][same], b[5][same], atol=1e-5, rtol=1e-3)
     assert int(a[3].sum()) == T * K and bool((a[0] >= 0).all()) and bool((a[0] < E).all())
     assert bool((a[0].sort(1).values.diff(dim=1) > 0).all())   # k distinct experts per token
+
+
+def test_route_plan_capacity_overflow_is_flagged_and_memory_safe():
+    """Buffers sized below the arrived slots: overflowing slots get dest -1, offsets stay inside the buffer and the
+    status word carries the capacity error (cleared here so that later tests start clean)."""
+    from steptronoss_b200.ops import moe, native
+
+    T, K, E = 1024, 2, 4
+    ids = torch.randint(0, E, (T, K), device="cuda")
+    rows = 1024                                            # half of the 2048 slots
+    plan = moe.RoutePlan(ids, E, rows)
+    torch.cuda.synchronize()
+    assert int(plan.offsets[-1]) <= rows and int(plan.dest.max()) < rows
+    kept = plan.dest >= 0
+    assert 0 < int(kept.sum()) <= rows
+    assert torch.equal(plan.slot_of_row[plan.dest[kept]].long(), torch.arange(T * K, device="cuda").view(T, K)[kept])
+    with pytest.raises(native.NativeLibraryError, match="capacity"):
+        native.raise_if_kernel_error()
+    native.status_word(ids.device).zero_()
+    ok = moe.RoutePlan(ids, E)                             # exact sizing: no flag
+    torch.cuda.synchronize()
+    native.raise_if_kernel_error()
+    assert int((ok.dest >= 0).sum()) == T * K

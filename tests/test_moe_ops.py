@@ -129,4 +129,4 @@ def test_expert_parallel_moe_block_on_two_gloo_ranks():
     out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=root)
     assert out.returncode == 0, out.stderr[-3000:]
     res = json.loads([l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
-    assert len(res) == 12 and max(res.values()) < 1e-6
+    assert len(res) == 24 and max(res.values()) < 1e-6
