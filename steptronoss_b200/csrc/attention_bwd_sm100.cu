@@ -11,8 +11,10 @@
 // work on tile i; the output accumulators stay in TMEM for the whole CTA.  Both passes recompute S, so
 // no atomics are needed and the gradients are bitwise reproducible.
 //
-// The dK/dV pass loops over the q heads of the GQA group inside the CTA, so dK and dV come out already
-// summed over the group.
+// The dK/dV pass loops over q heads of the GQA group inside the CTA, so dK and dV come out summed over them.
+// With few kv heads and key blocks (4 kv heads x 33 blocks is less than one wave of 148 SMs) the group is
+// split over `splits` CTAs; each writes fp32 partials and `attn_dkv_reduce_kernel` adds them in split order,
+// which keeps the gradients bitwise reproducible.
 #include "attention_common.cuh"
 
 namespace stb {
@@ -83,7 +85,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
   const int row_abs0 = p.blk_row0[blk];
   // fixed rows: keys (dkv) or queries (dq), relative to the segment
   const int f0 = row_abs0 - (DKV ? s.k_begin : s.q_begin);
-  const int head_f = blockIdx.x;  // dkv: kv head ; dq: q head
+  const int splits = DKV ? p.splits : 1;
+  const int head_f = DKV ? static_cast<int>(blockIdx.x) / splits : static_cast<int>(blockIdx.x);  // kv head ; q head
+  const int split = DKV ? static_cast<int>(blockIdx.x) % splits : 0;
+  const int gps = group / splits;  // q heads per CTA in the dK/dV pass
   const int kvh = DKV ? head_f : head_f / group;
 
   // streamed range [g_lo, g_hi) in rows of the other side
@@ -99,7 +104,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
   }
   const int sb0 = g_lo / kSB;
   const int nsb = (g_hi > g_lo) ? (g_hi + kSB - 1) / kSB - sb0 : 0;
-  const int iters = nsb * (DKV ? group : 1);
+  const int iters = nsb * (DKV ? gps : 1);
 
   if (threadIdx.x == 0) {
     mbar_init(f_full, 1);
@@ -136,7 +141,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
           *abort_flag = 1;
           break;
         }
-        const int hg = DKV ? kvh * group + it / nsb : kvh;
+        const int hg = DKV ? kvh * group + split * gps + it / nsb : kvh;
         const int grow = (DKV ? s.q_begin : s.k_begin) + (sb0 + it % nsb) * kSB;
         uint8_t* g1 = sG + st * 2 * kStreamTile;
         mbar_arrive_expect_tx(&g_full[st], 2 * kStreamTile);
@@ -212,7 +217,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
       if (*abort_flag) ok = false;
       if (DKV) {
         // per-column constants of the 64 streamed queries: threads 0..63 fetch lse, 64..127 fetch delta
-        const int hq_i = kvh * group + it / nsb;
+        const int hq_i = kvh * group + split * gps + it / nsb;
         const int c = t128 & 63;
         const long long q_abs = static_cast<long long>(s.q_begin) + g0 + c;
         const bool qok = (g0 + c < s.q_len) && (q_abs < p.total_q);
@@ -298,7 +303,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0u;
         }
-        if (store_ok) {
+        if (DKV && splits > 1) {
+          if (store_ok) {
+            float4* part = reinterpret_cast<float4*>(
+                p.dkv_part + (((static_cast<long long>(split) * 2 + which) * p.total_k + f_abs) * p.hkv + kvh) * kD +
+                c * 32);
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+              part[i >> 2] = make_float4(__uint_as_float(v[i]), __uint_as_float(v[i + 1]), __uint_as_float(v[i + 2]),
+                                         __uint_as_float(v[i + 3]));
+          }
+        } else if (store_ok) {
 #pragma unroll
           for (int i = 0; i < 32; i += 8) {
             uint4 o;
@@ -320,6 +335,27 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem, 512);
+  }
+}
+
+// dV / dK = sum over splits (in order) of the fp32 partials; one thread per 4 elements
+__global__ void __launch_bounds__(256)
+attn_dkv_reduce_kernel(const float* __restrict__ part, int splits, long long total_k, int hkv,
+                       __nv_bfloat16* __restrict__ dK, __nv_bfloat16* __restrict__ dV, long long dv_stride) {
+  const long long per = total_k * hkv * (kD / 4);  // float4 words of one [Tk][hkv][D] array
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < 2 * per;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int which = i >= per;
+    const long long w = i - which * per;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < splits; ++s) {
+      const float4 v = reinterpret_cast<const float4*>(part)[(static_cast<long long>(s) * 2 + which) * per + w];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const long long d4 = w % (kD / 4), th = w / (kD / 4);
+    const long long t = th / hkv, h = th % hkv;
+    __nv_bfloat16* dst = which == 0 ? dV + t * dv_stride + h * kD + d4 * 4 : dK + (t * hkv + h) * kD + d4 * 4;
+    *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
   }
 }
 
@@ -345,7 +381,21 @@ attn_delta2_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __r
 
 using namespace stb;
 
+// How many CTAs share the q heads of one kv head in the dK/dV pass: 1 when (kv heads x key blocks) already fills
+// two waves, otherwise the smallest divisor of the group size that does (at most the group size).
+extern "C" int stb_attn_bwd_splits(int hq, int hkv, int num_k_blocks) {
+  if (hkv <= 0 || hq % hkv) return 1;
+  const int group = hq / hkv;
+  const long long want = 2LL * sm_count();
+  for (int s = 1; s <= group; ++s) {
+    if (group % s) continue;
+    if (static_cast<long long>(hkv) * s * num_k_blocks >= want) return s;
+  }
+  return group;
+}
+
 // Backward. dq [Tq][hq][D], dk [Tk][hkv][D] contiguous; dv rows with stride dv_stride (elements).
+// dkv_part: fp32 scratch of splits * 2 * total_k * hkv * head_dim floats when splits > 1 (else unused).
 // q_blk_*: schedule over 128-row q blocks; k_blk_*: schedule over 128-row key blocks.
 // delta: scratch [hq][Tq] floats.
 extern "C" int stb_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
@@ -353,9 +403,11 @@ extern "C" int stb_attn_bwd(const void* q, const void* k, const void* v, const v
                             const int* cu_k, const int* q_blk_seg, const int* q_blk_row0, int num_q_blocks,
                             const int* k_blk_seg, const int* k_blk_row0, int num_k_blocks, int total_q, int total_k,
                             int hq, int hkv, int head_dim, long long q_stride, long long k_stride, long long v_stride,
-                            long long dv_stride, int causal, int window, float scale, int* status, cudaStream_t st) {
+                            long long dv_stride, int causal, int window, float scale, float* dkv_part, int splits,
+                            int* status, cudaStream_t st) {
   if (total_q <= 0 || total_k <= 0) return 0;
   if (head_dim != kD || hq % hkv) return -kErrBadArgument;
+  if (splits < 1 || (hq / hkv) % splits || (splits > 1 && dkv_part == nullptr)) return -kErrBadArgument;
   const long long do_stride = static_cast<long long>(hq) * kD;
   CUtensorMap q128, k128, v128, do128, q64, k64, v64, do64;
   int r;
@@ -385,10 +437,20 @@ extern "C" int stb_attn_bwd(const void* q, const void* k, const void* v, const v
   p.LSE = const_cast<float*>(lse); p.delta = delta;
   p.dQ = static_cast<__nv_bfloat16*>(dq); p.dK = static_cast<__nv_bfloat16*>(dk);
   p.dV = static_cast<__nv_bfloat16*>(dv); p.dv_stride = dv_stride; p.status = status;
+  p.dkv_part = dkv_part; p.splits = splits;
   // dK / dV: fixed = (K, V) of a kv head, streamed = (Q, dO) of the group's q heads
   p.blk_seg = k_blk_seg; p.blk_row0 = k_blk_row0;
-  if (num_k_blocks > 0)
-    attn_bwd_kernel<true><<<dim3(hkv, num_k_blocks), kBwdThreads, kBwdSmem, st>>>(k128, v128, q64, do64, p);
+  if (num_k_blocks > 0) {
+    attn_bwd_kernel<true><<<dim3(hkv * splits, num_k_blocks), kBwdThreads, kBwdSmem, st>>>(k128, v128, q64, do64, p);
+    if (splits > 1) {
+      const long long words = 2LL * total_k * hkv * (kD / 4);
+      long long blocks = (words + 255) / 256;
+      const long long cap = static_cast<long long>(sm_count()) * 16;
+      if (blocks > cap) blocks = cap;
+      attn_dkv_reduce_kernel<<<static_cast<unsigned>(blocks), 256, 0, st>>>(
+          dkv_part, splits, total_k, hkv, static_cast<__nv_bfloat16*>(dk), static_cast<__nv_bfloat16*>(dv), dv_stride);
+    }
+  }
   // dQ: fixed = (Q, dO) of a q head, streamed = (K, V)
   p.blk_seg = q_blk_seg; p.blk_row0 = q_blk_row0;
   if (num_q_blocks > 0)

@@ -33,6 +33,10 @@ struct AttnParams {
   __nv_bfloat16* dV;    // rows with stride dv_stride
   long long dv_stride;
   int* status;
+  // dK/dV pass with the q heads of a GQA group split over several CTAs (few kv heads, short sequences):
+  // fp32 partials [split][dV, dK][Tk][hkv][D], summed in split order by a second kernel
+  float* dkv_part;
+  int splits;
 };
 
 // 128-byte-swizzled address of (row, 16-byte chunk) inside a [128][64 bf16] slab.

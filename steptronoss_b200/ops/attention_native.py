@@ -55,6 +55,9 @@ def _default_cu(total: int, device) -> torch.Tensor:
     return hit[1]
 
 
+_FORCE_SPLITS = 0   # tests set this to exercise the split dK/dV path on shapes that would not choose it
+
+
 class _FlashAttnFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, cu_q, cu_k, causal, window, scale):
@@ -94,13 +97,17 @@ class _FlashAttnFn(torch.autograd.Function):
         delta = torch.empty((hq, Tq), dtype=torch.float32, device=q.device)
         qs, qr, nq = _schedule(cu_q, Tq)
         ks, kr, nk = _schedule(cu_k, Tk)
+        # few kv heads x key blocks: the q heads of a group are split over several CTAs (fp32 partials, ordered sum)
+        splits = _FORCE_SPLITS or lib.stb_attn_bwd_splits(hq, hkv, nk)
+        part = torch.empty((splits, 2, Tk, hkv, D), dtype=torch.float32, device=q.device) if splits > 1 else None
         rc = lib.stb_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
                               delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu_q.data_ptr(),
                               cu_k.data_ptr(), qs.data_ptr(), qr.data_ptr(), nq, ks.data_ptr(), kr.data_ptr(), nk, Tq, Tk,
                               hq, hkv, D, q.stride(0), k.stride(0), v.stride(0), dv.stride(0), int(causal), int(window),
-                              float(scale), native.status_word(q.device).data_ptr(), native.stream())
+                              float(scale), native.ptr(part), splits, native.status_word(q.device).data_ptr(),
+                              native.stream())
         native.check(rc, "attention backward")
-        count_launch(3)
+        count_launch(3 + (splits > 1))
         return dq, dk, dv, None, None, None, None, None
 
 

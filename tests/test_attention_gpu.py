@@ -68,3 +68,38 @@ def test_flash_attention_is_deterministic():
         outs.append((o.detach().clone(), q.grad.clone(), k.grad.clone(), v.grad.clone()))
     for a, b in zip(*outs):
         assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("splits", [1, 2, 4, 8])
+def test_dkv_pass_split_over_the_q_heads_of_a_group(splits):
+    """hq=16 / hkv=2 (group of 8): the dK/dV pass with the group on one CTA and split over 2, 4 and 8 CTAs gives the
+    gradients of the fp32 restatement, and each split count is bitwise reproducible."""
+    from steptronoss_b200.ops import attention_native, native
+    from steptronoss_b200.ops.attention import attention, attention_reference
+
+    torch.manual_seed(3)
+    lens = [700, 324, 129]
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    q = torch.randn(T, 16, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(T, 2, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(T, 2, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(T, 16, 128, device="cuda", dtype=torch.bfloat16)
+    old = attention_native._FORCE_SPLITS
+    attention_native._FORCE_SPLITS = splits
+    try:
+        runs = []
+        for _ in range(2):
+            for t in (q, k, v):
+                t.grad = None
+            attention(q, k, v, cu, cu, max(lens)).backward(g)
+            runs.append((k.grad.clone(), v.grad.clone(), q.grad.clone()))
+        torch.cuda.synchronize()
+        native.raise_if_kernel_error()
+    finally:
+        attention_native._FORCE_SPLITS = old
+    for a, b in zip(*runs):
+        assert torch.equal(a, b)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    attention_reference(qr, kr, vr, cu.cpu(), cu.cpu(), True, 0).backward(g.float())
+    assert _rel(runs[0][0], kr.grad) < 2e-2 and _rel(runs[0][1], vr.grad) < 2e-2 and _rel(runs[0][2], qr.grad) < 2e-2
