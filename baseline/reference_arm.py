@@ -40,6 +40,9 @@ def _unavailable(why: str):
 
 
 def run(args) -> None:
+    if getattr(args, "model", "qwen3_8b") != "qwen3_8b":
+        return _unavailable("the reference arm drives the Qwen3-8B dense configuration only: the reference's MoE path "
+                            "needs its Triton grouped GEMM / grouped_gemm wheel, neither of which is part of this arm")
     if not os.path.isdir(os.path.join(REF, "steptronoss")):
         return _unavailable("baseline/_ref/steptronoss is absent: copy the reference tree there first")
     sys.path.insert(0, os.path.join(HERE, "shims"))
