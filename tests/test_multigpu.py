@@ -96,3 +96,13 @@ def test_expert_parallel_moe_block_peer_vs_all_to_all():
     assert out.returncode == 0, "\n".join(l for l in out.stderr.splitlines() if l.startswith("[rank0]"))[-4000:]
     res = json.loads([l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
     assert max(res.values()) < 2e-2
+
+
+def test_muon_gathers_tp_shards_over_peer_memory():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29745", os.path.join(ROOT, "tests", "mp_muon_gather_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+    assert out.returncode == 0, "\n".join(l for l in out.stderr.splitlines() if l.startswith("[rank0]"))[-4000:]
+    res = json.loads([l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
+    assert res == {"rows": True, "cols": True, "blocks": True}     # every case took the peer path
