@@ -286,3 +286,48 @@ def sync_point(text: str = "") -> None:
 
     if dist.is_initialized():
         dist.barrier()
+
+
+def load(path: str, mode: str | None = None, **kwargs):
+    """Read a file by its extension (or ``mode``): ``json``, ``jsonl`` (list of records), ``hjson``, ``torch``
+    (``.pt`` / ``.pth``, on the CPU), ``pickle`` (``.pkl``), ``yaml``, ``npy`` / ``npz``, ``safetensors`` (dict of
+    tensors), ``text`` (``.txt``); reference ``steptronoss/utils/utils.py:546-590``."""
+    import json
+    import pickle
+
+    def is_(ext: tuple, name: str) -> bool:
+        return mode == name or (mode is None and path.endswith(ext))
+
+    if is_((".json",), "json"):
+        with open(path, "rb") as f:
+            return json.load(f, **kwargs)
+    if is_((".jsonl",), "jsonl"):
+        with open(path, encoding="utf-8") as f:
+            return [json.loads(line, **kwargs) for line in f if line.strip()]
+    if is_((".hjson",), "hjson"):
+        import hjson
+
+        with open(path, "rb") as f:
+            return hjson.load(f, **kwargs)
+    if is_((".pt", ".pth"), "torch"):
+        return torch.load(path, weights_only=False, map_location="cpu", **kwargs)
+    if is_((".pkl", ".pickle"), "pickle"):
+        with open(path, "rb") as f:
+            return pickle.load(f, **kwargs)
+    if is_((".yaml", ".yml"), "yaml"):
+        import yaml
+
+        with open(path, "rb") as f:
+            return yaml.safe_load(f)
+    if is_((".npy", ".npz"), "numpy"):
+        import numpy as np
+
+        return np.load(path, **kwargs)
+    if is_((".safetensors",), "safetensors"):
+        from safetensors.torch import load_file
+
+        return load_file(path, **kwargs)
+    if is_((".txt",), "text"):
+        with open(path, encoding="utf-8") as f:
+            return f.read()
+    raise ValueError(f"cannot tell how to load {path!r}: pass mode=json|jsonl|hjson|torch|pickle|yaml|numpy|safetensors|text")

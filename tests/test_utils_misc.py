@@ -127,3 +127,49 @@ def test_cli_overrides_use_literals_and_existing_keys_only():
     assert {c[0] for c in changes} == {"steps", "inner.lr", "inner.name", "inner.dims"}
     with pytest.raises(Exception):
         e.merge(parse_args(["inner.nope=1"]), exists_only=True)
+
+
+def test_generic_load_by_extension_and_mode(tmp_path):
+    import json
+    import pickle
+
+    import numpy as np
+
+    from steptronoss_b200.utils.general import load
+
+    (tmp_path / "a.json").write_text(json.dumps({"x": 1}))
+    (tmp_path / "a.jsonl").write_text('{"i": 0}\n\n{"i": 1}\n')
+    (tmp_path / "a.yaml").write_text("k: [1, 2]\n")
+    (tmp_path / "a.txt").write_text("hello")
+    (tmp_path / "weird.bin").write_text(json.dumps([3]))
+    pickle.dump({"p": 2}, open(tmp_path / "a.pkl", "wb"))
+    torch.save({"t": torch.arange(3)}, tmp_path / "a.pt")
+    np.save(tmp_path / "a.npy", np.arange(4))
+    assert load(str(tmp_path / "a.json")) == {"x": 1}
+    assert load(str(tmp_path / "a.jsonl")) == [{"i": 0}, {"i": 1}]
+    assert load(str(tmp_path / "a.yaml")) == {"k": [1, 2]} and load(str(tmp_path / "a.txt")) == "hello"
+    assert load(str(tmp_path / "a.pkl")) == {"p": 2} and load(str(tmp_path / "a.pt"))["t"].tolist() == [0, 1, 2]
+    assert load(str(tmp_path / "a.npy")).tolist() == [0, 1, 2, 3]
+    assert load(str(tmp_path / "weird.bin"), mode="json") == [3]
+    with pytest.raises(ValueError):
+        load(str(tmp_path / "weird.bin"))
+
+
+def test_debug_attach_only_listens_on_the_chosen_ranks(monkeypatch):
+    import sys
+    import types
+
+    import steptronoss_b200
+
+    calls = []
+    fake = types.SimpleNamespace(is_client_connected=lambda: False,
+                                 listen=lambda addr, in_process_debug_adapter=False: calls.append(("listen", addr[1])),
+                                 wait_for_client=lambda: calls.append(("wait",)), breakpoint=lambda: calls.append(("break",)))
+    monkeypatch.setitem(sys.modules, "debugpy", fake)
+    assert steptronoss_b200.debug(rank=[3, 5]) is None and calls == []          # this process is rank 0
+    host, port = steptronoss_b200.debug(rank=[2, 0], stop=True)
+    assert port == 5001 and calls == [("listen", 5001), ("wait",), ("break",)]
+    calls.clear()
+    assert steptronoss_b200.debug(any_rank=True, base_port=6000)[1] == 6000
+    fake.is_client_connected = lambda: True
+    assert steptronoss_b200.debug(rank=0) is None
