@@ -1,5 +1,6 @@
-"""``cfshow exp.py [-k subtree] [--diff other.py]``: print an experiment's config tree and run its
-``sanity_check`` (reference ``README.md:38-45``)."""
+"""``cfshow exp.py [-k subtree] [--diff [other.py]]``: print an experiment's config tree and run its
+``sanity_check`` (reference ``README.md:38-45``).  ``--diff`` without a file compares with the experiment class
+this one derives from (what the file changes on top of its base)."""
 from __future__ import annotations
 
 import argparse
@@ -22,10 +23,19 @@ def show(path: str, key: str | None = None, diff: str | None = None, check: bool
     else:
         print(repr(node), file=out)
     if diff:
-        other = get_object_from_file(diff, "Exp")()
-        print(f"--- diff vs {diff}", file=out)
-        for k, a, b in exp.diff(other):
-            print(f"  {k}: {a} | {b}", file=out)
+        if diff == "parent":
+            bases = [b for b in type(exp).__mro__[1:] if isinstance(b, type) and issubclass(b, Config) and b is not Config]
+            if not bases:
+                print("--- no parent experiment to diff against", file=out)
+                other = None
+            else:
+                other, diff = bases[0](), f"{bases[0].__module__}.{bases[0].__qualname__}"
+        else:
+            other = get_object_from_file(diff, "Exp")()
+        if other is not None:
+            print(f"--- diff vs {diff} (this | other)", file=out)
+            for k, a, b in exp.diff(other):
+                print(f"  {k}: {a} | {b}", file=out)
     if check:
         try:
             exp.sanity_check()
@@ -40,7 +50,8 @@ def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="cfshow", description=__doc__)
     ap.add_argument("exp_file")
     ap.add_argument("-k", "--key", default=None, help="dotted path of the subtree to print")
-    ap.add_argument("--diff", default=None, help="another experiment file to diff against")
+    ap.add_argument("--diff", nargs="?", const="parent", default=None,
+                    help="another experiment file to diff against; without a value: the parent experiment class")
     ap.add_argument("--no-check", action="store_true")
     ns, rest = ap.parse_known_args(argv)
     sys.argv = [ns.exp_file] + rest
