@@ -190,3 +190,83 @@ def test_controller_starts_waits_registers_and_stops(monkeypatch):
     assert c.process.poll() is not None
     c.shutdown()                                                        # idempotent
     assert [x[0] for x in calls].count("unregister") == 1
+
+
+def test_deploy_command_lists_the_configured_options(monkeypatch):
+    from steptronoss_b200.exp.inference import VLLMDeployConfig
+
+    monkeypatch.setenv("EXP_ID", "run7/trainer")
+    c = VLLMDeployConfig()
+    c.model_config_path, c.max_seq_len, c.vllm_tp, c.vllm_dp, c.max_cache_size = "/m/q", 4096, 2, 4, 32
+    c.reasoning_parser, c.enable_expert_parallel, c.vllm_enable_prefix_caching = "deepseek_r1", True, False
+    c.vllm_hf_overrides = {"rope_scaling": None}
+    c.vllm_mtp_num_tokens, c.vllm_mtp_method = 2, "mtp"
+    c.load_weight_from_config_path = False
+    cmd, env = c.get_entrypoint_command_and_envs()
+    assert cmd.startswith("vllm serve /m/q --port $PORT_SERVING")
+    for piece in ("--max-model-len 4096", "--tensor-parallel-size 2", "--data-parallel-size 4", "--max-num-seqs 32",
+                  "--reasoning-parser deepseek_r1", "--enable-expert-parallel", "--no-enable-prefix-caching",
+                  "--hf-overrides $HF_OVERRIDES", "--speculative-config $SPECULATIVE_CONFIG", "--load-format dummy",
+                  "--tokenizer /m/q", "--trust-remote-code", "--enable-chunked-prefill"):
+        assert piece in cmd, piece
+    assert "--pipeline-parallel-size" not in cmd and "--enforce-eager" not in cmd
+    assert json.loads(env["HF_OVERRIDES"].strip("'")) == {"rope_scaling": None}
+    assert json.loads(env["SPECULATIVE_CONFIG"].strip("'")) == {"num_speculative_tokens": 2, "method": "mtp"}
+    assert "run7" in c.model_name and f"--served-model-name {c.model_name}" in cmd
+
+
+class _Server(BaseHTTPRequestHandler):
+    """Plays the router (/get_info, /v1/completions) and a replica (/collective_rpc, /reset_prefix_cache)."""
+
+    def _send(self, obj):
+        out = json.dumps(obj).encode()
+        self.send_response(200)
+        self.send_header("content-type", "application/json")
+        self.send_header("content-length", str(len(out)))
+        self.end_headers()
+        self.wfile.write(out)
+
+    def do_GET(self):  # noqa: N802
+        self.server.log.append(("GET", self.path))
+        self._send([{"endpoint": f"127.0.0.1:{self.server.server_port}"}])
+
+    def do_POST(self):  # noqa: N802
+        n = int(self.headers.get("content-length", 0))
+        body = json.loads(self.rfile.read(n) or b"{}")
+        self.server.log.append(("POST", self.path, body))
+        self._send({"choices": [{"text": "pong", "token_ids": [1]}]} if "completions" in self.path else {"ok": True})
+
+    def log_message(self, *a):
+        pass
+
+
+def test_client_waits_completes_and_reloads_weights(monkeypatch):
+    import steptronoss_b200.utils.comm_utils as cu
+    from steptronoss_b200.generation.vllm.vllm_client import VLLMClient
+
+    srv = HTTPServer(("127.0.0.1", 0), _Server)
+    srv.log = []
+    threading.Thread(target=srv.serve_forever, daemon=True).start()
+
+    class Cfg:
+        router_addr_key, model_name = "k", "m"
+
+    store = _FakeStore()
+    store.set("VLLM_ROUTER_ADDR_PORT_k", f"127.0.0.1:{srv.server_port}")
+    store.set("VLLM_NUM_WORKERS_OF_m", 1)
+    monkeypatch.setattr(cu, "get_exp_redis", lambda: store)
+    monkeypatch.setattr(cu, "block_get_redis", lambda s, k, timeout=None: s.get(k))
+    cli = VLLMClient(Cfg())
+    try:
+        assert cli.wait_for_server(timeout=20) == [f"127.0.0.1:{srv.server_port}"]
+        out = cli.completion("hello", max_tokens=5)
+        assert out["choices"][0]["text"] == "pong"
+        sent = [x for x in srv.log if x[0] == "POST" and x[1] == "/v1/completions"][-1][2]
+        assert sent == {"prompt": "hello", "return_token_ids": True, "model": "m", "max_tokens": 5}
+        assert cli.reload_weights("/hot") is True
+        rpc = [x for x in srv.log if x[0] == "POST" and x[1] == "/collective_rpc"][-1][2]
+        assert rpc == {"method": "reload_weights", "kwargs": {"weights_path": "/hot"}}
+        assert any(x[1] == "/reset_prefix_cache" for x in srv.log)
+    finally:
+        cli.close()
+        srv.shutdown()
