@@ -140,6 +140,11 @@ class ProfilerConfig(Config):
     timing_log_level = 0
     timing_use_event = True
     log_path = Ref("..log_path", "./")
+    kernel_watchdog_s: float | None = None
+    """seconds between reads of the kernels' status word by a watchdog thread (None: the word is read when the
+    trainer logs); an error code ends training at once instead of at the next log line"""
+    stall_watchdog_s: float | None = None
+    """report (with the stacks of all threads) when no training step finished for this many seconds"""
 
 
 class TokenizerConfig(AbstractTokenizerConfig):

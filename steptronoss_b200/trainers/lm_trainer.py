@@ -96,15 +96,39 @@ class DecoderPretrainTrainer(BaseTrainer):
             self.train_iters = int(t.item())
 
     # ------------------------------------------------------------------ loop
+    def _start_watchdog(self):
+        pc = getattr(self.exp, "profiler_cfg", None)
+        every, stall = getattr(pc, "kernel_watchdog_s", None), getattr(pc, "stall_watchdog_s", None)
+        if not every and not stall:
+            return None
+        from ..utils.watchdog import KernelWatchdog
+
+        return KernelWatchdog(interval_s=float(every or min(stall / 4, 10.0)), stall_s=stall).start()
+
     def train_loop(self):
         tc = self.exp.trainer_cfg
         timers = get_timers()
         self._t_last = time.perf_counter()
+        self._watchdog = self._start_watchdog()
+        try:
+            self._train_iterations(tc, timers)
+        except KeyboardInterrupt:
+            if self._watchdog is not None and self._watchdog.tripped.is_set():
+                raise RuntimeError(self._watchdog.error) from None   # the watchdog interrupted the main thread
+            raise
+        finally:
+            if self._watchdog is not None:
+                self._watchdog.stop()
+
+    def _train_iterations(self, tc, timers):
         while self.iteration < self.train_iters:
             self.call_hooks("before_step")
             with timers.record("iteration", 0):
                 self.train_step()
             self.iteration += 1
+            if self._watchdog is not None:
+                self._watchdog.beat()
+                self._watchdog.raise_if_tripped()
             self.call_hooks("after_step")
             if self.iteration % tc.log_interval == 0:
                 self.training_log()
