@@ -34,8 +34,8 @@ def _load_file(path: str, name: str):
     return mod
 
 
-def _unavailable(why: str):
-    if int(os.environ.get("RANK", "0")) == 0:
+def _unavailable(why: str, any_rank: bool = False):
+    if any_rank or int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")[:400]}), flush=True)
 
 
@@ -52,7 +52,15 @@ def run(args) -> None:
     except BaseException as e:  # report instead of failing the driver
         sys.stderr.write(traceback.format_exc())
         tb = traceback.format_exc().strip().splitlines()
-        _unavailable(f"{type(e).__name__}: {e} | {tb[-3] if len(tb) > 3 else ''}")
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        # the rank that failed reports (the others may be waiting for it inside a collective and never will)
+        _unavailable(f"rank {os.environ.get('RANK', '0')}: {type(e).__name__}: {e} | {tb[-3] if len(tb) > 3 else ''}",
+                     any_rank=world > 1)
+        if world > 1:
+            # end the whole job now: a clean return would leave the other ranks in their collective until the
+            # process-group timeout; the launcher stops them when one worker exits with an error
+            sys.stdout.flush()
+            os._exit(3)
 
 
 def _run(args) -> None:

@@ -332,9 +332,11 @@ if __name__ == "__main__":
     import faulthandler
 
     faulthandler.enable()
-    if os.environ.get("STB200_BENCH_WATCHDOG_S"):
-        # development aid: dump every thread's stack and exit if the run exceeds the given seconds
-        faulthandler.dump_traceback_later(int(os.environ["STB200_BENCH_WATCHDOG_S"]), exit=True)
+    # a run that exceeds this many seconds (a rank lost in a collective after another one failed) dumps every
+    # thread's stack and exits instead of waiting for the process-group timeout; 0 switches the limit off
+    limit = int(os.environ.get("STB200_BENCH_WATCHDOG_S", "1800"))
+    if limit > 0:
+        faulthandler.dump_traceback_later(limit, exit=True)
     a = parse()
     if a.impl == "reference":
         run_reference(a)
