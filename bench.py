@@ -341,4 +341,14 @@ if __name__ == "__main__":
     if a.impl == "reference":
         run_reference(a)
     else:
-        run_ours(a)
+        try:
+            run_ours(a)
+        except BaseException:
+            if int(os.environ.get("WORLD_SIZE", "1")) > 1 and not isinstance(sys.exc_info()[1], SystemExit):
+                # the other ranks may sit in a collective waiting for this one: show why and end the job now
+                import traceback
+
+                traceback.print_exc()
+                sys.stderr.flush()
+                os._exit(1)
+            raise
