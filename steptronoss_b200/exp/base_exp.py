@@ -140,6 +140,8 @@ class ProfilerConfig(Config):
     timing_log_level = 0
     timing_use_event = True
     log_path = Ref("..log_path", "./")
+    nvtx_ranges: bool = False
+    """bracket every timed region (at the active timing level) with an NVTX range of the same name"""
     kernel_watchdog_s: float | None = None
     """seconds between reads of the kernels' status word by a watchdog thread (None: the word is read when the
     trainer logs); an error code ends training at once instead of at the next log line"""

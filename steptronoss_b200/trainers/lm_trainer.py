@@ -43,7 +43,8 @@ class DecoderPretrainTrainer(BaseTrainer):
         PM.set_mesh(exp.model_cfg.parallel_cfg)
         set_mpu_random_seed(exp.seed)
         prof = getattr(exp, "profiler_cfg", None)
-        init_timers(getattr(prof, "timing_log_level", 0), getattr(prof, "timing_use_event", True))
+        init_timers(getattr(prof, "timing_log_level", 0), getattr(prof, "timing_use_event", True),
+                    getattr(prof, "nvtx_ranges", False))
         GlobalMetrics.clear()
         if getattr(exp, "metric_cfg", None) is not None:
             exp.metric_cfg.register()

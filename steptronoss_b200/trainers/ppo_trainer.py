@@ -82,7 +82,8 @@ class PPOTrainer(BaseTrainer):
         PM.set_mesh(exp.actor_model_cfg.parallel_cfg)
         set_mpu_random_seed(exp.seed)
         prof = getattr(exp, "profiler_cfg", None)
-        self.timers = init_timers(getattr(prof, "timing_log_level", 0), getattr(prof, "timing_use_event", True))
+        self.timers = init_timers(getattr(prof, "timing_log_level", 0), getattr(prof, "timing_use_event", True),
+                    getattr(prof, "nvtx_ranges", False))
         GlobalMetrics.clear()
         exp.metric_cfg.register()
         if PM.world_rank == PM.world_size - 1 and getattr(exp.trainer_cfg, "writer_backend", None):

@@ -66,24 +66,32 @@ class _Noop:
 
 
 class _Scope:
-    def __init__(self, timer):
-        self.timer = timer
+    """Times a region; with ``nvtx`` also brackets it with an NVTX range of the timer's name, so the regions show
+    up by name on a profiler's timeline."""
+
+    def __init__(self, timer, nvtx: bool = False):
+        self.timer, self.nvtx = timer, nvtx and torch.cuda.is_available()
 
     def __enter__(self):
+        if self.nvtx:
+            torch.cuda.nvtx.range_push(self.timer.name)
         self.timer.start()
         return self.timer
 
     def __exit__(self, *a):
         self.timer.stop()
+        if self.nvtx:
+            torch.cuda.nvtx.range_pop()
         return False
 
 
 class Timers:
     """Levels: 0 always, 1 coarse (forward-backward, optimizer-step, dataloader-next), 2 fine."""
 
-    def __init__(self, log_level: int = 0, use_event: bool = True):
+    def __init__(self, log_level: int = 0, use_event: bool = True, nvtx: bool = False):
         self.log_level = log_level
         self.use_event = use_event
+        self.nvtx = nvtx
         self.timers: dict[str, Timer] = {}
         self._noop = _Noop()
 
@@ -96,7 +104,7 @@ class Timers:
 
     def record(self, name: str, log_level: int = 0):
         t = self(name, log_level)
-        return t if isinstance(t, _Noop) else _Scope(t)
+        return t if isinstance(t, _Noop) else _Scope(t, self.nvtx)
 
     def report(self, names=None, normalizer: float = 1.0, reset: bool = True) -> dict:
         names = names or list(self.timers)
@@ -110,9 +118,9 @@ class Timers:
 _GLOBAL = Timers()
 
 
-def init_timers(log_level: int = 0, use_event: bool = True) -> Timers:
+def init_timers(log_level: int = 0, use_event: bool = True, nvtx: bool = False) -> Timers:
     global _GLOBAL
-    _GLOBAL = Timers(log_level, use_event)
+    _GLOBAL = Timers(log_level, use_event, nvtx)
     return _GLOBAL
 
 
