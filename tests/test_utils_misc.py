@@ -173,3 +173,30 @@ def test_debug_attach_only_listens_on_the_chosen_ranks(monkeypatch):
     assert steptronoss_b200.debug(any_rank=True, base_port=6000)[1] == 6000
     fake.is_client_connected = lambda: True
     assert steptronoss_b200.debug(rank=0) is None
+
+
+def test_capture_trace_writes_forward_and_backward_traces(tmp_path):
+    import json
+
+    from steptronoss_b200.utils.dev_utils import capture_trace
+
+    fw, bw = str(tmp_path / "fw.json"), str(tmp_path / "bw.json")
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = torch.nn.Linear(8, 8)
+
+        @capture_trace(at=1, fw_file=fw, bw_file=bw, warmup=1)
+        def forward(self, x):
+            return self.lin(x).relu()
+
+    m = M()
+    for i in range(4):
+        m(torch.randn(4, 8)).sum().backward()
+        done = os.path.exists(fw) and os.path.exists(bw)
+        assert done == (i >= 2)                 # the window opens at call warmup + at (the third call)
+    for f in (fw, bw):
+        events = json.load(open(f))["traceEvents"]
+        assert len(events) > 0
+    assert any(e.get("name") == "FW" for e in json.load(open(fw))["traceEvents"])
