@@ -12,7 +12,6 @@ import json
 import os
 import shutil
 
-import torch
 
 from ..models.module import unwrap_model
 from ..parallel.state import PM

@@ -20,10 +20,8 @@ import os
 import pickle
 import re
 import threading
-import time
 
 import torch
-import torch.distributed as dist
 
 from ..config import recur_to_allowed_types
 from ..models.module import unwrap_model

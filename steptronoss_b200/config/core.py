@@ -17,7 +17,6 @@ from __future__ import annotations
 
 import contextlib
 import copy
-import inspect
 from typing import Any, Iterator
 
 _MISSING = object()

@@ -11,7 +11,6 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from ..config import Config
 from ..exp.base_exp import Megatron3DParallelModelConfig, MegatronTPConfig
 from ..parallel.random import checkpoint, get_rng_tracker
 from ..parallel.state import PM

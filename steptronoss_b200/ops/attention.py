@@ -14,8 +14,6 @@ import os
 
 import torch
 
-from . import native
-from .gemm import count_launch
 
 
 def _segment_mask(lq: int, lk: int, causal: bool, window: int, device):

@@ -8,7 +8,6 @@ implementation.
 from __future__ import annotations
 
 import ctypes
-import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from pathlib import Path
 

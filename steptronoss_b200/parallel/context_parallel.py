@@ -17,7 +17,6 @@ import weakref
 from dataclasses import dataclass, field
 
 import torch
-import torch.distributed as dist
 
 from ..ops import attention
 from . import comm

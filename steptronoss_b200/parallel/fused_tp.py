@@ -16,7 +16,6 @@ reduce-scatters the input gradient; the row layer all-gathers the output gradien
 from __future__ import annotations
 
 import torch
-import torch.distributed as dist
 
 from ..ops.gemm import gemm
 from . import comm

@@ -27,7 +27,7 @@ from ..utils.logger import logger
 from ..utils.memory_tracker import CMT
 from ..utils.metrics import GlobalMetrics
 from ..utils.rl_utils import RaggedPPOSampleDumper
-from ..utils.timers import get_timers, init_timers
+from ..utils.timers import init_timers
 from .base_trainer import BaseTrainer
 from .packed_model import PackedModel
 

@@ -7,7 +7,6 @@ travels pickled.
 from __future__ import annotations
 
 import io
-import pickle
 from typing import Any, Callable
 
 import torch

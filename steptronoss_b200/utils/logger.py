@@ -7,7 +7,6 @@ from __future__ import annotations
 
 import logging
 import os
-import sys
 
 
 def _rank() -> int:
