@@ -14,6 +14,7 @@ from __future__ import annotations
 
 import torch
 
+from ..utils.optimizable import optimizable
 from . import native
 from .fused import swiglu
 from .gemm import count_launch
@@ -258,6 +259,11 @@ def router_native_ok(logits: torch.Tensor, top_k: int) -> bool:
             and native.available())
 
 
+def _router_reference_alt(*a, **k):
+    return router_reference(*a, **k)
+
+
+@optimizable({"reference": _router_reference_alt})
 def fused_router(logits, bias, top_k: int, sigmoid: bool, norm_topk: bool, eps: float):
     """Scores, top-k and the per-expert sums of the auxiliary loss in one kernel (one warp per token).
 
@@ -320,6 +326,11 @@ def grouped_linear(x, w, offsets, tile_group=None):
     return _GroupedLinearFn.apply(x, w, offsets, tile_group)
 
 
+def _routed_ffn_reference_alt(x, expert_ids, weights, w1, w2, limit: float = 0.0, max_slots: int | None = None):
+    return routed_grouped_ffn_reference(x, expert_ids, weights, w1, w2, limit)
+
+
+@optimizable({"reference": _routed_ffn_reference_alt})
 def routed_grouped_ffn(x, expert_ids, weights, w1, w2, limit: float = 0.0, max_slots: int | None = None):
     """Top-k routed SwiGLU experts on one rank.
 

@@ -130,3 +130,28 @@ def test_expert_parallel_moe_block_on_two_gloo_ranks():
     assert out.returncode == 0, out.stderr[-3000:]
     res = json.loads([l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
     assert len(res) == 24 and max(res.values()) < 1e-6
+
+
+def test_set_optimization_switches_registered_ops_to_their_reference_statement():
+    from steptronoss_b200.utils.optimizable import OPTIMIZABLE_REGISTER, set_optimization
+
+    name = moe.routed_grouped_ffn.__optimizable_name__
+    assert name.endswith("ops.moe.routed_grouped_ffn") and "reference" in OPTIMIZABLE_REGISTER[name]["alternatives"]
+    torch.manual_seed(0)
+    x, w1, w2 = torch.randn(16, 8), torch.randn(3, 12, 8) * 0.3, torch.randn(3, 8, 6) * 0.3
+    ids = torch.randint(0, 3, (16, 2))
+    wt = torch.rand(16, 2)
+    base = moe.routed_grouped_ffn(x, ids, wt, w1, w2)
+    calls = []
+    OPTIMIZABLE_REGISTER[name]["alternatives"]["spy"] = lambda *a, **k: calls.append(1) or moe.routed_grouped_ffn_reference(*a[:5])
+    try:
+        assert set_optimization(routed_grouped_ffn="spy") == {name: "spy"}        # short name
+        assert torch.allclose(moe.routed_grouped_ffn(x, ids, wt, w1, w2), base, atol=1e-5) and calls == [1]
+        assert set_optimization(routed_grouped_ffn="no-such-backend") == {}          # unknown: kept, with a warning
+        assert OPTIMIZABLE_REGISTER[name]["use_optimize"] == "spy"
+        assert set_optimization(default="reference")[name] == "reference"           # every op that has one
+        assert set_optimization(**{name: "native"}) == {name: "native"}             # full name, back to the kernel path
+        assert OPTIMIZABLE_REGISTER[name]["use_optimize"] is None
+    finally:
+        set_optimization(routed_grouped_ffn=None, fused_router=None)
+        OPTIMIZABLE_REGISTER[name]["alternatives"].pop("spy", None)
