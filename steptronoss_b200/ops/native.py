@@ -43,10 +43,15 @@ def load(build_if_missing: bool = True):
 
 
 def available() -> bool:
+    """True when the native library loads.  On a machine with a GPU a library that cannot be loaded is an error
+    (the kernels are the only path there: nothing falls back to PyTorch silently); without a GPU the answer is
+    simply False and callers take the PyTorch restatements."""
     try:
         load()
         return True
     except Exception:
+        if torch.cuda.is_available():
+            raise
         return False
 
 
