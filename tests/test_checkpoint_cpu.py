@@ -6,7 +6,7 @@ import torch
 from tests.tiny_exp import make_tiny_exp
 
 
-def _exp(tmp, iters, interval):
+def _exp(tmp, iters, interval, qwen=False):
     from steptronoss_b200.exp.checkpointing import CheckpointConfig
 
     e = make_tiny_exp(gbs=2, seq=128, iters=iters, layers=1, hidden=64, heads=2, kv_heads=1, head_dim=32, ffn=128, vocab=256)
@@ -16,6 +16,12 @@ def _exp(tmp, iters, interval):
     e.checkpoint_cfg.exp_name = "ckpt_test"
     e.checkpoint_cfg.save_interval = interval
     e.checkpoint_cfg.async_save = False
+    if qwen:  # the Qwen model class carries the HF <-> native weight mapping
+        from steptronoss_b200.models.qwen_dense import QwenModel
+
+        cfg = e.model_cfg
+        object.__setattr__(cfg, "build_model", lambda vpp_rank=None: QwenModel(cfg=cfg, layer_map=cfg.build_layer_map(),
+                                                                                vpp_rank=vpp_rank))
     return e
 
 
@@ -63,3 +69,33 @@ def test_checkpoint_config_reference_names_aliases_and_save_options():
     import pytest
     with pytest.raises(AssertionError):
         c.sanity_check()
+
+
+def test_hf_view_beside_the_checkpoint_starts_a_new_run_and_save_options_drop_parts(tmp_path):
+    """``save_safetensors`` writes ``it<N>/hf``; a second run that loads it (weights only) starts from those weights
+    with fresh optimizer state and fp32 masters that follow them; ``save_option`` leaves the optimizer file out."""
+    e = _exp(tmp_path / "a", 2, 2, qwen=True)
+    e.checkpoint_cfg.save_safetensors = True
+    e.checkpoint_cfg.save_option.all(but=["optimizer", "data"])
+    first = _train(e)
+    it = open(tmp_path / "a" / "ckpt_test" / "latest_ckpt").read().strip()
+    assert os.path.exists(os.path.join(it, "hf", "model.safetensors.index.json"))
+    assert os.path.exists(os.path.join(it, "TP00_PP000_DP000.pt"))
+    assert not os.path.exists(os.path.join(it, "TP00_PP000_DP000_OPT.pt")) and not os.path.exists(os.path.join(it, "data.pkl"))
+    trained = {k: v.detach().clone() for k, v in first.models[0].named_parameters()}
+
+    e2 = _exp(tmp_path / "b", 1, None, qwen=True)
+    e2.checkpoint_cfg.load_safetensors = os.path.join(it, "hf")
+    e2.checkpoint_cfg.load_option.none(but=["model"])
+    tr = e2.trainer_cfg.get_trainer_cls()(exp=e2)
+    tr.before_train()
+    assert tr.iteration == 0
+    for k, v in tr.models[0].named_parameters():
+        assert torch.equal(v, trained[k]), k
+    for shard in tr.grad_manager.shards.values():          # masters were refreshed from the loaded weights
+        assert torch.equal(shard.master, shard.bucket.param_buf[shard.lo:shard.hi].float())
+        assert float(shard.exp_avg.abs().sum()) == 0.0
+    before = {k: v.detach().clone() for k, v in tr.models[0].named_parameters()}
+    tr.train_step()
+    moved = max(float((v - before[k]).abs().max()) for k, v in tr.models[0].named_parameters())
+    assert 0 < moved < 0.05                               # one small step away from the loaded weights, not a jump back to the initialisation
