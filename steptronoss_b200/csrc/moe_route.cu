@@ -189,7 +189,7 @@ __global__ void moe_scatter_kernel(const uint4* __restrict__ x, const int* __res
 
 // out[t] = sum_k w[t,k] * y[dest[t,k]]  (w == nullptr: plain sum, the backward of the scatter)
 template <int KT>
-__global__ void moe_gather_kernel(const uint4* __restrict__ y, const long long* __restrict__ dest,
+__global__ void __launch_bounds__(256, KT <= 8 ? 2 : 1) moe_gather_kernel(const uint4* __restrict__ y, const long long* __restrict__ dest,
                                   const float* __restrict__ w, int T, int K, int h16, uint4* __restrict__ out) {
   const int wpb = blockDim.x >> 5, lane = threadIdx.x & 31;
   for (int t = blockIdx.x * wpb + (threadIdx.x >> 5); t < T; t += gridDim.x * wpb) {
@@ -217,7 +217,7 @@ __global__ void moe_gather_kernel(const uint4* __restrict__ y, const long long* 
 
 // warps [0, T): token t -> gy rows of its slots and gw[t, :]; warps [T, T + rows): zero the padding rows of gy
 template <int KT>
-__global__ void moe_gather_bwd_kernel(const uint4* __restrict__ g, const uint4* __restrict__ y,
+__global__ void __launch_bounds__(256, KT <= 8 ? 2 : 1) moe_gather_bwd_kernel(const uint4* __restrict__ g, const uint4* __restrict__ y,
                                       const long long* __restrict__ dest, const float* __restrict__ w,
                                       const int* __restrict__ slot_of_row, const int* __restrict__ offsets, int E,
                                       int T, int K, int h16, int rows, uint4* __restrict__ gy,
