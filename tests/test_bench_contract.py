@@ -1,6 +1,7 @@
 """bench.py: command-line defaults, layout parsing, the FLOP model, the clock-sample summary, the reference arm's
 refusal line (what the driver reads must keep its shape)."""
 import json
+import os
 import subprocess
 import sys
 
@@ -53,3 +54,15 @@ def test_reference_arm_says_why_it_cannot_run_the_moe_model():
     assert out.returncode == 0
     line = json.loads(out.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and "unavailable" in line and "\n" not in line["unavailable"]
+
+
+def test_run_all_lists_single_and_multi_rank_benchmarks(tmp_path):
+    from benchmarks import run_all
+
+    one = run_all.commands(str(tmp_path), 1, set())
+    assert [n for n, _ in one] == ["gemm", "attention", "moe", "moe_layer"]            # the ZeRO step needs two GPUs
+    eight = dict(run_all.commands(str(tmp_path), 8, {"attention"}))
+    assert set(eight) == {"gemm", "moe", "moe_layer", "zero"} and "--nproc-per-node=8" in eight["zero"]
+    for cmd in list(dict(one).values()) + list(eight.values()):
+        script = next(c for c in cmd if c.endswith(".py"))
+        assert os.path.exists(script)
