@@ -200,3 +200,55 @@ def test_capture_trace_writes_forward_and_backward_traces(tmp_path):
         events = json.load(open(f))["traceEvents"]
         assert len(events) > 0
     assert any(e.get("name") == "FW" for e in json.load(open(fw))["traceEvents"])
+
+
+def test_misc_helpers(tmp_path, capsys):
+    from steptronoss_b200.utils import misc
+
+    assert misc.format_layermap({0: {0: {0: {"recompute": False}, 1: {"recompute": False}, 2: {"recompute": True}}},
+                                 1: {0: {3: {"recompute": True}}}}) == (
+        "pp0/vp0: 0-1: {recompute=False}; 2: {recompute=True}\npp1/vp0: 3: {recompute=True}")
+    assert misc.get_path_tree_repr(["a/b/c.pt", "a/b/d.pt", "a/e.txt", "f"]).splitlines() == [
+        "|-- a", "|   |-- b", "|   |   |-- c.pt", "|   |   +-- d.pt", "|   +-- e.txt", "+-- f"]
+    assert misc.get_path_tree_repr([]) == ""
+    recs = [{"a": 1}, {"b": "ü"}]
+    assert misc.safe_dump_jsonl(recs, str(tmp_path / "x.jsonl")) and misc.load_jsonl(str(tmp_path / "x.jsonl")) == recs
+    assert misc.safe_dump_jsonl(recs, str(tmp_path / "no" / "dir.jsonl")) is False            # logged, not raised
+    assert misc.safe_dump_msgpack({"k": [1, 2, b"x"]}, str(tmp_path / "x.mp")) and misc.load_msgpack(str(tmp_path / "x.mp")) == {"k": [1, 2, b"x"]}
+    (tmp_path / "src").mkdir()
+    misc.check_and_link(str(tmp_path / "src"), str(tmp_path / "ln"))
+    misc.check_and_link(str(tmp_path / "src") + "/", str(tmp_path / "ln"))                       # same target: fine
+    with pytest.raises(OSError):
+        misc.check_and_link(str(tmp_path / "other"), str(tmp_path / "ln"))
+    d = misc.RepeatedDict()
+    d["k"] = 1
+    d["k"] = 2
+    d.update({"k": 3, "j": 9}, repeat=2)
+    assert len(d) == 6 and d["k"] == 1 and d.pop("k") == 1 and d.pop("k") == 2 and d.pop("missing") is None
+    assert [d.pop("j"), d.pop("j"), d.pop("j")] == [9, 9, None] and "j" not in d
+    d2 = misc.RepeatedDict()
+    d2.load_state_dict(d.state_dict())
+    assert len(d2) == 2 and d2["k"] == 3
+    items = [{"t": torch.ones(2)}, {"t": torch.zeros(2)}]
+    seen = [x["t"].sum().item() for x in misc.moving_iter(items, active="cpu", default="cpu")]
+    assert seen == [2.0, 0.0]
+    assert misc.cos_sim(torch.tensor([1.0, 0.0]), torch.tensor([2.0, 0.0])) == pytest.approx(1.0)
+    assert "MemReport" in misc.get_mem_brief("x")
+    misc.force_clear_mem()
+    lin = torch.nn.Linear(3, 2, bias=False)
+    with torch.no_grad():
+        lin.weight.fill_(2.0)
+    assert misc.calc_params_l2_norm([lin, lin]) == pytest.approx((6 * 4.0) ** 0.5)              # shared parameters once
+    calls = []
+
+    @misc.deprecated("use g")
+    def f(x):
+        calls.append(x)
+        return x
+
+    assert f(1) == 1 and f(2) == 2 and calls == [1, 2]
+    bar = misc.GroupedProgressBar({"a": 2, "b": 1})
+    bar.update("a")
+    bar.update("b")
+    assert bar.total_bar.n == 2 and bar.group_bars["a"].n == 1
+    bar.close()
