@@ -252,3 +252,51 @@ def test_misc_helpers(tmp_path, capsys):
     bar.update("b")
     assert bar.total_bar.n == 2 and bar.group_bars["a"].n == 1
     bar.close()
+
+
+def test_patch_manager_replaces_wraps_and_restores():
+    import json as json_mod
+
+    import steptronoss_b200.utils.general as general
+    from steptronoss_b200.utils.patch_utils import PatchesManager, get_func_name
+
+    orig = general.safediv
+    assert get_func_name(orig) == "steptronoss_b200.utils.general.safediv"
+    PatchesManager.remove_patches()
+    PatchesManager.register_patch("steptronoss_b200.utils.general.safediv", lambda n, d: -1)
+
+    def doubling_wrapper(fn):
+        return lambda *a, **k: 2 * fn(*a, **k)
+
+    PatchesManager.register_patch(orig, doubling_wrapper)                                   # by function object
+    with pytest.raises(RuntimeError):
+        PatchesManager.register_patch("steptronoss_b200.utils.general.safediv", lambda n, d: 0)
+    PatchesManager.register_patch("no.such.package.fn", None, create_dummy=True)
+    PatchesManager.register_patch("json.brand_new_function", lambda: "new", create_dummy=True)
+    PatchesManager.apply_patches()
+    try:
+        assert general.safediv(6, 3) == -2
+        import importlib
+
+        assert json_mod.brand_new_function() == "new"
+        with pytest.raises(RuntimeError, match="does not exist"):
+            importlib.import_module("no.such.package").fn()
+    finally:
+        PatchesManager.remove_patches()
+    assert general.safediv is orig and general.safediv(6, 3) == 2 and not hasattr(json_mod, "brand_new_function")
+    with pytest.raises((ModuleNotFoundError, AttributeError)):
+        PatchesManager.register_patch("definitely.not.there.fn", lambda: 0).apply()
+    PatchesManager.remove_patches()
+
+
+def test_param_groups_by_multipliers_and_tags():
+    from steptronoss_b200.optim.utils import advanced_get_param_groups
+
+    m = torch.nn.Sequential(torch.nn.Linear(4, 4), torch.nn.LayerNorm(4), torch.nn.Linear(4, 2, bias=False))
+    m[2].weight._lr_scale = 0.1
+    m[0].weight.requires_grad_(False)
+    groups = advanced_get_param_groups(m, is_matrix=lambda n, p: p.dim() == 2)
+    keyed = {(g["wd_mult"], g["lr_mult"], g["is_matrix"]): len(g["params"]) for g in groups}
+    assert keyed == {(0.0, 1.0, False): 3, (1.0, 0.1, True): 1}      # bias + two norm vectors; the scaled head; frozen weight left out
+    opt = torch.optim.AdamW([{**g, "weight_decay": 0.1 * g["wd_mult"], "lr": 1e-3 * g["lr_mult"]} for g in groups])
+    assert len(opt.param_groups) == 2
