@@ -183,3 +183,16 @@ def test_multimodal_inputs():
         build_image_for_insert([(torch.zeros(1), 9)], patch_start_id=1, image_start_id=2)
     with pytest.raises(ValueError):
         compute_rope_args([], 14, to_cuda=False)
+
+
+def test_dialog_types_and_validation():
+    from steptronoss_b200.data.types import MessageContentType, Role, validate_dialog
+
+    assert Role.ASSISTANT == "assistant" and MessageContentType.TEXT.value == "text"
+    good = {"conversations": [{"role": "user", "content": "hi"},
+                              {"role": "assistant", "content": [{"type": "text", "value": "yo", "loss_mask": 1}], "loss_mask": 1}]}
+    assert validate_dialog(good) == []
+    bad = {"conversations": [{"role": "robot", "content": 3}, {"role": "user", "content": [{"type": "video", "value": "x"}], "loss_mask": 2}]}
+    probs = validate_dialog(bad)
+    assert len(probs) == 5 and any("robot" in p for p in probs) and any("no assistant turn" in p for p in probs)
+    assert validate_dialog({}) == ["'conversations' must be a non-empty list"]
