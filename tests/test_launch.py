@@ -91,3 +91,39 @@ def test_smartrun_rendezvous_assigns_ranks(tmp_path, monkeypatch):
     cmd = torchrun_command(["exp.py", "a=1"], 2, rank, master, 12345, 8)
     assert cmd[1:3] == ["-m", "torch.distributed.run"] and cmd[-2:] == ["exp.py", "a=1"] and "--node-rank" in cmd
     comm_utils.reset_exp_store()
+
+
+def test_submitter_template_resolves_tasks_and_stops_helpers_when_the_critical_task_ends(tmp_path, monkeypatch):
+    """A subclass whose ``launch_task`` starts local processes: both tasks get their command, environment and
+    rendezvous directory; the helper (which would sleep for a minute) is stopped once the trainer has ended."""
+    from steptronoss_b200.launch.example_submitter import Submitter
+
+    monkeypatch.delenv("EXP_ID", raising=False)
+    monkeypatch.setenv("OUT_DIR", str(tmp_path))
+    seen = {}
+
+    class Local(Submitter):
+        poll_s = 0.1
+        meet_dir = str(tmp_path / "meet")
+
+        def launch_task(self, sub):
+            seen[sub.task.name] = sub
+            env = os.environ | sub.task.envs | {"PYTHONPATH": os.getcwd()}
+            return subprocess.Popen(sub.task.command, shell=True, env=env)
+
+    with pytest.raises(NotImplementedError):
+        Submitter(_write_exp(tmp_path), ["marker=zzz"], interactive=False).run()
+    monkeypatch.delenv("EXP_ID", raising=False)
+    subs = Local(_write_exp(tmp_path), ["marker=zzz"], image="img:1", interactive=False).run()
+    assert set(seen) == {"trainer", "helper"}
+    t, h = seen["trainer"], seen["helper"]
+    assert t.task.is_critical and not h.task.is_critical and t.image == "img:1"
+    assert t.task.envs["ROLE"] == "trainer" and t.task.envs["COMMON"] == "1" and t.task.envs["NNODES"] == "1"
+    exp_id = t.task.envs["EXP_ID"].split("/")[0]
+    assert t.task.envs["EXP_ID"] == f"{exp_id}/trainer" and h.task.envs["EXP_ID"] == f"{exp_id}/helper"
+    assert t.task.envs["STEPTRON_MEET_DIR"] == os.path.join(str(tmp_path / "meet"), exp_id, "trainer")
+    assert "marker=zzz" in t.task.command
+    assert open(tmp_path / "trainer.txt").read().split()[0] == "zzz"
+    for s in subs:
+        s.handle.wait(timeout=10)
+        assert s.handle.poll() is not None
