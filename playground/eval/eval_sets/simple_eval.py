@@ -69,6 +69,9 @@ class SimpleBenchmarksEvalConfig(BenchmarkEvalConfig):
     max_model_len: int = Ref("..vllm_cfg.max_seq_len", 65536)
     rerun_level: str | None = None
     """None: use every cached answer; "error": generate failed requests again; "all": ignore the cache"""
+    benchmark_options: dict = {}
+    """extra constructor arguments per benchmark name, e.g. ``{"IFBENCH": {"sampling_params": {"temperature": 1.0}}}``
+    (``sampling_params`` may be given as a dict of :class:`SamplingParams` fields)"""
 
     BENCHMARKS = {"AIME2025": (AIME25Benchmark, "test.jsonl"), "HMMT2025": (HMMT25Benchmark, "test.jsonl"),
                   "GPQA_DIAMOND": (GPQADiamondBenchmark, "test.jsonl"), "MMLU_PRO": (MMLUProBenchmark, "test.jsonl"),
@@ -109,8 +112,11 @@ class SimpleBenchmarksEvalConfig(BenchmarkEvalConfig):
                     raise FileNotFoundError(f"benchmark {name} selected but {path} does not exist")
                 logger.warning(f"benchmark {name} skipped: {path} does not exist")
                 continue
+            extra = dict(self.benchmark_options.get(name, {}))
+            if isinstance(extra.get("sampling_params"), dict):
+                extra["sampling_params"] = SamplingParams(**extra["sampling_params"])
             out.append(cls(path, tok, self.sample_per_prompt.get(name, 1), self.down_sample_to, self.shuffle_prompts,
-                           dict(self.chat_template_args)))
+                           dict(self.chat_template_args), **extra))
         if not out:
             raise FileNotFoundError(f"no benchmark data under {self.datasets_dir}")
         return out

@@ -15,6 +15,7 @@ EXPERIMENTS = [
     ("playground.eval.qwen3.qwen3_eval_simple_benchmarks", "Exp"),
     ("playground.eval.qwen3.qwen3_eval_simple_benchmarks", "Exp1p7B"),
     ("playground.eval.step3p5.step3p5_eval_simple_benchmarks", "Exp"),
+    ("playground.eval.step3v.step3v_eval_simple_benchmarks", "Exp"),
     ("playground.sft.step3v.step3v_10b_sft_tp8_caption_smoke", "Exp"),
 ]
 
@@ -139,6 +140,31 @@ def test_simple_eval_set_runs_and_resumes_from_its_cache(tmp_path, monkeypatch):
     cfg.selected_datasets = "NOPE"
     with pytest.raises(ValueError):
         cfg.build_benchmarks()
+
+
+def test_step3v_eval_samples_ifbench_four_times_at_temperature_one(tmp_path):
+    from playground.eval.step3v.step3v_eval_simple_benchmarks import Exp
+    from steptronoss_b200.exp.base_exp import TokenizerConfig
+
+    (tmp_path / "IFBENCH").mkdir()
+    (tmp_path / "IFBENCH" / "IFBench_test.jsonl").write_text(json.dumps(
+        {"key": 1, "prompt": "no spaces please", "instruction_id_list": ["format:no_whitespace"], "kwargs": [{}]}))
+
+    class Tok(TokenizerConfig):
+        def build_tokenizer(self):
+            return _Tok()
+
+    exp = Exp()
+    assert exp.resource_cfg.find_leaf_task_specs()["vllm"]["replica"] == 1 and exp.resource_cfg.gpu == 1
+    assert exp.vllm_cfg.vllm_enforce_eager and exp.eval_cfg.tokenizer_cfg.tokenizer_path == exp.vllm_cfg.model_config_path
+    exp._allow_set_new_attr = True
+    exp.eval_cfg.tokenizer_cfg = Tok
+    exp.eval_cfg.datasets_dir = str(tmp_path)
+    (bench,) = exp.eval_cfg.build_benchmarks()
+    cases = bench.get_cases()
+    assert len(cases) == 4 and sorted(c.evaluation.run_index for c in cases) == [0, 1, 2, 3]
+    sp = cases[0].prompt.sampling_params
+    assert (sp.temperature, sp.top_p, sp.top_k) == (1.0, 1.0, 0)
 
 
 def test_image_caption_data_feeds_the_vision_language_model(tmp_path):
