@@ -137,3 +137,71 @@ class Stopwatch:
     def __exit__(self, *a):
         self.dt = time.perf_counter() - self.t0
         return False
+
+
+def text_chart(values, height: int = 18, width: int = 100, fmt: str = "{:.3e}") -> str:
+    """A line chart drawn with characters: one column per (down-sampled) value, the y axis labelled on the left."""
+    vals = [float(v) for v in values if v == v]
+    if not vals:
+        return "(no values)"
+    if len(vals) > width:                      # mean of equal slices, so that spikes do not vanish entirely
+        edges = [round(i * len(vals) / width) for i in range(width + 1)]
+        vals = [sum(vals[a:b]) / (b - a) for a, b in zip(edges[:-1], edges[1:]) if b > a]
+    lo, hi = min(vals), max(vals)
+    span = (hi - lo) or 1.0
+    rows = max(int(height), 2)
+    level = [round((v - lo) / span * (rows - 1)) for v in vals]
+    grid = [[" "] * len(vals) for _ in range(rows)]
+    for x, y in enumerate(level):
+        if x and level[x - 1] != y:            # join to the previous column
+            a, b = sorted((level[x - 1], y))
+            for yy in range(a + 1, b):
+                grid[yy][x] = "|"
+        grid[y][x] = "*"
+    labels = [fmt.format(lo + span * r / (rows - 1)) for r in range(rows)]
+    pad = max(len(s) for s in labels)
+    return "\n".join(f"{labels[r].rjust(pad)} |{''.join(grid[r])}" for r in reversed(range(rows)))
+
+
+class TBRecord(dict):
+    """The scalars of a TensorBoard run directory, read back: ``"train/loss" in rec``, ``rec["train/loss"]`` (a list
+    of events with ``.step`` / ``.value`` / ``.wall_time``, re-read on every access so a live run can be followed)
+    and ``rec.asciichart(key)`` for a look at a curve in a terminal (reference
+    ``steptronoss/utils/dev_utils.py:205-240``)."""
+
+    def __init__(self, path: str = ""):
+        super().__init__()
+        from tensorboard.backend.event_processing.event_accumulator import EventAccumulator
+
+        self.ea = EventAccumulator(path, size_guidance={"scalars": 0})
+        self.refresh()
+
+    def refresh(self):
+        self.ea.Reload()
+        self._keys = list(self.ea.Tags()["scalars"])
+
+    def keys(self):
+        return self._keys
+
+    def __iter__(self):
+        return iter(self._keys)
+
+    def __len__(self):
+        return len(self._keys)
+
+    def __contains__(self, key) -> bool:
+        return key in self._keys
+
+    def __getitem__(self, key):
+        self.refresh()
+        return self.ea.Scalars(key)
+
+    def values(self, key) -> list:
+        return [e.value for e in self[key]]
+
+    def asciichart(self, scalar_key: str, height: int = 18):
+        class _Shown(str):
+            def __repr__(self):
+                return str(self)
+
+        return _Shown(text_chart(self.values(scalar_key), height))

@@ -300,3 +300,25 @@ def test_param_groups_by_multipliers_and_tags():
     assert keyed == {(0.0, 1.0, False): 3, (1.0, 0.1, True): 1}      # bias + two norm vectors; the scaled head; frozen weight left out
     opt = torch.optim.AdamW([{**g, "weight_decay": 0.1 * g["wd_mult"], "lr": 1e-3 * g["lr_mult"]} for g in groups])
     assert len(opt.param_groups) == 2
+
+
+def test_tb_record_reads_back_what_the_step_writer_wrote(tmp_path):
+    from steptronoss_b200.utils.dev_utils import TBRecord, text_chart
+    from steptronoss_b200.utils.logger import StepWriter
+
+    w = StepWriter(str(tmp_path / "run"))
+    for i, v in enumerate([4.0, 2.0, 1.0, 0.5]):
+        w.add_scalar("train/loss", v, i)
+    w.flush()
+    w.close()
+    rec = TBRecord(str(tmp_path / "run"))
+    assert "train/loss" in rec and "nope" not in rec and list(rec.keys()) == ["train/loss"]
+    ev = rec["train/loss"]
+    assert [e.step for e in ev] == [0, 1, 2, 3] and rec.values("train/loss") == [4.0, 2.0, 1.0, 0.5]
+    chart = rec.asciichart("train/loss", height=4)
+    lines = chart.split("\n")
+    assert len(lines) == 4 and lines[0].lstrip().startswith("4.000e+00") and lines[-1].lstrip().startswith("5.000e-01")
+    assert lines[0].split("|", 1)[1][0] == "*" and lines[-1].rstrip().endswith("*") and repr(chart) == str(chart)
+    long = text_chart(range(1000), height=5, width=50)
+    assert all(len(line.split("|", 1)[1]) == 50 for line in long.split("\n"))
+    assert text_chart([]) == "(no values)" and "*" in text_chart([1.0, 1.0])
