@@ -54,13 +54,17 @@ class TrainerPromptStream(Nextable):
 
 
 def get_normalizer(x: torch.Tensor):
-    """Mean and std of ``x`` over the DP group."""
+    """Mean and std of ``x`` over the DP group; a NaN/Inf in any rank's values is an error (a silent NaN here would
+    poison every advantage of the batch)."""
     stats = torch.stack([x.sum(), (x * x).sum(), torch.as_tensor(float(x.numel()), device=x.device)]).double()
     group = PM.group_of("DP")
     if group is not None:
         torch.distributed.all_reduce(stats, group=group)
     mean = stats[0] / stats[2]
     var = (stats[1] / stats[2] - mean * mean).clamp_min(0)
+    if not bool(torch.isfinite(stats[:2]).all()):
+        raise ValueError(f"get_normalizer: non-finite result (mean={float(mean)}, std={float(var.sqrt())}); "
+                         f"the input holds NaN or Inf")
     return mean.float(), var.sqrt().float()
 
 

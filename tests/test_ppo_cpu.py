@@ -161,3 +161,18 @@ def test_ppo_trains_and_checkpoints(tmp_path, use_critic):
     assert os.path.isdir(os.path.join(it_dir, "actor")) and os.path.exists(os.path.join(it_dir, "data.pkl"))
     assert os.path.isdir(os.path.join(it_dir, "critic")) == use_critic
     assert open(os.path.join(exp.checkpoint_cfg.save_path, "latest_ckpt")).read().strip() == it_dir
+
+
+def test_get_normalizer_values_and_non_finite_inputs():
+    import pytest
+    import torch
+
+    from steptronoss_b200.trainers.ppo_trainer import get_normalizer
+
+    m, s = get_normalizer(torch.tensor([1.0, 2.0, 3.0, 4.0, 5.0]))
+    assert torch.isclose(m, torch.tensor(3.0)) and torch.isclose(s, torch.tensor(2.0).sqrt())
+    m, s = get_normalizer(torch.full((3,), 5.0))
+    assert float(m) == 5.0 and float(s) == 0.0
+    for bad in (float("nan"), float("inf")):
+        with pytest.raises(ValueError, match="non-finite"):
+            get_normalizer(torch.tensor([1.0, bad, 3.0]))
