@@ -14,6 +14,10 @@ from ..parallel.state import PM
 
 
 class MegatronModule(nn.Module):
+    need_mtp_sync: bool = False
+    """True on a chunk that holds a copy of the token embedding shared with another pipeline stage
+    (``parallel/embedding_sync.py``); such a chunk also defines ``shared_embedding_parameters()``."""
+
     def __init__(self, vpp_rank: int | None = None):
         super().__init__()
         self.vpp_rank = vpp_rank if vpp_rank is not None else PM.get_vpp_rank()
@@ -39,6 +43,9 @@ class MegatronModule(nn.Module):
 
     def set_input_tensor(self, t) -> None:
         self.input_tensor = t
+
+    def shared_embedding_parameters(self) -> list:
+        raise NotImplementedError(f"{type(self).__name__} sets need_mtp_sync but names no shared embedding parameters")
 
     # ---------------------------------------------------------------- forward skeleton
     def forward_head(self, **data):
