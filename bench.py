@@ -47,6 +47,9 @@ def parse():
     ap.add_argument("--seqs-per-gpu", type=int, default=None,
                     help="sequences per GPU per step (global batch = this x N); default 8 (dense) / 32 (MoE)")
     ap.add_argument("--seq-len", type=int, default=None, help="default 8192 (dense) / 4096 (MoE)")
+    ap.add_argument("--seqs-per-micro-batch", type=int, default=1,
+                    help="sequences packed into one forward/backward pass (as separate documents: attention, positions "
+                         "and loss stay per sequence); the global batch and the tokens of a step do not change")
     ap.add_argument("--recompute", default="auto", help="auto | none | full | comma list of block parts")
     ap.add_argument("--recompute-layers", type=int, default=None,
                     help="recompute only the first N layers (default: 4 of 36 on one GPU, all otherwise)")
@@ -57,6 +60,8 @@ def parse():
         a.seqs_per_gpu = 32 if moe else 8
     if a.seq_len is None:
         a.seq_len = 4096 if moe else 8192
+    if a.seqs_per_micro_batch < 1 or a.seqs_per_gpu % a.seqs_per_micro_batch:
+        ap.error("--seqs-per-micro-batch must divide the sequences per GPU")
     return a
 
 
@@ -167,8 +172,9 @@ def run_ours(args):
     pc.context_parallel_size = par["cp"]
     exp.model_cfg.tp_cfg.sequence_parallel = par["tp"] > 1
     tc = exp.trainer_cfg
-    tc.global_seq_length = args.seq_len
-    tc.global_batch_size = args.seqs_per_gpu * world
+    # a micro-batch of M sequences is one packed row of M x seq_len tokens whose documents are at most seq_len long
+    tc.global_seq_length = args.seq_len * args.seqs_per_micro_batch
+    tc.global_batch_size = args.seqs_per_gpu * world // args.seqs_per_micro_batch
     tc.train_iters = 10**9
     tc.writer_backend = []
     tc.log_interval = 10**9
@@ -301,8 +307,8 @@ def run_ours(args):
         "data": ("synthetic sequences of one document each (uniform token ids), random N(0,0.02) init" if moe else
                  "synthetic packed documents (lengths U[256,8192], uniform token ids), random N(0,0.02) init"),
         "mfu_of_measured_sustained_bf16": value * fpt / (peak * world),
-        "config": {"model": "Qwen3-30B-A3B-shape MoE" if moe else "Qwen3-8B", "layers": mc.num_layers, "global_batch": tc.global_batch_size,
-                   "seq_len": tc.global_seq_length, "micro_batch": 1, "parallelism": par_text,
+        "config": {"model": "Qwen3-30B-A3B-shape MoE" if moe else "Qwen3-8B", "layers": mc.num_layers, "global_batch": args.seqs_per_gpu * world,
+                   "seq_len": args.seq_len, "micro_batch": args.seqs_per_micro_batch, "parallelism": par_text,
                    "optimizer": "Adam fp32 master+state, ZeRO-1", "recompute": rec,
                    **({"moe_dispatcher": args.dispatcher, "moe_capacity_factor": args.moe_capacity_factor or None} if moe else {}),
                    "l2": "inputs larger than L2 (each step streams > 100 GB)"},

@@ -17,6 +17,12 @@ def test_defaults_follow_the_model(monkeypatch):
     monkeypatch.setattr(sys, "argv", ["bench.py", "--model", "qwen3_30b_a3b", "--gpus", "8"])
     a = bench.parse()
     assert (a.seqs_per_gpu, a.seq_len, a.dispatcher, a.moe_capacity_factor) == (32, 4096, "peer", 2.0)   # 256 x 4096 at 8 GPUs
+    assert a.seqs_per_micro_batch == 1
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--model", "qwen3_30b_a3b", "--seqs-per-micro-batch", "4"])
+    assert bench.parse().seqs_per_micro_batch == 4
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--seqs-per-micro-batch", "3"])       # 8 sequences per GPU
+    with pytest.raises(SystemExit):
+        bench.parse()
 
 
 def test_layouts():
