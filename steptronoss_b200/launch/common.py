@@ -63,5 +63,6 @@ def expand_tasks(exp, exp_path: str, extra_args: list, exp_id: str | None = None
     for name, cfg in rsc.extract().items():
         tasks.append(Task(name, cfg.command.format(TORCHRUN=SMARTRUN, COMMAND=command),
                           {k: str(v) for k, v in (cfg.envs | {"NNODES": str(cfg.replica)}).items()},
-                          int(cfg.replica), cfg.node_type, bool(cfg.is_critical)))
+                          int(cfg.replica), cfg.node_type, bool(cfg.is_critical),
+                          extra={"image": cfg.image, "mounts": list(cfg.mounts), "gpu": int(cfg.gpu)}))
     return exp_id, tasks

@@ -19,10 +19,9 @@ import os
 import sys
 import time
 from dataclasses import dataclass, field
-from uuid import uuid4
 
 from ..config.mock_imports import mock_imports
-from .common import SMARTRUN, Task, load_exp
+from .common import Task, expand_tasks, load_exp
 
 # packages an experiment file may import that a submit host often lacks
 HEAVY_PACKAGES = ("torch", "transformers", "vllm", "flash_attn", "safetensors", "tensorboardX", "wandb")
@@ -83,19 +82,13 @@ class Submitter:
 
     def resolve(self, exp, exp_id: str | None = None) -> list:
         """One :class:`Submission` per task of the experiment."""
-        exp_id = exp_id or os.environ.get("EXP_ID") or uuid4().hex[:5]
-        os.environ["EXP_ID"] = exp_id            # ResourceConfig.extract derives "<id>/<task>" from it
-        rsc = exp.resource_cfg
-        command = " ".join([self.exp_path, *self.exp_args])
+        exp_id, tasks = expand_tasks(exp, self.exp_path, self.exp_args, exp_id)
         out = []
-        for name, cfg in rsc.extract().items():
-            envs = {k: str(v) for k, v in cfg.envs.items()}
-            envs["NNODES"] = str(cfg.replica)
+        for task in tasks:
             if self.meet_dir:
-                envs["STEPTRON_MEET_DIR"] = os.path.join(self.meet_dir, exp_id, name)
-            task = Task(name, cfg.command.format(TORCHRUN=SMARTRUN, COMMAND=command), envs, int(cfg.replica),
-                        cfg.node_type, bool(cfg.is_critical))
-            out.append(Submission(task, cfg.image or self.image, list(cfg.mounts), int(cfg.gpu), self.code_dir))
+                task.envs["STEPTRON_MEET_DIR"] = os.path.join(self.meet_dir, exp_id, task.name)
+            out.append(Submission(task, task.extra["image"] or self.image, task.extra["mounts"], task.extra["gpu"],
+                                  self.code_dir))
         return out
 
     def spawn_tasks(self, subs: list) -> list:
