@@ -17,7 +17,6 @@ from __future__ import annotations
 import importlib.util
 import json
 import os
-import statistics
 import sys
 import time
 import traceback
@@ -79,7 +78,6 @@ def _run(args) -> None:
 
     from steptronoss.exp.base_exp import DataConfig
     from steptronoss.core.trainers.lm_trainer import DecoderPretrainTrainer
-    from steptronoss.utils.optimizable import set_optimization
 
     sft_base = _load_file(os.path.join(REF, "playground/sft/qwen3/qwen3_sft_base.py"), "_ref_qwen3_sft_base")
     q8 = _load_file(os.path.join(REF, "playground/pretrain/qwen3/qwen3_8b.py"), "_ref_qwen3_8b")

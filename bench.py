@@ -140,7 +140,6 @@ def model_flops_per_token(layers, hidden, heads, kv_heads, head_dim, ffn, vocab,
 
 
 def run_ours(args):
-    import numpy as np
     import torch
     import torch.distributed as dist
 
@@ -151,7 +150,6 @@ def run_ours(args):
         from playground.pretrain.qwen3.qwen3_8b import Exp
     from steptronoss_b200.ops import launch_count
     from steptronoss_b200.ops import native
-    from steptronoss_b200.parallel.state import PM
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

@@ -138,11 +138,8 @@ def test_async_accelerated_stream_is_the_serial_stream_and_resumes():
 def test_sft_pack_contract_and_training_on_packed_chat_samples():
     import torch
 
-    from steptronoss_b200.exp.base_exp import GradientManagerConfig, ProfilerConfig
     from steptronoss_b200.exp.lr_schedulers import ConstantSchedulerConfig
-    from steptronoss_b200.exp.ntp import NTPTrainerConfig, PretrainMetricConfig
     from steptronoss_b200.exp.sft import SFTDataConfig, SFTDatasetsConfig, SFTExp
-    from steptronoss_b200.models.decoder_model import DecoderLLMConfig
 
     class Chat:
         """prompt tokens masked out, answer = prompt reversed (learnable)"""

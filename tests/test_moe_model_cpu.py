@@ -3,7 +3,6 @@ single-process block output and gradients."""
 import os
 import socket
 
-import pytest
 import torch
 import torch.multiprocessing as mp
 

@@ -1,7 +1,6 @@
 """RoPE tables and rotation (fp32 caches, partial rotary, position ids, YaRN), metric reductions, indexed-bin /
 compiled / chat-JSON datasets with the chat template, multimodal input helpers."""
 import json
-import math
 import os
 
 import numpy as np
