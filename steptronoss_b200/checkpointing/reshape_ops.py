@@ -12,6 +12,7 @@ gate]`` and ``w1`` rows are ``[gate | up]``.
 """
 from __future__ import annotations
 
+import contextlib
 import fnmatch
 import re
 
@@ -87,7 +88,10 @@ class Inverse(ReshapeOp):
 
 
 class Rename(ReshapeOp):
-    """``"dst: src"`` (or a dict ``{dst: src}``): forward renames src -> dst, backward dst -> src."""
+    """``"dst: src"`` (or a dict ``{dst: src}``): forward renames src -> dst, backward dst -> src.  Both sides may
+    hold ``*`` wildcards (``"encoder.*: *"``, ``"a.*.fc1.*: a.*.c_fc.*"``): what the wildcards of one side capture
+    fills the wildcards of the other, in order.  A piece of one tensor under a rule without wildcards takes the
+    rule's name whatever it was called before (the product of a merge)."""
 
     def __init__(self, mapping):
         if isinstance(mapping, str):
@@ -95,14 +99,68 @@ class Rename(ReshapeOp):
             mapping = {dst: src}
         self.mapping = dict(mapping)
 
+    @staticmethod
+    def _apply(piece: dict, pairs: list) -> dict:
+        """``pairs``: (from, to) names or globs; the first pair that matches a key renames it."""
+        from ..utils.weight_loader import fill_target, key_pattern
+
+        globs = [(key_pattern(a), b) for a, b in pairs if "*" in a]
+        exact = {a: b for a, b in pairs if "*" not in a}
+        out = {}
+        for k, v in piece.items():
+            if k in exact:
+                out[exact[k]] = v
+                continue
+            for pat, target in globs:
+                m = pat.match(k)
+                if m:
+                    out[fill_target(m, target)] = v
+                    break
+            else:
+                out[k] = v
+        return out
+
     def forward(self, piece):
-        inv = {v: k for k, v in self.mapping.items()}
-        if len(piece) == 1 and len(inv) == 1 and next(iter(piece)) not in inv:
-            return {next(iter(self.mapping)): next(iter(piece.values()))}
-        return {inv.get(k, k): v for k, v in piece.items()}
+        if len(piece) == 1 and len(self.mapping) == 1:
+            (dst, src), (k, v) = next(iter(self.mapping.items())), next(iter(piece.items()))
+            if "*" not in dst and "*" not in src and k != src:
+                return {dst: v}
+        return self._apply(piece, [(src, dst) for dst, src in self.mapping.items()])
 
     def backward(self, piece):
-        return {self.mapping.get(k, k): v for k, v in piece.items()}
+        return self._apply(piece, list(self.mapping.items()))
+
+
+class Prefixed(ReshapeOp):
+    """A sub-module's own mapping inside a larger one: forward takes HF names below ``hf_prefix``, strips it, applies
+    ``hf_names`` (pairs of HF spelling -> the spelling ``inner`` expects, as globs), runs ``inner`` and puts
+    ``native_prefix`` in front; backward is the way back."""
+
+    def __init__(self, inner: ReshapeOp, hf_prefix: str, native_prefix: str, hf_names: list | None = None,
+                 mesh=None):
+        self.inner, self.hf_prefix, self.native_prefix = inner, hf_prefix, native_prefix
+        self.hf_names = list(hf_names or [])
+        self.mesh = mesh
+        """ParallelConfig of the sub-module when it lives on a mesh of its own (its TP size decides the splits)"""
+
+    def _on_mesh(self):
+        return PM.use_mesh(self.mesh) if self.mesh is not None else contextlib.nullcontext()
+
+    def forward(self, piece):
+        n = len(self.hf_prefix)
+        sub = {k[n:]: v for k, v in piece.items() if k.startswith(self.hf_prefix)}
+        sub = Rename._apply(sub, self.hf_names)
+        with self._on_mesh():
+            out = self.inner.forward(sub)
+        return {self.native_prefix + k: v for k, v in out.items()}
+
+    def backward(self, piece):
+        n = len(self.native_prefix)
+        sub = {k[n:]: v for k, v in piece.items() if k.startswith(self.native_prefix)}
+        with self._on_mesh():
+            out = self.inner.backward(sub)
+        out = Rename._apply(out, [(b, a) for a, b in self.hf_names])
+        return {self.hf_prefix + k: v for k, v in out.items()}
 
 
 class VocabPad(ReshapeOp):
@@ -364,7 +422,7 @@ class OnlineReshaper(ReshapeOp):
             if not piece:
                 continue
             res = sc.op.forward(piece)
-            if len(res) == 1:
+            if len(res) == 1 and "*" not in sc.dst:
                 native[sc.dst] = next(iter(res.values()))
             else:
                 native.update(res)
@@ -373,9 +431,12 @@ class OnlineReshaper(ReshapeOp):
     def backward(self, weights: dict) -> dict:
         hf = {}
         for sc in self.scripts:
-            if sc.dst not in weights:
-                continue
-            hf.update(sc.op.backward({sc.dst: weights[sc.dst]}))
+            if "*" in sc.dst:                      # a rule over a family of parameters
+                piece = self.get_piece_by_pattern(weights, sc.dst)
+                if piece:
+                    hf.update(sc.op.backward(piece))
+            elif sc.dst in weights:
+                hf.update(sc.op.backward({sc.dst: weights[sc.dst]}))
         return hf
 
 

@@ -133,6 +133,45 @@ class ImageInsertDecoderMixin:
         self.mesh_connector = MeshConnector(self.cfg.parallel_cfg, enc_cfg.parallel_cfg,
                                             is_data_source=self.is_first_stage, dup_dim=["TP"])
 
+    # ------------------------------------------------------------------ HF <-> native weights
+    # The text model's mapping (an attribute that its constructor assigns, or its ``build_reshaper``) is kept as it
+    # is; the vision encoder and the projector add their rules in front of it.  HF spelling: ``vision_model.*`` with
+    # torch's fused ``in_proj_weight / in_proj_bias`` for the attention input projection, and
+    # ``vit_large_projector.weight`` (reference ``steptronoss/model/common/image_insert_decoder.py:52-96``).
+    @property
+    def reshaper(self):
+        from ...checkpointing.reshape_ops import OnlineReshaper
+
+        base = self.__dict__.get("_text_reshaper")
+        if base is None and hasattr(super(), "build_reshaper"):
+            base = super().build_reshaper()
+        if base is None or "encoder" not in self._modules:
+            return base
+        return OnlineReshaper(self.multimodal_reshape_scripts() + list(base.scripts))
+
+    @reshaper.setter
+    def reshaper(self, value):
+        self.__dict__["_text_reshaper"] = value
+
+    def multimodal_reshape_scripts(self) -> list:
+        from ...checkpointing.reshape_ops import Duplicate, KeepThisTP, Prefixed, Rename, Script
+
+        if not self.is_first_stage:          # one pipeline stage exports the vision weights
+            return []
+        scripts = []
+        proj = getattr(getattr(self, "tok_embeddings", None), "align_projector", None)
+        if proj is not None:
+            for leaf in ("weight", "bias") if proj.bias is not None else ("weight",):
+                scripts.append(Script(src=f"vit_large_projector.{leaf}", dst=f"tok_embeddings.align_projector.{leaf}",
+                                      op=Duplicate() + KeepThisTP()
+                                      + Rename(f"tok_embeddings.align_projector.{leaf}: vit_large_projector.{leaf}")))
+        if hasattr(self.encoder, "reshaper"):
+            fused = [("*.attn.in_proj_weight", "*.attn.qkv_proj.weight"), ("*.attn.in_proj_bias", "*.attn.qkv_proj.bias")]
+            scripts.append(Script(src="vision_model.*", dst="encoder.*",
+                                  op=Prefixed(self.encoder.reshaper, "vision_model.", "encoder.", fused,
+                                              mesh=self.cfg.tok_embed_cfg.encoder_cfg.parallel_cfg)))
+        return scripts
+
     def _encode_images_for_insert(self, images: list | None) -> list | None:
         if not images:
             return images

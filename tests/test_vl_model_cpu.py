@@ -56,3 +56,63 @@ def test_vl_forward_backward():
     # the text embeddings under the image tokens received no gradient through the splice
     no_img = model(input_ids=ids, labels=labels, cu_seqlens=cu, max_seq_len=S)
     assert abs(float(no_img["loss"]) - float(out["loss"])) > 0
+
+
+def test_hf_weights_of_text_vision_and_projector_round_trip():
+    """Export in HF spelling (``model.*`` / ``lm_head``, ``vision_model.*`` with fused ``in_proj``,
+    ``vit_large_projector``), load into a differently initialised model: every parameter comes back."""
+    from steptronoss_b200.models.qwen_vl import QwenImageInsertModelConfig
+    from steptronoss_b200.parallel.state import PM
+
+    PM.initialize()
+    src_cfg = _cfg()
+    cfg = QwenImageInsertModelConfig()
+    cfg.merge(src_cfg.to_dict())
+    PM.set_mesh(cfg.parallel_cfg)
+    a, b = cfg.build_model(), cfg.build_model()
+    a.init_weights(1, 0.02)
+    b.init_weights(2, 0.02)
+    with torch.no_grad():                                   # the encoder keeps torch's own initialisation: make the two differ
+        for p in b.encoder.parameters():
+            p.add_(0.5)
+        b.tok_embeddings.align_projector.weight.add_(0.5)
+    hf = a.hf_state_dict()
+    assert "vit_large_projector.weight" in hf and "model.embed_tokens.weight" in hf
+    assert "vision_model.transformer.resblocks.0.attn.in_proj_weight" in hf
+    assert "vision_model.transformer.resblocks.0.mlp.c_fc.weight" in hf and "vision_model.conv1.weight" in hf
+    assert not any(k.startswith("encoder.") or "qkv_proj" in k for k in hf)
+    skipped = b.load_hf_state_dict({k: v.clone() for k, v in hf.items()})
+    assert skipped == []
+    pa, pb = dict(a.named_parameters()), dict(b.named_parameters())
+    assert set(pa) == set(pb)
+    for k in pa:
+        assert torch.equal(pa[k], pb[k]), k
+
+
+def test_step3v_exports_vision_rules_in_front_of_the_step3p5_mapping():
+    from steptronoss_b200.models.step3v import Step3VModelConfig
+    from steptronoss_b200.parallel.state import PM
+    from tests.test_step3p5_cpu import _make
+
+    PM.initialize()
+    text = _make().model_cfg
+    cfg = Step3VModelConfig()
+    d = text.to_dict()
+    d.pop("tok_embed_cfg", None)
+    cfg.merge(d)
+    t = cfg.tok_embed_cfg
+    t.vocab_size, t.hidden_size, t.img_start_token = 256, 64, 3
+    e = t.encoder_cfg
+    e.image_size, e.patch_size, e.hidden_size, e.ffn_hidden_size, e.num_layers, e.num_attention_heads = 32, 4, 16, 32, 1, 2
+    e.vit_downsampler_hidden_dim, e.output_dim = 24, 20
+    PM.set_mesh(cfg.parallel_cfg)
+    a, b = cfg.build_model(), cfg.build_model()
+    a.init_weights(1, 0.02)
+    b.init_weights(2, 0.02)
+    hf = a.hf_state_dict()
+    assert "vit_large_projector.weight" in hf and any(k.startswith("vision_model.") for k in hf)
+    assert any(k.startswith("model.layers.1.") for k in hf)
+    b.load_hf_state_dict({k: v.clone() for k, v in hf.items()})
+    pa, pb = dict(a.named_parameters()), dict(b.named_parameters())
+    differ = [k for k in pa if not torch.equal(pa[k], pb[k])]
+    assert all("router_bias" in k or "expert_bias" in k for k in differ), differ
