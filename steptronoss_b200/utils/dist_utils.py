@@ -63,8 +63,13 @@ def _comm_device(group, device):
         return torch.device("cpu")
 
 
-def broadcast_tensors(obj: Any, src: int, group=None, device=None):
-    """Broadcast a nested container from global rank ``src`` to the group; tensors arrive on ``device``."""
+def broadcast_tensors(obj: Any, src: int | None = None, group=None, device=None, src_rank: int | None = None):
+    """Broadcast a nested container from global rank ``src`` (``src_rank`` is the reference's name for the same
+    argument) to the group; tensors arrive on ``device``."""
+    if src is None:
+        src = src_rank
+    if src is None:
+        raise TypeError("broadcast_tensors needs the source rank (src= or src_rank=)")
     if not dist.is_initialized() or dist.get_world_size(group) == 1:
         return obj
     dev = _comm_device(group, device)

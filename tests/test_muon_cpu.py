@@ -68,3 +68,31 @@ def test_gradient_manager_with_muon_trains():
     tr.train_step()
     changed = [n for n, p in tr.models[0].named_parameters() if not torch.equal(p, before[n])]
     assert len(changed) == len(before)
+
+
+def test_update_shaping_alternatives_have_their_stated_norms():
+    """The choices of ``get_zeropower_fn`` that do not orthogonalise: each fixes a different norm of the update."""
+    import torch
+
+    from steptronoss_b200.optim.zeropower import get_zeropower_fn
+
+    torch.manual_seed(0)
+    G = torch.randn(2, 6, 10)                                             # a batch of two wide matrices
+    m, n = 6, 10
+    U = get_zeropower_fn("svd")(G[0], None)
+    assert torch.allclose(U @ U.T, torch.eye(m), atol=1e-5)
+    D = get_zeropower_fn("double_normalize")(G, 3)
+    assert torch.allclose(D.norm(dim=-1), torch.ones(2, m), atol=1e-5)     # wide: columns first, rows last, so the rows end at norm 1
+    S = get_zeropower_fn("sinkhorn_knopp")(G.abs(), 20)
+    assert torch.allclose(S.abs().sum(-1), torch.full((2, m), n ** 0.5), rtol=1e-4)
+    assert torch.allclose(S.abs().sum(-2), torch.full((2, n), m / n * n ** 0.5), rtol=2e-2)   # doubly scaled after enough rounds
+    A = get_zeropower_fn("dualize_1_to_1")(G)
+    assert torch.allclose(A.abs().sum(-2), torch.full((2, n), m ** 0.5), rtol=1e-5)
+    B = get_zeropower_fn("dualize_inf_to_inf")(G)
+    assert torch.allclose(B.abs().sum(-1), torch.full((2, m), n / m ** 0.5), rtol=1e-5)
+    F = get_zeropower_fn("dualize_schatten_2_norm")(G)
+    assert torch.allclose(torch.linalg.matrix_norm(F), torch.full((2,), m ** 0.5), rtol=1e-5)
+    tall = get_zeropower_fn("double_normalize")(G.mT, 2)
+    assert torch.allclose(tall.norm(dim=-2), torch.ones(2, m), atol=1e-5)
+    ns = get_zeropower_fn("polar_express", run_ns_in_fp16=False)(G[0], steps=8)
+    assert torch.allclose(ns @ ns.T, torch.eye(m), atol=2e-2)
