@@ -145,3 +145,78 @@ def test_dataclass_and_plain_types():
 def test_parse_args():
     out = parse_args(["a.b=1", "x=foo", "--flag", "y=[1,2]", "z=1e-3", "t=True"])
     assert out == {"a.b": 1, "x": "foo", "y": [1, 2], "z": 1e-3, "t": True}
+
+
+def test_diff_and_critical_attributes():
+    a, b = Exp(), Exp()
+    assert a.diff(b) == []
+    b.sched.lr = 0.2
+    b.model_cfg.hidden = 16
+    d = {k: (x, y) for k, x, y in a.diff(b)}
+    assert d["sched.lr"] == ("0.1", "0.2") and d["model_cfg.hidden"] == ("8", "16")   # printable values
+    assert "optimizer_cfg.optimizer_cfg.lr" in d                 # a Ref follows its target
+
+    class Guarded(Exp):
+        _critical_attrs = ("model_cfg.hidden",)
+
+    g = Guarded()
+    g.assert_critical_attrs_expected(g.to_dict(rep=True))
+    saved = g.to_dict(rep=True)
+    g.sched.lr = 5.0                                             # not critical: may change between runs
+    g.assert_critical_attrs_expected(saved)
+    g.model_cfg.hidden = 32
+    with pytest.raises(AssertionError, match="model_cfg.hidden"):
+        g.assert_critical_attrs_expected(saved)
+
+
+def test_mock_imports_stands_in_for_missing_packages_only(tmp_path):
+    import sys
+
+    from steptronoss_b200.config.mock_imports import get_object_from_file, mock_imports
+
+    f = tmp_path / "needs_heavy.py"
+    f.write_text(
+        "import json\n"
+        "import not_installed_pkg_xyz\n"
+        "from not_installed_pkg_xyz.sub.mod import Thing, helper\n"
+        "class Child(Thing):\n    pass\n"
+        "VALUE = helper(3).whatever\n"
+        "class Exp:\n    tag = json.dumps([1])\n")
+    with pytest.raises(ModuleNotFoundError):
+        get_object_from_file(str(f), "Exp")
+    with mock_imports("not_installed_pkg_xyz", "json"):
+        exp = get_object_from_file(str(f), "Exp")
+        assert exp.tag == "[1]"                                   # json is installed: the real module was used
+        assert list(sys.modules["not_installed_pkg_xyz"].anything) == []
+    assert not any(n.startswith("not_installed_pkg_xyz") for n in sys.modules)
+
+
+def test_cfshow_prints_subtrees_diffs_and_the_check_result(tmp_path):
+    import io
+
+    from steptronoss_b200.config.cfshow import show
+
+    base = tmp_path / "base_exp_file.py"
+    base.write_text(
+        "from steptronoss_b200.config import Config\n"
+        "class M(Config):\n    hidden: int = 8\n    layers: int\n"
+        "class Base(Config):\n    model_cfg = M\n    seed = 1\n"
+        "    def __init__(self):\n        super().__init__()\n        self.model_cfg.layers = 2\n"
+        "class Exp(Base):\n    seed = 7\n"
+        "    def __init__(self):\n        super().__init__()\n        self.model_cfg.hidden = 16\n")
+    out = io.StringIO()
+    assert show(str(base), out=out) == 0
+    text = out.getvalue()
+    assert "hidden" in text and "16" in text and "sanity_check: OK" in text
+    out = io.StringIO()
+    show(str(base), key="model_cfg", diff="parent", out=out)
+    text = out.getvalue()
+    assert text.startswith("M @") and "model_cfg.hidden: 16 | 8" in text and "seed: 7 | 1" in text
+    out = io.StringIO()
+    show(str(base), key="model_cfg.hidden", check=False, out=out)
+    assert out.getvalue().strip() == "16"
+    broken = tmp_path / "broken_exp_file.py"
+    broken.write_text("from steptronoss_b200.config import Config\nclass M(Config):\n    layers: int\n"
+                      "class Exp(Config):\n    model_cfg = M\n")
+    out = io.StringIO()
+    assert show(str(broken), out=out) == 1 and "sanity_check: FAILED" in out.getvalue() and "layers" in out.getvalue()
