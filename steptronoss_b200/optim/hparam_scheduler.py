@@ -14,7 +14,8 @@ _SHAPES: dict[str, Callable[[float, float, float], float]] = {
     "linear": lambda x, n, w: 1.0 - x / n,
     "cosine": lambda x, n, w: 0.5 * (math.cos(math.pi * min(x, n) / n) + 1.0),
     "cosine_incr": lambda x, n, w: 0.5 * (math.cos(math.pi * (1.0 - min(x, n) / n)) + 1.0),
-    "inv_sqrt": lambda x, n, w: (w ** 0.5) / ((x + w) ** 0.5) if (x + w) > 0 else 1.0,
+    # the reference's rule: sqrt(warmup / steps since the warm-up ended); above 1 (hence clipped) until 2 x warmup
+    "inv_sqrt": lambda x, n, w: (w ** 0.5) / (x ** 0.5) if x > 0 else 1.0,
 }
 
 
