@@ -94,6 +94,8 @@ class TransformerBlock(nn.Module):
         else:
             self.recompute_all, self.recompute = False, list(recompute or [])
         sp = bool(cfg.tp_cfg.sequence_parallel)
+        # with sequence parallelism the block input is already 1/TP per rank: nothing left to distribute
+        self.distribute_saved_activations = bool(cfg.tp_cfg.distribute_saved_activations) and not sp
         self.attention_norm = RMSNorm(cfg.hidden_size, cfg.layernorm_epsilon, sequence_parallel=sp,
                                       use_zero_init=cfg.rms_norm_zero_gamma, params_dtype=cfg.params_dtype)
         self.ffn_norm = RMSNorm(cfg.hidden_size, cfg.layernorm_epsilon, sequence_parallel=sp,
@@ -103,7 +105,7 @@ class TransformerBlock(nn.Module):
 
     def _maybe(self, part: str, fn, *args):
         if part in self.recompute and not self.recompute_all and torch.is_grad_enabled():
-            return checkpoint(fn, *args)
+            return checkpoint(fn, *args, distribute_saved_activations=self.distribute_saved_activations)
         return fn(*args)
 
     def _body(self, x, position_id, cu_seqlens, max_seqlen, cp_meta):
@@ -116,7 +118,8 @@ class TransformerBlock(nn.Module):
 
     def forward(self, x, position_id=None, cu_seqlens=None, max_seqlen=None, cp_meta=None):
         if self.recompute_all and torch.is_grad_enabled() and x.requires_grad:
-            return checkpoint(lambda t: self._body(t, position_id, cu_seqlens, max_seqlen, cp_meta), x)
+            return checkpoint(lambda t: self._body(t, position_id, cu_seqlens, max_seqlen, cp_meta), x,
+                              distribute_saved_activations=self.distribute_saved_activations)
         return self._body(x, position_id, cu_seqlens, max_seqlen, cp_meta)
 
 

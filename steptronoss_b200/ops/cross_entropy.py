@@ -29,7 +29,7 @@ class _VocabParallelCEFn(torch.autograd.Function):
     """PyTorch statement (any device): per-token loss from a vocab shard of logits."""
 
     @staticmethod
-    def forward(ctx, logits, labels, vocab_start, group):
+    def forward(ctx, logits, labels, vocab_start, group, label_smoothing=0.0):
         lf = logits.float()
         V = lf.shape[-1]
         m = _all_reduce(lf.max(dim=-1).values, dist.ReduceOp.MAX, group)
@@ -43,6 +43,17 @@ class _VocabParallelCEFn(torch.autograd.Function):
         se = _all_reduce(ex.sum(-1), dist.ReduceOp.SUM, group)
         loss = se.log() - tgt
         softmax = ex / se.unsqueeze(-1)
+        ctx.smoothing, ctx.vocab = 0.0, V
+        if label_smoothing > 0:
+            # (1 - a) on the label and a / (K - 1) on every other class, K = the whole vocabulary:
+            # loss = (1 - s) * nll - s * mean_i log p_i  with  s = a * K / (K - 1)
+            if not label_smoothing < 1.0:
+                raise ValueError("label_smoothing must be in [0, 1)")
+            K = V * (dist.get_world_size(group) if group is not None else 1)
+            s = label_smoothing * K / (K - 1)
+            mean_logp = _all_reduce(lf.sum(-1), dist.ReduceOp.SUM, group) / K - se.log()
+            loss = (1.0 - s) * loss - s * mean_logp
+            ctx.smoothing, ctx.vocab = s, K
         ctx.save_for_backward(softmax, inside, safe)
         ctx.in_dtype = logits.dtype
         # accuracy: global arg-max equals the label
@@ -59,13 +70,20 @@ class _VocabParallelCEFn(torch.autograd.Function):
         grad = softmax.clone()
         onehot = torch.zeros_like(grad)
         onehot.scatter_(-1, safe.unsqueeze(-1), inside.unsqueeze(-1).to(grad.dtype))
-        grad = (grad - onehot) * gloss.unsqueeze(-1)
-        return grad.to(ctx.in_dtype), None, None, None
+        if ctx.smoothing:
+            grad = grad - (1.0 - ctx.smoothing) * onehot - ctx.smoothing / ctx.vocab
+        else:
+            grad = grad - onehot
+        grad = grad * gloss.unsqueeze(-1)
+        return grad.to(ctx.in_dtype), None, None, None, None
 
 
-def vocab_parallel_cross_entropy(logits, labels, vocab_start: int = 0, group=None):
-    """Per-token loss ``[...]`` and arg-max prediction from (a vocab shard of) ``logits [..., V_local]``."""
-    return _VocabParallelCEFn.apply(logits, labels, vocab_start, group)
+def vocab_parallel_cross_entropy(logits, labels, vocab_start: int = 0, group=None, label_smoothing: float = 0.0):
+    """Per-token loss ``[...]`` and arg-max prediction from (a vocab shard of) ``logits [..., V_local]``.
+
+    ``label_smoothing`` spreads that much probability over the other classes of the WHOLE vocabulary (the
+    reference counts only the classes of the local shard, ``cross_entropy.py:91-108``; the two agree at TP=1)."""
+    return _VocabParallelCEFn.apply(logits, labels, vocab_start, group, label_smoothing)
 
 
 class _FusedLinearCEFn(torch.autograd.Function):

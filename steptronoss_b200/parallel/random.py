@@ -88,7 +88,7 @@ def _detach(args):
 
 class _CheckpointFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, run_function, n_tensor_args, *args):
+    def forward(ctx, run_function, distribute, *args):
         ctx.run_function = run_function
         ctx.cpu_rng = torch.get_rng_state()
         ctx.dev_rng = _device_rng_get()
@@ -98,6 +98,16 @@ class _CheckpointFn(torch.autograd.Function):
         tensors = [a for a in args if torch.is_tensor(a)]
         ctx.arg_is_tensor = [torch.is_tensor(a) for a in args]
         ctx.non_tensors = [a for a in args if not torch.is_tensor(a)]
+        ctx.full_shape = None
+        if distribute and tensors:
+            # keep 1/TP of the first tensor on every rank; backward gathers it again (for inputs that are equal on
+            # all TP ranks, i.e. without sequence parallelism)
+            from .state import PM
+
+            tp, r = PM.size_of("TP"), PM.rank_in("TP")
+            if tp > 1 and tensors[0].numel() % tp == 0:
+                ctx.full_shape = tensors[0].shape
+                tensors[0] = tensors[0].detach().reshape(-1).chunk(tp)[r].clone().requires_grad_(tensors[0].requires_grad)
         ctx.save_for_backward(*tensors)
         if os.environ.get("RECOMPUTE_SANITY_CHECK", "0") == "1":
             ctx.sanity = outputs.detach().clone() if torch.is_tensor(outputs) else [o.detach().clone() for o in outputs]
@@ -106,6 +116,13 @@ class _CheckpointFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, *grads):
         tensors = list(ctx.saved_tensors)
+        if ctx.full_shape is not None:
+            from .state import PM
+
+            shard = tensors[0]
+            full = torch.empty(shard.numel() * PM.size_of("TP"), dtype=shard.dtype, device=shard.device)
+            torch.distributed.all_gather_into_tensor(full, shard.detach().contiguous(), group=PM.group_of("TP"))
+            tensors[0] = full.view(ctx.full_shape).requires_grad_(shard.requires_grad)
         nts = list(ctx.non_tensors)
         args = [tensors.pop(0) if is_t else nts.pop(0) for is_t in ctx.arg_is_tensor]
         cpu_rng, dev_rng = torch.get_rng_state(), _device_rng_get()
@@ -133,6 +150,103 @@ class _CheckpointFn(torch.autograd.Function):
         return (None, None) + in_grads
 
 
-def checkpoint(function, *args):
-    """Run ``function(*args)`` without keeping its intermediate activations; recompute in backward."""
-    return _CheckpointFn.apply(function, len(args), *args)
+def checkpoint(function, *args, distribute_saved_activations: bool = False):
+    """Run ``function(*args)`` without keeping its intermediate activations; recompute in backward.
+    ``distribute_saved_activations``: every TP rank keeps only its 1/TP of the first tensor argument."""
+    return _CheckpointFn.apply(function, bool(distribute_saved_activations), *args)
+
+
+class _RngSnapshot:
+    """CPU, device and tracker generator states at one point, to replay a function under the same randomness."""
+
+    def __init__(self):
+        self.cpu, self.dev, self.tracker = torch.get_rng_state(), _device_rng_get(), get_rng_tracker().get_states()
+
+    @contextlib.contextmanager
+    def replay(self):
+        now = _RngSnapshot()
+        torch.set_rng_state(self.cpu)
+        _device_rng_set(self.dev)
+        get_rng_tracker().set_states(self.tracker)
+        try:
+            yield
+        finally:
+            torch.set_rng_state(now.cpu)
+            _device_rng_set(now.dev)
+            get_rng_tracker().set_states(now.tracker)
+
+
+class _DiscardableFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, owner, run_function, *args):
+        with torch.no_grad():
+            outputs = run_function(*args)
+        ctx.arg_is_tensor = [torch.is_tensor(a) for a in args]
+        ctx.non_tensors = [a for a in args if not torch.is_tensor(a)]
+        ctx.save_for_backward(*[a for a in args if torch.is_tensor(a)])
+        ctx.recomputed = None
+        owner._ctx = ctx
+        return outputs
+
+    @staticmethod
+    def backward(ctx, *grads):
+        if ctx.recomputed is None:
+            raise RuntimeError("the output was never recomputed: call discard_output_and_register_recompute(t) with a "
+                               "tensor t computed from the output, and run backward through t")
+        outputs, inputs = ctx.recomputed
+        ctx.recomputed = None
+        pairs = [(o, g) for o, g in zip(outputs, grads) if torch.is_tensor(o) and o.requires_grad and g is not None]
+        if pairs:
+            torch.autograd.backward([p[0] for p in pairs], [p[1] for p in pairs])
+        return (None, None) + tuple(a.grad if torch.is_tensor(a) else None for a in inputs)
+
+
+class CheckpointWithoutOutput:
+    """Recompute that also gives up the function's OUTPUT between forward and backward.
+
+    ``checkpoint`` keeps the output alive because the next operator saved it.  Here the caller says when the output
+    has been consumed; its storage is released then and filled again, by running the function a second time, just
+    before the consumer's backward reads it (a hook on the consumer's result)::
+
+        ck = CheckpointWithoutOutput()
+        h = ck.checkpoint(norm, x)            # cheap to recompute, large to keep
+        y = linear(h)
+        ck.discard_output_and_register_recompute(y)
+
+    Reference: ``steptronoss/core/tensor_parallel/random.py:311-381``.
+    """
+
+    def __init__(self):
+        self._fn = self._ctx = self._rng = self._outputs = None
+
+    def checkpoint(self, run_function, *args):
+        self._fn, self._rng = run_function, _RngSnapshot()
+        out = _DiscardableFn.apply(self, run_function, *args)
+        self._outputs = out if isinstance(out, tuple) else (out,)
+        return out
+
+    def discard_output_and_register_recompute(self, hook_tensor: torch.Tensor) -> None:
+        if self._outputs is None:
+            return
+        for o in self._outputs:
+            if torch.is_tensor(o):
+                o.untyped_storage().resize_(0)
+        if hook_tensor.requires_grad:
+            hook_tensor.register_hook(self._refill)
+
+    def _refill(self, grad):
+        ctx = self._ctx
+        tensors, nts = list(ctx.saved_tensors), list(ctx.non_tensors)
+        args = _detach([tensors.pop(0) if is_t else nts.pop(0) for is_t in ctx.arg_is_tensor])
+        with self._rng.replay(), torch.enable_grad():
+            again = self._fn(*args)
+        again = again if isinstance(again, tuple) else (again,)
+        with torch.no_grad():
+            for old, new in zip(self._outputs, again):
+                if torch.is_tensor(old):
+                    st = old.untyped_storage()
+                    st.resize_(new.untyped_storage().size())
+                    st.copy_(new.untyped_storage())
+        ctx.recomputed = (again, args)
+        self._fn = self._ctx = self._rng = self._outputs = None
+        return grad
