@@ -48,6 +48,10 @@ class AttentionConfig(Config):
     yarn_beta_fast: float = 32.0
     ntk_interp_ratio: float = 1.0
     rope_scaling_factor: float = 1.0
+    rope_use_adjacent_pair: bool = False
+    """rotate the pairs (2i, 2i+1) instead of (i, i + rot/2): q and k are brought into the half-split order first (as
+    the reference's ``RotaryEmbedding(use_adjacent_pair=True)`` does, ``model/common/rope.py:242-246``) and stay in it,
+    which leaves every q.k product unchanged"""
     original_max_position_embeddings: int | None = None
     max_position_embeddings: int = 32768
     num_attention_heads_per_layer: list | None = None
@@ -97,6 +101,10 @@ class GroupedQueryAttention(nn.Module):
         self.rope = RotaryEmbedding(self.rot_dim, theta, cfg.max_position_embeddings, cfg.rope_scaling_factor,
                                     cfg.original_max_position_embeddings, cfg.yarn_beta_fast, cfg.yarn_beta_slow,
                                     cfg.ntk_interp_ratio)
+        self.pair_perm = None
+        if cfg.rope_use_adjacent_pair:
+            r = self.rot_dim
+            self.pair_perm = torch.tensor(list(range(0, r, 2)) + list(range(1, r, 2)) + list(range(r, D)))
         sw = _per_layer(cfg.use_sliding_window, layer_id)
         self.window = int(cfg.sliding_window_size) if sw and cfg.sliding_window_size and cfg.sliding_window_size > 0 else 0
 
@@ -112,6 +120,13 @@ class GroupedQueryAttention(nn.Module):
         cos, sin = self.rope.tables(qkv.device, need if need is not None else self.cfg.max_position_embeddings)
         qw = self.q_norm.weight if self.use_qk_norm else None
         kw = self.k_norm.weight if self.use_qk_norm else None
+        if self.pair_perm is not None:
+            perm = self.pair_perm.to(qkv.device)
+            n_qk = (hq + hkv) * D
+            qk = qkv[:, :n_qk].reshape(T, hq + hkv, D).index_select(-1, perm).reshape(T, n_qk)
+            qkv = torch.cat([qk, qkv[:, n_qk:]], dim=1)
+            if self.use_qk_norm:                       # the per-dimension norm weights move with their dimensions
+                qw, kw = qw.index_select(0, perm), kw.index_select(0, perm)
         q, k, v = qknorm_rope(qkv if not self.use_gate else qkv[:, : (hq + 2 * hkv) * D], qw, kw, cos, sin, position_id,
                               hq, hkv, D, self.rot_dim, self.cfg.layernorm_epsilon, self.use_qk_norm,
                               self.cfg.rms_norm_zero_gamma)

@@ -118,6 +118,46 @@ def _set_rng_seed(seed: int) -> None:
         torch.cuda.manual_seed(seed)
 
 
+class GlobalMemoryBuffer:
+    """Named scratch tensors that live for the whole job: ``get_tensor(shape, dtype, name)`` returns a view of one
+    flat allocation per ``(name, dtype)``, grown when a larger request arrives.  Two users of the same name must not
+    overlap in time.  (Reference ``steptronoss/core/utils.py:23-41``, used there for the sequence-parallel gather;
+    the fused all-gather GEMM here keeps its landing area in the symmetric arena of ``parallel/symm.py`` instead.)"""
+
+    def __init__(self) -> None:
+        self.buffer: dict[tuple, torch.Tensor] = {}
+
+    def get_tensor(self, tensor_shape, dtype: torch.dtype, name: str, device=None) -> torch.Tensor:
+        need = 1
+        for d in tensor_shape:
+            need *= int(d)
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        cur = self.buffer.get((name, dtype))
+        if cur is None or cur.numel() < need or cur.device != torch.device(device):
+            cur = torch.empty(need, dtype=dtype, device=device, requires_grad=False)
+            self.buffer[(name, dtype)] = cur
+        return cur[:need].view(*tensor_shape)
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.buffer.values())
+
+
+_GLOBAL_MEMORY_BUFFER: GlobalMemoryBuffer | None = None
+
+
+def get_global_memory_buffer() -> GlobalMemoryBuffer:
+    global _GLOBAL_MEMORY_BUFFER
+    if _GLOBAL_MEMORY_BUFFER is None:
+        _GLOBAL_MEMORY_BUFFER = GlobalMemoryBuffer()
+    return _GLOBAL_MEMORY_BUFFER
+
+
+def destroy_global_memory_buffer() -> None:
+    global _GLOBAL_MEMORY_BUFFER
+    _GLOBAL_MEMORY_BUFFER = None
+
+
 class ParallelManager:
     def __init__(self) -> None:
         self.world_size = 1

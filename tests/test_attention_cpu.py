@@ -39,3 +39,49 @@ def test_sliding_window_and_offset_queries():
             mask[i, j] = (j <= qi) and (j > qi - 3)
     ref = torch.softmax(s.masked_fill(~mask, float("-inf")), -1) @ v[:, 0]
     assert torch.allclose(out[:, 0], ref, atol=1e-6)
+
+
+def test_adjacent_pair_rope_rotates_neighbouring_dimensions():
+    """With ``rope_use_adjacent_pair`` the attention output equals the plain module's on inputs whose q/k rows were
+    de-interleaved beforehand, and the rotation itself is the (2i, 2i+1) pair rotation."""
+    import torch
+
+    from steptronoss_b200.ops.fused import qknorm_rope_reference
+    from steptronoss_b200.parallel.state import PM
+
+    PM.initialize()
+
+    def build(adjacent):
+        from tests.tiny_exp import make_tiny_exp
+
+        exp = make_tiny_exp(gbs=1, seq=16, iters=1, layers=1, hidden=32, heads=2, kv_heads=1, head_dim=16, ffn=64, vocab=64)
+        c = exp.model_cfg.attn_cfg
+        c.rope_use_adjacent_pair, c.params_dtype = adjacent, torch.float32
+        PM.set_mesh(exp.model_cfg.parallel_cfg)
+        m = c.build_model(layer_id=0)
+        torch.manual_seed(0)
+        for p in m.parameters():
+            torch.nn.init.normal_(p, std=0.3)
+        return m
+
+    plain, adj = build(False), build(True)
+    adj.load_state_dict(plain.state_dict())
+    T, D = 6, 16
+    x = torch.randn(T, 32)
+    pos = torch.arange(T, dtype=torch.int32)
+    cu = torch.tensor([0, T], dtype=torch.int32)
+    out = adj(x, pos, cu, T)
+    assert out.shape == (T, 32) and torch.isfinite(out).all() and not torch.allclose(out, plain(x, pos, cu, T))
+
+    # the rotation: de-interleave, half-split rotate == rotate neighbours, then de-interleave
+    cos, sin = adj.rope.tables(x.device, T)
+    qkv = torch.randn(T, 4 * D)                                      # 2 q heads, 1 k head, 1 v head
+    perm = adj.pair_perm
+    qk = qkv[:, :3 * D].reshape(T, 3, D).index_select(-1, perm).reshape(T, 3 * D)
+    q, k, _ = qknorm_rope_reference(torch.cat([qk, qkv[:, 3 * D:]], 1), None, None, cos, sin, pos, 2, 1, D, D, use_norm=False)
+    raw = qkv[:, :2 * D].reshape(T, 2, D)
+    c, s = cos[pos.long()].unsqueeze(1), sin[pos.long()].unsqueeze(1)
+    want = torch.empty_like(raw)
+    want[..., 0::2] = raw[..., 0::2] * c - raw[..., 1::2] * s
+    want[..., 1::2] = raw[..., 1::2] * c + raw[..., 0::2] * s
+    assert torch.allclose(q, want.index_select(-1, perm), atol=1e-6)

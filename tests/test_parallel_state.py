@@ -75,3 +75,24 @@ def test_named_rng_streams_differ_across_family():
             second = torch.rand(1).item()
         assert second != seeds[-1]
     assert seeds[0] != seeds[1]
+
+
+def test_global_memory_buffer_reuses_and_grows():
+    import torch
+
+    from steptronoss_b200.parallel.state import destroy_global_memory_buffer, get_global_memory_buffer
+
+    destroy_global_memory_buffer()
+    buf = get_global_memory_buffer()
+    assert buf is get_global_memory_buffer()
+    a = buf.get_tensor((4, 8), torch.float32, "mpu")
+    a.fill_(3.0)
+    b = buf.get_tensor((2, 8), torch.float32, "mpu")
+    assert b.data_ptr() == a.data_ptr() and float(b.sum()) == 48.0            # same storage, no new allocation
+    c = buf.get_tensor((2, 8), torch.bfloat16, "mpu")
+    d = buf.get_tensor((2, 8), torch.float32, "other")
+    assert c.data_ptr() != a.data_ptr() and d.data_ptr() != a.data_ptr()      # keyed by name and dtype
+    big = buf.get_tensor((16, 8), torch.float32, "mpu")
+    assert big.shape == (16, 8) and buf.nbytes() == 16 * 8 * 4 + 16 * 2 + 16 * 4
+    destroy_global_memory_buffer()
+    assert get_global_memory_buffer().nbytes() == 0
