@@ -108,3 +108,56 @@ def test_expert_parallel_2_ranks_matches_single_process():
         assert torch.allclose(torch.from_numpy(out), outs[rank], atol=1e-5), f"rank {rank} output"
         # expert weight gradients: rank r owns experts [2r, 2r+2) and received tokens of both ranks
         assert torch.allclose(torch.from_numpy(gw1), w1_full[2 * rank: 2 * rank + 2], atol=1e-4)
+
+
+def test_router_options_scale_balance_and_raw_weights():
+    """``routed_scaling_factor`` multiplies the block output, ``force_balance`` deals tokens out round-robin,
+    ``norm_expert_weight=False`` keeps the raw softmax probabilities of the chosen experts."""
+    x = _inputs()
+    base = _build_block()
+    ref = base(x)
+    scaled = _build_block()
+    scaled.cfg.routed_scaling_factor = 2.5
+    assert torch.allclose(scaled(x), ref * 2.5, atol=1e-6)
+
+    forced = _build_block()
+    forced.cfg.force_balance = True
+    ids, w, _ = forced.forward_router(forced.gate(x))
+    assert ids.reshape(-1).tolist() == [i % 4 for i in range(48)]                 # 24 tokens x top-2 over 4 experts
+    assert torch.bincount(ids.reshape(-1), minlength=4).tolist() == [12, 12, 12, 12]
+    assert torch.allclose(w.sum(-1), torch.ones(24), atol=1e-5)
+
+    raw = _build_block()
+    raw.cfg.norm_expert_weight = False
+    logits = raw.gate(x)
+    ids, w, _ = raw.forward_router(logits)
+    prob = torch.softmax(logits.float(), dim=1)
+    assert torch.allclose(w, prob.gather(1, ids), atol=1e-6) and bool((w.sum(-1) < 1).all())
+
+
+def test_zero_centred_norm_weight_and_clamped_swiglu():
+    from steptronoss_b200.models.common.rms_norm import RMSNorm
+    from steptronoss_b200.ops import rmsnorm
+    from steptronoss_b200.ops.fused import swiglu_reference
+
+    torch.manual_seed(0)
+    x = torch.randn(5, 16)
+    plain, zero = RMSNorm(16, 1e-6, params_dtype=torch.float32), RMSNorm(16, 1e-6, use_zero_init=True, params_dtype=torch.float32)
+    assert plain.weight.init_kind == "ones" and zero.weight.init_kind == "zeros"
+    with torch.no_grad():
+        plain.weight.fill_(1.0)
+        zero.weight.zero_()                                                      # gamma = weight + 1
+    assert torch.allclose(plain(x), zero(x), atol=1e-6)
+    with torch.no_grad():
+        zero.weight.fill_(0.5)
+    want = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * 1.5
+    assert torch.allclose(zero(x), want, atol=1e-5)
+    xg = x.clone().requires_grad_(True)
+    rmsnorm(xg, zero.weight, 1e-6, True).sum().backward()
+    assert zero.weight.grad is not None and xg.grad is not None
+
+    h = torch.tensor([[10.0, -10.0, 1.0, 20.0, -20.0, 2.0]])                     # gate | up
+    out = swiglu_reference(h, limit=7.0)
+    g, u = torch.tensor([7.0, -10.0, 1.0]), torch.tensor([7.0, -7.0, 2.0])       # gate capped above, up on both sides
+    assert torch.allclose(out, torch.nn.functional.silu(g) * u)
+    assert not torch.allclose(out, swiglu_reference(h))
