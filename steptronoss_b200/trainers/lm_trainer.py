@@ -16,6 +16,7 @@ from ..models.module import Float16Module, unwrap_model
 from ..ops import native
 from ..parallel.state import PM, set_mpu_random_seed
 from ..utils.logger import logger
+from ..utils.memory_tracker import CMT
 from ..utils.metrics import GlobalMetrics
 from ..utils.timers import get_timers, init_timers
 from .base_trainer import BaseTrainer
@@ -155,10 +156,25 @@ class DecoderPretrainTrainer(BaseTrainer):
         sched.configure(self.models, self.data_iterators,
                         data_sync_fn=lambda it: tc.sync_get_data(it),
                         data_proc_fn=exp.data_cfg.preprocess, loss_fn=tc.loss_func, training=True)
+        # optimizer state (fp32 masters and moments) waits on the host while activations need the memory
+        offload = bool(getattr(tc, "offload_optimizer_state", False)) and hasattr(gm, "offload_state")
         with timers.record("forward-backward", 1):
+            if offload:
+                CMT.mark("before_cpu_offload_optimizer_state")
+                with timers.record("optimizer-offload", 2):
+                    gm.offload_state()
+                CMT.mark("after_cpu_offload_optimizer_state")
             sched.run(n_micro)
+        CMT.mark("after_forward_backward")
+        if getattr(tc, "empty_unused_memory_level", 0) >= 1 and torch.cuda.is_available():
+            torch.cuda.empty_cache()
+        if offload:
+            with timers.record("optimizer-backload", 2):
+                gm.reload_state()
+            CMT.mark("after_cpu_backload_optimizer_state")
         with timers.record("optimizer-step", 1):
             ok, grad_norm, zeros = gm.step()
+        CMT.mark("after_optimizer_step")
         GlobalMetrics.grad_norm.add(grad_norm)
         if zeros is not None:
             GlobalMetrics.grad_zeros.add(zeros)

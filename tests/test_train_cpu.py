@@ -114,3 +114,30 @@ def test_dp2_gloo_matches_single_process_exactly(zero1):
         assert losses == ref_losses, f"rank {rank}: {losses} vs {ref_losses}"
         for k, v in ref_params.items():
             assert torch.equal(torch.from_numpy(params[k]), v), f"rank {rank}: parameter {k} differs"
+
+
+def test_optimizer_state_offload_and_zero_count_do_not_change_the_run(monkeypatch):
+    """``offload_optimizer_state`` moves masters and moments off the device around forward/backward and back for
+    the update: the loss curve and the parameters stay bit-identical; the memory marks appear in order."""
+    from steptronoss_b200.utils.memory_tracker import CMT
+
+    base_losses, base_params, _ = _run(_make(), steps=4)
+    e = _make()
+    e.trainer_cfg.offload_optimizer_state = True
+    e.trainer_cfg.log_num_zeros_in_grad = True
+    monkeypatch.setattr(CMT, "enabled", True)
+    monkeypatch.setattr(CMT, "marks", [])
+    moved = []
+    losses, params, tr = _run(e, steps=4)
+    gm = tr.grad_manager
+    real_off, real_on = gm.offload_state, gm.reload_state
+    monkeypatch.setattr(gm, "offload_state", lambda: (moved.append("off"), real_off())[1])
+    monkeypatch.setattr(gm, "reload_state", lambda: (moved.append("on"), real_on())[1])
+    tr.train_step()
+    assert moved == ["off", "on"]
+    assert losses == base_losses
+    for k in base_params:
+        assert torch.equal(params[k], base_params[k]), k
+    names = [m.name for m in CMT.marks][:5]
+    assert names == ["before_cpu_offload_optimizer_state", "after_cpu_offload_optimizer_state", "after_forward_backward",
+                     "after_cpu_backload_optimizer_state", "after_optimizer_step"]
