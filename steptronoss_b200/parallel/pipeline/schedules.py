@@ -133,7 +133,8 @@ class PPScheduler(FWBWScheduler):
         steady = forward_num - warmup
         scale = 1.0 / forward_num
         inputs, outputs = [], []
-        ctx = torch.autograd.graph.save_on_cpu(pin_memory=True) if self.config.pipeline_activation_cpu_offload else None
+        ctx = (torch.autograd.graph.save_on_cpu(pin_memory=torch.cuda.is_available())
+               if self.config.pipeline_activation_cpu_offload else None)
 
         def fwd(inp):
             if ctx is not None:

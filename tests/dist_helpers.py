@@ -23,7 +23,15 @@ def _worker(rank, world, port, exp_kwargs, steps, q):
         from tests.tiny_exp import make_tiny_exp
 
         PM.initialize(backend="gloo")
+        exp_kwargs = dict(exp_kwargs)
+        extra = exp_kwargs.pop("set", {})                  # dotted config paths to set after the experiment is built
         exp = make_tiny_exp(**exp_kwargs)
+        for path, value in extra.items():
+            node = exp
+            *parents, leaf = path.split(".")
+            for part in parents:
+                node = getattr(node, part)
+            setattr(node, leaf, value)
         exp.seed = 0
         tr = exp.trainer_cfg.get_trainer_cls()(exp=exp)
         tr.before_train()

@@ -48,3 +48,15 @@ def test_pp2_interleaved(single):
     ref8 = run_single(dict(base4, gbs=4))
     res8 = run_ranks(2, dict(base4, pp=2, vpp=2, gbs=4))
     assert _close(res8[-1][1], ref8[0], 2e-5), (res8[-1][1], ref8[0])
+
+
+def test_pp2_with_activations_kept_on_the_host_and_tp2_with_split_saved_inputs(single):
+    """Two memory options that must not change the numbers: pipeline stages park saved activations on the host
+    (``pipeline_activation_cpu_offload``); recomputed blocks keep 1/TP of their input per rank
+    (``distribute_saved_activations``, tensor parallel without sequence parallel)."""
+    res = run_ranks(2, dict(BASE, pp=2, set={"model_cfg.pipeline_activation_cpu_offload": True}))
+    assert _close(res[-1][1], single[0], 2e-5), (res[-1][1], single[0])
+    res = run_ranks(2, dict(BASE, tp=2, sp=False, recompute=True, set={"model_cfg.tp_cfg.distribute_saved_activations": True}))
+    for rank, losses, norms, _ in res:
+        assert _close(losses, single[0], 2e-5), (rank, losses, single[0])
+        assert _close(norms, single[1], 1e-4), (rank, norms, single[1])
