@@ -234,3 +234,59 @@ def test_blockchain_write_copy_read_resume(tmp_path):
     rd3.load_state_dict(st)
     assert rd3.get()["i"] == 6
     rd.close()
+
+
+def test_samplers_cover_epochs_resume_and_skip_without_building_items():
+    from steptronoss_b200.data.nextable import DPMux, Nextable, SlowFastNextable
+    from steptronoss_b200.data.samplers import LoopedSequentialSampler, LoopedShuffleSampler
+
+    seq = LoopedSequentialSampler(3)
+    assert [next(seq) for _ in range(7)] == [0, 1, 2, 0, 1, 2, 0] and isinstance(seq, Nextable)
+    sh = LoopedShuffleSampler(5, seed=3)
+    first, second = [next(sh) for _ in range(5)], [next(sh) for _ in range(5)]
+    assert sorted(first) == sorted(second) == [0, 1, 2, 3, 4] and first != second      # a new order every epoch
+    again = LoopedShuffleSampler(5, seed=3)
+    for _ in range(3):
+        again.fast_step()                                                              # skipping == taking
+    assert [next(again) for _ in range(2)] == first[3:]
+    state = again.state_dict()
+    resumed = LoopedShuffleSampler(5, seed=99)
+    resumed.load_state_dict(state)                                                     # the seed travels with the state
+    assert [next(resumed) for _ in range(5)] == second
+
+    class Plain:                                                                       # duck-typed protocol member
+        def __next__(self):
+            return 1
+
+        def state_dict(self):
+            return {}
+
+        def load_state_dict(self, sd):
+            pass
+
+    assert isinstance(Plain(), Nextable) and not isinstance(Plain(), SlowFastNextable)
+    ranks = [DPMux(LoopedSequentialSampler(100), dp_size=3, dp_rank=r) for r in range(3)]
+    taken = [[next(m) for _ in range(3)] for m in ranks]
+    assert taken == [[0, 3, 6], [1, 4, 7], [2, 5, 8]]
+
+
+def test_local_futures_and_get_ready():
+    import threading
+    import time
+
+    from steptronoss_b200.utils.comm_utils import LocalFuture, get_ready, wait_by_finish_order
+
+    a, b, c = LocalFuture(), LocalFuture(), LocalFuture()
+    assert not a.completed
+    with pytest.raises(TimeoutError):
+        a.result(timeout=0.05)
+    ready, pending = get_ready([a, b], timeout=0.05)
+    assert ready == [] and pending == [a, b]
+    b.set_result("b")
+    ready, pending = get_ready([a, b, c])
+    assert ready == [b] and pending == [a, c] and b.result() == "b"
+    with pytest.raises(AssertionError):
+        b.set_result("again")
+    threading.Thread(target=lambda: (time.sleep(0.1), c.set_result(3), time.sleep(0.1), a.set_result(None))).start()
+    order = [f for f in wait_by_finish_order([a, c])]
+    assert order == [c, a] and a.completed and a.result() is None                      # None is a value, not "pending"
