@@ -274,6 +274,8 @@ def test_local_futures_and_get_ready():
     import threading
     import time
 
+    import pytest
+
     from steptronoss_b200.utils.comm_utils import LocalFuture, get_ready, wait_by_finish_order
 
     a, b, c = LocalFuture(), LocalFuture(), LocalFuture()
