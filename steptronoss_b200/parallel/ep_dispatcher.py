@@ -114,8 +114,15 @@ class AllToAllDispatcher:
         return out.to(y.dtype)
 
 
+PEER_KINDS = ("peer", "deepep", "nvlink")           # "deepep": the reference's name for its NVLink dispatcher
+ALLTOALL_KINDS = ("alltoall", "token", "nccl")      # "token": the reference's baseline TokenDispatcher
+
+
 def build_dispatcher(kind: str, group_name: str, num_experts: int, capacity_factor: float | None = None):
-    if kind == "peer":
+    kind = str(kind).lower()
+    if kind not in PEER_KINDS + ALLTOALL_KINDS:
+        raise ValueError(f"unknown MoE dispatcher {kind!r}; choose from {PEER_KINDS + ALLTOALL_KINDS}")
+    if kind in PEER_KINDS:
         from .peer_dispatcher import PeerMemoryDispatcher
 
         return PeerMemoryDispatcher(group_name, num_experts, capacity_factor)

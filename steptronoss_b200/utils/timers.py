@@ -129,21 +129,51 @@ def get_timers() -> Timers:
 
 
 class timeit:  # noqa: N801
-    """``@timeit("name", log_level=1)`` or ``with timeit("name"):``."""
+    """``@timeit("name", log_level=1)``, ``@timeit()`` (the function's name) or ``with timeit("name"):``.
 
-    def __init__(self, name: str, log_level: int = 2):
-        self.name, self.log_level = name, log_level
+    ``barrier`` joins the ranks and ``sync_device`` drains the GPU before the clock starts and before it stops, for
+    numbers that compare across ranks (both cost time: measurements only).  ``level`` is accepted as another
+    spelling of ``log_level`` (the reference's, ``steptronoss/timers.py:284-315``)."""
+
+    def __init__(self, name: str | None = None, log_level: int | None = None, level: int | None = None,
+                 barrier: bool = False, sync_device: bool = False):
+        self.name = name
+        self.log_level = log_level if log_level is not None else (level if level is not None else 2)
+        self.barrier, self.sync_device = barrier, sync_device
+
+    def _fence(self):
+        if self.sync_device:
+            import torch
+
+            if torch.cuda.is_available():
+                torch.cuda.synchronize()
+        if self.barrier:
+            import torch.distributed as dist
+
+            if dist.is_available() and dist.is_initialized():
+                dist.barrier()
+
+    def clone(self) -> "timeit":
+        return type(self)(self.name, self.log_level, None, self.barrier, self.sync_device)
 
     def __call__(self, fn):
+        scope = self.clone()
+        if scope.name is None:
+            scope.name = fn.__name__
+
         @functools.wraps(fn)
         def wrapper(*a, **k):
-            with get_timers().record(self.name, self.log_level):
+            with scope.clone():
                 return fn(*a, **k)
         return wrapper
 
     def __enter__(self):
+        if self.name is None:
+            raise ValueError("timeit used as a context needs a name")
+        self._fence()
         self._scope = get_timers().record(self.name, self.log_level)
         return self._scope.__enter__()
 
     def __exit__(self, *a):
+        self._fence()
         return self._scope.__exit__(*a)

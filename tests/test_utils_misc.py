@@ -322,3 +322,52 @@ def test_tb_record_reads_back_what_the_step_writer_wrote(tmp_path):
     long = text_chart(range(1000), height=5, width=50)
     assert all(len(line.split("|", 1)[1]) == 50 for line in long.split("\n"))
     assert text_chart([]) == "(no values)" and "*" in text_chart([1.0, 1.0])
+
+
+def test_timeit_takes_the_function_name_and_the_level_alias():
+    import time
+
+    import pytest
+
+    from steptronoss_b200.utils.timers import init_timers, timeit
+
+    timers = init_timers(log_level=1, use_event=False)
+
+    @timeit()
+    def plain_work():
+        time.sleep(0.01)
+
+    @timeit(level=2)
+    def too_fine():
+        pass
+
+    @timeit("synced", level=1, barrier=True, sync_device=True)           # no process group, no GPU: both are no-ops
+    def synced():
+        return 5
+
+    plain_work()
+    plain_work()
+    too_fine()
+    assert synced() == 5
+    rep = timers.report(reset=False)
+    assert set(rep) == {"synced"}                                        # default level 2 is finer than the timers' level 1
+    timers2 = init_timers(log_level=2, use_event=False)
+    plain_work()
+    too_fine()
+    rep = timers2.report()
+    assert rep["plain_work"] >= 9.0 and "too_fine" in rep
+    with pytest.raises(ValueError):
+        with timeit():
+            pass
+    init_timers(0)
+
+
+def test_dispatcher_names_of_the_reference_are_understood():
+    import pytest
+
+    from steptronoss_b200.parallel.ep_dispatcher import AllToAllDispatcher, build_dispatcher
+
+    for name in ("alltoall", "token", "Token"):
+        assert isinstance(build_dispatcher(name, "EP", 8), AllToAllDispatcher)
+    with pytest.raises(ValueError, match="unknown MoE dispatcher"):
+        build_dispatcher("carrier-pigeon", "EP", 8)
