@@ -60,3 +60,14 @@ def test_pp2_with_activations_kept_on_the_host_and_tp2_with_split_saved_inputs(s
     for rank, losses, norms, _ in res:
         assert _close(losses, single[0], 2e-5), (rank, losses, single[0])
         assert _close(norms, single[1], 1e-4), (rank, norms, single[1])
+
+
+def test_uneven_layer_map_with_an_empty_chunk_and_a_placeholder_layer():
+    """Three layers over 2 stages x 2 virtual chunks: the last chunk holds no layer at all, or one placeholder that
+    passes its input through; both reproduce the three-layer single-process run."""
+    base3 = dict(BASE, layers=3)
+    ref = run_single(dict(base3))
+    res = run_ranks(2, dict(base3, pp=2, vpp=2, set={"model_cfg.chunk_lengths": [1, 1, 1, 0]}))
+    assert _close(res[-1][1], ref[0], 2e-5), (res[-1][1], ref[0])
+    res = run_ranks(2, dict(base3, pp=2, vpp=2, set={"model_cfg.chunk_lengths": [1, 1, 1, 1], "model_cfg.noop_chunks": [3]}))
+    assert _close(res[-1][1], ref[0], 2e-5), (res[-1][1], ref[0])

@@ -11,7 +11,16 @@ from steptronoss_b200.models.decoder_model import DecoderLLMConfig
 
 
 class TinyModel(DecoderLLMConfig):
-    pass
+    chunk_lengths: list | None = None
+    """layers per (virtual) pipeline chunk, in chunk order; None: the even split of the base class"""
+    noop_chunks: list = []
+    """chunks whose layers are placeholders that pass their input through"""
+
+    def pp_vp_allocation(self, abs_pp_rank: int) -> list:
+        if self.chunk_lengths is None:
+            return super().pp_vp_allocation(abs_pp_rank)
+        opts = {"noop": True} if abs_pp_rank in self.noop_chunks else {}
+        return [dict(opts) for _ in range(self.chunk_lengths[abs_pp_rank])]
 
 
 class TinyExp(PretrainExp):
