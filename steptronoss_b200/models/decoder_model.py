@@ -138,6 +138,21 @@ class LlamaLikeModel(MegatronModule):
         self.sequence_parallel = bool(cfg.tp_cfg.sequence_parallel) and PM.size_of("TP") > 1
         self.name_parameters()
 
+    def name_parameters(self) -> None:
+        """Names under which gradient norms are logged: one per layer, the embeddings, the output head (with the
+        final norm), anything else (a vision encoder, ...) as ``other`` (reference ``model/decoder_model.py:288-301``)."""
+        for p in self.parameters():
+            p._log_name = "other"
+        for i in self.layer_ids:
+            for p in self.layers[str(i)].parameters():
+                p._log_name = f"layer{i}"
+        if hasattr(self, "tok_embeddings"):
+            for p in self.tok_embeddings.parameters():
+                p._log_name = "tok_embeddings"
+        if hasattr(self, "out_embeddings"):
+            for p in self.out_embeddings.parameters():
+                p._log_name = "output"
+
     # ------------------------------------------------------------------ stages
     def _cp_meta(self, data):
         if PM.size_of("CP") == 1:

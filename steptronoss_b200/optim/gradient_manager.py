@@ -294,6 +294,32 @@ class BaseGradientManager:
             z += (r.numel() - torch.count_nonzero(r)).float()
         return z
 
+    def _record_detailed_grad_norms(self, grad_scale: float) -> None:
+        """Squared norm of the reduced gradient per ``_log_name`` (set by the model's ``name_parameters``), each
+        element counted by exactly one rank: the owner under ZeRO-1, the first rank of the reduce group otherwise,
+        TP rank 0 for parameters that are equal on all TP ranks.  A debugging aid: it reads every gradient once more."""
+        from ..utils.metrics import GlobalMetrics
+
+        if "grad_norms" not in GlobalMetrics.metrics:
+            return
+        tp_rank = PM.rank_in("TP")
+        sums: dict = {}
+        for key, b in self.buckets.items():
+            if key.tp_replicated and tp_rank != 0:
+                continue
+            if self.shard_optimizer:
+                slots = b.own_slots()
+            else:
+                slots = b.slots if PM.rank_in(key.reduce_group) == 0 else []
+            for s in slots:
+                name = getattr(s.param, "_log_name", None)
+                if name is None:
+                    continue
+                sq = b.grad_buf[s.offset:s.offset + s.numel].double().pow(2).sum() * (grad_scale * grad_scale)
+                sums[name] = sums[name] + sq if name in sums else sq
+        for name, sq in sums.items():
+            GlobalMetrics.grad_norms.add(sq, subname=name)
+
     # ------------------------------------------------------------------ the step
     @torch.no_grad()
     def step(self):
@@ -307,6 +333,8 @@ class BaseGradientManager:
         grad_scale = self._reduce()
         self._compute_clip(grad_scale)
         zeros = self.count_zeros() if self.cfg.log_num_zeros_in_grad else None
+        if getattr(self.cfg, "log_detailed_grad_norms", False):
+            self._record_detailed_grad_norms(grad_scale)
         pg = self.param_groups[0]
         oc = self.opt_cfg
         for key, shard in self.shards.items():

@@ -34,6 +34,7 @@ class DecoderPretrainTrainer(BaseTrainer):
         self.writer = None
         self.train_iters = None
         self.history: list = []
+        self.last_metrics: dict = {}
         self.consumed_samples = 0
         self._t_last = time.perf_counter()
 
@@ -206,6 +207,7 @@ class DecoderPretrainTrainer(BaseTrainer):
                 f"{dt * 1e3:.1f} ms/iter | tokens-per-second-per-card {tps_card:.1f} | "
                 f"lr {self.scheduler.cur_lr:.3E} | global batch size {tc.global_batch_size} | "
                 f"grad-norm {float(metrics.get('grad_norm', 0.0)):.3f} | lm_loss {logs.get('lm_loss', 'n/a')}")
+        self.last_metrics = metrics                        # everything that was reduced for this log line
         self.history.append({"iteration": self.iteration, "ms_per_iter": dt * 1e3,
                              "lm_loss": float(metrics["lm_loss"]) if "lm_loss" in metrics else None,
                              "grad_norm": float(metrics.get("grad_norm", 0.0))})

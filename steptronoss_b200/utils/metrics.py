@@ -165,11 +165,36 @@ class ModelLayerMetric(GroupMetric):
 
 
 class GradNormMetric(GroupMetric):
-    """Per-parameter gradient norms (squared norms are summed over model-parallel ranks, then rooted)."""
+    """Gradient norms per named part of the model (``layer3``, ``tok_embeddings``, ``output`` ...).
+
+    ``add(squared_norm, subname=part)`` records what THIS rank contributes (its shards, its pipeline stage); ``reduce``
+    adds the contributions of all ranks and takes the root.  Ranks may hold different parts: the names are agreed on
+    first, so every rank joins the same all-reduce.  The last recorded step of the interval is reported."""
 
     def __init__(self) -> None:
         super().__init__()
         self.chain = [("last", "time")]
+
+    def reduce(self):
+        local = {}
+        for key, vals in self.sub.items():
+            if vals:
+                local[key] = float(torch.as_tensor(vals[-1]))
+        keys = sorted(local)
+        multi = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+        if multi:
+            every = [None] * dist.get_world_size()
+            dist.all_gather_object(every, keys)
+            keys = sorted(set().union(*every))
+        if not keys:
+            return {}
+        vec = torch.tensor([local.get(k, 0.0) for k in keys], dtype=torch.float64)
+        if multi:
+            on_gpu = dist.get_backend() == "nccl"
+            buf = vec.cuda() if on_gpu else vec
+            dist.all_reduce(buf)
+            vec = buf.cpu()
+        return {k: vec[i].sqrt().float() for i, k in enumerate(keys)}
 
 
 class AvgMetric(Metric):

@@ -42,6 +42,9 @@ def _worker(rank, world, port, exp_kwargs, steps, q):
             tr.training_log()
             losses.append(tr.history[-1]["lm_loss"])
         norms = [tr.history[i]["grad_norm"] for i in range(steps)]
+        parts = {k.split("/", 1)[1]: float(v) for k, v in tr.last_metrics.items() if k.startswith("grad_norms/")}
+        if parts:                                           # detailed norms were asked for: hand them back with the norms
+            norms = {"total": norms, "parts": parts}
         q.put((rank, losses, norms, None))
         torch.distributed.barrier()
     except BaseException as e:  # surface the failure to the parent instead of hanging it

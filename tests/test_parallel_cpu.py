@@ -71,3 +71,16 @@ def test_uneven_layer_map_with_an_empty_chunk_and_a_placeholder_layer():
     assert _close(res[-1][1], ref[0], 2e-5), (res[-1][1], ref[0])
     res = run_ranks(2, dict(base3, pp=2, vpp=2, set={"model_cfg.chunk_lengths": [1, 1, 1, 1], "model_cfg.noop_chunks": [3]}))
     assert _close(res[-1][1], ref[0], 2e-5), (res[-1][1], ref[0])
+
+
+@pytest.mark.parametrize("layout", [dict(pp=2), dict(), dict(tp=2, sp=True), dict(zero1=False)], ids=["pp2", "dp2_zero1", "tp2_sp", "dp2_allreduce"])
+def test_detailed_gradient_norms_agree_on_every_rank_and_add_up(layout):
+    """Per-part gradient norms: every rank reports the same numbers, each element is counted once whatever the
+    layout (pipeline stages hold different parts, ZeRO owners different parameters, TP ranks different shards)."""
+    res = run_ranks(2, dict(BASE, **layout, set={"trainer_cfg.log_detailed_grad_norms": True}))
+    parts0 = res[0][2]["parts"]
+    assert set(parts0) == {"layer0", "layer1", "tok_embeddings", "output"}
+    for rank, _, norms, _ in res:
+        assert norms["parts"] == pytest.approx(parts0, rel=1e-6)
+        total = norms["total"][-1]
+        assert sum(v * v for v in norms["parts"].values()) ** 0.5 == pytest.approx(total, rel=1e-4)

@@ -141,3 +141,18 @@ def test_optimizer_state_offload_and_zero_count_do_not_change_the_run(monkeypatc
     names = [m.name for m in CMT.marks][:5]
     assert names == ["before_cpu_offload_optimizer_state", "after_cpu_offload_optimizer_state", "after_forward_backward",
                      "after_cpu_backload_optimizer_state", "after_optimizer_step"]
+
+
+def test_detailed_gradient_norms_add_up_to_the_global_norm():
+    from steptronoss_b200.utils.metrics import GlobalMetrics
+
+    e = _make()
+    e.trainer_cfg.log_detailed_grad_norms = True
+    tr = e.trainer_cfg.get_trainer_cls()(exp=e)
+    tr.before_train()
+    tr.train_step()
+    parts = GlobalMetrics.grad_norms.reduce()
+    total = float(GlobalMetrics.grad_norm.reduce())
+    assert set(parts) == {"layer0", "layer1", "tok_embeddings", "output"}
+    assert all(float(v) > 0 for v in parts.values())
+    assert sum(float(v) ** 2 for v in parts.values()) ** 0.5 == pytest.approx(total, rel=1e-4)
