@@ -48,6 +48,16 @@ def analyze_dir(path: str) -> dict:
     return {"tp": tp, "pp": pp, "dp": dp, "files": n}
 
 
+def optimizer_dp_size(path: str) -> int:
+    """Number of data-parallel ranks that wrote optimizer files into ``path`` (0: none did)."""
+    dp = 0
+    for f in os.listdir(path):
+        m = _NAME.search(f)
+        if m and m.group(4):
+            dp = max(dp, int(m.group(3)) + 1)
+    return dp
+
+
 def _to_cpu(obj):
     if torch.is_tensor(obj):
         return obj.detach().to("cpu", copy=True)
@@ -236,7 +246,20 @@ class Checkpointer:
         opt_file = os.path.join(path, rank_file_name(opt=True))
         if not os.path.exists(opt_file):
             opt_file = os.path.join(path, src_name.replace(".pt", "_OPT.pt"))
-        if opts.optimizer and grad_manager is not None and os.path.exists(opt_file):
+        old_dp = optimizer_dp_size(path)
+        sharded = bool(getattr(grad_manager, "shard_optimizer", False))
+        if opts.optimizer and grad_manager is not None and sharded and old_dp not in (0, PM.size_of("DP")):
+            # the shards on disk were cut for another data-parallel size
+            if not getattr(self.cfg, "reshard_optimizer_state", False):
+                raise RuntimeError(
+                    f"checkpoint {path} holds optimizer shards of {old_dp} data-parallel ranks, this job has "
+                    f"{PM.size_of('DP')}: set checkpoint_cfg.reshard_optimizer_state=True to re-cut them, or load "
+                    f"without the optimizer (checkpoint_cfg.load_option.optimizer=False)")
+            prefix = f"TP{PM.rank_in('TP'):02d}_PP{PM.rank_in('PP'):03d}_DP"
+            grad_manager.load_resharded_state(
+                lambda r: torch.load(os.path.join(path, f"{prefix}{r:03d}_OPT.pt"), map_location="cpu", weights_only=False),
+                old_dp, strict=bool(getattr(self.cfg, "reshard_optimizer_strict", True)))
+        elif opts.optimizer and grad_manager is not None and os.path.exists(opt_file):
             grad_manager.load_state_dict(torch.load(opt_file, map_location="cpu", weights_only=False))
         elif opts.model and grad_manager is not None and hasattr(grad_manager, "refresh_masters_from_params"):
             grad_manager.refresh_masters_from_params()

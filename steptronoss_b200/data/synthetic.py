@@ -82,10 +82,15 @@ class SyntheticPackedLoader:
         return s
 
     def state_dict(self) -> dict:
-        return {"index": self.index}
+        # the position in the GLOBAL sample stream travels too, so that a job with another data-parallel size
+        # continues with the sample that comes next
+        return {"index": self.index, "consumed": self.index * self.dp_size}
 
     def load_state_dict(self, sd: dict) -> None:
-        self.index = int(sd["index"])
+        if "consumed" in sd:
+            self.index = -(-int(sd["consumed"]) // self.dp_size)
+        else:
+            self.index = int(sd["index"])
 
 
 class SyntheticDataConfig(DataConfig):

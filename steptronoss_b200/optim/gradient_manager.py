@@ -370,6 +370,56 @@ class BaseGradientManager:
         self._refresh_params()
         self.wait_param_gather()
 
+    def load_resharded_state(self, read_shard, old_dp: int, strict: bool = True) -> None:
+        """Restore optimizer state written by a job with ANOTHER data-parallel size.
+
+        ``read_shard(r)`` returns what old DP rank ``r`` saved (``state_dict()`` of its manager).  Every saved shard
+        lists which parameters it holds and where (``layout``); the state of each parameter this rank owns now is
+        cut out of the old owner's shard by name.  Old files are read one at a time.  ``strict``: a parameter that
+        the checkpoint lacks is an error; otherwise it starts from its current weights with zero moments."""
+        if any(k.reduce_group == "EDP" for k in self.buckets) and PM.size_of("EP") > 1:
+            raise NotImplementedError("optimizer state of expert-parallel buckets cannot be resharded; "
+                                      "load the weights only (load_option.none(but=['model']))")
+        first = read_shard(0)
+        first = first.get("optimizer", first)
+        self.step_count = int(first.get("step", 0))
+        for g, saved in zip(self.param_groups, first.get("param_groups", [])):
+            g.update(saved)
+        self.refresh_masters_from_params()                       # the starting point of whatever is not found
+        wanted: dict = {}                                        # old owner -> [(bucket key, my slot, old offset)]
+        missing = []
+        for key, shard in self.shards.items():
+            old = {name: (owner, off, n) for name, owner, off, n in first.get("layout", {}).get(str(key), [])}
+            for s in shard.bucket.own_slots():
+                if s.name in old and old[s.name][2] == s.numel:
+                    wanted.setdefault(old[s.name][0], []).append((key, s, old[s.name][1]))
+                else:
+                    missing.append(s.name)
+        muon_mine = {e["slot"].name for e in self.muon.entries} if self.muon is not None else set()
+        muon_found: dict = {}
+        for r in range(old_dp):
+            sd = first if r == 0 else read_shard(r)
+            sd = sd.get("optimizer", sd)
+            for key, s, old_off in wanted.get(r, []):
+                saved = sd["buckets"][str(key)]
+                base = r * saved["master"].numel()               # the old shard covered [base, base + shard size)
+                shard = self.shards[key]
+                for name in ("master", "exp_avg", "exp_avg_sq"):
+                    getattr(shard, name)[s.offset - shard.lo:s.offset - shard.lo + s.numel].copy_(
+                        saved[name][old_off - base:old_off - base + s.numel])
+            for name, st in sd.get("muon", {}).items():
+                if name in muon_mine:
+                    muon_found[name] = st
+        if self.muon is not None:
+            self.muon.load_state_dict(muon_found)
+            missing += sorted(muon_mine - set(muon_found))
+        if missing and strict:
+            raise RuntimeError(f"optimizer state of {len(missing)} parameters is not in the checkpoint: {missing[:5]} ...")
+        for shard in self.shards.values():
+            shard.bucket.param_buf[shard.lo:shard.hi].copy_(shard.master)
+        self._refresh_params()
+        self.wait_param_gather()
+
     def refresh_masters_from_params(self) -> None:
         """After loading model weights without optimizer state: fp32 masters follow the parameters."""
         for shard in self.shards.values():

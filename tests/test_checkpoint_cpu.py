@@ -99,3 +99,61 @@ def test_hf_view_beside_the_checkpoint_starts_a_new_run_and_save_options_drop_pa
     tr.train_step()
     moved = max(float((v - before[k]).abs().max()) for k, v in tr.models[0].named_parameters())
     assert 0 < moved < 0.05                               # one small step away from the loaded weights, not a jump back to the initialisation
+
+
+def _dp2_save_worker(rank, world, port, save_dir, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    torch.set_num_threads(1)
+    try:
+        from steptronoss_b200.parallel.state import PM
+
+        PM.initialize(backend="gloo")
+        tr = _train(_exp(save_dir, 3, 3))
+        q.put((rank, [h["lm_loss"] for h in tr.history], None))
+        torch.distributed.barrier()
+    except BaseException:
+        import traceback
+
+        q.put((rank, None, traceback.format_exc()))
+        raise
+
+
+def test_optimizer_shards_are_recut_when_the_data_parallel_size_changes(tmp_path):
+    """Two ZeRO-1 ranks write a checkpoint; one process resumes from it.  Without ``reshard_optimizer_state`` the
+    loader says what to do; with it the run continues exactly like an uninterrupted single-process run."""
+    import pytest
+    import torch.multiprocessing as mp
+
+    from tests.dist_helpers import free_port
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=_dp2_save_worker, args=(r, 2, port, str(tmp_path / "two"), q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        for _ in range(2):
+            rank, losses, err = q.get(timeout=300)
+            assert err is None, err
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
+    it = open(tmp_path / "two" / "ckpt_test" / "latest_ckpt").read().strip()
+    assert sorted(f for f in os.listdir(it) if f.endswith("_OPT.pt")) == ["TP00_PP000_DP000_OPT.pt", "TP00_PP000_DP001_OPT.pt"]
+
+    full = _train(_exp(tmp_path / "one", 6, None))
+    ref = {k: v.detach().clone() for k, v in full.models[0].named_parameters()}
+
+    e = _exp(tmp_path / "two", 6, None)
+    with pytest.raises(RuntimeError, match="reshard_optimizer_state"):
+        e.trainer_cfg.get_trainer_cls()(exp=e).before_train()
+    e = _exp(tmp_path / "two", 6, None)
+    e.checkpoint_cfg.reshard_optimizer_state = True
+    resumed = _train(e)
+    assert resumed.iteration == 6
+    for k, v in resumed.models[0].named_parameters():
+        assert torch.allclose(v, ref[k], atol=1e-6), k
