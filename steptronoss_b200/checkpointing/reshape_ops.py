@@ -472,6 +472,10 @@ def build_qwen_reshaper(cfg, layer_ids, first_stage: bool, last_stage: bool) -> 
         scripts.append(Script(src=f"{s}.self_attn.[qkv]_proj.weight", dst=f"{d}.attention.wqkv.weight",
                               op=GQAMergeQKV(ac.num_attention_groups, ac.head_dim or cfg.hidden_size // ac.num_attention_heads)
                               + KeepThisTP() + Rename(f"{d}.attention.wqkv.weight: {s}.self_attn.qkv_proj.weight")))
+        if getattr(ac, "use_qkv_bias", False):       # Qwen2-style projections carry a bias on q, k and v
+            scripts.append(Script(src=f"{s}.self_attn.[qkv]_proj.bias", dst=f"{d}.attention.wqkv.bias",
+                                  op=GQAMergeQKVBias(ac.num_attention_groups, ac.head_dim or cfg.hidden_size // ac.num_attention_heads)
+                                  + KeepThisTP() + Rename(f"{d}.attention.wqkv.bias: {s}.self_attn.qkv_proj.bias")))
         scripts.append(Script(src=f"{s}.self_attn.o_proj.weight", dst=f"{d}.attention.wo.weight",
                               op=RowParallel() + KeepThisTP() + Rename(f"{d}.attention.wo.weight: {s}.self_attn.o_proj.weight")))
         for hf_n, nat_n in (("input_layernorm", "attention_norm"), ("post_attention_layernorm", "ffn_norm"),

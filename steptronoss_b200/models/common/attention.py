@@ -85,7 +85,7 @@ class GroupedQueryAttention(nn.Module):
         if self.use_gate:
             blocks.append(nh)
         self.wqkv = ColumnParallelLinear(cfg.hidden_size, sum(blocks), params_dtype=dtype, sequence_parallel=sp,
-                                         blocks=blocks)
+                                         blocks=blocks, bias=bool(cfg.use_qkv_bias))
         self.wo = RowParallelLinear(nh * D, cfg.hidden_size, params_dtype=dtype, sequence_parallel=sp)
         self.use_qk_norm = cfg.qk_norm_enabled
         if self.use_qk_norm:

@@ -120,7 +120,8 @@ def init_parallel_weight_(param: torch.Tensor, name: str, seed: int, std: float 
 
 class ColumnParallelLinear(nn.Module):
     def __init__(self, input_size: int, output_size: int, *, params_dtype=torch.bfloat16, gather_output: bool = False,
-                 sequence_parallel: bool = False, group: str = "TP", blocks=None, out_dtype=None, device=None):
+                 sequence_parallel: bool = False, group: str = "TP", blocks=None, out_dtype=None, device=None,
+                 bias: bool = False):
         super().__init__()
         self.group = group
         world = PM.size_of(group)
@@ -135,6 +136,11 @@ class ColumnParallelLinear(nn.Module):
         self.out_dtype = out_dtype
         self.weight = nn.Parameter(torch.empty(self.output_size_per_partition, input_size, dtype=params_dtype, device=device))
         set_tensor_model_parallel_attributes(self.weight, world > 1, 0, 1, blocks, group)
+        self.bias = None
+        if bias:                                   # split like the rows of the weight; starts at zero
+            self.bias = nn.Parameter(torch.zeros(self.output_size_per_partition, dtype=params_dtype, device=device))
+            set_tensor_model_parallel_attributes(self.bias, world > 1, 0, 1, blocks, group)
+            self.bias.init_kind = "zeros"
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.sequence_parallel:
@@ -144,6 +150,8 @@ class ColumnParallelLinear(nn.Module):
         else:
             x = mappings.copy_to_tensor_model_parallel_region(x, self.group)
             y = linear(x, self.weight, self.out_dtype)
+        if self.bias is not None:
+            y = y + self.bias.to(y.dtype)
         if self.gather_output:
             y = mappings.gather_from_tensor_model_parallel_region(y, self.group)
         return y

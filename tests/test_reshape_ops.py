@@ -71,3 +71,37 @@ def test_qwen_model_hf_round_trip(tmp_path):
     m2.load_hf_state_dict(HFWeights(str(tmp_path)))
     for (n, p), (_, q) in zip(m.named_parameters(), m2.named_parameters()):
         assert torch.equal(p, q), n
+
+
+def test_qkv_bias_trains_and_round_trips_through_the_hf_layout():
+    """``use_qkv_bias`` (Qwen2-style): the fused projection gets a bias that starts at zero, receives gradients, and
+    maps to ``q_proj.bias / k_proj.bias / v_proj.bias`` and back."""
+    import torch
+
+    from steptronoss_b200.models.qwen_dense import QwenModel
+    from steptronoss_b200.parallel.state import PM
+    from tests.tiny_exp import make_tiny_exp
+
+    PM.initialize()
+    exp = make_tiny_exp(gbs=1, seq=32, iters=1, layers=1, hidden=32, heads=4, kv_heads=2, head_dim=8, ffn=64, vocab=64)
+    cfg = exp.model_cfg
+    cfg.attn_cfg.use_qkv_bias = True
+    PM.set_mesh(cfg.parallel_cfg)
+    model = QwenModel(cfg=cfg, layer_map=cfg.build_layer_map())
+    model.init_weights(0, 0.02)
+    bias = model.layers["0"].attention.wqkv.bias
+    assert bias.shape == (4 * 8 + 2 * 2 * 8,) and float(bias.abs().sum()) == 0.0
+    ids = torch.randint(0, 64, (1, 32))
+    out = model(input_ids=ids, labels=ids, cu_seqlens=torch.tensor([0, 32], dtype=torch.int32), max_seq_len=32,
+                position_id=torch.arange(32, dtype=torch.int32))
+    (out["loss"] if isinstance(out, dict) else out.float().mean()).backward()
+    assert bias.grad is not None and float(bias.grad.abs().sum()) > 0
+    with torch.no_grad():
+        bias.copy_(torch.arange(64.0))
+    hf = model.hf_state_dict()
+    q, k, v = (hf[f"model.layers.0.self_attn.{n}_proj.bias"] for n in "qkv")
+    assert q.tolist() == list(range(32)) and k.tolist() == list(range(32, 48)) and v.tolist() == list(range(48, 64))
+    other = QwenModel(cfg=cfg, layer_map=cfg.build_layer_map())
+    other.init_weights(1, 0.02)
+    other.load_hf_state_dict(hf)
+    assert torch.equal(other.layers["0"].attention.wqkv.bias, bias)
