@@ -218,19 +218,40 @@ class Checkpointer:
         main = None
         mine = os.path.join(path, rank_file_name())
         reader = PM.rank_in("DP") == 0
-        if reader:
-            main = torch.load(os.path.join(path, src_name), map_location="cpu", weights_only=False)
-        elif os.path.exists(mine):
-            main = torch.load(mine, map_location="cpu", weights_only=False)
-        if PM.size_of("DP") > 1:
+        ep = PM.size_of("EP") > 1
+        share = bool(getattr(self.cfg, "broadcast_from_dp0", True)) and PM.size_of("DP") > 1
+
+        def load(file):
+            return torch.load(file, map_location="cpu", weights_only=False)
+
+        def model_part(state: dict, experts: bool) -> dict:
+            """The model entries of a rank file, keeping expert tensors only (or everything else only)."""
+            return {k: {n: t for n, t in sd.items() if (".experts." in n) == experts}
+                    for k, sd in state.items() if k.startswith("model")}
+
+        own = load(mine) if os.path.exists(mine) else {}
+        # everything but expert weights is equal inside a DP group: the first replica's file holds it.  It reads and
+        # broadcasts; with broadcast_from_dp0 off every rank reads that file itself (file-system traffic, no collective)
+        first = own if reader else (None if share else load(os.path.join(path, src_name)))
+        common = None
+        if first is not None:
+            common = {k: v for k, v in first.items() if k in ("extra", "scheduler")}
+            common.update(model_part(first, experts=False) if ep else {k: v for k, v in first.items() if k.startswith("model")})
+        if share:
             dev = "cuda" if torch.cuda.is_available() and PM.backend == "nccl" else "cpu"
-            shared = {k: v for k, v in (main or {}).items() if k.startswith("model") or k in ("extra", "scheduler")}
-            shared = broadcast_tensors(shared if reader else None, src=PM.ranks_of("DP")[0], group=PM.group_of("DP"),
-                                       device=dev)
-            own = main or {}
-            main = dict(shared)
-            if "rng_state" in own:
-                main["rng_state"] = own["rng_state"]
+            common = broadcast_tensors(common, src=PM.ranks_of("DP")[0], group=PM.group_of("DP"), device=dev)
+        main = dict(common)
+        if ep:
+            # expert weights differ between the EP ranks of a DP group; they are equal inside an EDP group, whose first
+            # rank wrote them into its own file
+            experts = model_part(own, experts=True) if PM.rank_in("EDP") == 0 else None
+            if PM.size_of("EDP") > 1:
+                dev = "cuda" if torch.cuda.is_available() and PM.backend == "nccl" else "cpu"
+                experts = broadcast_tensors(experts, src=PM.ranks_of("EDP")[0], group=PM.group_of("EDP"), device=dev)
+            for k, sd in (experts or {}).items():
+                main[k] = {**main.get(k, {}), **sd}
+        if "rng_state" in own:
+            main["rng_state"] = own["rng_state"]
         extra = main.get("extra", {})
         if opts.model:
             for i, m in enumerate(models):
@@ -239,7 +260,7 @@ class Checkpointer:
                     um = unwrap_model(m)
                     missing = um.load_state_dict(main[key], strict=False)
                     lost = [k for k in missing.missing_keys if not k.endswith("_extra_state")]
-                    if lost and getattr(self.cfg, "strict_load_model", False) and PM.size_of("EP") == 1:
+                    if lost and getattr(self.cfg, "strict_load_model", False):
                         raise RuntimeError(f"checkpoint {path} lacks {len(lost)} tensors of {key}: {lost[:5]} ...")
                     if lost:
                         logger.warning(f"missing keys when loading {key}: {lost[:5]} ...", at=None)

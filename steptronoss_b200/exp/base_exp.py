@@ -236,8 +236,9 @@ class MegatronPPModelConfig(AbstractModelConfig):
     variable_seq_lengths: bool = False
     pp_comm_shape: tuple | None = None
     check_nan: bool = False
-    """When True a device-side finite check of the stage output is folded into the kernel status
-    word (no host synchronisation); the reference's per-forward host check is not reproduced."""
+    """When True every stage output is checked for NaN/Inf: on the GPU by a kernel that sets a device flag (no host
+    synchronisation; the trainer reads the flag when it logs and raises), on the CPU at once.  The reference
+    checks on the host after every forward (``core/pipeline_parallel/schedules.py:204-205``)."""
     pipeline_activation_cpu_offload: bool = False
     fp32_residual_connection: bool = False
     fp32_output: bool = True

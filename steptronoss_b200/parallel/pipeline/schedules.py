@@ -94,6 +94,10 @@ class FWBWScheduler:
         data["loss_scale"] = loss_scale
         with get_timers().record("forward-step", 2):
             output = model(**data)
+        if getattr(self.config, "check_nan", False):
+            from ...utils.dev_utils import note_nonfinite
+
+            note_nonfinite(output, f"output of pipeline stage {PM.rank_in('PP')} (chunk {vp_rank})")
         if _unwrap(model).is_last_stage:
             if self.collect_output:
                 self._collected.append(output)

@@ -15,6 +15,7 @@ import torch
 from ..models.module import Float16Module, unwrap_model
 from ..ops import native
 from ..parallel.state import PM, set_mpu_random_seed
+from ..utils.dev_utils import raise_if_nonfinite
 from ..utils.logger import logger
 from ..utils.memory_tracker import CMT
 from ..utils.metrics import GlobalMetrics
@@ -195,6 +196,7 @@ class DecoderPretrainTrainer(BaseTrainer):
         if torch.cuda.is_available():
             torch.cuda.synchronize()
             native.raise_if_kernel_error()
+            raise_if_nonfinite()
             now = time.perf_counter()
         dt = (now - self._t_last) / tc.log_interval
         self._t_last = now

@@ -129,6 +129,45 @@ def check_nan(tensor, flag: torch.Tensor | None = None):
     return flag
 
 
+_NONFINITE_FLAGS: dict = {}
+
+
+def nonfinite_flag(device) -> torch.Tensor:
+    """The job-wide "a checked tensor held NaN/Inf" flag of a device (int32, lives on that device)."""
+    device = torch.device(device)
+    if device not in _NONFINITE_FLAGS:
+        _NONFINITE_FLAGS[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _NONFINITE_FLAGS[device]
+
+
+def note_nonfinite(obj, where: str = "") -> None:
+    """Check every floating tensor in ``obj`` (tensor, dict, list).  On the GPU the result goes into the device flag
+    without a host synchronisation (read it later with :func:`raise_if_nonfinite`); on the CPU a bad value raises at
+    once, naming ``where``."""
+    if torch.is_tensor(obj):
+        if not obj.is_floating_point():
+            return
+        if obj.is_cuda:
+            check_nan(obj.detach(), nonfinite_flag(obj.device))
+        elif not bool(torch.isfinite(obj).all()):
+            raise FloatingPointError(f"non-finite values in {where or 'a checked tensor'}")
+    elif isinstance(obj, dict):
+        for k, v in obj.items():
+            note_nonfinite(v, f"{where}[{k!r}]" if where else repr(k))
+    elif isinstance(obj, (list, tuple)):
+        for i, v in enumerate(obj):
+            note_nonfinite(v, f"{where}[{i}]")
+
+
+def raise_if_nonfinite() -> None:
+    """Read the device flags (a host read: call where the device is synchronised anyway) and raise if one is set."""
+    for dev, flag in _NONFINITE_FLAGS.items():
+        if int(flag) != 0:
+            flag.zero_()
+            raise FloatingPointError(f"a checked tensor on {dev} held NaN or Inf since the last check "
+                                     f"(model_cfg.check_nan); the stage outputs of this interval are suspect")
+
+
 class Stopwatch:
     def __enter__(self):
         self.t0 = time.perf_counter()

@@ -156,3 +156,15 @@ def test_detailed_gradient_norms_add_up_to_the_global_norm():
     assert set(parts) == {"layer0", "layer1", "tok_embeddings", "output"}
     assert all(float(v) > 0 for v in parts.values())
     assert sum(float(v) ** 2 for v in parts.values()) ** 0.5 == pytest.approx(total, rel=1e-4)
+
+
+def test_check_nan_names_the_stage_whose_output_went_bad():
+    e = _make()
+    e.model_cfg.check_nan = True
+    tr = e.trainer_cfg.get_trainer_cls()(exp=e)
+    tr.before_train()
+    tr.train_step()                                              # finite: nothing happens
+    with torch.no_grad():
+        next(tr.models[0].parameters()).fill_(float("nan"))
+    with pytest.raises(FloatingPointError, match="pipeline stage 0"):
+        tr.train_step()
