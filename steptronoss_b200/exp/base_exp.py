@@ -233,6 +233,8 @@ class MegatronTPConfig(AbstractModelConfig):
 class MegatronPPModelConfig(AbstractModelConfig):
     params_dtype: torch.dtype = torch.bfloat16
     overlap_p2p_comm: bool = True
+    """accepted for compatibility: the interleaved schedule here always pairs a send with the receive it can overlap
+    in one batched exchange per step and waits for it before the next compute, whatever this says"""
     variable_seq_lengths: bool = False
     pp_comm_shape: tuple | None = None
     check_nan: bool = False

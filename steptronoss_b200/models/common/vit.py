@@ -220,6 +220,7 @@ class VisionAttention(nn.Module):
         grid = cfg.image_size // cfg.patch_size
         self.rope = EncoderRope2D(self.head_dim, grid, grid, use_cls_token=cfg.use_cls_token, theta=cfg.rope_theta,
                                   theta_rescale_factor=cfg.rope_theta_rescale_factor) if cfg.use_rope2d else None
+        self.attention_dropout = float(cfg.attention_dropout)
         self.qkv_proj = TPColumnLinear(cfg.hidden_size, cfg.hidden_size * 3, bias=True)
         self.out_proj = TPRowLinear(cfg.hidden_size, cfg.hidden_size, bias=True, input_is_parallel=True)
 
@@ -229,6 +230,11 @@ class VisionAttention(nn.Module):
         q, k, v = self.qkv_proj(x).reshape(B, L, 3, h, D).unbind(dim=2)
         if self.rope is not None:
             q, k = self.rope(q, k, grid_hw)
+        if self.attention_dropout > 0.0 and self.training:
+            # dropout on the attention probabilities is not part of the flash kernel: the library path is used
+            o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                               dropout_p=self.attention_dropout).transpose(1, 2)
+            return self.out_proj(o.reshape(B, L, h * D))
         cu = torch.arange(0, (B + 1) * L, L, dtype=torch.int32, device=x.device)  # one segment per image
         fn = attention if (D == 128 and x.is_cuda) else attention_reference
         args = (q.reshape(B * L, h, D), k.reshape(B * L, h, D), v.reshape(B * L, h, D), cu, cu)

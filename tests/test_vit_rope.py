@@ -55,3 +55,30 @@ def test_attention_block_with_and_without_rope():
     x = torch.randn(1, 4, 8)
     a, b = plain(x, grid_hw=(2, 2)), rope(x, grid_hw=(2, 2))
     assert a.shape == b.shape == (1, 4, 8) and torch.isfinite(b).all() and not torch.allclose(a, b)
+
+
+def test_attention_dropout_acts_in_training_only():
+    from steptronoss_b200.models.common.vit import VisionAttention, VisionTransformerConfig
+    from steptronoss_b200.parallel.state import PM
+
+    PM.initialize()
+    cfg = VisionTransformerConfig()
+    cfg.image_size, cfg.patch_size, cfg.hidden_size, cfg.num_attention_heads, cfg.use_cls_token = 4, 2, 8, 2, False
+    cfg.attention_dropout = 0.5
+    PM.set_mesh(cfg.parallel_cfg)
+    torch.manual_seed(0)
+    attn = VisionAttention(cfg)
+    for p in attn.parameters():
+        torch.nn.init.normal_(p, std=0.5)
+    x = torch.randn(2, 4, 8)
+    attn.eval()
+    a, b = attn(x, (2, 2)), attn(x, (2, 2))
+    assert torch.equal(a, b)                                       # evaluation: no dropout
+    attn.train()
+    c, d = attn(x, (2, 2)), attn(x, (2, 2))
+    assert not torch.allclose(c, d) and not torch.allclose(c, a)   # training: a fresh mask every call
+    cfg.attention_dropout = 0.0
+    plain = VisionAttention(cfg)
+    plain.load_state_dict(attn.state_dict())
+    plain.train()
+    assert torch.allclose(plain(x, (2, 2)), a, atol=1e-5)          # both paths compute the same attention
