@@ -195,6 +195,8 @@ class PPOTrainer(BaseTrainer):
         while self.iteration < tc.train_iters:
             t0 = time.perf_counter()
             self.call_hooks("before_step")
+            if self.eval_due():
+                self.eval()
             self.train_step()
             self.call_hooks("after_step")
             if torch.cuda.is_available():
@@ -442,8 +444,33 @@ class PPOTrainer(BaseTrainer):
         logger.info(" | ".join(f"{k}: {v}" for k, v in logs.items()), at=-1)
         CMT.report_over_world() if hasattr(CMT, "report_over_world") else None
 
+    def eval_due(self) -> bool:
+        """Evaluation runs before the training step of every ``eval_interval``-th iteration (the very first one
+        unless ``skip_first_eval``), when the experiment has an ``eval_cfg``."""
+        tc = self.ppo_cfg
+        every = getattr(tc, "eval_interval", None)
+        if not every or getattr(self.exp, "eval_cfg", None) is None:
+            return False
+        if self.iteration % every:
+            return False
+        return not (self.iteration == 0 and getattr(tc, "skip_first_eval", False))
+
     def eval(self):
-        pass
+        """Run the experiment's benchmarks against the inference servers (they hold the current policy after the
+        last weight push) on the logging rank; the scores go to the log and the writer.  Other ranks wait."""
+        cfg = getattr(self.exp, "eval_cfg", None)
+        summary = None
+        if cfg is not None and PM.world_rank == PM.world_size - 1:
+            summary = cfg.eval()
+            for bench, res in (summary or {}).items():
+                metric = res.get("metric", {}) if isinstance(res, dict) else {}
+                for k, v in metric.items():
+                    if isinstance(v, (int, float)):
+                        logger.info(f"eval @ iteration {self.iteration}: {bench}/{k} = {v:.4f}", at=None)
+                        if self.writer is not None:
+                            self.writer.add_scalar(f"eval/{bench}/{k}", v, self.iteration)
+        sync_point("evaluation done")
+        return summary
 
     # ------------------------------------------------------------------------------------ checkpoints
     def save_checkpoint(self, sync: bool = False):

@@ -176,3 +176,29 @@ def test_get_normalizer_values_and_non_finite_inputs():
     for bad in (float("nan"), float("inf")):
         with pytest.raises(ValueError, match="non-finite"):
             get_normalizer(torch.tensor([1.0, bad, 3.0]))
+
+
+def test_evaluation_schedule_and_score_logging():
+    import types
+
+    from steptronoss_b200.trainers.ppo_trainer import PPOTrainer
+
+    logged = []
+    writer = types.SimpleNamespace(add_scalar=lambda k, v, it: logged.append((k, v, it)))
+    evals = []
+    eval_cfg = types.SimpleNamespace(eval=lambda: (evals.append(1), {"AIME2025": {"metric": {"score_avg": 0.25, "by": {"x": 1}}}})[1])
+    tr = types.SimpleNamespace(ppo_cfg=types.SimpleNamespace(eval_interval=2, skip_first_eval=True),
+                               exp=types.SimpleNamespace(eval_cfg=eval_cfg), iteration=0, writer=writer)
+    due = []
+    for it in range(5):
+        tr.iteration = it
+        due.append(PPOTrainer.eval_due(tr))
+    assert due == [False, False, True, False, True]
+    tr.ppo_cfg.skip_first_eval, tr.iteration = False, 0
+    assert PPOTrainer.eval_due(tr)
+    tr.exp.eval_cfg = None
+    assert not PPOTrainer.eval_due(tr)
+    tr.exp.eval_cfg, tr.iteration = eval_cfg, 4
+    summary = PPOTrainer.eval(tr)
+    assert evals == [1] and summary["AIME2025"]["metric"]["score_avg"] == 0.25
+    assert logged == [("eval/AIME2025/score_avg", 0.25, 4)]
