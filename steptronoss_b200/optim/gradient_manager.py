@@ -302,6 +302,7 @@ class BaseGradientManager:
 
         if "grad_norms" not in GlobalMetrics.metrics:
             return
+        GlobalMetrics.grad_norms.armed = True
         tp_rank = PM.rank_in("TP")
         sums: dict = {}
         for key, b in self.buckets.items():

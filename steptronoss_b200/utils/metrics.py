@@ -174,8 +174,13 @@ class GradNormMetric(GroupMetric):
     def __init__(self) -> None:
         super().__init__()
         self.chain = [("last", "time")]
+        self.armed = False
+        """set by the producer on EVERY rank of a job that records detailed norms, also on ranks that contribute
+        nothing: only then does ``reduce`` talk to the other ranks (no collective in jobs that do not use this)"""
 
     def reduce(self):
+        if not self.armed:
+            return {}
         local = {}
         for key, vals in self.sub.items():
             if vals:
