@@ -168,3 +168,21 @@ def test_check_nan_names_the_stage_whose_output_went_bad():
         next(tr.models[0].parameters()).fill_(float("nan"))
     with pytest.raises(FloatingPointError, match="pipeline stage 0"):
         tr.train_step()
+
+
+@pytest.mark.parametrize("change", [
+    {"model_cfg.recompute": ["attention", "ffn_norm"]},
+    {"model_cfg.recompute": True, "model_cfg.recompute_num_layers": 1},
+    {"model_cfg.ffn_cfg.swiglu_recompute_silu_out_proj": True},
+], ids=["recompute_parts", "recompute_first_layer", "swiglu_in_down_projection"])
+def test_memory_options_leave_the_loss_curve_unchanged(change):
+    base, _, _ = _run(_make(), steps=3)
+    e = _make()
+    for path, value in change.items():
+        node = e
+        *parents, leaf = path.split(".")
+        for part in parents:
+            node = getattr(node, part)
+        setattr(node, leaf, value)
+    got, _, _ = _run(e, steps=3)
+    assert got == pytest.approx(base, rel=1e-6)
