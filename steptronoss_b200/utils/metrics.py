@@ -305,6 +305,12 @@ class MetricHolder:
         metric.name = name
         self.metrics[name] = metric
 
+    def __setattr__(self, name: str, value) -> None:
+        if isinstance(value, Metric):           # ``holder.loss = Metric().mean("time")`` registers, like ``register``
+            self.register(name, value)
+        else:
+            object.__setattr__(self, name, value)
+
     def batch_register(self, cfg) -> None:
         for k, v in cfg.items():
             if isinstance(v, Metric):

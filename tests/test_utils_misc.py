@@ -371,3 +371,73 @@ def test_dispatcher_names_of_the_reference_are_understood():
         assert isinstance(build_dispatcher(name, "EP", 8), AllToAllDispatcher)
     with pytest.raises(ValueError, match="unknown MoE dispatcher"):
         build_dispatcher("carrier-pigeon", "EP", 8)
+
+
+def test_retry_on_sync_and_async_with_backoff():
+    import asyncio
+
+    import pytest
+
+    from steptronoss_b200.utils.general import retry_on
+
+    seen = []
+
+    @retry_on((ValueError,), retries=3, delay=0.001, on_retry=lambda e, n: seen.append((str(e), n)))
+    def flaky(box=[0]):
+        box[0] += 1
+        if box[0] < 3:
+            raise ValueError(f"try {box[0]}")
+        return box[0]
+
+    assert flaky() == 3 and seen == [("try 1", 0), ("try 2", 1)]
+
+    @retry_on((ValueError,), retries=1, delay=0.001)
+    def hopeless():
+        raise ValueError("always")
+
+    with pytest.raises(ValueError, match="always"):
+        hopeless()
+
+    @retry_on((ValueError,), retries=2, delay=0.001)
+    def other_error():
+        raise KeyError("not retried")
+
+    with pytest.raises(KeyError):
+        other_error()
+
+    calls = []
+
+    @retry_on((RuntimeError,), retries=2, delay=0.001)
+    async def aflaky():
+        calls.append(1)
+        if len(calls) < 2:
+            raise RuntimeError("once")
+        return "ok"
+
+    assert asyncio.run(aflaky()) == "ok" and len(calls) == 2
+
+
+def test_metric_holder_fork_and_disable_and_inverse_reshape_op():
+    import torch
+
+    from steptronoss_b200.checkpointing.reshape_ops import ColumnParallel, Inverse
+    from steptronoss_b200.utils.metrics import GroupMetric, Metric, MetricHolder
+
+    h = MetricHolder()
+    h.loss = Metric().mean("time")
+    h.per_layer = GroupMetric().mean("time")
+    h.loss.add(1.0)
+    h.per_layer.add(2.0, subname="layer0")
+    with h.fork():                                               # e.g. an evaluation pass in the middle of an interval
+        h.loss.add(100.0)
+        assert float(h.loss.reduce()) == 100.0
+    with h.disable():
+        h.loss.add(1000.0)                                       # dropped
+    h.loss.add(3.0)
+    out = h.reduce_all()
+    assert float(out["loss"]) == 2.0 and float(out["per_layer/layer0"]) == 2.0
+
+    w = torch.arange(12.0).reshape(4, 3)
+    merged = Inverse(ColumnParallel()).forward({"w": list(w.chunk(2))})      # the backward of a split is the concatenation
+    assert torch.equal(merged["w"], w)
+    assert [t.tolist() for t in Inverse(ColumnParallel()).backward({"w": w})["w"]] == [w.tolist()]
