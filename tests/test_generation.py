@@ -270,3 +270,44 @@ def test_client_waits_completes_and_reloads_weights(monkeypatch):
     finally:
         cli.close()
         srv.shutdown()
+
+
+def test_deploy_training_model_writes_hf_weights_and_asks_the_servers_to_reload(tmp_path, monkeypatch):
+    """Weight push of an RL step: the training model goes to ``hot_path`` as safetensors in HF naming, then the
+    servers are told to load that directory."""
+    import json
+
+    import torch
+
+    from steptronoss_b200.exp.inference import VLLMDeployConfig
+    from steptronoss_b200.models.qwen_dense import QwenModel
+    from steptronoss_b200.parallel.state import PM
+    from tests.tiny_exp import make_tiny_exp
+
+    PM.initialize()
+    exp = make_tiny_exp(gbs=1, seq=32, iters=1, layers=1, hidden=32, heads=4, kv_heads=2, head_dim=8, ffn=64, vocab=64)
+    PM.set_mesh(exp.model_cfg.parallel_cfg)
+    model = QwenModel(cfg=exp.model_cfg, layer_map=exp.model_cfg.build_layer_map())
+    model.init_weights(0, 0.02)
+    calls = []
+
+    class FakeClient:
+        def wait_for_server(self):
+            calls.append("wait")
+
+        def reload_weights(self, path):
+            calls.append(("reload", path))
+
+    cfg = VLLMDeployConfig()
+    cfg.hot_path = str(tmp_path / "hot")
+    cfg.model_config_path = ""
+    monkeypatch.setattr(type(cfg), "build_cli", lambda self: FakeClient())
+    cfg.deploy_training_model([model])
+    assert calls == ["wait", ("reload", str(tmp_path / "hot")), "wait"]
+    index = json.load(open(tmp_path / "hot" / "model.safetensors.index.json"))
+    names = set(index["weight_map"])
+    assert "model.embed_tokens.weight" in names and "model.layers.0.self_attn.q_proj.weight" in names
+    from safetensors.torch import load_file
+
+    shard = load_file(str(tmp_path / "hot" / sorted(set(index["weight_map"].values()))[0]))
+    assert torch.equal(shard["model.embed_tokens.weight"], model.tok_embeddings.word_embeddings.weight.detach())
