@@ -79,3 +79,17 @@ def test_queue_distributor_and_futures(store):
     clones = [pickle.loads(pickle.dumps(f)) for f in futs]
     threading.Thread(target=lambda: [c.set_result(i * 10) for i, c in enumerate(clones)]).start()
     assert sorted(f.get_result(timeout=10) for f in wait_by_finish_order(futs)) == [0, 10, 20]
+
+
+def test_blocking_pop_and_score_increments_steer_the_least_loaded_choice(store):
+    import time
+
+    assert store.brpop("jobs", timeout=0.1) is None                     # nothing arrives: gives up after the timeout
+    threading.Thread(target=lambda: (time.sleep(0.1), store.lpush("jobs", "j1"))).start()
+    t0 = time.monotonic()
+    assert store.brpop("jobs", timeout=5) == b"j1" and time.monotonic() - t0 < 2
+    store.zadd("load", {"a": 0, "b": 0})
+    store.zincrby("load", 5, "a")                                       # "a" is busy: the next picks go to "b"
+    picks = [store.zpopmin_incr("load") for _ in range(5)]
+    assert picks == [b"b"] * 5
+    assert {store.zpopmin_incr("load") for _ in range(2)} == {b"a", b"b"}   # both at 5 now: they alternate
