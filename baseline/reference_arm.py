@@ -5,8 +5,16 @@ hatchling, is not installable offline) and imported from there.  Two of its depe
 installable either and are replaced by the small stand-ins under ``baseline/shims``:
 ``configurize`` (mapped to this repository's implementation of the same config-tree API) and
 ``megfile`` (local file system).  Everything on the training path — models, tensor-parallel layers,
-flash-attn attention core, gradient manager, optimizer, schedule, trainer — is the reference's own
-code, driven through its own ``Exp`` / trainer API with its own Qwen3-8B configuration file.
+flash-attn attention core, MoE block with its all-to-all ``TokenDispatcher`` and grouped GEMM, gradient
+manager, optimizer, schedule, trainer — is the reference's own code, driven through its own ``Exp`` /
+trainer API with its own configuration files (``playground/pretrain/qwen3/qwen3_8b.py`` for the dense
+model, ``playground/pretrain/qwen3/qwen3_30a3b.py`` for the MoE model).
+
+The MoE arm selects, through the reference's own ``set_optimization`` switch, the fastest alternatives the
+reference ships that can run here: flash-attn attention, its Triton grouped GEMM (the ``grouped_gemm`` wheel
+and DeepEP are not installed) and its Triton routing / scatter / gather kernels.
+``STB200_REF_GROUPED_GEMM`` (``triton_grouped_gemm`` | ``function_imple`` | ``default``) and
+``STB200_REF_MOE_TRITON=0`` choose the slower statements instead.
 
 Only two things are supplied from outside, because the reference does not ship them: a synthetic
 packed-document data config producing the reference's batch contract, and a weight initialiser
@@ -33,15 +41,21 @@ def _load_file(path: str, name: str):
     return mod
 
 
+def _scratch_dir() -> str:
+    """Where the run's own by-products (clock samples, the reference's log directory) go."""
+    import tempfile
+
+    d = os.environ.get("STB200_BENCH_OUT") or os.path.join(tempfile.gettempdir(), "stb200_bench")
+    os.makedirs(d, exist_ok=True)
+    return d
+
+
 def _unavailable(why: str, any_rank: bool = False):
     if any_rank or int(os.environ.get("RANK", "0")) == 0:
         print(json.dumps({"impl": "reference", "unavailable": why.replace("\n", " ")[:400]}), flush=True)
 
 
 def run(args) -> None:
-    if getattr(args, "model", "qwen3_8b") != "qwen3_8b":
-        return _unavailable("the reference arm drives the Qwen3-8B dense configuration only: the reference's MoE path "
-                            "needs its Triton grouped GEMM / grouped_gemm wheel, neither of which is part of this arm")
     if not os.path.isdir(os.path.join(REF, "steptronoss")):
         return _unavailable("baseline/_ref/steptronoss is absent: copy the reference tree there first")
     sys.path.insert(0, os.path.join(HERE, "shims"))
@@ -79,16 +93,23 @@ def _run(args) -> None:
     from steptronoss.exp.base_exp import DataConfig
     from steptronoss.core.trainers.lm_trainer import DecoderPretrainTrainer
 
+    moe = getattr(args, "model", "qwen3_8b") == "qwen3_30b_a3b"
     sft_base = _load_file(os.path.join(REF, "playground/sft/qwen3/qwen3_sft_base.py"), "_ref_qwen3_sft_base")
-    q8 = _load_file(os.path.join(REF, "playground/pretrain/qwen3/qwen3_8b.py"), "_ref_qwen3_8b")
+    if moe:
+        model_file = _load_file(os.path.join(REF, "playground/pretrain/qwen3/qwen3_30a3b.py"), "_ref_qwen3_30a3b")
+        model_cfg_cls = model_file.Qwen3_30A3BConfig
+    else:
+        model_file = _load_file(os.path.join(REF, "playground/pretrain/qwen3/qwen3_8b.py"), "_ref_qwen3_8b")
+        model_cfg_cls = model_file.Qwen3_8BConfig
 
     sys.path.insert(0, os.path.dirname(HERE))
     from bench import ClockSampler, default_parallelism, model_flops_per_token, parse_parallelism
     from steptronoss_b200.data.synthetic import make_packed_sample  # data generator only (numpy)
 
-    par_text = args.parallelism or default_parallelism(world)
+    par_text = args.parallelism or (f"ep{world}dp{world}" if moe else default_parallelism(world))
     par = parse_parallelism(par_text)
     seq = args.seq_len
+    min_doc = seq if moe else 256          # the MoE config trains on one document per sequence
 
     class Loader:
         def __init__(self, dp_rank, dp_size):
@@ -103,7 +124,7 @@ def _run(args) -> None:
         def __next__(self):
             rng = np.random.default_rng([0, self.i * self.dp_size + self.dp_rank])
             self.i += 1
-            s = make_packed_sample(rng, seq, 151936, 256, seq)
+            s = make_packed_sample(rng, seq, 151936, min_doc, seq)
             return {k: v.pin_memory() for k, v in s.items()}
 
         def state_dict(self):
@@ -132,8 +153,10 @@ def _run(args) -> None:
                             p.normal_(0.0, 0.02, generator=gen)
             return models
 
+    moe_choices = {}
+
     class Exp(sft_base.Exp):
-        model_cfg = q8.Qwen3_8BConfig
+        model_cfg = model_cfg_cls
         data_cfg = SyntheticData
 
         def __init__(self):
@@ -144,11 +167,16 @@ def _run(args) -> None:
             pc.context_parallel_size = par["cp"]
             self.model_cfg.tp_cfg.sequence_parallel = par["tp"] > 1
             self.model_cfg.check_nan = False
+            if moe:
+                pc.expert_model_parallel_size, pc.expert_tensor_parallel_size = par["ep"], 1
+                self.model_cfg.ffn_cfg.moe_cfg.moe_aux_loss_coef = 1e-3
             if args.debug_layers:
                 self.model_cfg.num_layers = args.debug_layers
+                if moe:
+                    self.model_cfg.ffn_cfg.moe_cfg.moe_layer_list = list(range(args.debug_layers))
             rec = args.recompute
             if rec == "auto":
-                rec = "full" if par["tp"] * par["pp"] == 1 else "none"
+                rec = "full" if par["tp"] * par["pp"] == 1 and not moe else "none"
             self.model_cfg.recompute = True if rec == "full" else ([] if rec == "none" else rec.split(","))
             self._recompute_text = rec
             t = self.trainer_cfg
@@ -163,13 +191,27 @@ def _run(args) -> None:
             self.scheduler_cfg.total_schedule = 10 ** 6
             self.scheduler_cfg.warmup_schedule = 0
             self.checkpoint_cfg.save_interval = None
-            self.log_dir = os.path.join(os.path.dirname(HERE), "gpurun_out", "reference_logs")
+            self.log_dir = os.path.join(_scratch_dir(), "reference_logs")
+
+        def configure_optimizable(self):
+            if not moe:
+                return super().configure_optimizable()    # the reference's own choice for its dense experiments
+            from steptronoss.utils.optimizable import set_optimization
+
+            gg = os.environ.get("STB200_REF_GROUPED_GEMM", "triton_grouped_gemm")
+            kw = {"AttentionCore": "flash-attn"}
+            if gg != "default":
+                kw["grouped_gemm"] = gg
+            if os.environ.get("STB200_REF_MOE_TRITON", "1") != "0":
+                kw.update(histogram="triton", index_compute="triton", moe_scatter="triton", moe_weighted_gather="triton")
+            set_optimization(**kw)
+            moe_choices.update(kw)
 
     exp = Exp()
     exp.sanity_check()
     os.environ["WORLD_SIZE"] = str(world)
     trainer = Trainer(exp=exp)
-    exp.configure_optimizable()  # the reference experiment's own choice: flash-attn attention core
+    exp.configure_optimizable()  # dense: the reference experiment's own choice (flash-attn core, torch.compile default)
     trainer.before_train()
     for m in trainer.models:
         m.train()
@@ -187,9 +229,8 @@ def _run(args) -> None:
     for _ in range(args.warmup):
         step()
     barrier_sync()
-    sampler = ClockSampler(os.path.join(os.path.dirname(HERE), "gpurun_out", "bench_clocks_reference.csv"), world) if rank == 0 else None
+    sampler = ClockSampler(os.path.join(_scratch_dir(), "bench_clocks_reference.csv"), world) if rank == 0 else None
     if sampler:
-        os.makedirs(os.path.dirname(sampler.path), exist_ok=True)
         sampler.start()
     barrier_sync()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -220,18 +261,28 @@ def _run(args) -> None:
     except Exception:
         pass
     peak = float(peaks.get("bf16_tflops_sustained", 1375.7)) * 1e12
-    avg_ctx = (seq ** 2 / 3.0) / ((256 + seq) / 2.0) / 2.0
-    fpt = model_flops_per_token(exp.model_cfg.num_layers, 4096, 32, 8, 128, 12288, 151936, avg_ctx)
+    if moe:
+        fpt = model_flops_per_token(exp.model_cfg.num_layers, 2048, 32, 4, 128, 8 * 768, 151936, seq / 2.0,
+                                    router_experts=128)
+    else:
+        avg_ctx = (seq ** 2 / 3.0) / ((256 + seq) / 2.0) / 2.0
+        fpt = model_flops_per_token(exp.model_cfg.num_layers, 4096, 32, 8, 128, 12288, 151936, avg_ctx)
+    from bench import DATA_TEXT, L2_TEXT, METRIC_TEXT, MODEL_TEXT
+
+    kind = "moe" if moe else "dense"
     out = {
-        "metric": "tokens/s/box (Qwen3-8B dense training, all GPUs of the node)", "value": value, "unit": "tokens/s",
+        "metric": METRIC_TEXT[kind], "value": value, "unit": "tokens/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic packed documents (lengths U[256,8192], uniform token ids), random N(0,0.02) init",
+        "data": DATA_TEXT[kind],
         "mfu_of_measured_sustained_bf16": value * fpt / (peak * world),
-        "config": {"model": "Qwen3-8B", "layers": exp.model_cfg.num_layers, "global_batch": tc.global_batch_size,
+        # the same keys, in the same words, as the other arm prints
+        "config": {"model": MODEL_TEXT[kind], "layers": exp.model_cfg.num_layers, "global_batch": tc.global_batch_size,
                    "seq_len": seq, "micro_batch": 1, "parallelism": par_text, "optimizer": "Adam fp32 master+state, ZeRO-1",
-                   "recompute": exp._recompute_text, "attention": "flash-attn 2 (reference AttentionCore)",
-                   "l2": "inputs larger than L2"},
+                   "recompute": exp._recompute_text, "l2": L2_TEXT},
+        "implementation": {"attention": "flash-attn 2 (reference AttentionCore)",
+                           **({"moe_dispatcher": "TokenDispatcher (NCCL all-to-all)", "optimizable": moe_choices}
+                              if moe else {"optimizable": "AttentionCore=flash-attn, default=torch_compile"})},
         "clocks": clocks,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": max(ms, wall) / args.steps},
         "impl": "reference",

@@ -29,6 +29,23 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# Wording shared by both arms, so that their JSON lines describe the same benchmark with the same `config`.
+METRIC_TEXT = {"dense": "tokens/s/box (Qwen3-8B dense training, all GPUs of the node)",
+               "moe": "tokens/s/box (Qwen3-30B-A3B-shape MoE pretraining, all GPUs of the node)"}
+MODEL_TEXT = {"dense": "Qwen3-8B", "moe": "Qwen3-30B-A3B-shape MoE"}
+DATA_TEXT = {"dense": "synthetic packed documents (lengths U[256,8192], uniform token ids), random N(0,0.02) init",
+             "moe": "synthetic sequences of one document each (uniform token ids), random N(0,0.02) init"}
+L2_TEXT = "inputs larger than L2 (each step streams > 100 GB)"
+
+
+def scratch_dir() -> str:
+    """Directory for the run's by-products (clock samples): ``STB200_BENCH_OUT`` or a temporary directory."""
+    import tempfile
+
+    d = os.environ.get("STB200_BENCH_OUT") or os.path.join(tempfile.gettempdir(), "stb200_bench")
+    os.makedirs(d, exist_ok=True)
+    return d
+
 
 def parse():
     ap = argparse.ArgumentParser()
@@ -204,8 +221,18 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
+    from steptronoss_b200.utils.metrics import GlobalMetrics
+
+    loss_step0 = None
+    for w in range(args.warmup):
         trainer.train_step()
+        if w == 0:
+            # Loss of the first micro-batch of the first step, before any update.  Rank 0's first sample is the same
+            # in every layout and the initial weights do not depend on the layout, so this number must agree
+            # across N = 1, 2, 4, 8 to bf16 rounding.
+            vals = GlobalMetrics.metrics["lm_loss"].values if "lm_loss" in GlobalMetrics.metrics else []
+            if vals:
+                loss_step0 = float(torch.as_tensor(vals[0]).float().mean().item())
     barrier_sync()
     native.raise_if_kernel_error()
 
@@ -232,9 +259,8 @@ def run_ours(args):
     live_iters = trainer.data_iterators
     staged = [Staged(it, n_micro * args.steps) for it in live_iters]
     trainer.data_iterators = [s if it is not None else None for s, it in zip(staged, live_iters)]
-    sampler = ClockSampler(os.path.join(ROOT, "gpurun_out", "bench_clocks.csv"), world) if rank == 0 else None
+    sampler = ClockSampler(os.path.join(scratch_dir(), "bench_clocks.csv"), world) if rank == 0 else None
     if sampler:
-        os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
         sampler.start()
     barrier_sync()
     l0 = launch_count()
@@ -256,8 +282,6 @@ def run_ours(args):
             h2d = sum(v.numel() * v.element_size() for v in s_.items[0].values()) * n_micro
             break
     barrier_sync()
-    from steptronoss_b200.utils.metrics import GlobalMetrics
-
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     f0.record()
@@ -296,21 +320,22 @@ def run_ours(args):
     except Exception:
         pass
     peak = float(peaks.get("bf16_tflops_sustained", 1375.7)) * 1e12
+    kind = "moe" if moe else "dense"
     out = {
-        "metric": ("tokens/s/box (Qwen3-30B-A3B-shape MoE pretraining, all GPUs of the node)" if moe
-                   else "tokens/s/box (Qwen3-8B dense training, all GPUs of the node)"),
+        "metric": METRIC_TEXT[kind],
         "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_a / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16",
-        "data": ("synthetic sequences of one document each (uniform token ids), random N(0,0.02) init" if moe else
-                 "synthetic packed documents (lengths U[256,8192], uniform token ids), random N(0,0.02) init"),
+        "data": DATA_TEXT[kind],
         "mfu_of_measured_sustained_bf16": value * fpt / (peak * world),
-        "config": {"model": "Qwen3-30B-A3B-shape MoE" if moe else "Qwen3-8B", "layers": mc.num_layers, "global_batch": args.seqs_per_gpu * world,
+        "config": {"model": MODEL_TEXT[kind], "layers": mc.num_layers, "global_batch": args.seqs_per_gpu * world,
                    "seq_len": args.seq_len, "micro_batch": args.seqs_per_micro_batch, "parallelism": par_text,
-                   "optimizer": "Adam fp32 master+state, ZeRO-1", "recompute": rec,
-                   **({"moe_dispatcher": args.dispatcher, "moe_capacity_factor": args.moe_capacity_factor or None} if moe else {}),
-                   "l2": "inputs larger than L2 (each step streams > 100 GB)"},
+                   "optimizer": "Adam fp32 master+state, ZeRO-1", "recompute": rec, "l2": L2_TEXT},
+        "implementation": {"attention": "tcgen05 flash attention (csrc/attention_sm100.cu)",
+                           **({"moe_dispatcher": args.dispatcher,
+                               "moe_capacity_factor": args.moe_capacity_factor or None} if moe else {})},
         "clocks": clocks,
+        "loss_step0": loss_step0,
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": ms_b / args.steps, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "last_loss": last_loss},
         "gpu_launches": launches,

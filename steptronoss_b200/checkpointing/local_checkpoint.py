@@ -176,6 +176,11 @@ class Checkpointer:
             grad_manager.wait_param_gather()
         if torch.cuda.is_available():
             torch.cuda.synchronize()
+            # a kernel that gave up a bounded wait (an unreduced gradient shard, an overfull expert buffer) left this
+            # state inconsistent: fail here rather than mark such a checkpoint as the latest
+            from ..ops import native
+
+            native.raise_if_kernel_error()
         files = self.make_ckpt(models, grad_manager, scheduler, dataloader, extra)
         if getattr(self.cfg, "save_safetensors", False):
             from .hf_checkpoint import dump_safetensors

@@ -98,7 +98,9 @@ zero_reduce_kernel(const __grid_constant__ ZeroPtrs grads, long long n4, int wor
   if (threadIdx.x == 0) {
     float t = 0.f;
     for (int w = 0; w < 8; ++w) t += red[w];
-    partials[blockIdx.x] = t;
+    // A shard whose wait ran out stays unreduced: poison its squared norm, so that the clip kernel sees a
+    // non-finite norm on every rank (the norm is all-reduced) and the Adam kernels skip this step everywhere.
+    partials[blockIdx.x] = ok ? t : __int_as_float(0x7fc00000);
   }
 }
 

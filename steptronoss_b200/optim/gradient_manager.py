@@ -287,6 +287,9 @@ class BaseGradientManager:
     def _refresh_params(self) -> None:
         pass
 
+    def _publish_loaded_shards(self) -> None:
+        """After optimizer state was loaded into the owned shards: make every replica see them (no-op here)."""
+
     def count_zeros(self) -> torch.Tensor:
         z = torch.zeros(1, dtype=torch.float32, device=self.device)
         for b in self.buckets.values():
@@ -368,6 +371,7 @@ class BaseGradientManager:
                 shard.bucket.param_buf[lo:hi].copy_(shard.master)
         if self.muon is not None and "muon" in sd:
             self.muon.load_state_dict(sd["muon"])
+        self._publish_loaded_shards()
         self._refresh_params()
         self.wait_param_gather()
 
@@ -418,6 +422,7 @@ class BaseGradientManager:
             raise RuntimeError(f"optimizer state of {len(missing)} parameters is not in the checkpoint: {missing[:5]} ...")
         for shard in self.shards.values():
             shard.bucket.param_buf[shard.lo:shard.hi].copy_(shard.master)
+        self._publish_loaded_shards()
         self._refresh_params()
         self.wait_param_gather()
 
@@ -582,6 +587,15 @@ class Zero1GradientManager(BaseGradientManager):
 
     def _norm_group(self):
         return None  # world
+
+    def _publish_loaded_shards(self) -> None:
+        # Buckets on the peer-memory path have no all-gather in `_refresh_params` (their Adam kernel stores the new
+        # shard into every rank's buffer), so shards that were just loaded from a checkpoint would stay local.
+        # The buffers are this rank's own mapping: NCCL never sees a peer pointer.
+        for key, b in self.buckets.items():
+            if b.world > 1 and self._peer_of(key) is not None:
+                lo, hi = b.own_range()
+                comm.all_gather_into_tensor(b.param_buf, b.param_buf[lo:hi], group=PM.group_of(key.reduce_group))
 
     def _refresh_params(self) -> None:
         for pz in self._peer.values():

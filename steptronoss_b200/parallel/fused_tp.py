@@ -10,16 +10,25 @@ one autograd function with two bodies:
   GEMM consumes the row tiles that have arrived, or whose epilogue stores partial tiles into the
   owner's memory where they are summed in fixed rank order.
 
-Backward mirrors the reference: the column layer re-gathers its input for the weight gradient and
-reduce-scatters the input gradient; the row layer all-gathers the output gradient.
+Backward mirrors the reference: the column layer needs its gathered input for the weight gradient and
+reduce-scatters the input gradient; the row layer all-gathers the output gradient.  The reference
+re-gathers the column layer's input in backward to keep only 1/TP of it alive.  On the peer-memory path
+the gathered rows are kept instead (``STB200_TP_KEEP_GATHERED``, default on): one copy out of the
+gathered slot costs a fifth of a second all-gather over NVLink, and tokens x hidden bf16 per column layer
+is small against 180 GB; ``0`` restores the re-gather.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
 from ..ops.gemm import gemm
 from . import comm
 from .state import PM
+
+
+KEEP_GATHERED = os.environ.get("STB200_TP_KEEP_GATHERED", "1") != "0"
 
 
 def _ag_rows(x, group_name):
@@ -61,12 +70,18 @@ class _AllGatherLinearFn(torch.autograd.Function):
     def forward(ctx, x, w, group_name, out_dtype):
         ctx.group_name = group_name
         ctx.weight_ref = w
-        ctx.save_for_backward(x, w)  # only the local 1/TP slice is kept
+        ctx.full = None
         if _peer(group_name, x.shape[0], x.shape[1], w.shape[0], x, w):
             from . import symm
 
-            y, _ = symm.all_gather_gemm(x, w, group_name, out_dtype=out_dtype, need_gathered=False)
+            keep = KEEP_GATHERED and ctx.needs_input_grad[1]   # not under no_grad (first pass of a recomputed block)
+            y, full = symm.all_gather_gemm(x, w, group_name, out_dtype=out_dtype, need_gathered=keep)
+            if keep:
+                # the gathered slot is reused by the second-next all-gather of the group: keep a private copy
+                ctx.full = full.clone()
+            ctx.save_for_backward(x, w)
             return y
+        ctx.save_for_backward(x, w)  # only the local 1/TP slice is kept
         full = _ag_rows(x, group_name)
         return gemm(full, w, out_dtype=out_dtype or x.dtype)
 
@@ -86,7 +101,10 @@ class _AllGatherLinearFn(torch.autograd.Function):
             else:
                 dx = _rs_rows(gemm(g2, w, b_mn_major=True, out_dtype=x.dtype), name)
         if ctx.needs_input_grad[1]:
-            full = symm.all_gather_gemm(x, None, name)[1] if peer else _ag_rows(x, name)
+            if ctx.full is not None:
+                full, ctx.full = ctx.full, None
+            else:
+                full = symm.all_gather_gemm(x, None, name)[1] if peer else _ag_rows(x, name)
             dw = _wgrad(ctx.weight_ref, g2, full)
         return dx, dw, None, None
 

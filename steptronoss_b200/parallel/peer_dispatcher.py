@@ -33,6 +33,7 @@ from ..ops import native
 from ..ops.gemm import count_launch
 from .ep_dispatcher import AllToAllDispatcher
 from .state import PM
+from . import symm
 from .symm import _WAIT_NS, SymmetricBuffer
 
 P, I, L, U, ULL = c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_uint, ctypes.c_ulonglong
@@ -220,17 +221,43 @@ class PeerMemoryDispatcher:
         self._used_fallback = False
         self.received_slots: int | None = None
         """(token, local expert) slots that arrived in the last dispatch; None on the all-to-all path."""
+        self._group_decision: bool | None = None
+        self._checked_tokens: set = set()
+
+    def _group_ok(self) -> bool:
+        """Decided once per dispatcher, collectively: the group is NCCL, 2 to 8 ranks, all on one node (peer memory
+        is mapped through CUDA IPC, which does not cross nodes)."""
+        if self._group_decision is None:
+            ok = dist.is_initialized() and 2 <= self.world <= 8
+            if ok:
+                group = PM.group_of(self.group_name)
+                ok = dist.get_backend(group) == "nccl" and symm._same_node(group)
+            self._group_decision = bool(ok)
+        return self._group_decision
+
+    def _check_equal_tokens(self, tokens: int, device) -> None:
+        """Landing rows are `source rank * T + token`: every rank of the group must dispatch the same number of
+        tokens.  Checked once per token count with one small all-reduce; unequal counts raise on every rank."""
+        if tokens in self._checked_tokens:
+            return
+        t = torch.tensor([tokens, -tokens], dtype=torch.int64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=PM.group_of(self.group_name))
+        hi, lo = int(t[0].item()), -int(t[1].item())
+        if hi != lo:
+            raise ValueError(f"the peer-memory dispatcher needs the same token count on every rank of "
+                             f"{self.group_name} (between {lo} and {hi} here); use the all-to-all dispatcher")
+        self._checked_tokens.add(tokens)
 
     def _peer_ok(self, x: torch.Tensor, expert_ids: torch.Tensor) -> bool:
         return (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and expert_ids.shape[1] <= 15
-                and dist.is_initialized() and 2 <= self.world <= 8
-                and dist.get_backend(PM.group_of(self.group_name)) == "nccl")
+                and self._group_ok())
 
     def dispatch(self, x, expert_ids, weights):
         self._used_fallback = not self._peer_ok(x, expert_ids)
         if self._used_fallback:
             self.received_slots = None
             return self._fallback.dispatch(x, expert_ids, weights)
+        self._check_equal_tokens(x.shape[0], x.device)
         if self.arena is None:
             self.arena = _arena(self.group_name)
         self.plan = _Plan(expert_ids, self.world, self.rank, self.per_rank)

@@ -32,6 +32,16 @@ from .base_trainer import BaseTrainer
 from .packed_model import PackedModel
 
 
+def _raise_if_kernel_error() -> None:
+    """Surface a kernel's bounded-wait failure (unreduced shard, overfull expert buffer) before its consequences
+    are logged or written to a checkpoint."""
+    if torch.cuda.is_available():
+        from ..ops import native
+
+        torch.cuda.synchronize()
+        native.raise_if_kernel_error()
+
+
 class TrainerPromptStream(Nextable):
     """The prompt loader seen through the experiment's ``preprocess`` (what the flow controller pulls from)."""
 
@@ -430,6 +440,7 @@ class PPOTrainer(BaseTrainer):
 
     def training_log(self):
         tc = self.ppo_cfg
+        _raise_if_kernel_error()
         metrics = GlobalMetrics.reduce_all()
         logs = {"iter": f"{self.iteration:8d}/{tc.train_iters:8d}"}
         for k in ("reward_mean", "ppo_loss", "critic_loss", "actor_grad_norm", "rollout_avg_tokens"):
@@ -476,6 +487,7 @@ class PPOTrainer(BaseTrainer):
     def save_checkpoint(self, sync: bool = False):
         ck = self.checkpointer
         ck.join()
+        _raise_if_kernel_error()
         sync_point("ready for dump")
         roles = [("actor", self.actor, self.actor_iteration), ("critic", self.critic, self.critic_iteration),
                  ("reference", self.reference_model, self.iteration)]

@@ -1,5 +1,7 @@
 """Worker for the multi-GPU tests: trains the tiny bf16 experiment under the layout given on the command
-line (launched by torch.distributed.run) and prints one JSON line with the loss curve from rank 0."""
+line (launched by torch.distributed.run) and prints one JSON line with the loss curve from rank 0.
+With ``cpu_fp32`` as third argument it trains the same experiment in fp32 through the PyTorch restatements
+(the caller hides the GPUs): the oracle of the single-GPU end-to-end test."""
 import json
 import os
 import sys
@@ -17,7 +19,8 @@ def main():
     from tests.tiny_exp import make_tiny_exp
 
     PM.initialize()
-    exp = make_tiny_exp(dtype=torch.bfloat16, **kw)
+    cpu_oracle = len(sys.argv) > 3 and sys.argv[3] == "cpu_fp32"
+    exp = make_tiny_exp(dtype=torch.float32 if cpu_oracle else torch.bfloat16, **kw)
     exp.seed = 0
     tr = exp.trainer_cfg.get_trainer_cls()(exp=exp)
     tr.before_train()
@@ -27,8 +30,9 @@ def main():
         tr.iteration += 1
         tr.training_log()
         losses.append(tr.history[-1]["lm_loss"])
-    torch.cuda.synchronize()
-    native.raise_if_kernel_error()
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+        native.raise_if_kernel_error()
     if PM.world_rank == PM.world_size - 1:
         gm = getattr(tr, "grad_manager", None) or getattr(tr, "gm", None)
         print("RESULT " + json.dumps({"losses": losses, "grad_norms": [h["grad_norm"] for h in tr.history],

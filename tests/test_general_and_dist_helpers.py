@@ -71,6 +71,14 @@ def test_pickled_tensors_and_tp_resharding():
     shards = du.redistributed_tp(list(full.chunk(2, dim=1)), dim=1, new_tp=3)
     assert len(shards) == 3 and torch.equal(torch.cat(shards, dim=1), full) and shards[0].shape == (4, 2)
     assert du.balanced_map(lambda v: v * v, [1, 2, 3]) == [1, 4, 9]           # one process: plain map
+    assert du.replicated_map(lambda v: v * v, [1, 2, 3]) == [1, 4, 9]
+    names = ["input", "ids", "n", "absent", "flag"]
+    table, payload = du.pack_tensors({"input": torch.arange(6.0).reshape(6, 1), "ids": torch.arange(5, dtype=torch.int32),
+                                      "n": 7, "absent": None, "flag": torch.tensor([True, False])}, names)
+    back = du.unpack_tensors(table, payload, names)
+    assert back["input"].shape == (6, 1) and back["ids"].dtype == torch.int32 and back["ids"].tolist() == [0, 1, 2, 3, 4]
+    assert back["n"].tolist() == [7] and back["absent"] is None and back["flag"].tolist() == [True, False]
+    assert du.concat_list_in_group([1, 2]) == [1, 2] and du.gather_object(["a"]) == [["a"]]
     assert du.all_to_all_objects(["only"]) == ["only"] and du.gather_dict({"k": 1}) == [{"k": 1}]
 
 
@@ -100,8 +108,27 @@ def _worker(rank, world, port, q):
             seen.append(v)
             return v * 10
 
-        out["map"] = du.balanced_map(work, [1, 2, 3, 4, 5], sizes=[5, 1, 1, 1, 1])
+        out["map"] = du.replicated_map(work, [1, 2, 3, 4, 5], sizes=[5, 1, 1, 1, 1])
         out["did"] = sorted(seen)
+        # per-rank lists of unequal length: evened out, mapped, results back at their owners
+        mine = [0, 1, 2, 3, 4] if rank == 0 else [5]
+        bal, info = du.list_balance(mine)
+        out["balanced"] = bal
+        out["restored"] = du.list_unbalance(bal, info)
+        out["bmap"] = du.balanced_map(lambda v: v + 100, mine)
+        out["concat"] = du.concat_list_in_group([rank, rank])
+        out["concat_one"] = du.concat_list_in_group([torch.arange(3)] if rank == 1 else [])[0].tolist()
+        out["gather_obj"] = du.gather_object([f"from{rank}"], dst=1)
+        got = du.all_to_all_tensors([torch.full((rank + 1, d + 1), float(rank * 10 + d)) for d in range(world)])
+        out["a2a_tensors"] = [(tuple(t.shape), float(t[0, 0])) for t in got]
+        if rank == 0:
+            du.send_obj({"k": [1, 2, torch.ones(2)]}, dst=1)
+            du.wait_all(du.isend_packed_tensors({"input": torch.ones(3, 1), "pos": torch.arange(3), "none": None}, dst=1))
+        else:
+            o = du.recv_obj(src=0)
+            out["recv_obj"] = (o["k"][:2], o["k"][2].tolist())
+            t = du.recv_packed_tensors(["input", "pos", "none"], src=0)
+            out["recv_packed"] = (tuple(t["input"].shape), t["pos"].tolist(), t["none"])
         b = du.broadcast_tensors({"x": torch.arange(4) + 1, "s": "hello"} if rank == 0 else None, src_rank=0)
         out["bcast"] = (b["x"].tolist(), b["s"])
         q.put((rank, out, None))
@@ -138,3 +165,12 @@ def test_object_collectives_on_two_ranks():
     assert res[0]["map"] == [10, 20, 30, 40, 50] == res[1]["map"]
     assert sorted(res[0]["did"] + res[1]["did"]) == [1, 2, 3, 4, 5] and res[0]["did"] and res[1]["did"]
     assert res[0]["bcast"] == ([1, 2, 3, 4], "hello") == res[1]["bcast"]
+    assert res[0]["balanced"] == [0, 1, 2] and res[1]["balanced"] == [3, 4, 5]
+    assert res[0]["restored"] == [0, 1, 2, 3, 4] and res[1]["restored"] == [5]
+    assert res[0]["bmap"] == [100, 101, 102, 103, 104] and res[1]["bmap"] == [105]
+    assert res[0]["concat"] == [0, 0, 1, 1] == res[1]["concat"]
+    assert res[0]["concat_one"] == [0, 1, 2] == res[1]["concat_one"]
+    assert res[0]["gather_obj"] == [[], []] and res[1]["gather_obj"] == [["from0"], ["from1"]]
+    assert res[0]["a2a_tensors"] == [((1, 1), 0.0), ((2, 1), 10.0)] and res[1]["a2a_tensors"] == [((1, 2), 1.0), ((2, 2), 11.0)]
+    assert res[1]["recv_obj"] == ([1, 2], [1.0, 1.0])
+    assert res[1]["recv_packed"] == ((3, 1), [0, 1, 2], None)

@@ -171,12 +171,31 @@ def test_adam_matches_torch_and_clip_scalars():
     assert abs(out[2].item() - 1.0 / (nrm + 1e-6)) < 1e-6 and out[3].item() == 1.0
 
 
-def test_tiny_model_trains_on_gpu_and_matches_cpu_reference_loss():
+def test_tiny_model_on_gpu_matches_the_cpu_fp32_loss_curve_and_gradient_norms():
+    """The whole model through the native kernels (bf16) against the same experiment trained in fp32 on the CPU
+    through the PyTorch restatements: same seed, same data, same optimizer; three steps.  Losses and gradient
+    norms must agree within bf16 tolerance."""
+    import json
+    import os
+    import subprocess
+    import sys
+
     from steptronoss_b200.ops import native
     from tests.tiny_exp import make_tiny_exp
 
-    exp = make_tiny_exp(dtype=torch.bfloat16, hidden=512, heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=2048,
-                        layers=2, seq=512, gbs=2, iters=3, min_doc=32, max_doc=256)
+    kw = dict(hidden=512, heads=4, kv_heads=2, head_dim=128, ffn=1024, vocab=2048, layers=2, seq=512, gbs=2, iters=3,
+              min_doc=32, max_doc=256)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    for k in ("WORLD_SIZE", "RANK", "LOCAL_RANK"):
+        env.pop(k, None)
+    cpu = subprocess.run([sys.executable, os.path.join(root, "tests", "mp_gpu_worker.py"), json.dumps(kw), "3", "cpu_fp32"],
+                         capture_output=True, text=True, timeout=600, env=env, cwd=root)
+    assert cpu.returncode == 0, cpu.stdout[-2000:] + cpu.stderr[-2000:]
+    oracle = json.loads([l for l in cpu.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
+
+    exp = make_tiny_exp(dtype=torch.bfloat16, **kw)
+    exp.seed = 0
     tr = exp.trainer_cfg.get_trainer_cls()(exp=exp)
     tr.before_train()
     for _ in range(3):
@@ -185,8 +204,13 @@ def test_tiny_model_trains_on_gpu_and_matches_cpu_reference_loss():
         tr.training_log()
     native.raise_if_kernel_error()
     losses = [h["lm_loss"] for h in tr.history]
+    norms = [h["grad_norm"] for h in tr.history]
     assert all(math.isfinite(l) for l in losses)
     assert abs(losses[0] - math.log(2048)) < 0.5
+    for a, b in zip(losses, oracle["losses"]):
+        assert abs(a - b) < 2e-2 * abs(b), (losses, oracle["losses"])
+    for a, b in zip(norms, oracle["grad_norms"]):
+        assert abs(a - b) < 5e-2 * abs(b), (norms, oracle["grad_norms"])
 
 
 @pytest.mark.parametrize("M,N,K", [(256, 4, 256), (130, 772, 64)])
