@@ -1,18 +1,27 @@
 // Sequence-parallel projections as single kernels over NVLink peer memory (sm_100a).
 //
-//   gemm_ag_kernel : C = all_gather_rows(x) * B^T.   The gathered matrix lives in symmetric memory.  Four
-//                    "comm" warps in every CTA push this rank's rows, 16-row slices at a time, straight into
-//                    every peer's gathered buffer (plain peer stores: posted writes keep NVLink busier than
-//                    loads, which pay a round trip) and raise a per-row-tile flag on the peer when a tile is
-//                    complete.  The TMA producer of the tcgen05 GEMM waits for the flag of the row tile it is
-//                    about to load, so products of rows that have arrived overlap the transfer of the rest.
-//                    Row tiles are visited own-rank first (read where the caller left them), then in ring
-//                    order.
-//   gemm_rs_kernel : out = reduce_scatter_rows(A * B^T).  The epilogue TMA-stores every bf16 partial tile
-//                    into the row owner's receive slot (peer stores), the last store of a row tile raises a
-//                    flag in the owner's memory, and four "reduce" warps per CTA add the tp slots of the row
-//                    tiles this rank owns in fixed rank order (fp32) as they complete.  Row blocks are
-//                    computed next-rank first, own block last.
+//   gemm_ag_kernel : C = all_gather_rows(x) * B^T.   The gathered matrix lives in symmetric memory.
+//   gemm_rs_kernel : out = reduce_scatter_rows(A * B^T).
+//
+// Both are the persistent tcgen05 GEMM of gemm_sm100.cu (TMA producer warp, MMA warp, four epilogue warps,
+// tiles claimed from a device counter) plus a communication role that a few CTAs take.  Measured on this
+// hardware, sixteen CTAs that each drive a ring of 32 KB cp.async.bulk copies (global -> shared -> peer global)
+// saturate a GPU's NVLink ports (about 675 GB/s per direction), while 16-byte stores issued by a few warps of
+// every CTA or 128-byte TMA tensor stores from the GEMM epilogue reach 440-550 GB/s and stall the tensor pipe.
+// So the first `n_comm` CTAs to start (a ticket from a device counter: roles never depend on a CTA that is not
+// resident) become "comm CTAs": one thread of theirs moves rows with bulk copies through the shared memory that
+// the GEMM stages would otherwise use.
+//
+//   all-gather -> GEMM   comm CTAs push this rank's rows, 32 KB at a time, into every peer's gathered matrix (one
+//                        load, tp-1 stores) and raise a per-row-tile flag on the peers when a tile is complete;
+//                        when the rows are out they turn into GEMM CTAs.  The TMA producer of a GEMM CTA waits
+//                        for the flag of the row tile it is about to load.  Own rows are multiplied first (read
+//                        where the caller left them), the peers' row tiles then in the order they arrive.
+//   GEMM -> reduce-scatter  the epilogue TMA-stores bf16 partial tiles into a local staging matrix at full speed;
+//                        comm CTAs copy every finished row tile that another rank owns into that rank's receive
+//                        slot and raise its flag; four "reduce" warps per CTA add the tp partial copies of the
+//                        row tiles this rank owns in fixed rank order (fp32) as they complete (the own partial
+//                        straight out of the staging matrix).  Row blocks are computed next-rank first, own last.
 //
 // They replace the NCCL collective + cuBLAS pairs of the reference's sequence-parallel linears
 // (steptronoss/core/tensor_parallel/layers.py:151-346, mappings.py:103-300).
@@ -23,10 +32,9 @@
 // used alternately by epoch parity.  A slot written in call e was last read in call e-2 (and by what the
 // caller ran right after it), and no rank can leave call e-1 before every peer has entered call e-1 (each
 // call consumes data that every peer produces inside the same call), so two slots need no further hand-shake.
-// GEMM tiles and the work of the comm / reduce warps are claimed from device counters, not assigned by CTA
-// index, so progress never depends on a CTA that is not resident (for instance while a collective of another
-// stream holds some SMs and is itself waiting for the peer).  Every wait is bounded by the caller's budget; on time-out
-// the kernel records a code in the status word, drains and returns.
+// GEMM tiles, communication units and reduce units are claimed from device counters, so progress never depends
+// on a CTA that is not resident.  Every wait is bounded by the caller's budget; on time-out the kernel records a
+// code in the status word, drains and returns.  No load uses cluster broadcast; peers are only written to.
 #include "common.cuh"
 #include <string.h>
 
@@ -36,10 +44,8 @@ constexpr int kTpBlockM = 128;
 constexpr int kTpBlockN = 256;
 constexpr int kTpBlockK = 64;
 constexpr int kTpStages = 4;
-constexpr int kTpThreads = 320;      // producer, MMA, 4 epilogue warps, 4 comm/reduce warps
+constexpr int kTpThreads = 320;      // producer / comm, MMA, 4 epilogue warps, 4 reduce warps (reduce-scatter only)
 constexpr int kTpAuxThreads = 128;
-constexpr int kTpParts = 8;          // a 128-row tile is moved as 8 slices of 16 rows
-constexpr int kTpPartRows = kTpBlockM / kTpParts;
 constexpr int kTpMaxRanks = 8;
 
 // Layout of the symmetric flag page (uint32 words).
@@ -47,27 +53,34 @@ constexpr int kTpMaxRowTiles = 1024;              // row tiles of 128 per rank
 constexpr int kFlagRsBase = 64;                   // [slot 2][row tile][src 8]   partial tile of `src` has landed
 constexpr int kFlagAgBase = kFlagRsBase + 2 * kTpMaxRowTiles * kTpMaxRanks;  // [slot 2][src 8][row tile] staged
 constexpr int kFlagWords = kFlagAgBase + 2 * kTpMaxRanks * kTpMaxRowTiles;
-constexpr int kAuxLoads = 16;                     // 16-byte loads each aux thread keeps in flight
 constexpr int kRsParts = 16;                      // the reduction works on 8-row slices: a short tail after the
 constexpr int kRsPartRows = kTpBlockM / kRsParts; // last partial tile has landed
 
 // Layout of the local counter scratch (uint32 words), zeroed by the host function before each launch.
-constexpr int kCtrClaim = 0;      // next comm / reduce unit
+constexpr int kCtrClaim = 0;      // next reduce unit
+constexpr int kCtrTicket = 1;     // CTAs that have started (the first n_comm become comm CTAs)
 constexpr int kCtrTileClaim = 2;  // next GEMM tile
+constexpr int kCtrCommClaim = 3;  // next communication unit
 constexpr int kSchedDepth = 4;    // claimed tiles the producer may run ahead of the slowest consumer
-constexpr int kCtrTiles = 8;      // AG: [row tile] slices landed;  RS: [row tile] epilogue warps finished
+constexpr int kCtrTiles = 8;      // [row tile]  all-gather: units pushed; reduce-scatter: epilogue warps finished
+                                  // [row tiles + row tile]  reduce-scatter: units copied to the owner
 
 constexpr int kTpABytes = kTpBlockM * kTpBlockK * 2;
 constexpr int kTpBBytes = kTpBlockN * kTpBlockK * 2;
 constexpr int kTpStageBytes = kTpABytes + kTpBBytes;
 constexpr int kTpStoreBytes = 4 * 2 * 4096;
-constexpr int kTpSmem = kTpStages * kTpStageBytes + kTpStoreBytes + 256 + 1024;
+constexpr int kTpBarrierBytes = 512;
+constexpr int kTpSmem = kTpStages * kTpStageBytes + kTpStoreBytes + kTpBarrierBytes + 1024;
+
+// Communication ring of a comm CTA: it reuses the GEMM operand stages.
+constexpr int kCommStageBytes = 32 * 1024;
+constexpr int kCommStages = (kTpStages * kTpStageBytes) / kCommStageBytes;   // 6
+constexpr int kCommLag = 3;       // a unit's completion is signalled once three younger store groups were issued
+constexpr int kCommPend = 8;      // ring of units stored but not yet signalled (> kCommLag)
+static_assert(kCommStages * kCommStageBytes <= kTpStages * kTpStageBytes, "ring must fit in the operand stages");
 
 struct PeerPtrs {
   void* p[kTpMaxRanks];
-};
-struct TmapArray {
-  CUtensorMap m[kTpMaxRanks];
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -83,14 +96,23 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ void red_release_gpu_add(uint32_t* p, uint32_t v) {
-  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 __device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
   uint4 v;
   asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
+}
+// Untiled bulk copies: global -> shared (completion counted on an mbarrier) and shared -> global (bulk group).
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(smem_dst)),
+               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+               "r"(bytes)
+               : "memory");
 }
 
 // Bounded spin until *p >= target (wrap-safe). Returns false on time-out or when the CTA has aborted.
@@ -111,13 +133,15 @@ __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target,
 
 __device__ __forceinline__ void aux_barrier() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 
-// logical row-tile index -> physical row tile; `first_block` is the rank block visited first
-__device__ __forceinline__ int physical_m_tile(int logical, int tiles_per_rank, int first_block, int tp) {
-  const int blk = logical / tiles_per_rank;
-  return ((first_block + blk) % tp) * tiles_per_rank + logical % tiles_per_rank;
+// All-gather: own rows first, then the peers' row tiles in arrival order (every peer pushes its tiles in
+// ascending order to all ranks at once, so tile i of every peer lands at about the same time).
+__device__ __forceinline__ int ag_m_tile(int logical, int tiles_per_rank, int rank, int tp) {
+  if (logical < tiles_per_rank) return rank * tiles_per_rank + logical;
+  const int j = logical - tiles_per_rank;
+  return ((rank + 1 + j % (tp - 1)) % tp) * tiles_per_rank + j / (tp - 1);
 }
-// Round-robin over the rank blocks (next rank first): the tiles bound for each peer are spread over the whole
-// kernel, so the NVLink write rate is 1/tp-th of the epilogue's output rate instead of all of it for a while.
+// Reduce-scatter: round-robin over the rank blocks (next rank first, own block last): the tiles bound for each
+// peer are spread over the whole kernel.
 __device__ __forceinline__ int interleaved_m_tile(int logical, int tiles_per_rank, int rank, int tp) {
   return ((rank + 1 + logical % tp) % tp) * tiles_per_rank + logical / tp;
 }
@@ -138,6 +162,7 @@ __device__ __forceinline__ void decode_tp_tile(int tile, int num_m, int num_n, i
 struct TpCommon {
   int M, N, K;          // M = tp * rows_local
   int rank, tp, rows_local;
+  int n_comm;           // CTAs that take the communication role
   uint32_t epoch;
   uint32_t* ctrs;       // local counter scratch
   unsigned long long wait_ns;
@@ -156,11 +181,13 @@ struct TpShared {
   uint8_t* smem;
   uint8_t* store_stage;
   uint64_t *full_bar, *empty_bar, *tmem_full, *tmem_empty;
+  uint64_t *sched_full, *sched_empty, *comm_bar;
   uint32_t* tmem_slot;
   volatile int* abort_flag;
   volatile int* claim_slot;
-  uint64_t *sched_full, *sched_empty;
+  volatile int* role_slot;
   volatile int* tile_ring;
+  volatile int* pend_tile;   // [kCommPend] completion ring of the comm thread
 };
 
 __device__ __forceinline__ TpShared tp_carve(uint8_t* smem_raw) {
@@ -171,16 +198,22 @@ __device__ __forceinline__ TpShared tp_carve(uint8_t* smem_raw) {
   s.empty_bar = s.full_bar + kTpStages;
   s.tmem_full = s.empty_bar + kTpStages;
   s.tmem_empty = s.tmem_full + 2;
-  s.tmem_slot = reinterpret_cast<uint32_t*>(s.tmem_empty + 2);
+  s.sched_full = s.tmem_empty + 2;
+  s.sched_empty = s.sched_full + kSchedDepth;
+  s.comm_bar = s.sched_empty + kSchedDepth;
+  s.tmem_slot = reinterpret_cast<uint32_t*>(s.comm_bar + kCommStages);
   s.abort_flag = reinterpret_cast<volatile int*>(s.tmem_slot + 1);
   s.claim_slot = s.abort_flag + 1;
-  s.sched_full = s.tmem_empty + 4;   // 8-byte aligned, past the three words above
-  s.sched_empty = s.sched_full + kSchedDepth;
-  s.tile_ring = reinterpret_cast<volatile int*>(s.sched_empty + kSchedDepth);
+  s.role_slot = s.abort_flag + 2;
+  s.tile_ring = s.abort_flag + 3;
+  s.pend_tile = s.tile_ring + kSchedDepth;
   return s;
 }
+static_assert((2 * kTpStages + 4 + 2 * kSchedDepth + kCommStages) * 8 + (5 + kSchedDepth + kCommPend) * 4 <= kTpBarrierBytes,
+              "barrier region too small");
 
-__device__ __forceinline__ void tp_prologue(const TpShared& s, int warp) {
+// Returns true when this CTA takes the communication role.
+__device__ __forceinline__ bool tp_prologue(const TpShared& s, const TpCommon& c, int warp) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < kTpStages; ++i) {
       mbar_init(&s.full_bar[i], 1);
@@ -194,7 +227,9 @@ __device__ __forceinline__ void tp_prologue(const TpShared& s, int warp) {
       mbar_init(&s.sched_full[i], 1);
       mbar_init(&s.sched_empty[i], 5);  // MMA thread + 4 epilogue warps
     }
+    for (int i = 0; i < kCommStages; ++i) mbar_init(&s.comm_bar[i], 1);
     *s.abort_flag = 0;
+    *s.role_slot = (atomicAdd(&c.ctrs[kCtrTicket], 1u) < static_cast<uint32_t>(c.n_comm)) ? 1 : 0;
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -204,6 +239,7 @@ __device__ __forceinline__ void tp_prologue(const TpShared& s, int warp) {
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  return *s.role_slot != 0;
 }
 
 __device__ __forceinline__ void tp_epilogue_sync(const TpShared& s, int warp, uint32_t tmem_base) {
@@ -237,7 +273,11 @@ __device__ __forceinline__ int sched_consume(const TpShared& s, const TpCommon& 
   mbar_arrive(&s.sched_empty[slot]);
   return tile;
 }
-// Producer side of a failed wait / end of stream: wake the consumers with the end marker where possible.
+// A CTA that computes no tiles at all: send the end marker as the first (and only) entry of the stream.
+__device__ __forceinline__ void sched_end_now(const TpShared& s) {
+  s.tile_ring[0] = -1;
+  mbar_arrive(&s.sched_full[0]);
+}
 __device__ __forceinline__ void sched_fail(const TpShared& s, const TpCommon& c, int code) {
   if (!*s.abort_flag) report_error(c.status, code);
   *s.abort_flag = 1;
@@ -342,7 +382,7 @@ __device__ __forceinline__ void tp_store_tile(const TpShared& s, uint32_t tmem_b
   }
 }
 
-// Claim the next unit of comm / reduce work for the 128 aux threads of this CTA.
+// Claim the next unit of reduce work for the 128 aux threads of this CTA.
 __device__ __forceinline__ int aux_claim(const TpShared& s, uint32_t* ctrs, int tid) {
   if (tid == 0) *s.claim_slot = static_cast<int>(atomicAdd(&ctrs[kCtrClaim], 1u));
   aux_barrier();
@@ -351,14 +391,121 @@ __device__ __forceinline__ int aux_claim(const TpShared& s, uint32_t* ctrs, int 
   return u;
 }
 
-// Thread 0 of the aux group waits, every aux thread learns the outcome.
-template <bool SYS>
-__device__ __forceinline__ bool aux_wait_flag(const TpShared& s, const TpCommon& c, const uint32_t* flag,
-                                              uint32_t target, int tid) {
-  if (tid == 0) *s.claim_slot = wait_flag_ge<SYS>(flag, target, c.wait_ns, s.abort_flag) ? 1 : 0;
-  aux_barrier();
-  const bool ok = *s.claim_slot != 0;
-  aux_barrier();
+// ------------------------------------------------------------------------------------- communication ring
+// How a [128 rows x cols] bf16 row tile is cut into units of at most kCommStageBytes: `rows` whole rows per unit
+// when a row fits (rows a power of two), else one row piece of `chunk_cols` columns per unit.
+struct CopyGeom {
+  int rows;          // rows per unit
+  int chunk_cols;    // columns per unit
+  int col_chunks;    // units per row (1 when whole rows are moved)
+  int units_per_tile;
+};
+__host__ __device__ inline CopyGeom copy_geom(int cols) {
+  CopyGeom g;
+  const int row_bytes = cols * 2;
+  if (row_bytes <= kCommStageBytes) {
+    int r = 1;
+    while (r * 2 * row_bytes <= kCommStageBytes && r * 2 <= kTpBlockM) r *= 2;
+    g.rows = r;
+    g.chunk_cols = cols;
+    g.col_chunks = 1;
+  } else {
+    g.rows = 1;
+    g.chunk_cols = kCommStageBytes / 2;
+    g.col_chunks = (cols + g.chunk_cols - 1) / g.chunk_cols;
+  }
+  g.units_per_tile = (kTpBlockM / g.rows) * g.col_chunks;
+  return g;
+}
+
+struct CommJob {
+  const uint8_t* src;     // first byte of the unit in local memory
+  long long src_pitch;    // bytes between rows at the source
+  long long dst_off;      // byte offset of the unit in every destination buffer (rows are contiguous there)
+  int rows, row_bytes;
+  int tile;               // row tile the unit belongs to (completion counting)
+};
+
+// One thread moves units through the ring until none is left: claim -> (wait until the unit's source is ready) ->
+// bulk load into a stage -> bulk store to every destination -> completion callback once the stores are done
+// (signalled kCommLag store groups later, so the ring never waits for a round trip over NVLink).
+// Policy: total_units(), describe(u, job), ready(job), num_dests(job), dest(job, i), complete(tile).
+template <class Policy>
+__device__ bool comm_ring_run(const TpShared& s, const TpCommon& c, const Policy& pol) {
+  const int total = pol.total_units();
+  uint32_t filled = 0, stored = 0, signalled = 0;
+  bool exhausted = false, have_next = false;
+  CommJob next{};
+  CommJob inflight[kCommStages];
+  uint64_t t_idle = 0;
+  bool ok = true;
+  for (;;) {
+    bool progress = false;
+    if (!exhausted && !have_next) {
+      const int u = static_cast<int>(atomicAdd(&c.ctrs[kCtrCommClaim], 1u));
+      if (u >= total) exhausted = true;
+      else {
+        pol.describe(u, next);
+        have_next = true;
+      }
+    }
+    if (have_next && filled - stored < static_cast<uint32_t>(kCommStages) && pol.ready(next)) {
+      const int st = filled % kCommStages;
+      uint8_t* dst = s.smem + st * kCommStageBytes;
+      const uint32_t bytes = static_cast<uint32_t>(next.rows) * next.row_bytes;
+      mbar_arrive_expect_tx(&s.comm_bar[st], bytes);
+      if (next.src_pitch == next.row_bytes) {
+        bulk_load(dst, next.src, bytes, &s.comm_bar[st]);
+      } else {
+        for (int r = 0; r < next.rows; ++r)
+          bulk_load(dst + r * next.row_bytes, next.src + r * next.src_pitch, next.row_bytes, &s.comm_bar[st]);
+      }
+#pragma unroll
+      for (int i = 0; i < kCommStages; ++i)
+        if (i == st) inflight[i] = next;
+      ++filled;
+      have_next = false;
+      progress = true;
+    }
+    if (stored < filled) {
+      const int st = stored % kCommStages;
+      if (mbar_try_wait(&s.comm_bar[st], (stored / kCommStages) & 1)) {
+        CommJob j{};
+#pragma unroll
+        for (int i = 0; i < kCommStages; ++i)
+          if (i == st) j = inflight[i];
+        const uint8_t* src = s.smem + st * kCommStageBytes;
+        const uint32_t bytes = static_cast<uint32_t>(j.rows) * j.row_bytes;
+        fence_proxy_async_smem();
+        const int nd = pol.num_dests(j);
+        for (int d = 0; d < nd; ++d) bulk_store(pol.dest(j, d) + j.dst_off, src, bytes);
+        tma_store_commit();
+        s.pend_tile[stored % kCommPend] = j.tile;
+        ++stored;
+        if (stored - signalled > static_cast<uint32_t>(kCommLag)) {
+          tma_store_wait<kCommLag>();              // every group but the newest kCommLag has completed
+          pol.complete(s.pend_tile[signalled % kCommPend]);
+          ++signalled;
+        }
+        tma_store_wait_read<0>();                  // the stage may be refilled
+        progress = true;
+      }
+    }
+    if (exhausted && !have_next && stored == filled) break;
+    if (progress) {
+      t_idle = 0;
+    } else {
+      if (t_idle == 0) t_idle = global_timer_ns();
+      else if (*s.abort_flag || global_timer_ns() - t_idle > c.wait_ns) {
+        ok = false;
+        break;
+      }
+      __nanosleep(64);
+    }
+  }
+  tma_store_wait<0>();
+  if (ok)
+    for (; signalled < stored; ++signalled) pol.complete(s.pend_tile[signalled % kCommPend]);
   return ok;
 }
 
@@ -371,6 +518,44 @@ struct AgArgs {
   int gather_own;                 // also copy this rank's own rows into the own gathered buffer
   PeerPtrs flags;                 // flag page of every rank
   int ldc;
+};
+
+struct AgCommPolicy {
+  const AgArgs& a;
+  CopyGeom g;
+  int tiles_per_rank, slot;
+  __device__ int total_units() const { return tiles_per_rank * g.units_per_tile; }
+  __device__ void describe(int u, CommJob& j) const {
+    const int m_local = u / g.units_per_tile, part = u % g.units_per_tile;
+    const int row = m_local * kTpBlockM + (g.col_chunks == 1 ? part * g.rows : part / g.col_chunks);
+    const int col0 = g.col_chunks == 1 ? 0 : (part % g.col_chunks) * g.chunk_cols;
+    const int cols = min(g.chunk_cols, a.c.K - col0);
+    j.src = reinterpret_cast<const uint8_t*>(a.x_local + static_cast<long long>(row) * a.ldx + col0);
+    j.src_pitch = a.ldx * 2;
+    j.rows = g.rows;
+    j.row_bytes = cols * 2;
+    if (g.col_chunks > 1) j.src_pitch = j.row_bytes;   // a single row piece: one contiguous load
+    j.dst_off = ((static_cast<long long>(a.c.rank) * a.c.rows_local + row) * a.c.K + col0) * 2;
+    j.tile = m_local;
+  }
+  __device__ bool ready(const CommJob&) const { return true; }
+  __device__ int num_dests(const CommJob&) const { return a.c.tp - 1 + (a.gather_own ? 1 : 0); }
+  __device__ uint8_t* dest(const CommJob&, int i) const {   // peers in ring order, the own buffer last
+    return static_cast<uint8_t*>(a.gathered.p[(a.c.rank + 1 + i) % a.c.tp]);
+  }
+  __device__ void complete(int m_local) const {
+    fence_proxy_async_global();
+    __threadfence_system();
+    const uint32_t done = atomicAdd(&a.c.ctrs[kCtrTiles + m_local], 1u);
+    if (done == static_cast<uint32_t>(g.units_per_tile - 1)) {
+      __threadfence_system();
+      for (int r = 0; r < a.c.tp; ++r)
+        if (r != a.c.rank)
+          st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[r]) + kFlagAgBase +
+                             (slot * kTpMaxRanks + a.c.rank) * kTpMaxRowTiles + m_local,
+                         a.c.epoch);
+    }
+  }
 };
 
 template <bool B_MN>
@@ -388,17 +573,28 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int k_blocks = (c.K + kTpBlockK - 1) / kTpBlockK;
   const int slot = c.epoch & 1;
 
-  tp_prologue(s, warp);
+  const bool comm_cta = tp_prologue(s, c, warp);
   const uint32_t tmem_base = *s.tmem_slot;
   if (threadIdx.x == 0) tp_trace(c, kTrEntry);
 
   if (warp == 0) {
-    // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
+      bool alive = true;
+      if (comm_cta) {
+        // ---------------------------------------------------------------- push this rank's rows to every peer
+        tp_trace(c, kTrAuxFirst);
+        const AgCommPolicy pol{a, copy_geom(c.K), tiles_per_rank, slot};
+        if (!comm_ring_run(s, c, pol)) {
+          sched_fail(s, c, kErrProducerWait);
+          alive = false;
+        }
+        tp_trace(c, kTrAuxDone);
+      }
+      // ------------------------------------------------------------------ TMA producer
       uint32_t it = 0;
       unsigned long long ready_mask = 0;  // row tiles < 64 already seen complete (and proxy-fenced) by this thread
-      uint32_t claimed = atomicAdd(&c.ctrs[kCtrTileClaim], 1u);
-      for (uint32_t q = 0;; ++q) {
+      uint32_t claimed = alive ? atomicAdd(&c.ctrs[kCtrTileClaim], 1u) : 0u;
+      for (uint32_t q = 0; alive; ++q) {
         const int tile = sched_produce(s, c, q, num_tiles, claimed);
         if (tile < 0) {
           if (tile == -2) sched_fail(s, c, kErrProducerWait);
@@ -407,7 +603,7 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         int m_log, n_tile;
         decode_tp_tile(tile, num_m, num_n, m_log, n_tile);
-        const int m_tile = physical_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
+        const int m_tile = ag_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
         // Own rows are read where the caller left them; a peer's rows must have landed in the gathered buffer
         // (the peer raises the tile's flag after its stores).
         const bool own = (m_tile / tiles_per_rank) == c.rank;
@@ -437,6 +633,19 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         }
         if (!ok) break;
       }
+      if (num_tiles == 0 && alive) {
+        // Gather only: no product consumes the tiles, so wait here until every peer's rows have landed
+        // (the row tiles are spread over the CTAs).
+        for (int t = blockIdx.x; t < num_m; t += gridDim.x) {
+          if (t / tiles_per_rank == c.rank) continue;
+          const uint32_t* flag = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagAgBase +
+                                 (slot * kTpMaxRanks + t / tiles_per_rank) * kTpMaxRowTiles + t % tiles_per_rank;
+          if (!wait_flag_ge<true>(flag, c.epoch, c.wait_ns, s.abort_flag)) {
+            sched_fail(s, c, kErrPeerFlagWait);
+            break;
+          }
+        }
+      }
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -457,7 +666,7 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       int m_log, n_tile;
       decode_tp_tile(tile, num_m, num_n, m_log, n_tile);
-      const int m_tile = physical_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
+      const int m_tile = ag_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
       const int acc = local_tile & 1;
       if (!mbar_wait_budget(&s.tmem_full[acc], (local_tile >> 1) & 1, c.wait_ns, s.abort_flag)) {
         sched_fail(s, c, kErrEpilogueWait);
@@ -473,82 +682,16 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     if (lane == 0) tma_store_wait<0>();
     if (warp == 2 && lane == 0) tp_trace(c, kTrEpilogueDone);
-  } else {
-    // ------------------------------------------------------------------ comm warps
-    // Unit = 16 rows of one of this rank's row tiles: read once, stored into every peer's gathered buffer
-    // (and the own one when asked to); the unit that completes a tile raises its flag on every peer.
-    const int tid = threadIdx.x - 192;
-    const int total_units = tiles_per_rank * kTpParts;
-    const int vec_per_row = c.K / 8;
-    const int total_vec = kTpPartRows * vec_per_row;
-    if (tid == 0) tp_trace(c, kTrAuxFirst);
-    for (;;) {
-      const int u = aux_claim(s, c.ctrs, tid);
-      if (u >= total_units || *s.abort_flag) {
-        if (tid == 0) tp_trace(c, kTrAuxDone);
-        break;
-      }
-      const int m_local = u / kTpParts, part = u % kTpParts;
-      const long long src_row = static_cast<long long>(m_local) * kTpBlockM + part * kTpPartRows;
-      const __nv_bfloat16* from = a.x_local + src_row * a.ldx;
-      const long long dst_off = (static_cast<long long>(c.rank) * c.rows_local + src_row) * c.K;
-      for (int base = tid; base < total_vec; base += kTpAuxThreads * kAuxLoads) {
-        uint4 v[kAuxLoads];
-#pragma unroll
-        for (int q = 0; q < kAuxLoads; ++q) {
-          const int idx = base + q * kTpAuxThreads;
-          if (idx < total_vec) {
-            const int r = idx / vec_per_row, col = idx - r * vec_per_row;
-            v[q] = ld_cg_v4(from + r * a.ldx + col * 8);
-          }
-        }
-        for (int pr = 1; pr <= c.tp; ++pr) {
-          const int dst_rank = (c.rank + pr) % c.tp;  // peers in ring order, own buffer last
-          if (dst_rank == c.rank && !a.gather_own) continue;
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.gathered.p[dst_rank]) + dst_off;
-#pragma unroll
-          for (int q = 0; q < kAuxLoads; ++q) {
-            const int idx = base + q * kTpAuxThreads;
-            if (idx < total_vec) *reinterpret_cast<uint4*>(dst + static_cast<long long>(idx) * 8) = v[q];
-          }
-        }
-      }
-      __threadfence_system();
-      aux_barrier();
-      if (tid == 0) {
-        const uint32_t done = atomicAdd(&c.ctrs[kCtrTiles + m_local], 1u);
-        if (done == static_cast<uint32_t>(kTpParts - 1)) {
-          __threadfence_system();
-          for (int r = 0; r < c.tp; ++r)
-            if (r != c.rank)
-              st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[r]) + kFlagAgBase +
-                                 (slot * kTpMaxRanks + c.rank) * kTpMaxRowTiles + m_local,
-                             c.epoch);
-        }
-      }
-    }
-    if (num_tiles == 0) {
-      // Gather only: no product consumes the tiles, so wait here until every peer's rows have landed
-      // (the row tiles are spread over the CTAs).
-      bool ok = true;
-      for (int t = blockIdx.x; t < num_m && ok; t += gridDim.x) {
-        if (t / tiles_per_rank == c.rank) continue;
-        const uint32_t* flag = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagAgBase +
-                               (slot * kTpMaxRanks + t / tiles_per_rank) * kTpMaxRowTiles + t % tiles_per_rank;
-        ok = aux_wait_flag<true>(s, c, flag, c.epoch, tid);
-        if (!ok && tid == 0) sched_fail(s, c, kErrPeerFlagWait);
-      }
-    }
   }
   tp_epilogue_sync(s, warp, tmem_base);
   if (threadIdx.x == 0) tp_trace(c, kTrExit);
 }
 
-// Sum the TP partial copies of 16 rows (fixed rank order, fp32) and write bf16.
+// Sum the TP partial copies of a few rows (fixed rank order, fp32) and write bf16.  in[src] points at the first
+// row of the unit inside the partial copy of rank `src`.
 template <int TP>
-__device__ __forceinline__ void reduce_unit(const __nv_bfloat16* __restrict__ in0, long long slot_stride,
-                                            __nv_bfloat16* __restrict__ out0, long long ldo, int vec_per_row,
-                                            int total_vec, int tid) {
+__device__ __forceinline__ void reduce_unit(const __nv_bfloat16* const (&in)[kTpMaxRanks], __nv_bfloat16* __restrict__ out0,
+                                            long long ldo, int vec_per_row, int total_vec, int tid) {
   constexpr int U = (8 / TP) > 0 ? (8 / TP) : 1;  // 8 loads in flight per thread
   for (int base = tid; base < total_vec; base += kTpAuxThreads * U) {
     uint4 v[U][TP];
@@ -557,7 +700,7 @@ __device__ __forceinline__ void reduce_unit(const __nv_bfloat16* __restrict__ in
       const int idx = base + q * kTpAuxThreads;
       if (idx < total_vec) {
 #pragma unroll
-        for (int src = 0; src < TP; ++src) v[q][src] = ld_cg_v4(in0 + src * slot_stride + static_cast<long long>(idx) * 8);
+        for (int src = 0; src < TP; ++src) v[q][src] = ld_cg_v4(in[src] + static_cast<long long>(idx) * 8);
       }
     }
 #pragma unroll
@@ -586,14 +729,59 @@ struct RsArgs {
   TpCommon c;
   __nv_bfloat16* out;             // [rows_local][ldo]
   long long ldo;
+  const __nv_bfloat16* staging;   // local [M][N]: every partial tile this rank computes
   const __nv_bfloat16* recv_self; // this call's receive slot of this rank: [tp src][rows_local][N]
+  PeerPtrs recv;                  // receive slot of every rank
   PeerPtrs flags;                 // flag page of every rank
+};
+
+struct RsCommPolicy {
+  const RsArgs& a;
+  CopyGeom g;
+  int tiles_per_rank, num_m, slot;
+  uint32_t tile_done;             // epilogue warps per finished row tile
+  __device__ int total_units() const { return (num_m - tiles_per_rank) * g.units_per_tile; }
+  __device__ void describe(int u, CommJob& j) const {
+    const int tp = a.c.tp;
+    const int jt = u / g.units_per_tile, part = u % g.units_per_tile;
+    const int logical = (jt / (tp - 1)) * tp + jt % (tp - 1);      // the order the tiles are computed in, own skipped
+    const int m_tile = interleaved_m_tile(logical, tiles_per_rank, a.c.rank, tp);
+    const int m_local = m_tile % tiles_per_rank;
+    const int row = g.col_chunks == 1 ? part * g.rows : part / g.col_chunks;
+    const int col0 = g.col_chunks == 1 ? 0 : (part % g.col_chunks) * g.chunk_cols;
+    const int cols = min(g.chunk_cols, a.c.N - col0);
+    j.src = reinterpret_cast<const uint8_t*>(a.staging + (static_cast<long long>(m_tile) * kTpBlockM + row) * a.c.N + col0);
+    j.rows = g.rows;
+    j.row_bytes = cols * 2;
+    j.src_pitch = g.col_chunks == 1 ? static_cast<long long>(a.c.N) * 2 : j.row_bytes;
+    j.dst_off = ((static_cast<long long>(a.c.rank) * a.c.rows_local + m_local * kTpBlockM + row) * a.c.N + col0) * 2;
+    j.tile = m_tile;
+  }
+  __device__ bool ready(const CommJob& j) const {
+    if (ld_acquire_gpu(&a.c.ctrs[kCtrTiles + j.tile]) < tile_done) return false;
+    fence_proxy_async_global();   // the epilogue's bulk stores, acquired above -> visible to the bulk loads
+    return true;
+  }
+  __device__ int num_dests(const CommJob&) const { return 1; }
+  __device__ uint8_t* dest(const CommJob& j, int) const { return static_cast<uint8_t*>(a.recv.p[j.tile / tiles_per_rank]); }
+  __device__ void complete(int m_tile) const {
+    fence_proxy_async_global();
+    __threadfence_system();
+    const uint32_t done = atomicAdd(&a.c.ctrs[kCtrTiles + num_m + m_tile], 1u);
+    if (done == static_cast<uint32_t>(g.units_per_tile - 1)) {
+      __threadfence_system();
+      const int dest = m_tile / tiles_per_rank, m_local = m_tile % tiles_per_rank;
+      st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[dest]) + kFlagRsBase +
+                         (slot * kTpMaxRowTiles + m_local) * kTpMaxRanks + a.c.rank,
+                     a.c.epoch);
+    }
+  }
 };
 
 template <bool B_MN>
 __global__ void __launch_bounds__(kTpThreads, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const __grid_constant__ TmapArray tmap_dst, const RsArgs a) {
+               const __grid_constant__ CUtensorMap tmap_stage, const RsArgs a) {
   extern __shared__ uint8_t smem_raw[];
   const TpShared s = tp_carve(smem_raw);
   const TpCommon& c = a.c;
@@ -604,37 +792,46 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int tiles_per_rank = c.rows_local / kTpBlockM;
   const int k_blocks = (c.K + kTpBlockK - 1) / kTpBlockK;
   const int slot = c.epoch & 1;
+  const uint32_t tile_done = static_cast<uint32_t>(num_n * 4);
 
-  tp_prologue(s, warp);
+  const bool comm_cta = tp_prologue(s, c, warp);
   const uint32_t tmem_base = *s.tmem_slot;
   if (threadIdx.x == 0) tp_trace(c, kTrEntry);
 
   if (warp == 0) {
     if (lane == 0) {
-      uint32_t it = 0;
-      uint32_t claimed = atomicAdd(&c.ctrs[kCtrTileClaim], 1u);
-      for (uint32_t q = 0;; ++q) {
-        const int tile = sched_produce(s, c, q, num_tiles, claimed);
-        if (tile < 0) {
-          if (tile == -2) sched_fail(s, c, kErrProducerWait);
-          tp_trace(c, kTrProducerDone);
-          break;
-        }
-        int m_log, n_tile;
-        decode_tp_tile(tile, num_m, num_n, m_log, n_tile);
-        const int m_tile = interleaved_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
-        bool ok = true;
-        if (q == 0) tp_trace(c, kTrFirstLoad);
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-          const int st = it % kTpStages;
-          if (!mbar_wait_budget(&s.empty_bar[st], ((it / kTpStages) & 1) ^ 1, c.wait_ns, s.abort_flag)) {
-            sched_fail(s, c, kErrProducerWait);
-            ok = false;
+      if (comm_cta) {
+        // ---------------------------------------------------------------- finished row tiles to their owners
+        sched_end_now(s);   // this CTA computes no tiles: its MMA and epilogue warps leave at once
+        const RsCommPolicy pol{a, copy_geom(c.N), tiles_per_rank, num_m, slot, tile_done};
+        if (!comm_ring_run(s, c, pol)) sched_fail(s, c, kErrProducerWait);
+        tp_trace(c, kTrProducerDone);
+      } else {
+        uint32_t it = 0;
+        uint32_t claimed = atomicAdd(&c.ctrs[kCtrTileClaim], 1u);
+        for (uint32_t q = 0;; ++q) {
+          const int tile = sched_produce(s, c, q, num_tiles, claimed);
+          if (tile < 0) {
+            if (tile == -2) sched_fail(s, c, kErrProducerWait);
+            tp_trace(c, kTrProducerDone);
             break;
           }
-          tp_load_stage<B_MN>(s, st, &tmap_a, &tmap_b, kb * kTpBlockK, m_tile * kTpBlockM, n_tile * kTpBlockN);
+          int m_log, n_tile;
+          decode_tp_tile(tile, num_m, num_n, m_log, n_tile);
+          const int m_tile = interleaved_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
+          bool ok = true;
+          if (q == 0) tp_trace(c, kTrFirstLoad);
+          for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+            const int st = it % kTpStages;
+            if (!mbar_wait_budget(&s.empty_bar[st], ((it / kTpStages) & 1) ^ 1, c.wait_ns, s.abort_flag)) {
+              sched_fail(s, c, kErrProducerWait);
+              ok = false;
+              break;
+            }
+            tp_load_stage<B_MN>(s, st, &tmap_a, &tmap_b, kb * kTpBlockK, m_tile * kTpBlockM, n_tile * kTpBlockN);
+          }
+          if (!ok) break;
         }
-        if (!ok) break;
       }
     }
   } else if (warp == 1) {
@@ -643,22 +840,15 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       tp_trace(c, kTrMmaDone);
     }
   } else if (warp < 6) {
-    // ------------------------------------------------------------------ epilogue: partial tiles to their owners
+    // ------------------------------------------------------------------ epilogue: partial tiles to the staging matrix
     const int quarter = warp & 3;
     uint32_t local_tile = 0, store_count = 0;
     int pending_m = -1;  // row tile whose stores are issued but not yet known complete
-    // lane 0: the bulk stores of `m_tile` by this warp have been performed -> count it, last one raises the flag
+    // lane 0: the bulk stores of `m_tile` by this warp have been performed -> count it
     auto signal_tile = [&](int m_tile) {
       fence_proxy_async_global();
-      __threadfence_system();
-      const uint32_t done = atomicAdd(&c.ctrs[kCtrTiles + m_tile], 1u);
-      if (done == static_cast<uint32_t>(num_n * 4 - 1)) {
-        __threadfence_system();
-        const int dest = m_tile / tiles_per_rank, m_local = m_tile % tiles_per_rank;
-        st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[dest]) + kFlagRsBase +
-                           (slot * kTpMaxRowTiles + m_local) * kTpMaxRanks + c.rank,
-                       c.epoch);
-      }
+      __threadfence();
+      atomicAdd(&c.ctrs[kCtrTiles + m_tile], 1u);
     };
     for (;;) {
       int tile = 0;
@@ -671,18 +861,15 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       int m_log, n_tile;
       decode_tp_tile(tile, num_m, num_n, m_log, n_tile);
       const int m_tile = interleaved_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
-      const int dest = m_tile / tiles_per_rank;
-      const int m_local = m_tile % tiles_per_rank;
       const int acc = local_tile & 1;
       if (!mbar_wait_budget(&s.tmem_full[acc], (local_tile >> 1) & 1, c.wait_ns, s.abort_flag)) {
         sched_fail(s, c, kErrEpilogueWait);
         break;
       }
       tc_fence_after();
-      // receive slot of `dest`: rows [rank * rows_local, (rank + 1) * rows_local) belong to this sender
       const uint32_t before = store_count;
-      tp_store_tile(s, tmem_base, acc, quarter, warp - 2, lane, &tmap_dst.m[dest], n_tile * kTpBlockN,
-                    c.rank * c.rows_local + m_local * kTpBlockM + quarter * 32, c.N, store_count);
+      tp_store_tile(s, tmem_base, acc, quarter, warp - 2, lane, &tmap_stage, n_tile * kTpBlockN,
+                    m_tile * kTpBlockM + quarter * 32, c.N, store_count);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
@@ -730,11 +917,19 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       }
       const int m_local = u / kRsParts, part = u % kRsParts;
       if (m_local != ready_tile) {
-        // one thread waits for the partial tile of every rank, then everybody learns the outcome
+        // one thread waits for the partial tile of every rank (the own one in the staging matrix), then
+        // everybody learns the outcome
         if (tid == 0) {
           int good = 1;
-          for (int src = 0; src < c.tp && good; ++src)
-            good = wait_flag_ge<true>(my_flags + m_local * kTpMaxRanks + src, c.epoch, c.wait_ns, s.abort_flag) ? 1 : 0;
+          for (int src = 0; src < c.tp && good; ++src) {
+            if (src == c.rank)
+              good = wait_flag_ge<false>(&c.ctrs[kCtrTiles + c.rank * tiles_per_rank + m_local], tile_done, c.wait_ns,
+                                         s.abort_flag) ? 1 : 0;
+            else
+              good = wait_flag_ge<true>(my_flags + m_local * kTpMaxRanks + src, c.epoch, c.wait_ns, s.abort_flag) ? 1 : 0;
+          }
+          // partial tiles were written through the async proxy (bulk stores): order them before the plain loads
+          fence_proxy_async_global();
           *s.claim_slot = good;
         }
         aux_barrier();
@@ -751,13 +946,17 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         ready_tile = m_local;
       }
       const long long row0 = static_cast<long long>(m_local) * kTpBlockM + part * kRsPartRows;
-      const __nv_bfloat16* in0 = a.recv_self + row0 * c.N;
+      const __nv_bfloat16* in[kTpMaxRanks];
+#pragma unroll
+      for (int src = 0; src < kTpMaxRanks; ++src)
+        in[src] = (src == c.rank) ? a.staging + (static_cast<long long>(c.rank) * c.rows_local + row0) * c.N
+                                  : a.recv_self + src * slot_stride + row0 * c.N;
       __nv_bfloat16* out0 = a.out + row0 * a.ldo;
       switch (c.tp) {
-        case 2: reduce_unit<2>(in0, slot_stride, out0, a.ldo, vec_per_row, total_vec, tid); break;
-        case 4: reduce_unit<4>(in0, slot_stride, out0, a.ldo, vec_per_row, total_vec, tid); break;
-        case 8: reduce_unit<8>(in0, slot_stride, out0, a.ldo, vec_per_row, total_vec, tid); break;
-        default: reduce_unit<1>(in0, slot_stride, out0, a.ldo, vec_per_row, total_vec, tid); break;
+        case 2: reduce_unit<2>(in, out0, a.ldo, vec_per_row, total_vec, tid); break;
+        case 4: reduce_unit<4>(in, out0, a.ldo, vec_per_row, total_vec, tid); break;
+        case 8: reduce_unit<8>(in, out0, a.ldo, vec_per_row, total_vec, tid); break;
+        default: reduce_unit<1>(in, out0, a.ldo, vec_per_row, total_vec, tid); break;
       }
     }
   }
@@ -778,6 +977,17 @@ static int tp_check(int rows_local, int N, int K, int tp, int rank) {
   return 0;
 }
 
+// Comm CTAs for a transfer of `bytes` over NVLink that should not outlast a GEMM of `flops`: one CTA moves about
+// 35 GB/s through its ring and sixteen saturate the links; a few more than the rate asks for keep the tail short.
+static int choose_comm_ctas(double bytes, double flops, int grid) {
+  const double t_gemm = flops / 1.3e15 + 5e-6;
+  int n = static_cast<int>(bytes / t_gemm / 35e9) + 3;
+  if (n < 4) n = 4;
+  if (n > 20) n = 20;
+  if (n > grid / 2) n = grid / 2 > 0 ? grid / 2 : 1;
+  return n;
+}
+
 }  // namespace stb
 
 using namespace stb;
@@ -785,7 +995,7 @@ using namespace stb;
 // Words of symmetric flag memory a rank must provide (zero-initialised once, before the first call).
 extern "C" int stb_tp_flag_words() { return kFlagWords; }
 // Words of local counter scratch needed for `row_tiles` = tp * rows_local / 128 row tiles.
-extern "C" int stb_tp_ctr_words(int row_tiles) { return kCtrTiles + row_tiles; }
+extern "C" int stb_tp_ctr_words(int row_tiles) { return kCtrTiles + 2 * row_tiles; }
 
 // C[tp*rows_local, N] = all_gather_rows(x_local) * B^T (b_mn_major = 0, B stored [N][ldb]) or * B
 // (b_mn_major = 1, B stored [K][ldb]); `gathered` [tp*rows_local][K] receives the gathered rows.
@@ -793,11 +1003,13 @@ extern "C" int stb_tp_ctr_words(int row_tiles) { return kCtrTiles + row_tiles; }
 // reads them from x_local).  gathered_ptrs[r] / flag_ptrs[r]: rank r's gathered buffer for this call (slot =
 // epoch & 1, tp*rows_local*K bf16, symmetric memory) and flag page, as mapped into this process; the result is
 // in gathered_ptrs[rank] and stays valid until the second-next call on the group.  epoch: 1, 2, 3, ... per group,
-// the same on every rank.  ctrs: local scratch of stb_tp_ctr_words(row tiles) words.
+// the same on every rank.  ctrs: local scratch of stb_tp_ctr_words(row tiles) words.  comm_ctas: CTAs that push
+// the rows before they join the product (0 = chosen from the sizes).
 extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* const* gathered_ptrs,
                                 void* const* flag_ptrs, const void* B, void* C, int rows_local, int N, int K, int ldb,
                                 int ldc, int b_mn_major, int gather_own, int rank, int tp, unsigned epoch, void* ctrs,
-                                unsigned long long wait_ns, int* status, void* trace, cudaStream_t stream) {
+                                unsigned long long wait_ns, int comm_ctas, int* status, void* trace,
+                                cudaStream_t stream) {
   int r = tp_check(rows_local, N, K, tp, rank);
   if (r) return r;
   if ((ldx & 7) || (N > 0 && ((ldb & 7) || (ldc & 7)))) return -kErrBadArgument;
@@ -817,8 +1029,21 @@ extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* const*
     tb = ta;
     tc = ta;
   }
+  int grid = sm_count();
+  const double out_bytes = static_cast<double>(tp - 1) * rows_local * K * 2;
+  if (comm_ctas <= 0) {
+    // these CTAs join the product once the rows are out, so a few more than the rate asks for cost nothing
+    comm_ctas = choose_comm_ctas(out_bytes, 2.0 * M * static_cast<double>(N) * K, grid);
+    if (comm_ctas < 12) comm_ctas = 12;
+  }
+  if (N == 0) {
+    comm_ctas = comm_ctas < 16 ? 16 : comm_ctas;   // nothing to multiply: only the comm CTAs are launched
+    grid = comm_ctas;
+  }
+  if (comm_ctas > grid) comm_ctas = grid;
   AgArgs a{};
   a.c.M = M; a.c.N = N; a.c.K = K; a.c.rank = rank; a.c.tp = tp; a.c.rows_local = rows_local;
+  a.c.n_comm = comm_ctas;
   a.c.epoch = epoch; a.c.ctrs = static_cast<uint32_t*>(ctrs); a.c.wait_ns = wait_ns; a.c.status = status;
   a.c.trace = static_cast<unsigned long long*>(trace);
   a.x_local = static_cast<const __nv_bfloat16*>(x_local);
@@ -829,7 +1054,7 @@ extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* const*
     a.gathered.p[i] = gathered_ptrs[i];
     a.flags.p[i] = flag_ptrs[i];
   }
-  cudaError_t e = cudaMemsetAsync(ctrs, 0, sizeof(uint32_t) * (kCtrTiles + M / kTpBlockM), stream);
+  cudaError_t e = cudaMemsetAsync(ctrs, 0, sizeof(uint32_t) * (kCtrTiles + 2 * (M / kTpBlockM)), stream);
   if (e != cudaSuccess) return -static_cast<int>(e);
   static bool configured[2] = {false, false};
   if (!configured[b_mn_major ? 1 : 0]) {
@@ -837,7 +1062,6 @@ extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* const*
     if (r) return r;
     configured[b_mn_major ? 1 : 0] = true;
   }
-  const int grid = sm_count();
   if (b_mn_major) gemm_ag_kernel<true><<<grid, kTpThreads, kTpSmem, stream>>>(ta, tx, tb, tc, a);
   else gemm_ag_kernel<false><<<grid, kTpThreads, kTpSmem, stream>>>(ta, tx, tb, tc, a);
   e = cudaGetLastError();
@@ -845,35 +1069,45 @@ extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* const*
 }
 
 // out[rows_local, N] = reduce_scatter_rows(A[tp*rows_local, K] * B^T or * B).  recv_ptrs[r]: rank r's receive
-// slot for this call (slot = epoch & 1; tp*rows_local*N bf16), flag_ptrs[r]: rank r's flag page.
+// slot for this call (slot = epoch & 1; tp*rows_local*N bf16), flag_ptrs[r]: rank r's flag page.  staging: local
+// scratch of tp*rows_local*N bf16 (the rank's partial products; free again when the call has finished).
+// comm_ctas: CTAs that copy finished row tiles to their owners instead of computing (0 = chosen from the sizes).
 extern "C" int stb_gemm_rs_bf16(const void* A, int lda, const void* B, int ldb, int b_mn_major, void* out,
-                                long long ldo, void* const* recv_ptrs, void* const* flag_ptrs, int rows_local, int N,
-                                int K, int rank, int tp, unsigned epoch, void* ctrs, unsigned long long wait_ns,
-                                int* status, void* trace, cudaStream_t stream) {
+                                long long ldo, void* staging, void* const* recv_ptrs, void* const* flag_ptrs,
+                                int rows_local, int N, int K, int rank, int tp, unsigned epoch, void* ctrs,
+                                unsigned long long wait_ns, int comm_ctas, int* status, void* trace,
+                                cudaStream_t stream) {
   int r = tp_check(rows_local, N, K, tp, rank);
   if (r) return r;
-  if (N <= 0 || (lda & 7) || (ldb & 7) || (ldo & 7)) return -kErrBadArgument;
+  if (N <= 0 || (lda & 7) || (ldb & 7) || (ldo & 7) || staging == nullptr) return -kErrBadArgument;
   const int M = tp * rows_local;
-  CUtensorMap ta, tb;
-  TmapArray td;
+  CUtensorMap ta, tb, ts;
   r = make_tmap_2d_bf16(&ta, A, K, M, static_cast<uint64_t>(lda) * 2, kTpBlockK, kTpBlockM, 1);
   if (r) return r;
   if (!b_mn_major) r = make_tmap_2d_bf16(&tb, B, K, N, static_cast<uint64_t>(ldb) * 2, kTpBlockK, kTpBlockN, 1);
   else r = make_tmap_2d_bf16(&tb, B, N, K, static_cast<uint64_t>(ldb) * 2, 64, kTpBlockK, 1);
   if (r) return r;
-  for (int i = 0; i < kTpMaxRanks; ++i) {
-    r = make_tmap_2d(&td.m[i], recv_ptrs[i < tp ? i : rank], 2, N, M, static_cast<uint64_t>(N) * 2, 64, 32, 1);
-    if (r) return r;
-  }
+  r = make_tmap_2d(&ts, staging, 2, N, M, static_cast<uint64_t>(N) * 2, 64, 32, 1);
+  if (r) return r;
+  const int grid = sm_count();
+  const double out_bytes = static_cast<double>(tp - 1) * rows_local * N * 2;
+  if (comm_ctas <= 0) comm_ctas = choose_comm_ctas(out_bytes, 2.0 * M * static_cast<double>(N) * K, grid);
+  if (comm_ctas >= grid) comm_ctas = grid - 1;
+  if (comm_ctas < 1) return -kErrBadArgument;    // one CTA cannot both compute and send
   RsArgs a{};
   a.c.M = M; a.c.N = N; a.c.K = K; a.c.rank = rank; a.c.tp = tp; a.c.rows_local = rows_local;
+  a.c.n_comm = comm_ctas;
   a.c.epoch = epoch; a.c.ctrs = static_cast<uint32_t*>(ctrs); a.c.wait_ns = wait_ns; a.c.status = status;
   a.c.trace = static_cast<unsigned long long*>(trace);
   a.out = static_cast<__nv_bfloat16*>(out);
   a.ldo = ldo;
+  a.staging = static_cast<const __nv_bfloat16*>(staging);
   a.recv_self = static_cast<const __nv_bfloat16*>(recv_ptrs[rank]);
-  for (int i = 0; i < tp; ++i) a.flags.p[i] = flag_ptrs[i];
-  cudaError_t e = cudaMemsetAsync(ctrs, 0, sizeof(uint32_t) * (kCtrTiles + M / kTpBlockM), stream);
+  for (int i = 0; i < tp; ++i) {
+    a.recv.p[i] = recv_ptrs[i];
+    a.flags.p[i] = flag_ptrs[i];
+  }
+  cudaError_t e = cudaMemsetAsync(ctrs, 0, sizeof(uint32_t) * (kCtrTiles + 2 * (M / kTpBlockM)), stream);
   if (e != cudaSuccess) return -static_cast<int>(e);
   static bool configured[2] = {false, false};
   if (!configured[b_mn_major ? 1 : 0]) {
@@ -881,9 +1115,8 @@ extern "C" int stb_gemm_rs_bf16(const void* A, int lda, const void* B, int ldb, 
     if (r) return r;
     configured[b_mn_major ? 1 : 0] = true;
   }
-  const int grid = sm_count();
-  if (b_mn_major) gemm_rs_kernel<true><<<grid, kTpThreads, kTpSmem, stream>>>(ta, tb, td, a);
-  else gemm_rs_kernel<false><<<grid, kTpThreads, kTpSmem, stream>>>(ta, tb, td, a);
+  if (b_mn_major) gemm_rs_kernel<true><<<grid, kTpThreads, kTpSmem, stream>>>(ta, tb, ts, a);
+  else gemm_rs_kernel<false><<<grid, kTpThreads, kTpSmem, stream>>>(ta, tb, ts, a);
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }

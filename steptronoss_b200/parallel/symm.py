@@ -14,7 +14,8 @@ CPU/gloo runs, groups that span nodes and shapes the kernels do not take (row bl
 multiple of 128).
 
 Environment: ``STB200_PEER_TP=0`` disables the peer path; ``STB200_PEER_WAIT_S`` (default 30) bounds every
-wait on another rank inside the kernels.
+wait on another rank inside the kernels; ``STB200_TP_COMM_CTAS`` fixes how many CTAs of a fused launch move data
+with bulk copies (default: chosen from the transfer size and the GEMM's length).
 """
 from __future__ import annotations
 
@@ -33,6 +34,7 @@ _MAX_RANKS = 8
 _ARENAS: dict[str, "Arena | None"] = {}
 _DISABLED = os.environ.get("STB200_PEER_TP", "1") == "0"
 _WAIT_NS = int(float(os.environ.get("STB200_PEER_WAIT_S", "30")) * 1e9)
+_COMM_CTAS = int(os.environ.get("STB200_TP_COMM_CTAS", "0"))   # CTAs in the communication role; 0 = from the sizes
 _TRACE = None  # int64 [SMs, 8] tensor set by trace(): per-CTA phase stamps of the next fused launches
 
 
@@ -64,10 +66,10 @@ native.register_signature("stb_symm_open", [P, P])
 native.register_signature("stb_symm_close", [P])
 native.register_signature("stb_symm_free", [P])
 native.register_signature(
-    "stb_gemm_ag_bf16", [P, L, P, P, P, P, I, I, I, I, I, I, I, I, I, U, P, ULL, P, P, P]
+    "stb_gemm_ag_bf16", [P, L, P, P, P, P, I, I, I, I, I, I, I, I, I, U, P, ULL, I, P, P, P]
 )
 native.register_signature(
-    "stb_gemm_rs_bf16", [P, I, P, I, I, P, L, P, P, I, I, I, I, I, U, P, ULL, P, P, P]
+    "stb_gemm_rs_bf16", [P, I, P, I, I, P, L, P, P, P, I, I, I, I, I, U, P, ULL, I, P, P, P]
 )
 
 
@@ -154,6 +156,7 @@ class Arena:
         self.recv: SymmetricBuffer | None = None    # 2 slots
         self.stage_slot = 0
         self.recv_slot = 0
+        self.partials: torch.Tensor | None = None   # local staging matrix of the reduce-scatter kernel
         self.ag_epoch = 0
         self.rs_epoch = 0
         self.ctrs = torch.zeros(self.lib.stb_tp_ctr_words(_MAX_RANKS * 1024), dtype=torch.int32, device="cuda")
@@ -178,6 +181,13 @@ class Arena:
             self._grow("stage", need)
         off = (epoch & 1) * self.stage_slot
         return self.stage.ptr_array(off), self.stage.own_tensor()[off: off + need]
+
+    def partial_staging(self, need: int) -> torch.Tensor:
+        """Local scratch for the partial products of one reduce-scatter launch (reused by the next launch: the
+        kernel that read it has finished by then, launches on a group are stream-ordered)."""
+        if self.partials is None or self.partials.numel() < need:
+            self.partials = torch.empty((need + (1 << 20) - 1) & ~((1 << 20) - 1), dtype=torch.uint8, device="cuda")
+        return self.partials
 
     def recv_ptrs(self, need: int, epoch: int):
         if need > self.recv_slot:
@@ -220,7 +230,8 @@ def usable(rows_local: int, k: int, n: int, *tensors) -> bool:
     """Shapes and dtypes the fused kernels take."""
     if rows_local <= 0 or rows_local % 128 or rows_local // 128 > 1024 or k % 8 or n % 8:
         return False
-    return all(t.is_cuda and t.dtype == torch.bfloat16 and t.stride(-1) == 1 for t in tensors)
+    return all(t.is_cuda and t.dtype == torch.bfloat16 and t.stride(-1) == 1 and t.data_ptr() % 16 == 0
+               and (t.dim() < 2 or t.stride(0) % 8 == 0) for t in tensors)
 
 
 def all_gather_gemm(x, w, group_name: str = "TP", *, b_mn_major: bool = False, out_dtype=None,
@@ -245,7 +256,7 @@ def all_gather_gemm(x, w, group_name: str = "TP", *, b_mn_major: bool = False, o
         x.data_ptr(), x.stride(0), ptrs, a._flag_arr,
         w.data_ptr() if n else None, y.data_ptr() if n else None, rows, n, k,
         w.stride(0) if n else 8, y.stride(0) if n else 8, int(b_mn_major), int(need_gathered), a.rank, a.world,
-        a.ag_epoch & 0xFFFFFFFF, a.ctrs.data_ptr(), _WAIT_NS, native.status_word(x.device).data_ptr(),
+        a.ag_epoch & 0xFFFFFFFF, a.ctrs.data_ptr(), _WAIT_NS, _COMM_CTAS, native.status_word(x.device).data_ptr(),
         _TRACE.data_ptr() if _TRACE is not None else None, native.stream(),
     )
     native.check(rc, f"all_gather_gemm rows={rows} N={n} K={k}")
@@ -264,10 +275,12 @@ def gemm_reduce_scatter(x, w, group_name: str = "TP", *, b_mn_major: bool = Fals
     out = torch.empty((rows, n), dtype=x.dtype, device=x.device)
     a.rs_epoch += 1
     recv = a.recv_ptrs(m * n * 2, a.rs_epoch)
+    staging = a.partial_staging(m * n * 2)
     rc = a.lib.stb_gemm_rs_bf16(
         x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), int(b_mn_major), out.data_ptr(), out.stride(0),
-        recv, a._flag_arr, rows, n, k, a.rank, a.world, a.rs_epoch & 0xFFFFFFFF, a.ctrs.data_ptr(), _WAIT_NS,
-        native.status_word(x.device).data_ptr(), _TRACE.data_ptr() if _TRACE is not None else None, native.stream(),
+        staging.data_ptr(), recv, a._flag_arr, rows, n, k, a.rank, a.world, a.rs_epoch & 0xFFFFFFFF, a.ctrs.data_ptr(),
+        _WAIT_NS, _COMM_CTAS, native.status_word(x.device).data_ptr(),
+        _TRACE.data_ptr() if _TRACE is not None else None, native.stream(),
     )
     native.check(rc, f"gemm_reduce_scatter M={m} N={n} K={k}")
     count_launch(2)

@@ -71,6 +71,17 @@ def test_fused_gemm_collectives_match_nccl_statement():
     assert res["max_err"] and max(res["max_err"].values()) < 1e-2
 
 
+def test_fused_gemm_collectives_match_nccl_statement_on_four_gpus():
+    """The same check at TP=4, the degree of the 8-GPU headline layout (three peers per push, four partial copies
+    per reduced tile)."""
+    import torch
+
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs >= 4 CUDA devices")
+    res = _launch_fused(4, "check", 29703)
+    assert res["max_err"] and max(res["max_err"].values()) < 1e-2
+
+
 def test_fused_gemm_collective_wait_runs_out_without_hanging():
     """A rank that stays away from one call: the peer's bounded wait reports code 5, the next call works."""
     res = _launch_fused(2, "timeout", 29702)
