@@ -54,6 +54,48 @@ __device__ __forceinline__ void load_stream_tile(void* dst, const CUtensorMap* m
   tma_load_3d(static_cast<uint8_t*>(dst) + kStreamSlab, m, bar, 64, head, row);
 }
 
+// Softmax-gradient math of one thread for its 32 columns of a streamed tile:
+//   P' = exp2(S' * c - lse),  dS' = P' o (dP' - delta)      (the softmax scale is applied to dK / dQ in the epilogue)
+// `cl` holds the per-column constants of the dK/dV pass ([64] lse * log2e, then [64] delta); the dQ pass has them
+// per row.  MASK is decided per tile by the caller, so interior tiles run without a predicate per element.
+template <bool DKV, bool MASK>
+__device__ __forceinline__ void bwd_tile_math(const AttnParams& p, const SegInfo& s, const uint32_t (&sv)[32],
+                                              const uint32_t (&dv)[32], const float* cl, int half, int r, int fi, int g0,
+                                              float sl2, float row_lse2, float row_delta, uint8_t* pP, uint8_t* pdS) {
+#pragma unroll
+  for (int c8l = 0; c8l < 4; ++c8l) {
+    const int c8 = half * 4 + c8l;
+    float lse8[8], dl8[8];
+    if (DKV) {
+      const float4 l0 = *reinterpret_cast<const float4*>(cl + c8 * 8), l1 = *reinterpret_cast<const float4*>(cl + c8 * 8 + 4);
+      const float4 d0 = *reinterpret_cast<const float4*>(cl + 64 + c8 * 8), d1 = *reinterpret_cast<const float4*>(cl + 64 + c8 * 8 + 4);
+      lse8[0] = l0.x; lse8[1] = l0.y; lse8[2] = l0.z; lse8[3] = l0.w; lse8[4] = l1.x; lse8[5] = l1.y; lse8[6] = l1.z; lse8[7] = l1.w;
+      dl8[0] = d0.x; dl8[1] = d0.y; dl8[2] = d0.z; dl8[3] = d0.w; dl8[4] = d1.x; dl8[5] = d1.y; dl8[6] = d1.z; dl8[7] = d1.w;
+    }
+    float pv[8], dd[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int lc = c8l * 8 + i;          // index into this thread's 32 columns
+      const float lse2 = DKV ? lse8[i] : row_lse2;
+      const float dl = DKV ? dl8[i] : row_delta;
+      float pr = exp2f(fmaf(__uint_as_float(sv[lc]), sl2, -lse2));
+      if (MASK) {
+        const int col = half * 32 + lc;    // column of the streamed tile
+        const bool vis = DKV ? visible(p, s, g0 + col, fi) : visible(p, s, fi, g0 + col);
+        if (!vis) pr = 0.f;
+      }
+      pv[i] = pr;
+      dd[i] = pr * (__uint_as_float(dv[lc]) - dl);
+    }
+    const uint32_t a = swz(r, c8);
+    if (DKV)
+      *reinterpret_cast<uint4*>(pP + a) =
+          make_uint4(pack_bf16(pv[0], pv[1]), pack_bf16(pv[2], pv[3]), pack_bf16(pv[4], pv[5]), pack_bf16(pv[6], pv[7]));
+    *reinterpret_cast<uint4*>(pdS + a) =
+        make_uint4(pack_bf16(dd[0], dd[1]), pack_bf16(dd[2], dd[3]), pack_bf16(dd[4], dd[5]), pack_bf16(dd[6], dd[7]));
+  }
+}
+
 template <bool DKV>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_constant__ CUtensorMap tmap_f2,
@@ -252,31 +294,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
       uint8_t* pP = sP + buf * 2 * kPTile;
       uint8_t* pdS = pP + kPTile;
       const float* cl = s_lse + buf * 128;
+      if (!frow_ok) {
+        // a fixed row past the end of its segment: its P' and dS' rows are zero
+        const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-      for (int c8l = 0; c8l < 4; ++c8l) {
-        const int c8 = half * 4 + c8l;
-        float pv[8], dd[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int lc = c8l * 8 + i;          // index into this thread's 32 columns
-          const int col = half * 32 + lc;      // column of the streamed tile
-          const float lse2 = DKV ? cl[col] : row_lse2;
-          const float dl = DKV ? cl[64 + col] : row_delta;
-          float pr = exp2f(__uint_as_float(sv[lc]) * sl2 - lse2);
-          if (need_mask) {
-            const bool vis = DKV ? visible(p, s, g0 + col, fi) : visible(p, s, fi, g0 + col);
-            if (!vis) pr = 0.f;
-          }
-          if (!frow_ok) pr = 0.f;
-          pv[i] = pr;
-          dd[i] = pr * (__uint_as_float(dv[lc]) - dl) * p.scale;
+        for (int c8l = 0; c8l < 4; ++c8l) {
+          const uint32_t a = swz(r, half * 4 + c8l);
+          if (DKV) *reinterpret_cast<uint4*>(pP + a) = z;
+          *reinterpret_cast<uint4*>(pdS + a) = z;
         }
-        const uint32_t a = swz(r, c8);
-        if (DKV)
-          *reinterpret_cast<uint4*>(pP + a) =
-              make_uint4(pack_bf16(pv[0], pv[1]), pack_bf16(pv[2], pv[3]), pack_bf16(pv[4], pv[5]), pack_bf16(pv[6], pv[7]));
-        *reinterpret_cast<uint4*>(pdS + a) =
-            make_uint4(pack_bf16(dd[0], dd[1]), pack_bf16(dd[2], dd[3]), pack_bf16(dd[4], dd[5]), pack_bf16(dd[6], dd[7]));
+      } else if (need_mask) {
+        bwd_tile_math<DKV, true>(p, s, sv, dv, cl, half, r, fi, g0, sl2, row_lse2, row_delta, pP, pdS);
+      } else {
+        bwd_tile_math<DKV, false>(p, s, sv, dv, cl, half, r, fi, g0, sl2, row_lse2, row_delta, pP, pdS);
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -299,6 +329,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
         if (iters > 0 && ok) {
           tmem_ld_32x32(tmem + lane_addr + 256 + which * 128 + c * 32, v);
           tmem_wait_ld();
+          if (!DKV || which == 1) {   // dK and dQ were accumulated from unscaled dS'
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * p.scale);
+          }
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0u;

@@ -167,17 +167,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         tmem_ld_32x32(tmem + lane_addr + st * 128 + half * 64 + c * 32, part);
       }
       tmem_wait_ld();
-      float mx = -INFINITY;
       if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
+        for (int i = 0; i < 64; ++i)
           if (!visible(p, s, qi, kb + i)) v[i] = 0xff800000u;  // -inf
-          mx = fmaxf(mx, __uint_as_float(v[i]));
-        }
-      } else {
-#pragma unroll
-        for (int i = 0; i < 64; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
       }
+      // eight independent chains instead of one of 64 dependent maxima
+      float mx8[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx8[i] = __uint_as_float(v[i]);
+#pragma unroll
+      for (int i = 8; i < 64; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(v[i]));
+      float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       // exchange the partial maximum with the thread that owns the other half of this row; both use the
       // bf16-rounded values so that they arrive at the same reference
       __nv_bfloat16* slot = xchg + (j & 1) * 256;
@@ -209,20 +210,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
         m_ref = m_new;
       }
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-      float rowsum = 0.f;
+      float rs8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // independent partial sums (no 64-long add chain)
       uint8_t* slab = (st ? sP1 : sP0) + half * kSlabBytes;  // 64 keys = one 128-byte-wide slab
 #pragma unroll
       for (int c8 = 0; c8 < 8; ++c8) {  // 8 chunks of 8 keys = 16 bytes of bf16
         float pr[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          pr[i] = exp2f(__uint_as_float(v[c8 * 8 + i]) * sl2 - m_use);
-          rowsum += pr[i];
+          pr[i] = exp2f(fmaf(__uint_as_float(v[c8 * 8 + i]), sl2, -m_use));
+          rs8[i] += pr[i];
         }
         *reinterpret_cast<uint4*>(slab + swz(r, c8)) =
             make_uint4(pack_bf16(pr[0], pr[1]), pack_bf16(pr[2], pr[3]), pack_bf16(pr[4], pr[5]), pack_bf16(pr[6], pr[7]));
       }
-      l += rowsum;
+      l += ((rs8[0] + rs8[1]) + (rs8[2] + rs8[3])) + ((rs8[4] + rs8[5]) + (rs8[6] + rs8[7]));
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&p_full[st]);

@@ -13,8 +13,9 @@
 // the GEMM stages would otherwise use.
 //
 //   all-gather -> GEMM   comm CTAs push this rank's rows, 32 KB at a time, into every peer's gathered matrix (one
-//                        load, tp-1 stores) and raise a per-row-tile flag on the peers when a tile is complete;
-//                        when the rows are out they turn into GEMM CTAs.  The TMA producer of a GEMM CTA waits
+//                        load, tp-1 stores).  A comm CTA owns whole 32-row parts of a row tile, so it alone knows
+//                        when a part has landed and raises that part's flag on the peers (no counting across
+//                        CTAs, no atomics on the path); when the rows are out the comm CTAs turn into GEMM CTAs.  The TMA producer of a GEMM CTA waits
 //                        for the flag of the row tile it is about to load.  Own rows are multiplied first (read
 //                        where the caller left them), the peers' row tiles then in the order they arrive.
 //   GEMM -> reduce-scatter  the epilogue TMA-stores bf16 partial tiles into a local staging matrix at full speed;
@@ -32,8 +33,9 @@
 // used alternately by epoch parity.  A slot written in call e was last read in call e-2 (and by what the
 // caller ran right after it), and no rank can leave call e-1 before every peer has entered call e-1 (each
 // call consumes data that every peer produces inside the same call), so two slots need no further hand-shake.
-// GEMM tiles, communication units and reduce units are claimed from device counters, so progress never depends
-// on a CTA that is not resident.  Every wait is bounded by the caller's budget; on time-out the kernel records a
+// GEMM tiles and reduce units are claimed from device counters and the communication work is striped over the
+// CTAs that hold a comm ticket (tickets go to CTAs that are running), so progress never depends on a CTA that is
+// not resident.  Every wait is bounded by the caller's budget; on time-out the kernel records a
 // code in the status word, drains and returns.  No load uses cluster broadcast; peers are only written to.
 #include "common.cuh"
 #include <string.h>
@@ -50,9 +52,11 @@ constexpr int kTpMaxRanks = 8;
 
 // Layout of the symmetric flag page (uint32 words).
 constexpr int kTpMaxRowTiles = 1024;              // row tiles of 128 per rank
-constexpr int kFlagRsBase = 64;                   // [slot 2][row tile][src 8]   partial tile of `src` has landed
-constexpr int kFlagAgBase = kFlagRsBase + 2 * kTpMaxRowTiles * kTpMaxRanks;  // [slot 2][src 8][row tile] staged
-constexpr int kFlagWords = kFlagAgBase + 2 * kTpMaxRanks * kTpMaxRowTiles;
+constexpr int kTpParts = 4;                       // a row tile travels as 4 parts of 32 rows, each with its own flag
+constexpr int kTpPartRows = kTpBlockM / kTpParts;
+constexpr int kFlagRsBase = 64;                   // [slot 2][row tile][src 8][part 4]   part of the partial tile of `src` has landed
+constexpr int kFlagAgBase = kFlagRsBase + 2 * kTpMaxRowTiles * kTpMaxRanks * kTpParts;  // [slot 2][src 8][row tile][part 4]
+constexpr int kFlagWords = kFlagAgBase + 2 * kTpMaxRanks * kTpMaxRowTiles * kTpParts;
 constexpr int kRsParts = 16;                      // the reduction works on 8-row slices: a short tail after the
 constexpr int kRsPartRows = kTpBlockM / kRsParts; // last partial tile has landed
 
@@ -60,10 +64,8 @@ constexpr int kRsPartRows = kTpBlockM / kRsParts; // last partial tile has lande
 constexpr int kCtrClaim = 0;      // next reduce unit
 constexpr int kCtrTicket = 1;     // CTAs that have started (the first n_comm become comm CTAs)
 constexpr int kCtrTileClaim = 2;  // next GEMM tile
-constexpr int kCtrCommClaim = 3;  // next communication unit
 constexpr int kSchedDepth = 4;    // claimed tiles the producer may run ahead of the slowest consumer
-constexpr int kCtrTiles = 8;      // [row tile]  all-gather: units pushed; reduce-scatter: epilogue warps finished
-                                  // [row tiles + row tile]  reduce-scatter: units copied to the owner
+constexpr int kCtrTiles = 8;      // [row tile]  reduce-scatter: epilogue warps that have stored their share of the tile
 
 constexpr int kTpABytes = kTpBlockM * kTpBlockK * 2;
 constexpr int kTpBBytes = kTpBlockN * kTpBlockK * 2;
@@ -76,7 +78,7 @@ constexpr int kTpSmem = kTpStages * kTpStageBytes + kTpStoreBytes + kTpBarrierBy
 constexpr int kCommStageBytes = 32 * 1024;
 constexpr int kCommStages = (kTpStages * kTpStageBytes) / kCommStageBytes;   // 6
 constexpr int kCommLag = 3;       // a unit's completion is signalled once three younger store groups were issued
-constexpr int kCommPend = 8;      // ring of units stored but not yet signalled (> kCommLag)
+constexpr int kCommPend = 8;      // ring of store groups issued but not yet known complete (> kCommLag)
 static_assert(kCommStages * kCommStageBytes <= kTpStages * kTpStageBytes, "ring must fit in the operand stages");
 
 struct PeerPtrs {
@@ -95,6 +97,9 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
 }
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 __device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
@@ -212,8 +217,8 @@ __device__ __forceinline__ TpShared tp_carve(uint8_t* smem_raw) {
 static_assert((2 * kTpStages + 4 + 2 * kSchedDepth + kCommStages) * 8 + (5 + kSchedDepth + kCommPend) * 4 <= kTpBarrierBytes,
               "barrier region too small");
 
-// Returns true when this CTA takes the communication role.
-__device__ __forceinline__ bool tp_prologue(const TpShared& s, const TpCommon& c, int warp) {
+// Returns this CTA's communication ticket (0 .. n_comm-1), or -1 when it only computes.
+__device__ __forceinline__ int tp_prologue(const TpShared& s, const TpCommon& c, int warp) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < kTpStages; ++i) {
       mbar_init(&s.full_bar[i], 1);
@@ -229,7 +234,8 @@ __device__ __forceinline__ bool tp_prologue(const TpShared& s, const TpCommon& c
     }
     for (int i = 0; i < kCommStages; ++i) mbar_init(&s.comm_bar[i], 1);
     *s.abort_flag = 0;
-    *s.role_slot = (atomicAdd(&c.ctrs[kCtrTicket], 1u) < static_cast<uint32_t>(c.n_comm)) ? 1 : 0;
+    const uint32_t ticket = atomicAdd(&c.ctrs[kCtrTicket], 1u);
+    *s.role_slot = ticket < static_cast<uint32_t>(c.n_comm) ? static_cast<int>(ticket) : -1;
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -239,7 +245,7 @@ __device__ __forceinline__ bool tp_prologue(const TpShared& s, const TpCommon& c
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  return *s.role_slot != 0;
+  return *s.role_slot;
 }
 
 __device__ __forceinline__ void tp_epilogue_sync(const TpShared& s, int warp, uint32_t tmem_base) {
@@ -392,20 +398,20 @@ __device__ __forceinline__ int aux_claim(const TpShared& s, uint32_t* ctrs, int 
 }
 
 // ------------------------------------------------------------------------------------- communication ring
-// How a [128 rows x cols] bf16 row tile is cut into units of at most kCommStageBytes: `rows` whole rows per unit
+// How a part ([32 rows x cols] bf16) is cut into units of at most kCommStageBytes: `rows` whole rows per unit
 // when a row fits (rows a power of two), else one row piece of `chunk_cols` columns per unit.
 struct CopyGeom {
   int rows;          // rows per unit
   int chunk_cols;    // columns per unit
   int col_chunks;    // units per row (1 when whole rows are moved)
-  int units_per_tile;
+  int units_per_part;
 };
 __host__ __device__ inline CopyGeom copy_geom(int cols) {
   CopyGeom g;
   const int row_bytes = cols * 2;
   if (row_bytes <= kCommStageBytes) {
     int r = 1;
-    while (r * 2 * row_bytes <= kCommStageBytes && r * 2 <= kTpBlockM) r *= 2;
+    while (r * 2 * row_bytes <= kCommStageBytes && r * 2 <= kTpPartRows) r *= 2;
     g.rows = r;
     g.chunk_cols = cols;
     g.col_chunks = 1;
@@ -414,8 +420,14 @@ __host__ __device__ inline CopyGeom copy_geom(int cols) {
     g.chunk_cols = kCommStageBytes / 2;
     g.col_chunks = (cols + g.chunk_cols - 1) / g.chunk_cols;
   }
-  g.units_per_tile = (kTpBlockM / g.rows) * g.col_chunks;
+  g.units_per_part = (kTpPartRows / g.rows) * g.col_chunks;
   return g;
+}
+// (row inside the part, first column, columns) of unit `sub` of a part
+__device__ __forceinline__ void unit_window(const CopyGeom& g, int sub, int total_cols, int& row, int& col0, int& cols) {
+  row = g.col_chunks == 1 ? sub * g.rows : sub / g.col_chunks;
+  col0 = g.col_chunks == 1 ? 0 : (sub % g.col_chunks) * g.chunk_cols;
+  cols = min(g.chunk_cols, total_cols - col0);
 }
 
 struct CommJob {
@@ -423,49 +435,54 @@ struct CommJob {
   long long src_pitch;    // bytes between rows at the source
   long long dst_off;      // byte offset of the unit in every destination buffer (rows are contiguous there)
   int rows, row_bytes;
-  int tile;               // row tile the unit belongs to (completion counting)
+  int item;               // the part this unit belongs to
+  int last;               // 1: the last unit of its part
 };
 
-// One thread moves units through the ring until none is left: claim -> (wait until the unit's source is ready) ->
-// bulk load into a stage -> bulk store to every destination -> completion callback once the stores are done
-// (signalled kCommLag store groups later, so the ring never waits for a round trip over NVLink).
-// Policy: total_units(), describe(u, job), ready(job), num_dests(job), dest(job, i), complete(tile).
+// One thread of a comm CTA moves its share of the parts through the ring: item = ticket, ticket + n_comm, ...;
+// per unit: (wait until the part's source is ready) -> bulk load into a stage -> bulk store to every destination.
+// A part's completion callback runs once the store group of its last unit has completed; that is checked
+// kCommLag store groups later, so the ring never waits for a round trip over NVLink.
+// Policy: num_items(), units_per_item(), describe(item, sub, job), ready(item), num_dests(job), dest(job, i), complete(item).
 template <class Policy>
-__device__ bool comm_ring_run(const TpShared& s, const TpCommon& c, const Policy& pol) {
-  const int total = pol.total_units();
+__device__ bool comm_ring_run(const TpShared& s, const TpCommon& c, int ticket, const Policy& pol) {
+  const int num_items = pol.num_items();
+  const int upi = pol.units_per_item();
+  int item = ticket, sub = 0;            // next unit to load
+  int ready_item = -1;                   // last item whose source was seen ready
   uint32_t filled = 0, stored = 0, signalled = 0;
-  bool exhausted = false, have_next = false;
-  CommJob next{};
   CommJob inflight[kCommStages];
   uint64_t t_idle = 0;
   bool ok = true;
   for (;;) {
     bool progress = false;
-    if (!exhausted && !have_next) {
-      const int u = static_cast<int>(atomicAdd(&c.ctrs[kCtrCommClaim], 1u));
-      if (u >= total) exhausted = true;
-      else {
-        pol.describe(u, next);
-        have_next = true;
-      }
-    }
-    if (have_next && filled - stored < static_cast<uint32_t>(kCommStages) && pol.ready(next)) {
-      const int st = filled % kCommStages;
-      uint8_t* dst = s.smem + st * kCommStageBytes;
-      const uint32_t bytes = static_cast<uint32_t>(next.rows) * next.row_bytes;
-      mbar_arrive_expect_tx(&s.comm_bar[st], bytes);
-      if (next.src_pitch == next.row_bytes) {
-        bulk_load(dst, next.src, bytes, &s.comm_bar[st]);
-      } else {
-        for (int r = 0; r < next.rows; ++r)
-          bulk_load(dst + r * next.row_bytes, next.src + r * next.src_pitch, next.row_bytes, &s.comm_bar[st]);
-      }
+    if (item < num_items && filled - stored < static_cast<uint32_t>(kCommStages)) {
+      if (ready_item != item && pol.ready(item)) ready_item = item;
+      if (ready_item == item) {
+        CommJob j;
+        pol.describe(item, sub, j);
+        j.item = item;
+        j.last = (sub == upi - 1) ? 1 : 0;
+        const int st = filled % kCommStages;
+        uint8_t* dst = s.smem + st * kCommStageBytes;
+        const uint32_t bytes = static_cast<uint32_t>(j.rows) * j.row_bytes;
+        mbar_arrive_expect_tx(&s.comm_bar[st], bytes);
+        if (j.src_pitch == j.row_bytes) {
+          bulk_load(dst, j.src, bytes, &s.comm_bar[st]);
+        } else {
+          for (int r = 0; r < j.rows; ++r)
+            bulk_load(dst + r * j.row_bytes, j.src + r * j.src_pitch, j.row_bytes, &s.comm_bar[st]);
+        }
 #pragma unroll
-      for (int i = 0; i < kCommStages; ++i)
-        if (i == st) inflight[i] = next;
-      ++filled;
-      have_next = false;
-      progress = true;
+        for (int i = 0; i < kCommStages; ++i)
+          if (i == st) inflight[i] = j;
+        ++filled;
+        if (++sub == upi) {
+          sub = 0;
+          item += c.n_comm;
+        }
+        progress = true;
+      }
     }
     if (stored < filled) {
       const int st = stored % kCommStages;
@@ -480,18 +497,21 @@ __device__ bool comm_ring_run(const TpShared& s, const TpCommon& c, const Policy
         const int nd = pol.num_dests(j);
         for (int d = 0; d < nd; ++d) bulk_store(pol.dest(j, d) + j.dst_off, src, bytes);
         tma_store_commit();
-        s.pend_tile[stored % kCommPend] = j.tile;
+        s.pend_tile[stored % kCommPend] = j.last ? j.item : -1;
         ++stored;
         if (stored - signalled > static_cast<uint32_t>(kCommLag)) {
-          tma_store_wait<kCommLag>();              // every group but the newest kCommLag has completed
-          pol.complete(s.pend_tile[signalled % kCommPend]);
+          const int done_item = s.pend_tile[signalled % kCommPend];
+          if (done_item >= 0) {
+            tma_store_wait<kCommLag>();            // every group but the newest kCommLag has completed
+            pol.complete(done_item);
+          }
           ++signalled;
         }
         tma_store_wait_read<0>();                  // the stage may be refilled
         progress = true;
       }
     }
-    if (exhausted && !have_next && stored == filled) break;
+    if (item >= num_items && stored == filled) break;
     if (progress) {
       t_idle = 0;
     } else {
@@ -505,7 +525,10 @@ __device__ bool comm_ring_run(const TpShared& s, const TpCommon& c, const Policy
   }
   tma_store_wait<0>();
   if (ok)
-    for (; signalled < stored; ++signalled) pol.complete(s.pend_tile[signalled % kCommPend]);
+    for (; signalled < stored; ++signalled) {
+      const int done_item = s.pend_tile[signalled % kCommPend];
+      if (done_item >= 0) pol.complete(done_item);
+    }
   return ok;
 }
 
@@ -524,37 +547,32 @@ struct AgCommPolicy {
   const AgArgs& a;
   CopyGeom g;
   int tiles_per_rank, slot;
-  __device__ int total_units() const { return tiles_per_rank * g.units_per_tile; }
-  __device__ void describe(int u, CommJob& j) const {
-    const int m_local = u / g.units_per_tile, part = u % g.units_per_tile;
-    const int row = m_local * kTpBlockM + (g.col_chunks == 1 ? part * g.rows : part / g.col_chunks);
-    const int col0 = g.col_chunks == 1 ? 0 : (part % g.col_chunks) * g.chunk_cols;
-    const int cols = min(g.chunk_cols, a.c.K - col0);
+  __device__ int num_items() const { return tiles_per_rank * kTpParts; }
+  __device__ int units_per_item() const { return g.units_per_part; }
+  __device__ void describe(int item, int sub, CommJob& j) const {
+    int row, col0, cols;
+    unit_window(g, sub, a.c.K, row, col0, cols);
+    row += item * kTpPartRows;                       // row inside this rank's block
     j.src = reinterpret_cast<const uint8_t*>(a.x_local + static_cast<long long>(row) * a.ldx + col0);
-    j.src_pitch = a.ldx * 2;
     j.rows = g.rows;
     j.row_bytes = cols * 2;
-    if (g.col_chunks > 1) j.src_pitch = j.row_bytes;   // a single row piece: one contiguous load
+    j.src_pitch = g.col_chunks == 1 ? a.ldx * 2 : j.row_bytes;   // a single row piece is one contiguous load
     j.dst_off = ((static_cast<long long>(a.c.rank) * a.c.rows_local + row) * a.c.K + col0) * 2;
-    j.tile = m_local;
   }
-  __device__ bool ready(const CommJob&) const { return true; }
+  __device__ bool ready(int) const { return true; }
   __device__ int num_dests(const CommJob&) const { return a.c.tp - 1 + (a.gather_own ? 1 : 0); }
   __device__ uint8_t* dest(const CommJob&, int i) const {   // peers in ring order, the own buffer last
     return static_cast<uint8_t*>(a.gathered.p[(a.c.rank + 1 + i) % a.c.tp]);
   }
-  __device__ void complete(int m_local) const {
+  // the part's rows have landed on every peer: tell them
+  __device__ void complete(int item) const {
     fence_proxy_async_global();
-    __threadfence_system();
-    const uint32_t done = atomicAdd(&a.c.ctrs[kCtrTiles + m_local], 1u);
-    if (done == static_cast<uint32_t>(g.units_per_tile - 1)) {
-      __threadfence_system();
-      for (int r = 0; r < a.c.tp; ++r)
-        if (r != a.c.rank)
-          st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[r]) + kFlagAgBase +
-                             (slot * kTpMaxRanks + a.c.rank) * kTpMaxRowTiles + m_local,
-                         a.c.epoch);
-    }
+    __threadfence_system();        // one release fence, then plain system-scope stores of the flag to every peer
+    for (int r = 0; r < a.c.tp; ++r)
+      if (r != a.c.rank)
+        st_relaxed_sys(reinterpret_cast<uint32_t*>(a.flags.p[r]) + kFlagAgBase +
+                           ((slot * kTpMaxRanks + a.c.rank) * kTpMaxRowTiles) * kTpParts + item,
+                       a.c.epoch);
   }
 };
 
@@ -573,18 +591,18 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int k_blocks = (c.K + kTpBlockK - 1) / kTpBlockK;
   const int slot = c.epoch & 1;
 
-  const bool comm_cta = tp_prologue(s, c, warp);
+  const int ticket = tp_prologue(s, c, warp);
   const uint32_t tmem_base = *s.tmem_slot;
   if (threadIdx.x == 0) tp_trace(c, kTrEntry);
 
   if (warp == 0) {
     if (lane == 0) {
       bool alive = true;
-      if (comm_cta) {
+      if (ticket >= 0) {
         // ---------------------------------------------------------------- push this rank's rows to every peer
         tp_trace(c, kTrAuxFirst);
         const AgCommPolicy pol{a, copy_geom(c.K), tiles_per_rank, slot};
-        if (!comm_ring_run(s, c, pol)) {
+        if (!comm_ring_run(s, c, ticket, pol)) {
           sched_fail(s, c, kErrProducerWait);
           alive = false;
         }
@@ -609,9 +627,12 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const bool own = (m_tile / tiles_per_rank) == c.rank;
         if (!own && !(m_tile < 64 && ((ready_mask >> m_tile) & 1ull))) {
           const uint32_t* flag = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagAgBase +
-                                 (slot * kTpMaxRanks + m_tile / tiles_per_rank) * kTpMaxRowTiles +
-                                 m_tile % tiles_per_rank;
-          if (!wait_flag_ge<true>(flag, c.epoch, c.wait_ns, s.abort_flag)) {
+                                 ((slot * kTpMaxRanks + m_tile / tiles_per_rank) * kTpMaxRowTiles +
+                                  m_tile % tiles_per_rank) * kTpParts;
+          bool landed = true;
+          for (int part = 0; part < kTpParts && landed; ++part)
+            landed = wait_flag_ge<true>(flag + part, c.epoch, c.wait_ns, s.abort_flag);
+          if (!landed) {
             sched_fail(s, c, kErrPeerFlagWait);
             break;
           }
@@ -639,8 +660,11 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         for (int t = blockIdx.x; t < num_m; t += gridDim.x) {
           if (t / tiles_per_rank == c.rank) continue;
           const uint32_t* flag = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagAgBase +
-                                 (slot * kTpMaxRanks + t / tiles_per_rank) * kTpMaxRowTiles + t % tiles_per_rank;
-          if (!wait_flag_ge<true>(flag, c.epoch, c.wait_ns, s.abort_flag)) {
+                                 ((slot * kTpMaxRanks + t / tiles_per_rank) * kTpMaxRowTiles + t % tiles_per_rank) * kTpParts;
+          bool landed = true;
+          for (int part = 0; part < kTpParts && landed; ++part)
+            landed = wait_flag_ge<true>(flag + part, c.epoch, c.wait_ns, s.abort_flag);
+          if (!landed) {
             sched_fail(s, c, kErrPeerFlagWait);
             break;
           }
@@ -740,41 +764,41 @@ struct RsCommPolicy {
   CopyGeom g;
   int tiles_per_rank, num_m, slot;
   uint32_t tile_done;             // epilogue warps per finished row tile
-  __device__ int total_units() const { return (num_m - tiles_per_rank) * g.units_per_tile; }
-  __device__ void describe(int u, CommJob& j) const {
-    const int tp = a.c.tp;
-    const int jt = u / g.units_per_tile, part = u % g.units_per_tile;
-    const int logical = (jt / (tp - 1)) * tp + jt % (tp - 1);      // the order the tiles are computed in, own skipped
-    const int m_tile = interleaved_m_tile(logical, tiles_per_rank, a.c.rank, tp);
-    const int m_local = m_tile % tiles_per_rank;
-    const int row = g.col_chunks == 1 ? part * g.rows : part / g.col_chunks;
-    const int col0 = g.col_chunks == 1 ? 0 : (part % g.col_chunks) * g.chunk_cols;
-    const int cols = min(g.chunk_cols, a.c.N - col0);
+  // item = (remote row tile in the order the tiles are computed, part)
+  __device__ int num_items() const { return (num_m - tiles_per_rank) * kTpParts; }
+  __device__ int units_per_item() const { return g.units_per_part; }
+  __device__ int tile_of(int item) const {
+    const int tp = a.c.tp, jt = item / kTpParts;
+    const int logical = (jt / (tp - 1)) * tp + jt % (tp - 1);      // own tiles (logical % tp == tp - 1) skipped
+    return interleaved_m_tile(logical, tiles_per_rank, a.c.rank, tp);
+  }
+  __device__ void describe(int item, int sub, CommJob& j) const {
+    const int m_tile = tile_of(item), m_local = m_tile % tiles_per_rank;
+    int row, col0, cols;
+    unit_window(g, sub, a.c.N, row, col0, cols);
+    row += (item % kTpParts) * kTpPartRows;          // row inside the tile
     j.src = reinterpret_cast<const uint8_t*>(a.staging + (static_cast<long long>(m_tile) * kTpBlockM + row) * a.c.N + col0);
     j.rows = g.rows;
     j.row_bytes = cols * 2;
     j.src_pitch = g.col_chunks == 1 ? static_cast<long long>(a.c.N) * 2 : j.row_bytes;
     j.dst_off = ((static_cast<long long>(a.c.rank) * a.c.rows_local + m_local * kTpBlockM + row) * a.c.N + col0) * 2;
-    j.tile = m_tile;
   }
-  __device__ bool ready(const CommJob& j) const {
-    if (ld_acquire_gpu(&a.c.ctrs[kCtrTiles + j.tile]) < tile_done) return false;
+  __device__ bool ready(int item) const {
+    if (ld_acquire_gpu(&a.c.ctrs[kCtrTiles + tile_of(item)]) < tile_done) return false;
     fence_proxy_async_global();   // the epilogue's bulk stores, acquired above -> visible to the bulk loads
     return true;
   }
   __device__ int num_dests(const CommJob&) const { return 1; }
-  __device__ uint8_t* dest(const CommJob& j, int) const { return static_cast<uint8_t*>(a.recv.p[j.tile / tiles_per_rank]); }
-  __device__ void complete(int m_tile) const {
+  __device__ uint8_t* dest(const CommJob& j, int) const {
+    return static_cast<uint8_t*>(a.recv.p[tile_of(j.item) / tiles_per_rank]);
+  }
+  __device__ void complete(int item) const {
+    const int m_tile = tile_of(item);
+    const int dest = m_tile / tiles_per_rank, m_local = m_tile % tiles_per_rank;
     fence_proxy_async_global();
-    __threadfence_system();
-    const uint32_t done = atomicAdd(&a.c.ctrs[kCtrTiles + num_m + m_tile], 1u);
-    if (done == static_cast<uint32_t>(g.units_per_tile - 1)) {
-      __threadfence_system();
-      const int dest = m_tile / tiles_per_rank, m_local = m_tile % tiles_per_rank;
-      st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[dest]) + kFlagRsBase +
-                         (slot * kTpMaxRowTiles + m_local) * kTpMaxRanks + a.c.rank,
-                     a.c.epoch);
-    }
+    st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[dest]) + kFlagRsBase +
+                       (((slot * kTpMaxRowTiles + m_local) * kTpMaxRanks + a.c.rank) * kTpParts) + item % kTpParts,
+                   a.c.epoch);
   }
 };
 
@@ -794,17 +818,17 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int slot = c.epoch & 1;
   const uint32_t tile_done = static_cast<uint32_t>(num_n * 4);
 
-  const bool comm_cta = tp_prologue(s, c, warp);
+  const int ticket = tp_prologue(s, c, warp);
   const uint32_t tmem_base = *s.tmem_slot;
   if (threadIdx.x == 0) tp_trace(c, kTrEntry);
 
   if (warp == 0) {
     if (lane == 0) {
-      if (comm_cta) {
+      if (ticket >= 0) {
         // ---------------------------------------------------------------- finished row tiles to their owners
         sched_end_now(s);   // this CTA computes no tiles: its MMA and epilogue warps leave at once
         const RsCommPolicy pol{a, copy_geom(c.N), tiles_per_rank, num_m, slot, tile_done};
-        if (!comm_ring_run(s, c, pol)) sched_fail(s, c, kErrProducerWait);
+        if (!comm_ring_run(s, c, ticket, pol)) sched_fail(s, c, kErrProducerWait);
         tp_trace(c, kTrProducerDone);
       } else {
         uint32_t it = 0;
@@ -905,8 +929,8 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int total_vec = kRsPartRows * vec_per_row;
     const long long slot_stride = static_cast<long long>(c.rows_local) * c.N;
     const uint32_t* my_flags = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagRsBase +
-                               slot * kTpMaxRowTiles * kTpMaxRanks;
-    int ready_tile = -1;
+                               slot * kTpMaxRowTiles * kTpMaxRanks * kTpParts;
+    int ready_part = -1;            // (row tile, part) whose partial copies were last seen complete
     bool failed = false;
     if (tid == 0) tp_trace(c, kTrAuxFirst);
     for (;;) {
@@ -916,9 +940,10 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         break;
       }
       const int m_local = u / kRsParts, part = u % kRsParts;
-      if (m_local != ready_tile) {
-        // one thread waits for the partial tile of every rank (the own one in the staging matrix), then
-        // everybody learns the outcome
+      const int tpart = part / (kRsParts / kTpParts);      // the 32-row part this 8-row slice lies in
+      if (m_local * kTpParts + tpart != ready_part) {
+        // one thread waits for that part of the partial tile of every rank (the own one in the staging matrix),
+        // then everybody learns the outcome
         if (tid == 0) {
           int good = 1;
           for (int src = 0; src < c.tp && good; ++src) {
@@ -926,7 +951,8 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
               good = wait_flag_ge<false>(&c.ctrs[kCtrTiles + c.rank * tiles_per_rank + m_local], tile_done, c.wait_ns,
                                          s.abort_flag) ? 1 : 0;
             else
-              good = wait_flag_ge<true>(my_flags + m_local * kTpMaxRanks + src, c.epoch, c.wait_ns, s.abort_flag) ? 1 : 0;
+              good = wait_flag_ge<true>(my_flags + (m_local * kTpMaxRanks + src) * kTpParts + tpart, c.epoch, c.wait_ns,
+                                        s.abort_flag) ? 1 : 0;
           }
           // partial tiles were written through the async proxy (bulk stores): order them before the plain loads
           fence_proxy_async_global();
@@ -943,7 +969,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           failed = true;
           continue;
         }
-        ready_tile = m_local;
+        ready_part = m_local * kTpParts + tpart;
       }
       const long long row0 = static_cast<long long>(m_local) * kTpBlockM + part * kRsPartRows;
       const __nv_bfloat16* in[kTpMaxRanks];
@@ -995,7 +1021,7 @@ using namespace stb;
 // Words of symmetric flag memory a rank must provide (zero-initialised once, before the first call).
 extern "C" int stb_tp_flag_words() { return kFlagWords; }
 // Words of local counter scratch needed for `row_tiles` = tp * rows_local / 128 row tiles.
-extern "C" int stb_tp_ctr_words(int row_tiles) { return kCtrTiles + 2 * row_tiles; }
+extern "C" int stb_tp_ctr_words(int row_tiles) { return kCtrTiles + row_tiles; }
 
 // C[tp*rows_local, N] = all_gather_rows(x_local) * B^T (b_mn_major = 0, B stored [N][ldb]) or * B
 // (b_mn_major = 1, B stored [K][ldb]); `gathered` [tp*rows_local][K] receives the gathered rows.
@@ -1054,7 +1080,7 @@ extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* const*
     a.gathered.p[i] = gathered_ptrs[i];
     a.flags.p[i] = flag_ptrs[i];
   }
-  cudaError_t e = cudaMemsetAsync(ctrs, 0, sizeof(uint32_t) * (kCtrTiles + 2 * (M / kTpBlockM)), stream);
+  cudaError_t e = cudaMemsetAsync(ctrs, 0, sizeof(uint32_t) * (kCtrTiles + M / kTpBlockM), stream);
   if (e != cudaSuccess) return -static_cast<int>(e);
   static bool configured[2] = {false, false};
   if (!configured[b_mn_major ? 1 : 0]) {
@@ -1107,7 +1133,7 @@ extern "C" int stb_gemm_rs_bf16(const void* A, int lda, const void* B, int ldb, 
     a.recv.p[i] = recv_ptrs[i];
     a.flags.p[i] = flag_ptrs[i];
   }
-  cudaError_t e = cudaMemsetAsync(ctrs, 0, sizeof(uint32_t) * (kCtrTiles + 2 * (M / kTpBlockM)), stream);
+  cudaError_t e = cudaMemsetAsync(ctrs, 0, sizeof(uint32_t) * (kCtrTiles + M / kTpBlockM), stream);
   if (e != cudaSuccess) return -static_cast<int>(e);
   static bool configured[2] = {false, false};
   if (!configured[b_mn_major ? 1 : 0]) {
