@@ -81,7 +81,8 @@ def main():
             row["trace"] = trace
         rows_out.append(row)
         if rank == 0:
-            print(json.dumps(row), flush=True)
+            shown = {k: v for k, v in row.items() if k != "trace"}
+            print(json.dumps(shown), flush=True)
 
     def traced(fn):
         if not args.trace:
@@ -90,6 +91,7 @@ def main():
         fn()
         torch.cuda.synchronize()
         out = symm.trace_summary()
+        out["rows"] = symm.trace_rows()
         symm.trace(False)
         return out
 

@@ -34,6 +34,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--mb", type=int, default=192, help="MiB moved per rank and direction")
     ap.add_argument("--iters", type=int, default=5)
+    ap.add_argument("--ring-mb", type=int, default=32, help="MiB per rank moved by the ring variants")
+    ap.add_argument("--ring-only", action="store_true", help="skip the plain / bulk sweeps")
     ap.add_argument("--json", default=None)
     args = ap.parse_args()
 
@@ -107,13 +109,52 @@ def main():
         return total / (float(t.item()) * 1e-3) / 1e9
 
     res = {"ranks": W, "mib_per_rank": total >> 20, "gbs": {}}
-    for grid in (16, 32, 64, 148, 296):
+    for grid in (() if args.ring_only else (16, 32, 64, 148, 296)):
         res["gbs"][f"push_st_g{grid}"] = timed(lambda: run(True, 0, grid, 0))
         res["gbs"][f"pull_ld_g{grid}"] = timed(lambda: run(False, 0, grid, 0))
-    for chunk in (2048, 8192, 32768):
+    for chunk in (() if args.ring_only else (2048, 8192, 32768)):
         for grid in (16, 32, 64, 148):
             res["gbs"][f"push_bulk_c{chunk}_g{grid}"] = timed(lambda: run(True, 1, grid, chunk))
             res["gbs"][f"pull_bulk_c{chunk}_g{grid}"] = timed(lambda: run(False, 1, grid, chunk))
+    # the ring of the fused kernels at their transfer size, extras switched on one by one (`--ring-mb` per rank)
+    native.register_signature("stb_peer_copy_ring", [P, P, P, P, L, I, I, I, I, P, P])
+    ring_bytes = min(per_peer, (args.ring_mb << 20) // len(peers) // 4096 * 4096)
+    scratch = torch.empty(ring_bytes, dtype=torch.uint8, device=dev)
+    flags = symm.SymmetricBuffer(4096, PM.group_of("TP"), lib)
+
+    def run_ring(grid, stages, feat):
+        g = max(1, grid // len(peers))
+        cur = torch.cuda.current_stream()
+        for i, p in enumerate(peers):
+            side[i].wait_stream(cur)
+            their_off = ((rank - p) % W - 1) * per_peer
+            rc = lib.stb_peer_copy_ring(local.data_ptr() + i * per_peer, buf.ptrs[p] + their_off, scratch.data_ptr(),
+                                        flags.ptrs[p], ring_bytes, g, 32768, stages, feat, status.data_ptr(),
+                                        side[i].cuda_stream)
+            native.check(rc, "stb_peer_copy_ring")
+        for s in side:
+            cur.wait_stream(s)
+
+    def timed_ring(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        beg, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        beg.record()
+        for _ in range(10):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([beg.elapsed_time(end) / 10], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return {"us": float(t.item()) * 1e3, "gbs": ring_bytes * len(peers) / (float(t.item()) * 1e-3) / 1e9}
+
+    res["ring"] = {"mib_per_rank": ring_bytes * len(peers) >> 20}
+    for grid in (16, 20, 32):
+        for stages in (4, 6):
+            for feat in (0, 1, 2, 3, 4, 8, 15):
+                res["ring"][f"g{grid}_s{stages}_f{feat}"] = timed_ring(lambda: run_ring(grid, stages, feat))
     res["gbs"]["memcpy_push"] = timed(lambda: run_memcpy(True))
     res["gbs"]["memcpy_pull"] = timed(lambda: run_memcpy(False))
     # correctness of the last push: what landed in my zone from each peer equals that peer's source slice
@@ -140,6 +181,7 @@ def main():
     torch.cuda.synchronize()
     dist.barrier()
     buf.release()
+    flags.release()
     dist.barrier()
 
 

@@ -1,42 +1,35 @@
 // Sequence-parallel projections as single kernels over NVLink peer memory (sm_100a).
 //
-//   gemm_ag_kernel : C = all_gather_rows(x) * B^T.   The gathered matrix lives in symmetric memory.
-//   gemm_rs_kernel : out = reduce_scatter_rows(A * B^T).
-//
-// Both are the persistent tcgen05 GEMM of gemm_sm100.cu (TMA producer warp, MMA warp, four epilogue warps,
-// tiles claimed from a device counter) plus a communication role that a few CTAs take.  Measured on this
-// hardware, sixteen CTAs that each drive a ring of 32 KB cp.async.bulk copies (global -> shared -> peer global)
-// saturate a GPU's NVLink ports (about 675 GB/s per direction), while 16-byte stores issued by a few warps of
-// every CTA or 128-byte TMA tensor stores from the GEMM epilogue reach 440-550 GB/s and stall the tensor pipe.
-// So the first `n_comm` CTAs to start (a ticket from a device counter: roles never depend on a CTA that is not
-// resident) become "comm CTAs": one thread of theirs moves rows with bulk copies through the shared memory that
-// the GEMM stages would otherwise use.
-//
-//   all-gather -> GEMM   comm CTAs push this rank's rows, 32 KB at a time, into every peer's gathered matrix (one
-//                        load, tp-1 stores).  A comm CTA owns whole 32-row parts of a row tile, so it alone knows
-//                        when a part has landed and raises that part's flag on the peers (no counting across
-//                        CTAs, no atomics on the path); when the rows are out the comm CTAs turn into GEMM CTAs.  The TMA producer of a GEMM CTA waits
-//                        for the flag of the row tile it is about to load.  Own rows are multiplied first (read
-//                        where the caller left them), the peers' row tiles then in the order they arrive.
-//   GEMM -> reduce-scatter  the epilogue TMA-stores bf16 partial tiles into a local staging matrix at full speed;
-//                        comm CTAs copy every finished row tile that another rank owns into that rank's receive
-//                        slot and raise its flag; four "reduce" warps per CTA add the tp partial copies of the
-//                        row tiles this rank owns in fixed rank order (fp32) as they complete (the own partial
-//                        straight out of the staging matrix).  Row blocks are computed next-rank first, own last.
+//   gemm_ag_kernel : C = all_gather_rows(x) * B^T.   The gathered matrix lives in symmetric memory.  Four
+//                    "comm" warps in every CTA push this rank's rows, 16-row slices at a time, straight into
+//                    every peer's gathered buffer (plain 16-byte peer stores: posted writes keep NVLink busy, a
+//                    few thousand threads saturate the links, and a slice is complete after one fence) and raise
+//                    a per-row-tile flag on the peer when a tile is complete.  The TMA producer of the tcgen05
+//                    GEMM waits for the flag of the row tile it is about to load, so products of rows that have
+//                    arrived overlap the transfer of the rest.  Own rows are multiplied first (read where the
+//                    caller left them); the peers' row tiles follow in the order they arrive (every peer pushes
+//                    its tiles in ascending order to all ranks at once: tile i of every peer, then tile i+1).
+//   gemm_rs_kernel : out = reduce_scatter_rows(A * B^T).  The epilogue TMA-stores every bf16 partial tile into a
+//                    local staging matrix, at full speed: no store of the tensor pipeline's critical path ever
+//                    crosses NVLink.  The four extra warps of every CTA forward finished row tiles that another
+//                    rank owns into that rank's receive slot (plain peer stores, a flag per tile) and add the tp
+//                    partial copies of the row tiles this rank owns in fixed rank order (fp32), the own partial
+//                    straight out of the staging matrix.  Row blocks are computed next-rank first, own block
+//                    last, and the forwarding / reduction units are handed out in that same order.
 //
 // They replace the NCCL collective + cuBLAS pairs of the reference's sequence-parallel linears
 // (steptronoss/core/tensor_parallel/layers.py:151-346, mappings.py:103-300).
 //
 // Cross-rank protocol.  Flags are uint32 words in each rank's symmetric flag page, written into the peer's
-// page with st.release.sys and read from the own page with ld.acquire.sys; they carry the call number
-// ("epoch", compared wrap-safe), so nothing is ever reset.  Gathered and receive buffers have two slots
-// used alternately by epoch parity.  A slot written in call e was last read in call e-2 (and by what the
-// caller ran right after it), and no rank can leave call e-1 before every peer has entered call e-1 (each
-// call consumes data that every peer produces inside the same call), so two slots need no further hand-shake.
-// GEMM tiles and reduce units are claimed from device counters and the communication work is striped over the
-// CTAs that hold a comm ticket (tickets go to CTAs that are running), so progress never depends on a CTA that is
-// not resident.  Every wait is bounded by the caller's budget; on time-out the kernel records a
-// code in the status word, drains and returns.  No load uses cluster broadcast; peers are only written to.
+// page with st.release.sys and polled in the own page (relaxed loads, one acquire fence after the poll that
+// succeeds); they carry the call number ("epoch", compared wrap-safe), so nothing is ever reset.  Gathered and
+// receive buffers have two slots used alternately by epoch parity.  A slot written in call e was last read in
+// call e-2 (and by what the caller ran right after it), and no rank can leave call e-1 before every peer has
+// entered call e-1 (each call consumes data that every peer produces inside the same call), so two slots need no
+// further hand-shake.  GEMM tiles and the work of the extra warps are claimed from device counters, not assigned
+// by CTA index, so progress never depends on a CTA that is not resident (for instance while a collective of
+// another stream holds some SMs and is itself waiting for the peer).  Every wait is bounded by the caller's
+// budget; on time-out the kernel records a code in the status word, drains and returns.
 #include "common.cuh"
 #include <string.h>
 
@@ -46,40 +39,33 @@ constexpr int kTpBlockM = 128;
 constexpr int kTpBlockN = 256;
 constexpr int kTpBlockK = 64;
 constexpr int kTpStages = 4;
-constexpr int kTpThreads = 320;      // producer / comm, MMA, 4 epilogue warps, 4 reduce warps (reduce-scatter only)
-constexpr int kTpAuxThreads = 128;
+constexpr int kTpThreads = 384;      // producer, MMA, 4 epilogue warps, 6 comm/reduce warps
+constexpr int kTpAuxThreads = 192;
+constexpr int kTpParts = 8;          // a 128-row tile is moved as 8 slices of 16 rows
+constexpr int kTpPartRows = kTpBlockM / kTpParts;
 constexpr int kTpMaxRanks = 8;
 
 // Layout of the symmetric flag page (uint32 words).
 constexpr int kTpMaxRowTiles = 1024;              // row tiles of 128 per rank
-constexpr int kTpParts = 4;                       // a row tile travels as 4 parts of 32 rows, each with its own flag
-constexpr int kTpPartRows = kTpBlockM / kTpParts;
-constexpr int kFlagRsBase = 64;                   // [slot 2][row tile][src 8][part 4]   part of the partial tile of `src` has landed
-constexpr int kFlagAgBase = kFlagRsBase + 2 * kTpMaxRowTiles * kTpMaxRanks * kTpParts;  // [slot 2][src 8][row tile][part 4]
-constexpr int kFlagWords = kFlagAgBase + 2 * kTpMaxRanks * kTpMaxRowTiles * kTpParts;
+constexpr int kFlagRsBase = 64;                   // [slot 2][row tile][src 8]   partial tile of `src` has landed
+constexpr int kFlagAgBase = kFlagRsBase + 2 * kTpMaxRowTiles * kTpMaxRanks;  // [slot 2][src 8][row tile] staged
+constexpr int kFlagWords = kFlagAgBase + 2 * kTpMaxRanks * kTpMaxRowTiles;
+constexpr int kAuxLoads = 8;                      // 16-byte loads each aux thread keeps in flight
 constexpr int kRsParts = 16;                      // the reduction works on 8-row slices: a short tail after the
 constexpr int kRsPartRows = kTpBlockM / kRsParts; // last partial tile has landed
 
 // Layout of the local counter scratch (uint32 words), zeroed by the host function before each launch.
-constexpr int kCtrClaim = 0;      // next reduce unit
-constexpr int kCtrTicket = 1;     // CTAs that have started (the first n_comm become comm CTAs)
+constexpr int kCtrClaim = 0;      // next comm (forward) unit; [1] next reduce unit
 constexpr int kCtrTileClaim = 2;  // next GEMM tile
 constexpr int kSchedDepth = 4;    // claimed tiles the producer may run ahead of the slowest consumer
-constexpr int kCtrTiles = 8;      // [row tile]  reduce-scatter: epilogue warps that have stored their share of the tile
+constexpr int kCtrTiles = 8;      // AG: [row tile] slices pushed;  RS: [row tile] epilogue warps finished,
+                                  //                                     [row tiles + row tile] slices forwarded
 
 constexpr int kTpABytes = kTpBlockM * kTpBlockK * 2;
 constexpr int kTpBBytes = kTpBlockN * kTpBlockK * 2;
 constexpr int kTpStageBytes = kTpABytes + kTpBBytes;
 constexpr int kTpStoreBytes = 4 * 2 * 4096;
-constexpr int kTpBarrierBytes = 512;
-constexpr int kTpSmem = kTpStages * kTpStageBytes + kTpStoreBytes + kTpBarrierBytes + 1024;
-
-// Communication ring of a comm CTA: it reuses the GEMM operand stages.
-constexpr int kCommStageBytes = 32 * 1024;
-constexpr int kCommStages = (kTpStages * kTpStageBytes) / kCommStageBytes;   // 6
-constexpr int kCommLag = 3;       // a unit's completion is signalled once three younger store groups were issued
-constexpr int kCommPend = 8;      // ring of store groups issued but not yet known complete (> kCommLag)
-static_assert(kCommStages * kCommStageBytes <= kTpStages * kTpStageBytes, "ring must fit in the operand stages");
+constexpr int kTpSmem = kTpStages * kTpStageBytes + kTpStoreBytes + 256 + 1024;
 
 struct PeerPtrs {
   void* p[kTpMaxRanks];
@@ -98,8 +84,8 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void red_release_gpu_add(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;" ::: "memory"); }
 __device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
@@ -107,46 +93,51 @@ __device__ __forceinline__ uint4 ld_cg_v4(const void* p) {
   asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
   return v;
 }
-// Untiled bulk copies: global -> shared (completion counted on an mbarrier) and shared -> global (bulk group).
-__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_u32(smem_dst)),
-               "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ void bulk_store(void* gdst, const void* smem_src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
-               "r"(bytes)
-               : "memory");
-}
 
-// Bounded spin until *p >= target (wrap-safe). Returns false on time-out or when the CTA has aborted.
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t ld_relaxed_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded spin until *p >= target (wrap-safe). Returns false on time-out or when the CTA has aborted.  The polls
+// are relaxed loads; one acquire fence follows the poll that succeeds.
 template <bool SYS>
 __device__ __forceinline__ bool wait_flag_ge(const uint32_t* p, uint32_t target, uint64_t budget_ns,
                                              const volatile int* abort_flag) {
-  const uint64_t t0 = global_timer_ns();
+  uint64_t t0 = 0;
   for (uint32_t i = 0;; ++i) {
-    const uint32_t v = SYS ? ld_acquire_sys(p) : ld_acquire_gpu(p);
-    if (static_cast<int32_t>(v - target) >= 0) return true;
-    if ((i & 15u) == 15u) {
+    const uint32_t v = SYS ? ld_relaxed_sys(p) : ld_relaxed_gpu(p);
+    if (static_cast<int32_t>(v - target) >= 0) {
+      if (SYS) asm volatile("fence.acq_rel.sys;" ::: "memory");
+      else asm volatile("fence.acq_rel.gpu;" ::: "memory");
+      return true;
+    }
+    if ((i & 63u) == 63u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > budget_ns) return false;
+      const uint64_t now = global_timer_ns();   // slow to read: once per 64 polls
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > budget_ns) return false;
     }
     if (i >= 4) __nanosleep(i < 64 ? 40 : 200);
   }
 }
 
-__device__ __forceinline__ void aux_barrier() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+__device__ __forceinline__ void aux_barrier() { asm volatile("bar.sync 2, 192;" ::: "memory"); }
 
-// All-gather: own rows first, then the peers' row tiles in arrival order (every peer pushes its tiles in
-// ascending order to all ranks at once, so tile i of every peer lands at about the same time).
+// All-gather: own rows first, then the peers' row tiles in arrival order (tile i of every peer lands at about the
+// same time, before tile i+1 of any peer).
 __device__ __forceinline__ int ag_m_tile(int logical, int tiles_per_rank, int rank, int tp) {
   if (logical < tiles_per_rank) return rank * tiles_per_rank + logical;
   const int j = logical - tiles_per_rank;
   return ((rank + 1 + j % (tp - 1)) % tp) * tiles_per_rank + j / (tp - 1);
 }
-// Reduce-scatter: round-robin over the rank blocks (next rank first, own block last): the tiles bound for each
-// peer are spread over the whole kernel.
+// Round-robin over the rank blocks (next rank first): the tiles bound for each peer are spread over the whole
+// kernel, so the NVLink write rate is 1/tp-th of the epilogue's output rate instead of all of it for a while.
 __device__ __forceinline__ int interleaved_m_tile(int logical, int tiles_per_rank, int rank, int tp) {
   return ((rank + 1 + logical % tp) % tp) * tiles_per_rank + logical / tp;
 }
@@ -167,7 +158,6 @@ __device__ __forceinline__ void decode_tp_tile(int tile, int num_m, int num_n, i
 struct TpCommon {
   int M, N, K;          // M = tp * rows_local
   int rank, tp, rows_local;
-  int n_comm;           // CTAs that take the communication role
   uint32_t epoch;
   uint32_t* ctrs;       // local counter scratch
   unsigned long long wait_ns;
@@ -186,13 +176,11 @@ struct TpShared {
   uint8_t* smem;
   uint8_t* store_stage;
   uint64_t *full_bar, *empty_bar, *tmem_full, *tmem_empty;
-  uint64_t *sched_full, *sched_empty, *comm_bar;
   uint32_t* tmem_slot;
   volatile int* abort_flag;
   volatile int* claim_slot;
-  volatile int* role_slot;
+  uint64_t *sched_full, *sched_empty;
   volatile int* tile_ring;
-  volatile int* pend_tile;   // [kCommPend] completion ring of the comm thread
 };
 
 __device__ __forceinline__ TpShared tp_carve(uint8_t* smem_raw) {
@@ -203,22 +191,16 @@ __device__ __forceinline__ TpShared tp_carve(uint8_t* smem_raw) {
   s.empty_bar = s.full_bar + kTpStages;
   s.tmem_full = s.empty_bar + kTpStages;
   s.tmem_empty = s.tmem_full + 2;
-  s.sched_full = s.tmem_empty + 2;
-  s.sched_empty = s.sched_full + kSchedDepth;
-  s.comm_bar = s.sched_empty + kSchedDepth;
-  s.tmem_slot = reinterpret_cast<uint32_t*>(s.comm_bar + kCommStages);
+  s.tmem_slot = reinterpret_cast<uint32_t*>(s.tmem_empty + 2);
   s.abort_flag = reinterpret_cast<volatile int*>(s.tmem_slot + 1);
   s.claim_slot = s.abort_flag + 1;
-  s.role_slot = s.abort_flag + 2;
-  s.tile_ring = s.abort_flag + 3;
-  s.pend_tile = s.tile_ring + kSchedDepth;
+  s.sched_full = s.tmem_empty + 4;   // 8-byte aligned, past the three words above
+  s.sched_empty = s.sched_full + kSchedDepth;
+  s.tile_ring = reinterpret_cast<volatile int*>(s.sched_empty + kSchedDepth);
   return s;
 }
-static_assert((2 * kTpStages + 4 + 2 * kSchedDepth + kCommStages) * 8 + (5 + kSchedDepth + kCommPend) * 4 <= kTpBarrierBytes,
-              "barrier region too small");
 
-// Returns this CTA's communication ticket (0 .. n_comm-1), or -1 when it only computes.
-__device__ __forceinline__ int tp_prologue(const TpShared& s, const TpCommon& c, int warp) {
+__device__ __forceinline__ void tp_prologue(const TpShared& s, int warp) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < kTpStages; ++i) {
       mbar_init(&s.full_bar[i], 1);
@@ -232,10 +214,7 @@ __device__ __forceinline__ int tp_prologue(const TpShared& s, const TpCommon& c,
       mbar_init(&s.sched_full[i], 1);
       mbar_init(&s.sched_empty[i], 5);  // MMA thread + 4 epilogue warps
     }
-    for (int i = 0; i < kCommStages; ++i) mbar_init(&s.comm_bar[i], 1);
     *s.abort_flag = 0;
-    const uint32_t ticket = atomicAdd(&c.ctrs[kCtrTicket], 1u);
-    *s.role_slot = ticket < static_cast<uint32_t>(c.n_comm) ? static_cast<int>(ticket) : -1;
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -245,7 +224,6 @@ __device__ __forceinline__ int tp_prologue(const TpShared& s, const TpCommon& c,
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  return *s.role_slot;
 }
 
 __device__ __forceinline__ void tp_epilogue_sync(const TpShared& s, int warp, uint32_t tmem_base) {
@@ -279,11 +257,7 @@ __device__ __forceinline__ int sched_consume(const TpShared& s, const TpCommon& 
   mbar_arrive(&s.sched_empty[slot]);
   return tile;
 }
-// A CTA that computes no tiles at all: send the end marker as the first (and only) entry of the stream.
-__device__ __forceinline__ void sched_end_now(const TpShared& s) {
-  s.tile_ring[0] = -1;
-  mbar_arrive(&s.sched_full[0]);
-}
+// Producer side of a failed wait / end of stream: wake the consumers with the end marker where possible.
 __device__ __forceinline__ void sched_fail(const TpShared& s, const TpCommon& c, int code) {
   if (!*s.abort_flag) report_error(c.status, code);
   *s.abort_flag = 1;
@@ -388,7 +362,7 @@ __device__ __forceinline__ void tp_store_tile(const TpShared& s, uint32_t tmem_b
   }
 }
 
-// Claim the next unit of reduce work for the 128 aux threads of this CTA.
+// Claim the next unit of comm / reduce work for the 128 aux threads of this CTA.
 __device__ __forceinline__ int aux_claim(const TpShared& s, uint32_t* ctrs, int tid) {
   if (tid == 0) *s.claim_slot = static_cast<int>(atomicAdd(&ctrs[kCtrClaim], 1u));
   aux_barrier();
@@ -397,138 +371,14 @@ __device__ __forceinline__ int aux_claim(const TpShared& s, uint32_t* ctrs, int 
   return u;
 }
 
-// ------------------------------------------------------------------------------------- communication ring
-// How a part ([32 rows x cols] bf16) is cut into units of at most kCommStageBytes: `rows` whole rows per unit
-// when a row fits (rows a power of two), else one row piece of `chunk_cols` columns per unit.
-struct CopyGeom {
-  int rows;          // rows per unit
-  int chunk_cols;    // columns per unit
-  int col_chunks;    // units per row (1 when whole rows are moved)
-  int units_per_part;
-};
-__host__ __device__ inline CopyGeom copy_geom(int cols) {
-  CopyGeom g;
-  const int row_bytes = cols * 2;
-  if (row_bytes <= kCommStageBytes) {
-    int r = 1;
-    while (r * 2 * row_bytes <= kCommStageBytes && r * 2 <= kTpPartRows) r *= 2;
-    g.rows = r;
-    g.chunk_cols = cols;
-    g.col_chunks = 1;
-  } else {
-    g.rows = 1;
-    g.chunk_cols = kCommStageBytes / 2;
-    g.col_chunks = (cols + g.chunk_cols - 1) / g.chunk_cols;
-  }
-  g.units_per_part = (kTpPartRows / g.rows) * g.col_chunks;
-  return g;
-}
-// (row inside the part, first column, columns) of unit `sub` of a part
-__device__ __forceinline__ void unit_window(const CopyGeom& g, int sub, int total_cols, int& row, int& col0, int& cols) {
-  row = g.col_chunks == 1 ? sub * g.rows : sub / g.col_chunks;
-  col0 = g.col_chunks == 1 ? 0 : (sub % g.col_chunks) * g.chunk_cols;
-  cols = min(g.chunk_cols, total_cols - col0);
-}
-
-struct CommJob {
-  const uint8_t* src;     // first byte of the unit in local memory
-  long long src_pitch;    // bytes between rows at the source
-  long long dst_off;      // byte offset of the unit in every destination buffer (rows are contiguous there)
-  int rows, row_bytes;
-  int item;               // the part this unit belongs to
-  int last;               // 1: the last unit of its part
-};
-
-// One thread of a comm CTA moves its share of the parts through the ring: item = ticket, ticket + n_comm, ...;
-// per unit: (wait until the part's source is ready) -> bulk load into a stage -> bulk store to every destination.
-// A part's completion callback runs once the store group of its last unit has completed; that is checked
-// kCommLag store groups later, so the ring never waits for a round trip over NVLink.
-// Policy: num_items(), units_per_item(), describe(item, sub, job), ready(item), num_dests(job), dest(job, i), complete(item).
-template <class Policy>
-__device__ bool comm_ring_run(const TpShared& s, const TpCommon& c, int ticket, const Policy& pol) {
-  const int num_items = pol.num_items();
-  const int upi = pol.units_per_item();
-  int item = ticket, sub = 0;            // next unit to load
-  int ready_item = -1;                   // last item whose source was seen ready
-  uint32_t filled = 0, stored = 0, signalled = 0;
-  CommJob inflight[kCommStages];
-  uint64_t t_idle = 0;
-  bool ok = true;
-  for (;;) {
-    bool progress = false;
-    if (item < num_items && filled - stored < static_cast<uint32_t>(kCommStages)) {
-      if (ready_item != item && pol.ready(item)) ready_item = item;
-      if (ready_item == item) {
-        CommJob j;
-        pol.describe(item, sub, j);
-        j.item = item;
-        j.last = (sub == upi - 1) ? 1 : 0;
-        const int st = filled % kCommStages;
-        uint8_t* dst = s.smem + st * kCommStageBytes;
-        const uint32_t bytes = static_cast<uint32_t>(j.rows) * j.row_bytes;
-        mbar_arrive_expect_tx(&s.comm_bar[st], bytes);
-        if (j.src_pitch == j.row_bytes) {
-          bulk_load(dst, j.src, bytes, &s.comm_bar[st]);
-        } else {
-          for (int r = 0; r < j.rows; ++r)
-            bulk_load(dst + r * j.row_bytes, j.src + r * j.src_pitch, j.row_bytes, &s.comm_bar[st]);
-        }
-#pragma unroll
-        for (int i = 0; i < kCommStages; ++i)
-          if (i == st) inflight[i] = j;
-        ++filled;
-        if (++sub == upi) {
-          sub = 0;
-          item += c.n_comm;
-        }
-        progress = true;
-      }
-    }
-    if (stored < filled) {
-      const int st = stored % kCommStages;
-      if (mbar_try_wait(&s.comm_bar[st], (stored / kCommStages) & 1)) {
-        CommJob j{};
-#pragma unroll
-        for (int i = 0; i < kCommStages; ++i)
-          if (i == st) j = inflight[i];
-        const uint8_t* src = s.smem + st * kCommStageBytes;
-        const uint32_t bytes = static_cast<uint32_t>(j.rows) * j.row_bytes;
-        fence_proxy_async_smem();
-        const int nd = pol.num_dests(j);
-        for (int d = 0; d < nd; ++d) bulk_store(pol.dest(j, d) + j.dst_off, src, bytes);
-        tma_store_commit();
-        s.pend_tile[stored % kCommPend] = j.last ? j.item : -1;
-        ++stored;
-        if (stored - signalled > static_cast<uint32_t>(kCommLag)) {
-          const int done_item = s.pend_tile[signalled % kCommPend];
-          if (done_item >= 0) {
-            tma_store_wait<kCommLag>();            // every group but the newest kCommLag has completed
-            pol.complete(done_item);
-          }
-          ++signalled;
-        }
-        tma_store_wait_read<0>();                  // the stage may be refilled
-        progress = true;
-      }
-    }
-    if (item >= num_items && stored == filled) break;
-    if (progress) {
-      t_idle = 0;
-    } else {
-      if (t_idle == 0) t_idle = global_timer_ns();
-      else if (*s.abort_flag || global_timer_ns() - t_idle > c.wait_ns) {
-        ok = false;
-        break;
-      }
-      __nanosleep(64);
-    }
-  }
-  tma_store_wait<0>();
-  if (ok)
-    for (; signalled < stored; ++signalled) {
-      const int done_item = s.pend_tile[signalled % kCommPend];
-      if (done_item >= 0) pol.complete(done_item);
-    }
+// Thread 0 of the aux group waits, every aux thread learns the outcome.
+template <bool SYS>
+__device__ __forceinline__ bool aux_wait_flag(const TpShared& s, const TpCommon& c, const uint32_t* flag,
+                                              uint32_t target, int tid) {
+  if (tid == 0) *s.claim_slot = wait_flag_ge<SYS>(flag, target, c.wait_ns, s.abort_flag) ? 1 : 0;
+  aux_barrier();
+  const bool ok = *s.claim_slot != 0;
+  aux_barrier();
   return ok;
 }
 
@@ -541,39 +391,6 @@ struct AgArgs {
   int gather_own;                 // also copy this rank's own rows into the own gathered buffer
   PeerPtrs flags;                 // flag page of every rank
   int ldc;
-};
-
-struct AgCommPolicy {
-  const AgArgs& a;
-  CopyGeom g;
-  int tiles_per_rank, slot;
-  __device__ int num_items() const { return tiles_per_rank * kTpParts; }
-  __device__ int units_per_item() const { return g.units_per_part; }
-  __device__ void describe(int item, int sub, CommJob& j) const {
-    int row, col0, cols;
-    unit_window(g, sub, a.c.K, row, col0, cols);
-    row += item * kTpPartRows;                       // row inside this rank's block
-    j.src = reinterpret_cast<const uint8_t*>(a.x_local + static_cast<long long>(row) * a.ldx + col0);
-    j.rows = g.rows;
-    j.row_bytes = cols * 2;
-    j.src_pitch = g.col_chunks == 1 ? a.ldx * 2 : j.row_bytes;   // a single row piece is one contiguous load
-    j.dst_off = ((static_cast<long long>(a.c.rank) * a.c.rows_local + row) * a.c.K + col0) * 2;
-  }
-  __device__ bool ready(int) const { return true; }
-  __device__ int num_dests(const CommJob&) const { return a.c.tp - 1 + (a.gather_own ? 1 : 0); }
-  __device__ uint8_t* dest(const CommJob&, int i) const {   // peers in ring order, the own buffer last
-    return static_cast<uint8_t*>(a.gathered.p[(a.c.rank + 1 + i) % a.c.tp]);
-  }
-  // the part's rows have landed on every peer: tell them
-  __device__ void complete(int item) const {
-    fence_proxy_async_global();
-    __threadfence_system();        // one release fence, then plain system-scope stores of the flag to every peer
-    for (int r = 0; r < a.c.tp; ++r)
-      if (r != a.c.rank)
-        st_relaxed_sys(reinterpret_cast<uint32_t*>(a.flags.p[r]) + kFlagAgBase +
-                           ((slot * kTpMaxRanks + a.c.rank) * kTpMaxRowTiles) * kTpParts + item,
-                       a.c.epoch);
-  }
 };
 
 template <bool B_MN>
@@ -591,28 +408,17 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int k_blocks = (c.K + kTpBlockK - 1) / kTpBlockK;
   const int slot = c.epoch & 1;
 
-  const int ticket = tp_prologue(s, c, warp);
+  tp_prologue(s, warp);
   const uint32_t tmem_base = *s.tmem_slot;
   if (threadIdx.x == 0) tp_trace(c, kTrEntry);
 
   if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      bool alive = true;
-      if (ticket >= 0) {
-        // ---------------------------------------------------------------- push this rank's rows to every peer
-        tp_trace(c, kTrAuxFirst);
-        const AgCommPolicy pol{a, copy_geom(c.K), tiles_per_rank, slot};
-        if (!comm_ring_run(s, c, ticket, pol)) {
-          sched_fail(s, c, kErrProducerWait);
-          alive = false;
-        }
-        tp_trace(c, kTrAuxDone);
-      }
-      // ------------------------------------------------------------------ TMA producer
       uint32_t it = 0;
       unsigned long long ready_mask = 0;  // row tiles < 64 already seen complete (and proxy-fenced) by this thread
-      uint32_t claimed = alive ? atomicAdd(&c.ctrs[kCtrTileClaim], 1u) : 0u;
-      for (uint32_t q = 0; alive; ++q) {
+      uint32_t claimed = atomicAdd(&c.ctrs[kCtrTileClaim], 1u);
+      for (uint32_t q = 0;; ++q) {
         const int tile = sched_produce(s, c, q, num_tiles, claimed);
         if (tile < 0) {
           if (tile == -2) sched_fail(s, c, kErrProducerWait);
@@ -627,12 +433,9 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         const bool own = (m_tile / tiles_per_rank) == c.rank;
         if (!own && !(m_tile < 64 && ((ready_mask >> m_tile) & 1ull))) {
           const uint32_t* flag = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagAgBase +
-                                 ((slot * kTpMaxRanks + m_tile / tiles_per_rank) * kTpMaxRowTiles +
-                                  m_tile % tiles_per_rank) * kTpParts;
-          bool landed = true;
-          for (int part = 0; part < kTpParts && landed; ++part)
-            landed = wait_flag_ge<true>(flag + part, c.epoch, c.wait_ns, s.abort_flag);
-          if (!landed) {
+                                 (slot * kTpMaxRanks + m_tile / tiles_per_rank) * kTpMaxRowTiles +
+                                 m_tile % tiles_per_rank;
+          if (!wait_flag_ge<true>(flag, c.epoch, c.wait_ns, s.abort_flag)) {
             sched_fail(s, c, kErrPeerFlagWait);
             break;
           }
@@ -653,22 +456,6 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
           tp_load_stage<B_MN>(s, st, ta, &tmap_b, kb * kTpBlockK, a_row, n_tile * kTpBlockN);
         }
         if (!ok) break;
-      }
-      if (num_tiles == 0 && alive) {
-        // Gather only: no product consumes the tiles, so wait here until every peer's rows have landed
-        // (the row tiles are spread over the CTAs).
-        for (int t = blockIdx.x; t < num_m; t += gridDim.x) {
-          if (t / tiles_per_rank == c.rank) continue;
-          const uint32_t* flag = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagAgBase +
-                                 ((slot * kTpMaxRanks + t / tiles_per_rank) * kTpMaxRowTiles + t % tiles_per_rank) * kTpParts;
-          bool landed = true;
-          for (int part = 0; part < kTpParts && landed; ++part)
-            landed = wait_flag_ge<true>(flag + part, c.epoch, c.wait_ns, s.abort_flag);
-          if (!landed) {
-            sched_fail(s, c, kErrPeerFlagWait);
-            break;
-          }
-        }
       }
     }
   } else if (warp == 1) {
@@ -706,6 +493,72 @@ gemm_ag_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     }
     if (lane == 0) tma_store_wait<0>();
     if (warp == 2 && lane == 0) tp_trace(c, kTrEpilogueDone);
+  } else {
+    // ------------------------------------------------------------------ comm warps
+    // Unit = 16 rows of one of this rank's row tiles: read once, stored into every peer's gathered buffer
+    // (and the own one when asked to); the unit that completes a tile raises its flag on every peer.
+    const int tid = threadIdx.x - 192;
+    const int total_units = tiles_per_rank * kTpParts;
+    const int vec_per_row = c.K / 8;
+    const int total_vec = kTpPartRows * vec_per_row;
+    if (tid == 0) tp_trace(c, kTrAuxFirst);
+    for (;;) {
+      const int u = aux_claim(s, c.ctrs, tid);
+      if (u >= total_units || *s.abort_flag) {
+        if (tid == 0) tp_trace(c, kTrAuxDone);
+        break;
+      }
+      const int m_local = u / kTpParts, part = u % kTpParts;
+      const long long src_row = static_cast<long long>(m_local) * kTpBlockM + part * kTpPartRows;
+      const __nv_bfloat16* from = a.x_local + src_row * a.ldx;
+      const long long dst_off = (static_cast<long long>(c.rank) * c.rows_local + src_row) * c.K;
+      for (int base = tid; base < total_vec; base += kTpAuxThreads * kAuxLoads) {
+        uint4 v[kAuxLoads];
+#pragma unroll
+        for (int q = 0; q < kAuxLoads; ++q) {
+          const int idx = base + q * kTpAuxThreads;
+          if (idx < total_vec) {
+            const int r = idx / vec_per_row, col = idx - r * vec_per_row;
+            v[q] = ld_cg_v4(from + r * a.ldx + col * 8);
+          }
+        }
+        for (int pr = 1; pr <= c.tp; ++pr) {
+          const int dst_rank = (c.rank + pr) % c.tp;  // peers in ring order, own buffer last
+          if (dst_rank == c.rank && !a.gather_own) continue;
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(a.gathered.p[dst_rank]) + dst_off;
+#pragma unroll
+          for (int q = 0; q < kAuxLoads; ++q) {
+            const int idx = base + q * kTpAuxThreads;
+            if (idx < total_vec) *reinterpret_cast<uint4*>(dst + static_cast<long long>(idx) * 8) = v[q];
+          }
+        }
+      }
+      __threadfence_system();
+      aux_barrier();
+      if (tid == 0) {
+        const uint32_t done = atomicAdd(&c.ctrs[kCtrTiles + m_local], 1u);
+        if (done == static_cast<uint32_t>(kTpParts - 1)) {
+          __threadfence_system();
+          for (int r = 0; r < c.tp; ++r)
+            if (r != c.rank)
+              st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[r]) + kFlagAgBase +
+                                 (slot * kTpMaxRanks + c.rank) * kTpMaxRowTiles + m_local,
+                             c.epoch);
+        }
+      }
+    }
+    if (num_tiles == 0) {
+      // Gather only: no product consumes the tiles, so wait here until every peer's rows have landed
+      // (the row tiles are spread over the CTAs).
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_m && ok; t += gridDim.x) {
+        if (t / tiles_per_rank == c.rank) continue;
+        const uint32_t* flag = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagAgBase +
+                               (slot * kTpMaxRanks + t / tiles_per_rank) * kTpMaxRowTiles + t % tiles_per_rank;
+        ok = aux_wait_flag<true>(s, c, flag, c.epoch, tid);
+        if (!ok && tid == 0) sched_fail(s, c, kErrPeerFlagWait);
+      }
+    }
   }
   tp_epilogue_sync(s, warp, tmem_base);
   if (threadIdx.x == 0) tp_trace(c, kTrExit);
@@ -759,49 +612,6 @@ struct RsArgs {
   PeerPtrs flags;                 // flag page of every rank
 };
 
-struct RsCommPolicy {
-  const RsArgs& a;
-  CopyGeom g;
-  int tiles_per_rank, num_m, slot;
-  uint32_t tile_done;             // epilogue warps per finished row tile
-  // item = (remote row tile in the order the tiles are computed, part)
-  __device__ int num_items() const { return (num_m - tiles_per_rank) * kTpParts; }
-  __device__ int units_per_item() const { return g.units_per_part; }
-  __device__ int tile_of(int item) const {
-    const int tp = a.c.tp, jt = item / kTpParts;
-    const int logical = (jt / (tp - 1)) * tp + jt % (tp - 1);      // own tiles (logical % tp == tp - 1) skipped
-    return interleaved_m_tile(logical, tiles_per_rank, a.c.rank, tp);
-  }
-  __device__ void describe(int item, int sub, CommJob& j) const {
-    const int m_tile = tile_of(item), m_local = m_tile % tiles_per_rank;
-    int row, col0, cols;
-    unit_window(g, sub, a.c.N, row, col0, cols);
-    row += (item % kTpParts) * kTpPartRows;          // row inside the tile
-    j.src = reinterpret_cast<const uint8_t*>(a.staging + (static_cast<long long>(m_tile) * kTpBlockM + row) * a.c.N + col0);
-    j.rows = g.rows;
-    j.row_bytes = cols * 2;
-    j.src_pitch = g.col_chunks == 1 ? static_cast<long long>(a.c.N) * 2 : j.row_bytes;
-    j.dst_off = ((static_cast<long long>(a.c.rank) * a.c.rows_local + m_local * kTpBlockM + row) * a.c.N + col0) * 2;
-  }
-  __device__ bool ready(int item) const {
-    if (ld_acquire_gpu(&a.c.ctrs[kCtrTiles + tile_of(item)]) < tile_done) return false;
-    fence_proxy_async_global();   // the epilogue's bulk stores, acquired above -> visible to the bulk loads
-    return true;
-  }
-  __device__ int num_dests(const CommJob&) const { return 1; }
-  __device__ uint8_t* dest(const CommJob& j, int) const {
-    return static_cast<uint8_t*>(a.recv.p[tile_of(j.item) / tiles_per_rank]);
-  }
-  __device__ void complete(int item) const {
-    const int m_tile = tile_of(item);
-    const int dest = m_tile / tiles_per_rank, m_local = m_tile % tiles_per_rank;
-    fence_proxy_async_global();
-    st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[dest]) + kFlagRsBase +
-                       (((slot * kTpMaxRowTiles + m_local) * kTpMaxRanks + a.c.rank) * kTpParts) + item % kTpParts,
-                   a.c.epoch);
-  }
-};
-
 template <bool B_MN>
 __global__ void __launch_bounds__(kTpThreads, 1)
 gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -816,46 +626,38 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int tiles_per_rank = c.rows_local / kTpBlockM;
   const int k_blocks = (c.K + kTpBlockK - 1) / kTpBlockK;
   const int slot = c.epoch & 1;
-  const uint32_t tile_done = static_cast<uint32_t>(num_n * 4);
+  const uint32_t tile_done = static_cast<uint32_t>(num_n * 4);   // epilogue warps that store a share of a row tile
 
-  const int ticket = tp_prologue(s, c, warp);
+  tp_prologue(s, warp);
   const uint32_t tmem_base = *s.tmem_slot;
   if (threadIdx.x == 0) tp_trace(c, kTrEntry);
 
   if (warp == 0) {
     if (lane == 0) {
-      if (ticket >= 0) {
-        // ---------------------------------------------------------------- finished row tiles to their owners
-        sched_end_now(s);   // this CTA computes no tiles: its MMA and epilogue warps leave at once
-        const RsCommPolicy pol{a, copy_geom(c.N), tiles_per_rank, num_m, slot, tile_done};
-        if (!comm_ring_run(s, c, ticket, pol)) sched_fail(s, c, kErrProducerWait);
-        tp_trace(c, kTrProducerDone);
-      } else {
-        uint32_t it = 0;
-        uint32_t claimed = atomicAdd(&c.ctrs[kCtrTileClaim], 1u);
-        for (uint32_t q = 0;; ++q) {
-          const int tile = sched_produce(s, c, q, num_tiles, claimed);
-          if (tile < 0) {
-            if (tile == -2) sched_fail(s, c, kErrProducerWait);
-            tp_trace(c, kTrProducerDone);
+      uint32_t it = 0;
+      uint32_t claimed = atomicAdd(&c.ctrs[kCtrTileClaim], 1u);
+      for (uint32_t q = 0;; ++q) {
+        const int tile = sched_produce(s, c, q, num_tiles, claimed);
+        if (tile < 0) {
+          if (tile == -2) sched_fail(s, c, kErrProducerWait);
+          tp_trace(c, kTrProducerDone);
+          break;
+        }
+        int m_log, n_tile;
+        decode_tp_tile(tile, num_m, num_n, m_log, n_tile);
+        const int m_tile = interleaved_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
+        bool ok = true;
+        if (q == 0) tp_trace(c, kTrFirstLoad);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int st = it % kTpStages;
+          if (!mbar_wait_budget(&s.empty_bar[st], ((it / kTpStages) & 1) ^ 1, c.wait_ns, s.abort_flag)) {
+            sched_fail(s, c, kErrProducerWait);
+            ok = false;
             break;
           }
-          int m_log, n_tile;
-          decode_tp_tile(tile, num_m, num_n, m_log, n_tile);
-          const int m_tile = interleaved_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
-          bool ok = true;
-          if (q == 0) tp_trace(c, kTrFirstLoad);
-          for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-            const int st = it % kTpStages;
-            if (!mbar_wait_budget(&s.empty_bar[st], ((it / kTpStages) & 1) ^ 1, c.wait_ns, s.abort_flag)) {
-              sched_fail(s, c, kErrProducerWait);
-              ok = false;
-              break;
-            }
-            tp_load_stage<B_MN>(s, st, &tmap_a, &tmap_b, kb * kTpBlockK, m_tile * kTpBlockM, n_tile * kTpBlockN);
-          }
-          if (!ok) break;
+          tp_load_stage<B_MN>(s, st, &tmap_a, &tmap_b, kb * kTpBlockK, m_tile * kTpBlockM, n_tile * kTpBlockN);
         }
+        if (!ok) break;
       }
     }
   } else if (warp == 1) {
@@ -886,32 +688,26 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       decode_tp_tile(tile, num_m, num_n, m_log, n_tile);
       const int m_tile = interleaved_m_tile(m_log, tiles_per_rank, c.rank, c.tp);
       const int acc = local_tile & 1;
+      if (lane == 0 && pending_m >= 0) {
+        // The stores of the previous tile were issued a tile's MMA time ago at most: let them complete and count
+        // the tile now, while this warp would only be waiting for the next accumulator anyway.  Forwarding and
+        // reduction of a row tile then start one GEMM wave earlier than with a count deferred past the next tile.
+        tma_store_wait<0>();
+        signal_tile(pending_m);
+        pending_m = -1;
+      }
       if (!mbar_wait_budget(&s.tmem_full[acc], (local_tile >> 1) & 1, c.wait_ns, s.abort_flag)) {
         sched_fail(s, c, kErrEpilogueWait);
         break;
       }
       tc_fence_after();
-      const uint32_t before = store_count;
       tp_store_tile(s, tmem_base, acc, quarter, warp - 2, lane, &tmap_stage, n_tile * kTpBlockN,
                     m_tile * kTpBlockM + quarter * 32, c.N, store_count);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(&s.tmem_empty[acc]);
-        if (pending_m >= 0) {
-          // bulk groups retire in order: with at most this tile's groups outstanding, the previous tile is done
-          if (store_count - before == 4) tma_store_wait<4>();
-          else tma_store_wait<0>();
-          signal_tile(pending_m);
-          if (store_count - before != 4) {
-            signal_tile(m_tile);
-            pending_m = -1;
-          } else {
-            pending_m = m_tile;
-          }
-        } else {
-          pending_m = m_tile;
-        }
+        pending_m = m_tile;
       }
       __syncwarp();
       ++local_tile;
@@ -922,69 +718,171 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       if (warp == 2) tp_trace(c, kTrEpilogueDone);
     }
   } else {
-    // ------------------------------------------------------------------ reduce warps: rows this rank owns
+    // ------------------------------------------------------------------ forward / reduce warps
+    // Two streams of units, each handed out in the order the row tiles are computed:
+    //   forward  16-row slices of finished row tiles that another rank owns: staging -> owner's receive slot
+    //   reduce   8-row slices of the row tiles this rank owns: sum of the tp partial copies
+    // The aux group of a CTA holds at most one claimed unit of each stream and never blocks on either: it polls
+    // whether the held unit of its preferred stream can run, else whether the other one can, else sleeps briefly.
+    // Groups of even CTAs prefer forwarding, groups of odd CTAs prefer reducing: half the groups already saturate
+    // NVLink, and the reduction (HBM traffic) then proceeds beside the forwarding instead of after it.  Every
+    // claimed forward unit is sent as soon as this rank's own GEMM has produced its tile and the group is free,
+    // whatever the peers do, so the waits between ranks cannot form a cycle.
     const int tid = threadIdx.x - 192;
-    const int total_units = tiles_per_rank * kRsParts;
+    constexpr int kFwdParts = kTpParts, kFwdRows = kTpPartRows;
+    const int total_fwd = (num_m - tiles_per_rank) * kFwdParts;
+    const int total_red = tiles_per_rank * kRsParts;
     const int vec_per_row = c.N / 8;
-    const int total_vec = kRsPartRows * vec_per_row;
     const long long slot_stride = static_cast<long long>(c.rows_local) * c.N;
     const uint32_t* my_flags = reinterpret_cast<const uint32_t*>(a.flags.p[c.rank]) + kFlagRsBase +
-                               slot * kTpMaxRowTiles * kTpMaxRanks * kTpParts;
-    int ready_part = -1;            // (row tile, part) whose partial copies were last seen complete
-    bool failed = false;
+                               slot * kTpMaxRowTiles * kTpMaxRanks;
+    // decision of thread 0 for this round, published to the group: 0 nothing ready, 1 forward, 2 reduce, 3 stop
+    auto publish = [&](int v) {
+      if (tid == 0) *s.claim_slot = v;
+      aux_barrier();
+      const int r = *s.claim_slot;
+      aux_barrier();
+      return r;
+    };
+    auto fwd_tile = [&](int u) {
+      const int jt = u / kFwdParts;
+      const int logical = (jt / (c.tp - 1)) * c.tp + jt % (c.tp - 1);   // own tiles (logical % tp == tp - 1) skipped
+      return interleaved_m_tile(logical, tiles_per_rank, c.rank, c.tp);
+    };
     if (tid == 0) tp_trace(c, kTrAuxFirst);
+    // thread 0 owns the claims and the readiness checks; the unit numbers travel through shared memory
+    int fwd_u = -1, red_u = -1;            // held units (-1: none held, -2: stream exhausted)
+    int fwd_ready_tile = -1, red_ready_tile = -1;
+    uint64_t t_idle = 0;
+    uint32_t idle_polls = 0;
     for (;;) {
-      const int u = aux_claim(s, c.ctrs, tid);
-      if (u >= total_units || failed || *s.abort_flag) {
-        if (tid == 0) tp_trace(c, kTrAuxDone);
-        break;
-      }
-      const int m_local = u / kRsParts, part = u % kRsParts;
-      const int tpart = part / (kRsParts / kTpParts);      // the 32-row part this 8-row slice lies in
-      if (m_local * kTpParts + tpart != ready_part) {
-        // one thread waits for that part of the partial tile of every rank (the own one in the staging matrix),
-        // then everybody learns the outcome
-        if (tid == 0) {
-          int good = 1;
-          for (int src = 0; src < c.tp && good; ++src) {
-            if (src == c.rank)
-              good = wait_flag_ge<false>(&c.ctrs[kCtrTiles + c.rank * tiles_per_rank + m_local], tile_done, c.wait_ns,
-                                         s.abort_flag) ? 1 : 0;
-            else
-              good = wait_flag_ge<true>(my_flags + (m_local * kTpMaxRanks + src) * kTpParts + tpart, c.epoch, c.wait_ns,
-                                        s.abort_flag) ? 1 : 0;
-          }
-          // partial tiles were written through the async proxy (bulk stores): order them before the plain loads
-          fence_proxy_async_global();
-          *s.claim_slot = good;
+      int decision = 0;
+      if (tid == 0) {
+        if (*s.abort_flag) decision = 3;
+        if (decision == 0 && fwd_u == -1) {
+          const int u = static_cast<int>(atomicAdd(&c.ctrs[kCtrClaim], 1u));
+          fwd_u = u < total_fwd ? u : -2;
         }
-        aux_barrier();
-        const bool ok = *s.claim_slot != 0;
-        aux_barrier();
-        if (!ok) {
-          if (tid == 0) {
-            report_error(c.status, kErrPeerFlagWait);
-            *s.abort_flag = 1;
-          }
-          failed = true;
-          continue;
+        if (decision == 0 && red_u == -1) {
+          const int u = static_cast<int>(atomicAdd(&c.ctrs[kCtrClaim + 1], 1u));
+          red_u = u < total_red ? u : -2;
         }
-        ready_part = m_local * kTpParts + tpart;
+        auto try_forward = [&]() {
+          if (decision != 0 || fwd_u < 0) return;
+          const int m_tile = fwd_tile(fwd_u);
+          if (m_tile == fwd_ready_tile || ld_relaxed_gpu(&c.ctrs[kCtrTiles + m_tile]) >= tile_done) {
+            if (m_tile != fwd_ready_tile) {
+              asm volatile("fence.acq_rel.gpu;" ::: "memory");
+              fence_proxy_async_global();   // the epilogue's bulk stores -> visible to plain loads
+              fwd_ready_tile = m_tile;
+            }
+            decision = 1;
+          }
+        };
+        auto try_reduce = [&]() {
+          if (decision != 0 || red_u < 0) return;
+          const int m_local = red_u / kRsParts;
+          bool ready = m_local == red_ready_tile;
+          if (!ready) {
+            ready = ld_relaxed_gpu(&c.ctrs[kCtrTiles + c.rank * tiles_per_rank + m_local]) >= tile_done;
+            for (int src = 0; src < c.tp && ready; ++src)
+              if (src != c.rank)
+                ready = static_cast<int32_t>(ld_relaxed_sys(my_flags + m_local * kTpMaxRanks + src) - c.epoch) >= 0;
+            if (ready) {
+              asm volatile("fence.acq_rel.sys;" ::: "memory");
+              fence_proxy_async_global();   // the own partial was written through the async proxy (bulk stores)
+              red_ready_tile = m_local;
+            }
+          }
+          if (ready) decision = 2;
+        };
+        if (blockIdx.x & 1) {
+          try_reduce();
+          try_forward();
+        } else {
+          try_forward();
+          try_reduce();
+        }
+        if (decision == 0 && fwd_u == -2 && red_u == -2) decision = 3;
+        if (decision == 0) {
+          if ((++idle_polls & 63u) == 0) {         // the timer is slow to read
+            const uint64_t now = global_timer_ns();
+            if (t_idle == 0) t_idle = now;
+            else if (now - t_idle > c.wait_ns) {
+              sched_fail(s, c, fwd_u >= 0 ? kErrEpilogueWait : kErrPeerFlagWait);
+              decision = 3;
+            }
+          }
+        } else {
+          t_idle = 0;
+          idle_polls = 0;
+        }
+        s.tile_ring[kSchedDepth] = decision == 1 ? fwd_u : red_u;   // spare word after the tile ring
       }
-      const long long row0 = static_cast<long long>(m_local) * kTpBlockM + part * kRsPartRows;
-      const __nv_bfloat16* in[kTpMaxRanks];
+      decision = publish(decision);
+      if (decision == 3) break;
+      if (decision == 0) {
+        __nanosleep(100);
+        continue;
+      }
+      const int u = s.tile_ring[kSchedDepth];
+      if (decision == 1) {
+        // ---- forward 16 rows of a finished remote tile to its owner
+        const int part = u % kFwdParts;
+        const int m_tile = fwd_tile(u);
+        const int dest = m_tile / tiles_per_rank, m_local = m_tile % tiles_per_rank;
+        const long long row_in_tile = static_cast<long long>(part) * kFwdRows;
+        const __nv_bfloat16* from = a.staging + (static_cast<long long>(m_tile) * kTpBlockM + row_in_tile) * c.N;
+        __nv_bfloat16* to = reinterpret_cast<__nv_bfloat16*>(a.recv.p[dest]) +
+                            (static_cast<long long>(c.rank) * c.rows_local + m_local * kTpBlockM + row_in_tile) * c.N;
+        const int total_vec = kFwdRows * vec_per_row;     // rows are contiguous on both sides
+        constexpr int kFwdLoads = 8;                      // 16-byte loads each thread keeps in flight
+        for (int base = tid; base < total_vec; base += kTpAuxThreads * kFwdLoads) {
+          uint4 v[kFwdLoads];
 #pragma unroll
-      for (int src = 0; src < kTpMaxRanks; ++src)
-        in[src] = (src == c.rank) ? a.staging + (static_cast<long long>(c.rank) * c.rows_local + row0) * c.N
-                                  : a.recv_self + src * slot_stride + row0 * c.N;
-      __nv_bfloat16* out0 = a.out + row0 * a.ldo;
-      switch (c.tp) {
-        case 2: reduce_unit<2>(in, out0, a.ldo, vec_per_row, total_vec, tid); break;
-        case 4: reduce_unit<4>(in, out0, a.ldo, vec_per_row, total_vec, tid); break;
-        case 8: reduce_unit<8>(in, out0, a.ldo, vec_per_row, total_vec, tid); break;
-        default: reduce_unit<1>(in, out0, a.ldo, vec_per_row, total_vec, tid); break;
+          for (int q = 0; q < kFwdLoads; ++q) {
+            const int idx = base + q * kTpAuxThreads;
+            if (idx < total_vec) v[q] = ld_cg_v4(from + static_cast<long long>(idx) * 8);
+          }
+#pragma unroll
+          for (int q = 0; q < kFwdLoads; ++q) {
+            const int idx = base + q * kTpAuxThreads;
+            if (idx < total_vec) *reinterpret_cast<uint4*>(to + static_cast<long long>(idx) * 8) = v[q];
+          }
+        }
+        __threadfence_system();
+        aux_barrier();
+        if (tid == 0) {
+          const uint32_t done = atomicAdd(&c.ctrs[kCtrTiles + num_m + m_tile], 1u);
+          if (done == static_cast<uint32_t>(kFwdParts - 1)) {
+            __threadfence_system();
+            st_release_sys(reinterpret_cast<uint32_t*>(a.flags.p[dest]) + kFlagRsBase +
+                               (slot * kTpMaxRowTiles + m_local) * kTpMaxRanks + c.rank,
+                           c.epoch);
+          }
+          fwd_u = -1;
+        }
+      } else {
+        // ---- reduce 8 rows of an own tile
+        const int m_local = u / kRsParts, part = u % kRsParts;
+        const long long row0 = static_cast<long long>(m_local) * kTpBlockM + part * kRsPartRows;
+        const __nv_bfloat16* in[kTpMaxRanks];
+#pragma unroll
+        for (int src = 0; src < kTpMaxRanks; ++src)
+          in[src] = (src == c.rank) ? a.staging + (static_cast<long long>(c.rank) * c.rows_local + row0) * c.N
+                                    : a.recv_self + src * slot_stride + row0 * c.N;
+        __nv_bfloat16* out0 = a.out + row0 * a.ldo;
+        const int total_vec = kRsPartRows * vec_per_row;
+        switch (c.tp) {
+          case 2: reduce_unit<2>(in, out0, a.ldo, vec_per_row, total_vec, tid); break;
+          case 4: reduce_unit<4>(in, out0, a.ldo, vec_per_row, total_vec, tid); break;
+          case 8: reduce_unit<8>(in, out0, a.ldo, vec_per_row, total_vec, tid); break;
+          default: reduce_unit<1>(in, out0, a.ldo, vec_per_row, total_vec, tid); break;
+        }
+        if (tid == 0) red_u = -1;
       }
     }
+    if (tid == 0) tp_trace(c, kTrAuxDone);
   }
   tp_epilogue_sync(s, warp, tmem_base);
   if (threadIdx.x == 0) tp_trace(c, kTrExit);
@@ -1003,17 +901,6 @@ static int tp_check(int rows_local, int N, int K, int tp, int rank) {
   return 0;
 }
 
-// Comm CTAs for a transfer of `bytes` over NVLink that should not outlast a GEMM of `flops`: one CTA moves about
-// 35 GB/s through its ring and sixteen saturate the links; a few more than the rate asks for keep the tail short.
-static int choose_comm_ctas(double bytes, double flops, int grid) {
-  const double t_gemm = flops / 1.3e15 + 5e-6;
-  int n = static_cast<int>(bytes / t_gemm / 35e9) + 3;
-  if (n < 4) n = 4;
-  if (n > 20) n = 20;
-  if (n > grid / 2) n = grid / 2 > 0 ? grid / 2 : 1;
-  return n;
-}
-
 }  // namespace stb
 
 using namespace stb;
@@ -1021,7 +908,7 @@ using namespace stb;
 // Words of symmetric flag memory a rank must provide (zero-initialised once, before the first call).
 extern "C" int stb_tp_flag_words() { return kFlagWords; }
 // Words of local counter scratch needed for `row_tiles` = tp * rows_local / 128 row tiles.
-extern "C" int stb_tp_ctr_words(int row_tiles) { return kCtrTiles + row_tiles; }
+extern "C" int stb_tp_ctr_words(int row_tiles) { return kCtrTiles + 2 * row_tiles; }
 
 // C[tp*rows_local, N] = all_gather_rows(x_local) * B^T (b_mn_major = 0, B stored [N][ldb]) or * B
 // (b_mn_major = 1, B stored [K][ldb]); `gathered` [tp*rows_local][K] receives the gathered rows.
@@ -1029,13 +916,11 @@ extern "C" int stb_tp_ctr_words(int row_tiles) { return kCtrTiles + row_tiles; }
 // reads them from x_local).  gathered_ptrs[r] / flag_ptrs[r]: rank r's gathered buffer for this call (slot =
 // epoch & 1, tp*rows_local*K bf16, symmetric memory) and flag page, as mapped into this process; the result is
 // in gathered_ptrs[rank] and stays valid until the second-next call on the group.  epoch: 1, 2, 3, ... per group,
-// the same on every rank.  ctrs: local scratch of stb_tp_ctr_words(row tiles) words.  comm_ctas: CTAs that push
-// the rows before they join the product (0 = chosen from the sizes).
+// the same on every rank.  ctrs: local scratch of stb_tp_ctr_words(row tiles) words.
 extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* const* gathered_ptrs,
                                 void* const* flag_ptrs, const void* B, void* C, int rows_local, int N, int K, int ldb,
                                 int ldc, int b_mn_major, int gather_own, int rank, int tp, unsigned epoch, void* ctrs,
-                                unsigned long long wait_ns, int comm_ctas, int* status, void* trace,
-                                cudaStream_t stream) {
+                                unsigned long long wait_ns, int* status, void* trace, cudaStream_t stream) {
   int r = tp_check(rows_local, N, K, tp, rank);
   if (r) return r;
   if ((ldx & 7) || (N > 0 && ((ldb & 7) || (ldc & 7)))) return -kErrBadArgument;
@@ -1055,21 +940,8 @@ extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* const*
     tb = ta;
     tc = ta;
   }
-  int grid = sm_count();
-  const double out_bytes = static_cast<double>(tp - 1) * rows_local * K * 2;
-  if (comm_ctas <= 0) {
-    // these CTAs join the product once the rows are out, so a few more than the rate asks for cost nothing
-    comm_ctas = choose_comm_ctas(out_bytes, 2.0 * M * static_cast<double>(N) * K, grid);
-    if (comm_ctas < 12) comm_ctas = 12;
-  }
-  if (N == 0) {
-    comm_ctas = comm_ctas < 16 ? 16 : comm_ctas;   // nothing to multiply: only the comm CTAs are launched
-    grid = comm_ctas;
-  }
-  if (comm_ctas > grid) comm_ctas = grid;
   AgArgs a{};
   a.c.M = M; a.c.N = N; a.c.K = K; a.c.rank = rank; a.c.tp = tp; a.c.rows_local = rows_local;
-  a.c.n_comm = comm_ctas;
   a.c.epoch = epoch; a.c.ctrs = static_cast<uint32_t*>(ctrs); a.c.wait_ns = wait_ns; a.c.status = status;
   a.c.trace = static_cast<unsigned long long*>(trace);
   a.x_local = static_cast<const __nv_bfloat16*>(x_local);
@@ -1080,7 +952,7 @@ extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* const*
     a.gathered.p[i] = gathered_ptrs[i];
     a.flags.p[i] = flag_ptrs[i];
   }
-  cudaError_t e = cudaMemsetAsync(ctrs, 0, sizeof(uint32_t) * (kCtrTiles + M / kTpBlockM), stream);
+  cudaError_t e = cudaMemsetAsync(ctrs, 0, sizeof(uint32_t) * (kCtrTiles + 2 * (M / kTpBlockM)), stream);
   if (e != cudaSuccess) return -static_cast<int>(e);
   static bool configured[2] = {false, false};
   if (!configured[b_mn_major ? 1 : 0]) {
@@ -1088,6 +960,7 @@ extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* const*
     if (r) return r;
     configured[b_mn_major ? 1 : 0] = true;
   }
+  const int grid = sm_count();
   if (b_mn_major) gemm_ag_kernel<true><<<grid, kTpThreads, kTpSmem, stream>>>(ta, tx, tb, tc, a);
   else gemm_ag_kernel<false><<<grid, kTpThreads, kTpSmem, stream>>>(ta, tx, tb, tc, a);
   e = cudaGetLastError();
@@ -1096,13 +969,11 @@ extern "C" int stb_gemm_ag_bf16(const void* x_local, long long ldx, void* const*
 
 // out[rows_local, N] = reduce_scatter_rows(A[tp*rows_local, K] * B^T or * B).  recv_ptrs[r]: rank r's receive
 // slot for this call (slot = epoch & 1; tp*rows_local*N bf16), flag_ptrs[r]: rank r's flag page.  staging: local
-// scratch of tp*rows_local*N bf16 (the rank's partial products; free again when the call has finished).
-// comm_ctas: CTAs that copy finished row tiles to their owners instead of computing (0 = chosen from the sizes).
+// scratch of tp*rows_local*N bf16 (this rank's partial products; free again when the call has finished).
 extern "C" int stb_gemm_rs_bf16(const void* A, int lda, const void* B, int ldb, int b_mn_major, void* out,
                                 long long ldo, void* staging, void* const* recv_ptrs, void* const* flag_ptrs,
                                 int rows_local, int N, int K, int rank, int tp, unsigned epoch, void* ctrs,
-                                unsigned long long wait_ns, int comm_ctas, int* status, void* trace,
-                                cudaStream_t stream) {
+                                unsigned long long wait_ns, int* status, void* trace, cudaStream_t stream) {
   int r = tp_check(rows_local, N, K, tp, rank);
   if (r) return r;
   if (N <= 0 || (lda & 7) || (ldb & 7) || (ldo & 7) || staging == nullptr) return -kErrBadArgument;
@@ -1115,14 +986,8 @@ extern "C" int stb_gemm_rs_bf16(const void* A, int lda, const void* B, int ldb, 
   if (r) return r;
   r = make_tmap_2d(&ts, staging, 2, N, M, static_cast<uint64_t>(N) * 2, 64, 32, 1);
   if (r) return r;
-  const int grid = sm_count();
-  const double out_bytes = static_cast<double>(tp - 1) * rows_local * N * 2;
-  if (comm_ctas <= 0) comm_ctas = choose_comm_ctas(out_bytes, 2.0 * M * static_cast<double>(N) * K, grid);
-  if (comm_ctas >= grid) comm_ctas = grid - 1;
-  if (comm_ctas < 1) return -kErrBadArgument;    // one CTA cannot both compute and send
   RsArgs a{};
   a.c.M = M; a.c.N = N; a.c.K = K; a.c.rank = rank; a.c.tp = tp; a.c.rows_local = rows_local;
-  a.c.n_comm = comm_ctas;
   a.c.epoch = epoch; a.c.ctrs = static_cast<uint32_t*>(ctrs); a.c.wait_ns = wait_ns; a.c.status = status;
   a.c.trace = static_cast<unsigned long long*>(trace);
   a.out = static_cast<__nv_bfloat16*>(out);
@@ -1133,7 +998,7 @@ extern "C" int stb_gemm_rs_bf16(const void* A, int lda, const void* B, int ldb, 
     a.recv.p[i] = recv_ptrs[i];
     a.flags.p[i] = flag_ptrs[i];
   }
-  cudaError_t e = cudaMemsetAsync(ctrs, 0, sizeof(uint32_t) * (kCtrTiles + M / kTpBlockM), stream);
+  cudaError_t e = cudaMemsetAsync(ctrs, 0, sizeof(uint32_t) * (kCtrTiles + 2 * (M / kTpBlockM)), stream);
   if (e != cudaSuccess) return -static_cast<int>(e);
   static bool configured[2] = {false, false};
   if (!configured[b_mn_major ? 1 : 0]) {
@@ -1141,6 +1006,7 @@ extern "C" int stb_gemm_rs_bf16(const void* A, int lda, const void* B, int ldb, 
     if (r) return r;
     configured[b_mn_major ? 1 : 0] = true;
   }
+  const int grid = sm_count();
   if (b_mn_major) gemm_rs_kernel<true><<<grid, kTpThreads, kTpSmem, stream>>>(ta, tb, ts, a);
   else gemm_rs_kernel<false><<<grid, kTpThreads, kTpSmem, stream>>>(ta, tb, ts, a);
   e = cudaGetLastError();

@@ -93,6 +93,103 @@ __global__ void __launch_bounds__(32) peer_copy_bulk_kernel(const uint8_t* __res
   tma_store_wait<0>();
 }
 
+
+// The same ring with the extras of the fused GEMM+collective kernels switched on one by one (`feat` bits):
+//   1  every chunk is also stored to a second, local destination (the own copy of gathered rows)
+//   2  every 8th chunk: wait until all but the newest 6 store groups have completed, fence, write a flag word
+//      at `flag` (peer memory) - the per-part completion signal
+//   4  five more warps of the CTA spin on an mbarrier that is only released at the end (the idle MMA and
+//      epilogue warps of a comm CTA)
+//   8  the ring is driven by the non-blocking state machine of the fused kernels (try_wait + nanosleep)
+template <int STAGES>
+__global__ void __launch_bounds__(192) peer_copy_ring_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                                             uint8_t* __restrict__ dst2, uint32_t* flag, long long bytes,
+                                                             int chunk, int feat, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + static_cast<size_t>(STAGES) * chunk);
+  uint64_t* park = bars + STAGES;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) mbar_init(&bars[i], 1);
+    mbar_init(park, 1);
+    fence_barrier_init();
+  }
+  __syncthreads();
+  if (threadIdx.x >= 32) {
+    if ((feat & 4) && (threadIdx.x & 31) == 0) mbar_wait(park, 0);   // bounded: 2 s
+    return;
+  }
+  if (threadIdx.x != 0) return;
+  const long long num_chunks = (bytes + chunk - 1) / chunk;
+  auto issue = [&](long long c, int st) {
+    const long long off = c * chunk;
+    const uint32_t len = static_cast<uint32_t>(min(static_cast<long long>(chunk), bytes - off));
+    mbar_arrive_expect_tx(&bars[st], len);
+    bulk_load(smem + static_cast<size_t>(st) * chunk, src + off, len, &bars[st]);
+  };
+  auto store = [&](long long c, int st, uint32_t n) {
+    const long long off = c * chunk;
+    const uint32_t len = static_cast<uint32_t>(min(static_cast<long long>(chunk), bytes - off));
+    fence_proxy_async_smem();
+    bulk_store(dst + off, smem + static_cast<size_t>(st) * chunk, len);
+    if (feat & 1) bulk_store(dst2 + off, smem + static_cast<size_t>(st) * chunk, len);
+    tma_store_commit();
+    if ((feat & 2) && (n & 7u) == 7u) {
+      tma_store_wait<6>();
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+      __threadfence_system();
+      asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(flag + blockIdx.x), "r"(n) : "memory");
+    }
+    tma_store_wait_read<0>();
+  };
+  long long next = blockIdx.x;
+  uint32_t filled = 0, stored = 0;
+  if (!(feat & 8)) {
+    for (; filled < STAGES && next < num_chunks; ++filled, next += gridDim.x) issue(next, filled);
+    for (long long c = blockIdx.x; c < num_chunks; c += gridDim.x, ++stored) {
+      const int st = stored % STAGES;
+      if (!mbar_wait(&bars[st], (stored / STAGES) & 1)) {
+        report_error(status, kErrProducerWait);
+        break;
+      }
+      store(c, st, stored);
+      if (next < num_chunks) {
+        issue(next, st);
+        next += gridDim.x;
+      }
+    }
+  } else {
+    long long c_store = blockIdx.x;
+    uint32_t idle = 0;
+    for (;;) {
+      bool progress = false;
+      if (next < num_chunks && filled - stored < static_cast<uint32_t>(STAGES)) {
+        issue(next, filled % STAGES);
+        next += gridDim.x;
+        ++filled;
+        progress = true;
+      }
+      if (stored < filled && mbar_try_wait(&bars[stored % STAGES], (stored / STAGES) & 1)) {
+        store(c_store, stored % STAGES, stored);
+        c_store += gridDim.x;
+        ++stored;
+        progress = true;
+      }
+      if (next >= num_chunks && stored == filled) break;
+      if (progress) idle = 0;
+      else {
+        if (++idle > (1u << 24)) {
+          report_error(status, kErrProducerWait);
+          break;
+        }
+        __nanosleep(32);
+      }
+    }
+  }
+  tma_store_wait<0>();
+  mbar_arrive(park);
+}
+
 }  // namespace stb
 
 using namespace stb;
@@ -114,5 +211,20 @@ extern "C" int stb_peer_copy(const void* src, void* dst, long long bytes, int gr
                                                       chunk, status);
   }
   cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -static_cast<int>(e);
+}
+
+// Ring variants (see peer_copy_ring_kernel): dst2 = local scratch of `bytes`, flag = grid words of peer memory.
+extern "C" int stb_peer_copy_ring(const void* src, void* dst, void* dst2, void* flag, long long bytes, int grid,
+                                  int chunk, int stages, int feat, int* status, cudaStream_t stream) {
+  if (bytes <= 0 || (bytes & 15) || grid <= 0 || chunk < 128 || (chunk & 127)) return -kErrBadArgument;
+  if (stages != 4 && stages != 6) return -kErrBadArgument;
+  const int smem = stages * chunk + 256 + 1024;
+  auto kern = stages == 4 ? peer_copy_ring_kernel<4> : peer_copy_ring_kernel<6>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+  if (e != cudaSuccess) return -static_cast<int>(e);
+  kern<<<grid, 192, smem, stream>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst),
+                                    static_cast<uint8_t*>(dst2), static_cast<uint32_t*>(flag), bytes, chunk, feat, status);
+  e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -static_cast<int>(e);
 }

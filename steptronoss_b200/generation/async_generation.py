@@ -1,104 +1,133 @@
-"""Run generatable items concurrently: one asyncio loop per worker, several worker processes, one
-controller-wide cap on items in flight.
+"""Concurrent execution of generatable items (rollouts, evaluation prompts).
 
-Reference: ``steptronoss/generation/async_generation.py:18-273``.  ``SingleGenerationController`` owns a
-thread with an event loop that starts a task per submitted item; ``GenerationController`` spreads items
-over ``num_workers`` such processes, keeps a FIFO of submissions beyond ``max_concurrent_genables`` and
-invokes the callbacks in the submitting process.  A failing item comes back as a ``RuntimeError`` value
-(plain, so that it pickles), never as a raised exception in a worker.
+Contract, shared with the reference's module of the same name
+(``steptronoss/generation/async_generation.py:18-273``):
+
+* an item is a ``GenableItem`` whose ``generate()`` (or, for training, a ``TrainableItem``'s
+  ``generate_for_train()``) is a coroutine that talks to an inference server;
+* ``SingleGenerationController`` runs every submitted item concurrently inside one process;
+  ``GenerationController`` spreads items over ``num_workers`` processes and admits at most
+  ``max_concurrent_genables`` of them at a time, the rest wait in submission order;
+* results are handed to a callback ``callback(item, result)`` in the submitting process, or yielded in
+  completion order by ``generate(items)``;
+* an item that raises comes back with a ``RuntimeError`` *value* as its result (a plain exception, so that it
+  survives pickling); nothing is raised inside a worker.
+
+Design.  Inside a process the items are tasks of one asyncio event loop that lives on its own thread; a
+submission is handed to the loop with ``run_coroutine_threadsafe`` (no polling).  Across processes the parent
+numbers every submission with a ticket, keeps the callbacks by ticket, and a collector thread feeds the
+results back and admits the next waiting items.
 """
 from __future__ import annotations
 
 import asyncio
+import itertools
 import multiprocessing as mp
+import queue
 import threading
 import traceback
 from collections import deque
-from collections.abc import Callable, Iterable
-from queue import Empty, Queue
+from collections.abc import Callable, Iterator
+from functools import partial
 from typing import Any
-from uuid import uuid4
 
-from ..utils.general import run_async
 from ..utils.logger import logger
 from .base_generatable import GenableItem, TrainableItem
 
 
-class SingleGenerationController:
-    def __init__(self):
-        self.input_queue: Queue = Queue()
-        self._alive = True
-        self._worker = threading.Thread(target=lambda: run_async(self._generate_loop()), daemon=True)
-        self._worker.start()
+async def _produce(item: GenableItem, for_train: bool):
+    if not for_train:
+        return await item.generate()
+    if not isinstance(item, TrainableItem):
+        raise TypeError(f"generation for training needs a TrainableItem, not a {type(item).__name__}")
+    return await item.generate_for_train()
 
-    @staticmethod
-    async def work_on_item(item: GenableItem, callback, for_train: bool) -> None:
+
+async def _run_item(item: GenableItem, for_train: bool, deliver: Callable) -> None:
+    """One item from start to delivery; a failure becomes the item's result."""
+    try:
+        result = await _produce(item, for_train)
+    except Exception as exc:                     # noqa: BLE001 - whatever the item raised is reported as its result
+        logger.error("generation item failed:\n" + "".join(traceback.format_exception(exc)))
+        result = RuntimeError(f"{type(exc).__name__}: {exc}")
+    deliver(item, result)
+
+
+class _LoopThread:
+    """An asyncio event loop on a daemon thread."""
+
+    def __init__(self, name: str = "generation-loop"):
+        self.loop = asyncio.new_event_loop()
+        self._thread = threading.Thread(target=self._serve, name=name, daemon=True)
+        self._thread.start()
+
+    def _serve(self) -> None:
+        asyncio.set_event_loop(self.loop)
         try:
-            if for_train:
-                if not isinstance(item, TrainableItem):
-                    raise TypeError(f"Expected TrainableItem for training generation, got {type(item).__name__}")
-                result = await item.generate_for_train()
-            else:
-                result = await item.generate()
-        except Exception as e:
-            logger.error("".join(traceback.format_exception(e)))
-            result = RuntimeError(f"{type(e).__name__}: {e}")
-        callback(item, result)
+            self.loop.run_forever()
+        finally:
+            for task in asyncio.all_tasks(self.loop):
+                task.cancel()
+            self.loop.run_until_complete(self.loop.shutdown_asyncgens())
+            self.loop.close()
 
-    def generate(self, gen_items: list, for_train: bool = False) -> Iterable:
-        out: Queue = Queue()
-        for item in gen_items:
-            self.input_queue.put((item, lambda a, b: out.put((a, b)), for_train))
-        for _ in gen_items:
-            yield out.get()
+    def spawn(self, coro) -> None:
+        asyncio.run_coroutine_threadsafe(coro, self.loop)
+
+    def stop(self, timeout: float = 2.0) -> None:
+        if self.loop.is_running():
+            self.loop.call_soon_threadsafe(self.loop.stop)
+        self._thread.join(timeout=timeout)
+
+
+class SingleGenerationController:
+    """All submitted items run concurrently on one event loop of this process."""
+
+    def __init__(self):
+        self._runner = _LoopThread()
 
     def submit_with_callback(self, genable: GenableItem, for_train: bool = False, callback: Callable | None = None,
                              task_meta: dict | None = None) -> None:
         if task_meta:
             genable.meta.update(task_meta)
-        self.input_queue.put((genable, callback or print, for_train))
+        self._runner.spawn(_run_item(genable, for_train, callback or print))
 
-    async def _generate_loop(self):
-        tasks: list = []
-        while self._alive:
-            while True:
-                try:
-                    tasks.append(asyncio.create_task(self.work_on_item(*self.input_queue.get_nowait())))
-                except Empty:
-                    break
-            if tasks:
-                done, pending = await asyncio.wait(tasks, timeout=0.05, return_when=asyncio.FIRST_COMPLETED)
-                for t in done:
-                    await t
-                tasks = list(pending)
-            else:
-                await asyncio.sleep(0.02)
-        for t in tasks:
-            t.cancel()
+    def generate(self, gen_items: list, for_train: bool = False) -> Iterator:
+        finished: queue.SimpleQueue = queue.SimpleQueue()
+        for item in gen_items:
+            self.submit_with_callback(item, for_train, callback=lambda it, res: finished.put((it, res)))
+        for _ in range(len(gen_items)):
+            yield finished.get()
 
-    def shutdown(self):
-        self._alive = False
-        self._worker.join(timeout=2)
+    def shutdown(self) -> None:
+        self._runner.stop()
 
 
-def _generation_worker_process(input_queue, result_queue) -> None:
-    worker = SingleGenerationController()
+def _report(outbox, ticket, item: GenableItem, result) -> None:
+    outbox.put((ticket, item, result))
+
+
+def _worker_main(inbox, outbox) -> None:
+    """Body of a worker process: items arrive as ``(ticket, item, for_train)``, ``None`` ends the process."""
+    runner = SingleGenerationController()
     while True:
         try:
-            task = input_queue.get()
-            if task is None:
-                break
-            item, task_id, for_train = task
-            item.meta["_gc_task_id"] = task_id
-            worker.submit_with_callback(
-                item, for_train=for_train,
-                callback=lambda x, r, q=result_queue: q.put((x.meta.pop("_gc_task_id"), x, r)))
-        except Exception as e:  # keep the worker alive: the controller is waiting on its queue
-            logger.error(f"Worker process error: {e}")
-    worker.shutdown()
+            message = inbox.get()
+        except (EOFError, OSError):
+            break
+        except Exception as exc:                 # noqa: BLE001 - e.g. an item that cannot be unpickled here
+            logger.error(f"generation worker could not read a submission: {exc}")
+            continue
+        if message is None:
+            break
+        ticket, item, for_train = message
+        runner.submit_with_callback(item, for_train, callback=partial(_report, outbox, ticket))
+    runner.shutdown()
 
 
 class GenerationController:
+    """Items run in ``num_workers`` processes; at most ``max_concurrent_genables`` are admitted at a time."""
+
     def __init__(self, num_workers: int | None = None, max_concurrent_genables: int | None = None,
                  start_method: str | None = None):
         if max_concurrent_genables is not None and max_concurrent_genables < 1:
@@ -106,21 +135,22 @@ class GenerationController:
         self.num_workers = num_workers or min(mp.cpu_count(), 16)
         self.max_concurrent_genables = max_concurrent_genables
         ctx = mp.get_context(start_method) if start_method else mp
-        self.input_queue, self.result_queue = ctx.Queue(), ctx.Queue()
-        self.callback_map: dict = {}
-        self._pending: deque = deque()
-        self._inflight: set = set()
+        self._inbox, self._outbox = ctx.Queue(), ctx.Queue()
+        self._tickets = itertools.count()
+        self._waiting: deque = deque()           # (ticket, item, for_train) not yet admitted
+        self._callbacks: dict = {}               # ticket -> callback, for every submission that has not finished
+        self._admitted: set = set()
         self._lock = threading.Lock()
         self._completed = 0
-        self._alive = True
-        self.worker_processes = []
-        for _ in range(self.num_workers):
-            p = ctx.Process(target=_generation_worker_process, args=(self.input_queue, self.result_queue), daemon=True)
-            p.start()
-            self.worker_processes.append(p)
-        self.callback_thread = threading.Thread(target=self._callback_loop, daemon=True)
-        self.callback_thread.start()
+        self._closing = threading.Event()
+        self.worker_processes = [ctx.Process(target=_worker_main, args=(self._inbox, self._outbox), daemon=True)
+                                 for _ in range(self.num_workers)]
+        for proc in self.worker_processes:
+            proc.start()
+        self._collector = threading.Thread(target=self._collect, name="generation-collector", daemon=True)
+        self._collector.start()
 
+    # ------------------------------------------------------------------ bookkeeping
     @property
     def completed_count(self) -> int:
         return self._completed
@@ -128,54 +158,57 @@ class GenerationController:
     @property
     def inflight_count(self) -> int:
         with self._lock:
-            return len(self._inflight)
+            return len(self._admitted)
 
-    def _callback_loop(self):
-        while self._alive:
+    def _admit_waiting(self) -> None:
+        """Caller holds the lock."""
+        cap = self.max_concurrent_genables
+        while self._waiting and (cap is None or len(self._admitted) < cap):
+            entry = self._waiting.popleft()
+            self._admitted.add(entry[0])
+            self._inbox.put(entry)
+
+    def _collect(self) -> None:
+        while not self._closing.is_set():
             try:
-                task_id, item, result = self.result_queue.get(timeout=0.2)
-            except Empty:
+                ticket, item, result = self._outbox.get(timeout=0.2)
+            except queue.Empty:
                 continue
             except (EOFError, OSError):
                 return
             with self._lock:
-                callback = self.callback_map.pop(task_id)
-                self._inflight.discard(task_id)
-                self._dispatch_locked()
-            try:
-                callback(item, result)
-            except Exception as e:
-                logger.error(f"generation callback failed: {e}")
+                callback = self._callbacks.pop(ticket, None)
+                self._admitted.discard(ticket)
+                self._admit_waiting()
+            if callback is not None:
+                try:
+                    callback(item, result)
+                except Exception as exc:         # noqa: BLE001 - a user callback must not stop the collector
+                    logger.error(f"generation callback raised: {exc}")
             self._completed += 1
 
-    def _dispatch_locked(self) -> None:
-        while self._pending and (self.max_concurrent_genables is None
-                                 or len(self._inflight) < self.max_concurrent_genables):
-            genable, task_id, for_train = self._pending.popleft()
-            self._inflight.add(task_id)
-            self.input_queue.put((genable, task_id, for_train))
-
-    def generate(self, gen_items: list, for_train: bool = False) -> Iterable:
-        out: Queue = Queue()
-        for item in gen_items:
-            self.submit_with_callback(item, for_train, lambda it, res, q=out: q.put((it, res)))
-        for _ in gen_items:
-            yield out.get()
-
+    # ------------------------------------------------------------------ public API
     def submit_with_callback(self, genable: GenableItem, for_train: bool = False, callback: Callable | None = None,
                              task_id: Any = None) -> None:
-        task_id = str(uuid4()) if task_id is None else task_id
+        ticket = next(self._tickets) if task_id is None else task_id
         with self._lock:
-            self.callback_map[task_id] = callback or print
-            self._pending.append((genable, task_id, for_train))
-            self._dispatch_locked()
+            self._callbacks[ticket] = callback or print
+            self._waiting.append((ticket, genable, for_train))
+            self._admit_waiting()
 
-    def shutdown(self):
-        self._alive = False
+    def generate(self, gen_items: list, for_train: bool = False) -> Iterator:
+        finished: queue.SimpleQueue = queue.SimpleQueue()
+        for item in gen_items:
+            self.submit_with_callback(item, for_train, callback=lambda it, res: finished.put((it, res)))
+        for _ in range(len(gen_items)):
+            yield finished.get()
+
+    def shutdown(self) -> None:
+        self._closing.set()
         for _ in self.worker_processes:
-            self.input_queue.put(None)
-        for p in self.worker_processes:
-            p.join(timeout=1)
-            if p.is_alive():
-                p.terminate()
-        self.callback_thread.join(timeout=0.5)
+            self._inbox.put(None)
+        for proc in self.worker_processes:
+            proc.join(timeout=1)
+            if proc.is_alive():
+                proc.terminate()
+        self._collector.join(timeout=0.5)

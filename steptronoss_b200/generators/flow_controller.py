@@ -1,15 +1,15 @@
 """Rollout scheduling between the trainer and the inference replicas.
 
-Reference: ``steptronoss/core/generators/flow_controller.py:22-505``.  World rank 0 runs two daemon threads
-around a :class:`~steptronoss_b200.utils.rl_utils.PersistentFlow` with three stages::
+Behaviour follows ``steptronoss/core/generators/flow_controller.py:22-505``.  World rank 0 schedules prompts
+through a :class:`~steptronoss_b200.utils.rl_utils.PersistentFlow` with three stages::
 
-    source --(control worker)--> pre_gen --(generation worker + callbacks)--> pre_train --> trainer
+    source --> pre_gen --(generation + callbacks)--> pre_train --> trainer
 
-* :class:`SimpleFlowController` (``on-policy`` / ``one-step-off``): the control worker writes
-  ``need_version(v), prompt x prompt_per_iter, train`` groups; the generation worker holds a group until
-  the replicas serve weight version ``v`` and closes it when all its prompts have returned.  ``on-policy``
-  schedules group ``k`` on version ``k``; ``one-step-off`` lets group ``k`` run on version ``k-1`` so that
-  generation overlaps the previous training step.
+* :class:`SimpleFlowController` (``on-policy`` / ``one-step-off``): ``pre_gen`` holds groups
+  ``need_version(v), prompt x prompt_per_iter, train``; a group is held until the replicas serve weight version
+  ``v`` and is closed when all its prompts have returned.  ``on-policy`` runs group ``k`` on version ``k``;
+  ``one-step-off`` lets group ``k`` run on version ``k-1`` so that generation overlaps the previous training
+  step.
 * :class:`FullyAsyncFlowController`: no groups; prompts flow continuously, bounded by
   ``max_untrained_prompts`` (back-pressure on inference) and ``max_staleness`` (the trainer waits before a
   weight update while prompts scheduled too many versions ago are still running).
@@ -77,9 +77,9 @@ class FlowController(metaclass=ABCMeta):
     def weight_dumped(self):
         """The weights trained on everything handed out so far are safely stored: acknowledge it."""
         if PM.world_rank == 0 and hasattr(self, "flow"):
-            for ack_id in self.yielded_but_not_acked_train_samples:
+            for ack_id in self._handed_out:
                 self.flow["pre_train"].ack(ack_id)
-            self.yielded_but_not_acked_train_samples.clear()
+            self._handed_out.clear()
             cv = getattr(self, "_cv", None)
             if cv is not None:
                 with cv:
@@ -87,110 +87,152 @@ class FlowController(metaclass=ABCMeta):
 
 
 class SimpleFlowController(FlowController):
+    """Group-at-a-time scheduling (``on-policy`` and ``one-step-off``).
+
+    A *group* is the ``prompt_per_iter`` prompts of one training iteration.  In the durable ``pre_gen`` stage a
+    group is written as ``need_version(v)``, its prompts, ``train``; group ``k`` asks for weight version
+    ``max(k - lead, 0)`` and may be written once ``k - lead <= train_weight_version + 1``, where ``lead`` is how
+    many groups generation may run ahead of training (0 on-policy, 1 one-step-off).
+
+    One *conductor* thread owns the stage: it writes the groups that have become admissible, holds a group at its
+    ``need_version`` marker until the replicas serve that version, submits the prompts, and moves the ``train``
+    marker downstream when the last prompt of the group has returned.  Everything waits on one condition
+    variable (the flow lock), which weight syncs, finished prompts and acknowledgements notify.
+    """
+
+    LEAD = {"on-policy": 0, "one-step-off": 1}
+
     def __init__(self, flow_cfg, generator=None, deploy_fn=None):
+        if flow_cfg.async_strategy not in self.LEAD:
+            raise ValueError(f"SimpleFlowController schedules {sorted(self.LEAD)}, not {flow_cfg.async_strategy!r}")
         self.cfg = flow_cfg
-        assert self.cfg.async_strategy in ("on-policy", "one-step-off")
+        self.lead = self.LEAD[flow_cfg.async_strategy]
         self.generator, self.deploy_fn = generator, deploy_fn
         self.infer_weight_version = self.train_weight_version = -1
-        self.yielded_but_not_acked_train_samples: list = []
+        self._handed_out: list = []
         self.source_exhausted = False
 
+    # ------------------------------------------------------------------ life cycle
     def start(self, dataloader, model, state_dict: dict | None = None):
         self.model = model
-        if PM.world_rank == 0:
-            self.generator = self._build_generator()
-            self.flow = PersistentFlow(source=PersistentSource(nextable=dataloader), pre_gen=PersistentQueue(),
-                                       pre_train=PersistentQueue())
-            if state_dict:
-                self._load_state_dict(state_dict)
-            Thread(target=self._generation_worker, daemon=True).start()
-            Thread(target=self._control_worker, daemon=True).start()
+        if PM.world_rank != 0:
+            return
+        self.generator = self._build_generator()
+        self.flow = PersistentFlow(source=PersistentSource(nextable=dataloader), pre_gen=PersistentQueue(),
+                                   pre_train=PersistentQueue())
+        self._cv = Condition(self.flow.lock)
+        self._load_state_dict(state_dict)
+        self.flow.meta.setdefault("groups_planned", 0)
+        Thread(target=self._conduct, name="rollout-conductor", daemon=True).start()
 
     def state_dict(self) -> dict:
-        if PM.world_rank == 0:
-            return {"infer_weight_version": self.infer_weight_version,
-                    "train_weight_version": self.train_weight_version, "flow": self.flow.state_dict()}
-        return {}
+        if PM.world_rank != 0:
+            return {}
+        return {"controller_type": "grouped", "train_weight_version": self.train_weight_version,
+                "infer_weight_version": self.infer_weight_version, "flow": self.flow.state_dict()}
 
     def _load_state_dict(self, state_dict):
         if PM.world_rank != 0 or not state_dict:
             return
+        # the replicas of a resumed job serve nothing yet; the trainer's version is whatever was saved
         self.infer_weight_version = -1
         self.train_weight_version = state_dict.get("train_weight_version", -1)
-        if "flow" in state_dict:
-            self.flow.load_state_dict(state_dict["flow"])
-            logger.warning(f"FlowCkpt loaded, flow:\n{self.flow}")
+        saved = state_dict.get("flow")
+        if saved is not None:
+            self.flow.load_state_dict(saved)
+            logger.info(f"rollout flow restored: {self.flow}")
 
-    def _control_worker(self):
-        first = 0 if self.cfg.async_strategy == "on-policy" else -1
-        self.flow.meta.setdefault("scheduled-weight-version", first)
-        while not self.source_exhausted:
-            if self.flow.meta["scheduled-weight-version"] <= self.train_weight_version + 1:
-                version = max(self.flow.meta["scheduled-weight-version"], 0)
-                with self.flow.lock:
-                    self.flow["pre_gen"].put(PersistentFlow.Signal("need_version", version=version))
-                    for _ in range(self.cfg.prompt_per_iter):
-                        try:
-                            self.flow["pre_gen"].put(self.flow["source"].pop())
-                        except StopIteration:
-                            self.source_exhausted = True
-                            return
-                    self.flow["pre_gen"].put(PersistentFlow.Signal("train"))
-                    self.flow.meta["scheduled-weight-version"] += 1
-            time.sleep(self.poll_s)
-
-    def _generation_worker(self):
-        active = [0]
-        ack_version = None
-
-        def on_done(genable, generated):
+    # ------------------------------------------------------------------ conductor (holds the flow lock)
+    def _write_admissible_groups(self) -> None:
+        pre_gen, source, meta = self.flow["pre_gen"], self.flow["source"], self.flow.meta
+        while not self.source_exhausted and meta["groups_planned"] - self.lead <= self.train_weight_version + 1:
+            wanted = max(meta["groups_planned"] - self.lead, 0)
+            prompts = []
             try:
-                if isinstance(generated, Exception):
-                    if not self.cfg.genable_allow_errors:
-                        raise generated
-                    generated = []
-                with self.flow.lock:
-                    self.flow["pre_train"].put(generated)
-                    self.flow["pre_gen"].ack(genable.meta.pop("ack_pre_id"))
+                for _ in range(self.cfg.prompt_per_iter):
+                    prompts.append(source.pop())
+            except StopIteration:
+                # an incomplete last group is still written, so that a snapshot keeps its prompts; without its
+                # closing marker it is never handed to the trainer
+                self.source_exhausted = True
+            pre_gen.put(PersistentFlow.Signal("need_version", version=wanted), *prompts)
+            if not self.source_exhausted:
+                pre_gen.put(PersistentFlow.Signal("train"))
+                meta["groups_planned"] += 1
+
+    def _conduct(self) -> None:
+        cv, pre_gen, pre_train = self._cv, self.flow["pre_gen"], self.flow["pre_train"]
+        group = {"outstanding": 0, "version_marker": None}
+        held = None                                # an entry taken from pre_gen that cannot be acted on yet
+
+        def prompt_returned(genable, generated):
+            try:
+                failed = isinstance(generated, Exception)
+                if failed and not self.cfg.genable_allow_errors:
+                    raise generated
+                with cv:
+                    pre_train.put([] if failed else generated)
+                    pre_gen.ack(genable.meta.pop("pre_gen_id"))
             finally:
-                active[0] -= 1
+                with cv:
+                    group["outstanding"] -= 1
+                    cv.notify_all()
 
-        while True:
-            ack_id, data = self.flow["pre_gen"].get()
-            if isinstance(data, PersistentFlow.Signal):
-                if data.name == "need_version":
-                    while self.infer_weight_version < data["version"]:
-                        time.sleep(self.poll_s)
-                    ack_version = ack_id
-                elif data.name == "train":
-                    while active[0]:
-                        time.sleep(self.poll_s)
-                    with self.flow.lock:
-                        if ack_version:
-                            self.flow["pre_gen"].ack(ack_version)
-                        self.flow["pre_train"].put(data)
-                        self.flow["pre_gen"].ack(ack_id)
-            else:
-                data.meta["ack_pre_id"] = ack_id
-                active[0] += 1
-                self.generator.submit_with_callback(data, for_train=True, callback=on_done)
+        with cv:
+            while True:
+                self._write_admissible_groups()
+                if held is None:
+                    if len(pre_gen) == 0:
+                        cv.wait(timeout=self.poll_s)
+                        continue
+                    held = pre_gen.get()
+                entry_id, entry = held
+                if not isinstance(entry, PersistentFlow.Signal):
+                    entry.meta["pre_gen_id"] = entry_id
+                    group["outstanding"] += 1
+                    self.generator.submit_with_callback(entry, for_train=True, callback=prompt_returned)
+                elif entry.name == "need_version":
+                    if self.infer_weight_version < entry["version"]:
+                        cv.wait(timeout=self.poll_s)
+                        continue
+                    group["version_marker"] = entry_id     # acknowledged together with the group's closing marker
+                elif entry.name == "train":
+                    if group["outstanding"] > 0:
+                        cv.wait(timeout=self.poll_s)
+                        continue
+                    pre_train.put(entry)
+                    if group["version_marker"] is not None:
+                        pre_gen.ack(group["version_marker"])
+                        group["version_marker"] = None
+                    pre_gen.ack(entry_id)
+                    cv.notify_all()
+                held = None
 
+    # ------------------------------------------------------------------ trainer side
     def get_train_samples(self) -> list:
-        """The trajectories of one training iteration; calling it is also what lets the next weights out."""
+        """The trajectories of one training iteration.  Asking for them is what announces the next weight version:
+        the replicas are brought up to date first, which releases the group that waits for it."""
         self.train_weight_version += 1
         self.sync_weight()
-        trajectories = []
-        if PM.world_rank == 0:
+        if PM.world_rank != 0:
+            return []
+        trajectories: list = []
+        pre_train = self.flow["pre_train"]
+        with self._cv:
             while True:
-                ack_id, trajs = self.flow["pre_train"].get()
-                self.yielded_but_not_acked_train_samples.append(ack_id)
-                if isinstance(trajs, PersistentFlow.Signal) and trajs.name == "train":
-                    break
-                prompt_id = str(uuid4())
-                for t in trajs:
-                    t.prompt_id = prompt_id
-                trajectories.extend(trajs)
-        return trajectories
+                if len(pre_train) == 0:
+                    self._cv.wait(timeout=self.poll_s)
+                    continue
+                taken_id, payload = pre_train.get()
+                self._handed_out.append(taken_id)
+                if isinstance(payload, PersistentFlow.Signal):
+                    if payload.name == "train":
+                        return trajectories
+                    continue
+                prompt_id = uuid4().hex                     # trajectories of one prompt share it (group baselines)
+                for traj in payload:
+                    traj.prompt_id = prompt_id
+                trajectories.extend(payload)
 
 
 class FullyAsyncFlowController(FlowController):
@@ -204,7 +246,7 @@ class FullyAsyncFlowController(FlowController):
                              f"{self.cfg.max_untrained_prompts} + 1 < {self.cfg.prompt_per_iter}")
         self.generator, self.deploy_fn = generator, deploy_fn
         self.infer_weight_version = self.train_weight_version = -1
-        self.yielded_but_not_acked_train_samples: list = []
+        self._handed_out: list = []
         self.running_genables: dict = {}
         self.source_exhausted = False
         self.started = False
@@ -334,7 +376,7 @@ class FullyAsyncFlowController(FlowController):
                     self._cv.wait(timeout=self.poll_s)
                 for _ in range(self.cfg.prompt_per_iter):
                     ack_id, trajs = self.flow["pre_train"].get()
-                    self.yielded_but_not_acked_train_samples.append(ack_id)
+                    self._handed_out.append(ack_id)
                     prompt_id = str(uuid4())
                     for t in trajs:
                         t.prompt_id = prompt_id

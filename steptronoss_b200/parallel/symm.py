@@ -14,8 +14,7 @@ CPU/gloo runs, groups that span nodes and shapes the kernels do not take (row bl
 multiple of 128).
 
 Environment: ``STB200_PEER_TP=0`` disables the peer path; ``STB200_PEER_WAIT_S`` (default 30) bounds every
-wait on another rank inside the kernels; ``STB200_TP_COMM_CTAS`` fixes how many CTAs of a fused launch move data
-with bulk copies (default: chosen from the transfer size and the GEMM's length).
+wait on another rank inside the kernels.
 """
 from __future__ import annotations
 
@@ -34,7 +33,6 @@ _MAX_RANKS = 8
 _ARENAS: dict[str, "Arena | None"] = {}
 _DISABLED = os.environ.get("STB200_PEER_TP", "1") == "0"
 _WAIT_NS = int(float(os.environ.get("STB200_PEER_WAIT_S", "30")) * 1e9)
-_COMM_CTAS = int(os.environ.get("STB200_TP_COMM_CTAS", "0"))   # CTAs in the communication role; 0 = from the sizes
 _TRACE = None  # int64 [SMs, 8] tensor set by trace(): per-CTA phase stamps of the next fused launches
 
 
@@ -43,6 +41,12 @@ def trace(enable: bool = True):
     global _TRACE
     _TRACE = torch.zeros((256, 8), dtype=torch.int64, device="cuda") if enable else None
     return _TRACE
+
+
+def trace_rows() -> list:
+    """The raw per-CTA stamps (rows of CTAs that ran), columns as in :func:`trace_summary`."""
+    t = _TRACE.cpu()
+    return t[t[:, 0] > 0].tolist()
 
 
 def trace_summary() -> dict:
@@ -66,10 +70,10 @@ native.register_signature("stb_symm_open", [P, P])
 native.register_signature("stb_symm_close", [P])
 native.register_signature("stb_symm_free", [P])
 native.register_signature(
-    "stb_gemm_ag_bf16", [P, L, P, P, P, P, I, I, I, I, I, I, I, I, I, U, P, ULL, I, P, P, P]
+    "stb_gemm_ag_bf16", [P, L, P, P, P, P, I, I, I, I, I, I, I, I, I, U, P, ULL, P, P, P]
 )
 native.register_signature(
-    "stb_gemm_rs_bf16", [P, I, P, I, I, P, L, P, P, P, I, I, I, I, I, U, P, ULL, I, P, P, P]
+    "stb_gemm_rs_bf16", [P, I, P, I, I, P, L, P, P, P, I, I, I, I, I, U, P, ULL, P, P, P]
 )
 
 
@@ -256,7 +260,7 @@ def all_gather_gemm(x, w, group_name: str = "TP", *, b_mn_major: bool = False, o
         x.data_ptr(), x.stride(0), ptrs, a._flag_arr,
         w.data_ptr() if n else None, y.data_ptr() if n else None, rows, n, k,
         w.stride(0) if n else 8, y.stride(0) if n else 8, int(b_mn_major), int(need_gathered), a.rank, a.world,
-        a.ag_epoch & 0xFFFFFFFF, a.ctrs.data_ptr(), _WAIT_NS, _COMM_CTAS, native.status_word(x.device).data_ptr(),
+        a.ag_epoch & 0xFFFFFFFF, a.ctrs.data_ptr(), _WAIT_NS, native.status_word(x.device).data_ptr(),
         _TRACE.data_ptr() if _TRACE is not None else None, native.stream(),
     )
     native.check(rc, f"all_gather_gemm rows={rows} N={n} K={k}")
@@ -279,7 +283,7 @@ def gemm_reduce_scatter(x, w, group_name: str = "TP", *, b_mn_major: bool = Fals
     rc = a.lib.stb_gemm_rs_bf16(
         x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), int(b_mn_major), out.data_ptr(), out.stride(0),
         staging.data_ptr(), recv, a._flag_arr, rows, n, k, a.rank, a.world, a.rs_epoch & 0xFFFFFFFF, a.ctrs.data_ptr(),
-        _WAIT_NS, _COMM_CTAS, native.status_word(x.device).data_ptr(),
+        _WAIT_NS, native.status_word(x.device).data_ptr(),
         _TRACE.data_ptr() if _TRACE is not None else None, native.stream(),
     )
     native.check(rc, f"gemm_reduce_scatter M={m} N={n} K={k}")
