@@ -9,6 +9,12 @@ and ``peer`` (rows written straight into the destination GPU's buffer over NVLin
 every rank, maximum over ranks.
 
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/benchmark_moe_layer.py
+
+``--impl reference`` times the same layer built from the unmodified reference framework under ``baseline/_ref``:
+its ``TokenDispatcher`` (NCCL all-to-alls), its ``routed_grouped_ffn`` with the fastest expert GEMM it ships that
+runs here (its Triton grouped GEMM; ``--ref-grouped-gemm default`` selects the per-expert loop) and its Triton
+routing / scatter / gather kernels, in the manner of its own ``benchmarks/benchmark_dispatcher.py:20-157``.  The
+router (top-k of the same logits) is this repository's on both arms and sits outside the timed region there.
 """
 from __future__ import annotations
 
@@ -23,6 +29,104 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
+def run_reference(args):
+    """The reference's dispatcher + grouped expert FFN + combine on the same workload, forward and backward."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref = os.path.join(root, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "steptronoss")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/steptronoss is absent"}), flush=True)
+        return
+    sys.path.insert(0, os.path.join(root, "baseline", "shims"))
+    sys.path.insert(0, ref)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29533")
+    for k, v in (("RANK", "0"), ("WORLD_SIZE", "1"), ("LOCAL_RANK", "0")):
+        os.environ.setdefault(k, v)
+    torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    from steptronoss.core.parallel_state import PM as RPM
+    from steptronoss.exp.base_exp import ParallelConfig as RParallelConfig
+    from steptronoss.model.ep_dispatcher.token_dispatcher import TokenDispatcher
+    from steptronoss.model.utils import moe_utils as rmoe
+    from steptronoss.utils.optimizable import set_optimization
+
+    from benchmarks.common import flush_l2, measured_peaks
+    from steptronoss_b200.ops import moe as moe_ops          # the router only: outside the timed region
+
+    if not dist.is_initialized():
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", int(os.environ["LOCAL_RANK"])))
+    world, rank = dist.get_world_size(), dist.get_rank()
+    RPM.initialize(backend="nccl")
+    mesh = RParallelConfig()
+    mesh.tensor_model_parallel_size = mesh.pipeline_model_parallel_size = mesh.context_parallel_size = 1
+    mesh.virtual_pipeline_model_parallel_size = 1
+    mesh.expert_model_parallel_size, mesh.expert_tensor_parallel_size = world, 1
+    RPM.set_mesh(mesh)
+    choices = {"histogram": "triton", "index_compute": "triton", "moe_scatter": "triton", "moe_weighted_gather": "triton"}
+    if args.ref_grouped_gemm != "default":
+        choices["grouped_gemm"] = args.ref_grouped_gemm
+    set_optimization(**choices)
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    T, H, E, F, K = args.tokens, args.hidden, args.experts, args.ffn, args.top_k
+    g = torch.Generator(device=dev).manual_seed(1234 + rank)
+    e_local = E // world
+    w1 = (torch.randn(e_local, 2 * F, H, device=dev, generator=g) * 0.02).to(torch.bfloat16).requires_grad_()
+    w2 = (torch.randn(e_local, H, F, device=dev, generator=g) * 0.02).to(torch.bfloat16).requires_grad_()
+    x = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16).requires_grad_()
+    gout = torch.randn(T, H, device=dev, generator=g).to(torch.bfloat16)
+    base_logits = torch.randn(T, E, device=dev, generator=g)
+    zipf = torch.log(1.0 / torch.arange(1, E + 1, device=dev, dtype=torch.float32))
+
+    def act(v):
+        a, b = torch.chunk(v, 2, dim=-1)
+        return torch.nn.functional.silu(a) * b
+
+    peaks = measured_peaks()
+    rows = []
+    for routing, logits in (("uniform", base_logits), ("zipf", base_logits + zipf)):
+        ids, w, _ps, _hist, _stats = moe_ops.fused_router(logits, None, K, False, True, 0.0)
+        ids, w = ids.long(), w.detach().float().requires_grad_()
+        dispatcher = TokenDispatcher("EP", num_experts=E) if world > 1 else None
+
+        def step():
+            if dispatcher is not None:
+                h, lid, lw = dispatcher.dispatch(x, ids, w)
+            else:
+                h, lid, lw = x, ids, w
+            y = rmoe.routed_grouped_ffn(w1, w2, act, h, lid.to(torch.int32), lw)
+            out = dispatcher.combine(y) if dispatcher is not None else y
+            return out, torch.autograd.grad(out, [x, w, w1, w2], gout)
+
+        for _ in range(args.warmup):
+            step()
+        times = []
+        for _ in range(args.iters):
+            dist.barrier()
+            flush_l2()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            step()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+        t = torch.tensor([min(times), sorted(times)[len(times) // 2]], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        flops = 3 * 2.0 * float(T * K * world) * H * 3 * F
+        row = {"bench": "moe_layer_fwd_bwd", "impl": "reference", "routing": routing,
+               "dispatcher": "TokenDispatcher (NCCL all-to-all)", "optimizable": choices, "ep": world,
+               "tokens_per_rank": T, "hidden": H, "experts": E, "ffn": F, "top_k": K, "best_ms": float(t[0]),
+               "median_ms": float(t[1]), "tokens_per_s_all_ranks": T * world / (float(t[0]) * 1e-3),
+               "expert_gemm_tflops_per_gpu": flops / world / (float(t[0]) * 1e-3) / 1e12,
+               "frac_of_measured_bf16_peak": flops / world / (float(t[0]) * 1e-3) / 1e12 / peaks["bf16_tflops"]}
+        rows.append(row)
+        if rank == 0:
+            print(json.dumps(row), flush=True)
+    dist.barrier()
+    if rank == 0 and args.json:
+        json.dump({"peaks": peaks, "rows": rows}, open(args.json, "w"), indent=1)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=4096)
@@ -33,7 +137,12 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", default=None)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ref-grouped-gemm", default="triton_grouped_gemm",
+                    help="reference arm: alternative of its grouped_gemm switch, or 'default' for the per-expert loop")
     args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
 
     from benchmarks.common import flush_l2, measured_peaks
     from steptronoss_b200.config import Config

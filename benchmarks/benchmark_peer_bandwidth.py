@@ -36,6 +36,7 @@ def main():
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--ring-mb", type=int, default=32, help="MiB per rank moved by the ring variants")
     ap.add_argument("--ring-only", action="store_true", help="skip the plain / bulk sweeps")
+    ap.add_argument("--no-ring", action="store_true", help="skip the ring variants")
     ap.add_argument("--json", default=None)
     args = ap.parse_args()
 
@@ -151,7 +152,7 @@ def main():
         return {"us": float(t.item()) * 1e3, "gbs": ring_bytes * len(peers) / (float(t.item()) * 1e-3) / 1e9}
 
     res["ring"] = {"mib_per_rank": ring_bytes * len(peers) >> 20}
-    for grid in (16, 20, 32):
+    for grid in (() if args.no_ring else (16, 20, 32)):
         for stages in (4, 6):
             for feat in (0, 1, 2, 3, 4, 8, 15):
                 res["ring"][f"g{grid}_s{stages}_f{feat}"] = timed_ring(lambda: run_ring(grid, stages, feat))
