@@ -424,6 +424,18 @@ class Config(metaclass=_ConfigMeta):
             raise AssertionError("critical config attributes differ from checkpoint: " + repr(bad))
 
     # ------------------------------------------------------------ presentation
+    @staticmethod
+    def _brief(v) -> str:
+        """``repr`` that never walks into another part of the tree: a config reached through a reference (or a bound
+        method of one, e.g. an activation function borrowed from the parent) is named, not printed, which also keeps
+        a child that points at its ancestor from recursing for ever."""
+        if isinstance(v, Config):
+            return f"<{type(v).__name__}>"
+        owner = getattr(v, "__self__", None)
+        if isinstance(owner, Config):
+            return f"<method {type(owner).__name__}.{getattr(v, '__name__', '?')}>"
+        return repr(v)
+
     def format_tree(self, indent: int = 0) -> str:
         pad = "  " * indent
         lines = []
@@ -438,9 +450,9 @@ class Config(metaclass=_ConfigMeta):
                 lines.append(f"{pad}{k}: {type(v).__name__}")
                 lines.append(v.format_tree(indent + 1))
             elif isinstance(raw, Ref):
-                lines.append(f"{pad}{k}: {v!r}    <- {raw!r}")
+                lines.append(f"{pad}{k}: {self._brief(v)}    <- {raw!r}")
             else:
-                lines.append(f"{pad}{k}: {v!r}")
+                lines.append(f"{pad}{k}: {self._brief(v)}")
         return "\n".join(x for x in lines if x)
 
     def __repr__(self) -> str:

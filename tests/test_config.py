@@ -220,3 +220,24 @@ def test_cfshow_prints_subtrees_diffs_and_the_check_result(tmp_path):
                       "class Exp(Config):\n    model_cfg = M\n")
     out = io.StringIO()
     assert show(str(broken), out=out) == 1 and "sanity_check: FAILED" in out.getvalue() and "layers" in out.getvalue()
+
+
+def test_repr_of_a_child_that_borrows_a_method_from_its_parent_terminates():
+    from steptronoss_b200.config import Config, Ref
+
+    class Child(Config):
+        def __init__(self):
+            super().__init__()
+            self.act = Ref("..activation")
+            self.owner = Ref("..")
+
+    class Parent(Config):
+        child = Child
+
+        def activation(self, x):
+            return x + 1
+
+    p = Parent()
+    text = repr(p)
+    assert "<method Parent.activation>" in text and "<Parent>" in text
+    assert p.child.act(1) == 2
