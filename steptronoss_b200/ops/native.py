@@ -123,8 +123,20 @@ def ptr(t: torch.Tensor | None):
     return None if t is None else t.data_ptr()
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_DEVICE_INDEX: int | None = None
+
+
 def stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The raw handle of the current CUDA stream.  Called once per kernel launch, so it avoids building a
+    ``torch.cuda.Stream`` object (about 15 us each, a tenth of the host time of a launch-bound step): one process
+    drives one device, whose index is looked up once."""
+    global _DEVICE_INDEX
+    if _RAW_STREAM is None:
+        return torch.cuda.current_stream().cuda_stream
+    if _DEVICE_INDEX is None:
+        _DEVICE_INDEX = torch.cuda.current_device()
+    return _RAW_STREAM(_DEVICE_INDEX)
 
 
 _ERRORS = {
