@@ -44,21 +44,40 @@ __device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
 constexpr int kNormThreads = 256;
 constexpr int kNormMaxVec = 4;  // up to 256*8*4 = 8192 columns held in registers
 
+// With `delta` the row that is normalised is s = bf16(x + delta), which is also written to `sum_out` (the residual
+// stream of a pre-norm block: one pass instead of an add kernel followed by a norm kernel).
 __global__ void __launch_bounds__(kNormThreads)
-rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
-                   __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int H, long long x_stride,
-                   long long y_stride, float eps, int zero_centered) {
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+                   const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                   __nv_bfloat16* __restrict__ sum_out, float* __restrict__ rstd_out, int H, long long x_stride,
+                   long long delta_stride, long long y_stride, long long sum_stride, float eps, int zero_centered) {
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * x_stride);
+  const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + row * delta_stride) : nullptr;
+  uint4* sr = sum_out ? reinterpret_cast<uint4*>(sum_out + row * sum_stride) : nullptr;
   const int nvec = H / 8;
   uint4 cache[kNormMaxVec];
   float ss = 0.f;
+  // s = bf16(x + delta): what an elementwise bf16 add would have produced, so the statistics see the rounded sum
+  auto load_row = [&](int v) -> uint4 {
+    uint4 u = xr[v];
+    if (dr != nullptr) {
+      float a[8], b[8];
+      unpack8(u, a);
+      unpack8(dr[v], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] += b[j];
+      u = pack8(a);
+      if (sr != nullptr) sr[v] = u;
+    }
+    return u;
+  };
 #pragma unroll
   for (int i = 0; i < kNormMaxVec; ++i) {
     const int v = threadIdx.x + i * kNormThreads;
     if (v < nvec) {
-      cache[i] = xr[v];
+      cache[i] = load_row(v);
       float f[8];
       unpack8(cache[i], f);
 #pragma unroll
@@ -67,7 +86,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
   for (int v = threadIdx.x + kNormMaxVec * kNormThreads; v < nvec; v += kNormThreads) {
     float f[8];
-    unpack8(xr[v], f);
+    unpack8(load_row(v), f);
 #pragma unroll
     for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
   }
@@ -91,7 +110,16 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
   for (int v = threadIdx.x + kNormMaxVec * kNormThreads; v < nvec; v += kNormThreads) {
     float f[8], g[8];
-    unpack8(xr[v], f);
+    if (dr != nullptr) {       // very wide rows: the sum is recomputed (it was written to sum_out by this thread)
+      float b[8];
+      unpack8(xr[v], f);
+      unpack8(dr[v], b);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += b[j];
+      unpack8(pack8(f), f);
+    } else {
+      unpack8(xr[v], f);
+    }
     unpack8(wr[v], g);
 #pragma unroll
     for (int j = 0; j < 8; ++j) f[j] = f[j] * rstd * (g[j] + woff);
@@ -105,8 +133,9 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                    const __nv_bfloat16* __restrict__ g, const float* __restrict__ rstd_in,
-                   __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows, int H, long long x_stride,
-                   long long g_stride, long long dx_stride, int zero_centered, int add_to_dx) {
+                   __nv_bfloat16* dx, float* __restrict__ dw_partial, int rows, int H, long long x_stride,
+                   long long g_stride, long long dx_stride, int zero_centered, const __nv_bfloat16* dres,
+                   long long dres_stride) {
   __shared__ float red[32];
   const int nvec = H / 8;
   float dw_acc[kNormMaxVec][8];
@@ -120,6 +149,8 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * x_stride);
     const uint4* gr = reinterpret_cast<const uint4*>(g + row * g_stride);
     uint4* dxr = reinterpret_cast<uint4*>(dx + row * dx_stride);
+    // gradient that reached the normalised tensor by another path (the residual stream); may alias dx
+    const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + row * dres_stride) : nullptr;
     const float rstd = rstd_in[row];
     float xh[kNormMaxVec][8], gw[kNormMaxVec][8];
     float dot = 0.f;
@@ -148,9 +179,9 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
         float o[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = (gw[i][j] - xh[i][j] * dot) * rstd;
-        if (add_to_dx) {
+        if (rr != nullptr) {
           float old[8];
-          unpack8(dxr[v], old);
+          unpack8(rr[v], old);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += old[j];
         }
@@ -170,14 +201,26 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
-// dw[c] (+)= sum_p partial[p][c], p ascending (deterministic).
-__global__ void rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int parts, int H,
-                                         int accumulate, long long part_stride) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= H) return;
+// dw[c] (+)= sum_p partial[p][c] in a fixed order (deterministic): a block owns 32 columns, its eight warps each
+// add every eighth partial row (coalesced 128-byte reads), and warp 0 adds the eight sub-sums in order.
+constexpr int kDwReduceWarps = 8;
+__global__ void __launch_bounds__(32 * kDwReduceWarps)
+rmsnorm_dw_reduce_kernel(const float* __restrict__ partial, float* __restrict__ dw, int parts, int H, int accumulate,
+                         long long part_stride) {
+  __shared__ float sub[kDwReduceWarps][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int p = 0; p < parts; ++p) s += partial[static_cast<long long>(p) * part_stride + c];
-  dw[c] = accumulate ? dw[c] + s : s;
+  if (c < H)
+    for (int p = ty; p < parts; p += kDwReduceWarps) s += partial[static_cast<long long>(p) * part_stride + c];
+  sub[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < H) {
+    float t = 0.f;
+#pragma unroll
+    for (int i = 0; i < kDwReduceWarps; ++i) t += sub[i][tx];
+    dw[c] = accumulate ? dw[c] + t : t;
+  }
 }
 
 // ============================================================================ QK-norm + RoPE
@@ -493,8 +536,22 @@ extern "C" int stb_rmsnorm_fwd(const void* x, const void* w, void* y, float* rst
   if (rows <= 0) return 0;
   if (H % 8) return -kErrBadArgument;
   rmsnorm_fwd_kernel<<<static_cast<unsigned>(rows), kNormThreads, 0, st>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), rstd,
-      H, x_stride, y_stride, eps, zero_centered);
+      static_cast<const __nv_bfloat16*>(x), nullptr, static_cast<const __nv_bfloat16*>(w),
+      static_cast<__nv_bfloat16*>(y), nullptr, rstd, H, x_stride, 0, y_stride, 0, eps, zero_centered);
+  return -static_cast<int>(cudaGetLastError());
+}
+
+// s = x + delta (bf16, written to `sum`) and y = rmsnorm(s) in one pass; rstd is that of s.
+extern "C" int stb_add_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* y, void* sum, float* rstd,
+                                   long long rows, int H, long long x_stride, long long delta_stride,
+                                   long long y_stride, long long sum_stride, float eps, int zero_centered,
+                                   cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (H % 8 || delta == nullptr || sum == nullptr) return -kErrBadArgument;
+  rmsnorm_fwd_kernel<<<static_cast<unsigned>(rows), kNormThreads, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(delta),
+      static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(sum), rstd, H,
+      x_stride, delta_stride, y_stride, sum_stride, eps, zero_centered);
   return -static_cast<int>(cudaGetLastError());
 }
 
@@ -514,9 +571,27 @@ extern "C" int stb_rmsnorm_bwd(const void* x, const void* w, const void* g, cons
   rmsnorm_bwd_kernel<<<grid, kNormThreads, 0, st>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(g),
       rstd, static_cast<__nv_bfloat16*>(dx), dw_partial, static_cast<int>(rows), H, x_stride, g_stride, dx_stride,
-      zero_centered, add_to_dx);
+      zero_centered, add_to_dx ? static_cast<const __nv_bfloat16*>(dx) : nullptr, dx_stride);
   if (dw != nullptr)
-    rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, st>>>(dw_partial, dw, grid, H, accumulate_dw, H);
+    rmsnorm_dw_reduce_kernel<<<(H + 31) / 32, 32 * kDwReduceWarps, 0, st>>>(dw_partial, dw, grid, H, accumulate_dw, H);
+  return -static_cast<int>(cudaGetLastError());
+}
+
+// Backward of stb_add_rmsnorm_fwd: ds = dsum + rmsnorm_bwd(s, dy) is the gradient of both x and delta.
+// s is the saved sum; dsum the gradient that reached it along the residual stream.
+extern "C" int stb_add_rmsnorm_bwd(const void* s_in, const void* w, const void* g, const void* dsum, const float* rstd,
+                                   void* ds, float* dw, float* dw_partial, long long rows, int H, long long s_stride,
+                                   long long g_stride, long long dsum_stride, long long ds_stride, int zero_centered,
+                                   int accumulate_dw, cudaStream_t st) {
+  if (rows <= 0) return 0;
+  if (H % 8 || H > kNormThreads * 8 * kNormMaxVec || dsum == nullptr) return -kErrBadArgument;
+  const int grid = stb_rmsnorm_bwd_grid(rows);
+  rmsnorm_bwd_kernel<<<grid, kNormThreads, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(s_in), static_cast<const __nv_bfloat16*>(w),
+      static_cast<const __nv_bfloat16*>(g), rstd, static_cast<__nv_bfloat16*>(ds), dw_partial, static_cast<int>(rows), H,
+      s_stride, g_stride, ds_stride, zero_centered, static_cast<const __nv_bfloat16*>(dsum), dsum_stride);
+  if (dw != nullptr)
+    rmsnorm_dw_reduce_kernel<<<(H + 31) / 32, 32 * kDwReduceWarps, 0, st>>>(dw_partial, dw, grid, H, accumulate_dw, H);
   return -static_cast<int>(cudaGetLastError());
 }
 
@@ -553,9 +628,10 @@ extern "C" int stb_qknorm_rope_bwd(const void* qkv, const void* qw, const void* 
       qkv_stride, dqkv_stride, rot, use_norm, zero_centered);
   if (use_norm && dqw != nullptr) {
     // partial layout [grid][2][128]: first half of each row -> dqw, second half -> dkw
-    rmsnorm_dw_reduce_kernel<<<1, 128, 0, st>>>(dw_partial, dqw, grid, kHeadDim, accumulate_dw, 2 * kHeadDim);
-    rmsnorm_dw_reduce_kernel<<<1, 128, 0, st>>>(dw_partial + kHeadDim, dkw, grid, kHeadDim, accumulate_dw,
-                                                2 * kHeadDim);
+    rmsnorm_dw_reduce_kernel<<<kHeadDim / 32, 32 * kDwReduceWarps, 0, st>>>(dw_partial, dqw, grid, kHeadDim,
+                                                                            accumulate_dw, 2 * kHeadDim);
+    rmsnorm_dw_reduce_kernel<<<kHeadDim / 32, 32 * kDwReduceWarps, 0, st>>>(dw_partial + kHeadDim, dkw, grid, kHeadDim,
+                                                                            accumulate_dw, 2 * kHeadDim);
   }
   return -static_cast<int>(cudaGetLastError());
 }
@@ -660,7 +736,8 @@ extern "C" int stb_rmsnorm_bwd_noalloc(const void* x, const void* w, const void*
   rmsnorm_bwd_kernel<<<grid, kNormThreads, 0, st>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w), static_cast<const __nv_bfloat16*>(g),
       rstd, static_cast<__nv_bfloat16*>(dx), scratch, static_cast<int>(rows), H, x_stride, g_stride, dx_stride,
-      zero_centered, add_to_dx);
-  if (dw != nullptr) rmsnorm_dw_reduce_kernel<<<(H + 255) / 256, 256, 0, st>>>(scratch, dw, grid, H, accumulate_dw, H);
+      zero_centered, add_to_dx ? static_cast<const __nv_bfloat16*>(dx) : nullptr, dx_stride);
+  if (dw != nullptr)
+    rmsnorm_dw_reduce_kernel<<<(H + 31) / 32, 32 * kDwReduceWarps, 0, st>>>(scratch, dw, grid, H, accumulate_dw, H);
   return -static_cast<int>(cudaGetLastError());
 }

@@ -8,7 +8,7 @@ from __future__ import annotations
 import torch
 import torch.nn as nn
 
-from ...ops import rmsnorm
+from ...ops import add_rmsnorm, rmsnorm
 
 
 class RMSNorm(nn.Module):
@@ -25,3 +25,7 @@ class RMSNorm(nn.Module):
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         return rmsnorm(x, self.weight, self.eps, self.zero_centered)
+
+    def forward_with_residual(self, x: torch.Tensor, delta: torch.Tensor):
+        """``(x + delta, norm(x + delta))`` in one kernel: the residual add in front of this norm fused into it."""
+        return add_rmsnorm(x, delta, self.weight, self.eps, self.zero_centered)

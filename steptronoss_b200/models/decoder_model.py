@@ -12,6 +12,7 @@ import torch
 import torch.nn as nn
 
 from ..exp.base_exp import Megatron3DParallelModelConfig, MegatronTPConfig
+from ..ops import residual_add
 from ..parallel.random import checkpoint, get_rng_tracker
 from ..parallel.state import PM
 from ..utils.general import get_position_id_from_cu_seqlens, list_split
@@ -111,10 +112,13 @@ class TransformerBlock(nn.Module):
     def _body(self, x, position_id, cu_seqlens, max_seqlen, cp_meta):
         h = self._maybe("attn_norm", self.attention_norm, x)
         a = self._maybe("attention", lambda t: self.attention(t, position_id, cu_seqlens, max_seqlen, cp_meta), h)
-        x = x + a
-        h = self._maybe("ffn_norm", self.ffn_norm, x)
+        if "ffn_norm" in self.recompute and not self.recompute_all:
+            x = residual_add(x, a)
+            h = self._maybe("ffn_norm", self.ffn_norm, x)
+        else:
+            x, h = self.ffn_norm.forward_with_residual(x, a)   # x + a and its norm in one pass
         f = self._maybe("feed_forward", self.feed_forward, h)
-        return x + f
+        return residual_add(x, f)
 
     def forward(self, x, position_id=None, cu_seqlens=None, max_seqlen=None, cp_meta=None):
         if self.recompute_all and torch.is_grad_enabled() and x.requires_grad:

@@ -78,6 +78,100 @@ def rmsnorm(x, weight, eps: float = 1e-6, zero_centered: bool = False):
     return _RMSNormFn.apply(x, weight, eps, zero_centered)
 
 
+class _AddRMSNormFn(torch.autograd.Function):
+    """``s = x + delta`` and ``y = rmsnorm(s)`` in one kernel (the residual add of a pre-norm block and the norm
+    that follows it); backward adds the residual-stream gradient inside the norm's backward kernel."""
+
+    @staticmethod
+    def forward(ctx, x, delta, weight, eps, zero_centered):
+        lib = native.load()
+        H = x.shape[-1]
+        x2, d2 = x.reshape(-1, H), delta.reshape(-1, H)
+        if x2.stride(-1) != 1:
+            x2 = x2.contiguous()
+        if d2.stride(-1) != 1:
+            d2 = d2.contiguous()
+        rows = x2.shape[0]
+        y = torch.empty((rows, H), dtype=x.dtype, device=x.device)
+        s = torch.empty((rows, H), dtype=x.dtype, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        native.check(
+            lib.stb_add_rmsnorm_fwd(x2.data_ptr(), d2.data_ptr(), weight.data_ptr(), y.data_ptr(), s.data_ptr(),
+                                    rstd.data_ptr(), rows, H, x2.stride(0), d2.stride(0), y.stride(0), s.stride(0),
+                                    float(eps), int(zero_centered), native.stream()),
+            "add_rmsnorm_fwd")
+        count_launch()
+        ctx.save_for_backward(s, weight, rstd)
+        ctx.weight_ref = weight
+        ctx.zero_centered = zero_centered
+        ctx.in_shape = x.shape
+        return s.view(x.shape), y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, gs, gy):
+        lib = native.load()
+        s, weight, rstd = ctx.saved_tensors
+        rows, H = s.shape
+        g2, r2 = gy.reshape(rows, H), gs.reshape(rows, H)
+        if g2.stride(-1) != 1:
+            g2 = g2.contiguous()
+        if r2.stride(-1) != 1:
+            r2 = r2.contiguous()
+        ds = torch.empty_like(s)
+        grid = lib.stb_rmsnorm_bwd_grid(rows)
+        partial = torch.empty((grid, H), dtype=torch.float32, device=s.device)
+        main_grad = getattr(ctx.weight_ref, "main_grad", None)
+        if main_grad is not None:
+            dw_buf, acc = main_grad, 1
+        else:
+            dw_buf, acc = torch.empty(H, dtype=torch.float32, device=s.device), 0
+        native.check(
+            lib.stb_add_rmsnorm_bwd(s.data_ptr(), weight.data_ptr(), g2.data_ptr(), r2.data_ptr(), rstd.data_ptr(),
+                                    ds.data_ptr(), dw_buf.data_ptr(), partial.data_ptr(), rows, H, s.stride(0),
+                                    g2.stride(0), r2.stride(0), ds.stride(0), int(ctx.zero_centered), acc,
+                                    native.stream()),
+            "add_rmsnorm_bwd")
+        count_launch(2)
+        dw = None
+        if main_grad is None:
+            dw = dw_buf.to(weight.dtype)
+        else:
+            ctx.weight_ref.grad_added_to_main_grad = True
+        ds = ds.view(ctx.in_shape)
+        return ds, ds, dw, None, None
+
+
+def add_rmsnorm(x, delta, weight, eps: float = 1e-6, zero_centered: bool = False):
+    """``(x + delta, rmsnorm(x + delta))``: the residual stream and the input of the next sub-block."""
+    if not x.is_cuda or x.dtype != torch.bfloat16 or delta.dtype != x.dtype or delta.shape != x.shape:
+        s = x + delta
+        return s, rmsnorm(s, weight, eps, zero_centered)
+    return _AddRMSNormFn.apply(x, delta, weight, eps, zero_centered)
+
+
+class _AddFn(torch.autograd.Function):
+    """bf16 ``a + b`` on the native kernel (the residual add that has no norm behind it)."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        lib = native.load()
+        a2, b2 = a.contiguous(), b.contiguous()
+        out = torch.empty_like(a2)
+        native.check(lib.stb_add_bf16(a2.data_ptr(), b2.data_ptr(), out.data_ptr(), a2.numel(), native.stream()), "add")
+        count_launch()
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, g
+
+
+def residual_add(a, b):
+    if not a.is_cuda or a.dtype != torch.bfloat16 or b.dtype != a.dtype or a.shape != b.shape or a.numel() % 8:
+        return a + b
+    return _AddFn.apply(a, b)
+
+
 # --------------------------------------------------------------------------- QK-norm + RoPE
 def rope_tables(max_pos: int, rot_dim: int, theta: float, device, scaling=None):
     """fp32 cos/sin tables ``[max_pos, rot_dim/2]`` (kept fp32 whatever the model dtype, as the

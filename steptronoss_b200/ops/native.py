@@ -63,6 +63,8 @@ _SIGNATURES = {
     "stb_gemm_bf16_grouped_rows": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
     "stb_gemm_bf16_grouped_reduce": [P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
     "stb_rmsnorm_fwd": [P, P, P, P, L, I, L, L, F, I, P],
+    "stb_add_rmsnorm_fwd": [P, P, P, P, P, P, L, I, L, L, L, L, F, I, P],
+    "stb_add_rmsnorm_bwd": [P, P, P, P, P, P, P, P, L, I, L, L, L, L, I, I, P],
     "stb_rmsnorm_bwd_grid": [L],
     "stb_rmsnorm_bwd": [P, P, P, P, P, P, P, L, I, L, L, L, I, I, I, P],
     "stb_qknorm_rope_fwd": [P, P, P, P, P, P, P, P, P, I, I, I, I, L, I, F, I, I, P],

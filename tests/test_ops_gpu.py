@@ -222,3 +222,35 @@ def test_gemm_with_unaligned_row_pitch_uses_the_library(M, N, K):
     out = gemm(a, b)
     ref = a.float() @ b.float().t()
     assert out.shape == (M, N) and float((out.float() - ref).abs().max() / ref.abs().max()) < 2e-2
+
+
+@pytest.mark.parametrize("rows,H", [(37, 512), (300, 4096), (5, 8192)])
+def test_add_rmsnorm_matches_the_unfused_statement(rows, H):
+    """x + delta and its RMSNorm in one kernel: forward and backward against fp32 PyTorch on the bf16-rounded sum."""
+    from steptronoss_b200.ops import add_rmsnorm, residual_add
+
+    torch.manual_seed(0)
+    x = torch.randn(rows, H, device="cuda").to(torch.bfloat16).requires_grad_()
+    d = torch.randn(rows, H, device="cuda").to(torch.bfloat16).requires_grad_()
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).to(torch.bfloat16).requires_grad_()
+    s, y = add_rmsnorm(x, d, w, 1e-6, False)
+    s_ref = (x.detach() + d.detach())                                        # bf16 add
+    assert torch.equal(s, s_ref)
+    xs = s_ref.float().requires_grad_()
+    wf = w.detach().float().requires_grad_()
+    y_ref = xs * torch.rsqrt(xs.pow(2).mean(-1, keepdim=True) + 1e-6) * wf
+    assert float((y.float() - y_ref).abs().max()) < 3e-2
+    gs = torch.randn_like(s)
+    gy = torch.randn_like(y)
+    torch.autograd.backward([s, y], [gs, gy])
+    y_ref.backward(gy.float())
+    ds_ref = xs.grad + gs.float()
+    assert torch.equal(x.grad, d.grad)
+    assert float((x.grad.float() - ds_ref).abs().max() / ds_ref.abs().max()) < 2e-2
+    assert float((w.grad.float() - wf.grad).abs().max() / wf.grad.abs().max()) < 2e-2
+    a = torch.randn(64, 256, device="cuda").to(torch.bfloat16).requires_grad_()
+    b = torch.randn(64, 256, device="cuda").to(torch.bfloat16).requires_grad_()
+    out = residual_add(a, b)
+    assert torch.equal(out, a.detach() + b.detach())
+    out.sum().backward()
+    assert torch.equal(a.grad, torch.ones_like(a)) and torch.equal(b.grad, torch.ones_like(b))
