@@ -151,3 +151,54 @@ def test_simulator_orders_strategies_by_overlap():
     assert max(b.staleness for b in on.batches) == 0 and max(b.staleness for b in off.batches) <= 1
     assert all(b.staleness <= 2 + 2 for b in fa.batches)
     assert "Train:" in on.render() and "Infer:" in on.render()
+
+
+def test_simulator_records_blocks_snapshots_and_traces():
+    from steptronoss_b200.generators.flow_controller_simulator import (
+        FlowControllerSimulator, FlowControllerSimulatorCLI, simulate_flow_controller)
+
+    r = simulate_flow_controller("one-step-off", 3, 4, "1,2,3,1,2,3,1,2,3")
+    assert [b.required_version for b in r.blocks] == [0, 0, 1] and [b.prompt_count for b in r.blocks] == [3, 3, 3]
+    assert r.blocks[1].start_tick == 0                   # the second group is generated beside the first, on version 0
+    assert [s.yielded for s in r.snapshots] == [(0, 1, 2), (3, 4, 5), (6, 7, 8)]
+    assert all(t.end_tick - t.start_tick == t.cost for t in r.traces) and [t.step for t in r.traces] == [0] * 3 + [1] * 3 + [2] * 3
+    text = r.render()
+    assert "Yield 0 @t=3" in text and "Block 2: prompts [6, 7, 8] need version 1" in text and text.count("Yield") == 3
+    fa = simulate_flow_controller("fully-async", 2, 3, [1, 5, 1, 1, 1, 1], max_untrained_prompts=4, max_staleness=1,
+                                  max_concurrent=3)
+    # the long prompt is still running when the first batch is handed over: it shows up as truncated
+    assert fa.snapshots[0].running and fa.snapshots[0].running[0][0] == 1 and fa.max_staleness <= 2
+    assert "trunc[1(" in fa.render()
+    cfg = _cfg(FullyAsyncFlowControllerConfig, prompt_per_iter=4, max_untrained_prompts=2, max_staleness=1)
+    with pytest.raises(ValueError):
+        FlowControllerSimulator(cfg)
+    table = FlowControllerSimulatorCLI.compare(3, 4, "1,2,3,1,2,3,1,2,3")
+    assert [line.split()[0] for line in table.splitlines()] == ["on-policy", "one-step-off", "fully-async"]
+
+
+@pytest.mark.parametrize("strategy", ["on-policy", "one-step-off"])
+def test_runtime_controller_follows_the_simulated_schedule(strategy):
+    """The real controller, fed prompts whose generation takes their simulated cost in wall-clock ticks and a
+    trainer that sleeps ``train_cost`` ticks, hands out the batches the simulator predicts, generated on the
+    versions it predicts."""
+    from steptronoss_b200.generators.flow_controller_simulator import (
+        FlowControllerSimulator, SimulatedGenableItem, simulate_flow_controller)
+
+    costs, ppi, train_cost, tick = [1, 3, 2, 2, 1, 3, 3, 1, 2], 3, 4, 0.03
+    predicted = simulate_flow_controller(strategy, ppi, train_cost, costs)
+    cfg = _cfg(FlowControllerConfig, async_strategy=strategy, prompt_per_iter=ppi)
+    ctrl = SimpleFlowController(cfg, generator=SingleGenerationController())
+    ctrl.deploy_fn = _deploy(ctrl)
+    ctrl.poll_s = 0.002
+    old_tick, SimulatedGenableItem.tick_seconds = SimulatedGenableItem.tick_seconds, tick
+    try:
+        ctrl.start(FlowControllerSimulator.build_dataloader(costs), model=None)
+        for step, batch in enumerate(predicted.batches):
+            trajs = ctrl.get_train_samples()
+            assert sorted(t.meta["item_id"] for t in trajs) == sorted(batch.prompts)
+            time.sleep(train_cost * tick)
+            ctrl.weight_dumped()
+        # versions: on-policy never lags, one-step-off lags by exactly one from the second batch on
+        assert predicted.max_staleness == (0 if strategy == "on-policy" else 1)
+    finally:
+        SimulatedGenableItem.tick_seconds = old_tick
