@@ -52,6 +52,12 @@ class MoEConfig(Config):
     layer).  f >= 1: sized for f x (tokens x top-k) without a host read; a rank that receives more fails the step
     with a capacity error (nothing is dropped silently)."""
     recompute_experts: bool = False
+    detailed_router_metrics: bool = False
+    """Also fill ``router_logits_std`` and ``moe_minp / moe_sumk / moe_std / moe_avg`` (per-token statistics of the
+    router probabilities, as the reference logs them).  They are computed with ordinary tensor operations over the
+    ``[tokens, experts]`` probabilities, about ten small launches per layer and micro-batch, so they are a
+    diagnostic switch; ``router_logits_max``, ``moe_max`` and ``expert_coef`` come out of the fused router kernel
+    and are always filled."""
 
     def get_aux_loss_calib_scale(self):
         return 1
@@ -171,6 +177,16 @@ class MoEBlock(nn.Module):
             GlobalMetrics.router_logits_max.add(stats[0], subname=sub)
             GlobalMetrics.expert_coef.add(hist.max().float() / hist.sum().clamp_min(1).float(), subname=sub)
             GlobalMetrics.moe_max.add(stats[1], subname=sub)
+            if cfg.detailed_router_metrics:
+                lg = logits.detach().float()
+                prob = torch.sigmoid(lg) if cfg.enable_sigmoid_router else torch.softmax(lg, dim=1)
+                if cfg.enable_sigmoid_router:
+                    prob = prob / (prob.sum(-1, keepdim=True) + eps)
+                GlobalMetrics.router_logits_std.add(lg.std(1).mean(), subname=sub)
+                GlobalMetrics.moe_minp.add(prob.min(1).values.mean(), subname=sub)
+                GlobalMetrics.moe_sumk.add(prob.topk(self.top_k, dim=1).values.sum(1).mean(), subname=sub)
+                GlobalMetrics.moe_std.add(prob.std(1).mean(), subname=sub)
+                GlobalMetrics.moe_avg.add(prob.mean(1).mean(), subname=sub)
         return ids, weights, aux
 
     # ------------------------------------------------------------------ expert paths

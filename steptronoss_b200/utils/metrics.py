@@ -292,6 +292,87 @@ class TextMetric(Metric):
         return vals[: self.max_items] if self.max_items else vals
 
 
+class WithDataDumpOutlierMetric(Metric):
+    """Counts, and keeps the evidence of, values that stand out against the recent past (e.g. a loss spike).
+
+    ``add({"real_value": v, "data": payload})`` records one observation together with whatever is needed to
+    reproduce it (typically the micro-batch).  At reduction time the mean of the observations since the last
+    reduction joins a sliding window (``max_window_size`` reductions); once the window is full every observation
+    above the window's mean is an outlier: its payload is written to ``<outlier_data_dump_dir>/outlier_losses/``
+    and the metric's value is the number of outliers summed over the data-parallel ranks.  Counterpart of the
+    reference's metric of the same name (``steptronoss/utils/metrics.py:617-693``)."""
+
+    def __init__(self, name: str | None = None, reductions=None, sample_interval: int = 1, is_group: bool = False,
+                 max_window_size: int = 100, outlier_data_dump_dir: str | None = None) -> None:
+        super().__init__(name=name, reductions=reductions, sample_interval=sample_interval)
+        import collections
+        import os
+
+        if outlier_data_dump_dir is None:
+            raise ValueError("WithDataDumpOutlierMetric needs outlier_data_dump_dir")
+        self.window = collections.deque(maxlen=max_window_size)
+        self.pending: list = []          # (value, payload) since the last reduction
+        self.output_dir = os.path.join(outlier_data_dump_dir, "outlier_losses")
+        self.dumped: list = []           # paths written so far
+        os.makedirs(self.output_dir, exist_ok=True)
+
+    def add(self, value, subname: str | None = None, iop=None) -> None:  # type: ignore[override]
+        if not self.enabled:
+            return
+        if subname is not None:
+            raise ValueError("WithDataDumpOutlierMetric has no sub-metrics")
+        if callable(iop):
+            value = iop(value)
+        if not (isinstance(value, dict) and {"real_value", "data"} <= set(value)):
+            raise ValueError("expected {'real_value': number, 'data': payload}")
+        self.pending.append((float(value["real_value"]), value["data"]))
+
+    def _count_local_outliers(self) -> float:
+        import os
+
+        if not self.pending:
+            return 0.0
+        mean_now = sum(v for v, _ in self.pending) / len(self.pending)
+        if len(self.window) < self.window.maxlen:       # still learning what "normal" is
+            self.window.append(mean_now)
+            return 0.0
+        baseline = sum(self.window) / len(self.window)
+        count = 0
+        for i, (v, payload) in enumerate(self.pending):
+            if v > baseline:
+                path = os.path.join(self.output_dir, f"value{v:.6g}_n{len(self.dumped)}.pt")
+                torch.save({"real_value": v, "baseline": baseline, "data": payload}, path)
+                self.dumped.append(path)
+                count += 1
+        self.window.append(mean_now)
+        return float(count)
+
+    def reduce(self):
+        local = torch.tensor(self._count_local_outliers())
+        return _reduce_group(local, "dp", "sum")
+
+    def reset(self) -> None:
+        self.pending = []
+
+
+class DummyMetric:
+    """Accepts and forgets: what ``GlobalMetrics.<unregistered name>`` resolves to."""
+
+    enabled = False
+
+    def add(self, *args, **kwargs) -> None:
+        pass
+
+    def reduce(self):
+        return None
+
+    def reset(self) -> None:
+        pass
+
+
+dummy_metric = DummyMetric()
+
+
 class MetricHolder:
     """Registry reachable as ``GlobalMetrics.<name>``; unknown names resolve to a disabled sink so
     that model code can record metrics that an experiment did not register."""
@@ -299,7 +380,7 @@ class MetricHolder:
     def __init__(self) -> None:
         object.__setattr__(self, "metrics", {})
         object.__setattr__(self, "_disabled", False)
-        object.__setattr__(self, "_sink", _Sink())
+        object.__setattr__(self, "_sink", dummy_metric)
 
     def register(self, name: str, metric: Metric) -> None:
         metric.name = name
@@ -368,11 +449,6 @@ class MetricHolder:
                 m.values = saved.get(k, [])
                 if isinstance(m, GroupMetric):
                     m.sub = saved_sub.get(k, {})
-
-
-class _Sink:
-    def add(self, *a, **k):
-        pass
 
 
 GlobalMetrics = MetricHolder()

@@ -161,3 +161,28 @@ def test_zero_centred_norm_weight_and_clamped_swiglu():
     g, u = torch.tensor([7.0, -10.0, 1.0]), torch.tensor([7.0, -7.0, 2.0])       # gate capped above, up on both sides
     assert torch.allclose(out, torch.nn.functional.silu(g) * u)
     assert not torch.allclose(out, swiglu_reference(h))
+
+
+def test_detailed_router_metrics_are_filled_when_asked_for():
+    from steptronoss_b200.utils.metrics import GlobalMetrics, Metric
+
+    names = ("router_logits_max", "router_logits_std", "moe_minp", "moe_sumk", "moe_std", "moe_avg", "moe_max",
+             "expert_coef")
+    for n in names:
+        GlobalMetrics.register(n, Metric(is_group=True).mean("time"))
+    try:
+        blk = _build_block()
+        blk.cfg.detailed_router_metrics = True
+        x = _inputs()
+        logits = blk.gate(x)
+        blk.forward_router(logits)
+        got = GlobalMetrics.reduce_all()
+        prob = torch.softmax(logits.float(), dim=1)
+        key = lambda n: next(k for k in got if k.startswith(n))
+        assert abs(float(got[key("moe_avg")]) - 1.0 / prob.shape[1]) < 1e-6            # softmax rows sum to one
+        assert abs(float(got[key("moe_minp")]) - float(prob.min(1).values.mean())) < 1e-6
+        assert abs(float(got[key("moe_sumk")]) - float(prob.topk(2, dim=1).values.sum(1).mean())) < 1e-6
+        assert abs(float(got[key("router_logits_std")]) - float(logits.float().std(1).mean())) < 1e-5
+        assert float(got[key("moe_max")]) >= float(got[key("moe_minp")])
+    finally:
+        GlobalMetrics.clear()

@@ -195,3 +195,28 @@ def test_dialog_types_and_validation():
     probs = validate_dialog(bad)
     assert len(probs) == 5 and any("robot" in p for p in probs) and any("no assistant turn" in p for p in probs)
     assert validate_dialog({}) == ["'conversations' must be a non-empty list"]
+
+
+def test_outlier_metric_dumps_the_data_of_values_above_the_recent_mean(tmp_path):
+    import torch
+
+    from steptronoss_b200.utils.metrics import DummyMetric, GlobalMetrics, WithDataDumpOutlierMetric, dummy_metric
+
+    m = WithDataDumpOutlierMetric(max_window_size=3, outlier_data_dump_dir=str(tmp_path))
+    for step in range(3):                                   # the window fills: nothing is an outlier yet
+        m.add({"real_value": 1.0 + 0.01 * step, "data": {"step": step}})
+        assert float(m.reduce()) == 0.0
+        m.reset()
+    m.add({"real_value": 0.9, "data": {"step": 3}})
+    m.add({"real_value": 5.0, "data": {"step": 4, "ids": torch.arange(3)}})
+    assert float(m.reduce()) == 1.0 and len(m.dumped) == 1
+    saved = torch.load(m.dumped[0], weights_only=False)
+    assert saved["real_value"] == 5.0 and saved["data"]["step"] == 4 and saved["data"]["ids"].tolist() == [0, 1, 2]
+    m.reset()
+    assert float(m.reduce()) == 0.0
+    import pytest
+
+    with pytest.raises(ValueError):
+        m.add({"value": 1})
+    assert isinstance(dummy_metric, DummyMetric) and GlobalMetrics.some_metric_nobody_registered is dummy_metric
+    dummy_metric.add(1, subname="x")
