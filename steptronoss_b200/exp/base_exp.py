@@ -233,8 +233,9 @@ class MegatronTPConfig(AbstractModelConfig):
 class MegatronPPModelConfig(AbstractModelConfig):
     params_dtype: torch.dtype = torch.bfloat16
     overlap_p2p_comm: bool = True
-    """accepted for compatibility: the interleaved schedule here always pairs a send with the receive it can overlap
-    in one batched exchange per step and waits for it before the next compute, whatever this says"""
+    """Pipeline sends that are not paired with a receive (warm-up forwards, cool-down gradients) are left in flight
+    on NCCL's stream instead of being waited for, so the next micro-batch's compute starts at once; exchanges that
+    receive stay one batched send+receive per step and are waited for (``parallel/pipeline/p2p.py``)."""
     variable_seq_lengths: bool = False
     pp_comm_shape: tuple | None = None
     check_nan: bool = False

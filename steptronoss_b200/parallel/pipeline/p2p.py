@@ -5,6 +5,14 @@ stays on NCCL send/recv (it is latency-tolerant and overlaps with compute); the 
 operations post every send and receive of one step as a single batch.  With
 ``variable_seq_lengths`` the shape is exchanged first (three int64: ndim-padded dims).
 Receives are posted on the current stream; the tensors are safe to use once ``wait`` returned.
+
+``overlap`` (the reference's ``overlap_p2p_comm``): a batch that only *sends* is not waited for.  NCCL runs the
+transfer on its own stream behind the kernel that produced the tensor, so without the wait the compute stream
+goes straight on with the next micro-batch while the activation (or gradient) is on its way; the tensor is kept
+alive until the transfer has finished (``P2P.drain`` at the end of a schedule, or as the list of transfers in
+flight grows).  Batches that receive are always waited for, because their result is the next kernel's input,
+and a send stays in the same batch as the receive it is paired with: NCCL matches the two directions between a
+pair of ranks inside one group, and splitting them can deadlock.
 """
 from __future__ import annotations
 
@@ -90,8 +98,34 @@ def communicate(send_next=None, send_prev=None, recv_prev: bool = False, recv_ne
 class P2P:
     """The nine send/recv combinations of the reference, bound to one shape/dtype policy."""
 
-    def __init__(self, tensor_shape=None, dtype=torch.bfloat16, variable_seq_lengths=False):
+    MAX_IN_FLIGHT = 8
+
+    def __init__(self, tensor_shape=None, dtype=torch.bfloat16, variable_seq_lengths=False, overlap: bool = False):
         self.kw = dict(tensor_shape=tensor_shape, dtype=dtype, variable_seq_lengths=variable_seq_lengths)
+        self.overlap = bool(overlap)
+        self._in_flight: list = []          # (requests, tensors kept alive) of sends nobody waited for yet
+
+    def _send_only(self, **sends) -> None:
+        if not self.overlap:
+            communicate(**sends, **self.kw)
+            return
+        # an alias of its own: the schedule frees an output's storage right after sending it (by re-pointing
+        # ``out.data``), which must not pull the buffer from under a transfer that is still running
+        sends = {k: t.detach() for k, t in sends.items() if t is not None}
+        _, _, reqs = communicate(wait=False, **sends, **self.kw)
+        self._in_flight.append((reqs, list(sends.values())))
+        if len(self._in_flight) > self.MAX_IN_FLIGHT:
+            self._reap(len(self._in_flight) - self.MAX_IN_FLIGHT)
+
+    def _reap(self, count: int) -> None:
+        for reqs, _tensors in self._in_flight[:count]:
+            for r in reqs:
+                r.wait()
+        del self._in_flight[:count]
+
+    def drain(self) -> None:
+        """Wait for every send that was left in flight (end of a schedule: buffers are about to be reused)."""
+        self._reap(len(self._in_flight))
 
     def recv_forward(self):
         if PM.is_pipeline_first_stage(ignore_virtual=True):
@@ -105,11 +139,11 @@ class P2P:
 
     def send_forward(self, out):
         if not PM.is_pipeline_last_stage(ignore_virtual=True):
-            communicate(send_next=out, **self.kw)
+            self._send_only(send_next=out)
 
     def send_backward(self, grad):
         if not PM.is_pipeline_first_stage(ignore_virtual=True):
-            communicate(send_prev=grad, **self.kw)
+            self._send_only(send_prev=grad)
 
     def send_forward_recv_backward(self, out):
         if PM.is_pipeline_last_stage(ignore_virtual=True):

@@ -125,7 +125,7 @@ class PPScheduler(FWBWScheduler):
     def _p2p(self) -> P2P:
         c = self.config
         return P2P(tensor_shape=tuple(c.pp_comm_shape) if not c.variable_seq_lengths else None, dtype=c.params_dtype,
-                   variable_seq_lengths=c.variable_seq_lengths)
+                   variable_seq_lengths=c.variable_seq_lengths, overlap=bool(getattr(c, "overlap_p2p_comm", False)))
 
     def run(self, forward_num: int = 1):
         self._collected.clear()
@@ -181,6 +181,7 @@ class PPScheduler(FWBWScheduler):
                 grad = p2p.recv_backward()
                 gin = self._backward(i0, o0, grad)
                 p2p.send_backward(gin)
+        p2p.drain()
         self._prefetched = None
         return self._collected
 
@@ -306,6 +307,7 @@ class VPPScheduler(PPScheduler):
                 recv_next = not (last_rank and nb == C - 1) and k != total - 1
                 grad = p2p.send_backward_recv_backward(gin, recv_next)
                 out_grads[nb].append(grad)
+        p2p.drain()
         PM.set_vpp_rank(0)
         self._prefetched = None
         return self._collected
