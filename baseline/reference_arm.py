@@ -233,15 +233,37 @@ def _run(args) -> None:
     if sampler:
         sampler.start()
     barrier_sync()
+    # STB200_REF_CPROFILE=1: run the timed steps under cProfile on rank 0 and report which share of the host time
+    # is spent inside the stand-in for `configurize` (this repository's config tree), i.e. how much the stand-in
+    # could distort the reference's number.  Off by default: profiling slows the host down.
+    profiler = None
+    if os.environ.get("STB200_REF_CPROFILE") == "1" and rank == 0:
+        import cProfile
+
+        profiler = cProfile.Profile()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     e0.record()
+    if profiler is not None:
+        profiler.enable()
     for _ in range(args.steps):
         step()
+    if profiler is not None:
+        profiler.disable()
     e1.record()
     barrier_sync()
     wall = (time.perf_counter() - t0) * 1e3
     ms = e0.elapsed_time(e1)
+    shim_share = None
+    if profiler is not None:
+        import pstats
+
+        stats = pstats.Stats(profiler)
+        total = sum(v[2] for v in stats.stats.values())                       # tottime over all functions
+        in_shim = sum(v[2] for (fname, _, _), v in stats.stats.items()
+                      if "steptronoss_b200/config/" in fname.replace(os.sep, "/") or "/shims/configurize/" in fname.replace(os.sep, "/"))
+        shim_share = {"host_seconds_profiled": total, "seconds_in_config_stand_in": in_shim,
+                      "share": in_shim / total if total else 0.0}
     clocks = sampler.stop() if sampler else None
     t = torch.tensor([ms, wall], dtype=torch.float64, device="cuda")
     if dist.is_initialized():
@@ -287,6 +309,9 @@ def _run(args) -> None:
         "e2e": {"value": e2e, "unit": "tokens/s", "ms_per_step": max(ms, wall) / args.steps},
         "impl": "reference",
     }
+    if shim_share is not None:
+        out["config_stand_in_profile"] = shim_share
+        out["invalid_profiled_run"] = True      # a number taken under a profiler is not a benchmark value
     if args.debug_layers:
         out["invalid_debug_config"] = True
     print(json.dumps(out), flush=True)

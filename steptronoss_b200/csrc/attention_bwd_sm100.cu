@@ -174,8 +174,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
   if (warp == 0) {
     if (lane == 0 && iters > 0) {
       mbar_arrive_expect_tx(f_full, 2 * kTileBytes);
-      load_tile(sF1, &tmap_f1, f_full, head_f, row_abs0);
-      load_tile(sF2, &tmap_f2, f_full, head_f, row_abs0);
+      const int f_row = DKV ? key_row(p, row_abs0) : row_abs0;   // fixed rows are keys in the dK/dV pass
+      load_tile(sF1, &tmap_f1, f_full, head_f, f_row);
+      load_tile(sF2, &tmap_f2, f_full, head_f, f_row);
       for (int it = 0; it < iters && !*abort_flag; ++it) {
         const int st = it % kBwdStages;
         if (!mbar_wait(&g_empty[st], ((it / kBwdStages) & 1) ^ 1)) {
@@ -184,7 +185,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
           break;
         }
         const int hg = DKV ? kvh * group + split * gps + it / nsb : kvh;
-        const int grow = (DKV ? s.q_begin : s.k_begin) + (sb0 + it % nsb) * kSB;
+        const int grow = DKV ? s.q_begin + (sb0 + it % nsb) * kSB : key_row(p, s.k_begin + (sb0 + it % nsb) * kSB);
         uint8_t* g1 = sG + st * 2 * kStreamTile;
         mbar_arrive_expect_tx(&g_full[st], 2 * kStreamTile);
         load_stream_tile(g1, &tmap_g1, &g_full[st], hg, grow);
@@ -241,7 +242,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
     float row_lse2 = 0.f, row_delta = 0.f;
     bool frow_ok;
     if (DKV) {
-      frow_ok = fi < s.k_len;
+      // keys in front of the document (context parallelism: the range starts at a tile boundary) belong to another
+      // segment, whose CTA writes their gradients
+      frow_ok = fi < s.k_len && fi >= s.k_skip;
     } else {
       const long long q_abs = static_cast<long long>(row_abs0) + r;
       frow_ok = (fi < s.q_len) && (q_abs < p.total_q);
@@ -285,11 +288,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
       // does any (fixed row, streamed row) pair of this tile fall outside the mask?
       bool need_mask;
       if (DKV) {
-        need_mask = (f0 + kBN > s.k_len) || (g0 + kSB > s.q_len) || (p.causal && f0 + kBN - 1 > g0 + s.off) ||
-                    (p.window > 0 && f0 <= g0 + kSB - 1 + s.off - p.window);
+        need_mask = (f0 + kBN > s.k_len) || (f0 < s.k_skip) || (g0 + kSB > s.q_len) ||
+                    (p.causal && f0 + kBN - 1 > g0 + s.off) || (p.window > 0 && f0 <= g0 + kSB - 1 + s.off - p.window);
       } else {
-        need_mask = (f0 + kBM > s.q_len) || (g0 + kSB > s.k_len) || (p.causal && g0 + kSB - 1 > f0 + s.off) ||
-                    (p.window > 0 && g0 <= f0 + kBM - 1 + s.off - p.window);
+        need_mask = (f0 + kBM > s.q_len) || (g0 + kSB > s.k_len) || (g0 < s.k_skip) ||
+                    (p.causal && g0 + kSB - 1 > f0 + s.off) || (p.window > 0 && g0 <= f0 + kBM - 1 + s.off - p.window);
       }
       uint8_t* pP = sP + buf * 2 * kPTile;
       uint8_t* pdS = pP + kPTile;
@@ -315,7 +318,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
     if (ok && iters > 0 && !*abort_flag) ok = mbar_wait(acc_full, 0);
     if (!ok) { report_error(p.status, kErrSoftmaxWait); *abort_flag = 1; }
     if (iters > 0) tc_fence_after();
-    const long long f_abs = static_cast<long long>(row_abs0) + r;
+    const long long f_abs = static_cast<long long>(DKV ? key_row(p, row_abs0) : row_abs0) + r;
     const bool store_ok = DKV ? (frow_ok && f_abs < p.total_k) : frow_ok;
 #pragma unroll 1
     for (int which = 0; which < (DKV ? 2 : 1); ++which) {
@@ -438,6 +441,7 @@ extern "C" int stb_attn_bwd(const void* q, const void* k, const void* v, const v
                             const int* k_blk_seg, const int* k_blk_row0, int num_k_blocks, int total_q, int total_k,
                             int hq, int hkv, int head_dim, long long q_stride, long long k_stride, long long v_stride,
                             long long dv_stride, int causal, int window, float scale, float* dkv_part, int splits,
+                            const int* seg_k_begin, const int* seg_k_len, const int* seg_k_skip, int cp, int chunk_len,
                             int* status, cudaStream_t st) {
   if (total_q <= 0 || total_k <= 0) return 0;
   if (head_dim != kD || hq % hkv) return -kErrBadArgument;
@@ -472,6 +476,11 @@ extern "C" int stb_attn_bwd(const void* q, const void* k, const void* v, const v
   p.dQ = static_cast<__nv_bfloat16*>(dq); p.dK = static_cast<__nv_bfloat16*>(dk);
   p.dV = static_cast<__nv_bfloat16*>(dv); p.dv_stride = dv_stride; p.status = status;
   p.dkv_part = dkv_part; p.splits = splits;
+  if (seg_k_begin != nullptr) {
+    if (cp < 1 || chunk_len <= 0 || (chunk_len % kBN) || seg_k_len == nullptr || seg_k_skip == nullptr)
+      return -kErrBadArgument;
+    p.seg_k_begin = seg_k_begin; p.seg_k_len = seg_k_len; p.seg_k_skip = seg_k_skip; p.cp = cp; p.chunk_len = chunk_len;
+  }
   // dK / dV: fixed = (K, V) of a kv head, streamed = (Q, dO) of the group's q heads
   p.blk_seg = k_blk_seg; p.blk_row0 = k_blk_row0;
   if (num_k_blocks > 0) {

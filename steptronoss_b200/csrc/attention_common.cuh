@@ -37,6 +37,14 @@ struct AttnParams {
   // fp32 partials [split][dV, dK][Tk][hkv][D], summed in split order by a second kernel
   float* dkv_part;
   int splits;
+  // Keys addressed by their global position (context parallelism): the K / V (and dK / dV) rows live in a
+  // rank-major buffer [cp][2 * chunk_len] that holds every rank's two load-balanced chunks, and per-segment tables
+  // replace cu_k.  A segment's key range starts at a multiple of 128 at or before its document, so that no
+  // 128-key tile straddles two chunks; the keys in front of the document are masked (seg_k_skip of them).
+  const int* seg_k_begin;  // global position of the first key row of the range (multiple of 128)
+  const int* seg_k_len;    // rows from seg_k_begin to the segment's last key
+  const int* seg_k_skip;   // leading rows of the range that belong to an earlier document
+  int cp, chunk_len;       // chunk_len == 0: keys are addressed by plain row numbers
 };
 
 // 128-byte-swizzled address of (row, 16-byte chunk) inside a [128][64 bf16] slab.
@@ -63,17 +71,34 @@ __device__ __forceinline__ void load_tile(void* dst, const CUtensorMap* m, uint6
 }
 
 struct SegInfo {
-  int q_begin, q_len, k_begin, k_len, off;
+  int q_begin, q_len, k_begin, k_len, off, k_skip;
 };
 
 __device__ __forceinline__ SegInfo seg_info(const AttnParams& p, int seg) {
   SegInfo s;
   s.q_begin = p.cu_q[seg];
   s.q_len = p.cu_q[seg + 1] - s.q_begin;
-  s.k_begin = p.cu_k[seg];
-  s.k_len = p.cu_k[seg + 1] - s.k_begin;
+  if (p.seg_k_begin != nullptr) {
+    s.k_begin = p.seg_k_begin[seg];
+    s.k_len = p.seg_k_len[seg];
+    s.k_skip = p.seg_k_skip[seg];
+  } else {
+    s.k_begin = p.cu_k[seg];
+    s.k_len = p.cu_k[seg + 1] - s.k_begin;
+    s.k_skip = 0;
+  }
   s.off = s.k_len - s.q_len;
   return s;
+}
+
+// Row of the K / V buffer that holds global key position g.  Load-balanced context parallelism cuts the sequence
+// into 2*cp chunks and gives rank r the chunks r and 2*cp-1-r; the buffer stores rank after rank.  g is a multiple
+// of 64 and chunk_len a multiple of 128, so a 64- or 128-row tile starting at g stays inside one chunk.
+__device__ __forceinline__ int key_row(const AttnParams& p, int g) {
+  if (p.chunk_len == 0) return g;
+  const int c = g / p.chunk_len, in_chunk = g - c * p.chunk_len;
+  const int rank = c < p.cp ? c : 2 * p.cp - 1 - c;
+  return rank * 2 * p.chunk_len + (c < p.cp ? 0 : p.chunk_len) + in_chunk;
 }
 
 // key-block range [jb0, jb1) visible to q rows [q0, q0+128) of a segment (relative indices)
@@ -88,7 +113,7 @@ __device__ __forceinline__ void kv_range(const AttnParams& p, const SegInfo& s, 
 }
 
 __device__ __forceinline__ bool visible(const AttnParams& p, const SegInfo& s, int qi, int kk) {
-  bool ok = (kk < s.k_len) && (qi < s.q_len);
+  bool ok = (kk < s.k_len) && (kk >= s.k_skip) && (qi < s.q_len);
   if (p.causal) ok = ok && (kk <= qi + s.off);
   if (p.window > 0) ok = ok && (kk > qi + s.off - p.window);
   return ok;

@@ -95,7 +95,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
           break;
         }
         mbar_arrive_expect_tx(&kv_full[st], 2 * kTileBytes);
-        const int krow = s.k_begin + (jb0 + j) * kBN;
+        const int krow = key_row(p, s.k_begin + (jb0 + j) * kBN);
         load_tile(sKV + st * 2 * kTileBytes, &tmap_k, &kv_full[st], kvh, krow);
         load_tile(sKV + st * 2 * kTileBytes + kTileBytes, &tmap_v, &kv_full[st], kvh, krow);
       }
@@ -158,7 +158,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const int kb = (jb0 + j) * kBN + half * 64;  // first key of this thread's 64 columns
       // a tile needs element masks when it touches the diagonal, the window edge or the segment end
       const int kt = (jb0 + j) * kBN;
-      const bool need_mask = (kt + kBN > s.k_len) || (p.causal && kt + kBN - 1 > q0 + s.off) ||
+      const bool need_mask = (kt + kBN > s.k_len) || (kt < s.k_skip) || (p.causal && kt + kBN - 1 > q0 + s.off) ||
                              (p.window > 0 && kt <= q0 + kBM - 1 + s.off - p.window) || (q0 + kBM > s.q_len);
       uint32_t v[64];
 #pragma unroll
@@ -293,10 +293,14 @@ using namespace stb;
 
 // q [Tq][hq][D] with row stride q_stride (elements); k, v [Tk][hkv][D] with row strides k_stride, v_stride.
 // blk_seg / blk_row0: schedule of q blocks (num_blocks entries, seg < 0 = unused).
+// seg_k_begin / seg_k_len / seg_k_skip (optional, with cp and chunk_len): keys addressed by global position in a
+// rank-major [cp][2*chunk_len] buffer, see AttnParams; cu_k is then unused.
 extern "C" int stb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* cu_q,
                             const int* cu_k, const int* blk_seg, const int* blk_row0, int num_blocks, int total_q,
                             int total_k, int hq, int hkv, int head_dim, long long q_stride, long long k_stride,
-                            long long v_stride, int causal, int window, float scale, int* status, cudaStream_t st) {
+                            long long v_stride, int causal, int window, float scale, const int* seg_k_begin,
+                            const int* seg_k_len, const int* seg_k_skip, int cp, int chunk_len, int* status,
+                            cudaStream_t st) {
   if (num_blocks <= 0 || total_q <= 0) return 0;
   if (head_dim != kD || hq % hkv) return -kErrBadArgument;
   CUtensorMap tq, tk, tv;
@@ -315,6 +319,11 @@ extern "C" int stb_attn_fwd(const void* q, const void* k, const void* v, void* o
   p.hq = hq; p.hkv = hkv; p.causal = causal; p.window = window; p.scale = scale;
   p.total_q = total_q; p.total_k = total_k;
   p.O = static_cast<__nv_bfloat16*>(o); p.LSE = lse; p.status = status;
+  if (seg_k_begin != nullptr) {
+    if (cp < 1 || chunk_len <= 0 || (chunk_len % kBN) || seg_k_len == nullptr || seg_k_skip == nullptr)
+      return -kErrBadArgument;
+    p.seg_k_begin = seg_k_begin; p.seg_k_len = seg_k_len; p.seg_k_skip = seg_k_skip; p.cp = cp; p.chunk_len = chunk_len;
+  }
   attn_fwd_kernel<<<dim3(hq, num_blocks), kFwdThreads, kFwdSmem, st>>>(tq, tk, tv, p);
   return -static_cast<int>(cudaGetLastError());
 }

@@ -75,7 +75,7 @@ class _FlashAttnFn(torch.autograd.Function):
         qs, qr, nq = _schedule(cu_q, Tq)
         rc = lib.stb_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), cu_q.data_ptr(),
                               cu_k.data_ptr(), qs.data_ptr(), qr.data_ptr(), nq, Tq, Tk, hq, hkv, D, q.stride(0),
-                              k.stride(0), v.stride(0), int(causal), int(window), float(scale),
+                              k.stride(0), v.stride(0), int(causal), int(window), float(scale), None, None, None, 0, 0,
                               native.status_word(q.device).data_ptr(), native.stream())
         native.check(rc, "attention forward")
         count_launch()
@@ -104,11 +104,84 @@ class _FlashAttnFn(torch.autograd.Function):
                               delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), cu_q.data_ptr(),
                               cu_k.data_ptr(), qs.data_ptr(), qr.data_ptr(), nq, ks.data_ptr(), kr.data_ptr(), nk, Tq, Tk,
                               hq, hkv, D, q.stride(0), k.stride(0), v.stride(0), dv.stride(0), int(causal), int(window),
-                              float(scale), native.ptr(part), splits, native.status_word(q.device).data_ptr(),
-                              native.stream())
+                              float(scale), native.ptr(part), splits, None, None, None, 0, 0,
+                              native.status_word(q.device).data_ptr(), native.stream())
         native.check(rc, "attention backward")
         count_launch(3 + (splits > 1))
         return dq, dk, dv, None, None, None, None, None
+
+
+# --------------------------------------------------------------------------- keys addressed by global position
+class GatheredKeyPlan:
+    """Segments of one call whose keys live in a rank-major ``[cp][2*chunk_len]`` buffer (context parallelism).
+
+    ``pieces``: list of ``(q_begin, q_end, k_begin)`` in *global* positions, one per document piece of the local q
+    rows of this call (``k_end == q_end``); ``q_local0``: global position of the call's first q row.  Device
+    tables are built once per micro-batch and shared by all layers."""
+
+    def __init__(self, pieces, cp: int, chunk_len: int, device):
+        self.cp, self.chunk_len = cp, chunk_len
+        q_lens = [qe - qs for qs, qe, _ in pieces]
+        k_begin = [ks // _BLOCK * _BLOCK for _, _, ks in pieces]
+        k_skip = [ks - kb for (_, _, ks), kb in zip(pieces, k_begin)]
+        k_len = [qe - kb for (_, qe, _), kb in zip(pieces, k_begin)]
+        i32 = dict(dtype=torch.int32, device=device)
+        self.cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0).tolist()), **i32)
+        self.seg_k_begin = torch.tensor(k_begin, **i32)
+        self.seg_k_len = torch.tensor(k_len, **i32)
+        self.seg_k_skip = torch.tensor(k_skip, **i32)
+        # q-block schedule from cu_q; key-block schedule: 128-row blocks of every segment's key range (global rows)
+        self.q_sched = _schedule(self.cu_q, sum(q_lens))
+        seg, row0 = [], []
+        for i, (kb, kl) in enumerate(zip(k_begin, k_len)):
+            for b in range((kl + _BLOCK - 1) // _BLOCK):
+                seg.append(i)
+                row0.append(kb + b * _BLOCK)
+        self.k_blk_seg = torch.tensor(seg, **i32)
+        self.k_blk_row0 = torch.tensor(row0, **i32)
+        self.num_k_blocks = len(seg)
+
+
+def gathered_attention_fwd(q, k_buf, v_buf, plan: GatheredKeyPlan, causal: bool, window: int, scale: float):
+    """Forward over keys addressed by global position; returns ``(o, lse)``.  ``k_buf`` / ``v_buf``: ``[cp*2L,hkv,D]``."""
+    lib = native.load()
+    Tq, hq, D = q.shape
+    Tk, hkv, _ = k_buf.shape
+    o = torch.empty((Tq, hq, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((hq, Tq), dtype=torch.float32, device=q.device)
+    qs, qr, nq = plan.q_sched
+    rc = lib.stb_attn_fwd(q.data_ptr(), k_buf.data_ptr(), v_buf.data_ptr(), o.data_ptr(), lse.data_ptr(),
+                          plan.cu_q.data_ptr(), None, qs.data_ptr(), qr.data_ptr(), nq, Tq, Tk, hq, hkv, D, q.stride(0),
+                          k_buf.stride(0), v_buf.stride(0), int(causal), int(window), float(scale),
+                          plan.seg_k_begin.data_ptr(), plan.seg_k_len.data_ptr(), plan.seg_k_skip.data_ptr(), plan.cp,
+                          plan.chunk_len, native.status_word(q.device).data_ptr(), native.stream())
+    native.check(rc, "attention forward (gathered keys)")
+    count_launch()
+    return o, lse
+
+
+def gathered_attention_bwd(q, k_buf, v_buf, o, do, lse, plan: GatheredKeyPlan, causal: bool, window: int, scale: float,
+                           dk_buf, dv_buf):
+    """Backward: returns ``dq``; writes this call's dK / dV into the rows of ``dk_buf`` / ``dv_buf`` (rank-major, like
+    the key buffers) that its segments cover, leaving every other row untouched."""
+    lib = native.load()
+    Tq, hq, D = q.shape
+    Tk, hkv, _ = k_buf.shape
+    dq = torch.empty((Tq, hq, D), dtype=q.dtype, device=q.device)
+    delta = torch.empty((hq, Tq), dtype=torch.float32, device=q.device)
+    qs, qr, nq = plan.q_sched
+    splits = _FORCE_SPLITS or lib.stb_attn_bwd_splits(hq, hkv, plan.num_k_blocks)
+    part = torch.zeros((splits, 2, Tk, hkv, D), dtype=torch.float32, device=q.device) if splits > 1 else None
+    rc = lib.stb_attn_bwd(q.data_ptr(), k_buf.data_ptr(), v_buf.data_ptr(), o.data_ptr(), do.data_ptr(), lse.data_ptr(),
+                          delta.data_ptr(), dq.data_ptr(), dk_buf.data_ptr(), dv_buf.data_ptr(), plan.cu_q.data_ptr(),
+                          None, qs.data_ptr(), qr.data_ptr(), nq, plan.k_blk_seg.data_ptr(), plan.k_blk_row0.data_ptr(),
+                          plan.num_k_blocks, Tq, Tk, hq, hkv, D, q.stride(0), k_buf.stride(0), v_buf.stride(0),
+                          dv_buf.stride(0), int(causal), int(window), float(scale), native.ptr(part), splits,
+                          plan.seg_k_begin.data_ptr(), plan.seg_k_len.data_ptr(), plan.seg_k_skip.data_ptr(), plan.cp,
+                          plan.chunk_len, native.status_word(q.device).data_ptr(), native.stream())
+    native.check(rc, "attention backward (gathered keys)")
+    count_launch(3 + (splits > 1))
+    return dq
 
 
 def flash_attention(q, k, v, cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen=None, causal=True, window=0, scale=None):

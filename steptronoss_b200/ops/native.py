@@ -94,8 +94,8 @@ _SIGNATURES = {
     "stb_scale_f32": [P, L, F, P],
     "stb_nonfinite_flag": [P, L, P, P],
     "stb_gae": [P, P, P, I, F, F, P, P, P],
-    "stb_attn_fwd": [P] * 9 + [I] * 6 + [L] * 3 + [I, I, F, P, P],
-    "stb_attn_bwd": [P] * 14 + [I] + [P] * 2 + [I] * 6 + [L] * 4 + [I, I, F, P, I, P, P],
+    "stb_attn_fwd": [P] * 9 + [I] * 6 + [L] * 3 + [I, I, F, P, P, P, I, I, P, P],
+    "stb_attn_bwd": [P] * 14 + [I] + [P] * 2 + [I] * 6 + [L] * 4 + [I, I, F, P, I, P, P, P, I, I, P, P],
     "stb_attn_bwd_splits": [I, I, I],
 }
 

@@ -7,12 +7,19 @@ queries stay local, K and V are all-gathered over the CP group (backward: reduce
 of the local queries attends, per packed document, to the keys from the document start up to its own
 end.
 
-Here the two halves become two calls of the variable-length attention kernel whose q segments are the
-tail of their key segments; the keys each half needs are packed from the gathered tensor with one
-row gather, whose backward sums the contributions of overlapping ranges.
+Two implementations.  On GPUs of one node the keys never get packed: K and V of all ranks are gathered over peer
+memory (one launch of the gather kernel of ``csrc/gemm_tp_sm100.cu``) into a rank-major buffer, and the attention
+kernels address a key by its *global position* (``key_row`` in ``csrc/attention_common.cuh``), with one segment
+per document piece; the forward is a single launch over both halves, the backward one launch group per half
+whose dK / dV land in rank-major buffers that are summed and reduce-scattered.  K / V are gathered again in the
+backward instead of being kept.  Elsewhere (CPU, other nodes) the two halves become two calls of the
+variable-length attention whose q segments are the tail of their key segments; the keys each half needs are
+packed from the gathered tensor with one row gather, whose backward sums the contributions of overlapping ranges.
 """
 from __future__ import annotations
 
+import math
+import os
 import weakref
 from dataclasses import dataclass, field
 
@@ -21,6 +28,8 @@ import torch
 from ..ops import attention
 from . import comm
 from .state import PM
+
+PEER_PATH = os.environ.get("STB200_CP_PEER", "1") != "0"
 
 
 def _cp():
@@ -95,6 +104,18 @@ class CPMeta:
     chunk_len: int
     token_index: torch.Tensor     # int64 [2L] global positions of this rank's tokens
     halves: list = field(default_factory=list)
+    pieces: list = field(default_factory=list)    # per half: [(q_begin, q_end, k_begin)] in global positions
+    cp: int = 1
+    _gathered: tuple | None = None                # (plan over both halves, [plan of half 0, plan of half 1])
+
+    def gathered_plans(self, device):
+        """Segment tables of the global-position kernels, built on first use."""
+        if self._gathered is None:
+            from ..ops.attention_native import GatheredKeyPlan
+
+            both = GatheredKeyPlan(self.pieces[0] + self.pieces[1], self.cp, self.chunk_len, device)
+            self._gathered = (both, [GatheredKeyPlan(p, self.cp, self.chunk_len, device) for p in self.pieces])
+        return self._gathered
 
     def local_position_id(self, position_id: torch.Tensor) -> torch.Tensor:
         return position_id.index_select(0, self.token_index.to(position_id.device))
@@ -138,8 +159,9 @@ def build_cp_meta(cu_seqlens, total: int, device=None) -> CPMeta:
     L = total // (2 * cp)
     a, b = balanced_chunk_ids(rank, cp)
     token_index = torch.cat([torch.arange(a * L, (a + 1) * L), torch.arange(b * L, (b + 1) * L)]).to(device)
-    meta = CPMeta(L, token_index)
+    meta = CPMeta(L, token_index, cp=cp)
     for pieces in cu_seqlens_to_balanced_cp(cu_list, total, cp, rank):
+        meta.pieces.append(pieces)
         q_lens = [qe - qs for qs, qe, _ in pieces]
         k_lens = [qe - ks for _, qe, ks in pieces]
         cu_q = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=device)
@@ -153,9 +175,69 @@ def build_cp_meta(cu_seqlens, total: int, device=None) -> CPMeta:
     return meta
 
 
+class _PeerCPAttention(torch.autograd.Function):
+    """Attention of the local queries against the keys of all CP ranks, addressed by global position."""
+
+    @staticmethod
+    def _gather(kv_local):
+        from . import symm
+
+        _, buf = symm.all_gather_gemm(kv_local, None, "CP")
+        return buf
+
+    @staticmethod
+    def forward(ctx, q, k, v, meta, causal, window):
+        from ..ops import attention_native as an
+
+        rows, hkv, D = k.shape
+        scale = 1.0 / math.sqrt(D)
+        q = q.contiguous()
+        kv_local = torch.cat([k.reshape(rows, hkv * D), v.reshape(rows, hkv * D)], dim=1)
+        buf = _PeerCPAttention._gather(kv_local).view(-1, 2, hkv, D)     # valid until the next gather on the group
+        both, _ = meta.gathered_plans(q.device)
+        o, lse = an.gathered_attention_fwd(q, buf[:, 0], buf[:, 1], both, causal, window, scale)
+        ctx.save_for_backward(q, kv_local, o, lse)
+        ctx.cfg = (meta, causal, window, scale, hkv, D)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        from ..ops import attention_native as an
+
+        q, kv_local, o, lse = ctx.saved_tensors
+        meta, causal, window, scale, hkv, D = ctx.cfg
+        L, cp = meta.chunk_len, meta.cp
+        do = do.contiguous()
+        buf = _PeerCPAttention._gather(kv_local).view(-1, 2, hkv, D)
+        _, halves = meta.gathered_plans(q.device)
+        # [half][dK | dV][rank-major key rows]: a half writes only the rows its segments cover
+        part = torch.zeros((2, 2, buf.shape[0], hkv, D), dtype=q.dtype, device=q.device)
+        dq = []
+        for h, plan in enumerate(halves):
+            rows = slice(h * L, (h + 1) * L)
+            dq.append(an.gathered_attention_bwd(q[rows], buf[:, 0], buf[:, 1], o[rows], do[rows],
+                                                lse[:, rows].contiguous(), plan, causal, window, scale,
+                                                part[h, 0], part[h, 1]))
+        total = part[0].add_(part[1])
+        dkv = torch.empty((2, 2 * L, hkv, D), dtype=q.dtype, device=q.device)
+        for i in range(2):                       # rank-major rows: exactly the layout reduce-scatter cuts
+            comm.reduce_scatter_tensor(dkv[i], total[i], group=PM.group_of("CP"))
+        return torch.cat(dq, dim=0), dkv[0], dkv[1], None, None, None
+
+
+def _peer_path_ok(q, k, v, meta: CPMeta) -> bool:
+    if not (PEER_PATH and q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] == 128 and meta.chunk_len % 128 == 0):
+        return False
+    from . import symm
+
+    return symm.enabled("CP") and symm.usable(2 * meta.chunk_len, 2 * k.shape[1] * k.shape[2], 0)
+
+
 def cp_attention(q, k, v, meta: CPMeta, causal: bool = True, window: int = 0):
     """q ``[2L,hq,D]`` (local zigzag chunks), k/v ``[2L,hkv,D]`` local -> ``[2L,hq,D]``."""
     L = meta.chunk_len
+    if _peer_path_ok(q, k, v, meta):
+        return _PeerCPAttention.apply(q, k, v, meta, causal, window)
     k_all = gather_from_balanced_cp_region(k.contiguous())
     v_all = gather_from_balanced_cp_region(v.contiguous())
     outs = []

@@ -243,8 +243,9 @@ def all_gather_gemm(x, w, group_name: str = "TP", *, b_mn_major: bool = False, o
     """``(all_gather_rows(x) @ w.T  [or @ w], all_gather_rows(x))`` in one launch.  ``w=None`` gathers only;
     ``need_gathered=False`` returns ``None`` for the gathered rows and saves the copy of the own block.
 
-    The gathered matrix is a view of the group's symmetric memory: it stays valid until the second-next
-    fused all-gather on the group (consume it, or copy it, before that)."""
+    The gathered matrix is a view of the group's symmetric memory and stays valid until the NEXT fused all-gather
+    on the group is launched: a peer may start writing the call after that one into the same slot as soon as it
+    has seen this rank's rows of the next call.  Consume it on the launching stream, or copy it, before that."""
     a = arena(group_name)
     rows, k = x.shape
     m = rows * a.world

@@ -117,3 +117,15 @@ def test_muon_gathers_tp_shards_over_peer_memory():
     assert out.returncode == 0, "\n".join(l for l in out.stderr.splitlines() if l.startswith("[rank0]"))[-4000:]
     res = json.loads([l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
     assert res == {"rows": True, "cols": True, "blocks": True}     # every case took the peer path
+
+
+def test_context_parallel_attention_over_peer_memory_matches_packed_keys_and_fp32():
+    """CP=2: K / V gathered over peer memory and addressed by global position inside the attention kernels, against
+    the packed-keys path over NCCL and fp32 attention over the whole sequence (forward, dq, dk, dv)."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29751", os.path.join(ROOT, "tests", "mp_cp_attention_worker.py")]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=env, cwd=ROOT)
+    assert out.returncode == 0, "\n".join(l for l in out.stderr.splitlines() if l.startswith("[rank0]"))[-4000:]
+    res = json.loads([l for l in out.stdout.splitlines() if l.startswith("RESULT ")][-1][len("RESULT "):])
+    assert res["worst_over_ranks"] < 2e-2, res
