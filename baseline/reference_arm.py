@@ -103,7 +103,7 @@ def _run(args) -> None:
         model_cfg_cls = model_file.Qwen3_8BConfig
 
     sys.path.insert(0, os.path.dirname(HERE))
-    from bench import ClockSampler, default_parallelism, model_flops_per_token, parse_parallelism
+    from bench import OPTIMIZER_TEXT, ClockSampler, default_parallelism, model_flops_per_token, parse_parallelism
     from steptronoss_b200.data.synthetic import make_packed_sample  # data generator only (numpy)
 
     par_text = args.parallelism or (f"ep{world}dp{world}" if moe else default_parallelism(world))
@@ -167,6 +167,10 @@ def _run(args) -> None:
             pc.context_parallel_size = par["cp"]
             self.model_cfg.tp_cfg.sequence_parallel = par["tp"] > 1
             self.model_cfg.check_nan = False
+            if args.optimizer == "muon":
+                from steptronoss.exp.optimizer import MuonConfig as RefMuonConfig
+
+                self.optimizer_cfg.optimizer_cfg = RefMuonConfig
             if moe:
                 pc.expert_model_parallel_size, pc.expert_tensor_parallel_size = par["ep"], 1
                 self.model_cfg.ffn_cfg.moe_cfg.moe_aux_loss_coef = 1e-3
@@ -300,7 +304,7 @@ def _run(args) -> None:
         "mfu_of_measured_sustained_bf16": value * fpt / (peak * world),
         # the same keys, in the same words, as the other arm prints
         "config": {"model": MODEL_TEXT[kind], "layers": exp.model_cfg.num_layers, "global_batch": tc.global_batch_size,
-                   "seq_len": seq, "micro_batch": 1, "parallelism": par_text, "optimizer": "Adam fp32 master+state, ZeRO-1",
+                   "seq_len": seq, "micro_batch": 1, "parallelism": par_text, "optimizer": OPTIMIZER_TEXT[args.optimizer],
                    "recompute": exp._recompute_text, "l2": L2_TEXT},
         "implementation": {"attention": "flash-attn 2 (reference AttentionCore)",
                            **({"moe_dispatcher": "TokenDispatcher (NCCL all-to-all)", "optimizable": moe_choices}

@@ -60,7 +60,9 @@ def parse():
     ap.add_argument("--moe-capacity-factor", type=float, default=2.0,
                     help="MoE + peer dispatcher: size the expert buffers for this multiple of the balanced load instead "
                          "of reading the arrived count back every layer (0 = exact count); overflow fails the run")
-    ap.add_argument("--parallelism", default=None, help="e.g. tp4dp2, dp8, tp2; default tp=min(N,4) x dp")
+    ap.add_argument("--parallelism", default=None, help="e.g. tp4dp2, dp8, tp2, tp2cp2pp2; default tp=min(N,4) x dp")
+    ap.add_argument("--optimizer", default="adam", choices=["adam", "muon"],
+                    help="muon: Newton-Schulz updates for the 2-D hidden matrices, AdamW for the rest")
     ap.add_argument("--seqs-per-gpu", type=int, default=None,
                     help="sequences per GPU per step (global batch = this x N); default 8 (dense) / 32 (MoE)")
     ap.add_argument("--seq-len", type=int, default=None, help="default 8192 (dense) / 4096 (MoE)")
@@ -131,6 +133,10 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+OPTIMIZER_TEXT = {"adam": "Adam fp32 master+state, ZeRO-1",
+                  "muon": "Muon (2-D hidden matrices) + AdamW, fp32 master+state, ZeRO-1"}
+
+
 def default_parallelism(n: int) -> str:
     tp = min(n, 4)
     dp = n // tp
@@ -186,6 +192,10 @@ def run_ours(args):
     pc.pipeline_model_parallel_size = par["pp"]
     pc.context_parallel_size = par["cp"]
     exp.model_cfg.tp_cfg.sequence_parallel = par["tp"] > 1
+    if args.optimizer == "muon":
+        from steptronoss_b200.exp.optimizer import MuonConfig
+
+        exp.optimizer_cfg.optimizer_cfg = MuonConfig
     tc = exp.trainer_cfg
     # a micro-batch of M sequences is one packed row of M x seq_len tokens whose documents are at most seq_len long
     tc.global_seq_length = args.seq_len * args.seqs_per_micro_batch
@@ -330,7 +340,7 @@ def run_ours(args):
         "mfu_of_measured_sustained_bf16": value * fpt / (peak * world),
         "config": {"model": MODEL_TEXT[kind], "layers": mc.num_layers, "global_batch": args.seqs_per_gpu * world,
                    "seq_len": args.seq_len, "micro_batch": args.seqs_per_micro_batch, "parallelism": par_text,
-                   "optimizer": "Adam fp32 master+state, ZeRO-1", "recompute": rec, "l2": L2_TEXT},
+                   "optimizer": OPTIMIZER_TEXT[args.optimizer], "recompute": rec, "l2": L2_TEXT},
         "implementation": {"attention": "tcgen05 flash attention (csrc/attention_sm100.cu)",
                            **({"moe_dispatcher": args.dispatcher,
                                "moe_capacity_factor": args.moe_capacity_factor or None} if moe else {})},

@@ -31,14 +31,20 @@ def test_timers_levels_scopes_and_report():
     init_timers()
 
 
-def test_memory_marks_only_when_enabled():
+def test_memory_marks_only_when_enabled(monkeypatch):
+    from steptronoss_b200.utils import memory_tracker
     from steptronoss_b200.utils.memory_tracker import MemoryTracker
+
+    # the resident set of a long test process need not grow when memory is recycled: count what the test allocates
+    held = [1 << 30]
+    monkeypatch.setattr(memory_tracker, "_rss_bytes", lambda: held[0])
 
     off = MemoryTracker(enabled=False)
     assert off.mark("a") is None and off.marks == []
     on = MemoryTracker(enabled=True)
     on.mark("start")
     blob = bytearray(64 << 20)
+    held[0] += len(blob)
     m = on.mark("after-alloc")
     assert m.rss > 0 and len(on.marks) == 2
     name, d_gpu, d_rss = on.deltas()[0]
