@@ -11,6 +11,11 @@
 // work on tile i; the output accumulators stay in TMEM for the whole CTA.  Both passes recompute S, so
 // no atomics are needed and the gradients are bitwise reproducible.
 //
+// The kernels are bound by shared-memory bandwidth rather than by the tensor pipe (a 128x64x16 product with both
+// operands in shared memory reads 6 KB in the 32 cycles it computes).  In the dQ pass the fixed tiles Q and dO are
+// therefore copied once per CTA into TMEM (64 columns each, two bf16 per column) and serve as the A operand of
+// S and dP from there; only the streamed K / V tiles are read from shared memory.
+//
 // The dK/dV pass loops over q heads of the GQA group inside the CTA, so dK and dV come out summed over them.
 // With few kv heads and key blocks (4 kv heads x 33 blocks is less than one wave of 148 SMs) the group is
 // split over `splits` CTAs; each writes fp32 partials and `attn_dkv_reduce_kernel` adds them in split order,
@@ -30,23 +35,33 @@ constexpr int kBwdSmem = 2 * kTileBytes + kBwdStages * 2 * kStreamTile + 2 * 2 *
 // A [128][K] K-major (two 64-col slabs of 16 KB) x B [64][K] K-major (two slabs of 8 KB) -> D [128 x 64]
 __device__ __forceinline__ void mma_fixed_stream_t(uint32_t d_tmem, uint32_t sa, uint32_t sb) {
   constexpr uint32_t idesc = umma_idesc_bf16(128, kSB, 0, 0);
-#pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const uint64_t da = umma_smem_desc(sa + (k >> 2) * kSlabBytes + (k & 3) * 32, 16, 1024);
-    const uint64_t db = umma_smem_desc(sb + (k >> 2) * kStreamSlab + (k & 3) * 32, 16, 1024);
-    umma_bf16(d_tmem, da, db, idesc, k > 0 ? 1u : 0u);
-  }
+  const uint64_t da = umma_smem_desc(sa, 16, 1024), db = umma_smem_desc(sb, 16, 1024);
+  umma4_ss(d_tmem, da, umma_desc_advance(da, 32), umma_desc_advance(da, 64), umma_desc_advance(da, 96), db,
+           umma_desc_advance(db, 32), umma_desc_advance(db, 64), umma_desc_advance(db, 96), idesc, 0u);
+  umma4_ss(d_tmem, umma_desc_advance(da, kSlabBytes), umma_desc_advance(da, kSlabBytes + 32),
+           umma_desc_advance(da, kSlabBytes + 64), umma_desc_advance(da, kSlabBytes + 96),
+           umma_desc_advance(db, kStreamSlab), umma_desc_advance(db, kStreamSlab + 32),
+           umma_desc_advance(db, kStreamSlab + 64), umma_desc_advance(db, kStreamSlab + 96), idesc, 1u);
+}
+
+// A [128][128] bf16 in TMEM (64 columns) x B [64][K] K-major (two slabs of 8 KB) -> D [128 x 64]
+__device__ __forceinline__ void mma_tmem_stream_t(uint32_t d_tmem, uint32_t a_tmem, uint32_t sb) {
+  constexpr uint32_t idesc = umma_idesc_bf16(128, kSB, 0, 0);
+  const uint64_t db = umma_smem_desc(sb, 16, 1024);
+  umma4_ts(d_tmem, a_tmem, a_tmem + 8, a_tmem + 16, a_tmem + 24, db, umma_desc_advance(db, 32),
+           umma_desc_advance(db, 64), umma_desc_advance(db, 96), idesc, 0u);
+  umma4_ts(d_tmem, a_tmem + 32, a_tmem + 40, a_tmem + 48, a_tmem + 56, umma_desc_advance(db, kStreamSlab),
+           umma_desc_advance(db, kStreamSlab + 32), umma_desc_advance(db, kStreamSlab + 64),
+           umma_desc_advance(db, kStreamSlab + 96), idesc, 1u);
 }
 
 // A [128][64] K-major (one slab) x B stored [64 rows = K][128 = N] (MN-major, two slabs of 8 KB) -> D [128 x 128]
 __device__ __forceinline__ void mma_p_stream(uint32_t d_tmem, uint32_t sa, uint32_t sb, bool accumulate) {
   constexpr uint32_t idesc = umma_idesc_bf16(128, 128, 0, 1);
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const uint64_t da = umma_smem_desc(sa + k * 32, 16, 1024);
-    const uint64_t db = umma_smem_desc(sb + k * 2048, kStreamSlab, 1024);
-    umma_bf16(d_tmem, da, db, idesc, (accumulate || k > 0) ? 1u : 0u);
-  }
+  const uint64_t da = umma_smem_desc(sa, 16, 1024), db = umma_smem_desc(sb, kStreamSlab, 1024);
+  umma4_ss(d_tmem, da, umma_desc_advance(da, 32), umma_desc_advance(da, 64), umma_desc_advance(da, 96), db,
+           umma_desc_advance(db, 2048), umma_desc_advance(db, 4096), umma_desc_advance(db, 6144), idesc,
+           accumulate ? 1u : 0u);
 }
 
 __device__ __forceinline__ void load_stream_tile(void* dst, const CUtensorMap* m, uint64_t* bar, int head, int row) {
@@ -115,7 +130,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
   uint64_t* sdp_full = bars + 7;                // [2] S', dP' in TMEM
   uint64_t* pds_full = bars + 9;                // [2] P', dS' in smem (128 arrivals)
   uint64_t* acc_full = bars + 11;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* f_tmem = bars + 12;                 // dQ pass: Q and dO copied into TMEM (256 arrivals)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -159,6 +175,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
       mbar_init(&pds_full[i], 256);
     }
     mbar_init(acc_full, 1);
+    mbar_init(f_tmem, 256);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -169,7 +186,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem = *tmem_slot;  // S'[2] 0,64 ; dP'[2] 128,192 ; acc1 256 ; acc2 384
+  const uint32_t tmem = *tmem_slot;  // S'[2] 0,64 ; dP'[2] 128,192 ; acc1 256 ; acc2 384 (dQ pass: Q 384, dO 448)
 
   if (warp == 0) {
     if (lane == 0 && iters > 0) {
@@ -195,14 +212,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
   } else if (warp == 1) {
     if (lane == 0 && iters > 0) {
       bool ok = mbar_wait(f_full, 0);
+      if (!DKV && ok) ok = mbar_wait(f_tmem, 0);
       const uint32_t aF1 = smem_u32(sF1), aF2 = smem_u32(sF2);
       auto issue_sdp = [&](int it) -> bool {
         const int st = it % kBwdStages;
         if (!mbar_wait(&g_full[st], (it / kBwdStages) & 1)) return false;
         tc_fence_after();
         const uint32_t g1 = smem_u32(sG + st * 2 * kStreamTile);
-        mma_fixed_stream_t(tmem + (it & 1) * kSB, aF1, g1);
-        mma_fixed_stream_t(tmem + 128 + (it & 1) * kSB, aF2, g1 + kStreamTile);
+        if (DKV) {
+          mma_fixed_stream_t(tmem + (it & 1) * kSB, aF1, g1);
+          mma_fixed_stream_t(tmem + 128 + (it & 1) * kSB, aF2, g1 + kStreamTile);
+        } else {
+          mma_tmem_stream_t(tmem + (it & 1) * kSB, tmem + 384, g1);
+          mma_tmem_stream_t(tmem + 128 + (it & 1) * kSB, tmem + 448, g1 + kStreamTile);
+        }
         umma_commit(&sdp_full[it & 1]);
         return true;
       };
@@ -254,6 +277,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
       }
     }
     bool ok = true;
+    if (!DKV && iters > 0) {
+      // group 0 copies its row of Q, group 1 its row of dO: 16 chunks of 16 bytes from the swizzled tile
+      ok = mbar_wait(f_full, 0);
+      const uint8_t* src = half == 0 ? sF1 : sF2;
+      const uint32_t dst = tmem + lane_addr + 384 + half * 64;
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {          // 64 columns of the row = one 128-byte slab row = 32 TMEM columns
+        uint32_t w[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 x = *reinterpret_cast<const uint4*>(src + hh * kSlabBytes + swz(r, c));
+          w[c * 4] = x.x; w[c * 4 + 1] = x.y; w[c * 4 + 2] = x.z; w[c * 4 + 3] = x.w;
+        }
+        tmem_st_32x32(dst + hh * 32, w);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive(f_tmem);
+    }
     // All softmax threads run every iteration (the dK/dV pass meets at a named barrier in each one); after
     // a timed-out wait the remaining waits are skipped, so a failure cannot strand the other threads.
     for (int it = 0; it < iters; ++it) {

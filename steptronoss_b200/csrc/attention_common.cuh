@@ -55,14 +55,30 @@ __device__ __forceinline__ uint32_t swz(uint32_t row, uint32_t chunk) { return r
 template <bool A_MN, bool B_MN>
 __device__ __forceinline__ void mma_128x128x128(uint32_t d_tmem, uint32_t sa, uint32_t sb, bool accumulate) {
   constexpr uint32_t idesc = umma_idesc_bf16(128, 128, A_MN ? 1 : 0, B_MN ? 1 : 0);
-#pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const uint64_t da = A_MN ? umma_smem_desc(sa + k * 2048, kSlabBytes, 1024)
-                             : umma_smem_desc(sa + (k >> 2) * kSlabBytes + (k & 3) * 32, 16, 1024);
-    const uint64_t db = B_MN ? umma_smem_desc(sb + k * 2048, kSlabBytes, 1024)
-                             : umma_smem_desc(sb + (k >> 2) * kSlabBytes + (k & 3) * 32, 16, 1024);
-    umma_bf16(d_tmem, da, db, idesc, (accumulate || k > 0) ? 1u : 0u);
-  }
+  // step k of an MN-major operand starts 16 rows = 2048 bytes further; of a K-major operand 32 bytes further inside
+  // a 64-column slab, and in the second slab from k = 4 on
+  const uint64_t da = A_MN ? umma_smem_desc(sa, kSlabBytes, 1024) : umma_smem_desc(sa, 16, 1024);
+  const uint64_t db = B_MN ? umma_smem_desc(sb, kSlabBytes, 1024) : umma_smem_desc(sb, 16, 1024);
+  constexpr uint32_t sa1 = A_MN ? 2048 : 32, sa4 = A_MN ? 4 * 2048 : kSlabBytes;
+  constexpr uint32_t sb1 = B_MN ? 2048 : 32, sb4 = B_MN ? 4 * 2048 : kSlabBytes;
+  umma4_ss(d_tmem, da, umma_desc_advance(da, sa1), umma_desc_advance(da, 2 * sa1), umma_desc_advance(da, 3 * sa1), db,
+           umma_desc_advance(db, sb1), umma_desc_advance(db, 2 * sb1), umma_desc_advance(db, 3 * sb1), idesc,
+           accumulate ? 1u : 0u);
+  umma4_ss(d_tmem, umma_desc_advance(da, sa4), umma_desc_advance(da, sa4 + sa1), umma_desc_advance(da, sa4 + 2 * sa1),
+           umma_desc_advance(da, sa4 + 3 * sa1), umma_desc_advance(db, sb4), umma_desc_advance(db, sb4 + sb1),
+           umma_desc_advance(db, sb4 + 2 * sb1), umma_desc_advance(db, sb4 + 3 * sb1), idesc, 1u);
+}
+
+// The same with A = [128 lanes][128 K] bf16 in TMEM (64 columns).
+template <bool B_MN>
+__device__ __forceinline__ void mma_128x128x128_ta(uint32_t d_tmem, uint32_t ta, uint32_t sb, bool accumulate) {
+  constexpr uint32_t idesc = umma_idesc_bf16(128, 128, 0, B_MN ? 1 : 0);
+  const uint64_t db = B_MN ? umma_smem_desc(sb, kSlabBytes, 1024) : umma_smem_desc(sb, 16, 1024);
+  constexpr uint32_t sb1 = B_MN ? 2048 : 32, sb4 = B_MN ? 4 * 2048 : kSlabBytes;
+  umma4_ts(d_tmem, ta, ta + 8, ta + 16, ta + 24, db, umma_desc_advance(db, sb1), umma_desc_advance(db, 2 * sb1),
+           umma_desc_advance(db, 3 * sb1), idesc, accumulate ? 1u : 0u);
+  umma4_ts(d_tmem, ta + 32, ta + 40, ta + 48, ta + 56, umma_desc_advance(db, sb4), umma_desc_advance(db, sb4 + sb1),
+           umma_desc_advance(db, sb4 + 2 * sb1), umma_desc_advance(db, sb4 + 3 * sb1), idesc, 1u);
 }
 
 __device__ __forceinline__ void load_tile(void* dst, const CUtensorMap* m, uint64_t* bar, int head, int row) {

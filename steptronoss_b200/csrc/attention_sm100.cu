@@ -304,17 +304,6 @@ constexpr int kFwd2Threads = 320;
 constexpr int kFwd2Stages = 4;
 constexpr int kFwd2Smem = (2 + kFwd2Stages) * kTileBytes + 1024 + 256;
 
-// D[tmem] (+)= A[tmem] * B[smem]: A is [128 lanes][K] with two bf16 per 32-bit column.
-__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
-                                                 uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
 __global__ void __launch_bounds__(kFwd2Threads, 1)
 attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                  const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
@@ -390,7 +379,6 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
   } else if (warp == 1) {
     if (lane == 0 && nkb > 0) {
-      constexpr uint32_t idesc_pv = umma_idesc_bf16(128, 128, 0, 1);
       const uint32_t aQ = smem_u32(sQ);
       bool ok = mbar_wait(q_full, 0);
       if (ok) ok = mbar_wait(&kv_full[0], 0);
@@ -414,10 +402,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
           if (!ok) break;
           tc_fence_after();
           // O_t += P_t V_j : A = P_t in TMEM (16 keys = 8 columns per step), B = V ([keys][D], MN-major)
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            umma_bf16_a_tmem(tmem + 256 + t * 128, tmem + t * 128 + k * 8,
-                             umma_smem_desc(aV + k * 2048, kSlabBytes, 1024), idesc_pv, (j > 0 || k > 0) ? 1u : 0u);
+          mma_128x128x128_ta<true>(tmem + 256 + t * 128, tmem + t * 128, aV, j > 0);
           if (more) {
             mma_128x128x128<false, false>(tmem + t * 128, aQ + t * kTileBytes, aK, false);
             umma_commit(&s_full[t]);

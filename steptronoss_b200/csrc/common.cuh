@@ -71,11 +71,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 // Bounded wait. Returns false when the phase did not complete within kWaitBudgetNs (wall time on the
-// device, checked every 256 polls) or within kSpinLimit polls, whichever comes first.
+// device) or within kSpinLimit polls, whichever comes first.  The wall clock (%globaltimer) is slow to read, on the
+// order of a microsecond, and most waits of a pipelined kernel end within a few polls: the first 1024 polls touch
+// no timer at all, and the clock is read for the first time only then.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+  for (uint32_t i = 0; i < 1024u; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
   const uint64_t t0 = global_timer_ns();
-  for (uint32_t i = 1; i < kSpinLimit; ++i) {
+  for (uint32_t i = 1024u; i < kSpinLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 255u) == 0 && global_timer_ns() - t0 > kWaitBudgetNs) return false;
   }
@@ -86,7 +91,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 // for kernels whose pipeline is gated by another rank, where the budget has to cover rank skew.
 __device__ __forceinline__ bool mbar_wait_budget(uint64_t* bar, uint32_t parity, uint64_t budget_ns,
                                                  const volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+  for (uint32_t i = 0; i < 1024u; ++i) {   // no timer on the fast path (see mbar_wait)
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  if (*abort_flag) return false;
   const uint64_t t0 = global_timer_ns();
   for (uint32_t i = 1;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -193,6 +202,58 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
       : "memory");
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]: A is [128 lanes][K] with two bf16 per 32-bit column (16 K = 8 columns per step).
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// ----------------------------------------------------------------------------- chains of UMMA steps
+// One thread feeds the tensor pipe, and a 128x128x16 step lasts 64 cycles: the instructions around every
+// tcgen05.mma (descriptor arithmetic, predicate set-up) have to stay well below that, or the issuing thread
+// becomes the bottleneck (measured: 86 cycles per step with descriptors rebuilt from addresses for every step).
+// The helpers below build a descriptor once per operand tile, advance it with one 32-bit add per step (the address
+// field sits in the low word and never carries out of it for shared-memory offsets) and issue the steps of a tile
+// from a single asm block with two predicates.
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t d, uint32_t bytes) {
+  return (d & 0xFFFFFFFF00000000ull) | static_cast<uint32_t>(static_cast<uint32_t>(d) + (bytes >> 4));
+}
+
+// 4 steps: D (+)= A_k * B_k, k = 0..3, A and B in shared memory; `accumulate` applies to the first step only.
+__device__ __forceinline__ void umma4_ss(uint32_t d, uint64_t a0, uint64_t a1, uint64_t a2, uint64_t a3, uint64_t b0,
+                                         uint64_t b1, uint64_t b2, uint64_t b3, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %10, 0;\n\t"
+      "setp.eq.b32 q, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %5, %9, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %2, %6, %9, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %3, %7, %9, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %4, %8, %9, q;\n\t}"
+      ::"r"(d), "l"(a0), "l"(a1), "l"(a2), "l"(a3), "l"(b0), "l"(b1), "l"(b2), "l"(b3), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 4 steps with A in TMEM (a0..a3: TMEM addresses, 8 columns apart for K = 16 per step).
+__device__ __forceinline__ void umma4_ts(uint32_t d, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint64_t b0,
+                                         uint64_t b1, uint64_t b2, uint64_t b3, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %10, 0;\n\t"
+      "setp.eq.b32 q, 0, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %5, %9, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], %6, %9, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %7, %9, q;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %8, %9, q;\n\t}"
+      ::"r"(d), "r"(a0), "r"(a1), "r"(a2), "r"(a3), "l"(b0), "l"(b1), "l"(b2), "l"(b3), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // 32 lanes x 32 consecutive fp32 columns: thread t of the warp receives row (lane base + t).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -215,6 +276,16 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
         "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr)
+      : "memory");
+}
+
+// 32 lanes x 16 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+      ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr)
       : "memory");
 }
 

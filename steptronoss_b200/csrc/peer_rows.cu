@@ -73,9 +73,10 @@ __global__ void peer_wait_flags_kernel(const uint32_t* flags, int flag_index, in
   const int r = threadIdx.x;
   if (r >= world) return;
   const uint32_t* f = flags + flag_index * kPeerMaxRanks + r;
-  const uint64_t t0 = global_timer_ns();
+  uint64_t t0 = 0;   // the wall clock is slow to read: not before the first miss
   for (uint32_t i = 0;; ++i) {
     if (static_cast<int32_t>(ld_acquire_sys_u32(f) - epoch) >= 0) return;
+    if (i == 0) t0 = global_timer_ns();
     if ((i & 15u) == 15u && global_timer_ns() - t0 > budget_ns) {
       report_error(status, kErrPeerFlagWait);
       return;

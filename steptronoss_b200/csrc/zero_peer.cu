@@ -53,9 +53,10 @@ zero_reduce_kernel(const __grid_constant__ ZeroPtrs grads, long long n4, int wor
   __syncthreads();
   if (threadIdx.x < world) {
     const uint32_t* f = flags_self + flag_index * kZeroMaxRanks + threadIdx.x;
-    const uint64_t t0 = global_timer_ns();
+    uint64_t t0 = 0;   // the wall clock is slow to read: not before the first miss
     for (uint32_t i = 0;; ++i) {
       if (static_cast<int32_t>(zld_acquire_sys_u32(f) - epoch) >= 0) break;
+      if (i == 0) t0 = global_timer_ns();
       if ((i & 15u) == 15u && global_timer_ns() - t0 > budget_ns) {
         report_error(status, kErrPeerFlagWait);
         ok = 0;
