@@ -137,6 +137,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--json", default=None)
+    ap.add_argument("--fp8", action="store_true",
+                    help="forward expert GEMMs in block-scaled e4m3 (1x128 activation, 128x128 weight scales)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--ref-grouped-gemm", default="triton_grouped_gemm",
                     help="reference arm: alternative of its grouped_gemm switch, or 'default' for the per-expert loop")
@@ -173,6 +175,7 @@ def main():
         c = h.moe_cfg
         c.hidden_size, c.moe_num_experts, c.moe_top_k, c.moe_hidden_size = H, E, K, F
         c.moe_layer_list, c.dispatcher, c.norm_expert_weight = [0], kind, True
+        c.fp8 = bool(args.fp8)
         holders.append(h)
         with torch.device(dev):
             return MoEBlock(c, 0)
@@ -234,6 +237,7 @@ def main():
                 dist.all_reduce(slots)
             flops = 3 * 2.0 * float(slots) * H * 3 * F  # forward + 2x backward of the two expert GEMMs, all ranks
             row = {"bench": "moe_layer_fwd_bwd", "routing": routing, "dispatcher": kind, "ep": world,
+                   "expert_forward": "fp8 e4m3, 1x128 / 128x128 block scales" if args.fp8 else "bf16",
                    "tokens_per_rank": T, "hidden": H, "experts": E, "ffn": F, "top_k": K, "best_ms": float(t[0]),
                    "median_ms": float(t[1]), "tokens_per_s_all_ranks": T * world / (float(t[0]) * 1e-3),
                    "expert_gemm_tflops_per_gpu": flops / world / (float(t[0]) * 1e-3) / 1e12,

@@ -79,7 +79,10 @@ int encode_cached(CUtensorMap* out, const TmapKey& key) {
   cuuint64_t strides[2] = {key.pitch[0], key.pitch[1]};
   cuuint32_t box[3] = {key.box[0], key.box[1], key.box[2]};
   cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(out, elem == 4 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank,
+  const CUtensorMapDataType dtype = elem == 4   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                    : elem == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                                : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUresult r = enc(out, dtype, rank,
                    const_cast<void*>(key.base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    swz ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -99,7 +102,7 @@ int make_tmap_2d(CUtensorMap* out, const void* base, int elem_bytes, uint64_t d0
   k.dims[0] = d0; k.dims[1] = d1;
   k.pitch[0] = pitch_bytes;
   k.box[0] = box0; k.box[1] = box1;
-  k.meta = 2u | (static_cast<uint32_t>(elem_bytes == 4 ? 4 : 2) << 4) | (swizzle128 ? 1u << 8 : 0u);
+  k.meta = 2u | (static_cast<uint32_t>(elem_bytes == 4 ? 4 : elem_bytes == 1 ? 1 : 2) << 4) | (swizzle128 ? 1u << 8 : 0u);
   return encode_cached(out, k);
 }
 

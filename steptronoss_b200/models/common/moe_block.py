@@ -52,6 +52,9 @@ class MoEConfig(Config):
     layer).  f >= 1: sized for f x (tokens x top-k) without a host read; a rank that receives more fails the step
     with a capacity error (nothing is dropped silently)."""
     recompute_experts: bool = False
+    fp8: bool = False
+    """Forward products of the routed expert GEMMs in block-scaled e4m3 (1 x 128 activation scales, 128 x 128 weight
+    scales, fp32 accumulation); the backward products stay in bf16."""
     detailed_router_metrics: bool = False
     """Also fill ``router_logits_std`` and ``moe_minp / moe_sumk / moe_std / moe_avg`` (per-token statistics of the
     router probabilities, as the reference logs them).  They are computed with ordinary tensor operations over the
@@ -120,9 +123,10 @@ class GroupedExperts(nn.Module):
             w.expert_model_parallel = ep > 1
         lim = cfg.get_experts_swiglu_limit(layer_id)
         self.limit = float(lim) if lim else 0.0
+        self.fp8 = bool(getattr(cfg, "fp8", False))
 
     def forward(self, x, local_ids, weights, max_slots=None):
-        return moe_ops.routed_grouped_ffn(x, local_ids, weights, self.w1, self.w2, self.limit, max_slots)
+        return moe_ops.routed_grouped_ffn(x, local_ids, weights, self.w1, self.w2, self.limit, max_slots, fp8=self.fp8)
 
 
 class MoEBlock(nn.Module):

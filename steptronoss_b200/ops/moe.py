@@ -296,10 +296,19 @@ class _GroupedLinearFn(torch.autograd.Function):
     """Per-expert ``x_g @ w[g].T`` over expert-major rows; wgrad accumulates into ``w.main_grad``."""
 
     @staticmethod
-    def forward(ctx, x, w, offsets, tile_group=None):
+    def forward(ctx, x, w, offsets, tile_group=None, fp8=False):
         if tile_group is None and x.is_cuda:
             tile_group = tile_groups_from_offsets(offsets, x.shape[0])
-        y = grouped_gemm_rows(x, w, offsets, trans_b=True, tile_group=tile_group)
+        if fp8 and x.is_cuda and x.shape[1] % 128 == 0 and w.shape[1] % 128 == 0 and x.dtype == torch.bfloat16:
+            # forward product in block-scaled e4m3 (1 x 128 activation, 128 x 128 weight scales); the backward
+            # products below stay in bf16 on the saved bf16 operands
+            from . import fp8 as fp8_ops
+
+            xq, sx = fp8_ops.quantize_rows_1x128(x)
+            wq, sw = fp8_ops.quantize_blocks_128x128(w.reshape(w.shape[0] * w.shape[1], w.shape[2]))
+            y = fp8_ops.grouped_gemm_fp8(xq, sx, wq, sw, offsets, w.shape[0], tile_group=tile_group)
+        else:
+            y = grouped_gemm_rows(x, w, offsets, trans_b=True, tile_group=tile_group)
         ctx.save_for_backward(x, w, offsets, tile_group if tile_group is not None else offsets)
         ctx.w_ref = w
         return y
@@ -319,33 +328,36 @@ class _GroupedLinearFn(torch.autograd.Function):
                 ctx.w_ref.grad_added_to_main_grad = True
             else:
                 dw = grouped_gemm_reduce(gy, x, offsets, G)
-        return dx, dw, None, None
+        return dx, dw, None, None, None
 
 
-def grouped_linear(x, w, offsets, tile_group=None):
-    return _GroupedLinearFn.apply(x, w, offsets, tile_group)
+def grouped_linear(x, w, offsets, tile_group=None, fp8: bool = False):
+    return _GroupedLinearFn.apply(x, w, offsets, tile_group, fp8)
 
 
-def _routed_ffn_reference_alt(x, expert_ids, weights, w1, w2, limit: float = 0.0, max_slots: int | None = None):
+def _routed_ffn_reference_alt(x, expert_ids, weights, w1, w2, limit: float = 0.0, max_slots: int | None = None,
+                              fp8: bool = False):
     return routed_grouped_ffn_reference(x, expert_ids, weights, w1, w2, limit)
 
 
 @optimizable({"reference": _routed_ffn_reference_alt})
-def routed_grouped_ffn(x, expert_ids, weights, w1, w2, limit: float = 0.0, max_slots: int | None = None):
+def routed_grouped_ffn(x, expert_ids, weights, w1, w2, limit: float = 0.0, max_slots: int | None = None,
+                       fp8: bool = False):
     """Top-k routed SwiGLU experts on one rank.
 
     ``x [T,H]``, ``expert_ids [T,k]`` (local expert index or -1), ``weights [T,k]``,
     ``w1 [E, 2F, H]`` (gate | up), ``w2 [E, H, F]``.  Returns ``[T,H]``.  ``max_slots``: an upper bound of the
     slots with an id >= 0 when the caller knows one (rows of a sparse receive buffer); it sizes the expert-major
-    buffers, which otherwise take the worst case ``T*k``."""
+    buffers, which otherwise take the worst case ``T*k``.  ``fp8``: forward products of both expert GEMMs in
+    block-scaled e4m3 (``ops/fp8.py``), backward in bf16."""
     E = w1.shape[0]
     T, K = expert_ids.shape
     if _native_rows(x) and K <= 16:
         plan = RoutePlan(expert_ids, E, None if max_slots is None else padded_rows(min(max_slots, T * K), E))
         xe = moe_scatter(x, plan.dest, plan.rows, plan)
-        h = grouped_linear(xe, w1, plan.offsets, plan.tile_group)
+        h = grouped_linear(xe, w1, plan.offsets, plan.tile_group, fp8)
         a = swiglu(h, limit)
-        y = grouped_linear(a, w2, plan.offsets, plan.tile_group)
+        y = grouped_linear(a, w2, plan.offsets, plan.tile_group, fp8)
         return moe_weighted_gather(y, plan.dest, weights, plan)
     dest, offsets, _ = index_compute(expert_ids, E)
     rows = padded_rows(T * K, E)
