@@ -14,6 +14,19 @@ def free_port() -> int:
         return s.getsockname()[1]
 
 
+def _build(make_tiny_exp, exp_kwargs):
+    exp_kwargs = dict(exp_kwargs)
+    extra = exp_kwargs.pop("set", {})                      # dotted config paths to set after the experiment is built
+    exp = make_tiny_exp(**exp_kwargs)
+    for path, value in extra.items():
+        node = exp
+        *parents, leaf = path.split(".")
+        for part in parents:
+            node = getattr(node, part)
+        setattr(node, leaf, value)
+    return exp
+
+
 def _worker(rank, world, port, exp_kwargs, steps, q):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
                       MASTER_PORT=str(port))
@@ -23,15 +36,7 @@ def _worker(rank, world, port, exp_kwargs, steps, q):
         from tests.tiny_exp import make_tiny_exp
 
         PM.initialize(backend="gloo")
-        exp_kwargs = dict(exp_kwargs)
-        extra = exp_kwargs.pop("set", {})                  # dotted config paths to set after the experiment is built
-        exp = make_tiny_exp(**exp_kwargs)
-        for path, value in extra.items():
-            node = exp
-            *parents, leaf = path.split(".")
-            for part in parents:
-                node = getattr(node, part)
-            setattr(node, leaf, value)
+        exp = _build(make_tiny_exp, exp_kwargs)
         exp.seed = 0
         tr = exp.trainer_cfg.get_trainer_cls()(exp=exp)
         tr.before_train()
@@ -80,7 +85,7 @@ def run_single(exp_kwargs: dict, steps: int = 3):
     from tests.tiny_exp import make_tiny_exp
 
     os.environ.pop("WORLD_SIZE", None)
-    exp = make_tiny_exp(**exp_kwargs)
+    exp = _build(make_tiny_exp, exp_kwargs)
     exp.seed = 0
     tr = exp.trainer_cfg.get_trainer_cls()(exp=exp)
     tr.before_train()

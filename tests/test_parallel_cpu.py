@@ -84,3 +84,16 @@ def test_detailed_gradient_norms_agree_on_every_rank_and_add_up(layout):
         assert norms["parts"] == pytest.approx(parts0, rel=1e-6)
         total = norms["total"][-1]
         assert sum(v * v for v in norms["parts"].values()) ** 0.5 == pytest.approx(total, rel=1e-4)
+
+
+def test_tp2_cp2_pp2_with_muon_on_eight_ranks_matches_one_process():
+    """The layout of the long-context configuration (TP=2 x CP=2 x PP=2, 1F1B with 4 micro-batches) with Muon on the
+    2-D hidden matrices: the last pipeline stage reports the loss curve of the single-process run."""
+    from steptronoss_b200.exp.optimizer import MuonConfig
+
+    muon = {"optimizer_cfg.optimizer_cfg": MuonConfig, "optimizer_cfg.optimizer_cfg.muon_run_ns_in_fp16": False}
+    base = dict(BASE, gbs=4, layers=4, seq=256, max_doc=256, lr=2e-3)
+    ref = run_single(dict(base, set=dict(muon)))
+    res = run_ranks(8, dict(base, tp=2, sp=True, cp=2, pp=2, set=dict(muon)), timeout=600)
+    last = res[-1]
+    assert _close(last[1], ref[0], 5e-5), (last[1], ref[0])
