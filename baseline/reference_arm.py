@@ -103,7 +103,7 @@ def _run(args) -> None:
         model_cfg_cls = model_file.Qwen3_8BConfig
 
     sys.path.insert(0, os.path.dirname(HERE))
-    from bench import OPTIMIZER_TEXT, ClockSampler, default_parallelism, model_flops_per_token, parse_parallelism
+    from bench import OPTIMIZER_TEXT, ClockSampler, default_parallelism, global_batch, model_flops_per_token, parse_parallelism
     from steptronoss_b200.data.synthetic import make_packed_sample  # data generator only (numpy)
 
     par_text = args.parallelism or (f"ep{world}dp{world}" if moe else default_parallelism(world))
@@ -184,7 +184,7 @@ def _run(args) -> None:
             self.model_cfg.recompute = True if rec == "full" else ([] if rec == "none" else rec.split(","))
             self._recompute_text = rec
             t = self.trainer_cfg
-            t.global_batch_size = args.seqs_per_gpu * world
+            t.global_batch_size = global_batch(args, world)
             t.global_seq_length = seq
             t.micro_batch_size = 1
             t.train_iters = 10 ** 9

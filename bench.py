@@ -33,7 +33,7 @@ sys.path.insert(0, ROOT)
 METRIC_TEXT = {"dense": "tokens/s/box (Qwen3-8B dense training, all GPUs of the node)",
                "moe": "tokens/s/box (Qwen3-30B-A3B-shape MoE pretraining, all GPUs of the node)"}
 MODEL_TEXT = {"dense": "Qwen3-8B", "moe": "Qwen3-30B-A3B-shape MoE"}
-DATA_TEXT = {"dense": "synthetic packed documents (lengths U[256,8192], uniform token ids), random N(0,0.02) init",
+DATA_TEXT = {"dense": "synthetic packed documents (lengths U[256,seq_len], uniform token ids), random N(0,0.02) init",
              "moe": "synthetic sequences of one document each (uniform token ids), random N(0,0.02) init"}
 L2_TEXT = "inputs larger than L2 (each step streams > 100 GB)"
 
@@ -65,6 +65,9 @@ def parse():
                     help="muon: Newton-Schulz updates for the 2-D hidden matrices, AdamW for the rest")
     ap.add_argument("--seqs-per-gpu", type=int, default=None,
                     help="sequences per GPU per step (global batch = this x N); default 8 (dense) / 32 (MoE)")
+    ap.add_argument("--global-batch", type=int, default=None,
+                    help="sequences per optimizer step of the whole job (overrides --seqs-per-gpu; e.g. 4 micro-batches "
+                         "of one long sequence on a tp2cp2pp2 layout whose data-parallel degree is 1)")
     ap.add_argument("--seq-len", type=int, default=None, help="default 8192 (dense) / 4096 (MoE)")
     ap.add_argument("--seqs-per-micro-batch", type=int, default=1,
                     help="sequences packed into one forward/backward pass (as separate documents: attention, positions "
@@ -137,6 +140,10 @@ OPTIMIZER_TEXT = {"adam": "Adam fp32 master+state, ZeRO-1",
                   "muon": "Muon (2-D hidden matrices) + AdamW, fp32 master+state, ZeRO-1"}
 
 
+def global_batch(args, world: int) -> int:
+    return args.global_batch if args.global_batch else args.seqs_per_gpu * world
+
+
 def default_parallelism(n: int) -> str:
     tp = min(n, 4)
     dp = n // tp
@@ -199,7 +206,7 @@ def run_ours(args):
     tc = exp.trainer_cfg
     # a micro-batch of M sequences is one packed row of M x seq_len tokens whose documents are at most seq_len long
     tc.global_seq_length = args.seq_len * args.seqs_per_micro_batch
-    tc.global_batch_size = args.seqs_per_gpu * world // args.seqs_per_micro_batch
+    tc.global_batch_size = global_batch(args, world) // args.seqs_per_micro_batch
     tc.train_iters = 10**9
     tc.writer_backend = []
     tc.log_interval = 10**9
@@ -242,7 +249,12 @@ def run_ours(args):
             # across N = 1, 2, 4, 8 to bf16 rounding.
             vals = GlobalMetrics.metrics["lm_loss"].values if "lm_loss" in GlobalMetrics.metrics else []
             if vals:
-                loss_step0 = float(torch.as_tensor(vals[0]).float().mean().item())
+                first = torch.as_tensor(vals[0]).float().mean().to(dev)
+                if par["cp"] > 1:   # a CP rank holds the sum over its own tokens divided by the count of all tokens
+                    from steptronoss_b200.parallel.state import PM
+
+                    dist.all_reduce(first, group=PM.group_of("CP"))
+                loss_step0 = float(first.item())
     barrier_sync()
     native.raise_if_kernel_error()
 
@@ -338,7 +350,7 @@ def run_ours(args):
         "dtype": "bf16",
         "data": DATA_TEXT[kind],
         "mfu_of_measured_sustained_bf16": value * fpt / (peak * world),
-        "config": {"model": MODEL_TEXT[kind], "layers": mc.num_layers, "global_batch": args.seqs_per_gpu * world,
+        "config": {"model": MODEL_TEXT[kind], "layers": mc.num_layers, "global_batch": global_batch(args, world),
                    "seq_len": args.seq_len, "micro_batch": args.seqs_per_micro_batch, "parallelism": par_text,
                    "optimizer": OPTIMIZER_TEXT[args.optimizer], "recompute": rec, "l2": L2_TEXT},
         "implementation": {"attention": "tcgen05 flash attention (csrc/attention_sm100.cu)",

@@ -104,6 +104,10 @@ class MoEGate(nn.Module):
         self.weight.sequence_parallel = bool(cfg.tp_cfg.sequence_parallel)
 
     def forward(self, x):
+        if x.is_cuda and x.dtype == torch.bfloat16 and self.weight.dtype == torch.bfloat16:
+            # one tcgen05 GEMM with fp32 accumulators written out as fp32: for bf16 operands this is the product that
+            # ``fp32_gate_output`` asks for (the conversions to fp32 are exact), and without the flag it saves the cast
+            return linear(x, self.weight, out_dtype=torch.float32)
         if self.fp32:
             return torch.nn.functional.linear(x.float(), self.weight.float())
         return linear(x, self.weight).float()

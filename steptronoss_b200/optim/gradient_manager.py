@@ -191,17 +191,30 @@ class BaseGradientManager:
             self._gather_event = None
 
     def _allreduce_tagged(self, tag: str, group_name: str = "TP") -> None:
+        """Sum the gradients of the parameters that carry ``tag`` over ``group_name`` (norm weights under sequence
+        parallelism: every TP rank saw its own rows).  A bucket all of whose parameters carry the tag is reduced in
+        place as one flat buffer (the usual case: the bucket of TP-replicated parameters); what is left goes through
+        one packed buffer and one multi-tensor copy back."""
         if PM.size_of(group_name) == 1:
             return
-        grads = [p.main_grad for _, p in self.named_params if getattr(p, tag, False) and p.requires_grad]
-        if not grads:
+        group = PM.group_of(group_name)
+        rest = []
+        for b in self.buckets.values():
+            tagged = [s.param for s in b.slots if getattr(s.param, tag, False) and s.param.requires_grad]
+            if not tagged:
+                continue
+            if len(tagged) == len(b.slots) and b.grad_buf is not None:
+                dist.all_reduce(b.grad_buf, group=group)
+            else:
+                rest += [p.main_grad for p in tagged]
+        in_buckets = {id(s.param) for b in self.buckets.values() for s in b.slots}
+        rest += [p.main_grad for _, p in self.named_params
+                 if getattr(p, tag, False) and p.requires_grad and id(p) not in in_buckets]
+        if not rest:
             return
-        flat = torch.cat([g.reshape(-1) for g in grads])
-        dist.all_reduce(flat, group=PM.group_of(group_name))
-        off = 0
-        for g in grads:
-            g.copy_(flat[off : off + g.numel()].view_as(g))
-            off += g.numel()
+        flat = torch.cat([g.reshape(-1) for g in rest])
+        dist.all_reduce(flat, group=group)
+        torch._foreach_copy_(rest, [v.view_as(g) for v, g in zip(flat.split([g.numel() for g in rest]), rest)])
 
     def _scale_expert_grads(self) -> None:
         """Expert parameters see tokens of the whole EP group: the reference rescales their gradients
