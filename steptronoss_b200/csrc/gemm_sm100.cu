@@ -40,6 +40,13 @@ struct GemmParams {
   long long group_c_stride;  // mode 2: elements between consecutive groups' C
   int* status;
   float alpha;
+  // dense mode, bf16 output written by TMA: C = alpha * A B^T + beta * addend (addend may be C itself)
+  const __nv_bfloat16* addend;
+  long long ld_add;
+  float beta;
+  // dense mode with a symmetric result (X X^T, A^2 of a symmetric A): tiles that lie entirely below the diagonal
+  // are not computed; the caller mirrors the upper triangle afterwards
+  int upper_only;
 };
 
 template <int BLOCK_N>
@@ -60,8 +67,26 @@ struct TileCoord {
 
 // Tile order: row tiles are walked in bands of kBand so that the CTAs running at the same time
 // share A and B tiles in L2.
-__device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int num_m, int num_n, TileCoord& t) {
+__device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int num_m, int num_n, TileCoord& t,
+                                            int block_n = 0) {
   constexpr int kBand = 8;
+  if (p.upper_only && block_n > 0) {
+    // compact enumeration of the tiles that reach the diagonal, row tile after row tile, so that the CTAs of the
+    // persistent grid get equal shares of real work
+    int rem = tile;
+    t.m_tile = 0; t.n_tile = 0;
+    for (int i = 0; i < num_m; ++i) {
+      const int n_min = (i * kBlockM) / block_n;
+      const int cnt = num_n - n_min;
+      if (rem < cnt) { t.m_tile = i; t.n_tile = n_min + rem; break; }
+      rem -= cnt;
+    }
+    t.k_begin = 0;
+    t.k_blocks = (p.K + kBlockK - 1) / kBlockK;
+    t.group = 0;
+    t.valid = true;
+    return;
+  }
   if (p.mode == 2) {
     const int per_group = num_m * num_n;
     t.group = tile / per_group;
@@ -91,6 +116,13 @@ __device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int n
   }
 }
 
+// Number of 128 x block_n tiles of a square result that reach the diagonal or lie above it.
+__host__ __device__ inline int upper_tile_count(int num_m, int num_n, int block_n) {
+  int total = 0;
+  for (int i = 0; i < num_m; ++i) total += num_n - (i * kBlockM) / block_n;
+  return total;
+}
+
 template <int BLOCK_N, bool A_MN, bool B_MN, bool OUT_F32, bool ACCUM>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -112,7 +144,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
   const int num_m = (p.M + kBlockM - 1) / kBlockM;
   const int num_n = (p.N + BLOCK_N - 1) / BLOCK_N;
-  const int num_tiles = num_m * num_n * (p.mode == 2 ? p.num_groups : 1);
+  const int num_tiles = p.upper_only ? upper_tile_count(num_m, num_n, BLOCK_N)
+                                     : num_m * num_n * (p.mode == 2 ? p.num_groups : 1);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -143,7 +176,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t it = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
         TileCoord t;
-        decode_tile(p, tile, num_m, num_n, t);
+        decode_tile(p, tile, num_m, num_n, t, BLOCK_N);
         if (!t.valid) continue;
         const int m0 = t.m_tile * kBlockM;
         const int n0 = t.n_tile * BLOCK_N;
@@ -185,7 +218,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t it = 0, local_tile = 0;
       for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
         TileCoord t;
-        decode_tile(p, tile, num_m, num_n, t);
+        decode_tile(p, tile, num_m, num_n, t, BLOCK_N);
         if (!t.valid) continue;
         const int acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
@@ -235,7 +268,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t store_count = 0;
     for (int tile = blockIdx.x; tile < num_tiles && !*abort_flag; tile += gridDim.x) {
       TileCoord t;
-      decode_tile(p, tile, num_m, num_n, t);
+      decode_tile(p, tile, num_m, num_n, t, BLOCK_N);
       if (!t.valid) continue;
       const int acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
@@ -285,11 +318,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               chunks[j].w = __float_as_uint(zero_acc ? 0.f : __uint_as_float(v[4 * j + 3]) * p.alpha);
             }
           } else {
+            // optional scaled addend: this lane's row, the 64 columns of the chunk (rows and columns past the matrix
+            // are clipped by the TMA store, so they only have to be kept from being read)
+            const int arow = row0 + lane;
+            const bool add_ok = p.addend != nullptr && arow < p.M;
+            const __nv_bfloat16* arow_ptr = p.addend + static_cast<long long>(add_ok ? arow : 0) * p.ld_add + col0;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               float f[8];
 #pragma unroll
               for (int q = 0; q < 8; ++q) f[q] = zero_acc ? 0.f : __uint_as_float(v[8 * j + q]) * p.alpha;
+              if (add_ok && col0 + 8 * j < p.N) {
+                const uint4 d = *reinterpret_cast<const uint4*>(arow_ptr + 8 * j);
+                f[0] = fmaf(p.beta, bf16_lo(d.x), f[0]); f[1] = fmaf(p.beta, bf16_hi(d.x), f[1]);
+                f[2] = fmaf(p.beta, bf16_lo(d.y), f[2]); f[3] = fmaf(p.beta, bf16_hi(d.y), f[3]);
+                f[4] = fmaf(p.beta, bf16_lo(d.z), f[4]); f[5] = fmaf(p.beta, bf16_hi(d.z), f[5]);
+                f[6] = fmaf(p.beta, bf16_lo(d.w), f[6]); f[7] = fmaf(p.beta, bf16_hi(d.w), f[7]);
+              }
               chunks[j].x = pack_bf16(f[0], f[1]); chunks[j].y = pack_bf16(f[2], f[3]);
               chunks[j].z = pack_bf16(f[4], f[5]); chunks[j].w = pack_bf16(f[6], f[7]);
             }
@@ -366,7 +411,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   }
   const int num_m = (p.M + kBlockM - 1) / kBlockM;
   const int num_n = (p.N + BLOCK_N - 1) / BLOCK_N;
-  const long long tiles = static_cast<long long>(num_m) * num_n * (p.mode == 2 ? p.num_groups : 1);
+  const long long tiles = p.upper_only ? upper_tile_count(num_m, num_n, BLOCK_N)
+                                       : static_cast<long long>(num_m) * num_n * (p.mode == 2 ? p.num_groups : 1);
   if (tiles == 0) return 0;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
   kern<<<grid, kGemmThreads, S::kTotal, st>>>(ta, tb, tc, C, p);
@@ -405,16 +451,68 @@ static int dispatch_major(const CUtensorMap& ta, const CUtensorMap& tb, void* C,
 // the narrow tile only pays off when N itself is narrow.
 static int choose_block_n(long long /*num_m*/, int N, int /*groups*/) { return N > 128 ? 256 : 128; }
 
+// C[r][c] = C[c][r] for c < r: completes a symmetric matrix whose upper triangle (by tiles) was computed.
+// One CTA of 32 x 8 threads per 32 x 32 block on or below the diagonal.
+__global__ void __launch_bounds__(256)
+mirror_upper_kernel(__nv_bfloat16* __restrict__ C, int n, long long ld) {
+  __shared__ __nv_bfloat16 tile[32][33];
+  const int bi = blockIdx.y, bj = blockIdx.x;     // destination block (rows bi, columns bj)
+  if (bj > bi) return;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  // source block (rows bj, columns bi), read row-wise
+  for (int r = ty; r < 32; r += 8) {
+    const int sr = bj * 32 + r, sc = bi * 32 + tx;
+    tile[r][tx] = (sr < n && sc < n) ? C[static_cast<long long>(sr) * ld + sc] : __float2bfloat16(0.f);
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    const int dr = bi * 32 + r, dc = bj * 32 + tx;
+    if (dr < n && dc < n && dc < dr) C[static_cast<long long>(dr) * ld + dc] = tile[tx][r];
+  }
+}
+
 }  // namespace stb
 
 using namespace stb;
 
+extern "C" int stb_mirror_upper_bf16(void* C, int n, long long ld, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const unsigned blocks = static_cast<unsigned>((n + 31) / 32);
+  mirror_upper_kernel<<<dim3(blocks, blocks), 256, 0, stream>>>(static_cast<__nv_bfloat16*>(C), n, ld);
+  return -static_cast<int>(cudaGetLastError());
+}
+
 // A: K-major -> stored [M][lda]; MN-major -> stored [K][lda].   (lda/ldb/ldc in elements)
 // B: K-major -> stored [N][ldb]; MN-major -> stored [K][ldb].
 // Requirements: 16-byte aligned bases, lda/ldb multiples of 8, N and ldc multiples of 8.
+// The same with C = alpha * A B^T + beta * addend (bf16 [M][ld_add], may be C; bf16 output only) and, for a square
+// symmetric result, only the tiles that reach the diagonal or lie above it (upper_only; mirror afterwards).
+extern "C" int stb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                             int a_mn_major, int b_mn_major, int out_f32, int accumulate, float alpha, int* status,
+                             cudaStream_t stream);
+static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                          int a_mn_major, int b_mn_major, int out_f32, int accumulate, float alpha, const void* addend,
+                          long long ld_add, float beta, int upper_only, int* status, cudaStream_t stream);
+
+extern "C" int stb_gemm_bf16_ex(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                                int a_mn_major, int b_mn_major, float alpha, const void* addend, long long ld_add,
+                                float beta, int upper_only, int* status, cudaStream_t stream) {
+  if (addend != nullptr && ((ld_add & 7) || (reinterpret_cast<uintptr_t>(addend) & 15))) return -kErrBadArgument;
+  if (upper_only && M != N) return -kErrBadArgument;
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, 0, 0, alpha, addend, ld_add, beta,
+                        upper_only, status, stream);
+}
+
 extern "C" int stb_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
                              int a_mn_major, int b_mn_major, int out_f32, int accumulate, float alpha, int* status,
                              cudaStream_t stream) {
+  return gemm_bf16_impl(A, B, C, M, N, K, lda, ldb, ldc, a_mn_major, b_mn_major, out_f32, accumulate, alpha, nullptr, 0,
+                        0.f, 0, status, stream);
+}
+
+static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc,
+                          int a_mn_major, int b_mn_major, int out_f32, int accumulate, float alpha, const void* addend,
+                          long long ld_add, float beta, int upper_only, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (N & 7) || (lda & 7) || (ldb & 7) || (ldc & 3)) return -kErrBadArgument;
   const int bn = choose_block_n((M + kBlockM - 1) / kBlockM, N, 1);
@@ -428,6 +526,7 @@ extern "C" int stb_gemm_bf16(const void* A, const void* B, void* C, int M, int N
   if (r) return r;
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.mode = 0; p.status = status; p.alpha = alpha;
+  p.addend = static_cast<const __nv_bfloat16*>(addend); p.ld_add = ld_add; p.beta = beta; p.upper_only = upper_only;
   return bn == 256 ? dispatch_major<256>(ta, tb, C, p, a_mn_major, b_mn_major, out_f32, accumulate, stream)
                    : dispatch_major<128>(ta, tb, C, p, a_mn_major, b_mn_major, out_f32, accumulate, stream);
 }

@@ -47,8 +47,16 @@ def gemm(
     out_dtype: torch.dtype | None = None,
     accumulate: bool = False,
     alpha: float = 1.0,
+    addend: torch.Tensor | None = None,
+    beta: float = 1.0,
+    upper_only: bool = False,
 ) -> torch.Tensor:
     """``C[M,N] (+)= alpha * A * B^T`` in the operand conventions of the kernel.
+
+    ``addend`` (bf16 ``[M, N]``): ``C = alpha * A B^T + beta * addend`` in the epilogue of the product (bf16 output,
+    no ``accumulate``).  ``upper_only``: the result is known to be symmetric (``X X^T``, the square of a symmetric
+    matrix, possibly plus a symmetric addend); only the tiles that reach the diagonal are computed and the lower
+    triangle is filled from the upper one by a second small kernel.
 
     ``a`` is stored ``[M, K]`` (K-major) or ``[K, M]`` (``a_mn_major``); ``b`` is stored ``[N, K]``
     (K-major) or ``[K, N]`` (``b_mn_major``).  Row strides may exceed the row length (views of a
@@ -76,6 +84,8 @@ def gemm(
         else:
             res = torch.matmul(am.float(), bm.float())
         res = res * alpha if alpha != 1.0 else res
+        if addend is not None:
+            res = res + beta * addend.float()
         if accumulate:
             out.add_(res.to(out.dtype))
         else:
@@ -86,6 +96,23 @@ def gemm(
     if a.stride(-1) != 1 or b.stride(-1) != 1 or out.stride(-1) != 1:
         raise ValueError("last dimension of every GEMM operand must be contiguous")
     lib = native.load()
+    if addend is not None or upper_only:
+        if accumulate or out.dtype != torch.bfloat16:
+            raise ValueError("addend / upper_only take a bf16 output without accumulate")
+        if addend is not None and (addend.dtype != torch.bfloat16 or addend.shape != out.shape or addend.stride(-1) != 1):
+            raise ValueError("addend must be a bf16 [M, N] matrix with a contiguous last dimension")
+        rc = lib.stb_gemm_bf16_ex(
+            a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
+            int(a_mn_major), int(b_mn_major), float(alpha), native.ptr(addend),
+            addend.stride(0) if addend is not None else 0, float(beta), int(upper_only),
+            native.status_word(a.device).data_ptr(), native.stream(),
+        )
+        native.check(rc, f"gemm M={M} N={N} K={K} (addend / upper_only)")
+        count_launch()
+        if upper_only:
+            native.check(lib.stb_mirror_upper_bf16(out.data_ptr(), M, out.stride(0), native.stream()), "mirror_upper")
+            count_launch()
+        return out
     rc = lib.stb_gemm_bf16(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, a.stride(0), b.stride(0), out.stride(0),
         int(a_mn_major), int(b_mn_major), int(out.dtype == torch.float32), int(accumulate), float(alpha),

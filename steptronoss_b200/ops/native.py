@@ -60,6 +60,8 @@ P, I, L, F = c_void_p, c_int, c_longlong, c_float
 _SIGNATURES = {
     "stb_sm_count": [],
     "stb_gemm_bf16": [P, P, P, I, I, I, I, I, I, I, I, I, I, F, P, P],
+    "stb_gemm_bf16_ex": [P, P, P, I, I, I, I, I, I, I, I, F, P, L, F, I, P, P],
+    "stb_mirror_upper_bf16": [P, I, L, P],
     "stb_gemm_bf16_grouped_rows": [P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P],
     "stb_gemm_bf16_grouped_reduce": [P, P, P, P, I, I, I, I, I, I, I, I, I, P, P],
     "stb_rmsnorm_fwd": [P, P, P, P, L, I, L, L, F, I, P],

@@ -6,7 +6,8 @@ ships (``steptronoss/optimizer/_helpers.py:36-98``) together with its non-orthog
 alternatives (SVD, double normalisation, Sinkhorn-Knopp, dualisations).
 
 On CUDA the three products of an iteration are tcgen05 GEMMs (``A`` and ``A^2`` are symmetric, so
-both are plain ``X X^T``-type products without a transposed copy); the iteration runs in bf16.  The
+both are plain ``X X^T``-type products without a transposed copy, computed on the upper triangle of
+tiles only, with the scaled adds of the polynomial in the epilogue); the iteration runs in bf16.  The
 reference casts to fp16 for the same step ("run_ns_in_fp16"); bf16 is what the sm_100a kernel takes
 and has the wider exponent range.
 """
@@ -64,14 +65,30 @@ def _schedule(coeffs, steps: int):
 
 
 def _ns_native_2d(X: torch.Tensor, table) -> torch.Tensor:
-    """X ``[m, n]`` bf16 CUDA with ``m <= n`` and both multiples of 8."""
+    """X ``[m, n]`` bf16 CUDA with ``m <= n`` and both multiples of 8.
+
+    ``A = X X^T`` and ``b A + c A^2`` are symmetric: their products compute only the tiles that reach the diagonal
+    (44 % of the tiles of a 4096 x 4096 result lie below it) and a small kernel mirrors the rest; the scaled adds
+    ``b A + ...`` and ``a X + ...`` run in the epilogue of the products."""
+    upper = _upper_triangle_pays(X.shape[0])
     for a, b, c in table:
-        A = gemm(X, X)                                   # X X^T            [m, m]
-        A2 = gemm(A, A)                                  # A A^T = A^2 (A symmetric)
-        B = torch.add(A2, A, alpha=b / c).mul_(c)        # b A + c A^2
-        BX = gemm(B, X, b_mn_major=True)                 # B X              [m, n]
-        X = BX.add_(X, alpha=a)
+        A = gemm(X, X, upper_only=upper)                                  # X X^T                 [m, m]
+        B = gemm(A, A, alpha=c, addend=A, beta=b, upper_only=upper)       # c A A^T + b A  (A symmetric)
+        X = gemm(B, X, b_mn_major=True, addend=X, beta=a)                 # B X + a X             [m, n]
     return X
+
+
+def _upper_triangle_pays(m: int) -> bool:
+    """Skipping the tiles below the diagonal only helps when it saves a wave of the persistent grid (a 3072-wide
+    result has 288 tiles of 128 x 256, 156 of them on or above the diagonal: two waves of 148 SMs either way)."""
+    from ..ops import native
+
+    sms = native.load().stb_sm_count() or 148
+    num_m, block_n = -(-m // 128), 256 if m > 128 else 128
+    num_n = -(-m // block_n)
+    full = num_m * num_n
+    upper = sum(num_n - (i * 128) // block_n for i in range(num_m))
+    return -(-upper // sms) < -(-full // sms)
 
 
 def zeropower(G: torch.Tensor, steps: int = 5, run_ns_in_fp16: bool = True, coeffs=ZEROPOWER_COEFFS["default"]):

@@ -118,3 +118,36 @@ def test_grouped_gemm_rows_and_reduce():
     dw = grouped_gemm_reduce(g_out, x, offsets, G)   # [G, N, K]
     refw = torch.stack([g_out[offs[g]:offs[g + 1]].float().t() @ x[offs[g]:offs[g + 1]].float() for g in range(G)])
     _check(dw, refw, 384)
+
+
+@pytest.mark.parametrize("n,k", [(256, 128), (1024, 384), (2304, 512), (520, 256)])
+def test_symmetric_product_with_scaled_addend_on_the_upper_triangle(n, k):
+    """``alpha X X^T + beta D`` with only the tiles that reach the diagonal computed and the rest mirrored."""
+    from steptronoss_b200.ops.gemm import gemm
+
+    torch.manual_seed(n)
+    x = (torch.randn(n, k, device="cuda") * 0.1).to(torch.bfloat16)
+    d = torch.randn(n, n, device="cuda")
+    d = ((d + d.t()) * 0.5).to(torch.bfloat16)
+    want = 0.75 * (x.float() @ x.float().t()) + (-1.5) * d.float()
+    full = gemm(x, x, alpha=0.75, addend=d, beta=-1.5)
+    upper = gemm(x, x, alpha=0.75, addend=d, beta=-1.5, upper_only=True)
+    torch.cuda.synchronize()
+    assert (full.float() - want).abs().max() < 3e-2 * want.abs().max()
+    assert torch.equal(upper, upper.t().contiguous())
+    assert (upper.float() - want).abs().max() < 3e-2 * want.abs().max()
+    iu = torch.triu_indices(n, n, device="cuda")
+    assert torch.equal(upper[iu[0], iu[1]], full[iu[0], iu[1]])     # the computed triangle is the same product
+
+
+def test_newton_schulz_on_the_gpu_matches_the_fp32_iteration():
+    from steptronoss_b200.optim.zeropower import ZEROPOWER_COEFFS, zeropower
+
+    torch.manual_seed(0)
+    for shape in ((512, 768), (1280, 512)):
+        g = torch.randn(*shape, device="cuda", dtype=torch.bfloat16)
+        got = zeropower(g, 5, True, ZEROPOWER_COEFFS["default"]).float()
+        want = zeropower(g.float().cpu(), 5, False, ZEROPOWER_COEFFS["default"]).to("cuda")
+        assert ((got - want).norm() / want.norm()).item() < 5e-2
+        s = torch.linalg.svdvals(got)
+        assert s.max() < 1.3 and s.min() > 0.5
