@@ -60,6 +60,7 @@ __global__ void __launch_bounds__(128, 1) mma_kernel(int groups, long long* out)
         else if (mode == 2) { umma_bf16(tmem, da, dbk, id_kk, k > 0); umma_bf16_a_tmem(tmem + 256, tmem + 128 + k * 8, dbmn, id_kmn, 1); }
         else if (mode == 3) umma_bf16(tmem, da, dbk, id_256, k > 0);
         else if (mode == 4) umma_bf16_a_tmem(tmem, tmem + 384 + k * 8, dbk, id_64, k > 0);
+        else if (mode == 8) umma_bf16(tm, da, dbk, id_64, k > 0);
         else umma_bf16_a_tmem(tmem, tmem + 384 + k * 8, dbk, id_kk, k > 0);
       }
     }
@@ -100,6 +101,8 @@ int main() {
   run<2, 1>("alternate", 2 * 128. * 128 * 16 * 2, d);
   run<3, 1>("128x256x16 A smem B smem", 128. * 256 * 16 * 2, d);
   run<5, 1>("128x128x16 A tmem B smem(K)", 128. * 128 * 16 * 2, d);
+  run<8, 1>("128x64x16 A smem B smem", 128. * 64 * 16 * 2, d);
+  run<4, 1>("128x64x16 A tmem B smem", 128. * 64 * 16 * 2, d);
   run<6, 1>("attention helper QK, runtime stage, commit per tile", 128. * 128 * 16 * 2, d);
   run<7, 1>("attention helper PV (B MN-major), runtime stage", 128. * 128 * 16 * 2, d);
   return 0;

@@ -22,6 +22,8 @@
 // which keeps the gradients bitwise reproducible.
 #include "attention_common.cuh"
 
+#include <cstdlib>
+
 namespace stb {
 
 constexpr int kSB = 64;                       // streamed rows per iteration
@@ -128,9 +130,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
   uint64_t* g_full = bars + 1;                  // [3]
   uint64_t* g_empty = bars + 4;                 // [3]
   uint64_t* sdp_full = bars + 7;                // [2] S', dP' in TMEM
-  uint64_t* pds_full = bars + 9;                // [2] P', dS' in smem (128 arrivals)
+  uint64_t* pds_full = bars + 9;                // [2] P', dS' in smem (one arrival per softmax warp)
   uint64_t* acc_full = bars + 11;
-  uint64_t* f_tmem = bars + 12;                 // dQ pass: Q and dO copied into TMEM (256 arrivals)
+  uint64_t* f_tmem = bars + 12;                 // dQ pass: Q and dO copied into TMEM (one arrival per softmax warp)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -172,10 +174,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&pds_full[i], 256);
+      mbar_init(&pds_full[i], 8);    // one arrival per softmax warp
     }
     mbar_init(acc_full, 1);
-    mbar_init(f_tmem, 256);
+    mbar_init(f_tmem, 8);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -294,7 +296,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
       }
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(f_tmem);
+      mbar_arrive_warp(f_tmem);
     }
     // All softmax threads run every iteration (the dK/dV pass meets at a named barrier in each one); after
     // a timed-out wait the remaining waits are skipped, so a failure cannot strand the other threads.
@@ -321,6 +323,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
         asm volatile("bar.sync 1, 256;" ::: "memory");
       }
       if (ok) ok = mbar_wait(&sdp_full[buf], (it >> 1) & 1);
+      ok = __all_sync(0xffffffffu, ok);             // warp-wide TMEM loads and the warp's single arrival follow
       if (!ok) continue;
       tc_fence_after();
       uint32_t sv[32], dv[32];
@@ -355,7 +358,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmap_f1, const __grid_consta
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(&pds_full[buf]);
+      mbar_arrive_warp(&pds_full[buf]);
     }
     if (ok && iters > 0 && !*abort_flag) ok = mbar_wait(acc_full, 0);
     if (!ok) { report_error(p.status, kErrSoftmaxWait); *abort_flag = 1; }
@@ -438,6 +441,270 @@ attn_dkv_reduce_kernel(const float* __restrict__ part, int splits, long long tot
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// dQ pass with 128-key tiles.
+//
+// A 128x64x16 step reads its A operand for 64 columns of output only and runs at 54 % (A in shared memory) or 72 %
+// (A in TMEM) of the tensor rate, a 128x128x16 step at 100 % (`benchmarks/micro/umma_rate.cu`).  This kernel
+// therefore streams K / V in tiles of 128 keys: S = Q K^T and dP = dO V^T are 128x128x128 products with Q and dO in
+// TMEM, dQ += dS K takes dS [128 q][128 keys] from shared memory.  S and dP have one TMEM buffer each; the softmax
+// threads free it as soon as their 64 columns are in registers, so the products of the next tile run while they
+// compute, and dS has one shared-memory tile whose previous consumer (dQ of the tile before) has long finished when
+// it is written again.
+//
+//   warp 0      TMA producer: Q, dO once; K_j, V_j (32 KB each) through a 3-stage ring whose third stage reuses the
+//               Q / dO landing zone once those are in TMEM
+//   warp 1      MMA issuer
+//   warps 2..17 warp w: TMEM lanes 32 * (w % 4) (its q rows), key columns 32 * ((w - 2) / 4) of every tile.  Sixteen
+//               softmax warps (four per scheduler) because the per-element chain scale -> exp2 -> subtract -> multiply
+//               is latency-bound: with eight warps the 64 columns of a thread took 2200 cycles per tile, twice
+//               what the exp2 pipe needs.
+// TMEM columns: S 0, dP 128, dQ 256, Q 384, dO 448.
+// dS of one thread's 32 columns of a tile: P = exp2(S c - lse), dS = P (dP - delta), packed in place into sv[0..15].
+template <bool MASK>
+__device__ __forceinline__ void dq_tile_math(const AttnParams& p, const SegInfo& s, uint32_t (&sv)[32],
+                                             const uint32_t (&dv)[32], int fi, int col0, float sl2, float row_lse2,
+                                             float row_delta) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    float pa = exp2f(fmaf(__uint_as_float(sv[2 * i]), sl2, -row_lse2));
+    float pb = exp2f(fmaf(__uint_as_float(sv[2 * i + 1]), sl2, -row_lse2));
+    if (MASK) {
+      if (!visible(p, s, fi, col0 + 2 * i)) pa = 0.f;
+      if (!visible(p, s, fi, col0 + 2 * i + 1)) pb = 0.f;
+    }
+    sv[i] = pack_bf16(pa * (__uint_as_float(dv[2 * i]) - row_delta), pb * (__uint_as_float(dv[2 * i + 1]) - row_delta));
+  }
+}
+
+constexpr int kDqThreads = 576;
+constexpr int kDqSoftmaxThreads = 512;
+constexpr int kDqStages = 3;
+constexpr int kDqSmem = 3 * 2 * kTileBytes + kTileBytes + 1024 + 256;   // ring (stage 2 = Q | dO zone) + dS
+
+__global__ void __launch_bounds__(kDqThreads, 1)
+attn_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_do,
+               const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
+               const AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sRing = smem;                                   // stage s: K at +0, V at +kTileBytes
+  uint8_t* sF = sRing + 2 * 2 * kTileBytes;                // Q | dO, later ring stage 2
+  uint8_t* sDS = sRing + 3 * 2 * kTileBytes;               // dS [128 q][128 keys] bf16, two 64-key slabs
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + kTileBytes);
+  uint64_t* f_full = bars;                 // Q, dO landed
+  uint64_t* f_tmem = bars + 1;             // Q, dO copied into TMEM (one arrival per softmax warp)
+  uint64_t* kv_full = bars + 2;            // [3]
+  uint64_t* kv_empty = bars + 5;           // [3]
+  uint64_t* sdp_full = bars + 8;           // S, dP of a tile are in TMEM
+  uint64_t* s_free = bars + 9;             // the softmax threads hold them in registers (one arrival per warp)
+  uint64_t* ds_full = bars + 10;           // dS of a tile is in shared memory (one arrival per warp)
+  uint64_t* ds_empty = bars + 11;          // dQ += dS K of a tile has finished
+  uint64_t* acc_full = bars + 12;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int blk = static_cast<int>(gridDim.y) - 1 - static_cast<int>(blockIdx.y);   // heavy causal blocks first
+  const int seg = p.blk_seg[blk];
+  if (seg < 0) return;
+  const SegInfo s = seg_info(p, seg);
+  const int row_abs0 = p.blk_row0[blk];
+  const int f0 = row_abs0 - s.q_begin;           // first q row of the block inside the segment
+  const int head = static_cast<int>(blockIdx.x);
+  const int kvh = head / (p.hq / p.hkv);
+  int g_hi = s.k_len;
+  if (p.causal) g_hi = min(g_hi, f0 + kBM + s.off);
+  const int g_lo = (p.window > 0) ? max(0, f0 + s.off - p.window + 1) : 0;
+  const int tb0 = g_lo / kBN;
+  const int iters = (g_hi > g_lo) ? (g_hi + kBN - 1) / kBN - tb0 : 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(f_full, 1);
+    mbar_init(f_tmem, kDqSoftmaxThreads / 32);      // barriers count warps: see mbar_arrive_warp
+    for (int i = 0; i < kDqStages; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(s_free, kDqSoftmaxThreads / 32);
+    mbar_init(ds_full, kDqSoftmaxThreads / 32);
+    mbar_init(ds_empty, 1);
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  auto stage_ptr = [&](int st) -> uint8_t* { return st == 2 ? sF : sRing + st * 2 * kTileBytes; };
+
+  if (warp == 0) {
+    if (lane == 0 && iters > 0) {
+      mbar_arrive_expect_tx(f_full, 2 * kTileBytes);
+      load_tile(sF, &tmap_q, f_full, head, row_abs0);
+      load_tile(sF + kTileBytes, &tmap_do, f_full, head, row_abs0);
+      for (int it = 0; it < iters && !*abort_flag; ++it) {
+        const int st = it % kDqStages;
+        bool ok = mbar_wait(&kv_empty[st], ((it / kDqStages) & 1) ^ 1);
+        if (ok && it == 2) ok = mbar_wait(f_tmem, 0);     // stage 2 is the Q | dO zone: free once they are in TMEM
+        if (!ok) {
+          report_error(p.status, kErrProducerWait);
+          *abort_flag = 1;
+          break;
+        }
+        uint8_t* dst = stage_ptr(st);
+        const int krow = key_row(p, s.k_begin + (tb0 + it) * kBN);
+        mbar_arrive_expect_tx(&kv_full[st], 2 * kTileBytes);
+        load_tile(dst, &tmap_k, &kv_full[st], kvh, krow);
+        load_tile(dst + kTileBytes, &tmap_v, &kv_full[st], kvh, krow);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && iters > 0) {
+      bool ok = mbar_wait(f_tmem, 0);
+      auto issue_sdp = [&](int it) -> bool {
+        const int st = it % kDqStages;
+        if (!mbar_wait(&kv_full[st], (it / kDqStages) & 1)) return false;
+        tc_fence_after();
+        const uint32_t kv = smem_u32(stage_ptr(st));
+        mma_128x128x128_ta<false>(tmem + 0, tmem + 384, kv, false);                  // S  = Q  K^T
+        mma_128x128x128_ta<false>(tmem + 128, tmem + 448, kv + kTileBytes, false);   // dP = dO V^T
+        umma_commit(sdp_full);
+        return true;
+      };
+      if (ok) ok = issue_sdp(0);
+      for (int it = 0; it < iters && ok && !*abort_flag; ++it) {
+        if (it + 1 < iters) {
+          ok = mbar_wait(s_free, it & 1);          // S, dP of tile `it` are in registers
+          if (ok) { tc_fence_after(); ok = issue_sdp(it + 1); }
+          if (!ok) break;
+        }
+        ok = mbar_wait(ds_full, it & 1);
+        if (!ok) break;
+        tc_fence_after();
+        const int st = it % kDqStages;
+        // dQ += dS K : A = dS (K-major over keys), B = K tile ([keys][D] -> MN-major)
+        mma_128x128x128<false, true>(tmem + 256, smem_u32(sDS), smem_u32(stage_ptr(st)), it > 0);
+        umma_commit(ds_empty);
+        umma_commit(&kv_empty[st]);
+      }
+      if (ok) umma_commit(acc_full);
+      if (!ok) { report_error(p.status, kErrMmaWaitFull); *abort_flag = 1; }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int part = (warp - 2) >> 2;               // key columns [32 * part, +32) of every tile
+    const int r = quarter * 32 + lane;              // q row of the block owned by this thread
+    const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
+    const float sl2 = p.scale * kLog2e;
+    const int fi = f0 + r;
+    const long long q_abs = static_cast<long long>(row_abs0) + r;
+    const bool frow_ok = (fi < s.q_len) && (q_abs < p.total_q);
+    float row_lse2 = 0.f, row_delta = 0.f;
+    if (frow_ok) {
+      row_lse2 = p.LSE[static_cast<long long>(head) * p.total_q + q_abs] * kLog2e;
+      row_delta = p.delta[static_cast<long long>(head) * p.total_q + q_abs];
+    }
+    bool ok = true;
+    if (iters > 0) {
+      // parts 0, 1 copy the two halves of their row of Q, parts 2, 3 of dO into TMEM (A operands of S and dP):
+      // 64 columns of the row = one 128-byte slab row = 32 TMEM columns
+      ok = mbar_wait(f_full, 0);
+      {
+        const uint8_t* src = sF + (part >> 1) * kTileBytes + (part & 1) * kSlabBytes;
+        uint32_t w[32];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 x = *reinterpret_cast<const uint4*>(src + swz(r, c));
+          w[c * 4] = x.x; w[c * 4 + 1] = x.y; w[c * 4 + 2] = x.z; w[c * 4 + 3] = x.w;
+        }
+        tmem_st_32x32(tmem + lane_addr + 384 + part * 32, w);
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      mbar_arrive_warp(f_tmem);
+    }
+    for (int it = 0; it < iters && ok; ++it) {
+      const int g0 = (tb0 + it) * kBN;              // first key of the tile (segment relative)
+      if (*abort_flag) { ok = false; break; }
+      ok = __all_sync(0xffffffffu, mbar_wait(sdp_full, it & 1));
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sv[32], dv[32];
+      tmem_ld_32x32(tmem + lane_addr + part * 32, sv);
+      tmem_ld_32x32(tmem + lane_addr + 128 + part * 32, dv);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive_warp(s_free);                        // the products of the next tile may overwrite S and dP
+      const bool need_mask = (f0 + kBM > s.q_len) || (g0 + kBN > s.k_len) || (g0 < s.k_skip) ||
+                             (p.causal && g0 + kBN - 1 > f0 + s.off) ||
+                             (p.window > 0 && g0 <= f0 + kBM - 1 + s.off - p.window);
+      // in place: sv[i] becomes the packed pair of dS values of columns (2i, 2i+1); the masked variant only runs on
+      // tiles that touch the diagonal, the window edge or the end of the segment
+      if (!frow_ok) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) sv[i] = 0u;
+      } else if (need_mask) {
+        dq_tile_math<true>(p, s, sv, dv, fi, g0 + part * 32, sl2, row_lse2, row_delta);
+      } else {
+        dq_tile_math<false>(p, s, sv, dv, fi, g0 + part * 32, sl2, row_lse2, row_delta);
+      }
+      // the dS tile of the previous iteration must have been consumed (asked this late, it almost always has)
+      if (it > 0) ok = __all_sync(0xffffffffu, mbar_wait(ds_empty, (it - 1) & 1));
+      uint8_t* slab = sDS + (part >> 1) * kSlabBytes;      // 64 keys per slab, this thread's 32 keys = 4 chunks of 16 bytes
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        *reinterpret_cast<uint4*>(slab + swz(r, (part & 1) * 4 + c)) = make_uint4(sv[c * 4], sv[c * 4 + 1], sv[c * 4 + 2], sv[c * 4 + 3]);
+      fence_proxy_async_smem();
+      mbar_arrive_warp(ds_full);
+    }
+    if (ok && iters > 0 && !*abort_flag) ok = mbar_wait(acc_full, 0);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) { report_error(p.status, kErrSoftmaxWait); *abort_flag = 1; }
+    if (iters > 0) tc_fence_after();
+    __nv_bfloat16* base = p.dQ + (q_abs * p.hq + head) * kD;
+    {
+      const int c = part;                           // each part stores 32 of the 128 columns of dQ
+      uint32_t v[32];
+      if (iters > 0 && ok) {
+        tmem_ld_32x32(tmem + lane_addr + 256 + c * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * p.scale);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = 0u;
+      }
+      if (frow_ok) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 o;
+          o.x = pack_bf16(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+          o.y = pack_bf16(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+          o.z = pack_bf16(__uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+          o.w = pack_bf16(__uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
+          *reinterpret_cast<uint4*>(base + c * 32 + i) = o;
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  __syncthreads();
+  if (*abort_flag) drain_delay();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
 // delta[h][t] = sum_d dO[t][h][d] * O[t][h][d]; one warp per (t, h)
 __global__ void __launch_bounds__(256)
 attn_delta2_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO, float* __restrict__ delta,
@@ -505,6 +772,8 @@ extern "C" int stb_attn_bwd(const void* q, const void* k, const void* v, const v
     if (e != cudaSuccess) return -static_cast<int>(e);
     e = cudaFuncSetAttribute(attn_bwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kBwdSmem);
     if (e != cudaSuccess) return -static_cast<int>(e);
+    e = cudaFuncSetAttribute(attn_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmem);
+    if (e != cudaSuccess) return -static_cast<int>(e);
     configured = true;
   }
   const long long warps = static_cast<long long>(total_q) * hq;
@@ -538,7 +807,11 @@ extern "C" int stb_attn_bwd(const void* q, const void* k, const void* v, const v
   }
   // dQ: fixed = (Q, dO) of a q head, streamed = (K, V)
   p.blk_seg = q_blk_seg; p.blk_row0 = q_blk_row0;
-  if (num_q_blocks > 0)
-    attn_bwd_kernel<false><<<dim3(hq, num_q_blocks), kBwdThreads, kBwdSmem, st>>>(q128, do128, k64, v64, p);
+  // STB200_ATTN_DQ=1 selects the earlier dQ pass with 64-key tiles
+  static const bool dq64 = [] { const char* e = getenv("STB200_ATTN_DQ"); return e != nullptr && e[0] == '1'; }();
+  if (num_q_blocks > 0) {
+    if (dq64) attn_bwd_kernel<false><<<dim3(hq, num_q_blocks), kBwdThreads, kBwdSmem, st>>>(q128, do128, k64, v64, p);
+    else attn_dq_kernel<<<dim3(hq, num_q_blocks), kDqThreads, kDqSmem, st>>>(q128, do128, k128, v128, p);
+  }
   return -static_cast<int>(cudaGetLastError());
 }

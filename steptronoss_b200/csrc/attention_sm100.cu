@@ -67,7 +67,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 256);
+      mbar_init(&p_full[i], 8);      // one arrival per softmax warp
     }
     mbar_init(pv_done, 1);
     *abort_flag = 0;
@@ -152,6 +152,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       const int st = j & 1;
       if (*abort_flag) ok = false;
       if (ok) ok = mbar_wait(&s_full[st], (j >> 1) & 1);
+      ok = __all_sync(0xffffffffu, ok);             // warp-wide TMEM loads and the warp's single arrival follow
       if (!ok) {
         asm volatile("bar.sync 1, 256;" ::: "memory");
         continue;
@@ -228,7 +229,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constan
       l += ((rs8[0] + rs8[1]) + (rs8[2] + rs8[3])) + ((rs8[4] + rs8[5]) + (rs8[6] + rs8[7]));
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(&p_full[st]);
+      mbar_arrive_warp(&p_full[st]);
     }
     // total row sum = sum of the two halves (fp32 exchange through the same scratch, viewed as floats)
     float* fx = reinterpret_cast<float*>(xchg);
@@ -342,7 +343,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
+      mbar_init(&p_full[i], 4);      // one arrival per softmax warp of the head
       mbar_init(&o_done[i], 1);
     }
     *abort_flag = 0;
@@ -495,7 +496,7 @@ attn_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_consta
       l += ((rs8[0] + rs8[1]) + (rs8[2] + rs8[3])) + ((rs8[4] + rs8[5]) + (rs8[6] + rs8[7]));
       tmem_wait_st();
       tc_fence_before();
-      mbar_arrive(&p_full[t]);
+      mbar_arrive_warp(&p_full[t]);
     }
     float inv = 0.f;
     if (ok && nkb > 0 && !*abort_flag) {

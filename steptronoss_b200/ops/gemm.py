@@ -30,7 +30,7 @@ def count_launch(n: int = 1) -> None:
 
 def _tma_compatible(*tensors: torch.Tensor) -> bool:
     """TMA wants 16-byte aligned bases and row pitches; odd shapes (a router with 4 experts, a gate column
-    count that is not a multiple of 8) go to the library GEMM instead."""
+    count that is not a multiple of 8, whatever the output type) go to the library GEMM instead."""
     for t in tensors:
         if t.data_ptr() % 16 or (t.stride(0) * t.element_size()) % 16 or t.stride(-1) != 1:
             return False
@@ -76,7 +76,7 @@ def gemm(
         out_dtype = out_dtype or a.dtype
         out = torch.empty((M, N), dtype=out_dtype, device=a.device)
         accumulate = False
-    if not a.is_cuda or _FORCE_LIBRARY_GEMM or not _tma_compatible(a, b, out):
+    if not a.is_cuda or _FORCE_LIBRARY_GEMM or N % 8 or not _tma_compatible(a, b, out):
         am = a.t() if a_mn_major else a
         bm = b if b_mn_major else b.t()
         if a.is_cuda:
