@@ -28,7 +28,7 @@ def test_environment_variables_named_in_the_documents_are_read_somewhere():
     src = ""
     for base in ("steptronoss_b200", "playground", "bench.py"):
         full = os.path.join(ROOT, base)
-        files = [full] if os.path.isfile(full) else [os.path.join(d, f) for d, _, fs in os.walk(full) for f in fs if f.endswith(".py")]
+        files = [full] if os.path.isfile(full) else [os.path.join(d, f) for d, _, fs in os.walk(full) for f in fs if f.endswith((".py", ".cu", ".cuh", ".cpp", ".h"))]
         for f in files:
             src += open(f, encoding="utf-8").read()
     missing = sorted(n for n in names if n not in src)
