@@ -589,6 +589,54 @@ static int router_grid(int T) {
 
 }  // namespace stb
 
+// Sums of the per-CTA partials of router_fwd_kernel in one launch: prob_sum [E], hist [E] (int32 and a float copy for
+// the auxiliary loss), stats = [max |logit|, mean over tokens of the largest probability] and the share of the
+// busiest expert (max hist / sum hist).  One CTA; thread e owns expert e (E <= 512).
+__global__ void __launch_bounds__(512)
+router_finalize_kernel(const float* __restrict__ part_prob, const int* __restrict__ part_hist,
+                       const float* __restrict__ part_stats, int grid, int E, int T, float* __restrict__ prob_sum,
+                       int* __restrict__ hist, float* __restrict__ hist_f, float* __restrict__ stats3) {
+  __shared__ int s_max[16], s_sum[16];
+  __shared__ float s_lmax[16], s_psum[16];
+  const int e = threadIdx.x;
+  float ps = 0.f;
+  int h = 0;
+  if (e < E) {
+    for (int g = 0; g < grid; ++g) {
+      ps += part_prob[static_cast<long long>(g) * E + e];
+      h += part_hist[static_cast<long long>(g) * E + e];
+    }
+    prob_sum[e] = ps;
+    hist[e] = h;
+    hist_f[e] = static_cast<float>(h);
+  }
+  float lmax = 0.f, psum = 0.f;
+  for (int g = e; g < grid; g += blockDim.x) {
+    lmax = fmaxf(lmax, part_stats[2 * g]);
+    psum += part_stats[2 * g + 1];
+  }
+  int hm = h, hs = h;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    hm = max(hm, __shfl_xor_sync(0xffffffffu, hm, o));
+    hs += __shfl_xor_sync(0xffffffffu, hs, o);
+    lmax = fmaxf(lmax, __shfl_xor_sync(0xffffffffu, lmax, o));
+    psum += __shfl_xor_sync(0xffffffffu, psum, o);
+  }
+  const int w = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) == 0) { s_max[w] = hm; s_sum[w] = hs; s_lmax[w] = lmax; s_psum[w] = psum; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int nw = (blockDim.x + 31) >> 5;
+    for (int i = 1; i < nw; ++i) {
+      hm = max(hm, s_max[i]); hs += s_sum[i]; lmax = fmaxf(lmax, s_lmax[i]); psum += s_psum[i];
+    }
+    stats3[0] = lmax;
+    stats3[1] = psum / static_cast<float>(T > 0 ? T : 1);
+    stats3[2] = static_cast<float>(hm) / static_cast<float>(hs > 0 ? hs : 1);
+  }
+}
+
 extern "C" int stb_router_grid(int T) { return router_grid(T); }
 
 // part_prob / part_hist: [stb_router_grid(T), E]; part_stats: [grid, 2] (max |logit|, sum over tokens of max prob)
@@ -625,4 +673,15 @@ extern "C" int stb_router_bwd(const void* logits, int T, int E, int K, int sigmo
                                                                static_cast<const float*>(g_ps),
                                                                static_cast<float*>(dlogits));
   return last_error();
+}
+
+extern "C" int stb_router_finalize(const void* part_prob, const void* part_hist, const void* part_stats, int grid, int E,
+                                   int T, void* prob_sum, void* hist, void* hist_f, void* stats3, cudaStream_t stream) {
+  if (E <= 0 || E > 512 || grid <= 0) return -kErrBadArgument;
+  const int threads = (E + 31) / 32 * 32;
+  router_finalize_kernel<<<1, threads, 0, stream>>>(
+      static_cast<const float*>(part_prob), static_cast<const int*>(part_hist), static_cast<const float*>(part_stats),
+      grid, E, T, static_cast<float*>(prob_sum), static_cast<int*>(hist), static_cast<float*>(hist_f),
+      static_cast<float*>(stats3));
+  return -static_cast<int>(cudaGetLastError());
 }

@@ -170,7 +170,7 @@ class MoEBlock(nn.Module):
             weights = (top_prob / (top_prob.sum(-1, keepdim=True) + eps)
                        if cfg.enable_sigmoid_router or cfg.norm_expert_weight else top_prob)
             hist = moe_ops.histogram(ids, self.num_experts)
-        ce = hist.clone().float()
+        ce = hist.float()
         for fam in ("TP", "EP"):
             if PM.size_of(fam) > 1:
                 dist.all_reduce(ce, group=PM.group_of(fam))
@@ -183,7 +183,8 @@ class MoEBlock(nn.Module):
         sub = f"layer{self.moe_layer_id}"
         with torch.no_grad():
             GlobalMetrics.router_logits_max.add(stats[0], subname=sub)
-            GlobalMetrics.expert_coef.add(hist.max().float() / hist.sum().clamp_min(1).float(), subname=sub)
+            GlobalMetrics.expert_coef.add(stats[2] if stats.numel() > 2 and not cfg.force_balance
+                                          else hist.max().float() / hist.sum().clamp_min(1).float(), subname=sub)
             GlobalMetrics.moe_max.add(stats[1], subname=sub)
             if cfg.detailed_router_metrics:
                 lg = logits.detach().float()

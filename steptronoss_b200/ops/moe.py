@@ -234,8 +234,16 @@ class _RouterFn(torch.autograd.Function):
         count_launch()
         ctx.save_for_backward(logits, ids)
         ctx.cfg = (top_k, int(sigmoid), int(norm_topk), float(eps))
-        prob_sum, hist = part_prob.sum(0), part_hist.sum(0, dtype=torch.int32)
-        stats = torch.stack([part_stats[:, 0].max(), part_stats[:, 1].sum() / max(T, 1)])
+        # one launch adds up the per-CTA partials; stats also carries the busiest expert's share of the slots
+        prob_sum = torch.empty(E, dtype=torch.float32, device=dev)
+        hist = torch.empty(E, dtype=torch.int32, device=dev)
+        hist_f = torch.empty(E, dtype=torch.float32, device=dev)
+        stats = torch.empty(3, dtype=torch.float32, device=dev)
+        rc = lib.stb_router_finalize(part_prob.data_ptr(), part_hist.data_ptr(), part_stats.data_ptr(), grid, E, T,
+                                     prob_sum.data_ptr(), hist.data_ptr(), hist_f.data_ptr(), stats.data_ptr(),
+                                     native.stream())
+        native.check(rc, "router_finalize")
+        count_launch()
         ctx.mark_non_differentiable(ids, hist, stats)
         return ids, weights, prob_sum, hist, stats
 
@@ -270,7 +278,7 @@ def fused_router(logits, bias, top_k: int, sigmoid: bool, norm_topk: bool, eps: 
     ``logits [T,E]`` fp32.  Returns ``ids [T,k]`` int64 (order and tie-break of a stable descending sort of
     ``prob + bias``), ``weights [T,k]`` fp32, ``prob_sum [E]`` (sum over tokens of the probabilities, for sigmoid
     scores of the probabilities renormalised per token), ``hist [E]`` int32 and ``stats = [max |logit|,
-    mean over tokens of the largest probability]``.  ``weights`` and ``prob_sum`` are differentiable."""
+    mean over tokens of the largest probability, share of the busiest expert in the routed slots]``.  ``weights`` and ``prob_sum`` are differentiable."""
     return _RouterFn.apply(logits.float(), bias, top_k, sigmoid, norm_topk, eps)
 
 
@@ -287,9 +295,10 @@ def router_reference(logits, bias, top_k: int, sigmoid: bool, norm_topk: bool, e
         prob = prob / (prob.sum(-1, keepdim=True) + eps)
     elif norm_topk:
         weights = top / (top.sum(-1, keepdim=True) + eps)
+    hist = histogram(ids, logits.shape[1])
     stats = torch.stack([logits.detach().abs().max(), (torch.sigmoid(logits) if sigmoid else torch.softmax(logits, 1))
-                         .detach().max(1).values.mean()])
-    return ids, weights, prob.sum(0), histogram(ids, logits.shape[1]), stats
+                         .detach().max(1).values.mean(), hist.max().float() / hist.sum().clamp_min(1).float()])
+    return ids, weights, prob.sum(0), hist, stats
 
 
 class _GroupedLinearFn(torch.autograd.Function):

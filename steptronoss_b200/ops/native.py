@@ -86,6 +86,7 @@ _SIGNATURES = {
     "stb_moe_gather_bwd": [P, P, P, P, P, P, I, I, I, I, I, P, P, P],
     "stb_router_grid": [I],
     "stb_router_fwd": [P, P, I, I, I, I, I, F, P, P, P, P, P, P],
+    "stb_router_finalize": [P, P, P, I, I, I, P, P, P, P, P],
     "stb_router_bwd": [P, I, I, I, I, I, F, P, P, P, P, P],
     "stb_sqnorm_grid": [],
     "stb_sqnorm": [P, L, P, P, I, P],
