@@ -12,8 +12,11 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SINGLE = {"gemm": ["benchmark_gemm.py"], "attention": ["benchmark_attention.py"], "moe": ["benchmark_moe.py"]}
-MULTI = {"moe_layer": ["benchmark_moe_layer.py"], "zero": ["benchmark_zero_peer.py"]}
+SINGLE = {"gemm": ["benchmark_gemm.py"], "fp8_gemm": ["benchmark_fp8_gemm.py"], "attention": ["benchmark_attention.py"],
+          "moe": ["benchmark_moe.py"], "muon": ["benchmark_muon.py"]}
+# the multi-rank ones need at least two GPUs, except the MoE layer (which then runs its single-rank variant)
+MULTI = {"moe_layer": ["benchmark_moe_layer.py"], "zero": ["benchmark_zero_peer.py"], "fused_tp": ["benchmark_fused_tp.py"],
+         "cp_attention": ["benchmark_cp_attention.py"], "peer_bandwidth": ["benchmark_peer_bandwidth.py", "--no-ring"]}
 
 
 def commands(out: str, gpus: int, skip: set) -> list:
@@ -24,7 +27,7 @@ def commands(out: str, gpus: int, skip: set) -> list:
         extra = [] if name == "attention" else ["--json", os.path.join(out, f"{name}.json")]
         cmds.append((name, [sys.executable, os.path.join(HERE, script), *rest, *extra]))
     for name, (script, *rest) in MULTI.items():
-        if name in skip or (name == "zero" and gpus < 2):
+        if name in skip or (name != "moe_layer" and gpus < 2):
             continue
         launcher = ([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={gpus}",
                      "--master-addr", "127.0.0.1", "--master-port", "29871"] if gpus > 1 else [sys.executable])

@@ -66,9 +66,11 @@ def test_run_all_lists_single_and_multi_rank_benchmarks(tmp_path):
     from benchmarks import run_all
 
     one = run_all.commands(str(tmp_path), 1, set())
-    assert [n for n, _ in one] == ["gemm", "attention", "moe", "moe_layer"]            # the ZeRO step needs two GPUs
+    # the multi-rank benchmarks other than the MoE layer need two GPUs
+    assert [n for n, _ in one] == ["gemm", "fp8_gemm", "attention", "moe", "muon", "moe_layer"]
     eight = dict(run_all.commands(str(tmp_path), 8, {"attention"}))
-    assert set(eight) == {"gemm", "moe", "moe_layer", "zero"} and "--nproc-per-node=8" in eight["zero"]
+    assert set(eight) == {"gemm", "fp8_gemm", "moe", "muon", "moe_layer", "zero", "fused_tp", "cp_attention",
+                          "peer_bandwidth"} and "--nproc-per-node=8" in eight["zero"]
     for cmd in list(dict(one).values()) + list(eight.values()):
         script = next(c for c in cmd if c.endswith(".py"))
         assert os.path.exists(script)
