@@ -22,6 +22,8 @@
 // warps 2..5 = epilogue (each owns the 32 TMEM lanes of its warp-id mod 4).
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace stb {
 
 constexpr int kBlockM = 128;
@@ -47,6 +49,9 @@ struct GemmParams {
   // dense mode with a symmetric result (X X^T, A^2 of a symmetric A): tiles that lie entirely below the diagonal
   // are not computed; the caller mirrors the upper triangle afterwards
   int upper_only;
+  // dense mode with fp32 reduce-add output (weight gradients): the reduction extent is cut into k_splits parts that
+  // different CTAs add into C, so that a product with few output tiles still fills whole waves of the grid
+  int k_splits;
 };
 
 template <int BLOCK_N>
@@ -99,6 +104,11 @@ __device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int n
     t.valid = true;
     return;
   }
+  int split = 0;
+  if (p.k_splits > 1) {   // splits of one output tile are a whole pass over the tiles apart
+    split = tile / (num_m * num_n);
+    tile -= split * num_m * num_n;
+  }
   const int in_band = kBand * num_n;
   const int band = tile / in_band;
   const int first_m = band * kBand;
@@ -108,6 +118,11 @@ __device__ __forceinline__ void decode_tile(const GemmParams& p, int tile, int n
   t.n_tile = r / band_rows;
   t.k_begin = 0;
   t.k_blocks = (p.K + kBlockK - 1) / kBlockK;
+  if (p.k_splits > 1) {
+    const int per = (t.k_blocks + p.k_splits - 1) / p.k_splits;
+    t.k_begin = split * per * kBlockK;
+    t.k_blocks = max(0, min(per, t.k_blocks - split * per));
+  }
   t.group = 0;
   t.valid = true;
   if (p.mode == 1) {
@@ -145,7 +160,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int num_m = (p.M + kBlockM - 1) / kBlockM;
   const int num_n = (p.N + BLOCK_N - 1) / BLOCK_N;
   const int num_tiles = p.upper_only ? upper_tile_count(num_m, num_n, BLOCK_N)
-                                     : num_m * num_n * (p.mode == 2 ? p.num_groups : 1);
+                                     : num_m * num_n * (p.mode == 2 ? p.num_groups : (p.k_splits > 1 ? p.k_splits : 1));
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -412,7 +427,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
   const int num_m = (p.M + kBlockM - 1) / kBlockM;
   const int num_n = (p.N + BLOCK_N - 1) / BLOCK_N;
   const long long tiles = p.upper_only ? upper_tile_count(num_m, num_n, BLOCK_N)
-                                       : static_cast<long long>(num_m) * num_n * (p.mode == 2 ? p.num_groups : 1);
+                                       : static_cast<long long>(num_m) * num_n *
+                                             (p.mode == 2 ? p.num_groups : (p.k_splits > 1 ? p.k_splits : 1));
   if (tiles == 0) return 0;
   const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
   kern<<<grid, kGemmThreads, S::kTotal, st>>>(ta, tb, tc, C, p);
@@ -450,6 +466,27 @@ static int dispatch_major(const CUtensorMap& ta, const CUtensorMap& tb, void* C,
 // operands per 64-deep k-block, which is the shared-memory bandwidth of an SM at tensor-core rate, so
 // the narrow tile only pays off when N itself is narrow.
 static int choose_block_n(long long /*num_m*/, int N, int /*groups*/) { return N > 128 ? 256 : 128; }
+
+// Split of the reduction extent for products that add into an fp32 C (TMA reduce-add makes the partial sums of
+// several CTAs safe): the smallest split that brings the last wave of the persistent grid to 92 % or more of a full
+// one, with at least 16 k blocks per part.  STB200_WGRAD_SPLITK=0 switches it off (then the sums of a tile always
+// come from one CTA, in one order).
+static int choose_k_splits(int M, int N, int K, int bn) {
+  static const bool off = [] { const char* e = getenv("STB200_WGRAD_SPLITK"); return e != nullptr && e[0] == '0'; }();
+  if (off) return 1;
+  const long long tiles = static_cast<long long>((M + kBlockM - 1) / kBlockM) * ((N + bn - 1) / bn);
+  const int kb = (K + kBlockK - 1) / kBlockK, sms = sm_count();
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= 4; ++s) {   // every part adds the whole tile into C once more: keep the extra traffic small
+    if (s > 1 && kb / s < 16) break;
+    const long long units = tiles * s;
+    const double eff = static_cast<double>(units) / (static_cast<double>((units + sms - 1) / sms) * sms);
+    if (eff > best_eff + 0.02) { best_eff = eff; best = s; }
+    if (best_eff >= 0.92) break;
+  }
+  return best;
+}
 
 // C[r][c] = C[c][r] for c < r: completes a symmetric matrix whose upper triangle (by tiles) was computed.
 // One CTA of 32 x 8 threads per 32 x 32 block on or below the diagonal.
@@ -527,6 +564,7 @@ static int gemm_bf16_impl(const void* A, const void* B, void* C, int M, int N, i
   GemmParams p{};
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.mode = 0; p.status = status; p.alpha = alpha;
   p.addend = static_cast<const __nv_bfloat16*>(addend); p.ld_add = ld_add; p.beta = beta; p.upper_only = upper_only;
+  p.k_splits = (out_f32 && accumulate) ? choose_k_splits(M, N, K, bn) : 1;
   return bn == 256 ? dispatch_major<256>(ta, tb, C, p, a_mn_major, b_mn_major, out_f32, accumulate, stream)
                    : dispatch_major<128>(ta, tb, C, p, a_mn_major, b_mn_major, out_f32, accumulate, stream);
 }

@@ -151,3 +151,20 @@ def test_newton_schulz_on_the_gpu_matches_the_fp32_iteration():
         assert ((got - want).norm() / want.norm()).item() < 5e-2
         s = torch.linalg.svdvals(got)
         assert s.max() < 1.3 and s.min() > 0.5
+
+
+def test_weight_gradient_product_with_the_reduction_split_over_ctas():
+    """fp32 accumulate-into-C products with few output tiles cut their reduction extent into parts that several
+    CTAs add into C (8 tiles x 4 parts here); the sum must still be the product."""
+    from steptronoss_b200.ops import gemm
+
+    torch.manual_seed(5)
+    M, N, K = 512, 512, 4096
+    a = (torch.randn(K, M, device="cuda") * 0.1).to(torch.bfloat16)
+    b = (torch.randn(K, N, device="cuda") * 0.1).to(torch.bfloat16)
+    c0 = torch.randn(M, N, device="cuda", dtype=torch.float32)
+    c = c0.clone()
+    gemm(a, b, a_mn_major=True, b_mn_major=True, out=c, accumulate=True)
+    torch.cuda.synchronize()
+    ref = c0 + _ref(a, b, True, True)
+    assert ((c - ref).abs().max() / ref.abs().max()).item() < 2e-3
