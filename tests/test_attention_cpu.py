@@ -85,3 +85,27 @@ def test_adjacent_pair_rope_rotates_neighbouring_dimensions():
     want[..., 0::2] = raw[..., 0::2] * c - raw[..., 1::2] * s
     want[..., 1::2] = raw[..., 1::2] * c + raw[..., 0::2] * s
     assert torch.allclose(q, want.index_select(-1, perm), atol=1e-6)
+
+
+def test_gathered_key_plan_tables_for_context_parallel_pieces():
+    """Segment tables of the kernels that address keys by global position: a range starts at the multiple of 128 at
+    or before its document, the keys in front of the document are counted as skipped, and the key-block schedule
+    walks every range in 128-row steps."""
+    import torch
+
+    from steptronoss_b200.ops.attention_native import GatheredKeyPlan
+    from steptronoss_b200.parallel.context_parallel import cu_seqlens_to_balanced_cp
+
+    # two documents [0, 700) and [700, 2048) over CP = 2 (chunks of 512): rank 0 holds chunks 0 and 3
+    halves = cu_seqlens_to_balanced_cp([0, 700, 2048], 2048, 2, 0)
+    assert halves == [[(0, 512, 0)], [(1536, 2048, 700)]]
+    plan = GatheredKeyPlan(halves[0] + halves[1], 2, 512, "cpu")
+    assert plan.cu_q.tolist() == [0, 512, 1024]
+    assert plan.seg_k_begin.tolist() == [0, 640]            # 700 rounded down to a multiple of 128
+    assert plan.seg_k_skip.tolist() == [0, 60]
+    assert plan.seg_k_len.tolist() == [512, 2048 - 640]
+    assert plan.k_blk_seg.tolist() == [0] * 4 + [1] * 11
+    assert plan.k_blk_row0.tolist() == [0, 128, 256, 384] + [640 + 128 * i for i in range(11)]
+    # rank 1 holds chunks 1 and 2: its first half sees document 0 up to 700 and then document 1 from 700 on
+    halves1 = cu_seqlens_to_balanced_cp([0, 700, 2048], 2048, 2, 1)
+    assert halves1[0] == [(512, 700, 0), (700, 1024, 700)] and halves1[1] == [(1024, 1536, 700)]
