@@ -57,9 +57,11 @@ def parse():
                     help="qwen3_8b: the headline dense config; qwen3_30b_a3b: the MoE config (EP = N, attention DP = N, "
                          "sequences of 4096, 32 per GPU; its static state needs N >= 4)")
     ap.add_argument("--dispatcher", default="peer", choices=["peer", "alltoall"], help="MoE token dispatcher")
-    ap.add_argument("--moe-capacity-factor", type=float, default=2.0,
+    ap.add_argument("--moe-capacity-factor", type=float, default=0.0,
                     help="MoE + peer dispatcher: size the expert buffers for this multiple of the balanced load instead "
-                         "of reading the arrived count back every layer (0 = exact count); overflow fails the run")
+                         "of reading the arrived count back every layer (0 = exact count, the default: the randomly "
+                         "initialised 48-layer model on random tokens sends one rank more than twice its share at "
+                         "EP=8, which a factor of 2 reports as the capacity error); overflow fails the run")
     ap.add_argument("--parallelism", default=None, help="e.g. tp4dp2, dp8, tp2, tp2cp2pp2; default tp=min(N,4) x dp")
     ap.add_argument("--optimizer", default="adam", choices=["adam", "muon"],
                     help="muon: Newton-Schulz updates for the 2-D hidden matrices, AdamW for the rest")

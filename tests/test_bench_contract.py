@@ -16,7 +16,7 @@ def test_defaults_follow_the_model(monkeypatch):
     assert (a.gpus, a.steps, a.warmup, a.impl, a.model, a.seqs_per_gpu, a.seq_len) == (1, 3, 3, "ours", "qwen3_8b", 8, 8192)
     monkeypatch.setattr(sys, "argv", ["bench.py", "--model", "qwen3_30b_a3b", "--gpus", "8"])
     a = bench.parse()
-    assert (a.seqs_per_gpu, a.seq_len, a.dispatcher, a.moe_capacity_factor) == (32, 4096, "peer", 2.0)   # 256 x 4096 at 8 GPUs
+    assert (a.seqs_per_gpu, a.seq_len, a.dispatcher, a.moe_capacity_factor) == (32, 4096, "peer", 0.0)   # 256 x 4096 at 8 GPUs
     assert a.seqs_per_micro_batch == 1
     monkeypatch.setattr(sys, "argv", ["bench.py", "--model", "qwen3_30b_a3b", "--seqs-per-micro-batch", "4"])
     assert bench.parse().seqs_per_micro_batch == 4
