@@ -34,6 +34,7 @@ STORE_ADDR: str | None = None
 STORE_PORT: int | None = None
 _SERVER_PROC = None
 _LOCK = threading.Lock()
+_THREAD_LOCAL = threading.local()
 
 
 def get_exp_id() -> str:
@@ -323,6 +324,38 @@ def get_exp_redis() -> ExpStore:
 get_exp_store = get_exp_redis
 
 
+class AsyncExpStore:
+    """``await``-able view of the experiment store for coroutines (generation workers, routers).
+
+    Every store method becomes a coroutine that runs the blocking socket call in the event loop's default executor,
+    so a poll of the store never stalls the loop.  The reference offers an ``aioredis`` client for the same purpose
+    (utils/comm_utils.py:251-264, used by ``RemoteFuture.aget_result`` at :549-568)."""
+
+    def __init__(self, store: ExpStore):
+        self._store = store
+
+    def __getattr__(self, name):
+        fn = getattr(self._store, name)
+        if not callable(fn):
+            return fn
+
+        async def call(*args, **kwargs):
+            import asyncio
+            import functools
+
+            return await asyncio.get_running_loop().run_in_executor(None, functools.partial(fn, *args, **kwargs))
+
+        call.__name__ = name
+        return call
+
+
+def get_exp_aredis() -> AsyncExpStore:
+    """The coroutine view of this thread over the experiment store (one per thread, created on first use)."""
+    if getattr(_THREAD_LOCAL, "astore", None) is None or _THREAD_LOCAL.astore._store is not STORE:
+        _THREAD_LOCAL.astore = AsyncExpStore(get_exp_redis())
+    return _THREAD_LOCAL.astore
+
+
 def reset_exp_store(stop_server: bool = True) -> None:
     """Forget the client (tests); the hosting process also stops its server."""
     global STORE, IS_STORE_HOST, _SERVER_PROC
@@ -517,6 +550,25 @@ class RemoteFuture(LocalFuture):
             if timeout is not None and time.monotonic() - t0 >= timeout:
                 raise TimeoutError(f"RemoteFuture {self.task_id} timed out after {timeout} seconds")
             time.sleep(0.05)
+        if isinstance(self.value, Exception):
+            raise self.value
+        return self.value
+
+    async def aget_result(self, timeout: float | None = None, interval: float = 0.05):
+        """``get_result`` for coroutines: polls through the coroutine view of the store and sleeps on the loop."""
+        import asyncio
+
+        store = get_exp_aredis()
+        t0 = time.monotonic()
+        while not self.completed:
+            raw = await store.get(self._key)
+            if raw is not None:
+                self.value = pickle.loads(raw)
+                await store.delete(self._key)
+                break
+            if timeout is not None and time.monotonic() - t0 >= timeout:
+                raise TimeoutError(f"RemoteFuture {self.task_id} timed out after {timeout} seconds")
+            await asyncio.sleep(interval)
         if isinstance(self.value, Exception):
             raise self.value
         return self.value

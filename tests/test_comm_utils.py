@@ -81,6 +81,39 @@ def test_queue_distributor_and_futures(store):
     assert sorted(f.get_result(timeout=10) for f in wait_by_finish_order(futs)) == [0, 10, 20]
 
 
+def test_coroutines_reach_the_store_without_blocking_the_loop(store):
+    import asyncio
+
+    from steptronoss_b200.utils.comm_utils import RemoteFuture, get_exp_aredis
+
+    async def main():
+        a = get_exp_aredis()
+        assert a is get_exp_aredis()                                    # one view per thread
+        await a.set("k", b"v")
+        assert await a.get("k") == b"v" and await a.incr("n", 3) == 3
+        fut, bad = RemoteFuture(), RemoteFuture()
+        ticks = []
+
+        async def ticker():
+            while True:
+                ticks.append(1)
+                await asyncio.sleep(0.01)
+
+        t = asyncio.create_task(ticker())
+        threading.Timer(0.15, lambda: pickle.loads(pickle.dumps(fut)).set_result({"x": 1})).start()
+        assert await fut.aget_result(timeout=10) == {"x": 1}
+        assert len(ticks) >= 3                                          # the loop kept running while the future was polled
+        assert store.get(fut._key) is None                              # read once, then removed
+        pickle.loads(pickle.dumps(bad)).set_result(ValueError("boom"))
+        with pytest.raises(ValueError):
+            await bad.aget_result(timeout=10)
+        with pytest.raises(TimeoutError):
+            await RemoteFuture().aget_result(timeout=0.1)
+        t.cancel()
+
+    asyncio.run(main())
+
+
 def test_blocking_pop_and_score_increments_steer_the_least_loaded_choice(store):
     import time
 
