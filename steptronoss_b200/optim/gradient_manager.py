@@ -93,6 +93,7 @@ class BaseGradientManager:
         for pz in self._peer.values():
             pz.finish_allocation()
         self.step_count = 0
+        self._steps_since_load = 0
         self._hooks = []
         self._install_hooks()
         self._build_optimizers()
@@ -101,6 +102,9 @@ class BaseGradientManager:
         self.scalars = torch.zeros(4, dtype=torch.float32, device=dev)
         self.scalars[2] = 1.0
         self.scalars[3] = 1.0
+        # steps whose update was applied: scalars[3] of every step added up on the device, so that the steps which a
+        # non-finite gradient norm skipped can be counted at log time without a host read per step
+        self.applied_steps = torch.zeros(1, dtype=torch.float32, device=dev)
         self._gather_event = None
         self._side_stream = torch.cuda.Stream() if dev.type == "cuda" else None
         self._sq_partial = None
@@ -343,12 +347,14 @@ class BaseGradientManager:
         """Reduce, clip, update, refresh. Returns ``(ok, grad_norm tensor, num_zeros tensor|None)``;
         both tensors stay on the device, reading them is the caller's (logging) decision."""
         self.step_count += 1
+        self._steps_since_load += 1
         self._allreduce_tagged("sequence_parallel", "TP")
         self._allreduce_tagged("micro_dp", "TP")
         self._allreduce_tagged("tp_partial_grad", "TP")
         self._scale_expert_grads()
         grad_scale = self._reduce()
         self._compute_clip(grad_scale)
+        self.applied_steps.add_(self.scalars[3:4])
         zeros = self.count_zeros() if self.cfg.log_num_zeros_in_grad else None
         if getattr(self.cfg, "log_detailed_grad_norms", False):
             self._record_detailed_grad_norms(grad_scale)
@@ -361,6 +367,12 @@ class BaseGradientManager:
             self.muon.step(float(pg["lr"]), float(pg["weight_decay"]), grad_scale, self.scalars)
         self._refresh_params()
         return True, self.scalars[1], zeros
+
+    def skipped_steps(self) -> int:
+        """Steps since construction (or the last load) whose update was skipped because the gradient norm was not
+        finite.  Reads one float from the device: call it where the host waits anyway (the log line).  The reference
+        counts the same thing on the host per step (core/trainers/lm_trainer.py:242-298, ``N-skipped``)."""
+        return self._steps_since_load - int(round(float(self.applied_steps.item())))
 
     # ------------------------------------------------------------------ state
     def state_dict(self) -> dict:

@@ -202,12 +202,14 @@ class DecoderPretrainTrainer(BaseTrainer):
         self._t_last = now
         GlobalMetrics.iteration_time.add(dt)
         metrics = GlobalMetrics.reduce_all()
+        skipped = self.grad_manager.skipped_steps() if hasattr(self.grad_manager, "skipped_steps") else 0
+        metrics["N-skipped"] = skipped
         tokens = tc.global_batch_size * tc.global_seq_length
         tps_card = tokens / dt / max(PM.world_size, 1)
         logs = tc.make_logs(self.iteration, metrics, self.writer)
         line = (f"iter {self.iteration}/{self.train_iters} | consumed samples {self.consumed_samples} | "
                 f"{dt * 1e3:.1f} ms/iter | tokens-per-second-per-card {tps_card:.1f} | "
-                f"lr {self.scheduler.cur_lr:.3E} | global batch size {tc.global_batch_size} | "
+                f"lr {self.scheduler.cur_lr:.3E} | global batch size {tc.global_batch_size} | #skipped-iters {skipped} | "
                 f"grad-norm {float(metrics.get('grad_norm', 0.0)):.3f} | lm_loss {logs.get('lm_loss', 'n/a')}")
         self.last_metrics = metrics                        # everything that was reduced for this log line
         self.history.append({"iteration": self.iteration, "ms_per_iter": dt * 1e3,

@@ -170,6 +170,28 @@ def test_check_nan_names_the_stage_whose_output_went_bad():
         tr.train_step()
 
 
+def test_step_with_a_non_finite_gradient_is_skipped_and_counted():
+    e = _make()
+    e.data_cfg = FixedDataConfig
+    tr = e.trainer_cfg.get_trainer_cls()(exp=e)
+    tr.before_train()
+    tr.train_step()
+    gm = tr.grad_manager
+    assert gm.skipped_steps() == 0
+    before = [p.detach().clone() for p in tr.models[0].parameters()]
+    hook = next(tr.models[0].parameters()).register_hook(lambda g: torch.full_like(g, float("inf")))
+    tr.train_step()
+    hook.remove()
+    assert gm.skipped_steps() == 1
+    assert all(torch.equal(a, b) for a, b in zip(before, tr.models[0].parameters()))    # no update was applied
+    tr.train_step()                                                                     # and training goes on
+    assert gm.skipped_steps() == 1
+    assert not all(torch.equal(a, b) for a, b in zip(before, tr.models[0].parameters()))
+    tr.iteration += 1
+    tr.training_log()
+    assert tr.last_metrics["N-skipped"] == 1
+
+
 @pytest.mark.parametrize("change", [
     {"model_cfg.recompute": ["attention", "ffn_norm"]},
     {"model_cfg.recompute": True, "model_cfg.recompute_num_layers": 1},
