@@ -450,3 +450,66 @@ def set_mpu_random_seed(seed: int) -> None:
     tracker.reset()
     tracker.add("model-parallel-rng", base + 2718 + tp)
     tracker.add("expert-model-parallel-rng", base + 3718 + etp + ep * etp_size)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Module-level spellings of the manager's queries.  Model and schedule code written against the reference calls
+# these as free functions (core/parallel_state.py:269-394); each one asks ``PM``, so there is one source of truth.
+# ---------------------------------------------------------------------------------------------------------------
+def is_unitialized() -> bool:
+    """True before any mesh was set (the reference's spelling, core/parallel_state.py:269)."""
+    return not PM.has("DP")
+
+
+def model_parallel_is_initialized() -> bool:
+    return all(PM.has(f) for f in ("TP", "PP", "DP"))
+
+
+def get_vpp_rank() -> int:
+    return PM.get_vpp_rank()
+
+
+def set_vpp_rank(rank: int) -> None:
+    PM.set_vpp_rank(int(rank or 0))
+
+
+def get_vpp_size() -> int:
+    return PM.get_vpp_size()
+
+
+def set_vpp_size(world_size: int | None) -> None:
+    PM._vpp_size = int(world_size or 1)
+
+
+def get_pipeline_model_parallel_world_size(ignore_virtual: bool = True) -> int:
+    """Pipeline stages; with ``ignore_virtual=False`` the model chunks of the whole pipeline (stages x VPP)."""
+    return PM.size_of("PP") * (1 if ignore_virtual else PM.get_vpp_size())
+
+
+def get_pipeline_model_parallel_rank(ignore_virtual: bool = True) -> int:
+    """Stage of this rank; with ``ignore_virtual=False`` the index of the current model chunk in pipeline order."""
+    return PM.rank_in("PP") + (0 if ignore_virtual else PM.get_vpp_rank() * PM.size_of("PP"))
+
+
+def get_pipeline_model_parallel_next_rank() -> int:
+    return PM.pipeline_next_rank()
+
+
+def get_pipeline_model_parallel_prev_rank() -> int:
+    return PM.pipeline_prev_rank()
+
+
+def is_pipeline_first_stage(ignore_virtual: bool = False) -> bool:
+    return PM.is_pipeline_first_stage(ignore_virtual)
+
+
+def is_pipeline_last_stage(ignore_virtual: bool = False) -> bool:
+    return PM.is_pipeline_last_stage(ignore_virtual)
+
+
+def get_data_rank() -> int:
+    return PM.get_data_rank()
+
+
+def get_data_world_size() -> int:
+    return PM.get_data_world_size()

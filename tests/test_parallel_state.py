@@ -96,3 +96,33 @@ def test_global_memory_buffer_reuses_and_grows():
     assert big.shape == (16, 8) and buf.nbytes() == 16 * 8 * 4 + 16 * 2 + 16 * 4
     destroy_global_memory_buffer()
     assert get_global_memory_buffer().nbytes() == 0
+
+
+def test_free_functions_answer_from_the_manager():
+    import steptronoss_b200.parallel.state as st
+
+    pm = ParallelManager()
+    pm.world_size, pm.world_rank = 8, 5
+    old = st.PM
+    st.PM = pm
+    try:
+        assert st.is_unitialized() and not st.model_parallel_is_initialized()
+        for name, pattern, sizes in (("TP", "(p d t) -> (p d) t", {"p": 2, "t": 2}), ("PP", "(p d t) -> (d t) p", {"p": 2, "t": 2}),
+                                     ("DP", "(p d t) -> (p t) d", {"p": 2, "t": 2}), ("CP", "(p d c t) -> (p d t) c", {"p": 2, "t": 2, "c": 1})):
+            pm.new_parallel(name, pm.define_parallel(pattern, **sizes))
+        assert not st.is_unitialized() and st.model_parallel_is_initialized()
+        # rank 5 = stage 1, data replica 0, tensor rank 1; its pipeline row is [1, 5]
+        assert st.get_pipeline_model_parallel_rank() == 1 and st.get_pipeline_model_parallel_world_size() == 2
+        assert st.get_pipeline_model_parallel_next_rank() == 1 and st.get_pipeline_model_parallel_prev_rank() == 1
+        assert st.is_pipeline_last_stage() and not st.is_pipeline_first_stage()
+        assert (st.get_data_rank(), st.get_data_world_size()) == (0, 2)
+        st.set_vpp_size(3)
+        st.set_vpp_rank(1)
+        assert (st.get_vpp_size(), st.get_vpp_rank()) == (3, 1)
+        assert st.get_pipeline_model_parallel_world_size(ignore_virtual=False) == 6
+        assert st.get_pipeline_model_parallel_rank(ignore_virtual=False) == 1 * 2 + 1      # chunk 1 of stage 1
+        assert not st.is_pipeline_last_stage() and st.is_pipeline_last_stage(ignore_virtual=True)
+        st.set_vpp_rank(2)
+        assert st.is_pipeline_last_stage()
+    finally:
+        st.PM = old
