@@ -106,7 +106,10 @@ class GroupedQueryAttention(nn.Module):
             r = self.rot_dim
             self.pair_perm = torch.tensor(list(range(0, r, 2)) + list(range(1, r, 2)) + list(range(r, D)))
         sw = _per_layer(cfg.use_sliding_window, layer_id)
-        self.window = int(cfg.sliding_window_size) if sw and cfg.sliding_window_size and cfg.sliding_window_size > 0 else 0
+        # ``sliding_window_size = w`` is handed to flash-attn as ``window_size=(w, w)`` by the reference
+        # (model/common/grouped_query_attention.py:125, attention_core.py:102): a query sees the w keys before it and
+        # itself.  The kernels here count the visible keys, so that is w + 1.
+        self.window = int(cfg.sliding_window_size) + 1 if sw and cfg.sliding_window_size and cfg.sliding_window_size > 0 else 0
 
     def forward(self, x, position_id, cu_seqlens=None, max_seqlen=None, cp_meta=None):
         """x ``[tokens(/TP), H]`` -> same shape. ``position_id`` int32 ``[tokens]`` (full sequence on this CP rank)."""

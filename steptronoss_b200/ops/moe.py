@@ -12,6 +12,8 @@ and all sizes stay on the device: the expert-major buffer has a static worst-cas
 """
 from __future__ import annotations
 
+import itertools
+
 import torch
 
 from ..utils.optimizable import optimizable
@@ -21,6 +23,7 @@ from .gemm import count_launch
 from .grouped import SEGMENT_ALIGNMENT, grouped_gemm_reduce, grouped_gemm_rows, tile_groups_from_offsets
 
 
+@optimizable(native_names=("triton",))
 def histogram(ids: torch.Tensor, num_experts: int) -> torch.Tensor:
     """Count of every expert id in ``ids``; entries equal to -1 (foreign experts) are ignored."""
     flat = ids.reshape(-1)
@@ -35,6 +38,7 @@ def padded_rows(num_slots: int, num_experts: int) -> int:
     return (worst + SEGMENT_ALIGNMENT - 1) // SEGMENT_ALIGNMENT * SEGMENT_ALIGNMENT
 
 
+@optimizable(native_names=("triton",))
 def index_compute(ids: torch.Tensor, num_experts: int):
     """Destination row of every (token, k) slot in the expert-major buffer.
 
@@ -154,6 +158,11 @@ class _ScatterFn(torch.autograd.Function):
         return picked.view(T, K, -1).sum(1).to(g.dtype), None, None, None
 
 
+def _moe_scatter_reference_alt(x, dest, rows, plan=None):
+    return _ScatterFn.apply(x, dest, rows, None)
+
+
+@optimizable({"reference": _moe_scatter_reference_alt}, native_names=("triton",))
 def moe_scatter(x, dest, rows, plan: RoutePlan | None = None):
     """Copy the rows of ``x`` into expert-major order.  With a ``plan`` (bf16 on the GPU) one kernel writes
     every used row exactly once, padding rows as zeros; rows past the last segment stay unwritten."""
@@ -208,6 +217,11 @@ class _WeightedGatherFn(torch.autograd.Function):
         return gy, None, gw, None
 
 
+def _moe_gather_reference_alt(y, dest, weights, plan=None):
+    return _WeightedGatherFn.apply(y, dest, weights, None)
+
+
+@optimizable({"reference": _moe_gather_reference_alt}, native_names=("triton",))
 def moe_weighted_gather(y, dest, weights, plan: RoutePlan | None = None):
     """``out[t] = sum_k weights[t,k] * y[dest[t,k]]`` (ignored slots contribute nothing)."""
     return _WeightedGatherFn.apply(y, dest, weights, plan)
@@ -342,6 +356,35 @@ class _GroupedLinearFn(torch.autograd.Function):
 
 def grouped_linear(x, w, offsets, tile_group=None, fp8: bool = False):
     return _GroupedLinearFn.apply(x, w, offsets, tile_group, fp8)
+
+
+def _grouped_gemm_loop(mat_a_flat, mat_b, batch_sizes, trans_b: bool = False):
+    outs, start = [], 0
+    for g, n in enumerate(int(b) for b in batch_sizes.tolist()):
+        rhs = mat_b[g].t() if trans_b else mat_b[g]
+        outs.append(mat_a_flat[start:start + n] @ rhs)
+        start += n
+    if not outs:
+        return mat_a_flat.new_zeros((0, mat_b.shape[1] if trans_b else mat_b.shape[2]))
+    return torch.cat(outs, 0)
+
+
+@optimizable({"function_imple": _grouped_gemm_loop, "reference": _grouped_gemm_loop},
+             native_names=("nv_grouped_gemm", "triton_grouped_gemm"))
+def grouped_gemm(mat_a_flat, mat_b, batch_sizes, trans_b: bool = False):
+    """The reference's grouped-GEMM entry (model/utils/moe_utils.py:435-453): rows of ``mat_a_flat [sum, K]`` in
+    consecutive groups of ``batch_sizes[g]`` rows, ``mat_b [G, N, K]`` (``trans_b``) or ``[G, K, N]``.
+
+    The sizes are read on the host, as the reference's back-ends do.  Groups whose sizes are all multiples of 128
+    with ``trans_b`` and bf16 operands on the GPU run as one grouped tcgen05 GEMM (differentiable, weight gradient
+    by the grouped reduce kernel); anything else runs one product per group.  The model path does not come through
+    here: ``routed_grouped_ffn`` keeps its offsets on the device."""
+    sizes = [int(b) for b in batch_sizes.tolist()]
+    if (trans_b and sizes and _native_rows(mat_a_flat) and mat_b.dtype == torch.bfloat16 and mat_b.is_contiguous()
+            and all(n % SEGMENT_ALIGNMENT == 0 for n in sizes) and mat_a_flat.shape[1] % 8 == 0):
+        offsets = torch.tensor([0] + list(itertools.accumulate(sizes)), dtype=torch.int32, device=mat_a_flat.device)
+        return grouped_linear(mat_a_flat.contiguous(), mat_b, offsets)
+    return _grouped_gemm_loop(mat_a_flat, mat_b, batch_sizes, trans_b)
 
 
 def _routed_ffn_reference_alt(x, expert_ids, weights, w1, w2, limit: float = 0.0, max_slots: int | None = None,

@@ -15,6 +15,7 @@ from __future__ import annotations
 import torch
 import torch.distributed as dist
 
+from ..utils.optimizable import optimizable
 from .state import PM
 
 
@@ -114,6 +115,22 @@ class AllToAllDispatcher:
         return out.to(y.dtype)
 
 
+def _peer_token_dispatcher(parallel: str, num_experts: int):
+    from .peer_dispatcher import PeerMemoryDispatcher
+
+    return PeerMemoryDispatcher(parallel, num_experts)
+
+
+@optimizable({"deep_ep": _peer_token_dispatcher, "peer": _peer_token_dispatcher})
+def TokenDispatcher(parallel: str, num_experts: int):
+    """The dispatcher of the expert-parallel family ``parallel`` under the reference's name and constructor
+    (model/ep_dispatcher/token_dispatcher.py:14-25): ``dispatch(hidden, expert_ids, weights)`` /
+    ``combine(hidden)`` over all-to-alls.  ``set_optimization(TokenDispatcher="deep_ep")`` - the reference's switch to
+    its NVLink dispatcher - returns the peer-memory dispatcher instead; ``MoEConfig.dispatcher`` set to anything but
+    the default overrides the switch."""
+    return AllToAllDispatcher(parallel, num_experts)
+
+
 PEER_KINDS = ("peer", "deepep", "nvlink")           # "deepep": the reference's name for its NVLink dispatcher
 ALLTOALL_KINDS = ("alltoall", "token", "nccl")      # "token": the reference's baseline TokenDispatcher
 
@@ -126,4 +143,6 @@ def build_dispatcher(kind: str, group_name: str, num_experts: int, capacity_fact
         from .peer_dispatcher import PeerMemoryDispatcher
 
         return PeerMemoryDispatcher(group_name, num_experts, capacity_factor)
+    if kind == "alltoall":          # the default: the registry switch of the reference's experiment files applies
+        return TokenDispatcher(group_name, num_experts)
     return AllToAllDispatcher(group_name, num_experts)

@@ -16,12 +16,18 @@ from .logger import logger
 OPTIMIZABLE_REGISTER: dict = {}
 
 
-def optimizable(alternatives: dict | None = None):
-    """Register ``func`` under ``module.qualname`` with named alternatives (same arguments, allclose output)."""
+def optimizable(alternatives: dict | None = None, aliases: tuple = (), native_names: tuple = ()):
+    """Register ``func`` under ``module.qualname`` with named alternatives (same arguments, allclose output).
+
+    ``aliases``: further short names that ``set_optimization`` accepts for this entry (the name the reference
+    registers the same operator under, e.g. ``AttentionCore`` for the attention function).  ``native_names``:
+    back-end names of the reference that all mean the kernel path here (``"flash-attn-3"``, ``"triton"``,
+    ``"nv_grouped_gemm"`` ...), so that an experiment file written for the reference selects it without a warning."""
 
     def wrapper(func: Callable):
         reg = f"{getattr(func, '__module__', 'unknown')}.{getattr(func, '__qualname__', func.__name__)}"
-        OPTIMIZABLE_REGISTER[reg] = {"alternatives": dict(alternatives or {}), "use_optimize": None, "base": func}
+        OPTIMIZABLE_REGISTER[reg] = {"alternatives": dict(alternatives or {}), "use_optimize": None, "base": func,
+                                     "aliases": tuple(aliases), "native_names": tuple(native_names)}
 
         @wraps(func)
         def wrapped(*a, **k):
@@ -41,8 +47,10 @@ def set_optimization(default: str | None = None, **kwargs) -> dict:
     """Select alternatives by function name (short or full). Unknown alternative names are ignored with a
     warning (experiment files written for the reference name back-ends that do not exist here)."""
     short = {}
-    for k in OPTIMIZABLE_REGISTER:
-        short.setdefault(k.split(".")[-1], []).append(k)
+    for k, meta in OPTIMIZABLE_REGISTER.items():
+        for nick in (k.split(".")[-1],) + tuple(meta.get("aliases", ())):
+            if k not in short.setdefault(nick, []):
+                short[nick].append(k)
     chosen = {}
     for reg, meta in OPTIMIZABLE_REGISTER.items():
         if default and default in meta["alternatives"]:
@@ -55,7 +63,7 @@ def set_optimization(default: str | None = None, **kwargs) -> dict:
             continue
         for reg in targets:
             meta = OPTIMIZABLE_REGISTER[reg]
-            if alt in (None, "native", "default"):
+            if alt in (None, "native", "default") or alt in meta.get("native_names", ()):
                 meta["use_optimize"] = None
             elif alt in meta["alternatives"]:
                 meta["use_optimize"] = alt
@@ -64,3 +72,11 @@ def set_optimization(default: str | None = None, **kwargs) -> dict:
                 continue
             chosen[reg] = alt
     return chosen
+
+
+def current_optimization(name: str) -> str | None:
+    """The alternative selected for ``name`` (full name, short name or alias); None = the kernel path."""
+    for reg, meta in OPTIMIZABLE_REGISTER.items():
+        if name == reg or name == reg.split(".")[-1] or name in meta.get("aliases", ()):
+            return meta["use_optimize"]
+    raise KeyError(name)

@@ -17,6 +17,8 @@ CASES = [
     ([1000, 24, 512, 200], None, 8, 2, True, 0),
     ([384, 129], None, 4, 2, False, 0),
     ([700, 300], None, 4, 2, True, 128),
+    ([700, 300, 77], None, 4, 2, True, 65),     # odd windows: a sliding_window_size of w shows w + 1 keys
+    ([1100], None, 4, 4, True, 513),
     ([200, 100], [500, 228], 4, 2, True, 0),   # q rows are the tail of longer key segments
     ([2048], None, 4, 4, True, 0),
 ]

@@ -31,6 +31,28 @@ def test_routed_grouped_ffn_gpu_matches_expert_loop(T, E, K, H, F):
         assert err < 3e-2, (name, err)
 
 
+def test_grouped_gemm_entry_runs_the_grouped_kernel_for_aligned_groups_and_the_loop_otherwise():
+    from steptronoss_b200.ops import gemm as gemm_ops
+    from steptronoss_b200.ops.moe import grouped_gemm
+
+    dev = "cuda"
+    g = torch.Generator(device=dev).manual_seed(0)
+    w = (torch.randn(4, 192, 256, device=dev, generator=g) * 0.05).to(torch.bfloat16).requires_grad_()
+    for sizes, launches in (([256, 0, 128, 384], 1), ([100, 28, 0, 7], 0)):
+        a = torch.randn(sum(sizes), 256, device=dev, generator=g).to(torch.bfloat16).requires_grad_()
+        before = gemm_ops.launch_count()
+        y = grouped_gemm(a, w, torch.tensor(sizes), trans_b=True)
+        assert gemm_ops.launch_count() - before == launches          # one grouped launch, or the per-group products
+        y.float().pow(2).sum().backward()
+        ar, wr = a.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+        ref = torch.cat([ar[sum(sizes[:i]):sum(sizes[:i + 1])] @ wr[i].t() for i in range(4)])
+        ref.pow(2).sum().backward()
+        for name, got, want in (("y", y, ref), ("da", a.grad, ar.grad), ("dw", w.grad, wr.grad)):
+            err = float((got.float() - want).abs().max() / want.abs().max().clamp_min(1e-6))
+            assert err < 3e-2, (sizes, name, err)
+        w.grad = None
+
+
 def test_gae_kernel_matches_host_recursion():
     from steptronoss_b200.utils.rl_utils import compute_gae
 

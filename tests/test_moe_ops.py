@@ -1,5 +1,6 @@
 """MoE routing ops on CPU: histogram with ignored ids, stable aligned index computation,
 scatter / weighted gather with gradients, and the routed FFN against a per-expert loop."""
+import pytest
 import torch
 
 from steptronoss_b200.ops import moe
@@ -155,3 +156,73 @@ def test_set_optimization_switches_registered_ops_to_their_reference_statement()
     finally:
         set_optimization(routed_grouped_ffn=None, fused_router=None)
         OPTIMIZABLE_REGISTER[name]["alternatives"].pop("spy", None)
+
+
+def test_reference_experiment_switches_select_what_exists_here():
+    """An experiment file written for the reference calls ``set_optimization`` with its own operator and back-end
+    names; every one of them maps to an entry here, accelerated back-ends mean the kernel path."""
+    import importlib
+
+    from steptronoss_b200.parallel import ep_dispatcher
+
+    attn_ops = importlib.import_module("steptronoss_b200.ops.attention")      # the package also exports the function
+    from steptronoss_b200.utils.optimizable import current_optimization, set_optimization
+
+    chosen = set_optimization(routed_grouped_ffn="fused", moe_weighted_gather="triton", moe_scatter="triton",
+                              histogram="triton", index_compute="triton", TokenDispatcher="deep_ep",
+                              grouped_gemm="nv_grouped_gemm", AttentionCore="flash-attn-3")
+    try:
+        assert chosen[ep_dispatcher.TokenDispatcher.__optimizable_name__] == "deep_ep"
+        assert chosen[attn_ops.attention.__optimizable_name__] == "flash-attn-3"
+        assert current_optimization("AttentionCore") is None and current_optimization("grouped_gemm") is None
+        assert current_optimization("TokenDispatcher") == "deep_ep"
+        set_optimization(AttentionCore="sdpa", grouped_gemm="function_imple")
+        assert current_optimization("attention") == "sdpa" and current_optimization("grouped_gemm") == "function_imple"
+        q = torch.randn(12, 4, 8)
+        cu = torch.tensor([0, 5, 12], dtype=torch.int32)
+        assert torch.equal(attn_ops.attention(q, q[:, :2], q[:, :2], cu, cu, 7),
+                           attn_ops.attention_reference(q, q[:, :2], q[:, :2], cu, cu))
+    finally:
+        set_optimization(AttentionCore=None, grouped_gemm=None, TokenDispatcher=None)
+    assert current_optimization("TokenDispatcher") is None
+
+
+def test_grouped_gemm_entry_with_the_reference_signature():
+    a = torch.randn(9, 6, dtype=torch.float64, requires_grad=True)
+    w = torch.randn(3, 4, 6, dtype=torch.float64, requires_grad=True)
+    sizes = torch.tensor([2, 0, 7])
+    y = moe.grouped_gemm(a, w, sizes, trans_b=True)
+    want = torch.cat([a[:2] @ w[0].t(), a[2:] @ w[2].t()])
+    assert torch.allclose(y, want)
+    y.sum().backward()
+    assert torch.allclose(w.grad[1], torch.zeros(4, 6, dtype=torch.float64)) and a.grad is not None
+    y2 = moe.grouped_gemm(a.detach(), w.detach().transpose(1, 2).contiguous(), sizes)          # [G, K, N]
+    assert torch.allclose(y2, want)
+    assert moe.grouped_gemm(a[:0].detach(), w.detach(), torch.tensor([0, 0, 0]), trans_b=True).shape == (0, 4)
+
+
+def test_attention_core_module_follows_the_reference_call_surface():
+    from steptronoss_b200.ops.attention import AttentionCore, FlashAttention, parse_cu_seqlens
+
+    torch.manual_seed(0)
+    q, k, v = torch.randn(2, 10, 4, 8), torch.randn(2, 10, 2, 8), torch.randn(2, 10, 2, 8)
+    qi, kj = torch.arange(10)[:, None], torch.arange(10)[None]
+    kk, vv = (t.transpose(1, 2).repeat_interleave(2, 1) for t in (k, v))
+    for w, mask in ((-1, kj <= qi), (3, (kj <= qi) & (kj >= qi - 3))):           # w keys to the left and the query itself
+        out = AttentionCore(sliding_window=w).eval()(q, k, v)
+        want = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), kk, vv, attn_mask=mask).transpose(1, 2)
+        assert torch.allclose(out, want, atol=1e-5)
+    # packed stream: 20 rows cut at 7; the second table form names queries and keys separately
+    cu = torch.tensor([0, 7, 20])
+    packed = FlashAttention()(q, k, v, cu_seqlens=cu)
+    assert torch.allclose(packed.reshape(20, 4, 8)[:7], AttentionCore()(q[:, :7][:1], k[:, :7][:1], v[:, :7][:1])[0], atol=1e-5)
+    cq, ck, mq, mk = parse_cu_seqlens({"q": torch.tensor([0, 3]), "k": torch.tensor([0, 10])})
+    assert (cq.dtype, mq, mk) == (torch.int32, 3, 10)
+    tail = AttentionCore()(q[:1, 7:], k[:1], v[:1], cu_seqlens={"q": torch.tensor([0, 3]), "k": torch.tensor([0, 10])})
+    assert torch.allclose(tail, AttentionCore()(q[:1], k[:1], v[:1])[:, 7:], atol=1e-5)    # causality aligned to the key end
+    m = AttentionCore(attention_dropout=0.5).train()
+    torch.manual_seed(1)
+    a = m(q, k, v)
+    assert not torch.allclose(a, m.eval()(q, k, v)) and torch.isfinite(a).all()
+    with pytest.raises(ValueError):
+        AttentionCore(causal=False, sliding_window=4)

@@ -58,7 +58,7 @@ def test_step3p5_layers_follow_the_swa_list_and_train():
     model = getattr(model, "module", model)
     blocks = [model.layers[str(i)] for i in model.layer_ids]
     assert all(isinstance(b, Step3p5Block) for b in blocks)
-    assert [b.attention.window for b in blocks] == [16, 0, 16]
+    assert [b.attention.window for b in blocks] == [17, 0, 17]       # 16 keys to the left and the query itself
     assert [b.attention.num_heads for b in blocks] == [8, 4, 8]
     assert not hasattr(blocks[0].feed_forward, "moe") and hasattr(blocks[1].feed_forward, "moe")
     assert blocks[1].feed_forward.enable_share_expert
