@@ -168,3 +168,64 @@ def get_zeropower_fn(name: str, run_ns_in_fp16: bool = True):
 def adjust_ratio_for_muon(matched_adamw_rms: float, shape) -> float:
     """Scale that gives an orthogonalised update the RMS of an AdamW update: ``rms * sqrt(max(m, n))``."""
     return matched_adamw_rms * (max(shape[-2], shape[-1]) ** 0.5)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Spectral tools built on an orthogonaliser ``fn(G, steps) ~ U V^T`` (reference: optimizer/_helpers.py:176-247)
+# ---------------------------------------------------------------------------------------------------------------
+def get_step_fun(fn, threshold: float, steps: int = 5):
+    """``G = U diag(s) V^T  ->  U diag(step(s - threshold)) V^T``: singular directions above ``threshold`` are kept
+    with value 1, those below are removed.  Two orthogonalisations: ``sign(s)`` and ``sign(s - threshold)`` share
+    the singular vectors, so their mean is the step."""
+
+    @torch.no_grad()
+    def step_fun(G):
+        first = fn(G, steps)
+        return 0.5 * (first + fn(G - threshold * first, steps))
+
+    return step_fun
+
+
+def get_clip_fun(fn, threshold: float, steps: int = 5):
+    """``M = U diag(s) V^T  ->  U diag(min(s, threshold)) V^T`` without an SVD.  With ``P = fn(M)`` and
+    ``Q = fn(M - threshold P)`` (signs of ``s`` and of ``s - threshold``):
+    ``min(s, t) = (s + t - |s - t|) / 2`` and ``U diag(|s - t|) V^T = (M P^T - t I) Q``."""
+
+    @torch.no_grad()
+    def clip_fun(M):
+        P = fn(M, steps)
+        Q = fn(M - threshold * P, steps)
+        eye = torch.eye(M.shape[-2], device=M.device, dtype=M.dtype)
+        return 0.5 * (M + threshold * P - (M @ P.mT - threshold * eye) @ Q)
+
+    return clip_fun
+
+
+def get_max_singular_value(M):
+    return torch.linalg.svdvals(M.float()).max()
+
+
+@torch.no_grad()
+def weight_decay_in_spectral_norm(M, steps: int = 10, pre_iters: int = 3):
+    """Gradient of the spectral norm, ``u1 v1^T`` of the leading singular pair, for ``[m, n]`` or a batch
+    ``[B, m, n]``, by power iteration.  The matrix is first scaled to a spectral norm a little below one and
+    multiplied ``pre_iters`` times by ``M^T M``: that raises every singular value to the power ``2 pre_iters + 1``
+    and so widens the gap that the ``steps`` power iterations then work with."""
+    single = M.dim() == 2
+    X = M.unsqueeze(0) if single else M
+    wide = X.shape[-1] > X.shape[-2]
+    if wide:                                                       # work on the tall orientation
+        X = X.mT
+    X = X / ((X.norm(dim=(-2, -1), keepdim=True) + 1e-7) / X.shape[-1] ** 0.5)
+    gram = X.mT @ X
+    for _ in range(pre_iters):
+        X = X @ gram
+    gram = X.mT @ X
+    v = torch.randn((X.shape[0], X.shape[-1], 1), device=X.device, dtype=X.dtype)
+    for _ in range(steps):
+        v = torch.nn.functional.normalize(gram @ v, dim=1)
+    u = torch.nn.functional.normalize(X @ v, dim=1)
+    grad = u @ v.mT
+    if wide:
+        grad = grad.mT.contiguous()
+    return grad[0] if single else grad

@@ -96,3 +96,43 @@ def run_single(exp_kwargs: dict, steps: int = 3):
         tr.training_log()
         losses.append(tr.history[-1]["lm_loss"])
     return losses, [h["grad_norm"] for h in tr.history]
+
+
+def _call_worker(rank, world, port, fn, q):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    torch.set_num_threads(1)
+    try:
+        from steptronoss_b200.parallel.state import PM
+
+        PM.initialize(backend="gloo")
+        q.put((rank, fn(rank, world), None))
+        torch.distributed.barrier()
+    except BaseException:
+        import traceback
+
+        q.put((rank, None, traceback.format_exc()))
+        raise
+
+
+def call_on_ranks(fn, world: int, timeout: int = 120) -> dict:
+    """Run the module-level function ``fn(rank, world)`` on ``world`` gloo ranks; returns ``{rank: result}``."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = free_port()
+    procs = [ctx.Process(target=_call_worker, args=(r, world, port, fn, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    out = {}
+    try:
+        for _ in range(world):
+            rank, res, err = q.get(timeout=timeout)
+            if err is not None:
+                raise RuntimeError(f"rank {rank} failed:\n{err}")
+            out[rank] = res
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    return out

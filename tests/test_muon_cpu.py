@@ -1,4 +1,5 @@
 """Muon: orthogonalisation quality, the stand-alone optimizer step, and the gradient-manager path."""
+import pytest
 import torch
 
 from steptronoss_b200.optim.muon import Muon
@@ -96,3 +97,24 @@ def test_update_shaping_alternatives_have_their_stated_norms():
     assert torch.allclose(tall.norm(dim=-2), torch.ones(2, m), atol=1e-5)
     ns = get_zeropower_fn("polar_express", run_ns_in_fp16=False)(G[0], steps=8)
     assert torch.allclose(ns @ ns.T, torch.eye(m), atol=2e-2)
+
+
+def test_spectral_step_clip_and_norm_gradient_against_the_svd():
+    from steptronoss_b200.optim.zeropower import (get_clip_fun, get_max_singular_value, get_step_fun,
+                                                  weight_decay_in_spectral_norm, zeropower_via_svd)
+
+    torch.manual_seed(0)
+    U, _ = torch.linalg.qr(torch.randn(6, 4, dtype=torch.float64))
+    V, _ = torch.linalg.qr(torch.randn(4, 4, dtype=torch.float64))
+    s = torch.tensor([3.0, 1.5, 0.7, 0.2], dtype=torch.float64)
+    M = U @ torch.diag(s) @ V.mT
+    exact = lambda G, steps: zeropower_via_svd(G).to(G.dtype)
+    assert torch.allclose(get_step_fun(exact, 1.0)(M), U @ torch.diag((s > 1.0).double()) @ V.mT, atol=1e-5)
+    assert torch.allclose(get_clip_fun(exact, 1.0)(M), U @ torch.diag(s.clamp(max=1.0)) @ V.mT, atol=1e-5)
+    assert float(get_max_singular_value(M)) == pytest.approx(3.0, rel=1e-5)
+    lead = U[:, :1] @ V[:, :1].mT
+    for mat in (M, M.mT.contiguous(), torch.stack([M, 2 * M])):
+        g = weight_decay_in_spectral_norm(mat.clone(), steps=20)
+        want = lead if mat.shape == M.shape else (lead.mT if mat.dim() == 2 else torch.stack([lead, lead]))
+        sign = torch.sign((g * want).sum())                              # the pair is defined up to a common sign
+        assert torch.allclose(g * sign, want, atol=1e-4)

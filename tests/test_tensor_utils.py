@@ -1,0 +1,85 @@
+"""Partition and viewless-tensor helpers of the tensor-parallel layer: one process, and two gloo ranks for the
+gather of flat shards."""
+import pytest
+import torch
+
+from steptronoss_b200.exp.base_exp import ParallelConfig
+
+from steptronoss_b200.parallel import tensor_utils as tu
+
+
+def test_divide_and_vocab_ranges():
+    assert tu.divide(12, 4) == 3
+    with pytest.raises(AssertionError):
+        tu.divide(10, 4)
+    assert tu.VocabUtility.vocab_range_from_global_vocab_size(1024, 3, 4) == (768, 1024)
+    assert tu.VocabUtility.vocab_range_from_per_partition_vocab_size(100, 2, 8) == (200, 300)
+
+
+def test_split_along_last_dim():
+    x = torch.arange(24).view(2, 12)
+    a, b, c = tu.split_tensor_along_last_dim(x, 3)
+    assert torch.equal(b, x[:, 4:8]) and b._base is not None
+    parts = tu.split_tensor_along_last_dim(x, 3, contiguous_split_chunks=True)
+    assert all(p.is_contiguous() for p in parts)
+    with pytest.raises(AssertionError):
+        tu.split_tensor_along_last_dim(x, 5)
+
+
+def test_flat_shards_on_one_rank_round_trip():
+    x = torch.arange(10.0).view(2, 5)
+    piece = tu.split_tensor_into_1d_equal_chunks(x)
+    assert piece.data_ptr() == x.data_ptr() and piece.shape == (10,)
+    copy = tu.split_tensor_into_1d_equal_chunks(x, new_buffer=True)
+    assert copy.data_ptr() != x.data_ptr()
+    assert torch.equal(tu.gather_split_1d_tensor(piece), x.reshape(-1))
+
+
+def test_viewless_tensor_drops_the_base_but_keeps_the_graph():
+    base = torch.randn(4, 6, requires_grad=True)
+    view = (base * 2)[1:3]
+    assert view._base is not None
+    with pytest.raises(AssertionError):
+        tu.assert_viewless_tensor(view)
+    out = tu.make_viewless_tensor(view, requires_grad=True, keep_graph=True)
+    assert out._base is None and out.data_ptr() == view.data_ptr() and tu.assert_viewless_tensor([out]) == [out]
+    out.sum().backward()
+    assert torch.equal(base.grad[1:3], torch.full((2, 6), 2.0)) and float(base.grad[0].abs().sum()) == 0.0
+    detached = tu.make_viewless_tensor(view.detach(), requires_grad=False, keep_graph=False)
+    assert detached._base is None and not detached.requires_grad
+    plain = torch.zeros(3)
+    assert tu.make_viewless_tensor(plain, False, False) is plain
+    tu.safely_set_viewless_tensor_data(detached, torch.ones(2))
+    assert detached.shape == (2,)
+    with pytest.raises(AssertionError):
+        tu.safely_set_viewless_tensor_data(view, torch.ones(2))
+
+
+def test_which_parameter_copy_counts():
+    p = torch.nn.Parameter(torch.zeros(2))
+    assert tu.param_is_not_shared(p) and tu.param_is_not_tensor_parallel_duplicate(p)     # one rank: TP rank 0
+    p.shared = True
+    p.tensor_model_parallel = True
+    assert not tu.param_is_not_shared(p) and tu.param_is_not_tensor_parallel_duplicate(p)
+    assert tu.param_is_not_expert_parallel_duplicate(p)
+
+
+def _flat_shards_worker(rank, world):
+    from steptronoss_b200.parallel.state import PM
+
+    pc = ParallelConfig()
+    pc.tensor_model_parallel_size = 2
+    PM.set_mesh(pc)
+    full = torch.arange(12.0).view(3, 4)
+    mine = tu.split_tensor_into_1d_equal_chunks(full)
+    return {"piece": mine.tolist(), "gathered": tu.gather_split_1d_tensor(mine).tolist(),
+            "counts": tu.param_is_not_tensor_parallel_duplicate(torch.nn.Parameter(torch.zeros(1)))}
+
+
+def test_flat_shards_gather_over_two_ranks():
+    from tests.dist_helpers import call_on_ranks
+
+    got = call_on_ranks(_flat_shards_worker, 2)
+    assert got[0]["piece"] == list(range(6)) and got[1]["piece"] == list(range(6, 12))
+    assert got[0]["gathered"] == got[1]["gathered"] == [float(i) for i in range(12)]
+    assert got[0]["counts"] and not got[1]["counts"]                      # a replicated parameter counts once
