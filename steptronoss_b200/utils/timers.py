@@ -59,8 +59,14 @@ class Timer:
 
 
 class _Noop:
-    def start(self): pass   # noqa: E704
-    def stop(self): pass    # noqa: E704
+    """Stands in for a timer whose level is above the configured one: every call is free."""
+
+    name = "noop"
+
+    def start(self, *a, **k): pass   # noqa: E704
+    def stop(self, *a, **k): pass    # noqa: E704
+    def reset(self): pass            # noqa: E704
+    def elapsed(self, *a, **k): return 0.0   # noqa: E704
     def __enter__(self): return self   # noqa: E704
     def __exit__(self, *a): return False   # noqa: E704
 
@@ -113,6 +119,51 @@ class Timers:
     def log_string(self, normalizer: float = 1.0, reset: bool = True) -> str:
         rep = self.report(normalizer=normalizer, reset=reset)
         return "time (ms) | " + " | ".join(f"{k}: {v:.2f}" for k, v in rep.items())
+
+    def write(self, writer, iteration: int, normalizer: float = 1.0, reset: bool = False) -> dict:
+        """One ``Timers/<name>`` scalar per timer that ran, in seconds per ``normalizer`` calls (this rank's times;
+        reference: timers.py:241-254).  Returns what was written."""
+        if normalizer <= 0:
+            raise ValueError("normalizer must be positive")
+        rep = {n: ms / 1e3 for n, ms in self.report(normalizer=normalizer, reset=reset).items() if ms > 0}
+        if writer is not None:
+            for name, seconds in rep.items():
+                writer.add_scalar("Timers/" + name, seconds, iteration)
+        return rep
+
+    def log(self, iteration: int, normalizer: float = 1.0, reset: bool = True, prefix: str = "") -> str:
+        """Log the timers that ran, one per line, in seconds (reference: timers.py:256-266)."""
+        rep = {n: ms / 1e3 for n, ms in self.report(normalizer=normalizer, reset=reset).items() if ms > 0}
+        if not rep:
+            return ""
+        from .logger import logger
+
+        text = f"{prefix or f'iteration {iteration}'} | Activated Timers:\n" + "".join(
+            f"{name}".ljust(48, ".") + f"{seconds:.4e} s\n" for name, seconds in rep.items())
+        logger.info(text, at=0)
+        return text
+
+    def reload(self, new_log_level: int, new_use_event: bool) -> None:
+        """Change level and clock at run time (a profiler window that wants finer timers for some iterations).
+        Timers that exist keep their accumulated time and take the new clock from their next ``start``."""
+        self.log_level = min(int(new_log_level), 2)
+        self.use_event = bool(new_use_event)
+        for t in self.timers.values():
+            if not t.started:
+                t.use_event = self.use_event and torch.cuda.is_available()
+
+
+# the reference's class names: its code checks ``isinstance(timers, DummyTimers)`` and annotates with ``LocalTimers``
+LocalTimers = Timers
+TimerBase = Timer
+DummyTimer = _Noop
+
+
+class DummyTimers(Timers):
+    """Timers that time nothing (log level below every timer's level)."""
+
+    def __init__(self):
+        super().__init__(log_level=-(10 ** 6))
 
 
 _GLOBAL = Timers()

@@ -31,6 +31,44 @@ def test_timers_levels_scopes_and_report():
     init_timers()
 
 
+def test_timers_write_log_and_reload():
+    from steptronoss_b200.utils.timers import DummyTimers, LocalTimers, init_timers
+
+    t = init_timers(log_level=1, use_event=False)
+    assert isinstance(t, LocalTimers) and not isinstance(t, DummyTimers)
+    with t.record("step", 1):
+        time.sleep(0.02)
+    t("never-ran", 1)
+
+    class Writer:
+        def __init__(self):
+            self.rows = []
+
+        def add_scalar(self, name, value, it):
+            self.rows.append((name, value, it))
+
+    w = Writer()
+    wrote = t.write(w, 7, normalizer=2.0)
+    assert list(wrote) == ["step"] and w.rows == [("Timers/step", wrote["step"], 7)] and 0.005 < wrote["step"] < 0.05
+    text = t.log(7, prefix="iteration 7/100")
+    assert text.startswith("iteration 7/100 | Activated Timers:") and "step....." in text and "never-ran" not in text
+    assert t.log(8) == ""                                         # the log reset the timers
+    with t.record("fine", 2):
+        pass
+    assert "fine" not in t.timers
+    t.reload(5, False)                                            # levels are capped at 2
+    assert t.log_level == 2
+    with t.record("fine", 2):
+        time.sleep(0.005)
+    assert t.report()["fine"] > 0
+    d = DummyTimers()
+    with d.record("anything", 0):
+        pass
+    d("x").start()
+    assert d.report() == {} and d("x").elapsed() == 0.0
+    init_timers()
+
+
 def test_memory_marks_only_when_enabled(monkeypatch):
     from steptronoss_b200.utils import memory_tracker
     from steptronoss_b200.utils.memory_tracker import MemoryTracker
@@ -52,6 +90,13 @@ def test_memory_marks_only_when_enabled(monkeypatch):
     rep = on.report()
     assert "after-alloc" in rep and "largest deltas" in rep
     del blob
+    unnamed = on.mark()                                          # named after the calling module and line
+    assert unnamed.name.startswith(__name__ + ":")
+    rec = on.records()[-1]
+    assert rec["mark"] == unnamed.name and rec["cpu_rss"] == float(held[0]) and rec["time"] > 0
+    assert "largest peaks" in on.report_over_world()             # one process: this rank's report
+    assert memory_tracker.get_caller_name() == __name__ and memory_tracker.get_caller_name(50) == "<unknown>"
+    assert memory_tracker.CudaMemoryTracker is MemoryTracker
     on.reset()
     assert on.marks == []
 
