@@ -10,6 +10,52 @@ from __future__ import annotations
 import math
 from abc import ABC, abstractmethod
 from dataclasses import dataclass, field, replace
+from typing import TypeAlias, TypedDict
+
+# ---- shapes of the JSON payloads that travel through prompts and prediction dumps ------------------------------
+JsonScalar: TypeAlias = None | bool | int | float | str
+JsonValue: TypeAlias = JsonScalar | list["JsonValue"] | dict[str, "JsonValue"]
+JsonObject: TypeAlias = dict[str, JsonValue]
+
+
+class GroundTruthValue(TypedDict):
+    """Which benchmark item a turn of an exported conversation refers to."""
+
+    item_id: str
+    dataset: str
+
+
+class GroundTruth(TypedDict):
+    value: GroundTruthValue
+
+
+class ChatMessage(TypedDict, total=False):
+    """One chat turn as the tokenizer template and the chat API take it; ``ground_truth`` rides along on exported
+    assistant turns and is never rendered."""
+
+    role: str
+    content: str
+    ground_truth: GroundTruth
+
+
+Messages: TypeAlias = list[ChatMessage]
+
+
+class CompletionMessage(TypedDict, total=False):
+    """``message`` of a chat/completions choice."""
+
+    content: str
+    reasoning_content: str
+
+
+class CompletionChoice(TypedDict, total=False):
+    """A sampled completion as kept in prediction dumps: ``text`` from completion-style back-ends, ``message`` from
+    chat-style ones, ``raw`` the back-end's own object."""
+
+    finish_reason: str
+    text: str
+    message: CompletionMessage
+    raw: JsonObject
 
 
 @dataclass(frozen=True)
@@ -121,6 +167,16 @@ class Generated:
                             extra_body=sp))
         case = EvaluationCase(prompt, BenchmarkMeta(**d["benchmark"]), EvaluationMeta(**d["evaluation"]))
         return cls(case, d.get("choice"), d.get("response", ""), d.get("reasoning_content"), d.get("error"))
+
+
+def build_demo_generated(response: str = "3") -> Generated:
+    """The smallest complete prompt -> answer record, for documentation and for tests of new benchmarks."""
+    case = EvaluationCase(
+        prompt=Prompt(messages=[ChatMessage(role="user", content="How many r are in strawberry?")], prompt_token_count=3,
+                      sampling_params=SamplingParams(seed=0, max_tokens=8)),
+        benchmark=BenchmarkMeta(benchmark_name="demo_count_r", item_id="strawberry_r_count_0", context={"answer": "3"}),
+        evaluation=EvaluationMeta(prompt_index=0, run_index=0))
+    return Generated(case=case, response=response)
 
 
 def estimate_pass_at_k(num_samples: int, num_successes: int, k: int) -> float:

@@ -70,6 +70,13 @@ class RNGStatesTracker:
 _TRACKER = RNGStatesTracker()
 
 
+CudaRNGStatesTracker = RNGStatesTracker          # the reference's names (core/tensor_parallel/random.py)
+
+
+def get_cuda_rng_tracker() -> RNGStatesTracker:
+    return get_rng_tracker()
+
+
 def get_rng_tracker() -> RNGStatesTracker:
     return _TRACKER
 

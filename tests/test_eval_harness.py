@@ -101,3 +101,19 @@ def test_benchmark_eval_config_runs_items(tmp_path):
     out = cfg.eval()
     assert abs(out["GPQA_DIAMOND"].score_avg - 2 / 6) < 1e-9
     assert sum(1 for _ in open(tmp_path / "dump" / "GPQA_DIAMOND.jsonl")) == 12
+
+
+def test_demo_record_round_trips_and_payload_shapes_are_plain_dicts():
+    from steptronoss_b200.generation.base_benchmark import (ChatMessage, CompletionChoice, CompletionMessage, Generated,
+                                                            GroundTruth, GroundTruthValue, build_demo_generated)
+
+    g = build_demo_generated()
+    assert g.response == "3" and g.case.benchmark.context == {"answer": "3"} and g.finish_reason == "unknown"
+    again = Generated.from_dict(g.to_dict())
+    assert again.case == g.case and again.response == "3"
+    gt: GroundTruth = {"value": GroundTruthValue(item_id="q1", dataset="demo")}
+    msg = ChatMessage(role="assistant", content="3", ground_truth=gt)
+    choice = CompletionChoice(finish_reason="stop", message=CompletionMessage(content="3"), raw={"index": 0})
+    assert msg == {"role": "assistant", "content": "3", "ground_truth": {"value": {"item_id": "q1", "dataset": "demo"}}}
+    g.choice = choice
+    assert g.finish_reason == "stop" and Generated.from_dict(g.to_dict()).choice == dict(choice)

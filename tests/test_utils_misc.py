@@ -492,3 +492,20 @@ def test_metric_holder_fork_and_disable_and_inverse_reshape_op():
     merged = Inverse(ColumnParallel()).forward({"w": list(w.chunk(2))})      # the backward of a split is the concatenation
     assert torch.equal(merged["w"], w)
     assert [t.tolist() for t in Inverse(ColumnParallel()).backward({"w": w})["w"]] == [w.tolist()]
+
+
+def test_seeding_helper_and_rng_tracker_names():
+    import random
+
+    import numpy as np
+
+    from steptronoss_b200 import initialize
+    from steptronoss_b200.parallel.random import CudaRNGStatesTracker, get_cuda_rng_tracker, get_rng_tracker
+
+    draws = []
+    for _ in range(2):
+        initialize.set_random_seed(5)
+        draws.append((random.random(), float(np.random.rand()), float(torch.rand(1))))
+    assert draws[0] == draws[1]
+    assert get_cuda_rng_tracker() is get_rng_tracker() and isinstance(get_rng_tracker(), CudaRNGStatesTracker)
+    assert callable(initialize.mtp_initialize) and callable(initialize.set_mpu_random_seed)
