@@ -35,6 +35,9 @@ class MoEPretrainMetricConfig(PretrainMetricConfig):
             setattr(self, name, ModelLayerMetric().mean("time").mean("dp").sum("pp"))
 
 
+MoePretrainMetricConfig = MoEPretrainMetricConfig        # the reference's spelling (exp/ntp.py)
+
+
 class NTPTrainerConfig(TrainerConfig):
     micro_batch_size: int = 1
     global_batch_size: int = 8

@@ -133,13 +133,26 @@ class PPOCheckpointCfg(CheckpointConfig):
 class PPOMetricConfig(MetricConfig):
     def __init__(self):
         super().__init__()
-        from ..utils.metrics import GroupMetric, Metric, PercentageMetric, TextMetric
+        from ..utils.metrics import GroupMetric, HistogramMetric, Metric, PercentageMetric, TextMetric
 
         self.reward_mean = Metric().mean("time").mean("dp")
         self.reward_max = Metric().max("time").max("dp")
         self.reward_min = Metric().min("time").min("dp")
         self.correctness = PercentageMetric().sum("world")
+        self.correctness_subclass = PercentageMetric().sum("world")       # the same, split by reward function
         self.reward_func_mean = GroupMetric().mean("time").mean("world")
+        self.reward_func_max = GroupMetric().mean("time").max("world")
+        self.reward_func_min = GroupMetric().mean("time").min("world")
+        # rewards, response lengths, truncation and log-probabilities grouped by the data file a prompt came from
+        # and by its reward function
+        self.reward_filename_mean = GroupMetric().mean("time").mean("world")
+        self.reward_filename_max = GroupMetric().mean("time").max("world")
+        self.reward_filename_min = GroupMetric().mean("time").min("world")
+        self.rollout_avg_tokens_grouped = GroupMetric().mean("time").mean("world")
+        self.truncated_rate_grouped = GroupMetric().mean("time").mean("world")
+        self.rollout_logprob_grouped = GroupMetric().mean("time").mean("world")
+        self.rollout_samples = Metric().mean("time")
+        self.rollout_tokens_hist = HistogramMetric().disable()
         self.rollout_avg_tokens = Metric().mean("time")
         self.rollout_avg_solution_tokens = Metric().mean("time")
         self.rollout_avg_think_tokens = Metric().mean("time")
@@ -170,6 +183,25 @@ class PPOMetricConfig(MetricConfig):
         self.sample_filter_rate = Metric().mean("time")
         self.logprob_diff_mean = Metric().mean("time").mean("dp")
         self.logprob_diff_max = Metric().max("time").max("dp")
+        # off-policy diagnostics: the policy that trains against the one that sampled (an inference engine's
+        # numerics when the run is on-policy).  Quantile groups carry min, max, q01, q05, q10, q90, q95, q99.
+        self.sampling_logprob_diff = Metric().mean("time").mean("dp")
+        self.sampling_logprob_diff_max = Metric().max("time").max("dp")
+        self.sampling_logprob_diff_quantile = GroupMetric().mean("time").mean("dp")
+        self.sampling_ratio_diff = GroupMetric().mean("time").mean("dp")
+        self.new_logprob = GroupMetric().mean("time").mean("dp")
+        self.old_logprob = GroupMetric().mean("time").mean("dp")
+        self.new_prob = GroupMetric().mean("time").mean("dp")
+        self.old_prob = GroupMetric().mean("time").mean("dp")
+        self.ppo_clip_count = Metric().mean("time").mean("dp")                # share of clipped tokens
+        self.ppo_lower_bound_clip_count = Metric().mean("time").mean("dp")
+        self.ppo_upper_bound_clip_count = Metric().mean("time").mean("dp")
+        self.ratio_diff = Metric().mean("time").mean("dp")                    # mean |pi / pi_old - 1|
+        self.ratio_diff_quantile = GroupMetric().mean("time").mean("dp")
+        self.reverse_kl_with_sample_dist = Metric().mean("time").mean("dp")
+        self.ppo_value_clip_count = Metric().mean("time").mean("dp")
+        self.ppo_returns = Metric().mean("time").mean("dp")
+        self.ppo_values = Metric().mean("time").mean("dp")
         self.training_generation_text = TextMetric(20)
         self.eval_generation_text = TextMetric(10)
 
@@ -387,7 +419,15 @@ class PPOLikeTrainerConfig(TrainerConfig):
         if self.dual_clip_eps and self.dual_clip_eps > 1:
             pg = torch.where(adv < 0, torch.minimum(pg, -self.dual_clip_eps * adv), pg)
         loss = pg.mean()
-        GlobalMetrics.ppo_clip_frac.add(((ratio - 1).abs() > self.ppo_clip).float().mean().detach())
+        with torch.no_grad():
+            low, high = (ratio < 1 - self.ppo_clip) & (adv < 0), (ratio > 1 + self.ppo_clip) & (adv > 0)
+            GlobalMetrics.ppo_clip_frac.add(((ratio - 1).abs() > self.ppo_clip).float().mean())
+            GlobalMetrics.ppo_clip_count.add((low | high).float().mean())     # tokens whose gradient the clip removed
+            GlobalMetrics.ppo_lower_bound_clip_count.add(low.float().mean())
+            GlobalMetrics.ppo_upper_bound_clip_count.add(high.float().mean())
+            GlobalMetrics.ratio_diff.add((ratio - 1).abs().mean())
+            # E_old[r log r]: KL(new || old) estimated on the old policy's samples
+            GlobalMetrics.reverse_kl_with_sample_dist.add((ratio * (new_lp - old_lp)).mean())
         if samples.ref_logprobs is not None and self.ref_kl_loss_coeff > 0:
             kl = (new_lp - samples.ref_logprobs.to(new_lp.device)).mean()
             loss = loss + self.ref_kl_loss_coeff * kl
@@ -416,6 +456,9 @@ class PPOLikeTrainerConfig(TrainerConfig):
         l1, l2 = (values - target) ** 2, (clipped - target) ** 2
         loss = 0.5 * torch.maximum(l1, l2).mean()
         GlobalMetrics.value_clip_frac.add((l2 > l1).float().mean().detach())
+        GlobalMetrics.ppo_value_clip_count.add((l2 > l1).float().mean().detach())
+        GlobalMetrics.ppo_returns.add(target.mean().detach())
+        GlobalMetrics.ppo_values.add(values.mean().detach())
         GlobalMetrics.critic_loss.add(loss.detach())
         return loss * loss_scale
 
@@ -457,6 +500,15 @@ class PPOLikeTrainerConfig(TrainerConfig):
         lps = [s.logprobs.float().mean() for s in all_samples if s.logprobs is not None and len(s.logprobs)]
         if lps:
             GlobalMetrics.rollout_logprob.add(torch.stack(lps).mean())
+        GlobalMetrics.rollout_samples.add(float(len(all_samples)))
+        for s, n in zip(all_samples, n_gen):
+            GlobalMetrics.rollout_tokens_hist.add(float(n))
+            cut = float(s.stop_type in (StopType.MAX_LEN, StopType.MAX_DECODE))
+            for tag in _sample_tags(s):
+                GlobalMetrics.rollout_avg_tokens_grouped.add(float(n), subname=tag)
+                GlobalMetrics.truncated_rate_grouped.add(cut, subname=tag)
+                if s.logprobs is not None and len(s.logprobs):
+                    GlobalMetrics.rollout_logprob_grouped.add(s.logprobs.float().mean(), subname=tag)
 
     def log_reward_metrics(self, all_samples: list) -> None:
         from ..utils.metrics import GlobalMetrics
@@ -468,17 +520,26 @@ class PPOLikeTrainerConfig(TrainerConfig):
         GlobalMetrics.reward_max.add(r.max())
         GlobalMetrics.reward_min.add(r.min())
         groups: dict = {}
+        kind_of_prompt: dict = {}
         for s in all_samples:
             groups.setdefault(s.prompt_id, []).append(float(s.raw_reward))
+            fn_tag, file_tag = _sample_tags(s)
+            kind_of_prompt[s.prompt_id] = fn_tag
+            for m in (GlobalMetrics.reward_func_mean, GlobalMetrics.reward_func_max, GlobalMetrics.reward_func_min):
+                m.add(float(s.raw_reward), subname=fn_tag)
+            for m in (GlobalMetrics.reward_filename_mean, GlobalMetrics.reward_filename_max, GlobalMetrics.reward_filename_min):
+                m.add(float(s.raw_reward), subname=file_tag)
         for s in all_samples:
             g = groups[s.prompt_id]
             if s.meta is None:
                 s.meta = {}
             s.meta["group_mean_reward"] = sum(g) / len(g)
         kinds = {"all_correct": 0, "all_fail": 0, "some_correct": 0}
-        for g in groups.values():
+        for pid, g in groups.items():
             ok = sum(x >= 0.5 for x in g)
-            kinds["all_correct" if ok == len(g) else "all_fail" if ok == 0 else "some_correct"] += 1
+            kind = "all_correct" if ok == len(g) else "all_fail" if ok == 0 else "some_correct"
+            kinds[kind] += 1
+            GlobalMetrics.correctness_subclass.add(1.0, subname=f"{kind}/{kind_of_prompt[pid]}")
         for k, v in kinds.items():
             GlobalMetrics.correctness.add(float(v), subname=k)
 
@@ -491,6 +552,36 @@ class PPOLikeTrainerConfig(TrainerConfig):
             d = torch.cat(diffs)
             GlobalMetrics.logprob_diff_mean.add(d.mean())
             GlobalMetrics.logprob_diff_max.add(d.max())
+            GlobalMetrics.sampling_logprob_diff.add(torch.stack([x.mean() for x in diffs]).mean())   # mean over samples
+            GlobalMetrics.sampling_logprob_diff_max.add(d.max())
+            pairs = [(s.actor_logprobs.float().cpu(), s.logprobs.float().cpu()) for s in samples
+                     if s.actor_logprobs is not None and s.logprobs is not None and len(s.logprobs)]
+            new, old = torch.cat([a for a, _ in pairs]), torch.cat([b for _, b in pairs])
+            for metric, data in ((GlobalMetrics.sampling_logprob_diff_quantile, d),
+                                 (GlobalMetrics.sampling_ratio_diff, (torch.exp(new - old) - 1).abs()),
+                                 (GlobalMetrics.ratio_diff_quantile, torch.exp(new - old) - 1),
+                                 (GlobalMetrics.new_logprob, new), (GlobalMetrics.old_logprob, old),
+                                 (GlobalMetrics.new_prob, new.exp()), (GlobalMetrics.old_prob, old.exp())):
+                for tag, value in quantile_summary(data).items():
+                    metric.add(value, subname=tag)
+
+
+def _sample_tags(sample) -> tuple[str, str]:
+    """``(reward function, data file)`` a sample's prompt belongs to, from its ground truth (``"default"`` /
+    ``"unknown"`` when the data does not say), the two keys the grouped rollout metrics are kept under."""
+    gt = sample.ground_truth if isinstance(getattr(sample, "ground_truth", None), dict) else {}
+    path = str(gt.get("file_path", "unknown"))
+    return str(gt.get("reward_fn_type", "default")), os.path.basename(path).split(".")[0] or "unknown"
+
+
+def quantile_summary(data: torch.Tensor, max_elems: int = 200000) -> dict:
+    """``min / max`` of all entries and ``q01 q05 q10 q90 q95 q99`` of a random tenth of them (at most ``max_elems``;
+    quantiles of a million token log-probabilities per step would cost more than they tell)."""
+    flat = data.detach().float().flatten().cpu()
+    take = max(min(flat.numel() // 10, max_elems), 1)
+    picked = flat[torch.randperm(flat.numel())[:take]]
+    q = torch.quantile(picked, torch.tensor([0.01, 0.05, 0.1, 0.9, 0.95, 0.99]))
+    return {"min": flat.min(), "max": flat.max(), **dict(zip(("q01", "q05", "q10", "q90", "q95", "q99"), q))}
 
 
 class PPOLikeExp(BaseExp):

@@ -296,8 +296,19 @@ class MoeShareExpertFFN(nn.Module):
             if lim:
                 self.share_expert.limit = float(lim)
 
+    def _log_norm(self, t, which: str) -> None:
+        # mean row norm of the routed and of the shared branch (reference: model/common/moe_share_expert_ffn.py:59-74);
+        # computed only where an experiment registers the metric - its default metric sets do not
+        if "shared_routed_avgnorm" in GlobalMetrics:
+            with torch.no_grad():
+                GlobalMetrics.shared_routed_avgnorm.add(t.detach().float().norm(dim=-1).mean(),
+                                                        subname=f"layer{self.moe.moe_layer_id}.{which}")
+
     def forward(self, x, recompute: bool = False):
         out = self.moe(x, recompute=recompute)
+        self._log_norm(out, "routed")
         if self.enable_share_expert:
-            out = out + self.share_expert(x)
+            shared = self.share_expert(x)
+            self._log_norm(shared, "shared")
+            out = out + shared
         return out

@@ -229,7 +229,11 @@ class PPOTrainer(BaseTrainer):
                 s.logprobs = torch.zeros(int(s.is_gen_mask.sum()), dtype=torch.float32)
             if s.meta is None:
                 s.meta = {}
-            out.append(PPOSample(**dict(s.items())))
+            sample = PPOSample(**dict(s.items()))
+            gt = s.meta.get("ground_truth")                 # what the prompt's data row says about scoring and origin
+            if isinstance(gt, dict):
+                sample.ground_truth = gt
+            out.append(sample)
         return out
 
     def generate_trajectory(self) -> list:

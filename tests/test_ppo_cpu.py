@@ -40,7 +40,9 @@ class FakeRollout(TrainableItem):
             # reward: fraction of even tokens in the response (something a policy can learn)
             r = sum(t % 2 == 0 for t in toks[p:]) / g
             out.append(EnvTrajectory(trajectory=toks, is_gen_mask=[0] * p + [1] * g, raw_reward=r,
-                                     logprobs=[-3.0] * g, meta={"idx": self.idx}))
+                                     logprobs=[-3.0] * g,
+                                     meta={"idx": self.idx, "ground_truth": {"reward_fn_type": "parity",
+                                                                             "file_path": "/data/evens.jsonl"}}))
         return out
 
 
@@ -157,6 +159,14 @@ def test_ppo_trains_and_checkpoints(tmp_path, use_critic):
     assert moved > 0
     keys = tr.history[-1]
     assert "reward_mean" in keys and "ppo_loss" in keys and (not use_critic or "critic_loss" in keys)
+    # grouped by the prompt's reward function and data file, and the off-policy quantile groups
+    for key in ("reward_func_max/parity", "reward_filename_mean/evens", "rollout_avg_tokens_grouped/parity",
+                "truncated_rate_grouped/evens", "correctness_subclass/some_correct/parity", "new_logprob/q90",
+                "sampling_ratio_diff/max", "ppo_clip_count", "ratio_diff", "rollout_samples"):
+        assert key in keys, key
+    assert float(keys["reward_func_min/parity"]) <= float(keys["reward_func_mean/parity"]) <= float(keys["reward_func_max/parity"])
+    assert float(keys["old_logprob/min"]) == pytest.approx(-3.0) and float(keys["rollout_samples"]) == 12.0
+    assert (not use_critic) or "ppo_values" in keys
     it_dir = os.path.join(exp.checkpoint_cfg.save_path, "it2")
     assert os.path.isdir(os.path.join(it_dir, "actor")) and os.path.exists(os.path.join(it_dir, "data.pkl"))
     assert os.path.isdir(os.path.join(it_dir, "critic")) == use_critic
@@ -202,3 +212,17 @@ def test_evaluation_schedule_and_score_logging():
     summary = PPOTrainer.eval(tr)
     assert evals == [1] and summary["AIME2025"]["metric"]["score_avg"] == 0.25
     assert logged == [("eval/AIME2025/score_avg", 0.25, 4)]
+
+
+def test_quantile_summary_and_sample_tags():
+    from steptronoss_b200.exp.rl import _sample_tags, quantile_summary
+
+    torch.manual_seed(0)
+    q = quantile_summary(torch.arange(1000.0))
+    assert float(q["min"]) == 0.0 and float(q["max"]) == 999.0
+    assert float(q["q01"]) <= float(q["q10"]) <= float(q["q90"]) <= float(q["q99"]) and 700 < float(q["q90"])
+    assert set(quantile_summary(torch.tensor([2.0]))) == {"min", "max", "q01", "q05", "q10", "q90", "q95", "q99"}
+    s = PPOSample()
+    assert _sample_tags(s) == ("default", "unknown")
+    s.ground_truth = {"reward_fn_type": "math", "file_path": "s3://bucket/train/gsm8k.v2.jsonl"}
+    assert _sample_tags(s) == ("math", "gsm8k")

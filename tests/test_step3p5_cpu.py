@@ -62,6 +62,9 @@ def test_step3p5_layers_follow_the_swa_list_and_train():
     assert [b.attention.num_heads for b in blocks] == [8, 4, 8]
     assert not hasattr(blocks[0].feed_forward, "moe") and hasattr(blocks[1].feed_forward, "moe")
     assert blocks[1].feed_forward.enable_share_expert
+    from steptronoss_b200.utils.metrics import GlobalMetrics, ModelLayerMetric
+
+    GlobalMetrics.register("shared_routed_avgnorm", ModelLayerMetric().mean("time"))    # opt-in diagnostic
     losses = []
     for _ in range(4):
         tr.train_step()
@@ -69,6 +72,9 @@ def test_step3p5_layers_follow_the_swa_list_and_train():
         tr.training_log()
         losses.append(tr.history[-1]["lm_loss"])
     assert all(l == l for l in losses) and losses[-1] < losses[0]
+    norms = {k: float(v) for k, v in tr.last_metrics.items() if k.startswith("shared_routed_avgnorm/")}
+    assert set(norms) == {f"shared_routed_avgnorm/layer{i}.{b}" for i in (0, 1) for b in ("routed", "shared")}
+    assert all(v > 0 for v in norms.values())
 
 
 def test_step3p5_hf_mapping_round_trip():
