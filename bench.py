@@ -230,6 +230,7 @@ def run_ours(args):
         rec = f"{rec} (first {rec_layers} layers)"
     exp.resource_cfg.gpu = world
     os.environ.setdefault("WORLD_SIZE", str(world))
+    os.environ.setdefault("STEPTRON_QUIET_EXP", "1")     # the config tree is not part of a benchmark log
     exp.sanity_check()
     trainer = exp.trainer_cfg.get_trainer_cls()(exp=exp)
     trainer.before_train()

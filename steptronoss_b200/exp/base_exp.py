@@ -79,6 +79,35 @@ class TrainerConfig(AbstractTrainerConfig):
     model_cfg = Ref("..model_cfg", None)
     data_cfg = Ref("..data_cfg", None)
 
+    # ---- hook points: each returns a list of ``fn(trainer)``; override in an experiment's trainer config -----------
+    def build_after_init_hooks(self) -> list:
+        """Run once the process group, the mesh and the metrics exist, before any model is built.  By default the
+        log rank prints the resolved experiment tree, so that a job's log says what was run."""
+
+        def print_exp(trainer):
+            from ..utils.logger import logger
+
+            if int(os.getenv("RANK", "0")) == 0 and not os.getenv("STEPTRON_QUIET_EXP"):
+                try:
+                    logger.info(f"experiment:\n{self.root()}", at=None)
+                except Exception as e:      # a tree that cannot be printed must not stop a job
+                    logger.warning(f"could not print the experiment tree: {e}", at=None)
+
+        return [print_exp]
+
+    def build_before_train_hooks(self) -> list:
+        """Run right after the ``after_init`` hooks, before models, optimizer and data are built."""
+        return []
+
+    def build_before_step_hooks(self) -> list:
+        return []
+
+    def build_after_step_hooks(self) -> list:
+        return []
+
+    def build_after_train_hooks(self) -> list:
+        return []
+
     def make_logs(self, iteration: int, metrics: dict, tb_writer: Any = None) -> dict:
         """Route reduced metrics: scalars to the writer and to the console line."""
         scalars = {}

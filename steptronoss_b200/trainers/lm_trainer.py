@@ -56,7 +56,9 @@ class DecoderPretrainTrainer(BaseTrainer):
                 self.writer = exp.build_log_writer()
             except Exception as e:
                 logger.warning(f"no log writer: {e}", at=None)
+        self.build_hooks(exp.trainer_cfg)
         self.call_hooks("after_init")
+        self.call_hooks("before_train")
         self.setup_model()
         self.grad_manager = exp.optimizer_cfg.build_gradient_manager(self.models)
         self.build_dataloader()

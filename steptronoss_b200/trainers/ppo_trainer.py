@@ -105,7 +105,9 @@ class PPOTrainer(BaseTrainer):
                 self.writer = exp.build_log_writer()
             except Exception as e:
                 logger.warning(f"no log writer: {e}", at=None)
+        self.build_hooks(exp.trainer_cfg)
         self.call_hooks("after_init")
+        self.call_hooks("before_train")
 
     def before_train(self):
         self.initialize_dist()

@@ -208,3 +208,41 @@ def test_memory_options_leave_the_loss_curve_unchanged(change):
         setattr(node, leaf, value)
     got, _, _ = _run(e, steps=3)
     assert got == pytest.approx(base, rel=1e-6)
+
+
+def test_hooks_built_by_the_trainer_config_run_at_their_points():
+    from steptronoss_b200.exp.ntp import NTPTrainerConfig
+
+    calls = []
+
+    class HookedTrainer(NTPTrainerConfig):
+        def build_after_init_hooks(self):
+            return super().build_after_init_hooks() + [lambda tr: calls.append(("after_init", bool(getattr(tr, "models", None))))]
+
+        def build_before_train_hooks(self):
+            return [lambda tr: calls.append(("before_train", None))]
+
+        def build_before_step_hooks(self):
+            return [lambda tr: calls.append(("before_step", tr.iteration))]
+
+        def build_after_step_hooks(self):
+            return [lambda tr: calls.append(("after_step", tr.iteration))]
+
+        def build_after_train_hooks(self):
+            return [lambda tr: calls.append(("after_train", tr.iteration))]
+
+    e = _make()
+    e.data_cfg = FixedDataConfig
+    old = e.trainer_cfg
+    e.trainer_cfg = HookedTrainer
+    for k in ("global_batch_size", "global_seq_length", "micro_batch_size", "train_iters", "writer_backend", "log_interval"):
+        setattr(e.trainer_cfg, k, getattr(old, k))
+    e.trainer_cfg.train_iters = 2
+    tr = e.trainer_cfg.get_trainer_cls()(exp=e)
+    tr.train()
+    names = [c[0] for c in calls]
+    assert names[:2] == ["after_init", "before_train"] and names[-1] == "after_train"
+    assert names.count("before_step") == names.count("after_step") == 2
+    assert calls[0] == ("after_init", False)                                       # runs before the models exist
+    tr.build_hooks(e.trainer_cfg)                                                  # a second call adds nothing
+    assert len(tr._hooks["before_step"]) == 1
