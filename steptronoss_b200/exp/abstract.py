@@ -25,6 +25,9 @@ class MetricConfig(Config):
     def to_dict(self, rep: bool = False):
         return {k: repr(v) for k, v in self.items()}
 
+    def register_metric(self) -> None:
+        """Hook for metric configs that create metrics at run time (the declared ones are registered by ``register``)."""
+
     def register(self) -> None:
         pass
 

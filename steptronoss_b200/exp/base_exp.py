@@ -52,6 +52,7 @@ class MetricConfig(AbstractMetricConfig):
     def register(self) -> None:
         from ..utils.metrics import GlobalMetrics
 
+        self.register_metric()
         GlobalMetrics.batch_register(self)
 
     def __init__(self) -> None:
@@ -331,6 +332,11 @@ class BaseExp(Config):
 
     @property
     def log_path(self):
+        return os.path.join(self.log_dir, self.exp_name)
+
+    @writable_property
+    def exp_log_dir(self):
+        """Where this experiment's logs go: ``log_dir/exp_name`` unless assigned (reference: exp/abstract.py:154-159)."""
         return os.path.join(self.log_dir, self.exp_name)
 
     def update_from_args(self, argv=None):

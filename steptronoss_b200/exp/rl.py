@@ -501,6 +501,9 @@ class PPOLikeTrainerConfig(TrainerConfig):
         if lps:
             GlobalMetrics.rollout_logprob.add(torch.stack(lps).mean())
         GlobalMetrics.rollout_samples.add(float(len(all_samples)))
+        tokenizer = self.build_tokenizer() if callable(getattr(self, "build_tokenizer", None)) else None
+        if tokenizer is not None:
+            self.log_solution_think_tokens(all_samples, tokenizer)
         for s, n in zip(all_samples, n_gen):
             GlobalMetrics.rollout_tokens_hist.add(float(n))
             cut = float(s.stop_type in (StopType.MAX_LEN, StopType.MAX_DECODE))
@@ -509,6 +512,26 @@ class PPOLikeTrainerConfig(TrainerConfig):
                 GlobalMetrics.truncated_rate_grouped.add(cut, subname=tag)
                 if s.logprobs is not None and len(s.logprobs):
                     GlobalMetrics.rollout_logprob_grouped.add(s.logprobs.float().mean(), subname=tag)
+
+    def log_solution_think_tokens(self, all_samples: list, tokenizer) -> None:
+        """Average generated tokens up to and including the first ``</think>`` token, and after it (a response
+        without the marker is all solution).  The marker is looked up as a token id, nothing is decoded; a
+        tokenizer that does not have it as one token fills neither metric.  Reference: exp/rl.py:700-740."""
+        from ..text_processing.content_parsing import THINK_END_TOKEN
+        from ..utils.metrics import GlobalMetrics
+
+        ids = tokenizer.encode(THINK_END_TOKEN, add_special_tokens=False)
+        if len(ids) != 1 or not all_samples:
+            return
+        think = solution = 0
+        for s in all_samples:
+            gen = torch.as_tensor(s.trajectory)[torch.as_tensor(s.is_gen_mask).bool()]
+            hits = (gen == ids[0]).nonzero()
+            cut = int(hits[0]) + 1 if hits.numel() else 0
+            think += cut
+            solution += gen.numel() - cut
+        GlobalMetrics.rollout_avg_think_tokens.add(think / len(all_samples))
+        GlobalMetrics.rollout_avg_solution_tokens.add(solution / len(all_samples))
 
     def log_reward_metrics(self, all_samples: list) -> None:
         from ..utils.metrics import GlobalMetrics

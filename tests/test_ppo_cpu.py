@@ -226,3 +226,27 @@ def test_quantile_summary_and_sample_tags():
     assert _sample_tags(s) == ("default", "unknown")
     s.ground_truth = {"reward_fn_type": "math", "file_path": "s3://bucket/train/gsm8k.v2.jsonl"}
     assert _sample_tags(s) == ("math", "gsm8k")
+
+
+def test_think_and_solution_token_split():
+    from steptronoss_b200.utils.metrics import GlobalMetrics, Metric
+
+    class Tok:
+        def __init__(self, ids):
+            self.ids = ids
+
+        def encode(self, text, add_special_tokens=False):
+            return self.ids
+
+    GlobalMetrics.clear()
+    GlobalMetrics.register("rollout_avg_think_tokens", Metric().mean("time"))
+    GlobalMetrics.register("rollout_avg_solution_tokens", Metric().mean("time"))
+    cfg = PPOLikeTrainerConfig()
+    a = PPOSample(trajectory=torch.tensor([5, 5, 9, 7, 60, 3, 3]), is_gen_mask=torch.tensor([0, 0, 1, 1, 1, 1, 1]))
+    b = PPOSample(trajectory=torch.tensor([5, 1, 2, 3]), is_gen_mask=torch.tensor([0, 1, 1, 1]))        # no marker
+    cfg.log_solution_think_tokens([a, b], Tok([60]))
+    out = GlobalMetrics.reduce_all()
+    assert float(out["rollout_avg_think_tokens"]) == 1.5 and float(out["rollout_avg_solution_tokens"]) == 2.5
+    cfg.log_solution_think_tokens([a, b], Tok([60, 61]))                   # the marker is not one token: nothing logged
+    assert GlobalMetrics.rollout_avg_think_tokens.values == []
+    GlobalMetrics.clear()
