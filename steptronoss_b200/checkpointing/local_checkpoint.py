@@ -199,6 +199,20 @@ class Checkpointer:
             self._thread.start()
         return path
 
+    @staticmethod
+    def size_stat(file_objects: dict) -> str:
+        """Log (rank 0) and return the tensor bytes per file of a checkpoint about to be written."""
+        from .utils import size_report
+
+        text = size_report(file_objects)
+        if text:
+            logger.info(text, at=0)
+        return text
+
+    def join_dumping_thread(self) -> None:
+        """The reference's name for ``join``."""
+        self.join()
+
     def join(self) -> None:
         if self._thread is not None:
             self._thread.join()
