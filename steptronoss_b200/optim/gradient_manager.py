@@ -459,6 +459,19 @@ class BaseGradientManager:
             for e in self.muon.entries:
                 e["master"].copy_(e["low"])
 
+    def reload_model_params(self) -> None:
+        """The reference's name for ``refresh_masters_from_params`` (optimizer/gradient_manager.py:84-87)."""
+        self.refresh_masters_from_params()
+
+    def to_device(self, device, non_blocking: bool = False) -> None:
+        """Move the optimizer state (masters, moments) to ``device``: the host while another role owns the GPU, back
+        before the next step.  ``non_blocking`` is accepted for call compatibility; the copies are ordered on the
+        current stream either way.  Reference: optimizer/gradient_manager.py:127-151."""
+        if torch.device(device).type == "cpu":
+            self.offload_state()
+        else:
+            self.reload_state()
+
     # ------------------------------------------------------------------ offload (RL role swapping)
     def offload_state(self) -> None:
         for shard in self.shards.values():

@@ -135,6 +135,13 @@ def test_optimizer_state_offload_and_zero_count_do_not_change_the_run(monkeypatc
     monkeypatch.setattr(gm, "reload_state", lambda: (moved.append("on"), real_on())[1])
     tr.train_step()
     assert moved == ["off", "on"]
+    gm.to_device("cpu")                                   # the reference's spellings take the same paths
+    gm.to_device("cuda:0")                                # any non-host device means: back to where the manager lives
+    assert moved == ["off", "on", "off", "on"]
+    shard = next(iter(gm.shards.values()))
+    shard.master.add_(1.0)
+    gm.reload_model_params()                              # masters follow the parameters again
+    assert torch.equal(shard.master, shard.bucket.param_buf[shard.lo:shard.hi].float())
     assert losses == base_losses
     for k in base_params:
         assert torch.equal(params[k], base_params[k]), k
