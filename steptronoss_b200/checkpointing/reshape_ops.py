@@ -415,7 +415,22 @@ class OnlineReshaper(ReshapeOp):
                     out[k] = weights[k]
         return out
 
+    def check_forwardable(self) -> None:
+        """Every rule names its HF side (``src``): the map can be applied to an HF state dict."""
+        missing = [sc for sc in self.scripts if not sc.src]
+        if missing:
+            raise RuntimeError(f"{len(missing)} reshape rule(s) without .src (first: dst={missing[0].dst!r}): "
+                               "the HF names are unknown, so an HF state cannot be mapped in")
+
+    def check_backwardable(self) -> None:
+        """Every rule names its native side (``dst``): parameters can be mapped out to HF names."""
+        missing = [sc for sc in self.scripts if not sc.dst]
+        if missing:
+            raise RuntimeError(f"{len(missing)} reshape rule(s) without .dst (first: src={missing[0].src!r}): "
+                               "the parameter names are unknown, so nothing can be exported")
+
     def forward(self, weights: dict) -> dict:
+        self.check_forwardable()
         native = {}
         for sc in self.scripts:
             piece = self.get_piece_by_pattern(weights, sc.src)
@@ -429,6 +444,7 @@ class OnlineReshaper(ReshapeOp):
         return native
 
     def backward(self, weights: dict) -> dict:
+        self.check_backwardable()
         hf = {}
         for sc in self.scripts:
             if "*" in sc.dst:                      # a rule over a family of parameters

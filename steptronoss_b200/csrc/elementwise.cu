@@ -397,8 +397,8 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat1
 }
 
 // ============================================================================ SwiGLU
-// in [rows][2F] = (gate | up) -> out [rows][F] = silu(gate') * up' with gate' = min(gate, limit),
-// up' = clamp(up, -limit, limit) when limit > 0.
+// in [rows][2F] = (gate | up) -> out [rows][F] = min(silu(gate), limit) * clamp(up, -limit, limit) when limit > 0
+// (the activated gate is clamped from above, after the SiLU), silu(gate) * up otherwise.
 __global__ void __launch_bounds__(256)
 swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restrict__ out, long long rows, int F,
                   long long in_stride, long long out_stride, float limit) {
@@ -415,12 +415,14 @@ swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ in, __nv_bfloat16* __restric
     unpack8(uraw, u);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      float gg = g[j], uu = u[j];
+      const float gg = g[j];
+      float uu = u[j];
+      float act = gg / (1.f + __expf(-gg));
       if (limit > 0.f) {
-        gg = fminf(gg, limit);
+        act = fminf(act, limit);
         uu = fminf(fmaxf(uu, -limit), limit);
       }
-      o[j] = gg / (1.f + __expf(-gg)) * uu;
+      o[j] = act * uu;
     }
     *reinterpret_cast<uint4*>(out + r * out_stride + v * 8) = pack8(o);
   }
@@ -445,18 +447,20 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ in, const __nv_bfloat16* __r
     unpack8(draw, d);
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      float gg = g[j], uu = u[j];
-      bool g_live = true, u_live = true;
-      if (limit > 0.f) {
-        g_live = gg <= limit;
-        u_live = (uu >= -limit) && (uu <= limit);
-        gg = fminf(gg, limit);
-        uu = fminf(fmaxf(uu, -limit), limit);
-      }
+      const float gg = g[j];
+      float uu = u[j];
       const float sig = 1.f / (1.f + __expf(-gg));
       const float silu = gg * sig;
+      float act = silu;
+      bool g_live = true, u_live = true;
+      if (limit > 0.f) {                       // a clamp passes the gradient where its input lies inside the bounds
+        g_live = silu <= limit;
+        u_live = (uu >= -limit) && (uu <= limit);
+        act = fminf(silu, limit);
+        uu = fminf(fmaxf(uu, -limit), limit);
+      }
       dg[j] = g_live ? d[j] * uu * (sig + silu * (1.f - sig)) : 0.f;
-      du[j] = u_live ? d[j] * silu : 0.f;
+      du[j] = u_live ? d[j] * act : 0.f;
     }
     *reinterpret_cast<uint4*>(din + r * din_stride + v * 8) = pack8(dg);
     *reinterpret_cast<uint4*>(din + r * din_stride + F + v * 8) = pack8(du);

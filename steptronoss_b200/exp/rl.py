@@ -133,7 +133,7 @@ class PPOCheckpointCfg(CheckpointConfig):
 class PPOMetricConfig(MetricConfig):
     def __init__(self):
         super().__init__()
-        from ..utils.metrics import GroupMetric, HistogramMetric, Metric, PercentageMetric, TextMetric
+        from ..utils.metrics import AvgMetric, GroupMetric, HistogramMetric, Metric, PercentageMetric, TextMetric
 
         self.reward_mean = Metric().mean("time").mean("dp")
         self.reward_max = Metric().max("time").max("dp")
@@ -160,10 +160,11 @@ class PPOMetricConfig(MetricConfig):
         self.rollout_logprob = Metric().mean("time")
         self.rollout_logprob_correct = Metric().mean("time")
         self.rollout_logprob_incorrect = Metric().mean("time")
-        self.repeatness_score = Metric().mean("time").mean("world")
-        self.repeatness_rate = Metric().mean("time").mean("world")
-        self.repeatness_rate_correct = Metric().mean("time").mean("world")
-        self.repeatness_rate_incorrect = Metric().mean("time").mean("world")
+        # per-sample means pooled over all ranks: ranks score different numbers of responses
+        self.repeatness_score = AvgMetric().mean("world")
+        self.repeatness_rate = AvgMetric().mean("world")
+        self.repeatness_rate_correct = AvgMetric().mean("world")
+        self.repeatness_rate_incorrect = AvgMetric().mean("world")
         self.actor_grad_norm = Metric().mean("time")
         self.critic_grad_norm = Metric().mean("time")
         self.kl_with_ref_dist = Metric().mean("time").mean("dp")

@@ -23,6 +23,13 @@ class FeedForwardConfig(Config):
     swiglu_recompute_silu_out_proj: bool = False
     swiglu_limit: float | list | None = None
 
+    def activation(self, x, swiglu_limit=None):
+        """SwiGLU on ``[gate | up]`` halves of the last dimension, optionally clamped (gate above, up on both sides).
+        The PyTorch statement of what the fused kernel computes (reference: model/common/feed_forward.py:20-26)."""
+        from ...ops.fused import swiglu_reference
+
+        return swiglu_reference(x, float(swiglu_limit) if swiglu_limit else 0.0)
+
     def build_model(self, layer_id: int = 0):
         return FeedForward(self, layer_id)
 

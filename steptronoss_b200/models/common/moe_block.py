@@ -153,6 +153,23 @@ class MoEBlock(nn.Module):
         self.micro_batch_count = 0
         self._dispatcher = None
 
+    def maintain_float32_router_balance_bias(self) -> None:
+        """The selection bias moves by ``router_bias_update_rate`` (1e-3) per step: in bf16 such steps vanish next to a
+        bias of order one.  Whatever cast the module went through, the buffer is put back to fp32
+        (reference: model/common/moe_block.py:423-436)."""
+        b = self.router_balance_bias
+        if b is not None and b.dtype != torch.float32:
+            self.router_balance_bias.data = b.data.float()
+
+    def _apply(self, fn, recurse=True):
+        out = super()._apply(fn, recurse)
+        self.maintain_float32_router_balance_bias()
+        return out
+
+    def _load_from_state_dict(self, *args, **kwargs):
+        self.maintain_float32_router_balance_bias()
+        return super()._load_from_state_dict(*args, **kwargs)
+
     # ------------------------------------------------------------------ router
     def forward_router(self, logits):
         cfg = self.cfg

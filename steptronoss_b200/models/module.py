@@ -67,7 +67,20 @@ class MegatronModule(nn.Module):
             return self.forward_tail(hidden, **data)
         return hidden
 
+    def abstract_forward(self, **data):
+        """The whole model on one stage: head, chunk and tail in a row (what the pipeline split is a split of)."""
+        if self.pp_size != 1:
+            raise AssertionError("abstract_forward describes the unsplit model; this one is split over pipeline stages")
+        return self.forward_tail(self.forward_chunk(self.forward_head(**data), **data), **data)
+
     # ---------------------------------------------------------------- weights
+    def init_model_weight(self, seed: int = 0, std: float = 0.02) -> None:
+        """``init_weights`` under the reference's name (model/module.py:142-159): afterwards every parameter carries
+        ``has_initialized = True``, which the checkpoint loaders read to tell loaded from merely initialised weights."""
+        self.init_weights(seed, std)
+        for p in self.parameters():
+            p.has_initialized = True
+
     def init_weights(self, seed: int = 0, std: float = 0.02) -> None:
         """Seed-deterministic N(0, std) init, independent of the parallel layout; norm weights 1 (or 0)."""
         for name, p in self.named_parameters():

@@ -296,10 +296,11 @@ def qknorm_rope(qkv, q_weight, k_weight, cos, sin, pos, hq, hkv, head_dim, rot_d
 def swiglu_reference(x, limit: float = 0.0):
     F = x.shape[-1] // 2
     g, u = x[..., :F].float(), x[..., F:].float()
-    if limit and limit > 0:
-        g = g.clamp(max=limit)
+    act = torch.nn.functional.silu(g)
+    if limit and limit > 0:      # the activated gate is clamped from above, the up branch on both sides
+        act = act.clamp(max=limit)                       # (reference: model/common/feed_forward.py:20-26)
         u = u.clamp(min=-limit, max=limit)
-    return (torch.nn.functional.silu(g) * u).to(x.dtype)
+    return (act * u).to(x.dtype)
 
 
 class _SwiGLUFn(torch.autograd.Function):

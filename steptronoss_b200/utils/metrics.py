@@ -203,12 +203,39 @@ class GradNormMetric(GroupMetric):
 
 
 class AvgMetric(Metric):
-    """Mean over the values recorded in the interval, then the chain over groups."""
+    """Statistic of the pooled samples: every value recorded in the interval on every rank of the group goes into one
+    list, and ``mean`` / ``max`` / ``min`` / ``std`` is taken over that list - a true per-sample statistic, where a
+    plain ``Metric`` would average per-rank means whatever the number of samples behind each.  One reduction
+    (``AvgMetric().mean("world")``; the last one chained wins), over ``dp`` or ``world``; values are python numbers.
+    Reference: utils/metrics.py:268-336."""
+
+    def std(self, axis: str):
+        return self._link("std", axis)
+
+    def add(self, value, subname=None, iop=None) -> None:  # type: ignore[override]
+        if not self.enabled:
+            return
+        if callable(iop):
+            value = iop(value)
+        self.values.append(float(value))
 
     def reduce(self):
-        if not any(ax == "time" for _, ax in self.chain):
-            self.chain = [("mean", "time")] + self.chain
-        return super().reduce()
+        pairs = [(op, ax) for op, ax in self.chain if ax != "time"]
+        op, axis = pairs[-1] if pairs else ("mean", "world")
+        if op not in ("mean", "max", "min", "std"):
+            raise ValueError(f"AvgMetric reduces with mean, max, min or std, not {op!r}")
+        pooled = list(self.values)
+        group, size = _group_for(axis)
+        if size > 1 and dist.is_initialized():
+            from .dist_utils import all_gather_object
+
+            pooled = [v for part in all_gather_object(pooled, group=group) for v in part]
+        if not pooled:
+            return None
+        data = torch.tensor(pooled, dtype=torch.float32)
+        if op == "std":
+            return data.std() if data.numel() > 1 else torch.zeros(())
+        return {"mean": data.mean, "max": data.max, "min": data.min}[op]()
 
 
 class PercentageMetric(Metric):

@@ -3,6 +3,7 @@ single-process block output and gradients."""
 import os
 import socket
 
+import pytest
 import torch
 import torch.multiprocessing as mp
 
@@ -158,9 +159,16 @@ def test_zero_centred_norm_weight_and_clamped_swiglu():
 
     h = torch.tensor([[10.0, -10.0, 1.0, 20.0, -20.0, 2.0]])                     # gate | up
     out = swiglu_reference(h, limit=7.0)
-    g, u = torch.tensor([7.0, -10.0, 1.0]), torch.tensor([7.0, -7.0, 2.0])       # gate capped above, up on both sides
-    assert torch.allclose(out, torch.nn.functional.silu(g) * u)
+    # the activated gate is capped above (silu(10) = 9.9995 -> 7), the up branch on both sides
+    act = torch.nn.functional.silu(torch.tensor([10.0, -10.0, 1.0])).clamp(max=7.0)
+    assert float(act[0]) == 7.0
+    assert torch.allclose(out, act * torch.tensor([7.0, -7.0, 2.0]))
     assert not torch.allclose(out, swiglu_reference(h))
+    # a gate of exactly the limit is not cut: silu(7) < 7
+    assert float(swiglu_reference(torch.tensor([[7.0, 1.0]]), limit=7.0)) == pytest.approx(7.0 / (1 + 2.718281828 ** -7), rel=1e-6)
+    from steptronoss_b200.models.common.feed_forward import FeedForwardConfig
+
+    assert torch.equal(FeedForwardConfig().activation(h, swiglu_limit=7.0), out)
 
 
 def test_detailed_router_metrics_are_filled_when_asked_for():

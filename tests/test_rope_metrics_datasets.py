@@ -220,3 +220,35 @@ def test_outlier_metric_dumps_the_data_of_values_above_the_recent_mean(tmp_path)
         m.add({"value": 1})
     assert isinstance(dummy_metric, DummyMetric) and GlobalMetrics.some_metric_nobody_registered is dummy_metric
     dummy_metric.add(1, subname="x")
+
+
+def _pooled_worker(rank, world):
+    from steptronoss_b200.exp.base_exp import ParallelConfig
+    from steptronoss_b200.parallel.state import PM
+    from steptronoss_b200.utils.metrics import AvgMetric, Metric
+
+    PM.set_mesh(ParallelConfig())                                        # two data-parallel ranks
+    pooled, plain = AvgMetric().mean("world"), Metric().mean("time").mean("world")
+    spread, top = AvgMetric().std("world"), AvgMetric().max("dp")
+    for v in ([1.0] if rank == 0 else [3.0, 3.0, 3.0]):                  # one sample here, three there
+        for m in (pooled, plain, spread, top):
+            m.add(v)
+    return float(pooled.reduce()), float(plain.reduce()), float(spread.reduce()), float(top.reduce())
+
+
+def test_avg_metric_pools_samples_over_ranks():
+    from steptronoss_b200.utils.metrics import AvgMetric
+    from tests.dist_helpers import call_on_ranks
+
+    got = call_on_ranks(_pooled_worker, 2)
+    for rank in (0, 1):
+        pooled, plain, spread, top = got[rank]
+        assert pooled == 2.5 and plain == 2.0                               # per-sample mean against mean of means
+        assert spread == pytest.approx(1.0) and top == 3.0
+    one = AvgMetric().std("world")
+    one.add(2)
+    assert float(one.reduce()) == 0.0 and AvgMetric().mean("world").reduce() is None
+    with pytest.raises(ValueError):
+        m = AvgMetric().sum("world")
+        m.add(1.0)
+        m.reduce()

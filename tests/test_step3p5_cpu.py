@@ -94,3 +94,22 @@ def test_step3p5_hf_mapping_round_trip():
         if k in back:
             assert torch.equal(back[k], v), k
     assert set(back) >= {k for k in native if "rope" not in k and "tokens_per_expert" not in k}
+
+
+def test_selection_bias_stays_fp32_through_casts_and_loads():
+    exp = _make()
+    exp.seed = 0
+    tr = exp.trainer_cfg.get_trainer_cls()(exp=exp)
+    tr.before_train()
+    model = getattr(tr.models[0], "module", tr.models[0])
+    moe = model.layers["1"].feed_forward.moe
+    assert moe.router_balance_bias.dtype == torch.float32
+    model.to(torch.bfloat16)
+    assert moe.gate.weight.dtype == torch.bfloat16 and moe.router_balance_bias.dtype == torch.float32
+    sd = {k: v.clone() for k, v in moe.state_dict().items()}
+    sd["router_balance_bias"] = torch.full_like(sd["router_balance_bias"], 1.0 + 1e-3).to(torch.bfloat16)
+    moe.load_state_dict(sd)
+    assert moe.router_balance_bias.dtype == torch.float32
+    assert model.pp_size == 1 and callable(model.abstract_forward)
+    model.init_model_weight(seed=3)
+    assert all(getattr(p, "has_initialized", False) for p in model.parameters())
