@@ -256,7 +256,9 @@ class MoEBlock(nn.Module):
         else:
             out = fn(x2, ids, weights)
         if self.cfg.moe_aux_loss_coef:
-            aux = aux * (self.cfg.moe_aux_loss_coef / PM.size_of("TP"))
+            # the reference divides by TP on the expert-parallel path and by ETP (= 1) otherwise
+            # (model/common/moe_block.py:394,407); kept, so that a coefficient tuned there means the same here
+            aux = aux * (self.cfg.moe_aux_loss_coef / (PM.size_of("TP") if ep else max(PM.size_of("ETP"), 1)))
             out = bind_aux_loss(out, aux)
             GlobalMetrics.moe_aux_loss.add(aux.detach(), subname=f"layer{self.moe_layer_id}")
         if self.cfg.routed_scaling_factor != 1.0:
