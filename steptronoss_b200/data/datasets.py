@@ -57,7 +57,7 @@ class StepChatJsonDataset(Dataset):
 
 def compile_dataset(dataset: Dataset, save_path: str, n_shards: int = 1, cfg: dict | None = None) -> dict:
     os.makedirs(save_path, exist_ok=True)
-    writers = [IndexedBinWriter(os.path.join(save_path, f"shard_{s:05d}"), cfg) for s in range(n_shards)]
+    writers = [IndexedBinWriter(os.path.join(save_path, f"shard_{s:05d}"), cfg=cfg) for s in range(n_shards)]
     meta = []
     for i in range(len(dataset)):
         sample = dataset[i]

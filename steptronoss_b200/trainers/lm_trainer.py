@@ -206,6 +206,12 @@ class DecoderPretrainTrainer(BaseTrainer):
         metrics = GlobalMetrics.reduce_all()
         skipped = self.grad_manager.skipped_steps() if hasattr(self.grad_manager, "skipped_steps") else 0
         metrics["N-skipped"] = skipped
+        # run-level counters next to the per-interval metrics, as the reference writes them (core/trainers/
+        # lm_trainer.py:292-298)
+        metrics["batch-size"] = tc.global_batch_size
+        metrics["world-size"] = PM.world_size
+        metrics["N-samples"] = self.consumed_samples
+        metrics["N-tokens"] = self.consumed_samples * tc.global_seq_length
         tokens = tc.global_batch_size * tc.global_seq_length
         tps_card = tokens / dt / max(PM.world_size, 1)
         logs = tc.make_logs(self.iteration, metrics, self.writer)

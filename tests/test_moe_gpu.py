@@ -32,8 +32,11 @@ def test_routed_grouped_ffn_gpu_matches_expert_loop(T, E, K, H, F):
 
 
 def test_grouped_gemm_entry_runs_the_grouped_kernel_for_aligned_groups_and_the_loop_otherwise():
-    from steptronoss_b200.ops import gemm as gemm_ops
+    import importlib
+
     from steptronoss_b200.ops.moe import grouped_gemm
+
+    gemm_ops = importlib.import_module("steptronoss_b200.ops.gemm")      # the package exports the function by this name
 
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(0)

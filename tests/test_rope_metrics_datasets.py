@@ -133,7 +133,7 @@ def test_indexed_bin_compiled_and_chat_datasets(tmp_path):
     from steptronoss_b200.data.datasets import CompiledDataset, StepChatJsonDataset, compile_dataset
     from steptronoss_b200.data.indexed_bin import IndexedBinReader, IndexedBinWriter
 
-    with IndexedBinWriter(str(tmp_path / "bin"), {"note": "x"}) as w:
+    with IndexedBinWriter(str(tmp_path / "bin"), cfg={"note": "x"}) as w:
         ids = [w.append({"i": i, "blob": np.arange(i)}) for i in range(5)]
     assert ids == list(range(5)) and os.path.exists(tmp_path / "bin" / ".success")
     r = IndexedBinReader(str(tmp_path / "bin"))
