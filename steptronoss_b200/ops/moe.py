@@ -376,12 +376,13 @@ def grouped_gemm(mat_a_flat, mat_b, batch_sizes, trans_b: bool = False):
     consecutive groups of ``batch_sizes[g]`` rows, ``mat_b [G, N, K]`` (``trans_b``) or ``[G, K, N]``.
 
     The sizes are read on the host, as the reference's back-ends do.  Groups whose sizes are all multiples of 128
-    with ``trans_b`` and bf16 operands on the GPU run as one grouped tcgen05 GEMM (differentiable, weight gradient
+    with ``trans_b``, an output width that is a multiple of 128 and bf16 operands on the GPU run as one grouped tcgen05 GEMM (differentiable, weight gradient
     by the grouped reduce kernel); anything else runs one product per group.  The model path does not come through
     here: ``routed_grouped_ffn`` keeps its offsets on the device."""
     sizes = [int(b) for b in batch_sizes.tolist()]
     if (trans_b and sizes and _native_rows(mat_a_flat) and mat_b.dtype == torch.bfloat16 and mat_b.is_contiguous()
-            and all(n % SEGMENT_ALIGNMENT == 0 for n in sizes) and mat_a_flat.shape[1] % 8 == 0):
+            and all(n % SEGMENT_ALIGNMENT == 0 for n in sizes) and mat_a_flat.shape[1] % 8 == 0
+            and mat_b.shape[1] % 128 == 0):        # an output tile must not run into the next group's weights
         offsets = torch.tensor([0] + list(itertools.accumulate(sizes)), dtype=torch.int32, device=mat_a_flat.device)
         return grouped_linear(mat_a_flat.contiguous(), mat_b, offsets)
     return _grouped_gemm_loop(mat_a_flat, mat_b, batch_sizes, trans_b)

@@ -234,6 +234,28 @@ def test_blockchain_write_copy_read_resume(tmp_path):
     rd3.load_state_dict(st)
     assert rd3.get()["i"] == 6
     rd.close()
+    # peek / skip, the whole chain at once, a moved directory
+    walk = Chain(str(dst), reusable=True)
+    assert walk.get_nostep()["i"] == 0 and walk.get_nostep()["i"] == 0 and walk.next() and walk.get()["i"] == 1
+    assert walk.extend() == 5                                   # root + 3 blocks of the first writer + 1 appended
+    assert [(n, ok) for _, n, ok in walk.validate()] == [(0, True), (4, True), (4, True), (2, True), (1, True)]
+    assert all(b.loaded for b in walk.blocks[:2])               # reusable: what was read stays in memory
+    quick = Chain(str(dst))
+    assert quick.fastload() == 4 and not quick.verify and [quick.get()["i"] for _ in range(11)] == list(range(11))
+    moved = tmp_path / "c"
+    shutil.move(str(dst), str(moved))
+    walk.root = str(moved)
+    assert walk.get()["i"] == 2 and str(moved) in repr(walk) and "in-block id" in repr(walk)
+    other = Chain(str(tmp_path / "elsewhere"))
+    other.load_state_dict(walk.state_dict())                    # a full state carries root and blocks along
+    assert other.root == str(moved) and other.get()["i"] == 3
+    blk = walk.blocks[2]
+    blk.load()
+    blk.data[0] = {"i": -1}
+    blk.save()                                                  # a block changed behind the chain's back
+    assert [ok for _, _, ok in Chain(str(moved)).validate()] == [True, True, False, True, True]
+    empty = Chain(str(tmp_path / "nothing"))
+    assert empty.get() is None and empty.get_nostep() is None and not empty.next()
 
 
 def test_samplers_cover_epochs_resume_and_skip_without_building_items():

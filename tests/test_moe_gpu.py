@@ -40,7 +40,11 @@ def test_grouped_gemm_entry_runs_the_grouped_kernel_for_aligned_groups_and_the_l
 
     dev = "cuda"
     g = torch.Generator(device=dev).manual_seed(0)
-    w = (torch.randn(4, 192, 256, device=dev, generator=g) * 0.05).to(torch.bfloat16).requires_grad_()
+    w = (torch.randn(4, 256, 256, device=dev, generator=g) * 0.05).to(torch.bfloat16).requires_grad_()
+    narrow = (torch.randn(4, 192, 256, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    before = gemm_ops.launch_count()
+    assert grouped_gemm(torch.zeros(128, 256, device=dev, dtype=torch.bfloat16), narrow, torch.tensor([128, 0, 0, 0]),
+                        trans_b=True).shape == (128, 192) and gemm_ops.launch_count() == before   # 192 wide: the loop
     for sizes, launches in (([256, 0, 128, 384], 1), ([100, 28, 0, 7], 0)):
         a = torch.randn(sum(sizes), 256, device=dev, generator=g).to(torch.bfloat16).requires_grad_()
         before = gemm_ops.launch_count()
