@@ -331,3 +331,104 @@ def load(path: str, mode: str | None = None, **kwargs):
         with open(path, encoding="utf-8") as f:
             return f.read()
     raise ValueError(f"cannot tell how to load {path!r}: pass mode=json|jsonl|hjson|torch|pickle|yaml|numpy|safetensors|text")
+
+
+# ---- files, modules, pickles ---------------------------------------------------------------------------------------
+def check_and_link(src: str, dst: str) -> None:
+    """Symlink ``dst -> src``; an existing link to the same target is fine, anything else in the way raises."""
+    import os
+
+    src, dst = src.rstrip("/"), dst.rstrip("/")
+    try:
+        os.symlink(src, dst)
+    except OSError:
+        if not os.path.islink(dst) or os.readlink(dst) != src:
+            raise
+
+
+def try_save(*args, **kwargs):
+    """``torch.save`` that logs a failure instead of raising (a side dump must not end a job)."""
+    from .logger import logger
+
+    try:
+        return torch.save(*args, **kwargs)
+    except Exception as e:
+        logger.error(f"torch.save failed: {e}")
+        return None
+
+
+def get_object_from_file(file: str, name: str = "Exp"):
+    """``name`` from the python file ``file`` given as a path relative to an import root (``playground/x/y.py`` ->
+    module ``playground.x.y``), e.g. the experiment class of an experiment file."""
+    import os
+
+    stem, _ = os.path.splitext(file)
+    module = ".".join(p for p in stem.replace(os.sep, "/").split("/") if p not in ("", "."))
+    return getattr(importlib.import_module(module), name)
+
+
+def hack_pickle_load() -> None:
+    """Let ``pickle.load`` get past classes that cannot be imported any more (an old dump naming a module that
+    moved): such objects come back as inert placeholders.  Process-wide; for inspection tools, not for training."""
+    import pickle
+
+    class LoadFailure:
+        def __init__(self, *a, **k):
+            pass
+
+        def __setstate__(self, state):
+            self.state = state
+
+    pickle.Unpickler = pickle._Unpickler                     # the pure-python unpickler can be patched
+    if getattr(pickle._Unpickler.find_class, "_tolerant", False):
+        return
+    find = pickle._Unpickler.find_class
+
+    def find_class(self, module, name):
+        try:
+            return find(self, module, name)
+        except Exception:
+            print(f"Cannot Load {module}.{name}: replaced by a placeholder.")
+            return LoadFailure
+
+    find_class._tolerant = True
+    pickle._Unpickler.find_class = find_class
+
+
+def deprecated(message: str = "This function is deprecated."):
+    """Decorator: warn (once per function) when a deprecated function is called."""
+
+    def decorate(fn):
+        warned = []
+
+        @functools.wraps(fn)
+        def wrapper(*a, **k):
+            if not warned:
+                from .logger import logger
+
+                logger.warning(f"{fn.__qualname__}: {message}")
+                warned.append(True)
+            return fn(*a, **k)
+
+        return wrapper
+
+    return decorate
+
+
+class GroupedProgressBar:
+    """One progress bar over everything plus one per named group (``totals``: name -> count)."""
+
+    def __init__(self, totals: dict):
+        from tqdm import tqdm
+
+        self.total_bar = tqdm(total=sum(totals.values()), desc="All Groups", position=0, dynamic_ncols=True)
+        self.group_bars = {name: tqdm(total=n, desc=name, position=i, dynamic_ncols=True)
+                           for i, (name, n) in enumerate(totals.items(), start=1)}
+
+    def update(self, name: str, n: int = 1) -> None:
+        self.total_bar.update(n)
+        self.group_bars[name].update(n)
+
+    def close(self) -> None:
+        for bar in [self.total_bar, *self.group_bars.values()]:
+            bar.close()

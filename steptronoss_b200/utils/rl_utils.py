@@ -110,7 +110,24 @@ def compute_gae(values: torch.Tensor, rewards: torch.Tensor, lambd: float = 0.95
     return adv, adv + v
 
 
-compute_gae_opt = compute_gae
+def gae_coefficients(T: int, lambd: float = 0.95, gamma: float = 1.0, device=None) -> torch.Tensor:
+    """``C[s, t] = (gamma * lambd) ** (s - t)`` for ``s >= t``, else 0: ``advantages = delta @ C``."""
+    idx = torch.arange(T, device=device)
+    power = (idx[:, None] - idx[None, :]).float()
+    return torch.where(power >= 0, torch.tensor(float(gamma * lambd), device=device) ** power.clamp_min(0), torch.zeros((), device=device))
+
+
+def compute_gae_opt(values, rewards, lambd: float = 0.95, gamma: float = 1.0, gae_coeff: torch.Tensor | None = None):
+    """``compute_gae`` with the reference's signature (utils/rl_utils.py:195-210).  With a precomputed coefficient
+    matrix (``gae_coefficients``; its top-left ``T x T`` corner is used) the recursion becomes one product, which
+    is how batches of equal-length rows are best done; without it this is ``compute_gae`` (one kernel on CUDA)."""
+    if gae_coeff is None:
+        return compute_gae(values, rewards, lambd, gamma)
+    v, r = values.float(), rewards.float()
+    T = v.shape[-1]
+    nxt = torch.cat([v[..., 1:], torch.zeros_like(v[..., :1])], dim=-1)
+    adv = (r + gamma * nxt - v) @ gae_coeff[:T, :T].to(device=v.device, dtype=v.dtype)
+    return adv, adv + v
 
 
 class RaggedPPOSampleDumper:

@@ -2,6 +2,7 @@
 import os
 import random
 
+import pytest
 import torch
 import torch.multiprocessing as mp
 
@@ -174,3 +175,59 @@ def test_object_collectives_on_two_ranks():
     assert res[0]["a2a_tensors"] == [((1, 1), 0.0), ((2, 1), 10.0)] and res[1]["a2a_tensors"] == [((1, 2), 1.0), ((2, 2), 11.0)]
     assert res[1]["recv_obj"] == ([1, 2], [1.0, 1.0])
     assert res[1]["recv_packed"] == ((3, 1), [0, 1, 2], None)
+
+
+def test_links_modules_placeholders_and_progress(tmp_path, capsys):
+    import io
+    import os
+    import pickle
+
+    from steptronoss_b200.utils import general as g
+
+    (tmp_path / "data").mkdir()
+    g.check_and_link(str(tmp_path / "data") + "/", str(tmp_path / "link"))
+    g.check_and_link(str(tmp_path / "data"), str(tmp_path / "link"))            # same target again: fine
+    assert os.readlink(tmp_path / "link") == str(tmp_path / "data")
+    with pytest.raises(OSError):
+        g.check_and_link(str(tmp_path / "other"), str(tmp_path / "link"))
+    assert g.try_save({"a": 1}, str(tmp_path / "no" / "such" / "dir" / "x.pt")) is None       # logged, not raised
+    g.try_save({"a": torch.ones(2)}, str(tmp_path / "x.pt"))
+    assert torch.load(tmp_path / "x.pt")["a"].sum() == 2
+    assert g.get_object_from_file("steptronoss_b200/utils/general.py", "safediv") is g.safediv
+
+    calls = []
+
+    @g.deprecated("use new_thing")
+    def old_thing(x):
+        calls.append(x)
+        return x + 1
+
+    assert old_thing(1) == 2 and old_thing(2) == 3 and calls == [1, 2]
+
+    blob = pickle.dumps(g.safediv).replace(b"safediv", b"gone_fn")              # a dump that names something removed
+    saved = (pickle.Unpickler, pickle._Unpickler.find_class)
+    try:
+        g.hack_pickle_load()
+        g.hack_pickle_load()                                                    # patching twice changes nothing
+        assert pickle._Unpickler(io.BytesIO(blob)).load().__name__ == "LoadFailure"
+        assert "Cannot Load" in capsys.readouterr().out
+    finally:
+        pickle.Unpickler, pickle._Unpickler.find_class = saved                  # the patch is process-wide: undo it
+
+    bars = g.GroupedProgressBar({"a": 2, "b": 1})
+    bars.update("a")
+    bars.update("b")
+    assert bars.total_bar.n == 2 and bars.group_bars["a"].n == 1
+    bars.close()
+
+
+def test_gae_by_coefficient_matrix_matches_the_recursion():
+    from steptronoss_b200.utils.rl_utils import compute_gae, compute_gae_opt, gae_coefficients
+
+    torch.manual_seed(0)
+    v, r = torch.randn(3, 9), torch.randn(3, 9)
+    want = compute_gae(v, r, 0.9, 0.99)
+    got = compute_gae_opt(v, r, 0.9, 0.99, gae_coeff=gae_coefficients(16, 0.9, 0.99))
+    assert torch.allclose(got[0], want[0], atol=1e-5) and torch.allclose(got[1], want[1], atol=1e-5)
+    same = compute_gae_opt(v, r, 0.9, 0.99)
+    assert torch.equal(same[0], want[0])
