@@ -37,6 +37,40 @@ class WarmupShape:
         return min(max(v, self.clip_min), self.clip_max)
 
 
+class ScaleFunction:
+    """Base of user-written schedules: ``__call__(progress) -> scale`` with the horizon in ``self.n``."""
+
+    def __init__(self, n: float):
+        self.n = n
+
+    def __call__(self, x: float) -> float:
+        raise NotImplementedError
+
+
+class ScaleFnWithWarmUpAndClip(WarmupShape, ScaleFunction):
+    """A schedule of one's own with the stock warm-up, floor and clipping: override ``get(x)``, the shape after
+    warm-up as a function of the progress since warm-up ended (``self.n`` is the horizon without the warm-up, as in
+    the reference: optimizer/hparam_scheduler.py:29-62)::
+
+        class Quadratic(ScaleFnWithWarmUpAndClip):
+            def get(self, x):
+                return (1 - min(x, self.n) / self.n) ** 2
+    """
+
+    def __init__(self, n: float = 0, warmup: float = 0, min_scale: float = 0.0, clip_max: float = 1.0, clip_min: float = 0.0):
+        WarmupShape.__init__(self, "constant", n, warmup, min_scale, clip_max, clip_min)
+        self.n = self.span
+
+    def get(self, x: float) -> float:
+        return 1.0
+
+    def __call__(self, x: float) -> float:
+        if self.warmup and x <= self.warmup:
+            return x / self.warmup
+        v = (1.0 - self.min_scale) * self.get(x - self.warmup) + self.min_scale
+        return min(max(v, self.clip_min), self.clip_max)
+
+
 def FuncConstant(n=0, warmup=0, min_scale=0, **kw):  # noqa: N802
     return WarmupShape("constant", n, warmup, min_scale, **kw)
 

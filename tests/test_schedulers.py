@@ -74,3 +74,22 @@ def test_scheduler_writes_groups_and_restores():
     assert r.cur_lr == 0.0                                            # the second warm-up starts from re_warmup_min
     with pytest.raises(AssertionError):
         Scheduler(None, 1.0, 0.0, 1.0, lambda x: 1.0)
+
+
+def test_custom_shape_by_overriding_get():
+    from steptronoss_b200.optim.hparam_scheduler import FuncLinear, ScaleFnWithWarmUpAndClip, ScaleFunction
+
+    class Quadratic(ScaleFnWithWarmUpAndClip):
+        def get(self, x):
+            return (1 - min(x, self.n) / self.n) ** 2
+
+    f = Quadratic(n=110, warmup=10, min_scale=0.1, clip_min=0.15)
+    assert isinstance(f, ScaleFunction) and f.n == 100
+    assert f(5) == 0.5 and f(10) == 1.0                                   # linear warm-up, then the shape from its start
+    assert f(60) == pytest.approx(0.9 * 0.25 + 0.1) and f(110) == 0.15 and f(500) == 0.15     # floor, then the clip
+    base = ScaleFnWithWarmUpAndClip(n=20, warmup=0)
+    assert base(7) == 1.0
+    lin, mine = FuncLinear(n=50, warmup=5, min_scale=0.2), type("L", (ScaleFnWithWarmUpAndClip,), {"get": lambda s, x: 1 - x / s.n})(50, 5, 0.2)
+    assert all(lin(x) == pytest.approx(mine(x)) for x in (0, 3, 5, 20, 50))
+    with pytest.raises(NotImplementedError):
+        ScaleFunction(3)(1)
