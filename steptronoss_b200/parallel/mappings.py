@@ -111,3 +111,23 @@ gather_from_sequence_parallel_region_no_reduce = _make(_gather_first, _split_fir
 reduce_scatter_to_sequence_parallel_region = _make(_reduce_scatter_first, _gather_first,
                                                    "reduce-scatter first dim forward, all-gather backward")
 slice_sequence_parallel_region = _make(_split_first, _gather_first, "take this rank's slice of the first dim")
+slice_to_sequence_parallel_region = slice_sequence_parallel_region      # the reference's spelling
+
+
+def split_along_first_dim_with_padding(input_, contiguous: bool = True, group: str = "TP"):
+    """This rank's share of dimension 0 when its length does not divide by the group: every rank takes
+    ``ceil(len / world)`` rows and the last one fills up with uninitialised rows.  Returns ``(share, padding rows)``;
+    a group of one returns the input as it is (no tuple), as the reference does
+    (core/tensor_parallel/mappings.py:127-156)."""
+    world, rank = _size(group), PM.rank_in(group) if _size(group) > 1 else 0
+    if world == 1:
+        return input_
+    n = input_.shape[0]
+    if n <= (world - 1) ** 2:
+        raise AssertionError(f"{n} rows are too few to pad for {world} ranks: an earlier rank would run past the end")
+    share = -(-n // world)
+    pad = share * world - n
+    out = input_[rank * share:(rank + 1) * share]
+    if rank == world - 1 and pad:
+        out = torch.cat([out, input_.new_empty((pad, *input_.shape[1:]))])
+    return (out.contiguous() if contiguous else out), pad

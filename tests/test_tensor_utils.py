@@ -83,3 +83,36 @@ def test_flat_shards_gather_over_two_ranks():
     assert got[0]["piece"] == list(range(6)) and got[1]["piece"] == list(range(6, 12))
     assert got[0]["gathered"] == got[1]["gathered"] == [float(i) for i in range(12)]
     assert got[0]["counts"] and not got[1]["counts"]                      # a replicated parameter counts once
+
+
+def _padded_split_worker(rank, world):
+    from steptronoss_b200.parallel import mappings
+    from steptronoss_b200.parallel.state import PM
+
+    pc = ParallelConfig()
+    pc.tensor_model_parallel_size = 2
+    PM.set_mesh(pc)
+    x = torch.arange(14.0).view(7, 2)
+    share, pad = mappings.split_along_first_dim_with_padding(x)
+    even, pad0 = mappings.split_along_first_dim_with_padding(x[:6])
+    sliced = mappings.slice_to_sequence_parallel_region(x[:6].clone().requires_grad_())
+    try:
+        mappings.split_along_first_dim_with_padding(x[:1])
+        few = False
+    except AssertionError:
+        few = True
+    return tuple(share.shape), pad, share[:3].tolist(), tuple(even.shape), pad0, sliced.tolist(), few
+
+
+def test_first_dim_split_with_padding_over_two_ranks():
+    from steptronoss_b200.parallel import mappings
+    from tests.dist_helpers import call_on_ranks
+
+    x = torch.zeros(5, 2)
+    assert mappings.split_along_first_dim_with_padding(x) is x                 # a group of one: untouched
+    got = call_on_ranks(_padded_split_worker, 2)
+    assert got[0][:3] == ((4, 2), 1, [[0.0, 1.0], [2.0, 3.0], [4.0, 5.0]])
+    assert got[1][:3] == ((4, 2), 1, [[8.0, 9.0], [10.0, 11.0], [12.0, 13.0]])  # three real rows and one of padding
+    assert got[0][3:5] == got[1][3:5] == ((3, 2), 0)
+    assert got[0][5] == [[0.0, 1.0], [2.0, 3.0], [4.0, 5.0]] and got[1][5] == [[6.0, 7.0], [8.0, 9.0], [10.0, 11.0]]
+    assert got[0][6] and got[1][6]
