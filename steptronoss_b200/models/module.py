@@ -166,3 +166,58 @@ def unwrap_model(m):
     while isinstance(m, Float16Module):
         m = m.module
     return m
+
+
+def init_weight_callback(cls, init_method: str = "init_model_weight"):
+    """Class decorator: after ``cls(...)`` has built an instance of exactly ``cls`` (not of a subclass, whose own
+    decoration does it), call ``init_method()`` on every sub-module that has one, children before parents, and then
+    on the instance (reference: model/utils/utils.py:7-25)."""
+    built = cls.__init__
+
+    def run(module):
+        for child in module.children():
+            run(child)
+        fn = getattr(module, init_method, None)
+        if callable(fn):
+            fn()
+
+    def __init__(self, *args, **kwargs):
+        built(self, *args, **kwargs)
+        if type(self) is cls:
+            run(self)
+
+    cls.__init__ = __init__
+    return cls
+
+
+def load_model_checkpoint(models, state_dict: dict, strict_load_model: bool = True) -> None:
+    """Load ``state_dict["model"]`` into the model chunks of this rank: a list with one native state dict per chunk,
+    or a path to HF safetensors (every chunk takes what it holds through its reshaper).  Parameters that received a
+    value are marked ``has_initialized`` (reference: model/utils/utils.py:28-65)."""
+    from ..utils.logger import logger
+
+    if "model" not in state_dict:
+        raise AssertionError("state_dict must contain 'model' key.")
+    source = state_dict["model"]
+    if isinstance(source, str):
+        from ..utils.weight_loader import HFWeights
+
+        source = state_dict["model"] = HFWeights(source)
+        from_hf = True
+    else:
+        from_hf = False
+    for vid, model in enumerate(models):
+        model = unwrap_model(model)
+        PM.set_vpp_rank(vid)
+        if from_hf:
+            skipped = set(model.load_hf_state_dict(source, strict=strict_load_model))
+            if skipped:
+                logger.warning(f"model chunk {vid}: not loaded (shape differs): {sorted(skipped)}", at=None)
+            continue                                      # load_hf_state_dict marks what it copied
+        msg = model.load_state_dict(source[vid], strict=strict_load_model)
+        missing = set(msg.missing_keys)
+        if missing or msg.unexpected_keys:
+            logger.warning(f"model chunk {vid}: {msg}", at=None)
+        for name, p in model.named_parameters():
+            if name not in missing:
+                p.has_initialized = True

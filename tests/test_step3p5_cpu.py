@@ -1,5 +1,6 @@
 """Step-3.5 decoder on CPU: sliding-window and full-attention layers, routed experts with a shared expert,
 head-wise attention gate; one training step and the HF <-> native weight mapping round trip."""
+import pytest
 import torch
 
 from steptronoss_b200.data.synthetic import SyntheticDataConfig
@@ -113,3 +114,54 @@ def test_selection_bias_stays_fp32_through_casts_and_loads():
     assert model.pp_size == 1 and callable(model.abstract_forward)
     model.init_model_weight(seed=3)
     assert all(getattr(p, "has_initialized", False) for p in model.parameters())
+
+
+def test_load_model_checkpoint_and_init_callback():
+    import torch.nn as nn
+
+    from steptronoss_b200.models.module import init_weight_callback, load_model_checkpoint
+
+    exp = _make()
+    exp.seed = 0
+    tr = exp.trainer_cfg.get_trainer_cls()(exp=exp)
+    tr.before_train()
+    model = getattr(tr.models[0], "module", tr.models[0])
+    saved = {k: v.detach().clone() for k, v in model.state_dict().items()}
+    with torch.no_grad():
+        for p in model.parameters():
+            p.add_(1.0)
+            p.has_initialized = False
+    partial = {k: v for k, v in saved.items() if "tok_embeddings" not in k}
+    load_model_checkpoint(tr.models, {"model": [partial]}, strict_load_model=False)
+    named = dict(model.named_parameters())
+    emb = next(k for k in named if "tok_embeddings" in k)
+    other = next(k for k in named if "tok_embeddings" not in k)
+    assert torch.equal(named[other], saved[other]) and named[other].has_initialized
+    assert not torch.equal(named[emb], saved[emb]) and not named[emb].has_initialized       # was not in the checkpoint
+    with pytest.raises(RuntimeError):
+        load_model_checkpoint(tr.models, {"model": [partial]}, strict_load_model=True)
+    with pytest.raises(AssertionError):
+        load_model_checkpoint(tr.models, {})
+
+    order = []
+
+    class Leaf(nn.Module):
+        def init_model_weight(self):
+            order.append("leaf")
+
+    @init_weight_callback
+    class Net(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a = Leaf()
+
+        def init_model_weight(self):
+            order.append("net")
+
+    class Bigger(Net):                                    # the callback belongs to Net's own instances
+        pass
+
+    Net()
+    assert order == ["leaf", "net"]
+    Bigger()
+    assert order == ["leaf", "net"]
