@@ -8,7 +8,14 @@ import numpy as np
 from .nextable import LazyUpdateNextable
 
 
-class LoopedSequentialSampler(LazyUpdateNextable):
+class BaseSampler(LazyUpdateNextable):
+    """What a sampler is: a resumable stream of indices into ``size`` items (``next(sampler) -> int``); a sampler of
+    one's own subclasses this and gives ``get`` / ``update`` / ``state_dict`` / ``load_state_dict``."""
+
+    size: int
+
+
+class LoopedSequentialSampler(BaseSampler):
     def __init__(self, size: int):
         self.size, self.idx = size, 0
 
@@ -25,7 +32,7 @@ class LoopedSequentialSampler(LazyUpdateNextable):
         self.idx = state["idx"]
 
 
-class LoopedShuffleSampler(LazyUpdateNextable):
+class LoopedShuffleSampler(BaseSampler):
     def __init__(self, size: int, seed: int = 0):
         self.size, self.seed, self.idx = size, seed, 0
         self._epoch, self._perm = -1, None
@@ -51,7 +58,7 @@ class LoopedShuffleSampler(LazyUpdateNextable):
         self._epoch = -1
 
 
-class WeightedRandomSampler(LazyUpdateNextable):
+class WeightedRandomSampler(BaseSampler):
     """Chooses among ``len(weights)`` sources so that the served counts follow the weights: the next source
     is ``argmin((served + 1) / weight)`` (ties to the lower index) — deterministic and resumable."""
 
