@@ -7,6 +7,7 @@ travels pickled.
 from __future__ import annotations
 
 import io
+import pickle
 from typing import Any, Callable
 
 import torch
@@ -61,6 +62,19 @@ def _comm_device(group, device):
         return torch.device("cuda", torch.cuda.current_device()) if dist.get_backend(group) == "nccl" else torch.device("cpu")
     except Exception:
         return torch.device("cpu")
+
+
+def object_to_tensor(obj, device):
+    """Pickle ``obj`` into a uint8 tensor on ``device``; returns ``(bytes, length)`` (the length as a 1-element int64
+    tensor, ready to be exchanged before the payload)."""
+    raw = pickle.dumps(obj)
+    data = torch.frombuffer(bytearray(raw), dtype=torch.uint8).to(device)
+    return data, torch.tensor([len(raw)], dtype=torch.int64, device=device)
+
+
+def tensor_to_object(tensor: torch.Tensor, tensor_size):
+    """Inverse of ``object_to_tensor``; ``tensor`` may be longer than the pickled bytes (padded for a collective)."""
+    return pickle.loads(tensor.cpu().numpy().tobytes()[: int(tensor_size)])
 
 
 def broadcast_tensors(obj: Any, src: int | None = None, group=None, device=None, src_rank: int | None = None):

@@ -17,6 +17,23 @@ import torch.distributed as dist
 _OPS = ("mean", "sum", "max", "min", "last", "first")
 
 
+class ROps:
+    """Names of the reductions a metric chain takes (``Metric()._link(ROps.mean, RDims.dp)`` = ``.mean("dp")``)."""
+
+    sum, mean, max, min, gather, last, first, std = "sum", "mean", "max", "min", "gather", "last", "first", "std"
+
+
+class RDims:
+    """Names of the axes a metric reduces over: ``time`` (the values of one log interval) and the parallel families."""
+
+    time, tp, pp, dp, ep, mp, cp, world = "time", "tp", "pp", "dp", "ep", "mp", "cp", "world"
+
+    @classmethod
+    def _get_group(cls, dim: str):
+        """The process group of an axis (None for ``world``, as ``torch.distributed`` spells the default group)."""
+        return None if dim == cls.world else _group_for(dim)[0]
+
+
 def _group_for(axis: str):
     from ..parallel.state import PM
 

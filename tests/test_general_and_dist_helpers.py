@@ -231,3 +231,18 @@ def test_gae_by_coefficient_matrix_matches_the_recursion():
     assert torch.allclose(got[0], want[0], atol=1e-5) and torch.allclose(got[1], want[1], atol=1e-5)
     same = compute_gae_opt(v, r, 0.9, 0.99)
     assert torch.equal(same[0], want[0])
+
+
+def test_objects_as_byte_tensors_and_metric_axis_names():
+    from steptronoss_b200.utils.dist_utils import object_to_tensor, tensor_to_object
+    from steptronoss_b200.utils.metrics import Metric, RDims, ROps
+
+    data, size = object_to_tensor({"a": [1, 2, torch.ones(2)]}, "cpu")
+    assert data.dtype == torch.uint8 and int(size) == data.numel()
+    padded = torch.cat([data, torch.zeros(7, dtype=torch.uint8)])            # as after a padded all-gather
+    back = tensor_to_object(padded, size)
+    assert back["a"][:2] == [1, 2] and back["a"][2].tolist() == [1.0, 1.0]
+    m = Metric()._link(ROps.sum, RDims.time)
+    m.add(1)
+    m.add(2)
+    assert float(m.reduce()) == 3.0 and RDims._get_group(RDims.world) is None
