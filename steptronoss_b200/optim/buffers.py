@@ -125,3 +125,8 @@ def build_buffers(named_params: list, shard: bool = True, allocator=None) -> dic
             s.param.grad_added_to_main_grad = False
         buckets[key] = b
     return buckets
+
+
+# the reference's names for the same things (model/utils/comm_buffer.py)
+ParamBucketKey = BucketKey
+get_bucket_key_from_param_attrs = bucket_key_of

@@ -534,6 +534,9 @@ class BaseGradientManager:
             s.param.data = buf[s.offset : s.offset + s.numel].view(s.param.shape)
 
 
+GradientManager = BaseGradientManager      # the reference's name for the base (optimizer/base_gradient_manager.py)
+
+
 class AccInFP32GradientManager(BaseGradientManager):
     """All-reduce gradients over DP; every rank keeps the full optimizer state."""
 
