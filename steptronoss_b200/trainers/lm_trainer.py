@@ -229,11 +229,26 @@ class DecoderPretrainTrainer(BaseTrainer):
             logger.info(tl.log_string(normalizer=tc.log_interval), at=0)
 
     # ------------------------------------------------------------------ checkpoints
+    def set_autoresume(self) -> bool:
+        """When ``auto_resume`` is on and this job has written a complete checkpoint before, point the configuration
+        at it: ``load_path`` = the latest checkpoint, every load option on (a run configured to start from someone
+        else's weights without their optimizer must still resume its OWN optimizer, scheduler and data position),
+        no safetensors.  Returns whether it did.  Reference: core/trainers/lm_trainer.py:415-436."""
+        ck = self.exp.checkpoint_cfg
+        latest = self.checkpointer.latest() if ck.auto_resume and self.checkpointer is not None else None
+        if latest is None:
+            return False
+        logger.info(f"AutoResume from: {latest}", at=0)
+        if ck.load_path and ck.load_path != latest:
+            logger.warning(f'AutoResume is overwriting checkpoint_cfg.load_path! Was: "{ck.load_path}"', at=0)
+        ck.load_path = latest
+        ck.load_option.all()
+        ck.load_safetensors = None
+        return True
+
     def load_checkpoint(self):
         ck = self.exp.checkpoint_cfg
-        path = None
-        if ck.auto_resume:
-            path = self.checkpointer.latest()
+        path = ck.load_path if self.set_autoresume() else None
         hf_dir = ck.load_safetensors
         if hf_dir is True:  # the HF view that a native checkpoint carries beside it
             hf_dir = os.path.join(ck.load_path, "hf")

@@ -157,3 +157,23 @@ def test_optimizer_shards_are_recut_when_the_data_parallel_size_changes(tmp_path
     assert resumed.iteration == 6
     for k, v in resumed.models[0].named_parameters():
         assert torch.allclose(v, ref[k], atol=1e-6), k
+
+
+def test_auto_resume_loads_everything_whatever_the_start_options_say(tmp_path):
+    """A job configured to START from foreign weights without their optimizer still RESUMES its own optimizer."""
+    full = _train(_exp(tmp_path / "a", 6, None))
+    ref = {k: v.detach().clone() for k, v in full.models[0].named_parameters()}
+    _train(_exp(tmp_path / "b", 3, 3))
+    e = _exp(tmp_path / "b", 6, None)
+    e.checkpoint_cfg.load_path = "/somewhere/pretrained"              # what a first start would load ...
+    e.checkpoint_cfg.load_option.none(but=["model"])                  # ... weights only
+    resumed = _train(e)
+    ck = e.checkpoint_cfg
+    assert ck.load_path.endswith("it3") and ck.load_option.optimizer and ck.load_option.data and ck.load_safetensors is None
+    assert resumed.iteration == 6
+    for k, v in resumed.models[0].named_parameters():
+        assert torch.equal(v, ref[k]), k
+    fresh = _exp(tmp_path / "c", 1, None)                             # nothing to resume: configuration untouched
+    fresh.checkpoint_cfg.load_option.none(but=["model"])
+    tr = _train(fresh)
+    assert not tr.set_autoresume() and not fresh.checkpoint_cfg.load_option.optimizer
