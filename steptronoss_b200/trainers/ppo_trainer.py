@@ -122,7 +122,7 @@ class PPOTrainer(BaseTrainer):
     def _build_role(self, name: str, model_cfg, gm_cfg, sched_cfg, training: bool) -> PackedModel:
         role_ck = getattr(self.exp.checkpoint_cfg, name if name != "reference_model" else "reference")
         pm = PackedModel(self.ppo_cfg, model_cfg, gm_cfg, sched_cfg, training=training, name=name, seed=self.exp.seed)
-        path = self._resume_dir(name if name != "reference_model" else "reference") or role_ck.load_path
+        path = role_ck.load_path
         if path:
             old = self.exp.checkpoint_cfg.load_option
             self.exp.checkpoint_cfg.load_option = role_ck.load_option
@@ -142,6 +142,27 @@ class PPOTrainer(BaseTrainer):
                 pm.grad_manager.refresh_masters_from_params()
         return pm
 
+    def set_autoresume(self) -> bool:
+        """When ``auto_resume`` is on and this job has written a complete checkpoint before: every role's
+        ``load_path`` becomes its directory in that checkpoint, every load option is switched on and safetensors
+        sources are dropped, so that a job set up to start from foreign weights resumes its own optimizers,
+        schedulers and flow state.  Reference: core/trainers/ppo_trainer.py:752-784."""
+        ck = self.exp.checkpoint_cfg
+        latest = self._resume_dir()
+        if latest is None:
+            return False
+        logger.info(f"AutoResume from: {latest}", at=0)
+        if ck.load_path and ck.load_path != latest:
+            logger.warning(f'AutoResume is overwriting checkpoint_cfg.load_path! Was: "{ck.load_path}"', at=0)
+        ck.load_path, ck.load_safetensors = latest, None
+        ck.load_option.all()
+        for role in ("actor", "critic", "reference"):
+            rc = getattr(ck, role, None)
+            if rc is not None and os.path.isdir(os.path.join(latest, role)):   # a role the checkpoint does not hold
+                rc.load_path, rc.load_safetensors = os.path.join(latest, role), None   # keeps its original source
+                rc.load_option.all()
+        return True
+
     def _resume_dir(self, sub: str | None = None) -> str | None:
         ck = self.exp.checkpoint_cfg
         if not ck.auto_resume or self.checkpointer is None:
@@ -158,6 +179,7 @@ class PPOTrainer(BaseTrainer):
     def build_models_and_flow_controller(self):
         exp = self.exp
         self.checkpointer = exp.checkpoint_cfg.build_checkpointer()
+        self.set_autoresume()
         with self.timers.record("build_actor_model", 1):
             self.actor = self._build_role("actor", exp.actor_model_cfg, exp.actor_grad_manager_cfg,
                                           exp.actor_scheduler_cfg, True)

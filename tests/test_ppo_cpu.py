@@ -250,3 +250,31 @@ def test_think_and_solution_token_split():
     cfg.log_solution_think_tokens([a, b], Tok([60, 61]))                   # the marker is not one token: nothing logged
     assert GlobalMetrics.rollout_avg_think_tokens.values == []
     GlobalMetrics.clear()
+
+
+def test_ppo_auto_resume_takes_every_role_from_the_latest_checkpoint(tmp_path):
+    exp = _exp(tmp_path, True)
+    exp.sanity_check()
+    tr = exp.trainer_cfg.get_trainer_cls()(exp)
+    tr.before_train()
+    tr.train_loop()                                                    # writes it2 (interval 2 of 3 iterations)
+    trained = {n: p.detach().clone() for n, p in tr.actor.models.named_parameters()}
+    again = _exp(tmp_path, True)
+    again.checkpoint_cfg.actor.load_option.none(but=["model"])         # how the job was told to START
+    again.checkpoint_cfg.actor.load_safetensors = "/models/pretrained"
+    again.sanity_check()
+    tr2 = again.trainer_cfg.get_trainer_cls()(again)
+    tr2.before_train()
+    ck = again.checkpoint_cfg
+    assert ck.load_path.endswith("it2") and ck.actor.load_path.endswith(os.path.join("it2", "actor"))
+    assert ck.actor.load_option.optimizer and ck.actor.load_safetensors is None and ck.critic.load_path.endswith("critic")
+    assert all(os.path.isdir(r.load_path) for r in (ck.actor, ck.critic, ck.reference) if r.load_path)
+    assert tr2.actor_iteration > 0
+    first = next(iter(trained))
+    # the parameters are those of iteration 2, not of a fresh initialisation and not those after iteration 3
+    fresh = _exp(tmp_path / "other", True)
+    fresh.sanity_check()
+    tr3 = fresh.trainer_cfg.get_trainer_cls()(fresh)
+    tr3.before_train()
+    p2, p3 = dict(tr2.actor.models.named_parameters())[first], dict(tr3.actor.models.named_parameters())[first]
+    assert not torch.equal(p2, p3)
