@@ -127,15 +127,16 @@ class DecoderPretrainTrainer(BaseTrainer):
                 self._watchdog.stop()
 
     def _train_iterations(self, tc, timers):
+        first = self.iteration
         while self.iteration < self.train_iters:
-            self.call_hooks("before_step")
             with timers.record("iteration", 0):
-                self.train_step()
+                self.train_step()                  # runs the before_step / after_step hooks itself
+            if self.iteration == first and torch.cuda.is_available():
+                torch.cuda.empty_cache()           # buffers that only the first step needed (workspace sizing, init)
             self.iteration += 1
             if self._watchdog is not None:
                 self._watchdog.beat()
                 self._watchdog.raise_if_tripped()
-            self.call_hooks("after_step")
             if self.iteration % tc.log_interval == 0:
                 self.training_log()
             ck = getattr(self.exp, "checkpoint_cfg", None)
@@ -163,6 +164,9 @@ class DecoderPretrainTrainer(BaseTrainer):
         # optimizer state (fp32 masters and moments) waits on the host while activations need the memory
         offload = bool(getattr(tc, "offload_optimizer_state", False)) and hasattr(gm, "offload_state")
         with timers.record("forward-backward", 1):
+            # the step hooks run inside the step, as in the reference (core/trainers/lm_trainer.py:203-204, 257-259),
+            # so that code which drives train_step() itself gets them too
+            self.call_hooks("before_step")
             if offload:
                 CMT.mark("before_cpu_offload_optimizer_state")
                 with timers.record("optimizer-offload", 2):
@@ -190,6 +194,11 @@ class DecoderPretrainTrainer(BaseTrainer):
         self.consumed_samples += tc.global_batch_size
         self.scheduler.step(exp.scheduler_cfg.increment(tc.global_batch_size, tokens)
                             if hasattr(exp.scheduler_cfg, "increment") else 1)
+        if getattr(tc, "empty_unused_memory_level", 0) >= 2 and torch.cuda.is_available():
+            torch.cuda.empty_cache()               # level 2: also after the update
+        with timers.record("after-step-hooks", 1):
+            self.call_hooks("after_step")
+        CMT.mark("after_step_hooks")
         return ok
 
     def training_log(self):

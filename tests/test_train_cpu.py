@@ -253,3 +253,7 @@ def test_hooks_built_by_the_trainer_config_run_at_their_points():
     assert calls[0] == ("after_init", False)                                       # runs before the models exist
     tr.build_hooks(e.trainer_cfg)                                                  # a second call adds nothing
     assert len(tr._hooks["before_step"]) == 1
+    assert [c for c in calls if c[0].endswith("_step")] == [("before_step", 0), ("after_step", 0), ("before_step", 1),
+                                                             ("after_step", 1)]    # both inside the step
+    tr.train_step()                                                                # driven by hand: hooks still run
+    assert [c[0] for c in calls][-2:] == ["before_step", "after_step"]
