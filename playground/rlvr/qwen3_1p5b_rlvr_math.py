@@ -155,10 +155,12 @@ class OnPolicyFlowControllerConfig(FlowControllerConfig):
 
 
 class RLVRTrainerConfig(PPOLikeTrainerConfig):
-    """GAE over the response tokens with the outcome reward on the last one, the clipped surrogate and the value
-    regression are the trainer configuration's defaults."""
+    """GAE over the response tokens with the outcome reward on the last one and the clipped surrogate are the trainer
+    configuration's defaults; the critic regresses on the returns with a plain mean-squared error, as in the reference's
+    experiment of the same name."""
 
     flow_cfg = OnPolicyFlowControllerConfig
+    critic_value_clip = None
 
 
 class Exp(PPOLikeExp):

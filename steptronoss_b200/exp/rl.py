@@ -277,7 +277,8 @@ class PPOLikeTrainerConfig(TrainerConfig):
     ppo_gae_gamma: float = 1.0
     advantage_clip_min: float = -5
     advantage_clip_max: float = 4.5
-    critic_value_clip: float = 0.2
+    critic_value_clip: float | None = 0.2
+    """range of the clipped value loss around the values of the sampling pass; None or 0: plain MSE"""
     ppo_clip: float = 0.2
     reward_clip: float = 20
     sample_kl_loss_coeff: float = 0.0
@@ -452,10 +453,16 @@ class PPOLikeTrainerConfig(TrainerConfig):
         mask = samples.is_gen_mask.reshape(-1).to(values.device).bool()
         values = values[mask]
         target = samples.returns.to(values.device).float()
-        old = samples.values.to(values.device).float() if samples.values is not None else values.detach()
-        clipped = old + (values - old).clamp(-self.critic_value_clip, self.critic_value_clip)
-        l1, l2 = (values - target) ** 2, (clipped - target) ** 2
-        loss = 0.5 * torch.maximum(l1, l2).mean()
+        if not self.critic_value_clip:
+            # no clip range: the plain mean-squared error against the returns, which is what the reference's RLVR
+            # experiment trains its critic with (playground/rlvr/qwen3_1p5b_rlvr_math.py:289-305)
+            l1 = l2 = (values - target) ** 2
+            loss = l1.mean()
+        else:
+            old = samples.values.to(values.device).float() if samples.values is not None else values.detach()
+            clipped = old + (values - old).clamp(-self.critic_value_clip, self.critic_value_clip)
+            l1, l2 = (values - target) ** 2, (clipped - target) ** 2
+            loss = 0.5 * torch.maximum(l1, l2).mean()
         GlobalMetrics.value_clip_frac.add((l2 > l1).float().mean().detach())
         GlobalMetrics.ppo_value_clip_count.add((l2 > l1).float().mean().detach())
         GlobalMetrics.ppo_returns.add(target.mean().detach())

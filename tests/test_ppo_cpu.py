@@ -278,3 +278,24 @@ def test_ppo_auto_resume_takes_every_role_from_the_latest_checkpoint(tmp_path):
     tr3.before_train()
     p2, p3 = dict(tr2.actor.models.named_parameters())[first], dict(tr3.actor.models.named_parameters())[first]
     assert not torch.equal(p2, p3)
+
+
+def test_critic_loss_is_plain_mse_without_a_clip_range():
+    from steptronoss_b200.utils.metrics import GlobalMetrics
+
+    GlobalMetrics.clear()
+    cfg = PPOLikeTrainerConfig()
+    s = PackedPPOSamples()
+    s.is_gen_mask = torch.tensor([[0, 1, 1, 1]]).bool()
+    s.returns, s.values = torch.tensor([1.0, 0.0, 2.0]), torch.tensor([0.9, 0.0, 0.0])
+    out = torch.tensor([[5.0], [1.5], [0.0], [1.0]])                       # the value of the prompt token is not trained
+    cfg.critic_value_clip = None
+    assert float(cfg.critic_loss_func({"_samples": s}, out)) == pytest.approx(float(((torch.tensor([1.5, 0.0, 1.0]) - s.returns) ** 2).mean()))
+    cfg.critic_value_clip = 0.2
+    # clipped: values may move 0.2 from the sampling pass; the worse of the two errors counts, halved
+    clipped = torch.tensor([0.9 + 0.2, 0.0, 0.2])
+    want = 0.5 * torch.maximum((torch.tensor([1.5, 0.0, 1.0]) - s.returns) ** 2, (clipped - s.returns) ** 2).mean()
+    assert float(cfg.critic_loss_func({"_samples": s}, out)) == pytest.approx(float(want))
+    from playground.rlvr.qwen3_1p5b_rlvr_math import RLVRTrainerConfig
+
+    assert RLVRTrainerConfig().critic_value_clip is None
