@@ -44,7 +44,7 @@ class Qwen3MoEConfig(MoEConfig):
         self.moe_num_experts = 128
         self.moe_top_k = 8
         self.moe_hidden_size = 768
-        self.moe_aux_loss_coef = 1e-3
+        self.moe_aux_loss_coef = 0.0         # as the reference's experiment; HF's config for this model says 1e-3
         self.norm_expert_weight = True
         self.share_expert_dim = 0
         self.moe_layer_list = list(range(48))
