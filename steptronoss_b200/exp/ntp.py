@@ -129,5 +129,10 @@ class PretrainExp(BaseExp):
         self.update_from_args()
         self.sanity_check()
         trainer = self.trainer_cfg.get_trainer_cls()(exp=self)
+        self.configure_optimizable()
         trainer.train()
         return trainer
+
+    def configure_optimizable(self) -> None:
+        """Hook between building the trainer and training: an experiment selects operator back-ends here with
+        ``utils.optimizable.set_optimization`` (the reference's experiment files do; its names are understood)."""

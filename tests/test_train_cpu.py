@@ -257,3 +257,25 @@ def test_hooks_built_by_the_trainer_config_run_at_their_points():
                                                              ("after_step", 1)]    # both inside the step
     tr.train_step()                                                                # driven by hand: hooks still run
     assert [c[0] for c in calls][-2:] == ["before_step", "after_step"]
+
+
+def test_experiment_hook_selects_operator_back_ends_before_training(monkeypatch):
+    import sys
+
+    from steptronoss_b200.utils.optimizable import current_optimization, set_optimization
+
+    e = _make()
+    e.data_cfg = FixedDataConfig
+    e.trainer_cfg.train_iters = 1
+    seen = []
+
+    def configure():
+        seen.append(set_optimization(AttentionCore="sdpa", grouped_gemm="nv_grouped_gemm"))
+
+    object.__setattr__(e, "configure_optimizable", configure)
+    monkeypatch.setattr(sys, "argv", ["exp.py"])
+    try:
+        e.train()
+        assert len(seen) == 1 and current_optimization("AttentionCore") == "sdpa"
+    finally:
+        set_optimization(AttentionCore=None)
