@@ -162,8 +162,44 @@ class Float16Module(nn.Module):
             return getattr(self.module, name)
 
 
+class ModelWrapperBase(nn.Module):
+    """A wrapper that stands for the model it holds: ``forward``, ``state_dict`` and ``load_state_dict`` go to
+    ``self.module`` (so checkpoints carry the inner model's keys), ``unwrap_model`` sees through it.  Base for wrappers
+    of one's own (an activation logger, a precision shim); reference: model/module.py:176-191."""
+
+    def __init__(self, module: nn.Module):
+        super().__init__()
+        self.module = module
+
+    def forward(self, *inputs, **kwargs):
+        return self.module(*inputs, **kwargs)
+
+    def state_dict(self, *a, **k):
+        return self.module.state_dict(*a, **k)
+
+    def load_state_dict(self, sd, strict=True):
+        return self.module.load_state_dict(sd, strict=strict)
+
+
+def conversion_helper(val, conversion):
+    """``conversion`` applied to ``val``, or to every leaf of nested tuples / lists (their types are kept)."""
+    if isinstance(val, (tuple, list)):
+        return type(val)(conversion_helper(v, conversion) for v in val)
+    return conversion(val)
+
+
+def fp32_to_float16(val, dtype=torch.bfloat16):
+    """fp32 tensors inside ``val`` cast to ``dtype``; everything else untouched."""
+    return conversion_helper(val, lambda v: v.to(dtype) if torch.is_tensor(v) and v.dtype == torch.float32 else v)
+
+
+def float16_to_fp32(val):
+    """bf16 / fp16 tensors inside ``val`` cast to fp32; everything else untouched."""
+    return conversion_helper(val, lambda v: v.float() if torch.is_tensor(v) and v.dtype in (torch.bfloat16, torch.float16) else v)
+
+
 def unwrap_model(m):
-    while isinstance(m, Float16Module):
+    while isinstance(m, (Float16Module, ModelWrapperBase)):
         m = m.module
     return m
 

@@ -116,3 +116,19 @@ def test_first_dim_split_with_padding_over_two_ranks():
     assert got[0][3:5] == got[1][3:5] == ((3, 2), 0)
     assert got[0][5] == [[0.0, 1.0], [2.0, 3.0], [4.0, 5.0]] and got[1][5] == [[6.0, 7.0], [8.0, 9.0], [10.0, 11.0]]
     assert got[0][6] and got[1][6]
+
+
+def test_model_wrapper_base_and_precision_helpers():
+    from steptronoss_b200.models.module import (ModelWrapperBase, conversion_helper, float16_to_fp32, fp32_to_float16,
+                                                unwrap_model)
+
+    inner = torch.nn.Linear(3, 2)
+    wrapped = ModelWrapperBase(ModelWrapperBase(inner))
+    assert unwrap_model(wrapped) is inner and set(wrapped.state_dict()) == {"weight", "bias"}
+    wrapped.load_state_dict({"weight": torch.ones(2, 3), "bias": torch.zeros(2)})
+    assert torch.equal(wrapped(torch.ones(1, 3)), torch.full((1, 2), 3.0))
+    nest = (torch.ones(2), [torch.ones(2, dtype=torch.int64), "text"], None)
+    low = fp32_to_float16(nest)
+    assert isinstance(low, tuple) and low[0].dtype == torch.bfloat16 and low[1][0].dtype == torch.int64 and low[1][1] == "text"
+    assert float16_to_fp32(low)[0].dtype == torch.float32 and fp32_to_float16(nest, torch.float16)[0].dtype == torch.float16
+    assert conversion_helper([1, (2, 3)], lambda v: v * 2) == [2, (4, 6)]
