@@ -143,6 +143,8 @@ class GenerationController:
         self._lock = threading.Lock()
         self._completed = 0
         self._closing = threading.Event()
+        self._bar = None                         # progress over completed items; configured by ``set_tqdm``
+        self._bar_cfg = {"disabled": True, "total": None, "desc": "Cumulative Completed"}
         self.worker_processes = [ctx.Process(target=_worker_main, args=(self._inbox, self._outbox), daemon=True)
                                  for _ in range(self.num_workers)]
         for proc in self.worker_processes:
@@ -159,6 +161,32 @@ class GenerationController:
     def inflight_count(self) -> int:
         with self._lock:
             return len(self._admitted)
+
+    def set_tqdm(self, disabled: bool, total: int, desc: str) -> None:
+        """Show (or hide) a progress bar that advances with every finished item: ``total`` items expected, ``desc`` as
+        its label.  A bar that is already open is closed; the next finished item opens the new one.  Off until called
+        (reference: generation/async_generation.py:159-201, where the bar is on by default)."""
+        if total < 0:
+            raise ValueError(f"Expected total >= 0, got {total}")
+        with self._lock:
+            self._bar_cfg = {"disabled": bool(disabled), "total": total, "desc": desc}
+            self._close_bar()
+
+    def _close_bar(self) -> None:
+        """Caller holds the lock."""
+        if self._bar is not None:
+            self._bar.close()
+            self._bar = None
+
+    def _tick_bar(self) -> None:
+        """Caller holds the lock."""
+        if self._bar_cfg["disabled"]:
+            return
+        if self._bar is None:
+            from tqdm import tqdm
+
+            self._bar = tqdm(total=self._bar_cfg["total"], desc=self._bar_cfg["desc"], dynamic_ncols=True)
+        self._bar.update(1)
 
     def _admit_waiting(self) -> None:
         """Caller holds the lock."""
@@ -185,7 +213,9 @@ class GenerationController:
                     callback(item, result)
                 except Exception as exc:         # noqa: BLE001 - a user callback must not stop the collector
                     logger.error(f"generation callback raised: {exc}")
-            self._completed += 1
+            with self._lock:
+                self._completed += 1
+                self._tick_bar()
 
     # ------------------------------------------------------------------ public API
     def submit_with_callback(self, genable: GenableItem, for_train: bool = False, callback: Callable | None = None,
@@ -205,6 +235,8 @@ class GenerationController:
 
     def shutdown(self) -> None:
         self._closing.set()
+        with self._lock:
+            self._close_bar()
         for _ in self.worker_processes:
             self._inbox.put(None)
         for proc in self.worker_processes:

@@ -38,6 +38,9 @@ def test_multi_process_controller_caps_items_in_flight():
             with lock:
                 done.append((item.x, res))
 
+        c.set_tqdm(disabled=False, total=6, desc="squares")
+        with pytest.raises(ValueError):
+            c.set_tqdm(False, -1, "x")
         for i in range(6):
             c.submit_with_callback(Square(i, delay=0.15), callback=cb)
             seen_inflight.append(c.inflight_count)
@@ -46,7 +49,13 @@ def test_multi_process_controller_caps_items_in_flight():
             seen_inflight.append(c.inflight_count)
             time.sleep(0.02)
         assert sorted(done) == [(i, i * i) for i in range(6)]
+        deadline = time.time() + 10
+        while c.completed_count < 6 and time.time() < deadline:       # the count follows the callback
+            time.sleep(0.01)
         assert max(seen_inflight) <= 2 and c.completed_count == 6
+        assert c._bar is not None and c._bar.n == 6 and c._bar.total == 6 and c._bar.desc.startswith("squares")
+        c.set_tqdm(disabled=True, total=0, desc="off")
+        assert c._bar is None
         with pytest.raises(ValueError):
             GenerationController(num_workers=1, max_concurrent_genables=0)
     finally:
