@@ -534,13 +534,21 @@ class RemoteFuture(LocalFuture):
         store.set(self._key, pickle.dumps(value))
         store.expire(self._key, self.ttl)
 
+    def handle_value(self, raw: bytes):
+        """What the bytes in the store stand for: the value, or - for a worker's ``{"status": "error", "error": msg}``
+        report - an exception that ``get_result`` raises (reference: utils/comm_utils.py:492-520)."""
+        value = pickle.loads(raw)
+        if isinstance(value, dict) and value.get("status") == "error":
+            return RuntimeError(f"task {self.task_id} failed: {value.get('error', 'unknown worker error')}")
+        return value
+
     def poll(self) -> bool:
         if self.completed:
             return True
         raw = get_exp_redis().get(self._key)
         if raw is None:
             return False
-        self.value = pickle.loads(raw)
+        self.value = self.handle_value(raw)
         get_exp_redis().delete(self._key)
         return True
 
@@ -563,7 +571,7 @@ class RemoteFuture(LocalFuture):
         while not self.completed:
             raw = await store.get(self._key)
             if raw is not None:
-                self.value = pickle.loads(raw)
+                self.value = self.handle_value(raw)
                 await store.delete(self._key)
                 break
             if timeout is not None and time.monotonic() - t0 >= timeout:

@@ -79,6 +79,10 @@ def test_queue_distributor_and_futures(store):
     clones = [pickle.loads(pickle.dumps(f)) for f in futs]
     threading.Thread(target=lambda: [c.set_result(i * 10) for i, c in enumerate(clones)]).start()
     assert sorted(f.get_result(timeout=10) for f in wait_by_finish_order(futs)) == [0, 10, 20]
+    failed = RemoteFuture()
+    pickle.loads(pickle.dumps(failed)).set_result({"status": "error", "error": "out of memory"})     # a worker's report
+    with pytest.raises(RuntimeError, match="out of memory"):
+        failed.get_result(timeout=10)
 
 
 def test_coroutines_reach_the_store_without_blocking_the_loop(store):
