@@ -36,6 +36,22 @@ def _rotate_pairs(x: torch.Tensor) -> torch.Tensor:
     return torch.stack((-x2, x1), dim=-1).flatten(-2)
 
 
+rotate_half = _rotate_pairs          # the reference's name: adjacent pairs (x0, x1) -> (-x1, x0)
+
+
+def apply_rotary_emb(freqs: torch.Tensor, tensor: torch.Tensor, *, start_index: int = 0, scale: float = 1.0) -> torch.Tensor:
+    """Rotate the channels ``[start_index, start_index + freqs.shape[-1])`` of a q / k tensor by the angles ``freqs``
+    (adjacent-pair convention, fp32 arithmetic, result in the tensor's dtype); the channels left and right of the
+    range pass through.  ``freqs`` broadcasts against the tensor (reference: model/common/vit.py:32-53)."""
+    width = freqs.shape[-1]
+    if start_index + width > tensor.shape[-1]:
+        raise ValueError(f"feature dimension {tensor.shape[-1]} is too small for rot_dim {width} at {start_index}")
+    ang = freqs.to(device=tensor.device, dtype=torch.float32)
+    mid = tensor[..., start_index:start_index + width].float()
+    mid = (mid * ang.cos() + _rotate_pairs(mid) * ang.sin()) * scale
+    return torch.cat((tensor[..., :start_index], mid.to(tensor.dtype), tensor[..., start_index + width:]), dim=-1)
+
+
 class EncoderRope2D(nn.Module):
     """Rotary embedding over a 2-D patch grid: half of the head dimension rotates with the column index, half
     with the row index (adjacent-pair convention); the CLS token, if any, is not rotated."""

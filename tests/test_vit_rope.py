@@ -82,3 +82,20 @@ def test_attention_dropout_acts_in_training_only():
     plain.load_state_dict(attn.state_dict())
     plain.train()
     assert torch.allclose(plain(x, (2, 2)), a, atol=1e-5)          # both paths compute the same attention
+
+
+def test_apply_rotary_emb_rotates_a_channel_range():
+    from steptronoss_b200.models.common.vit import apply_rotary_emb, rotate_half
+
+    x = torch.tensor([[1.0, 2.0, 3.0, 4.0, 5.0, 6.0]])
+    assert rotate_half(x[:, :4]).tolist() == [[-2.0, 1.0, -4.0, 3.0]]
+    quarter = torch.full((1, 2), torch.pi / 2)
+    out = apply_rotary_emb(quarter, x, start_index=2)
+    assert torch.allclose(out, torch.tensor([[1.0, 2.0, -4.0, 3.0, 5.0, 6.0]]), atol=1e-6)     # 90 degrees on channels 2..3
+    assert torch.allclose(apply_rotary_emb(quarter, x, start_index=2, scale=2.0)[:, 2:4], torch.tensor([[-8.0, 6.0]]), atol=1e-5)
+    half = apply_rotary_emb(quarter, x.to(torch.bfloat16))
+    assert half.dtype == torch.bfloat16 and half[0, :2].tolist() == [-2.0, 1.0]
+    import pytest
+
+    with pytest.raises(ValueError):
+        apply_rotary_emb(torch.zeros(1, 8), x)
