@@ -29,7 +29,8 @@ import torch
 from ..checkpointing.hf_checkpoint import HFWeights as _LazyWeights
 from ..parallel.state import PM
 
-__all__ = ["HFWeights", "Is", "Cat", "parse_rules", "key_pattern", "fill_target"]
+__all__ = ["HFWeights", "Is", "Cat", "parse_rules", "key_pattern", "fill_target", "translate", "apply_match",
+           "parse_indicator_from_str"]
 
 
 def key_pattern(glob: str) -> re.Pattern:
@@ -59,6 +60,15 @@ def fill_target(match: re.Match, target: str) -> str:
     for i in sorted(range(len(groups)), reverse=True):   # $10 before $1
         target = target.replace(f"${i + 1}", groups[i])
     return target
+
+
+def translate(pat: str) -> str:
+    """The regular expression (as text) that ``key_pattern`` compiles: the reference's name for the glob translation."""
+    return key_pattern(pat).pattern
+
+
+apply_match = fill_target                  # the reference's names for the same two steps of the rule language
+parse_indicator_from_str = None            # bound below, once parse_rules exists
 
 
 class Is:
@@ -107,6 +117,9 @@ def parse_rules(rules) -> dict:
         else:
             raise ValueError(f"unknown operation in rule {line!r}")
     return out
+
+
+parse_indicator_from_str = parse_rules
 
 
 def _rank_slice(t: torch.Tensor, family: str, dim: int) -> torch.Tensor:
