@@ -199,6 +199,28 @@ def start_store_server(port: int = 0) -> tuple[subprocess.Popen, int]:
     return proc, int(line.split()[1])
 
 
+def safely_start_redis(retries: int = 3, wait_per_retry: float = 1.0) -> int:
+    """Start the store server on a free port, check that it answers (a write read back), and return the port; a
+    failed start is retried.  The reference's name and return value for the same step (utils/comm_utils.py:33-100):
+    the server process stays with this module, ``reset_exp_store`` stops it."""
+    global _SERVER_PROC
+    last = None
+    for _ in range(max(1, retries)):
+        try:
+            proc, port = start_store_server()
+            probe = ExpStore("127.0.0.1", port, connect_timeout=10)
+            probe.set("redis_start_mark", str(os.getpid()))
+            if probe.get("redis_start_mark") == str(os.getpid()).encode():
+                probe.delete("redis_start_mark")
+                _SERVER_PROC = proc
+                return port
+            proc.kill()
+        except Exception as e:                  # a port taken between the pick and the bind, a slow start
+            last = e
+        time.sleep(wait_per_retry)
+    raise RuntimeError(f"could not start the experiment store after {retries} attempts: {last}")
+
+
 def block_get_redis(client: ExpStore, key: str, timeout: float = 1200, interval: float = 1.0):
     """Poll ``key`` until it exists (name kept from the reference)."""
     t0 = time.time()

@@ -130,3 +130,20 @@ def test_blocking_pop_and_score_increments_steer_the_least_loaded_choice(store):
     picks = [store.zpopmin_incr("load") for _ in range(5)]
     assert picks == [b"b"] * 5
     assert {store.zpopmin_incr("load") for _ in range(2)} == {b"a", b"b"}   # both at 5 now: they alternate
+
+
+def test_safely_start_returns_the_port_of_a_server_that_answers():
+    from steptronoss_b200.utils import comm_utils
+
+    comm_utils.reset_exp_store()
+    port = comm_utils.safely_start_redis(retries=2, wait_per_retry=0.1)
+    try:
+        c = comm_utils.ExpStore("127.0.0.1", port, connect_timeout=10)
+        assert c.ping() and c.get("redis_start_mark") is None              # the start probe cleaned up after itself
+        c.set("k", "v")
+        assert c.get("k") == b"v"
+    finally:
+        c.shutdown()
+        if comm_utils._SERVER_PROC is not None:
+            comm_utils._SERVER_PROC.wait(timeout=5)
+            comm_utils._SERVER_PROC = None
