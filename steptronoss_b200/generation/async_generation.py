@@ -86,6 +86,12 @@ class SingleGenerationController:
     def __init__(self):
         self._runner = _LoopThread()
 
+    @staticmethod
+    async def work_on_item(item: GenableItem, callback: Callable, for_train: bool) -> None:
+        """One item from start to ``callback(item, result)``; a failure is delivered as a ``RuntimeError`` result.
+        The coroutine a subclass with its own event loop schedules (the reference's name and argument order)."""
+        await _run_item(item, for_train, callback)
+
     def submit_with_callback(self, genable: GenableItem, for_train: bool = False, callback: Callable | None = None,
                              task_meta: dict | None = None) -> None:
         if task_meta:
