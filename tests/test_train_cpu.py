@@ -259,7 +259,7 @@ def test_hooks_built_by_the_trainer_config_run_at_their_points():
     assert [c[0] for c in calls][-2:] == ["before_step", "after_step"]
 
 
-def test_experiment_hook_selects_operator_back_ends_before_training(monkeypatch):
+def test_experiment_hook_selects_operator_back_ends_before_training(monkeypatch, tmp_path):
     import sys
 
     from steptronoss_b200.utils.optimizable import current_optimization, set_optimization
@@ -267,6 +267,7 @@ def test_experiment_hook_selects_operator_back_ends_before_training(monkeypatch)
     e = _make()
     e.data_cfg = FixedDataConfig
     e.trainer_cfg.train_iters = 1
+    e.log_dir = str(tmp_path)                          # Exp.train() opens a log file under log_dir / exp_name
     seen = []
 
     def configure():
