@@ -143,6 +143,11 @@ class TrainBatch:
 
 
 @dataclass
+# the reference's names for the two records of the fully asynchronous strategy
+FullyAsyncPromptTrace = PromptTrace
+FullyAsyncTrainBatch = TrainBatch
+
+
 class FlowSimulationResult:
     strategy: str
     genables: list = field(default_factory=list)
