@@ -142,12 +142,12 @@ class TrainBatch:
         return max(self.step - v for v in self.versions) if self.versions else 0
 
 
-@dataclass
 # the reference's names for the two records of the fully asynchronous strategy
 FullyAsyncPromptTrace = PromptTrace
 FullyAsyncTrainBatch = TrainBatch
 
 
+@dataclass
 class FlowSimulationResult:
     strategy: str
     genables: list = field(default_factory=list)
