@@ -21,6 +21,8 @@ import pickle
 import re
 import threading
 
+from typing import TypedDict
+
 import torch
 
 from ..config import recur_to_allowed_types
@@ -66,6 +68,17 @@ def _to_cpu(obj):
     if isinstance(obj, (list, tuple)):
         return type(obj)(_to_cpu(v) for v in obj)
     return obj
+
+
+class CheckpointDict(TypedDict, total=False):
+    """What ``load_ckpt`` hands back beside what it loaded in place."""
+
+    iteration: int
+    model: list
+    optimizer: dict
+    scheduler: dict
+    data: dict
+    extra_info: dict
 
 
 class Checkpointer:

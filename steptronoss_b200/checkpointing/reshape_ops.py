@@ -12,6 +12,8 @@ gate]`` and ``w1`` rows are ``[gate | up]``.
 """
 from __future__ import annotations
 
+import os
+
 import contextlib
 import fnmatch
 import re
@@ -29,6 +31,16 @@ def _size(group: str) -> int:
 
 def _rank(group: str) -> int:
     return PM.rank_in(group) if PM.has(group) else 0
+
+
+def common_pattern(strs: list) -> str:
+    """What a family of names shares: ``['aan', 'abn', 'acn'] -> 'a{}n'`` (one name comes back unchanged)."""
+    names = sorted(set(strs))
+    if len(names) == 1:
+        return names[0]
+    head = os.path.commonprefix(names)
+    tail = os.path.commonprefix([n[len(head):][::-1] for n in names])[::-1]
+    return f"{head}{{}}{tail}"
 
 
 class ReshapeOp:
