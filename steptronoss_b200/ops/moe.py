@@ -436,3 +436,7 @@ def routed_grouped_ffn_reference(x, expert_ids, weights, w1, w2, limit: float = 
         y = a @ w2[e].float().t()
         out.index_add_(0, tok, y * weights[tok, slot].float().unsqueeze(-1))
     return out.to(x.dtype)
+
+
+# the reference's names for the autograd functions behind the three movers (model/utils/moe_utils.py)
+MoEGateFunction, MoEScatter, MoEWeightedGather = _RouterFn, _ScatterFn, _WeightedGatherFn

@@ -157,6 +157,9 @@ class _CheckpointFn(torch.autograd.Function):
         return (None, None) + in_grads
 
 
+CheckpointFunction = CheckpointFunctionWithSanityCheck = _CheckpointFn      # one class does both (env switch)
+
+
 def checkpoint(function, *args, distribute_saved_activations: bool = False):
     """Run ``function(*args)`` without keeping its intermediate activations; recompute in backward.
     ``distribute_saved_activations``: every TP rank keeps only its 1/TP of the first tensor argument."""
