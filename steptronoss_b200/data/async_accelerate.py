@@ -59,6 +59,15 @@ def _worker(nextable: SlowFastNextable, out_q, wid: int, n_workers: int) -> None
         out_q.put(RuntimeError(f"data worker {wid}: {type(e).__name__}: {e}"))
 
 
+def soft_kill_process(process, timeout: float = 2) -> None:
+    """Ask a worker process to stop (SIGTERM), give it ``timeout`` seconds, then kill it if it is still alive."""
+    process.terminate()
+    process.join(timeout=timeout)
+    if process.is_alive():
+        process.kill()
+        process.join(timeout=timeout)
+
+
 class _RoundRobinPrefetcher:
     """Multi-in / single-out: take from the worker queues in turn, pin, keep a few items ready."""
 

@@ -26,6 +26,9 @@ def _missing(name: str):
     return missing
 
 
+dummy_function_wrapper = _missing         # the reference's name: a stand-in that raises when called
+
+
 def _resolve_owner(path: str, create_dummy: bool):
     """Import the longest importable prefix of ``path`` and walk the remaining attributes (classes, sub-objects)."""
     parts = path.split(".")

@@ -314,3 +314,25 @@ def test_local_futures_and_get_ready():
     threading.Thread(target=lambda: (time.sleep(0.1), c.set_result(3), time.sleep(0.1), a.set_result(None))).start()
     order = [f for f in wait_by_finish_order([a, c])]
     assert order == [c, a] and a.completed and a.result() is None                      # None is a value, not "pending"
+
+
+def _ignores_sigterm():
+    import signal
+    import time
+
+    signal.signal(signal.SIGTERM, signal.SIG_IGN)
+    time.sleep(60)
+
+
+def test_soft_kill_ends_a_worker_that_ignores_the_polite_request():
+    import multiprocessing as mp
+    import time
+
+    from steptronoss_b200.data.async_accelerate import soft_kill_process
+
+    p = mp.get_context("fork").Process(target=_ignores_sigterm)
+    p.start()
+    time.sleep(0.3)
+    t0 = time.time()
+    soft_kill_process(p, timeout=0.5)
+    assert not p.is_alive() and time.time() - t0 < 5
