@@ -166,3 +166,52 @@ class P2P:
     def send_forward_backward_recv_forward_backward(self, out, grad, recv_prev: bool, recv_next: bool):
         r = communicate(send_next=out, send_prev=grad, recv_prev=recv_prev, recv_next=recv_next, **self.kw)
         return r[0], r[1]
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Free-function spellings (reference: core/pipeline_parallel/p2p_communication.py:327-560), for a schedule of one's
+# own written against them: the first argument is the model config (``params_dtype`` / ``pipeline_dtype`` and
+# ``variable_seq_lengths`` are read from it), ``tensor_shape`` the shape of the activation that travels.
+# ---------------------------------------------------------------------------------------------------------------
+def _bound(cfg, tensor_shape) -> P2P:
+    dtype = getattr(cfg, "pipeline_dtype", None) or getattr(cfg, "params_dtype", None) or torch.bfloat16
+    return P2P(tensor_shape, dtype, bool(getattr(cfg, "variable_seq_lengths", False)))
+
+
+def recv_forward(cfg, tensor_shape=None):
+    return _bound(cfg, tensor_shape).recv_forward()
+
+
+def recv_backward(cfg, tensor_shape=None):
+    return _bound(cfg, tensor_shape).recv_backward()
+
+
+def send_forward(cfg, output_tensor, tensor_shape=None) -> None:
+    _bound(cfg, tensor_shape).send_forward(output_tensor)
+
+
+def send_backward(cfg, input_tensor_grad, tensor_shape=None) -> None:
+    _bound(cfg, tensor_shape).send_backward(input_tensor_grad)
+
+
+def send_forward_recv_backward(cfg, output_tensor, tensor_shape=None):
+    return _bound(cfg, tensor_shape).send_forward_recv_backward(output_tensor)
+
+
+def send_backward_recv_forward(cfg, input_tensor_grad, tensor_shape=None):
+    return _bound(cfg, tensor_shape).send_backward_recv_forward(input_tensor_grad)
+
+
+def send_forward_recv_forward(cfg, output_tensor, recv_prev: bool, tensor_shape=None, overlap_p2p_comm: bool = False):
+    """With ``overlap_p2p_comm`` the transfer is left in flight: ``(tensor, requests to wait on)`` comes back."""
+    return _bound(cfg, tensor_shape).send_forward_recv_forward(output_tensor, recv_prev, wait=not overlap_p2p_comm)
+
+
+def send_backward_recv_backward(cfg, input_tensor_grad, recv_next: bool, tensor_shape=None, overlap_p2p_comm: bool = False):
+    return _bound(cfg, tensor_shape).send_backward_recv_backward(input_tensor_grad, recv_next, wait=not overlap_p2p_comm)
+
+
+def send_forward_backward_recv_forward_backward(cfg, output_tensor, input_tensor_grad, recv_prev: bool, recv_next: bool,
+                                                tensor_shape=None):
+    return _bound(cfg, tensor_shape).send_forward_backward_recv_forward_backward(output_tensor, input_tensor_grad,
+                                                                                 recv_prev, recv_next)

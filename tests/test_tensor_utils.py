@@ -132,3 +132,37 @@ def test_model_wrapper_base_and_precision_helpers():
     assert isinstance(low, tuple) and low[0].dtype == torch.bfloat16 and low[1][0].dtype == torch.int64 and low[1][1] == "text"
     assert float16_to_fp32(low)[0].dtype == torch.float32 and fp32_to_float16(nest, torch.float16)[0].dtype == torch.float16
     assert conversion_helper([1, (2, 3)], lambda v: v * 2) == [2, (4, 6)]
+
+
+def _p2p_worker(rank, world):
+    from types import SimpleNamespace
+
+    from steptronoss_b200.parallel.pipeline import p2p
+    from steptronoss_b200.parallel.state import PM
+
+    pc = ParallelConfig()
+    pc.pipeline_model_parallel_size = 2
+    PM.set_mesh(pc)
+    cfg = SimpleNamespace(params_dtype=torch.float32, variable_seq_lengths=False)
+    shape = (3, 2)
+    if rank == 0:
+        assert p2p.recv_forward(cfg, shape) is None                       # the first stage receives nothing
+        p2p.send_forward(cfg, torch.full(shape, 7.0), shape)
+        grad = p2p.recv_backward(cfg, shape)
+        p2p.send_backward(cfg, grad, shape)                               # no previous stage: nothing happens
+        back = p2p.send_forward_recv_backward(cfg, torch.full(shape, 9.0), shape)
+        return grad.tolist(), back.tolist()
+    act = p2p.recv_forward(cfg, shape)
+    p2p.send_forward(cfg, act, shape)                                     # the last stage sends nothing
+    p2p.send_backward(cfg, act * 2, shape)
+    assert p2p.recv_backward(cfg, shape) is None
+    again = p2p.send_backward_recv_forward(cfg, torch.full(shape, -1.0), shape)
+    return act.tolist(), again.tolist()
+
+
+def test_p2p_free_functions_over_two_stages():
+    from tests.dist_helpers import call_on_ranks
+
+    got = call_on_ranks(_p2p_worker, 2)
+    assert got[1][0] == [[7.0, 7.0]] * 3 and got[0][0] == [[14.0, 14.0]] * 3
+    assert got[1][1] == [[9.0, 9.0]] * 3 and got[0][1] == [[-1.0, -1.0]] * 3
